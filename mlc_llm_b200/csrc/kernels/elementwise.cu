@@ -1,0 +1,306 @@
+// Memory-bound per-token kernels: RMSNorm, fused residual-add + RMSNorm, SiLU*mul, rotary embedding
+// fused with the paged KV append, (dequantising) embedding lookup, row gather/scatter.
+//
+// Reference counterparts: compiler_pass/fuse_add_norm.py:14-146 (add + RMSNorm, fp32 accumulate),
+// model/llama/llama_model.py:122-125 (SwiGLU split), nn/kv_cache.py:29-37 (RoPE applied inside the
+// KV-cache append), compiler_pass/fuse_dequantize_take.py:15-91 (dequantising embedding lookup).
+#include "common.cuh"
+
+namespace mlcb {
+
+// ------------------------------------------------------------------ (add +) RMSNorm
+// One CTA per token. If `residual` is non-null:  residual += x  (written back), out = norm(residual).
+// Otherwise out = norm(x). 8 elements (16 bytes) per thread per step.
+template <typename T, bool ADD>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                               const T* __restrict__ w, T* __restrict__ out, int hidden, float eps,
+                               float w_offset) {
+  extern __shared__ float row[];  // hidden floats + 32 scratch
+  float* scratch = row + hidden;
+  const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + base + i);
+    const T* xe = reinterpret_cast<const T*>(&xv);
+    float v[8];
+    if (ADD) {
+      uint4 rv = *reinterpret_cast<const uint4*>(residual + base + i);
+      const T* re = reinterpret_cast<const T*>(&rv);
+      T o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // the sum is rounded to the storage type first, as the unfused add would do
+        o[j] = Cvt<T>::from_f(Cvt<T>::to_f(xe[j]) + Cvt<T>::to_f(re[j]));
+        v[j] = Cvt<T>::to_f(o[j]);
+      }
+      *reinterpret_cast<uint4*>(residual + base + i) = *reinterpret_cast<uint4*>(o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = Cvt<T>::to_f(xe[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      row[i + j] = v[j];
+      ss += v[j] * v[j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / hidden + eps);
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+    const T* we = reinterpret_cast<const T*>(&wv);
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      o[j] = Cvt<T>::from_f(row[i + j] * inv * (Cvt<T>::to_f(we[j]) + w_offset));
+    *reinterpret_cast<uint4*>(out + base + i) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+// in: [T, 2*I] (gate half then up half), out: [T, I]. act: 0 = SiLU, 1 = GELU(tanh).
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
+                               size_t total_vec, int act) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const int vec_per_row = inter / 8;
+  for (size_t v = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_vec;
+       v += stride) {
+    const size_t t = v / vec_per_row;
+    const int c = static_cast<int>(v % vec_per_row) * 8;
+    uint4 g = *reinterpret_cast<const uint4*>(in + t * 2 * inter + c);
+    uint4 u = *reinterpret_cast<const uint4*>(in + t * 2 * inter + inter + c);
+    const T* ge = reinterpret_cast<const T*>(&g);
+    const T* ue = reinterpret_cast<const T*>(&u);
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a = Cvt<T>::to_f(ge[j]);
+      float r;
+      if (act == 0) {
+        r = a / (1.f + __expf(-a));
+      } else {
+        float k = 0.7978845608028654f * (a + 0.044715f * a * a * a);
+        r = 0.5f * a * (1.f + tanhf(k));
+      }
+      // round the activation to the storage type before the product, as the unfused ops do
+      r = Cvt<T>::to_f(Cvt<T>::from_f(r));
+      o[j] = Cvt<T>::from_f(r * Cvt<T>::to_f(ue[j]));
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + c) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE + paged KV append
+// qkv: [T, (hq + 2*hkv) * d], heads ordered q.., k.., v.. . Rotates q and k in place (non-interleaved
+// halves over the first `rot_dim` elements) at position pos[t], then copies k and v of token t into
+// its page slot. kv_pages layout: [num_pages, 2, hkv, page, d]. slot[t] = page_id * page + offset,
+// a negative slot skips the append (used when only q needs rotating).
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, T* __restrict__ kv_pages,
+                                   const int* __restrict__ pos, const int* __restrict__ slot,
+                                   const float* __restrict__ inv_freq, int hq, int hkv, int d,
+                                   int rot_dim, int page, float attn_factor, int* status,
+                                   long long num_slots) {
+  const int t = blockIdx.x;
+  const int heads = hq + 2 * hkv;
+  const int half = rot_dim / 2;
+  const float p = static_cast<float>(pos[t]);
+  T* row = qkv + static_cast<size_t>(t) * heads * d;
+  // rotate q and k heads
+  const int pairs = (hq + hkv) * half;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    float s, c;
+    sincosf(p * inv_freq[j], &s, &c);
+    s *= attn_factor;
+    c *= attn_factor;
+    T* hp = row + h * d;
+    const float a = Cvt<T>::to_f(hp[j]), b = Cvt<T>::to_f(hp[j + half]);
+    hp[j] = Cvt<T>::from_f(a * c - b * s);
+    hp[j + half] = Cvt<T>::from_f(b * c + a * s);
+  }
+  const long long sl = slot[t];
+  if (sl < 0) return;
+  if (sl >= num_slots) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, ERR_BAD_INDEX);
+    return;
+  }
+  __syncthreads();
+  const long long pg = sl / page;
+  const int off = static_cast<int>(sl % page);
+  const int vec_per_head = d / 8;
+  for (int i = threadIdx.x; i < 2 * hkv * vec_per_head; i += blockDim.x) {
+    const int kvsel = i / (hkv * vec_per_head);
+    const int rem = i % (hkv * vec_per_head);
+    const int h = rem / vec_per_head, v = rem % vec_per_head;
+    const uint4 val =
+        *reinterpret_cast<const uint4*>(row + (hq + kvsel * hkv + h) * d + v * 8);
+    T* dst = kv_pages + (((pg * 2 + kvsel) * hkv + h) * page + off) * static_cast<size_t>(d) + v * 8;
+    *reinterpret_cast<uint4*>(dst) = val;
+  }
+}
+
+// ------------------------------------------------------------------ embedding lookup
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             T* __restrict__ out, int hidden, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * hidden + i);
+    if (scale != 1.f) {
+      T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = Cvt<T>::from_f(Cvt<T>::to_f(e[j]) * scale);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + i) = v;
+  }
+}
+
+// q4f16_1 table in the *artifact* nibble order (element j of a word at bits 4*(j%8)).
+__global__ void embed_q4_kernel(const int* __restrict__ ids, const uint32_t* __restrict__ qw,
+                                const __half* __restrict__ qs, __half* __restrict__ out, int hidden,
+                                int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const int words = hidden / 8;
+  for (int wi = threadIdx.x; wi < words; wi += blockDim.x) {
+    const uint32_t x = qw[static_cast<size_t>(id) * words + wi];
+    const float s = __half2float(qs[static_cast<size_t>(id) * (hidden / 32) + wi / 4]);
+    __half o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      o[j] = __float2half_rn((static_cast<float>((x >> (4 * j)) & 0xf) - 7.f) * s);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden + wi * 8) =
+        *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ------------------------------------------------------------------ row gather / scatter
+// dst[i, :] = src[idx[i], :] (gather) or dst[idx[i], :] = src[i, :] (scatter); rows of `row_bytes`.
+__global__ void row_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                const int* __restrict__ idx, int row_bytes, int scatter) {
+  const int i = blockIdx.x;
+  const size_t s = scatter ? static_cast<size_t>(i) : static_cast<size_t>(idx[i]);
+  const size_t d = scatter ? static_cast<size_t>(idx[i]) : static_cast<size_t>(i);
+  const uint4* sp = reinterpret_cast<const uint4*>(src + s * row_bytes);
+  uint4* dp = reinterpret_cast<uint4*>(dst + d * row_bytes);
+  for (int v = threadIdx.x; v < row_bytes / 16; v += blockDim.x) dp[v] = sp[v];
+}
+
+// Copies whole KV pages (all layers are handled by the caller looping or by a large row): used for
+// copy-on-write of a partially filled last page when a sequence is forked.
+__global__ void page_copy_kernel(uint8_t* __restrict__ pages, const int* __restrict__ src_dst,
+                                 size_t page_bytes, size_t layer_stride, int pairs) {
+  const int pair = blockIdx.x % pairs;
+  const int layer = blockIdx.x / pairs;
+  const uint4* sp = reinterpret_cast<const uint4*>(pages + layer * layer_stride +
+                                                   static_cast<size_t>(src_dst[2 * pair]) * page_bytes);
+  uint4* dp = reinterpret_cast<uint4*>(pages + layer * layer_stride +
+                                       static_cast<size_t>(src_dst[2 * pair + 1]) * page_bytes);
+  for (size_t v = threadIdx.x; v < page_bytes / 16; v += blockDim.x) dp[v] = sp[v];
+}
+
+}  // namespace mlcb
+
+using namespace mlcb;
+
+// dtype: 0 fp16, 1 bf16
+MLCB_API int mlcb_rmsnorm(const void* x, void* residual, const void* w, void* out, int tokens,
+                          int hidden, float eps, float w_offset, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return -1;
+  int threads = hidden / 8;
+  threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : (threads + 31) / 32 * 32);
+  size_t smem = (hidden + 32) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+#define LAUNCH(T)                                                                                  \
+  if (residual)                                                                                    \
+    rmsnorm_kernel<T, true><<<tokens, threads, smem, stream>>>(                                    \
+        (const T*)x, (T*)residual, (const T*)w, (T*)out, hidden, eps, w_offset);                   \
+  else                                                                                             \
+    rmsnorm_kernel<T, false><<<tokens, threads, smem, stream>>>((const T*)x, nullptr,              \
+                                                                (const T*)w, (T*)out, hidden, eps, \
+                                                                w_offset);
+  if (dtype == 0) {
+    LAUNCH(__half)
+  } else {
+    LAUNCH(__nv_bfloat16)
+  }
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_act_mul(const void* in, void* out, int tokens, int inter, int act, int dtype,
+                          cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (inter % 8) return -1;
+  size_t total = static_cast<size_t>(tokens) * (inter / 8);
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  if (dtype == 0)
+    act_mul_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)in, (__half*)out, inter, total, act);
+  else
+    act_mul_kernel<__nv_bfloat16>
+        <<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total, act);
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_rope_append(void* qkv, void* kv_pages, const int* pos, const int* slot,
+                              const float* inv_freq, int tokens, int hq, int hkv, int d, int rot_dim,
+                              int page, float attn_factor, long long num_slots, int dtype,
+                              int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8 || rot_dim % 2 || rot_dim > d) return -1;
+  if (dtype == 0)
+    rope_append_kernel<__half><<<tokens, 256, 0, stream>>>((__half*)qkv, (__half*)kv_pages, pos, slot,
+                                                          inv_freq, hq, hkv, d, rot_dim, page,
+                                                          attn_factor, status, num_slots);
+  else
+    rope_append_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        (__nv_bfloat16*)qkv, (__nv_bfloat16*)kv_pages, pos, slot, inv_freq, hq, hkv, d, rot_dim, page,
+        attn_factor, status, num_slots);
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_embed(const int* ids, const void* table, void* out, int tokens, int hidden,
+                        int vocab, float scale, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return -1;
+  if (dtype == 0)
+    embed_kernel<__half><<<tokens, 256, 0, stream>>>(ids, (const __half*)table, (__half*)out, hidden,
+                                                    vocab, scale);
+  else
+    embed_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table,
+                                                           (__nv_bfloat16*)out, hidden, vocab, scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_embed_q4(const int* ids, const void* qw, const void* qs, void* out, int tokens,
+                           int hidden, int vocab, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 32) return -1;
+  embed_q4_kernel<<<tokens, 256, 0, stream>>>(ids, (const uint32_t*)qw, (const __half*)qs,
+                                              (__half*)out, hidden, vocab);
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_row_copy(const void* src, void* dst, const int* idx, int rows, int row_bytes,
+                           int scatter, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (row_bytes % 16) return -1;
+  row_copy_kernel<<<rows, 256, 0, stream>>>((const uint8_t*)src, (uint8_t*)dst, idx, row_bytes,
+                                            scatter);
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_page_copy(void* pages, const int* src_dst, int pairs, int layers,
+                            long long page_bytes, long long layer_stride, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  page_copy_kernel<<<pairs * layers, 256, 0, stream>>>((uint8_t*)pages, src_dst, (size_t)page_bytes,
+                                                      (size_t)layer_stride, pairs);
+  return static_cast<int>(cudaGetLastError());
+}

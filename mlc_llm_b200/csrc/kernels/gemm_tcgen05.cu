@@ -1,0 +1,432 @@
+// Linear layers on the 5th-gen tensor cores:  Y[M, N] = X[M, K] . W[N, K]^T (+ bias)
+//
+// One persistent, warp-specialised kernel serves both serving phases and both weight formats:
+//   * W dense 16-bit (fp16 / bf16), loaded by TMA straight into the 128-byte-swizzled UMMA layout;
+//   * W int4 group-quantised (q4f16_1: 8 nibbles per uint32, one fp16 scale per 32 weights along K).
+//     The packed tile is fetched by TMA, four "dequant" warps expand it to fp16 in the swizzled
+//     layout ((nibble - 7) * scale, one rounding), and the tensor core consumes it from there.
+//
+// The weight tile is the UMMA "A" operand (M = 128 output features), the token tile is the "B"
+// operand (N = TN tokens, 16..256), so each expanded weight tile is reused by up to 256 tokens and
+// small decode batches do not pad to 128 rows. Accumulators live in TMEM (two buffers of 256
+// columns, so the epilogue of one tile overlaps the main loop of the next).
+//
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
+// warps 2-5 = dequant, warps 6-9 = epilogue (TMEM -> registers -> global).
+//
+// Reference counterparts: dense matmul dispatched to cuBLAS (compiler_pass/blas_dispatch.py:15-52)
+// and the fused dequantize+matmul produced by compiler_pass/fuse_dequantize_matmul_ewise.py:9-85
+// from quantization/group_quantization.py:390-440.
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace mlcb {
+
+constexpr int BM = 128;       // weight rows (output features) per tile == UMMA M
+constexpr int BK = 64;        // K elements per pipeline stage (128 bytes of 16-bit data)
+constexpr int MAX_TN = 256;   // tokens per tile == UMMA N
+constexpr int STAGES = 4;
+constexpr int X_STAGE_BYTES = MAX_TN * BK * 2;   // 32 KiB
+constexpr int W_STAGE_BYTES = BM * BK * 2;       // 16 KiB
+constexpr int RAW_STAGE_BYTES = BM * (BK / 2);   // 4 KiB of packed nibbles
+constexpr int GEMM_THREADS = 320;
+constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES + RAW_STAGE_BYTES) + 1024 + 256;
+
+struct GemmParams {
+  const void* scale;    // [N, K/32] fp16 (q4 only)
+  const void* bias;     // [N] in the activation dtype, may be null
+  void* y;
+  int* status;
+  int M, N, K;
+  int ldy;              // elements
+  int tn;               // tokens per tile (multiple of 16)
+  int num_m_blocks, num_n_blocks;
+  int out_dtype;        // 0 fp16, 1 bf16, 2 fp32
+  int ab_fmt;           // 0 fp16, 1 bf16
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
+  reinterpret_cast<OutT*>(y)[idx] = Cvt<OutT>::from_f(v);
+}
+
+template <bool Q4>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+            const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sx = smem;                                   // STAGES x 32 KiB
+  uint8_t* sw = sx + STAGES * X_STAGE_BYTES;            // STAGES x 16 KiB
+  uint8_t* sraw = sw + STAGES * W_STAGE_BYTES;          // STAGES x 4 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sraw + STAGES * RAW_STAGE_BYTES);
+  uint64_t* full = bars;                 // [STAGES] TMA landed
+  uint64_t* empty = bars + STAGES;       // [STAGES] MMA done reading
+  uint64_t* deq_full = bars + 2 * STAGES;  // [STAGES] dequantised tile written
+  uint64_t* acc_full = bars + 3 * STAGES;  // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&deq_full[s], 4);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      tma_prefetch_desc(&tmap_w);
+      uint32_t it = 0;
+      const uint32_t tx_bytes =
+          static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? RAW_STAGE_BYTES : W_STAGE_BYTES);
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int nb = t % p.num_n_blocks, mb = t / p.num_n_blocks;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (it >= STAGES) {
+            ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
+            if (!ok) break;
+          }
+          mbar_expect_tx(&full[s], tx_bytes);
+          tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], kb * BK, mb * p.tn);
+          if (Q4)
+            tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &full[s], kb * (BK / 8), nb * BM);
+          else
+            tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], kb * BK, nb * BM);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(p.ab_fmt, BM, p.tn, 0, 0);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+        const int a = tile_i & 1;
+        const uint32_t aph = (tile_i >> 1) & 1;
+        if (tile_i >= 2) {
+          ok = mbar_wait(&acc_empty[a], aph ^ 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * MAX_TN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
+          if (!ok) break;
+          if (Q4) {
+            ok = mbar_wait(&deq_full[s], ph, abort_flag, p.status, ERR_WAIT_DEQUANT);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = umma_smem_desc(smem_u32(sw + s * W_STAGE_BYTES), 16, 1024);
+          const uint64_t bdesc = umma_smem_desc(smem_u32(sx + s * X_STAGE_BYTES), 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // advancing 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
+            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[a]);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ dequant warps (q4 only)
+    if (Q4) {
+      const int row = (warp - 2) * 32 + lane;  // 0..127 inside the tile
+      const __half* scale = reinterpret_cast<const __half*>(p.scale);
+      const int groups_per_row = p.K / 32;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int nb = t % p.num_n_blocks;
+        const int n = nb * BM + row;
+        const bool n_ok = n < p.N;
+        const __half* srow = scale + static_cast<size_t>(n_ok ? n : 0) * groups_per_row;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          // the two group scales of this 64-wide K block (issued before the wait to hide latency)
+          __half2 sc = __floats2half2_rn(0.f, 0.f);
+          if (n_ok && (kb * 2 + 1) < groups_per_row)
+            sc = *reinterpret_cast<const __half2*>(srow + kb * 2);
+          else if (n_ok && kb * 2 < groups_per_row)
+            sc = __halves2half2(srow[kb * 2], __float2half(0.f));
+          ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
+          ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
+          if (!ok) break;
+          const uint4* raw = reinterpret_cast<const uint4*>(sraw + s * RAW_STAGE_BYTES + row * 32);
+          uint4 r0 = raw[0], r1 = raw[1];
+          uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+          uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
+            const __half2 s2 = __half2half2(sv);
+            // (1024 + q) * s - 1031 * s == (q - 7) * s, one rounding in the fma
+            const __half2 off = __hmul2(s2, __float2half2_rn(-1031.f));
+            const uint32_t x = words[w];
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // device layout: nibble pair (2j, 2j+1) sits at bits [4j, 4j+4) and [16+4j, 20+4j)
+              uint32_t v = ((x >> (4 * j)) & 0x000f000fu) | 0x64006400u;
+              __half2 hv = __hfma2(*reinterpret_cast<__half2*>(&v), s2, off);
+              h[j] = *reinterpret_cast<uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
+                make_uint4(h[0], h[1], h[2], h[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&deq_full[s]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+      const int nb = t % p.num_n_blocks, mb = t / p.num_n_blocks;
+      const int a = tile_i & 1;
+      const uint32_t aph = (tile_i >> 1) & 1;
+      ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, ERR_WAIT_MMA);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+      if (!ok) break;
+      tc_fence_after();
+      const int n = nb * BM + q * 32 + lane;  // output feature of this thread
+      const bool n_ok = n < p.N;
+      float bias = 0.f;
+      if (p.bias && n_ok) {
+        bias = p.ab_fmt == 0 ? __half2float(reinterpret_cast<const __half*>(p.bias)[n])
+                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
+      }
+      const int m0 = mb * p.tn;
+      for (int c = 0; c < p.tn; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * MAX_TN + c, r);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c + j;
+            if (c + j < p.tn && m < p.M) {
+              const float v = __uint_as_float(r[j]) + bias;
+              const size_t idx = static_cast<size_t>(m) * p.ldy + n;
+              if (p.out_dtype == 0) store_out<__half>(p.y, idx, v);
+              else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx, v);
+              else store_out<float>(p.y, idx, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+struct MapKey {
+  uint64_t v[14];
+  bool operator==(const MapKey& o) const {
+    for (int i = 0; i < 14; ++i)
+      if (v[i] != o.v[i]) return false;
+    return true;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 14; ++i) h = (h ^ k.v[i]) * 1099511628211ull;
+    return static_cast<size_t>(h);
+  }
+};
+
+const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, const uint64_t* dims,
+                                  const uint64_t* strides_bytes, const uint32_t* box,
+                                  int swizzle_128, int is_fp8) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> cache;
+  MapKey key{};
+  key.v[0] = reinterpret_cast<uint64_t>(base);
+  key.v[1] = static_cast<uint64_t>(elem_bytes) | (static_cast<uint64_t>(rank) << 8) |
+             (static_cast<uint64_t>(swizzle_128) << 16) | (static_cast<uint64_t>(is_fp8) << 24);
+  for (int i = 0; i < rank; ++i) {
+    key.v[2 + i] = dims[i];
+    key.v[6 + i] = i + 1 < rank ? strides_bytes[i] : 0;
+    key.v[10 + i] = box[i];
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return nullptr;
+  CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                           : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[5];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  CUtensorMap* m = new CUtensorMap;
+  CUresult r = fn(m, dt, rank, const_cast<void*>(base), gdims, gstrides, gbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    delete m;
+    return nullptr;
+  }
+  if (cache.size() > 65536) cache.clear();  // bounded; entries are tiny and re-creatable
+  cache.emplace(key, m);
+  return m;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+static int pick_tn(int M) {
+  if (M <= 16) return 16;
+  int blocks = (M + MAX_TN - 1) / MAX_TN;
+  int tn = (M + blocks - 1) / blocks;
+  tn = (tn + 15) / 16 * 16;
+  return tn > MAX_TN ? MAX_TN : tn;
+}
+
+}  // namespace mlcb
+
+using namespace mlcb;
+
+// Returns 0 on success, a negative value for a rejected shape, a positive CUDA error otherwise.
+// x: [M, K] row-major (ldx elements) fp16/bf16.  w: dense [N, K] (same dtype) or, with
+// scale != nullptr, the device-layout packed int4 [N, K/8] uint32 with scale [N, K/32] fp16.
+MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const void* bias, void* y,
+                       int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
+                       int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const bool q4 = scale != nullptr;
+  if (K % 8 != 0 || ldx % 8 != 0) return -1;
+  if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    attr_set = true;
+  }
+  GemmParams p;
+  p.scale = scale;
+  p.bias = bias;
+  p.y = y;
+  p.status = status;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  p.tn = pick_tn(M);
+  p.num_m_blocks = (M + p.tn - 1) / p.tn;
+  p.num_n_blocks = (N + BM - 1) / BM;
+  p.out_dtype = out_dtype;
+  p.ab_fmt = ab_fmt;
+
+  uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+  uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
+  uint32_t xb[2] = {BK, static_cast<uint32_t>(p.tn)};
+  const CUtensorMap* mx = get_tensor_map(x, 2, 2, xd, xs, xb, 1);
+  const CUtensorMap* mw;
+  if (q4) {
+    uint64_t wd[2] = {static_cast<uint64_t>(K / 8), static_cast<uint64_t>(N)};
+    uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
+    uint32_t wb[2] = {BK / 8, BM};
+    mw = get_tensor_map(w, 4, 2, wd, ws, wb, 0);
+  } else {
+    uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
+    uint32_t wb[2] = {BK, BM};
+    mw = get_tensor_map(w, 2, 2, wd, ws, wb, 1);
+  }
+  if (!mx || !mw) return -4;
+  int tiles = p.num_m_blocks * p.num_n_blocks;
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (q4)
+    gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  else
+    gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,354 @@
+"""Operator front-end: every function takes torch tensors and runs the hand-written sm_100a kernel
+when the tensors live on a GPU, or the fp32 PyTorch restatement (``ops.reference``) on CPU.
+
+There is no silent fallback on a GPU: a shape a kernel does not take raises ``KernelError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Optional
+
+import torch
+
+from .. import quantization as Q
+from . import reference as ref
+from ._lib import DTYPE_CODE, KernelError, check, check_status, lib, ptr, status_word, stream_ptr
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_ll = ctypes.c_longlong
+
+
+# --------------------------------------------------------------------------- linear
+@dataclasses.dataclass
+class LinearWeight:
+    """A linear layer's parameters in their run-time layout.
+
+    kind ``dense``: ``w [N, K]``.  kind ``q4``: ``w`` is packed int4 ``[N, K/8]`` int32 (artifact
+    nibble order on CPU, device order on GPU -- see ``quantization.to_device_layout_q4``) and
+    ``scale [N, K/32]``.  kind ``fp8_block``: ``w [N, K]`` e4m3, ``scale [N/128, K/128]`` fp32.
+    kind ``fp8_tensor``: fp8 ``w`` with a scalar ``scale``.
+    """
+
+    kind: str
+    w: torch.Tensor
+    scale: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+    quant: Optional[Q.Quantization] = None
+    out_features: int = 0
+    in_features: int = 0
+    device_layout: bool = False
+    # dense fp16/bf16 copy used by kernels that do not take the packed form (built lazily)
+    _dense: Optional[torch.Tensor] = None
+
+    def to(self, device) -> "LinearWeight":
+        dev = torch.device(device)
+        w, dl = self.w, self.device_layout
+        if self.kind == "q4" and self.quant is not None and self.quant.bits == 4:
+            if dev.type == "cuda" and not dl:
+                w, dl = Q.to_device_layout_q4(w), True
+            elif dev.type == "cpu" and dl:
+                w, dl = Q.from_device_layout_q4(w.cpu()), False
+        return LinearWeight(self.kind, w.to(dev), None if self.scale is None else self.scale.to(dev),
+                            None if self.bias is None else self.bias.to(dev), self.quant,
+                            self.out_features, self.in_features, dl)
+
+    def dense(self, dtype: torch.dtype) -> torch.Tensor:
+        """Materialise the full-precision weight (used by oracles and by cold paths)."""
+        if self.kind == "dense":
+            return self.w.to(dtype)
+        if self._dense is None or self._dense.dtype != dtype:
+            if self.kind == "q4":
+                qw = Q.from_device_layout_q4(self.w) if self.device_layout else self.w
+                self._dense = Q.group_dequantize(qw, self.scale, self.quant, k=self.in_features,
+                                                 out_dtype=dtype)
+            elif self.kind == "fp8_block":
+                self._dense = Q.fp8_block_dequantize(self.w, self.scale, out_dtype=dtype)
+            elif self.kind == "fp8_tensor":
+                self._dense = (self.w.float() * self.scale.float()).to(dtype)
+            else:
+                raise ValueError(self.kind)
+        return self._dense
+
+
+def dense_weight(w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> LinearWeight:
+    return LinearWeight("dense", w, None, bias, None, w.shape[0], w.shape[1])
+
+
+def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``y = x @ W^T (+ bias)`` for ``x [..., K]``."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    od = out_dtype or x.dtype
+    if not x.is_cuda:
+        w = lw.dense(torch.float32)
+        y = ref.linear_dense(x2, w, lw.bias, od)
+        return y.reshape(*lead, -1)
+    m, k = x2.shape
+    n = lw.out_features or lw.w.shape[0]
+    if x2.dtype not in (torch.float16, torch.bfloat16):
+        raise KernelError(f"linear: unsupported activation dtype {x2.dtype}")
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    y = torch.empty(m, n, dtype=od, device=x.device)
+    if m == 0:
+        return y.reshape(*lead, n)
+    ab = DTYPE_CODE[x2.dtype]
+    if lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and x2.dtype == torch.float16 \
+            and k % 64 == 0:
+        assert lw.device_layout
+        rc = lib().mlcb_gemm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m),
+                             c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
+                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
+    elif lw.kind == "fp8_block" and x2.dtype == torch.bfloat16 and k % 128 == 0:
+        from .fp8 import linear_fp8_block  # pylint: disable=import-outside-toplevel
+
+        return linear_fp8_block(x2, lw, od).reshape(*lead, n)
+    else:
+        w = lw.dense(x2.dtype)
+        rc = lib().mlcb_gemm(ptr(x2), ptr(w), ptr(None), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
+                             c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
+                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
+    check(rc, f"mlcb_gemm(M={m},N={n},K={k},{lw.kind})")
+    return y.reshape(*lead, n)
+
+
+# --------------------------------------------------------------------------- norms / activations
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, w_offset: float = 0.0) -> torch.Tensor:
+    if not x.is_cuda:
+        return ref.rmsnorm(x, w, eps, w_offset)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    out = torch.empty_like(x2)
+    rc = lib().mlcb_rmsnorm(ptr(x2), ptr(None), ptr(w), ptr(out), c_int(x2.shape[0]),
+                            c_int(x2.shape[1]), c_float(eps), c_float(w_offset),
+                            c_int(DTYPE_CODE[x.dtype]), stream_ptr())
+    check(rc, "mlcb_rmsnorm")
+    return out.reshape(x.shape)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float,
+                w_offset: float = 0.0) -> torch.Tensor:
+    """``residual += x`` in place; returns ``rmsnorm(residual)``. Both ``[T, H]`` contiguous."""
+    if not x.is_cuda:
+        return ref.add_rmsnorm(x, residual, w, eps, w_offset)
+    assert x.is_contiguous() and residual.is_contiguous()
+    out = torch.empty_like(x)
+    rc = lib().mlcb_rmsnorm(ptr(x), ptr(residual), ptr(w), ptr(out), c_int(x.shape[0]),
+                            c_int(x.shape[1]), c_float(eps), c_float(w_offset),
+                            c_int(DTYPE_CODE[x.dtype]), stream_ptr())
+    check(rc, "mlcb_rmsnorm(add)")
+    return out
+
+
+def act_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    if not x.is_cuda:
+        return ref.act_mul(x, act)
+    assert x.is_contiguous()
+    inter = x.shape[-1] // 2
+    out = torch.empty(*x.shape[:-1], inter, dtype=x.dtype, device=x.device)
+    tokens = x.numel() // x.shape[-1]
+    rc = lib().mlcb_act_mul(ptr(x), ptr(out), c_int(tokens), c_int(inter),
+                            c_int(0 if act == "silu" else 1), c_int(DTYPE_CODE[x.dtype]), stream_ptr())
+    check(rc, "mlcb_act_mul")
+    return out
+
+
+def embed(ids: torch.Tensor, table, hidden: int, dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:
+    """Embedding lookup. ``table`` is a dense tensor ``[V, H]`` or a q4 ``LinearWeight`` in the
+    artifact nibble order (the embedding table is never re-laid-out)."""
+    if isinstance(table, LinearWeight) and table.kind == "q4":
+        if not ids.is_cuda:
+            rows = Q.group_dequantize(table.w[ids.long()], table.scale[ids.long()], table.quant,
+                                      k=hidden, out_dtype=dtype)
+            return rows * scale if scale != 1.0 else rows
+        out = torch.empty(ids.shape[0], hidden, dtype=torch.float16, device=ids.device)
+        rc = lib().mlcb_embed_q4(ptr(ids), ptr(table.w), ptr(table.scale), ptr(out),
+                                 c_int(ids.shape[0]), c_int(hidden), c_int(table.w.shape[0]),
+                                 stream_ptr())
+        check(rc, "mlcb_embed_q4")
+        if scale != 1.0:
+            out = out * scale
+        return out.to(dtype)
+    tbl = table.w if isinstance(table, LinearWeight) else table
+    if not ids.is_cuda:
+        rows = tbl[ids.long()].to(dtype)
+        return rows * scale if scale != 1.0 else rows
+    out = torch.empty(ids.shape[0], hidden, dtype=tbl.dtype, device=ids.device)
+    rc = lib().mlcb_embed(ptr(ids), ptr(tbl), ptr(out), c_int(ids.shape[0]), c_int(hidden),
+                          c_int(tbl.shape[0]), c_float(scale), c_int(DTYPE_CODE[tbl.dtype]),
+                          stream_ptr())
+    check(rc, "mlcb_embed")
+    return out
+
+
+# --------------------------------------------------------------------------- RoPE + KV append
+def rope_append(qkv: torch.Tensor, kv_pages: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor,
+                inv_freq: Optional[torch.Tensor], hq: int, hkv: int, d: int, rot_dim: int, page: int,
+                attn_factor: float = 1.0) -> None:
+    if not qkv.is_cuda:
+        ref.rope_append(qkv, kv_pages, pos, slot, inv_freq, hq, hkv, d, rot_dim, page, attn_factor)
+        return
+    assert qkv.is_contiguous() and kv_pages.is_contiguous()
+    if inv_freq is None:
+        rot_dim = 0
+        inv_freq = torch.zeros(1, dtype=torch.float32, device=qkv.device)
+    num_slots = kv_pages.shape[0] * page
+    rc = lib().mlcb_rope_append(ptr(qkv), ptr(kv_pages), ptr(pos), ptr(slot), ptr(inv_freq),
+                                c_int(qkv.shape[0]), c_int(hq), c_int(hkv), c_int(d), c_int(rot_dim),
+                                c_int(page), c_float(attn_factor), c_ll(num_slots),
+                                c_int(DTYPE_CODE[qkv.dtype]), ptr(status_word(qkv.device)),
+                                stream_ptr())
+    check(rc, "mlcb_rope_append")
+
+
+# --------------------------------------------------------------------------- attention
+def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor,
+                    q_kvlen: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor,
+                    hq: int, hkv: int, d: int, page: int, sm_scale: float,
+                    q_kvstart: Optional[torch.Tensor] = None, sink: int = 0,
+                    tree_mask: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                    return_lse: bool = False, plan=None):
+    """``q``: ``[T, hq*d]`` view (row stride may exceed ``hq*d``). Returns ``[T, hq*d]``."""
+    t = q.shape[0]
+    if not q.is_cuda:
+        res = ref.paged_attention(q.reshape(t, hq, d), kv_pages, q_seq, q_kvlen, page_indptr,
+                                  page_indices, hq, hkv, d, page, sm_scale, q_kvstart, sink,
+                                  tree_mask, softcap, return_lse)
+        if return_lse:
+            return res[0].reshape(t, hq * d), res[1]
+        return res.reshape(t, hq * d)
+    out = torch.empty(t, hq * d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(t, hq, dtype=torch.float32, device=q.device) if return_lse else None
+    if plan is not None and plan.use_tensor_core and tree_mask is None and softcap == 0.0 \
+            and q_kvstart is None and d == 128 and page == 16:
+        from .attention import attention_tcgen05  # pylint: disable=import-outside-toplevel
+
+        attention_tcgen05(q, kv_pages, out, lse, plan, hq, hkv, sm_scale)
+    else:
+        rc = lib().mlcb_attn_simt(ptr(q), ptr(kv_pages), ptr(out), ptr(lse), ptr(q_seq), ptr(q_kvlen),
+                                  ptr(q_kvstart), ptr(tree_mask), ptr(page_indptr), ptr(page_indices),
+                                  c_int(t), c_int(q.stride(0)), c_int(hq), c_int(hkv), c_int(d),
+                                  c_int(page), c_int(sink), c_float(sm_scale), c_float(softcap),
+                                  c_int(DTYPE_CODE[q.dtype]), stream_ptr())
+        check(rc, "mlcb_attn_simt")
+    return (out, lse) if return_lse else out
+
+
+# --------------------------------------------------------------------------- logits / sampling
+def softmax_temperature(logits: torch.Tensor, temperature: torch.Tensor, active_vocab: int = 0):
+    if not logits.is_cuda:
+        return ref.softmax_temperature(logits, temperature, active_vocab)
+    probs = torch.empty_like(logits)
+    rc = lib().mlcb_softmax_temperature(ptr(logits), ptr(probs), ptr(temperature),
+                                        c_int(logits.shape[0]), c_int(logits.shape[1]),
+                                        c_int(active_vocab), stream_ptr())
+    check(rc, "mlcb_softmax_temperature")
+    return probs
+
+
+def argmax(x: torch.Tensor) -> torch.Tensor:
+    if not x.is_cuda:
+        return torch.argmax(x, dim=-1).to(torch.int32)
+    out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    rc = lib().mlcb_argmax(ptr(x), ptr(out), ptr(None), c_int(x.shape[0]), c_int(x.shape[1]),
+                           stream_ptr())
+    check(rc, "mlcb_argmax")
+    return out
+
+
+def apply_logit_bias(logits, pos2seq, token, bias) -> None:
+    if not logits.is_cuda:
+        return ref.apply_logit_bias(logits, pos2seq, token, bias)
+    rc = lib().mlcb_logit_bias(ptr(logits), ptr(pos2seq), ptr(token), ptr(bias),
+                               c_int(token.shape[0]), c_int(logits.shape[1]), stream_ptr())
+    check(rc, "mlcb_logit_bias")
+
+
+def apply_penalty(logits, pos2seq, token, cnt, penalties) -> None:
+    if not logits.is_cuda:
+        return ref.apply_penalty(logits, pos2seq, token, cnt, penalties)
+    rc = lib().mlcb_penalty(ptr(logits), ptr(pos2seq), ptr(token), ptr(cnt), ptr(penalties),
+                            c_int(token.shape[0]), c_int(logits.shape[1]), stream_ptr())
+    check(rc, "mlcb_penalty")
+
+
+def apply_bitmask(logits, rows, bitmask) -> None:
+    if not logits.is_cuda:
+        return ref.apply_bitmask(logits, rows, bitmask)
+    rc = lib().mlcb_bitmask(ptr(logits), ptr(rows), ptr(bitmask), c_int(rows.shape[0]),
+                            c_int(logits.shape[1]), stream_ptr())
+    check(rc, "mlcb_bitmask")
+
+
+def sample(probs, rows, uniform, top_p, top_k=None):
+    """Returns (token ids int32 [n], renormalised prob of each sampled token fp32 [n])."""
+    if not probs.is_cuda:
+        return ref.sample(probs, rows, uniform, top_p, top_k)
+    n = uniform.shape[0]
+    tok = torch.empty(n, dtype=torch.int32, device=probs.device)
+    pr = torch.empty(n, dtype=torch.float32, device=probs.device)
+    rc = lib().mlcb_sample(ptr(probs), ptr(rows), ptr(uniform), ptr(top_p), ptr(top_k), ptr(tok),
+                           ptr(pr), c_int(n), c_int(probs.shape[1]), stream_ptr())
+    check(rc, "mlcb_sample")
+    return tok, pr
+
+
+def renorm_top_p(probs, rows, top_p) -> None:
+    if not probs.is_cuda:
+        return ref.renorm_top_p(probs, rows, top_p)
+    rc = lib().mlcb_renorm_top_p(ptr(probs), ptr(rows), ptr(top_p), c_int(top_p.shape[0]),
+                                 c_int(probs.shape[1]), stream_ptr())
+    check(rc, "mlcb_renorm_top_p")
+
+
+def take_probs(probs, rows, token, k: int):
+    if not probs.is_cuda:
+        return ref.take_probs(probs, rows, token, k)
+    n = token.shape[0]
+    outp = torch.empty(n, dtype=torch.float32, device=probs.device)
+    tp = torch.empty(n, max(k, 1), dtype=torch.float32, device=probs.device)
+    ti = torch.empty(n, max(k, 1), dtype=torch.int32, device=probs.device)
+    rc = lib().mlcb_take_probs(ptr(probs), ptr(rows), ptr(token), ptr(outp), ptr(tp), ptr(ti),
+                               c_int(n), c_int(k), c_int(probs.shape[1]), stream_ptr())
+    check(rc, "mlcb_take_probs")
+    return outp, tp[:, :k], ti[:, :k]
+
+
+def verify_tree(draft_probs, draft_tokens, model_probs, first_child, next_sibling, uniform,
+                parent_ptr) -> None:
+    if not model_probs.is_cuda:
+        return ref.verify_tree(draft_probs, draft_tokens, model_probs, first_child, next_sibling,
+                               uniform, parent_ptr)
+    rc = lib().mlcb_verify_tree(ptr(draft_probs), ptr(draft_tokens), ptr(model_probs),
+                                ptr(first_child), ptr(next_sibling), ptr(uniform), ptr(parent_ptr),
+                                c_int(parent_ptr.shape[0]), c_int(model_probs.shape[1]),
+                                c_int(draft_tokens.shape[0] + 1), stream_ptr())
+    check(rc, "mlcb_verify_tree")
+
+
+def row_gather(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    if not src.is_cuda:
+        return src[idx.long()].clone()
+    out = torch.empty(idx.shape[0], *src.shape[1:], dtype=src.dtype, device=src.device)
+    row_bytes = src[0].numel() * src.element_size()
+    rc = lib().mlcb_row_copy(ptr(src), ptr(out), ptr(idx), c_int(idx.shape[0]), c_int(row_bytes),
+                             c_int(0), stream_ptr())
+    check(rc, "mlcb_row_copy")
+    return out
+
+
+def row_scatter(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> None:
+    if not dst.is_cuda:
+        dst[idx.long()] = src
+        return
+    row_bytes = dst[0].numel() * dst.element_size()
+    rc = lib().mlcb_row_copy(ptr(src), ptr(dst), ptr(idx), c_int(idx.shape[0]), c_int(row_bytes),
+                             c_int(1), stream_ptr())
+    check(rc, "mlcb_row_copy")
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

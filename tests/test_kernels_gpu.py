@@ -1,0 +1,241 @@
+"""CUDA kernels against the fp32 PyTorch oracle (``ops.reference``)."""
+import math
+
+import pytest
+import torch
+
+from mlc_llm_b200 import ops, quantization as Q
+from mlc_llm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, rtol, atol):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g}, worst tol {tol.min().item():.4g}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (16, 256, 256), (100, 384, 512), (256, 512, 4096),
+                                   (300, 1376, 256), (1000, 640, 704), (513, 128, 128)])
+def test_gemm_dense(dtype, m, n, k):
+    torch.manual_seed(0)
+    x = (torch.randn(m, k) * 0.5).to(dtype).to(DEV)
+    w = (torch.randn(n, k) * 0.05).to(dtype).to(DEV)
+    y = ops.linear(x, ops.dense_weight(w))
+    ops.check_status(x.device)
+    yr = ref.linear_dense(x.cpu(), w.cpu())
+    _close(y, yr, 2e-2, 2e-2)
+
+
+def test_gemm_dense_bias_fp32_out():
+    torch.manual_seed(1)
+    x = (torch.randn(40, 256) * 0.5).half().to(DEV)
+    w = (torch.randn(384, 256) * 0.05).half().to(DEV)
+    b = torch.randn(384).half().to(DEV)
+    y = ops.linear(x, ops.dense_weight(w, b), out_dtype=torch.float32)
+    ops.check_status(x.device)
+    assert y.dtype == torch.float32
+    _close(y, ref.linear_dense(x.cpu(), w.cpu(), b.cpu(), torch.float32), 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (7, 256, 128), (64, 512, 4096), (256, 384, 1024),
+                                   (600, 1376, 256)])
+def test_gemm_q4f16(m, n, k):
+    torch.manual_seed(2)
+    quant = Q.get("q4f16_1")
+    w = (torch.randn(n, k) * 0.02).half()
+    qw, qs = Q.group_quantize(w, quant)
+    lw = ops.LinearWeight("q4", qw, qs, None, quant, n, k).to(DEV)
+    x = (torch.randn(m, k) * 0.5).half().to(DEV)
+    y = ops.linear(x, lw)
+    ops.check_status(x.device)
+    wd = Q.group_dequantize(qw, qs, quant)
+    yr = ref.linear_dense(x.cpu(), wd)
+    _close(y, yr, 2e-2, 2e-2)
+
+
+def test_q4_device_layout_roundtrip():
+    qw = torch.randint(-2**31, 2**31 - 1, (64, 32), dtype=torch.int64).to(torch.int32)
+    assert torch.equal(Q.from_device_layout_q4(Q.to_device_layout_q4(qw)), qw)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [256, 4096, 8192])
+def test_rmsnorm_and_add(dtype, hidden):
+    torch.manual_seed(3)
+    x = torch.randn(37, hidden).to(dtype).to(DEV)
+    r = torch.randn(37, hidden).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(hidden)).to(dtype).to(DEV)
+    _close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x.cpu(), w.cpu(), 1e-5), 1e-2, 1e-2)
+    r_ref = r.cpu().clone()
+    out_ref = ref.add_rmsnorm(x.cpu(), r_ref, w.cpu(), 1e-5)
+    out = ops.add_rmsnorm(x, r, w, 1e-5)
+    _close(out, out_ref, 1e-2, 1e-2)
+    assert torch.equal(r.cpu(), r_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_act_mul(dtype):
+    x = torch.randn(33, 2 * 1376).to(dtype).to(DEV)
+    _close(ops.act_mul(x), ref.act_mul(x.cpu()), 1e-2, 1e-2)
+    _close(ops.act_mul(x, "gelu"), ref.act_mul(x.cpu(), "gelu"), 1e-2, 1e-2)
+
+
+def _mk_paged(nseq, lens, hkv, d, page, dtype):
+    npages = sum((l + page - 1) // page for l in lens) + 3
+    perm = torch.randperm(npages)
+    indptr, indices, c = [0], [], 0
+    for l in lens:
+        n = (l + page - 1) // page
+        indices += perm[c:c + n].tolist()
+        c += n
+        indptr.append(len(indices))
+    kv = (torch.randn(npages, 2, hkv, page, d) * 0.5).to(dtype)
+    return kv, torch.tensor(indptr, dtype=torch.int32), torch.tensor(indices, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rope_append(dtype):
+    torch.manual_seed(4)
+    hq, hkv, d, page = 8, 2, 128, 16
+    t = 19
+    qkv = torch.randn(t, (hq + 2 * hkv) * d).to(dtype)
+    kv = torch.zeros(6, 2, hkv, page, d, dtype=dtype)
+    pos = torch.randint(0, 5000, (t,), dtype=torch.int32)
+    slot = torch.randperm(6 * page)[:t].to(torch.int32)
+    slot[3] = -1
+    inv = ref.rope_inv_freq(d, 500000.0)
+    q_ref, kv_ref = qkv.clone(), kv.clone()
+    ref.rope_append(q_ref, kv_ref, pos, slot, inv, hq, hkv, d, d, page)
+    qg, kvg = qkv.to(DEV), kv.to(DEV)
+    ops.rope_append(qg, kvg, pos.to(DEV), slot.to(DEV), inv.to(DEV), hq, hkv, d, d, page)
+    _close(qg[:, : (hq + hkv) * d], q_ref[:, : (hq + hkv) * d], 2e-2, 2e-2)
+    _close(kvg, kv_ref, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_simt(d):
+    torch.manual_seed(5)
+    hq, hkv, page = 8, 2, 16
+    lens = [5, 33, 16, 70]
+    kv, indptr, indices = _mk_paged(len(lens), lens, hkv, d, page, torch.float16)
+    q_seq, q_kvlen = [], []
+    for b, l in enumerate(lens):
+        nq = min(l, 3)
+        for i in range(nq):
+            q_seq.append(b)
+            q_kvlen.append(l - nq + i + 1)
+    t = len(q_seq)
+    q = (torch.randn(t, hq * d) * 0.5).half()
+    q_seq = torch.tensor(q_seq, dtype=torch.int32)
+    q_kvlen = torch.tensor(q_kvlen, dtype=torch.int32)
+    o_ref = ops.paged_attention(q, kv, q_seq, q_kvlen, indptr, indices, hq, hkv, d, page, d ** -0.5)
+    o = ops.paged_attention(q.to(DEV), kv.to(DEV), q_seq.to(DEV), q_kvlen.to(DEV), indptr.to(DEV),
+                            indices.to(DEV), hq, hkv, d, page, d ** -0.5)
+    _close(o, o_ref, 2e-2, 2e-2)
+
+
+def test_attention_simt_tree_and_window():
+    torch.manual_seed(6)
+    hq, hkv, d, page = 4, 2, 64, 16
+    lens = [40]
+    kv, indptr, indices = _mk_paged(1, lens, hkv, d, page, torch.float16)
+    # 4 tree tokens appended at positions 36..39; prefix 36; masks: chain 0-1, 0-2, 2-3
+    q_seq = torch.zeros(4, dtype=torch.int32)
+    q_kvlen = torch.full((4,), 36, dtype=torch.int32)
+    masks = torch.tensor([0b0001, 0b0011, 0b0101, 0b1101], dtype=torch.int64)
+    start = torch.full((4,), 20, dtype=torch.int32)
+    q = (torch.randn(4, hq * d) * 0.5).half()
+    o_ref = ops.paged_attention(q, kv, q_seq, q_kvlen, indptr, indices, hq, hkv, d, page, 0.125,
+                                q_kvstart=start, sink=4, tree_mask=masks)
+    o = ops.paged_attention(q.to(DEV), kv.to(DEV), q_seq.to(DEV), q_kvlen.to(DEV), indptr.to(DEV),
+                            indices.to(DEV), hq, hkv, d, page, 0.125, q_kvstart=start.to(DEV), sink=4,
+                            tree_mask=masks.to(DEV))
+    _close(o, o_ref, 2e-2, 2e-2)
+
+
+def test_softmax_argmax_sample():
+    torch.manual_seed(7)
+    n, v = 6, 32000
+    logits = torch.randn(n, v) * 3
+    temp = torch.tensor([1.0, 0.7, 0.0, 1.3, 0.0, 1.0])
+    p_ref = ref.softmax_temperature(logits, temp)
+    p = ops.softmax_temperature(logits.to(DEV), temp.to(DEV))
+    _close(p, p_ref, 1e-3, 1e-7)
+    assert torch.equal(ops.argmax(logits.to(DEV)).cpu().long(), logits.argmax(-1))
+    u = torch.tensor([0.1, 0.5, 0.9, 0.3, 0.7, 0.999])
+    for top_p in (1.0, 0.9, 0.3):
+        tp = torch.full((n,), top_p)
+        tok_ref, pr_ref = ref.sample(p_ref, None, u, tp)
+        tok, pr = ops.sample(p, None, u.to(DEV), tp.to(DEV))
+        # kept sets agree up to fp summation order; tokens must agree except at CDF boundaries
+        agree = (tok.cpu() == tok_ref).float().mean().item()
+        assert agree >= 0.8, (top_p, tok.cpu(), tok_ref)
+        for r in range(n):
+            if tok.cpu()[r] == tok_ref[r]:
+                assert abs(pr.cpu()[r] - pr_ref[r]) < 1e-3 * max(1.0, pr_ref[r])
+
+
+def test_sample_distribution_top_p():
+    torch.manual_seed(8)
+    v = 1000
+    probs = torch.softmax(torch.randn(1, v) * 2, -1)
+    n = 4000
+    u = torch.rand(n)
+    rows = torch.zeros(n, dtype=torch.int32)
+    tp = torch.full((n,), 0.8)
+    tok, _ = ops.sample(probs.to(DEV), rows.to(DEV), u.to(DEV), tp.to(DEV))
+    cutoff, mass = ref.top_p_cutoff(probs[0], 0.8)
+    kept = probs[0] >= cutoff
+    assert bool(kept[tok.cpu().long()].all())
+    emp = torch.bincount(tok.cpu().long(), minlength=v).float() / n
+    expect = torch.where(kept, probs[0] / mass, torch.zeros(v))
+    assert (emp - expect).abs().max() < 0.03
+
+
+def test_logit_edits_and_take_probs_and_verify():
+    torch.manual_seed(9)
+    n, v = 3, 515
+    logits = torch.randn(n, v)
+    lg = logits.to(DEV)
+    pos2seq = torch.tensor([0, 0, 2], dtype=torch.int32)
+    token = torch.tensor([5, 9, 100], dtype=torch.int32)
+    bias = torch.tensor([1.5, -2.0, 3.0])
+    cnt = torch.tensor([2, 1, 4], dtype=torch.int32)
+    pen = torch.tensor([[0.5, 0.2, 1.2], [0, 0, 1], [0.1, 0.3, 0.8]])
+    lr = logits.clone()
+    ref.apply_logit_bias(lr, pos2seq, token, bias)
+    ref.apply_penalty(lr, pos2seq, token, cnt, pen)
+    ops.apply_logit_bias(lg, pos2seq.to(DEV), token.to(DEV), bias.to(DEV))
+    ops.apply_penalty(lg, pos2seq.to(DEV), token.to(DEV), cnt.to(DEV), pen.to(DEV))
+    rows = torch.tensor([1], dtype=torch.int32)
+    bm = torch.randint(-2**31, 2**31 - 1, (1, (v + 31) // 32), dtype=torch.int64).to(torch.int32)
+    ref.apply_bitmask(lr, rows, bm)
+    ops.apply_bitmask(lg, rows.to(DEV), bm.to(DEV))
+    _close(lg, lr, 1e-5, 1e-5)
+    probs = torch.softmax(torch.randn(n, v), -1)
+    tok = torch.tensor([3, 4, 5], dtype=torch.int32)
+    o, tp, ti = ops.take_probs(probs.to(DEV), None, tok.to(DEV), 5)
+    orf, tpr, tir = ref.take_probs(probs, None, tok, 5)
+    _close(o, orf, 1e-6, 1e-8)
+    _close(tp, tpr, 1e-6, 1e-8)
+    assert torch.equal(ti.cpu(), tir)
+    # verify: 2 sequences, chain of 2 drafts each. nodes: 0,1 roots; 2,3 children of 0; 4 child of 1
+    nodes = 6
+    dp = torch.softmax(torch.randn(nodes, v), -1)
+    mp = torch.softmax(torch.randn(nodes, v), -1)
+    dt = torch.randint(0, v, (nodes,), dtype=torch.int32)
+    fc = torch.tensor([2, 4, -1, -1, 5, -1], dtype=torch.int32)
+    ns = torch.tensor([-1, -1, 3, -1, -1, -1], dtype=torch.int32)
+    u = torch.rand(nodes)
+    pp = torch.tensor([0, 1], dtype=torch.int32)
+    mp_ref, pp_ref = mp.clone(), pp.clone()
+    ref.verify_tree(dp, dt, mp_ref, fc, ns, u, pp_ref)
+    mpg, ppg = mp.to(DEV), pp.to(DEV)
+    ops.verify_tree(dp.to(DEV), dt.to(DEV), mpg, fc.to(DEV), ns.to(DEV), u.to(DEV), ppg)
+    assert torch.equal(ppg.cpu(), pp_ref)
+    _close(mpg, mp_ref, 1e-4, 1e-7)
