@@ -60,6 +60,16 @@ def _run(cmd: List[str], log: Path) -> None:
         raise RuntimeError(f"build step failed ({' '.join(cmd)}):\n{proc.stdout[-8000:]}")
 
 
+def _dynamic_stdcxx() -> List[str]:
+    """Link against the system's shared libstdc++ explicitly. Some toolchains default to the static
+    archive, which would export a second copy of the C++ runtime's unique symbols into the process
+    and break other extension modules (PyTorch among them)."""
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6"):
+        if os.path.exists(cand):
+            return [cand]
+    return []
+
+
 def kernels_lib_path() -> Path:
     return LIB_DIR / "libmlcb200_kernels.so"
 
@@ -94,7 +104,8 @@ def build_kernels(verbose: bool = False) -> Path:
                 print((OBJ_DIR / (s.stem + ".log")).read_text())
     if jobs or not out.exists():
         _run(
-            [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart"],
+            [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart",
+             *[a for f in _dynamic_stdcxx() for a in ("-Xlinker", f)]],
             OBJ_DIR / "link_kernels.log",
         )
     return out
@@ -146,7 +157,8 @@ def build_core(verbose: bool = False) -> Path:
             for f in futs:
                 f.result()
     if jobs or not out.exists():
-        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, objs)], OBJ_DIR / "link_core.log")
+        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, objs), *_dynamic_stdcxx()],
+             OBJ_DIR / "link_core.log")
     if verbose:
         print(f"built {out}")
     return out

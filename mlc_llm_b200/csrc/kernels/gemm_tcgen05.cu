@@ -33,7 +33,7 @@ constexpr int X_STAGE_BYTES = MAX_TN * BK * 2;   // 32 KiB
 constexpr int W_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int RAW_STAGE_BYTES = BM * (BK / 2);   // 4 KiB of packed nibbles
 constexpr int GEMM_THREADS = 320;
-constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES + RAW_STAGE_BYTES) + 1024 + 256;
+constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES + RAW_STAGE_BYTES) + 1024 + 512;
 
 struct GemmParams {
   const void* scale;    // [N, K/32] fp16 (q4 only)
@@ -46,6 +46,10 @@ struct GemmParams {
   int num_m_blocks, num_n_blocks;
   int out_dtype;        // 0 fp16, 1 bf16, 2 fp32
   int ab_fmt;           // 0 fp16, 1 bf16
+  int splits;           // split-K factor (1 = none)
+  int kb_per_split;     // K blocks handled by one work item
+  float* workspace;     // [tiles, splits, tn, BM] fp32 partial sums (split-K only)
+  int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
 };
 
 template <typename OutT>
@@ -69,13 +73,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   uint64_t* deq_full = bars + 2 * STAGES;  // [STAGES] dequantised tile written
   uint64_t* acc_full = bars + 3 * STAGES;  // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* ep_bar = acc_empty + 2;        // [2] epilogue-group sync for the split-K reduction
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ep_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;  // work items
+  const int total_kb = (p.K + BK - 1) / BK;
+  __shared__ int last_flag;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -86,6 +92,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
+      mbar_init(&ep_bar[a], 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -109,8 +116,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? RAW_STAGE_BYTES : W_STAGE_BYTES);
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int nb = t % p.num_n_blocks, mb = t / p.num_n_blocks;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int tile = t / p.splits, sp = t % p.splits;
+        const int nb = tile % p.num_n_blocks, mb = tile / p.num_n_blocks;
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (it >= STAGES) {
@@ -141,7 +151,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * MAX_TN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (t % p.splits) * p.kb_per_split;
+        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
@@ -156,7 +168,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             // advancing 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
-            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) ? 1u : 0u);
+            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
           }
           umma_commit(&empty[s]);
         }
@@ -172,11 +184,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int nb = t % p.num_n_blocks;
+        const int nb = (t / p.splits) % p.num_n_blocks;
+        const int kb0 = (t % p.splits) * p.kb_per_split;
+        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
         const int n = nb * BM + row;
         const bool n_ok = n < p.N;
         const __half* srow = scale + static_cast<size_t>(n_ok ? n : 0) * groups_per_row;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           // the two group scales of this 64-wide K block (issued before the wait to hide latency)
@@ -196,15 +210,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           for (int w = 0; w < 8; ++w) {
             const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
             const __half2 s2 = __half2half2(sv);
-            // (1024 + q) * s - 1031 * s == (q - 7) * s, one rounding in the fma
-            const __half2 off = __hmul2(s2, __float2half2_rn(-1031.f));
+            // 0x6400 | q is the fp16 value 1024 + q; subtracting 1031 is exact, so the product
+            // (q - 7) * s is rounded once
+            const __half2 off = __float2half2_rn(1031.f);
             const uint32_t x = words[w];
             uint32_t h[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               // device layout: nibble pair (2j, 2j+1) sits at bits [4j, 4j+4) and [16+4j, 20+4j)
               uint32_t v = ((x >> (4 * j)) & 0x000f000fu) | 0x64006400u;
-              __half2 hv = __hfma2(*reinterpret_cast<__half2*>(&v), s2, off);
+              __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v), off), s2);
               h[j] = *reinterpret_cast<uint32_t*>(&hv);
             }
             *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
@@ -222,14 +237,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     uint32_t tile_i = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
-      const int nb = t % p.num_n_blocks, mb = t / p.num_n_blocks;
+      const int tile = t / p.splits, sp = t % p.splits;
+      const int nb = tile % p.num_n_blocks, mb = tile / p.num_n_blocks;
       const int a = tile_i & 1;
       const uint32_t aph = (tile_i >> 1) & 1;
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, ERR_WAIT_MMA);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
       tc_fence_after();
-      const int n = nb * BM + q * 32 + lane;  // output feature of this thread
+      const int row = q * 32 + lane;     // row inside the tile
+      const int n = nb * BM + row;       // output feature of this thread
       const bool n_ok = n < p.N;
       float bias = 0.f;
       if (p.bias && n_ok) {
@@ -237,6 +254,68 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
       }
       const int m0 = mb * p.tn;
+      float* ws_tile = p.workspace + static_cast<size_t>(tile) * p.splits * p.tn * BM;
+      if (p.splits > 1) {
+        // park this split's partial sums: [split][token][feature] so a warp writes 128 bytes
+        float* ws = ws_tile + static_cast<size_t>(sp) * p.tn * BM;
+        for (int c = 0; c < p.tn; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * MAX_TN + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j < p.tn) ws[(c + j) * BM + row] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[a]);
+        // the last split to arrive for this tile performs the reduction
+        __threadfence();
+        __syncwarp();
+        // bounded group syncs over mbarriers (one arrival per epilogue warp)
+        if (lane == 0) mbar_arrive(&ep_bar[0]);
+        ok = mbar_wait(&ep_bar[0], tile_i & 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (warp == 6 && lane == 0) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          last_flag = (prev == p.splits - 1);
+          if (last_flag) p.counters[tile] = 0;
+          __threadfence_block();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ep_bar[1]);
+        ok = mbar_wait(&ep_bar[1], tile_i & 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (last_flag) {
+          __threadfence();
+          const int jmax = min(p.tn, p.M - m0);
+          for (int j0 = 0; j0 < jmax; j0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = bias;
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+              const float* src = ws_tile + (static_cast<size_t>(s2) * p.tn + j0) * BM + row;
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                if (j0 + u < jmax) v[u] += __ldcg(src + u * BM);
+            }
+            if (n_ok) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                if (j0 + u < jmax) {
+                  const size_t idx = static_cast<size_t>(m0 + j0 + u) * p.ldy + n;
+                  if (p.out_dtype == 0) store_out<__half>(p.y, idx, v[u]);
+                  else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx, v[u]);
+                  else store_out<float>(p.y, idx, v[u]);
+                }
+              }
+            }
+          }
+        }
+        continue;
+      }
       for (int c = 0; c < p.tn; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * MAX_TN + c, r);
@@ -378,7 +457,8 @@ using namespace mlcb;
 // scale != nullptr, the device-layout packed int4 [N, K/8] uint32 with scale [N, K/32] fp16.
 MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
-                       int* status, cudaStream_t stream) {
+                       int* status, float* workspace, long long workspace_bytes, int* counters,
+                       int num_counters, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   const bool q4 = scale != nullptr;
   if (K % 8 != 0 || ldx % 8 != 0) return -1;
@@ -404,6 +484,24 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
   p.num_n_blocks = (N + BM - 1) / BM;
   p.out_dtype = out_dtype;
   p.ab_fmt = ab_fmt;
+  // split-K when the output tiles alone cannot fill the GPU (decode-sized M with a narrow N)
+  {
+    const int tiles = p.num_m_blocks * p.num_n_blocks;
+    const int total_kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (workspace && counters && tiles * 2 <= sm_count() && tiles <= num_counters) {
+      splits = sm_count() / tiles;
+      if (splits > 8) splits = 8;
+      if (splits > total_kb / 4) splits = total_kb / 4;
+      if (splits < 1) splits = 1;
+      while (splits > 1 && static_cast<long long>(tiles) * splits * p.tn * BM * 4 > workspace_bytes)
+        --splits;
+    }
+    p.kb_per_split = (total_kb + splits - 1) / splits;
+    p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.workspace = workspace;
+    p.counters = counters;
+  }
 
   uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
   uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
@@ -422,7 +520,7 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
     mw = get_tensor_map(w, 2, 2, wd, ws, wb, 1);
   }
   if (!mx || !mw) return -4;
-  int tiles = p.num_m_blocks * p.num_n_blocks;
+  int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (q4)
     gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);

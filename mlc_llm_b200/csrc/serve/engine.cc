@@ -1,0 +1,1191 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <sstream>
+#include <stdexcept>
+
+namespace mlcb {
+
+namespace {
+
+using json::Object;
+using json::Value;
+
+struct EntryRef {
+  RequestState* rs;
+  int idx;
+  RequestStateEntry& e() const { return rs->entries[idx]; }
+  bool operator==(const EntryRef& o) const { return rs == o.rs && idx == o.idx; }
+};
+
+class IdManager {
+ public:
+  int64_t Get() {
+    if (!free_.empty()) {
+      int64_t id = free_.back();
+      free_.pop_back();
+      return id;
+    }
+    return next_++;
+  }
+  void Recycle(int64_t id) { free_.push_back(id); }
+  void Reset() {
+    free_.clear();
+    next_ = 0;
+  }
+
+ private:
+  std::vector<int64_t> free_;
+  int64_t next_ = 0;
+};
+
+// Ref-counted slots of the on-device draft-probability storage.
+class SlotManager {
+ public:
+  explicit SlotManager(int n = 0) { Resize(n); }
+  void Resize(int n) {
+    free_.clear();
+    for (int i = n - 1; i >= 0; --i) free_.push_back(i);
+  }
+  int Alloc() {
+    if (free_.empty()) throw std::runtime_error("draft token workspace exhausted");
+    int s = free_.back();
+    free_.pop_back();
+    return s;
+  }
+  void Free(int s) { free_.push_back(s); }
+
+ private:
+  std::vector<int> free_;
+};
+
+std::string LogprobJSON(const Tokenizer* tok, const SampleResult& r) {
+  auto one = [&](int32_t token, float prob) {
+    Object o;
+    const std::string& bytes = tok ? tok->TokenBytes(token) : std::string();
+    o["token"] = tok ? tok->Decode({token}) : std::to_string(token);
+    o["logprob"] = static_cast<double>(std::log(std::max(prob, 1e-30f)));
+    json::Array b;
+    for (unsigned char c : bytes) b.emplace_back(static_cast<int>(c));
+    o["bytes"] = Value(std::move(b));
+    return o;
+  };
+  Object o = one(r.token, r.prob);
+  json::Array top;
+  for (auto& p : r.top) top.emplace_back(one(p.first, p.second));
+  o["top_logprobs"] = Value(std::move(top));
+  return Value(std::move(o)).dump();
+}
+
+// ====================================================================== EngineImpl
+class EngineImpl : public Engine {
+ public:
+  EngineImpl(EngineConfig config, std::vector<EngineModelInfo> models,
+             std::shared_ptr<ModelBackend> backend, std::shared_ptr<const Tokenizer> tokenizer,
+             std::shared_ptr<GrammarBackend> grammar, std::shared_ptr<EventTraceRecorder> trace,
+             StreamCallback callback)
+      : cfg_(std::move(config)), models_(std::move(models)), backend_(std::move(backend)),
+        tok_(std::move(tokenizer)), grammar_(std::move(grammar)), trace_(std::move(trace)),
+        callback_(std::move(callback)),
+        prefix_cache_(cfg_.prefix_cache_mode == PrefixCacheMode::kRadix,
+                      cfg_.prefix_cache_max_num_recycling_seqs,
+                      [this](int64_t id) { this->OnPrefixCacheRemove(id); }) {
+    if (models_.empty()) throw std::runtime_error("Engine: no model");
+    const int64_t max_seqs = cfg_.max_num_sequence * 2 + cfg_.prefix_cache_max_num_recycling_seqs + 8;
+    for (auto& m : models_)
+      kv_.emplace_back(new KVManager(m.num_pages, cfg_.kv_cache_page_size, max_seqs));
+    if (!models_[0].generation_defaults_json.empty()) {
+      Value v = json::parse(models_[0].generation_defaults_json);
+      if (v.is_object()) default_gen_ = GenerationConfig::DefaultsFromModelConfig(v.as_object());
+    }
+    spec_ = cfg_.speculative_mode != SpeculativeMode::kDisable && models_.size() > 1;
+    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * 2 * (MaxDraftLength() + 1));
+    std::random_device rd;
+    seed_rng_.seed(rd());
+  }
+
+  // ---------------------------------------------------------------- public API
+  void SetStreamCallback(StreamCallback cb) override { callback_ = std::move(cb); }
+  const GenerationConfig& DefaultGenerationConfig() const override { return default_gen_; }
+  const EngineConfig& Config() const override { return cfg_; }
+  bool Empty() const override { return states_.empty(); }
+  std::string JSONMetrics() const override { return metrics_.AsJSON().dump(); }
+  std::string DebugStats() const override {
+    Object o;
+    o["num_prefill_steps"] = num_prefill_steps_;
+    o["num_decode_steps"] = num_decode_steps_;
+    o["num_verify_steps"] = num_verify_steps_;
+    o["num_preemptions"] = num_preemptions_;
+    o["num_running"] = static_cast<int64_t>(running_.size());
+    o["num_waiting"] = static_cast<int64_t>(waiting_.size());
+    o["kv_available_pages"] = kv_[0]->NumAvailablePages();
+    o["kv_total_sequence_length"] = kv_[0]->TotalSequenceLength();
+    o["prefix_cache_recycling"] = prefix_cache_.NumRecycling();
+    return Value(std::move(o)).dump();
+  }
+
+  void AddRequest(Request request) override {
+    Trace(request.id, "request added to engine");
+    auto rs = std::make_unique<RequestState>();
+    rs->request = std::move(request);
+    Request& req = rs->request;
+    req.prompt_tokens = 0;
+    for (auto& in : req.inputs) req.prompt_tokens += in.Length();
+    rs->metrics.prompt_tokens = req.prompt_tokens;
+    rs->metrics.add_time = NowSeconds();
+    if (req.cfg.debug_config.special_request == SpecialRequestKind::kQueryEngineMetrics) {
+      RequestStreamOutput out;
+      out.request_id = req.id;
+      out.group_delta_token_ids.resize(1);
+      out.group_delta_logprob_json_strs.resize(1);
+      out.group_finish_reason = {"stop"};
+      out.group_extra_prefix_string = {""};
+      Object usage;
+      usage["prompt_tokens"] = 0;
+      usage["completion_tokens"] = 0;
+      usage["total_tokens"] = 0;
+      usage["extra"] = metrics_.AsJSON();
+      out.request_final_usage_json_str = Value(std::move(usage)).dump();
+      Emit({std::move(out)});
+      return;
+    }
+    if (states_.count(req.id)) throw std::runtime_error("duplicate request id " + req.id);
+    const int n = req.cfg.n;
+    const int num_entries = n == 1 ? 1 : n + 1;
+    rs->entries.resize(num_entries);
+    const uint64_t base_seed = req.cfg.seed >= 0 ? static_cast<uint64_t>(req.cfg.seed) : seed_rng_();
+    for (int i = 0; i < num_entries; ++i) {
+      RequestStateEntry& e = rs->entries[i];
+      e.mstates.resize(models_.size());
+      e.rng.seed(base_seed + static_cast<uint64_t>(i) * 0x9E3779B97F4A7C15ull);
+      e.stop_handler = std::make_unique<StopStrHandler>(req.cfg.stop_strs, tok_);
+      if (i > 0) {
+        e.parent_idx = 0;
+        rs->entries[0].child_indices.push_back(i);
+      }
+    }
+    for (size_t m = 0; m < models_.size(); ++m)
+      for (auto& in : req.inputs) rs->entries[0].mstates[m].inputs.push_back(in);
+    rs->num_unfinished = n;
+    // requests longer than the engine can ever hold finish immediately with "length"
+    if (req.prompt_tokens >= cfg_.max_single_sequence_length || req.prompt_tokens == 0) {
+      RequestStreamOutput out;
+      out.request_id = req.id;
+      out.group_delta_token_ids.resize(n);
+      out.group_delta_logprob_json_strs.resize(n);
+      out.group_finish_reason.assign(n, "length");
+      out.group_extra_prefix_string.assign(n, "");
+      rs->metrics.finish_time = rs->metrics.prefill_end_time = NowSeconds();
+      out.request_final_usage_json_str = rs->metrics.AsUsageJSON(true).dump();
+      Emit({std::move(out)});
+      return;
+    }
+    if (grammar_ && req.cfg.response_format.type == "json_object") {
+      const std::string rf = req.cfg.response_format.AsJSON().dump();
+      for (int i = (n == 1 ? 0 : 1); i < num_entries; ++i) rs->entries[i].grammar_handle = grammar_->Create(rf);
+    }
+    RequestState* raw = rs.get();
+    states_[req.id] = std::move(rs);
+    waiting_.push_back(raw);
+  }
+
+  void AbortRequest(const std::string& request_id) override {
+    auto it = states_.find(request_id);
+    if (it == states_.end()) return;
+    RequestState* rs = it->second.get();
+    Trace(request_id, "abort");
+    for (auto& e : rs->entries) ReleaseEntry(e, /*recycle=*/false);
+    RemoveFromQueues(rs);
+    states_.erase(it);
+  }
+
+  void AbortAllRequests() override {
+    std::vector<std::string> ids;
+    for (auto& kv : states_) ids.push_back(kv.first);
+    for (auto& id : ids) AbortRequest(id);
+  }
+
+  void Reset() override {
+    AbortAllRequests();
+    running_.clear();
+    waiting_.clear();
+    states_.clear();
+    prefix_cache_.Reset();
+    for (auto& kv : kv_) kv->Clear();
+    ids_.Reset();
+    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * 2 * (MaxDraftLength() + 1));
+    metrics_.Reset();
+    if (backend_) backend_->Reset();
+  }
+
+  void Step() override {
+    touched_.clear();
+    bool did = StepPrefill();
+    if (!did) {
+      if (spec_) did = StepSpecDecode();
+      else did = StepDecode();
+    }
+    if (did) PostProcess();
+  }
+
+ private:
+  // ---------------------------------------------------------------- helpers
+  int MaxDraftLength() const { return cfg_.spec_draft_length > 0 ? cfg_.spec_draft_length : 4; }
+
+  void Trace(const std::string& id, const std::string& ev) {
+    if (trace_) trace_->AddEvent(id, ev);
+  }
+  void TraceBatch(const std::vector<EntryRef>& batch, const std::string& ev) {
+    if (!trace_) return;
+    std::vector<std::string> ids;
+    for (auto& r : batch) ids.push_back(r.rs->request.id);
+    trace_->AddEvent(ids, ev);
+  }
+  void Emit(std::vector<RequestStreamOutput> outs) {
+    if (callback_ && !outs.empty()) callback_(std::move(outs));
+  }
+  void Touch(RequestState* rs) {
+    if (std::find(touched_.begin(), touched_.end(), rs) == touched_.end()) touched_.push_back(rs);
+  }
+  void RemoveFromQueues(RequestState* rs) {
+    running_.erase(std::remove(running_.begin(), running_.end(), rs), running_.end());
+    waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), rs), waiting_.end());
+  }
+
+  void OnPrefixCacheRemove(int64_t id) {
+    for (auto& kv : kv_)
+      if (kv->Has(id)) kv->RemoveSequence(id);
+    ids_.Recycle(id);
+  }
+
+  // Frees everything an entry holds. recycle == true hands the sequence to the prefix cache.
+  void ReleaseEntry(RequestStateEntry& e, bool recycle) {
+    if (e.kv_released) return;
+    e.kv_released = true;
+    if (e.grammar_handle >= 0 && grammar_) {
+      grammar_->Release(e.grammar_handle);
+      e.grammar_handle = -1;
+    }
+    for (auto& ms : e.mstates) {
+      for (int s : ms.draft_slots) draft_slots_.Free(s);
+      ms.draft_slots.clear();
+      ms.draft_tokens.clear();
+      ms.draft_parents.clear();
+      for (auto& in : ms.inputs)
+        if (in.kind == 1 && backend_) backend_->ReleaseEmbedding(in.embed_handle);
+    }
+    const int64_t id = e.mstates[0].internal_id;
+    if (id < 0) return;
+    for (auto& ms : e.mstates) ms.internal_id = -1;
+    if (prefix_cache_.HasSequence(id)) {
+      if (recycle) {
+        // the cache indexes exactly the tokens it was told about: drop any KV beyond them
+        const int64_t keep = prefix_cache_.SequenceLength(id);
+        for (auto& kv : kv_)
+          if (kv->Has(id) && kv->SequenceLength(id) > keep) kv->PopN(id, kv->SequenceLength(id) - keep);
+      }
+      prefix_cache_.RecycleSequence(id, recycle);  // may call OnPrefixCacheRemove
+    } else {
+      OnPrefixCacheRemove(id);
+    }
+  }
+
+  int64_t NumActiveSequences() const {
+    int64_t n = 0;
+    for (RequestState* rs : running_)
+      for (auto& e : rs->entries)
+        if (!e.kv_released && e.mstates[0].internal_id >= 0) ++n;
+    return n;
+  }
+
+  std::vector<EntryRef> ReadyToDecode() {
+    std::vector<EntryRef> out;
+    for (RequestState* rs : running_)
+      for (int i = 0; i < static_cast<int>(rs->entries.size()); ++i) {
+        RequestStateEntry& e = rs->entries[i];
+        if (e.status == EntryStatus::kAlive && e.mstates[0].inputs.empty() && !e.committed_tokens.empty())
+          out.push_back({rs, i});
+      }
+    return out;
+  }
+
+  bool IsStopToken(const Request& req, int32_t token) const {
+    for (int t : req.cfg.stop_token_ids)
+      if (t == token) return true;
+    if (!req.cfg.debug_config.ignore_eos)
+      for (int32_t t : models_[0].eos_token_ids)
+        if (t == token) return true;
+    return false;
+  }
+
+  void CommitToken(EntryRef r, const SampleResult& s) {
+    RequestStateEntry& e = r.e();
+    e.committed_tokens.push_back(s);
+    ++e.appeared_token_ids[s.token];
+    ++r.rs->metrics.completion_tokens;
+    if (e.grammar_handle >= 0 && grammar_ && !IsStopToken(r.rs->request, s.token))
+      grammar_->AcceptToken(e.grammar_handle, s.token);
+    Touch(r.rs);
+  }
+
+  // Appends the sampling parameters of one row.
+  void AddSampleRow(SampleParams* sp, EntryRef r, int32_t logit_token_index) {
+    RequestStateEntry& e = r.e();
+    const GenerationConfig& g = r.rs->request.cfg;
+    const int row = static_cast<int>(sp->logit_token_index.size());
+    sp->logit_token_index.push_back(logit_token_index);
+    sp->temperature.push_back(static_cast<float>(g.temperature));
+    sp->top_p.push_back(static_cast<float>(g.top_p));
+    sp->top_k.push_back(g.top_k);
+    sp->uniform.push_back(static_cast<float>(e.NextUniform()));
+    const bool has_pen = g.frequency_penalty != 0 || g.presence_penalty != 0 || g.repetition_penalty != 1.0;
+    sp->penalties.push_back(static_cast<float>(g.presence_penalty));
+    sp->penalties.push_back(static_cast<float>(g.frequency_penalty));
+    sp->penalties.push_back(static_cast<float>(g.repetition_penalty));
+    if (has_pen)
+      for (auto& kv : e.appeared_token_ids) {
+        sp->pen_row.push_back(row);
+        sp->pen_token.push_back(kv.first);
+        sp->pen_count.push_back(kv.second);
+      }
+    for (auto& b : g.logit_bias) {
+      sp->bias_row.push_back(row);
+      sp->bias_token.push_back(b.first);
+      sp->bias_value.push_back(b.second);
+    }
+    if (e.grammar_handle >= 0 && grammar_) {
+      std::vector<int32_t> bits = grammar_->NextTokenBitmask(e.grammar_handle);
+      sp->mask_rows.push_back(row);
+      sp->mask_bits.insert(sp->mask_bits.end(), bits.begin(), bits.end());
+    }
+    if (g.logprobs) sp->num_top_logprobs = std::max(sp->num_top_logprobs, g.top_logprobs);
+  }
+
+  SampleResult RowResult(const SampleOutput& out, int row, int num_top, const GenerationConfig& g) {
+    SampleResult s;
+    s.token = out.tokens[row];
+    s.prob = row < static_cast<int>(out.probs.size()) ? out.probs[row] : 1.f;
+    if (g.logprobs && num_top > 0)
+      for (int k = 0; k < g.top_logprobs && k < num_top; ++k)
+        s.top.emplace_back(out.top_tokens[row * num_top + k], out.top_probs[row * num_top + k]);
+    return s;
+  }
+
+  // Makes room for `pages` KV pages in model 0, evicting recycled prefixes first.
+  bool EnsurePages(int64_t pages) {
+    while (kv_[0]->NumAvailablePages() < pages) {
+      if (!prefix_cache_.TryFreeMemory()) return false;
+    }
+    return true;
+  }
+
+  // ---------------------------------------------------------------- preemption
+  void PreemptLast() {
+    // last alive entry of the last running request
+    for (auto rit = running_.rbegin(); rit != running_.rend(); ++rit) {
+      RequestState* rs = *rit;
+      for (int i = static_cast<int>(rs->entries.size()) - 1; i >= 0; --i) {
+        RequestStateEntry& e = rs->entries[i];
+        if (e.status != EntryStatus::kAlive || e.mstates[0].internal_id < 0) continue;
+        Trace(rs->request.id, "preempt");
+        ++num_preemptions_;
+        const int64_t id = e.mstates[0].internal_id;
+        // drop the KV now (non-lazy): memory is what we are short of
+        if (prefix_cache_.HasSequence(id)) prefix_cache_.RecycleSequence(id, /*lazy=*/false);
+        else OnPrefixCacheRemove(id);
+        for (auto& ms : e.mstates) {
+          for (int s : ms.draft_slots) draft_slots_.Free(s);
+          ms = ModelState();
+          for (auto& in : rs->request.inputs) ms.inputs.push_back(in);
+          if (!e.committed_tokens.empty()) {
+            InputItem it;
+            for (auto& c : e.committed_tokens) it.tokens.push_back(c.token);
+            ms.inputs.push_back(std::move(it));
+          }
+          // those tokens reach the prefix cache again as prefilled inputs
+          ms.cached_committed_tokens = static_cast<int64_t>(e.committed_tokens.size());
+        }
+        e.status = EntryStatus::kPending;
+        e.parent_idx = -1;  // re-prefilled as a self-contained sequence
+        // if nothing of this request still runs, move it to the front of the waiting queue
+        bool any_alive = false;
+        for (auto& o : rs->entries) any_alive |= (o.status == EntryStatus::kAlive);
+        if (!any_alive) {
+          running_.erase(std::remove(running_.begin(), running_.end(), rs), running_.end());
+          waiting_.insert(waiting_.begin(), rs);
+        }
+        return;
+      }
+    }
+    throw std::runtime_error("Engine: nothing left to preempt");
+  }
+
+  // ---------------------------------------------------------------- prefill
+  struct PrefillItem {
+    EntryRef ref;
+    int64_t take;       // tokens of this step
+    bool completes;     // inputs exhausted after this step
+    bool is_decode;     // hybrid: a running sequence contributing its single next token
+  };
+
+  // First scheduling of an entry: allocate / fork / reuse its KV sequence.
+  void MatchPrefixAndCreateSequence(EntryRef r) {
+    RequestStateEntry& e = r.e();
+    ModelState& ms = e.mstates[0];
+    std::vector<int32_t> tokens;
+    bool all_tokens = true;
+    for (auto& in : ms.inputs) {
+      if (in.kind != 0) { all_tokens = false; break; }
+      tokens.insert(tokens.end(), in.tokens.begin(), in.tokens.end());
+    }
+    int64_t id = ids_.Get();
+    int64_t offset = 0;
+    int64_t draft_offset = 0;
+    if (all_tokens && prefix_cache_.enabled()) {
+      PrefixMatch m = prefix_cache_.InsertSequence(id, tokens, static_cast<int>(cfg_.sliding_window_size),
+                                                   static_cast<int>(std::max<int64_t>(0, cfg_.attention_sink_size)));
+      if (m.reused_seq_id >= 0) {
+        ids_.Recycle(id);
+        id = m.reused_seq_id;
+        offset = m.prefilled_offset;
+        if (kv_[0]->SequenceLength(id) > offset) kv_[0]->PopN(id, kv_[0]->SequenceLength(id) - offset);
+        for (size_t d = 1; d < kv_.size(); ++d) {
+          if (!kv_[d]->Has(id)) kv_[d]->AddSequence(id);
+          const int64_t dl = kv_[d]->SequenceLength(id);
+          if (dl > offset) kv_[d]->PopN(id, dl - offset);
+          draft_offset = std::min(dl, offset);
+        }
+      } else if (m.forked_seq_id >= 0) {
+        // the fork may need a page for the copy-on-write of the last partial page
+        EnsurePages(1);
+        kv_[0]->ForkSequence(m.forked_seq_id, id, m.prefilled_offset);
+        offset = m.prefilled_offset;
+        for (size_t d = 1; d < kv_.size(); ++d) {
+          if (kv_[d]->Has(m.forked_seq_id) && kv_[d]->NumAvailablePages() > 0) {
+            draft_offset = std::min(kv_[d]->SequenceLength(m.forked_seq_id), offset);
+            kv_[d]->ForkSequence(m.forked_seq_id, id, draft_offset);
+          } else {
+            kv_[d]->AddSequence(id);
+          }
+        }
+      } else {
+        for (auto& kv : kv_) kv->AddSequence(id);
+      }
+      if (r.rs->request.cfg.debug_config.pinned_system_prompt) prefix_cache_.PinSequence(id);
+    } else {
+      for (auto& kv : kv_) kv->AddSequence(id);
+    }
+    if (cfg_.sliding_window_size > 0 && e.child_indices.empty())
+      for (auto& kv : kv_)
+        kv->EnableSlidingWindow(id, static_cast<int32_t>(cfg_.sliding_window_size),
+                                static_cast<int32_t>(std::max<int64_t>(0, cfg_.attention_sink_size)));
+    for (auto& s : e.mstates) s.internal_id = id;
+    auto drop_prefix = [](ModelState& st, int64_t n) {
+      st.num_prefilled_tokens = n;
+      int64_t left = n;
+      while (left > 0 && !st.inputs.empty()) {
+        InputItem& in = st.inputs.front();
+        if (static_cast<int64_t>(in.tokens.size()) <= left) {
+          left -= static_cast<int64_t>(in.tokens.size());
+          st.inputs.pop_front();
+        } else {
+          in.tokens.erase(in.tokens.begin(), in.tokens.begin() + left);
+          left = 0;
+        }
+      }
+    };
+    if (offset > 0) {
+      // drop the matched prefix from the pending inputs
+      ms.prefilled_tokens.assign(tokens.begin(), tokens.begin() + offset);
+      drop_prefix(ms, offset);
+    }
+    for (size_t d = 1; d < e.mstates.size(); ++d)
+      if (draft_offset > 0) drop_prefix(e.mstates[d], draft_offset);
+  }
+
+  bool StepPrefill() {
+    const double t0 = NowSeconds();
+    // candidates in priority order: running requests with leftover inputs, then waiting requests
+    std::vector<EntryRef> cands;
+    auto collect = [&](RequestState* rs) {
+      for (int i = 0; i < static_cast<int>(rs->entries.size()); ++i) {
+        RequestStateEntry& e = rs->entries[i];
+        if (e.status == EntryStatus::kFinished) continue;
+        if (!e.mstates[0].inputs.empty()) cands.push_back({rs, i});
+      }
+    };
+    for (RequestState* rs : running_) collect(rs);
+    for (RequestState* rs : waiting_) collect(rs);
+    if (cands.empty()) return false;
+
+    std::vector<EntryRef> decode_ready = ReadyToDecode();
+    int64_t budget = cfg_.prefill_chunk_size;
+    int64_t active = NumActiveSequences();
+    int64_t pages_reserved = 0;
+    int64_t total_new = 0;
+    std::vector<PrefillItem> items;
+    const int64_t page = cfg_.kv_cache_page_size;
+    for (EntryRef r : cands) {
+      if (budget <= 0) break;
+      RequestStateEntry& e = r.e();
+      ModelState& ms = e.mstates[0];
+      const bool is_new = ms.internal_id < 0;
+      if (is_new) {
+        const int64_t seqs_needed = 1 + static_cast<int64_t>(e.child_indices.size());
+        if (active + seqs_needed > cfg_.max_num_sequence) break;
+        // memory admission is evaluated on the unmatched length (a prefix hit only helps)
+        int64_t input_len = 0;
+        for (auto& in : ms.inputs) input_len += in.Length();
+        const int64_t first_take = std::min(input_len, budget);
+        const int64_t need = (first_take + page - 1) / page + 1 + seqs_needed;
+        if (!EnsurePages(pages_reserved + need)) break;
+        if (kv_[0]->TotalSequenceLength() + total_new + first_take + 8 * (active + seqs_needed) >
+            cfg_.max_total_sequence_length) {
+          // try to shed cached prefixes, then give up for this step
+          bool freed = false;
+          while (prefix_cache_.TryFreeMemory()) {
+            freed = true;
+            if (kv_[0]->TotalSequenceLength() + total_new + first_take + 8 * (active + seqs_needed) <=
+                cfg_.max_total_sequence_length)
+              break;
+          }
+          if (!freed || kv_[0]->TotalSequenceLength() + total_new + first_take + 8 * (active + seqs_needed) >
+                            cfg_.max_total_sequence_length)
+            break;
+        }
+        MatchPrefixAndCreateSequence(r);
+        active += seqs_needed;
+        if (std::find(running_.begin(), running_.end(), r.rs) == running_.end()) {
+          waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), r.rs), waiting_.end());
+          running_.push_back(r.rs);
+        }
+        e.status = EntryStatus::kAlive;
+      }
+      int64_t input_len = 0;
+      for (auto& in : ms.inputs) input_len += in.Length();
+      if (input_len == 0) continue;  // fully matched by the prefix cache (cannot happen: last token kept)
+      int64_t take = std::min(input_len, budget);
+      // embeddings are never split
+      if (take < input_len) {
+        int64_t acc = 0;
+        for (auto& in : ms.inputs) {
+          if (acc + in.Length() <= take) { acc += in.Length(); continue; }
+          if (in.kind == 1) take = acc;  // stop before this embedding item
+          break;
+        }
+        if (take == 0) break;
+      }
+      const int64_t need = kv_[0]->PagesNeeded(ms.internal_id, take) + 1;
+      if (!EnsurePages(pages_reserved + need)) {
+        if (items.empty() && decode_ready.empty()) {
+          // nothing else can make progress: shed the newest running sequence
+          if (NumActiveSequences() > 1) { PreemptLast(); return true; }
+        }
+        break;
+      }
+      pages_reserved += need;
+      total_new += take;
+      budget -= take;
+      items.push_back({r, take, take == input_len, false});
+    }
+    if (items.empty()) return false;
+    if (cfg_.prefill_mode == PrefillMode::kHybrid) {
+      for (EntryRef r : decode_ready) {
+        if (budget <= 0) break;
+        const int64_t need = kv_[0]->PagesNeeded(r.e().mstates[0].internal_id, 1);
+        if (!EnsurePages(pages_reserved + need)) break;
+        pages_reserved += need;
+        budget -= 1;
+        r.rs->metrics.decode_tokens += 1;
+        items.push_back({r, 1, true, true});
+      }
+    }
+    std::vector<EntryRef> batch;
+    for (auto& it : items) batch.push_back(it.ref);
+    TraceBatch(batch, "start prefill");
+
+    // ---- assemble the model call
+    std::vector<int64_t> seq_ids;
+    std::vector<int32_t> lens, token_ids;
+    std::vector<int64_t> embed_handles;
+    SampleParams sp;
+    struct RowOwner { EntryRef ref; int child; };
+    std::vector<RowOwner> owners;
+    int32_t tok_off = 0;
+    for (auto& it : items) {
+      RequestStateEntry& e = it.ref.e();
+      ModelState& ms = e.mstates[0];
+      seq_ids.push_back(ms.internal_id);
+      lens.push_back(static_cast<int32_t>(it.take));
+      if (it.is_decode) {
+        token_ids.push_back(e.committed_tokens.back().token);
+        embed_handles.push_back(-1);
+      } else {
+        int64_t left = it.take;
+        std::vector<int32_t> fed;
+        while (left > 0) {
+          InputItem& in = ms.inputs.front();
+          if (in.kind == 1) {
+            for (int32_t k = 0; k < in.embed_len; ++k) {
+              token_ids.push_back(k);  // row inside the embedding
+              embed_handles.push_back(in.embed_handle);
+            }
+            left -= in.embed_len;
+            ms.inputs.pop_front();
+            continue;
+          }
+          const int64_t n = std::min<int64_t>(left, static_cast<int64_t>(in.tokens.size()));
+          token_ids.insert(token_ids.end(), in.tokens.begin(), in.tokens.begin() + n);
+          embed_handles.insert(embed_handles.end(), n, -1);
+          fed.insert(fed.end(), in.tokens.begin(), in.tokens.begin() + n);
+          if (n == static_cast<int64_t>(in.tokens.size())) ms.inputs.pop_front();
+          else in.tokens.erase(in.tokens.begin(), in.tokens.begin() + n);
+          left -= n;
+        }
+        ms.num_prefilled_tokens += it.take;
+        ms.prefilled_tokens.insert(ms.prefilled_tokens.end(), fed.begin(), fed.end());
+        it.ref.rs->metrics.prefill_tokens += it.take;
+        if (prefix_cache_.HasSequence(ms.internal_id)) prefix_cache_.ExtendSequence(ms.internal_id, fed);
+      }
+      if (it.completes) {
+        const int32_t last = tok_off + static_cast<int32_t>(it.take) - 1;
+        if (!it.is_decode && !e.child_indices.empty()) {
+          for (int c : e.child_indices) {
+            AddSampleRow(&sp, {it.ref.rs, c}, last);
+            owners.push_back({it.ref, c});
+          }
+        } else {
+          AddSampleRow(&sp, it.ref, last);
+          owners.push_back({it.ref, -1});
+        }
+      }
+      tok_off += static_cast<int32_t>(it.take);
+    }
+    ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens);
+    SampleOutput out = backend_->ForwardSample(0, plan, token_ids, embed_handles, sp);
+    prefix_cache_.CommitSequenceExtention();
+    if (spec_) PrefillDraftModel(items);
+
+    // ---- commit
+    const double now = NowSeconds();
+    for (size_t row = 0; row < owners.size(); ++row) {
+      EntryRef parent = owners[row].ref;
+      const GenerationConfig& g = parent.rs->request.cfg;
+      SampleResult s = RowResult(out, static_cast<int>(row), sp.num_top_logprobs, g);
+      if (owners[row].child >= 0) {
+        EntryRef child{parent.rs, owners[row].child};
+        RequestStateEntry& ce = child.e();
+        const int64_t cid = ids_.Get();
+        EnsurePages(1);
+        for (size_t m = 0; m < kv_.size(); ++m)
+          if (kv_[m]->Has(parent.e().mstates[m].internal_id))
+            kv_[m]->ForkSequence(parent.e().mstates[m].internal_id, cid, -1);
+        for (auto& ms : ce.mstates) ms.internal_id = cid;
+        ce.mstates[0].prefilled_tokens = parent.e().mstates[0].prefilled_tokens;
+        ce.status = EntryStatus::kAlive;
+        CommitToken(child, s);
+      } else {
+        CommitToken(parent, s);
+      }
+      if (!parent.rs->prefill_done) {
+        parent.rs->prefill_done = true;
+        parent.rs->metrics.prefill_end_time = now;
+      }
+    }
+    // a parent whose children took over stays only as the holder of the shared prompt KV
+    for (auto& it : items)
+      if (it.completes && !it.is_decode && !it.ref.e().child_indices.empty())
+        it.ref.e().status = EntryStatus::kFinished;
+    for (auto& it : items) Touch(it.ref.rs);
+    TraceBatch(batch, "finish prefill");
+    ++num_prefill_steps_;
+    metrics_.engine_prefill_time_sum += NowSeconds() - t0;
+    return true;
+  }
+
+  // ---------------------------------------------------------------- decode
+  // Shrinks `ready` (preempting from the back) until one token per sequence fits in memory.
+  bool FitDecodeBatch(std::vector<EntryRef>* ready, int64_t tokens_per_seq) {
+    while (!ready->empty()) {
+      int64_t need = 0;
+      for (auto& r : *ready) need += kv_[0]->PagesNeeded(r.e().mstates[0].internal_id, tokens_per_seq);
+      if (EnsurePages(need)) return true;
+      if (ready->size() == 1 && NumActiveSequences() <= 1)
+        throw std::runtime_error("Engine: KV cache too small for a single sequence");
+      PreemptLast();
+      *ready = ReadyToDecode();
+    }
+    return false;
+  }
+
+  bool StepDecode() {
+    const double t0 = NowSeconds();
+    std::vector<EntryRef> ready = ReadyToDecode();
+    if (ready.empty()) return false;
+    if (!FitDecodeBatch(&ready, 1)) return false;
+    if (static_cast<int64_t>(ready.size()) > cfg_.max_num_sequence) ready.resize(cfg_.max_num_sequence);
+    TraceBatch(ready, "start decode");
+    std::vector<int64_t> seq_ids;
+    std::vector<int32_t> lens(ready.size(), 1), token_ids;
+    std::vector<int64_t> embed_handles(ready.size(), -1);
+    SampleParams sp;
+    for (size_t i = 0; i < ready.size(); ++i) {
+      RequestStateEntry& e = ready[i].e();
+      seq_ids.push_back(e.mstates[0].internal_id);
+      token_ids.push_back(e.committed_tokens.back().token);
+      AddSampleRow(&sp, ready[i], static_cast<int32_t>(i));
+    }
+    ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens);
+    SampleOutput out = backend_->ForwardSample(0, plan, token_ids, embed_handles, sp);
+    for (size_t i = 0; i < ready.size(); ++i) {
+      ready[i].rs->metrics.decode_tokens += 1;
+      CommitToken(ready[i], RowResult(out, static_cast<int>(i), sp.num_top_logprobs, ready[i].rs->request.cfg));
+    }
+    TraceBatch(ready, "finish decode");
+    ++num_decode_steps_;
+    const double dt = NowSeconds() - t0;
+    metrics_.engine_decode_time_sum += dt;
+    metrics_.UpdateDecodeTimeByBatchSize(static_cast<int>(ready.size()), dt);
+    return true;
+  }
+
+  // ---------------------------------------------------------------- speculative decoding
+  int DraftLengthFor(int batch) const {
+    if (cfg_.spec_draft_length > 0) return cfg_.spec_draft_length;
+    // automatic mode: shorter drafts as the batch grows, plain decode for large batches
+    if (batch < 10) return 4;
+    if (batch < 20) return 3;
+    if (batch < 30) return 2;
+    return 0;
+  }
+
+  // Keeps the draft model's KV in step with the main model for the prompt part.
+  void PrefillDraftModel(const std::vector<PrefillItem>& items) {
+    std::vector<int64_t> seq_ids;
+    std::vector<int32_t> lens, token_ids;
+    std::vector<int64_t> embed_handles;
+    for (auto& it : items) {
+      RequestStateEntry& e = it.ref.e();
+      ModelState& ms = e.mstates[1];
+      if (it.is_decode) continue;  // the draft phase catches up on decode tokens by itself
+      if (!kv_[1]->Has(ms.internal_id)) kv_[1]->AddSequence(ms.internal_id);
+      // catch up to wherever the main model's prefill now stands
+      int64_t left = e.mstates[0].num_prefilled_tokens - ms.num_prefilled_tokens;
+      int64_t fed = 0;
+      while (left > 0 && !ms.inputs.empty()) {
+        InputItem& in = ms.inputs.front();
+        if (in.kind == 1) {
+          for (int32_t k = 0; k < in.embed_len; ++k) {
+            token_ids.push_back(k);
+            embed_handles.push_back(in.embed_handle);
+          }
+          left -= in.embed_len;
+          fed += in.embed_len;
+          ms.inputs.pop_front();
+          continue;
+        }
+        const int64_t n = std::min<int64_t>(left, static_cast<int64_t>(in.tokens.size()));
+        token_ids.insert(token_ids.end(), in.tokens.begin(), in.tokens.begin() + n);
+        embed_handles.insert(embed_handles.end(), n, -1);
+        if (n == static_cast<int64_t>(in.tokens.size())) ms.inputs.pop_front();
+        else in.tokens.erase(in.tokens.begin(), in.tokens.begin() + n);
+        left -= n;
+        fed += n;
+      }
+      if (fed == 0) continue;
+      ms.num_prefilled_tokens += fed;
+      seq_ids.push_back(ms.internal_id);
+      lens.push_back(static_cast<int32_t>(fed));
+    }
+    if (seq_ids.empty()) return;
+    ForwardPlan plan = kv_[1]->BeginForward(seq_ids, lens);
+    SampleParams none;
+    backend_->ForwardSample(1, plan, token_ids, embed_handles, none);
+  }
+
+  bool StepSpecDecode() {
+    std::vector<EntryRef> ready = ReadyToDecode();
+    if (ready.empty()) return false;
+    const int k = DraftLengthFor(static_cast<int>(ready.size()));
+    if (k == 0) return StepDecode();
+    if (!FitDecodeBatch(&ready, k + 1)) return false;
+    if (static_cast<int64_t>(ready.size()) > cfg_.max_num_sequence) ready.resize(cfg_.max_num_sequence);
+    // the draft model needs the same room
+    {
+      int64_t need = 0;
+      for (auto& r : ready) need += kv_[1]->PagesNeeded(r.e().mstates[1].internal_id, k + 8);
+      if (kv_[1]->NumAvailablePages() < need) return StepDecode();
+    }
+    const int64_t prompt_extra = 0;
+    (void)prompt_extra;
+    // ---- draft phase: k rounds of the small model
+    double t0 = NowSeconds();
+    TraceBatch(ready, "start draft");
+    for (int round = 0; round < k; ++round) {
+      std::vector<int64_t> seq_ids;
+      std::vector<int32_t> lens, token_ids;
+      SampleParams sp;
+      int32_t off = 0;
+      for (auto& r : ready) {
+        RequestStateEntry& e = r.e();
+        ModelState& ds = e.mstates[1];
+        if (!kv_[1]->Has(ds.internal_id)) kv_[1]->AddSequence(ds.internal_id);
+        std::vector<int32_t> feed;
+        if (round == 0) {
+          // everything the draft model has not seen yet: lagging committed tokens
+          const int64_t total = r.rs->request.prompt_tokens + static_cast<int64_t>(e.committed_tokens.size());
+          const int64_t have = kv_[1]->SequenceLength(ds.internal_id);
+          int64_t lag = total - have;
+          if (lag > static_cast<int64_t>(e.committed_tokens.size()))
+            throw std::runtime_error("Engine: draft model KV lags behind the prompt");
+          for (int64_t j = static_cast<int64_t>(e.committed_tokens.size()) - lag;
+               j < static_cast<int64_t>(e.committed_tokens.size()); ++j)
+            feed.push_back(e.committed_tokens[j].token);
+        } else {
+          feed.push_back(ds.draft_tokens.back().token);
+        }
+        seq_ids.push_back(ds.internal_id);
+        lens.push_back(static_cast<int32_t>(feed.size()));
+        token_ids.insert(token_ids.end(), feed.begin(), feed.end());
+        off += static_cast<int32_t>(feed.size());
+        AddSampleRow(&sp, r, off - 1);
+        const int slot = draft_slots_.Alloc();
+        ds.draft_slots.push_back(slot);
+        sp.prob_slots.push_back(slot);
+      }
+      std::vector<int64_t> embed_handles(token_ids.size(), -1);
+      ForwardPlan plan = kv_[1]->BeginForward(seq_ids, lens);
+      SampleOutput out = backend_->ForwardSample(1, plan, token_ids, embed_handles, sp);
+      for (size_t i = 0; i < ready.size(); ++i) {
+        ModelState& ds = ready[i].e().mstates[1];
+        SampleResult s;
+        s.token = out.tokens[i];
+        s.prob = out.probs.empty() ? 1.f : out.probs[i];
+        ds.draft_tokens.push_back(s);
+        ds.draft_parents.push_back(round - 1);  // chain: node j hangs under node j-1 (-1 = root)
+      }
+    }
+    double t1 = NowSeconds();
+    metrics_.UpdateDraftTimeByBatchSize(static_cast<int>(ready.size()), t1 - t0);
+    TraceBatch(ready, "finish draft");
+
+    // ---- verify phase: one main-model pass over [last committed, drafts...]
+    TraceBatch(ready, "start verify");
+    std::vector<int64_t> seq_ids;
+    std::vector<int32_t> lens, token_ids, tree_parents;
+    VerifyParams vp;
+    vp.node_indptr.push_back(0);
+    int32_t off = 0;
+    for (auto& r : ready) {
+      RequestStateEntry& e = r.e();
+      ModelState& ds = e.mstates[1];
+      seq_ids.push_back(e.mstates[0].internal_id);
+      lens.push_back(k + 1);
+      token_ids.push_back(e.committed_tokens.back().token);
+      tree_parents.push_back(-1);
+      // row for the root (distribution after the last committed token)
+      AddSampleRow(&vp.sampling, r, off);
+      for (int j = 0; j < k; ++j) {
+        token_ids.push_back(ds.draft_tokens[j].token);
+        tree_parents.push_back(j);  // chunk-local: node j+1 hangs under node j (root is node 0)
+        vp.draft_tokens.push_back(ds.draft_tokens[j].token);
+        vp.draft_prob_slots.push_back(ds.draft_slots[j]);
+        vp.parents.push_back(j - 1);
+        vp.uniform.push_back(static_cast<float>(e.NextUniform()));
+        AddSampleRow(&vp.sampling, r, off + 1 + j);
+      }
+      vp.node_indptr.push_back(static_cast<int32_t>(vp.draft_tokens.size()));
+      vp.final_uniform.push_back(static_cast<float>(e.NextUniform()));
+      off += k + 1;
+    }
+    ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens, &tree_parents);
+    VerifyOutput vo = backend_->ForwardVerify(0, plan, token_ids, vp);
+    for (size_t i = 0; i < ready.size(); ++i) {
+      EntryRef r = ready[i];
+      RequestStateEntry& e = r.e();
+      ModelState& ds = e.mstates[1];
+      const int beg = vo.accepted_indptr[i], end = vo.accepted_indptr[i + 1];
+      const int accepted = end - beg;
+      // KV: node 0 (the last committed token) is always kept; accepted draft nodes follow
+      std::vector<int32_t> keep{0};
+      for (int j = beg; j < end; ++j) keep.push_back(vo.accepted_nodes[j] + 1);
+      std::vector<int32_t> moves = kv_[0]->CommitTreeNodes(e.mstates[0].internal_id, k + 1, keep);
+      if (!moves.empty()) backend_->MoveKVTokens(0, moves);
+      // draft KV holds [.., last committed, d_0 .. d_{k-2}]; keep the accepted part
+      const int draft_valid = std::min(accepted, k - 1);
+      if (k - 1 - draft_valid > 0) kv_[1]->PopN(ds.internal_id, k - 1 - draft_valid);
+      for (int j = beg; j < end; ++j) {
+        CommitToken(r, ds.draft_tokens[vo.accepted_nodes[j]]);
+      }
+      SampleResult fin;
+      fin.token = vo.final_tokens[i];
+      fin.prob = vo.final_probs.empty() ? 1.f : vo.final_probs[i];
+      CommitToken(r, fin);
+      r.rs->metrics.decode_tokens += accepted + 1;
+      metrics_.spec_decode.Update(k, accepted);
+      for (int s : ds.draft_slots) draft_slots_.Free(s);
+      ds.draft_slots.clear();
+      ds.draft_tokens.clear();
+      ds.draft_parents.clear();
+    }
+    TraceBatch(ready, "finish verify");
+    ++num_verify_steps_;
+    const double t2 = NowSeconds();
+    metrics_.UpdateVerifyTimeByBatchSize(static_cast<int>(ready.size()), t2 - t1);
+    metrics_.engine_decode_time_sum += t2 - t0;
+    return true;
+  }
+
+  // ---------------------------------------------------------------- post-processing
+  void FinishEntry(RequestState* rs, RequestStateEntry& e, const std::string& reason) {
+    e.status = EntryStatus::kFinished;
+    e.finish_reason = reason;
+    --rs->num_unfinished;
+  }
+
+  void PostProcess() {
+    std::vector<RequestStreamOutput> outs;
+    const double now = NowSeconds();
+    for (RequestState* rs : touched_) {
+      if (!states_.count(rs->request.id)) continue;
+      const Request& req = rs->request;
+      const int n = req.cfg.n;
+      RequestStreamOutput out;
+      out.request_id = req.id;
+      out.group_delta_token_ids.resize(n);
+      out.group_delta_logprob_json_strs.resize(n);
+      out.group_finish_reason.assign(n, "");
+      out.group_extra_prefix_string.assign(n, "");
+      bool any = false;
+      for (int g = 0; g < n; ++g) {
+        const int idx = n == 1 ? 0 : g + 1;
+        RequestStateEntry& e = rs->entries[idx];
+        if (e.status != EntryStatus::kAlive) continue;
+        std::vector<int32_t>& delta = out.group_delta_token_ids[g];
+        std::string finish;
+        auto emit_tokens = [&](const std::vector<int32_t>& released, int64_t upto) {
+          (void)upto;
+          for (int32_t t : released) delta.push_back(t);
+        };
+        const int64_t first_new = e.next_callback_token_pos;
+        while (e.next_callback_token_pos < static_cast<int64_t>(e.committed_tokens.size()) && finish.empty()) {
+          const SampleResult& s = e.committed_tokens[e.next_callback_token_pos];
+          ++e.next_callback_token_pos;
+          if (IsStopToken(req, s.token)) {
+            emit_tokens(e.stop_handler->Finish(), e.next_callback_token_pos);
+            finish = "stop";
+            break;
+          }
+          emit_tokens(e.stop_handler->Put(s.token), e.next_callback_token_pos);
+          if (e.stop_handler->stop_triggered()) {
+            finish = "stop";
+            break;
+          }
+          if (e.grammar_handle >= 0 && grammar_ && grammar_->IsTerminated(e.grammar_handle)) {
+            emit_tokens(e.stop_handler->Finish(), e.next_callback_token_pos);
+            finish = "stop";
+            break;
+          }
+          if (req.cfg.max_tokens >= 0 && e.next_callback_token_pos >= req.cfg.max_tokens) {
+            emit_tokens(e.stop_handler->Finish(), e.next_callback_token_pos);
+            finish = "length";
+            break;
+          }
+          if (req.prompt_tokens + e.next_callback_token_pos >= cfg_.max_single_sequence_length) {
+            emit_tokens(e.stop_handler->Finish(), e.next_callback_token_pos);
+            finish = "length";
+            break;
+          }
+        }
+        // tokens sampled beyond a finish point (speculative decoding) are dropped
+        if (!finish.empty() && e.next_callback_token_pos < static_cast<int64_t>(e.committed_tokens.size())) {
+          const int64_t extra = static_cast<int64_t>(e.committed_tokens.size()) - e.next_callback_token_pos;
+          rs->metrics.completion_tokens -= extra;
+          e.committed_tokens.resize(e.next_callback_token_pos);
+        }
+        if (req.cfg.logprobs) {
+          // logprob entries follow the released tokens one to one (released tokens are a suffix-
+          // delayed view of the committed tokens, so walk backwards from the release point)
+          const int64_t released_total = e.next_callback_token_pos;
+          (void)first_new;
+          int64_t start = released_total - static_cast<int64_t>(delta.size());
+          if (start < 0) start = 0;
+          // find where the delta tokens sit among the committed tokens
+          int64_t pos = e.logprob_cursor;
+          for (int32_t t : delta) {
+            while (pos < static_cast<int64_t>(e.committed_tokens.size()) && e.committed_tokens[pos].token != t) ++pos;
+            if (pos < static_cast<int64_t>(e.committed_tokens.size())) {
+              out.group_delta_logprob_json_strs[g].push_back(LogprobJSON(tok_.get(), e.committed_tokens[pos]));
+              ++pos;
+            }
+          }
+          e.logprob_cursor = pos;
+        }
+        // feed the prefix cache with tokens whose KV now exists (all committed but the last)
+        {
+          ModelState& ms = e.mstates[0];
+          const int64_t with_kv = static_cast<int64_t>(e.committed_tokens.size()) - 1;
+          if (prefix_cache_.HasSequence(ms.internal_id) && with_kv > ms.cached_committed_tokens && finish.empty()) {
+            std::vector<int32_t> toks;
+            for (int64_t j = ms.cached_committed_tokens; j < with_kv; ++j) toks.push_back(e.committed_tokens[j].token);
+            prefix_cache_.ExtendSequence(ms.internal_id, toks);
+            ms.cached_committed_tokens = with_kv;
+          }
+        }
+        if (!delta.empty()) any = true;
+        if (!finish.empty()) {
+          any = true;
+          out.group_finish_reason[g] = finish;
+          FinishEntry(rs, e, finish);
+          // the KV may hold tokens past the finish point (speculation): trim, then recycle
+          ReleaseEntry(e, /*recycle=*/true);
+        }
+      }
+      if (rs->num_unfinished == 0) {
+        rs->metrics.finish_time = now;
+        if (!rs->prefill_done) rs->metrics.prefill_end_time = now;
+        out.request_final_usage_json_str = rs->metrics.AsUsageJSON(true).dump();
+        metrics_.RequestFinishUpdate(rs->metrics);
+        for (auto& e : rs->entries) ReleaseEntry(e, /*recycle=*/true);
+        any = true;
+      }
+      if (any) outs.push_back(std::move(out));
+      if (rs->num_unfinished == 0) {
+        Trace(req.id, "finish");
+        RemoveFromQueues(rs);
+        states_.erase(req.id);
+      }
+    }
+    prefix_cache_.CommitSequenceExtention();
+    touched_.clear();
+    Emit(std::move(outs));
+  }
+
+  EngineConfig cfg_;
+  std::vector<EngineModelInfo> models_;
+  std::shared_ptr<ModelBackend> backend_;
+  std::shared_ptr<const Tokenizer> tok_;
+  std::shared_ptr<GrammarBackend> grammar_;
+  std::shared_ptr<EventTraceRecorder> trace_;
+  StreamCallback callback_;
+  PrefixCache prefix_cache_;
+  std::vector<std::unique_ptr<KVManager>> kv_;
+  GenerationConfig default_gen_;
+  std::unordered_map<std::string, std::unique_ptr<RequestState>> states_;
+  std::vector<RequestState*> running_, waiting_, touched_;
+  IdManager ids_;
+  SlotManager draft_slots_;
+  EngineMetrics metrics_;
+  std::mt19937_64 seed_rng_;
+  bool spec_ = false;
+  int64_t num_prefill_steps_ = 0, num_decode_steps_ = 0, num_verify_steps_ = 0, num_preemptions_ = 0;
+};
+
+// ====================================================================== mock echo engine
+class MockEchoEngine : public Engine {
+ public:
+  MockEchoEngine(EngineConfig cfg, std::string model_config_json, std::shared_ptr<const Tokenizer> tok,
+                 StreamCallback cb)
+      : cfg_(std::move(cfg)), tok_(std::move(tok)), callback_(std::move(cb)) {
+    if (!model_config_json.empty()) {
+      Value v = json::parse(model_config_json);
+      if (v.is_object()) default_gen_ = GenerationConfig::DefaultsFromModelConfig(v.as_object());
+    }
+    if (cfg_.max_single_sequence_length <= 0) cfg_.max_single_sequence_length = 1 << 20;
+  }
+  void SetStreamCallback(StreamCallback cb) override { callback_ = std::move(cb); }
+  const GenerationConfig& DefaultGenerationConfig() const override { return default_gen_; }
+  const EngineConfig& Config() const override { return cfg_; }
+  bool Empty() const override { return pending_.empty(); }
+  void Reset() override { pending_.clear(); }
+  std::string JSONMetrics() const override { return metrics_.AsJSON().dump(); }
+  void AddRequest(Request r) override {
+    State st;
+    for (auto& in : r.inputs) st.prompt.insert(st.prompt.end(), in.tokens.begin(), in.tokens.end());
+    st.req = std::move(r);
+    st.metrics.prompt_tokens = static_cast<int64_t>(st.prompt.size());
+    st.metrics.add_time = NowSeconds();
+    pending_.push_back(std::move(st));
+  }
+  void AbortRequest(const std::string& id) override {
+    pending_.erase(std::remove_if(pending_.begin(), pending_.end(), [&](const State& s) { return s.req.id == id; }),
+                   pending_.end());
+  }
+  void AbortAllRequests() override { pending_.clear(); }
+  void Step() override {
+    // one token per request per step, so streaming and abort behave like a real engine
+    std::vector<RequestStreamOutput> outs;
+    for (auto& st : pending_) {
+      const int n = st.req.cfg.n;
+      RequestStreamOutput out;
+      out.request_id = st.req.id;
+      out.group_delta_token_ids.resize(n);
+      out.group_delta_logprob_json_strs.resize(n);
+      out.group_finish_reason.assign(n, "");
+      out.group_extra_prefix_string.assign(n, "");
+      const int64_t limit = st.req.cfg.max_tokens >= 0
+                                ? std::min<int64_t>(st.req.cfg.max_tokens, static_cast<int64_t>(st.prompt.size()))
+                                : static_cast<int64_t>(st.prompt.size());
+      if (st.pos == 0) st.metrics.prefill_end_time = NowSeconds();
+      if (st.pos < limit) {
+        for (int g = 0; g < n; ++g) out.group_delta_token_ids[g].push_back(st.prompt[st.pos]);
+        ++st.pos;
+        st.metrics.completion_tokens += 1;
+      }
+      if (st.pos >= limit) {
+        const bool by_len = st.req.cfg.max_tokens >= 0 && st.req.cfg.max_tokens <= static_cast<int64_t>(st.prompt.size());
+        out.group_finish_reason.assign(n, by_len ? "length" : "stop");
+        st.metrics.finish_time = NowSeconds();
+        st.metrics.prefill_tokens = st.metrics.prompt_tokens;
+        st.metrics.decode_tokens = st.metrics.completion_tokens;
+        Value usage = st.metrics.AsUsageJSON(true);
+        // the echo engine reports the parsed generation config for API-plumbing tests
+        usage.as_object()["extra"] = st.req.cfg.AsJSON();
+        out.request_final_usage_json_str = usage.dump();
+        metrics_.RequestFinishUpdate(st.metrics);
+        st.done = true;
+      }
+      outs.push_back(std::move(out));
+    }
+    pending_.erase(std::remove_if(pending_.begin(), pending_.end(), [](const State& s) { return s.done; }),
+                   pending_.end());
+    if (callback_ && !outs.empty()) callback_(std::move(outs));
+  }
+
+ private:
+  struct State {
+    Request req;
+    std::vector<int32_t> prompt;
+    int64_t pos = 0;
+    bool done = false;
+    RequestMetrics metrics;
+  };
+  EngineConfig cfg_;
+  std::shared_ptr<const Tokenizer> tok_;
+  StreamCallback callback_;
+  GenerationConfig default_gen_;
+  std::vector<State> pending_;
+  EngineMetrics metrics_;
+};
+
+}  // namespace
+
+std::unique_ptr<Engine> Engine::Create(EngineConfig config, std::vector<EngineModelInfo> models,
+                                       std::shared_ptr<ModelBackend> backend,
+                                       std::shared_ptr<const Tokenizer> tokenizer,
+                                       std::shared_ptr<GrammarBackend> grammar,
+                                       std::shared_ptr<EventTraceRecorder> trace, StreamCallback callback) {
+  return std::make_unique<EngineImpl>(std::move(config), std::move(models), std::move(backend),
+                                      std::move(tokenizer), std::move(grammar), std::move(trace),
+                                      std::move(callback));
+}
+
+std::unique_ptr<Engine> Engine::CreateMockEcho(EngineConfig config, std::string model_config_json,
+                                               std::shared_ptr<const Tokenizer> tokenizer,
+                                               StreamCallback callback) {
+  return std::make_unique<MockEchoEngine>(std::move(config), std::move(model_config_json),
+                                          std::move(tokenizer), std::move(callback));
+}
+
+}  // namespace mlcb

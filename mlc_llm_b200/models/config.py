@@ -1,0 +1,332 @@
+"""Normalised architecture description shared by every decoder family.
+
+Each supported ``model_type`` maps its HuggingFace / mlc-chat-config fields onto one
+``ModelConfig``; the generic decoder in ``models/transformer.py`` is driven entirely by it.
+Reference: the per-family config classes under ``python/mlc_llm/model/*/`` (canonical one:
+``model/llama/llama_model.py:24-103``) and the registry ``model/model.py:134+``.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Any, Dict, List, Optional
+
+
+@dataclasses.dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 0
+    head_dim: int = 0
+    vocab_size: int = 32000
+    rms_norm_eps: float = 1e-5
+    # positions
+    position_embedding: str = "rope"  # "rope" | "learned" | "none"
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[Dict[str, Any]] = None
+    partial_rotary_factor: float = 1.0
+    max_position_embeddings: int = 0
+    # sizes the runtime cares about
+    context_window_size: int = 0
+    prefill_chunk_size: int = 0
+    sliding_window_size: int = -1
+    attention_sink_size: int = -1
+    tensor_parallel_shards: int = 1
+    pipeline_parallel_stages: int = 1
+    max_batch_size: int = 128
+    # structure switches
+    norm_type: str = "rms"              # "rms" | "layernorm"
+    norm_weight_offset: float = 0.0     # gemma stores (w - 1)
+    hidden_act: str = "silu"            # "silu" | "gelu_tanh" | "gelu" | "relu2"
+    gated_mlp: bool = True
+    attention_bias: bool = False        # bias on q/k/v
+    attention_out_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False               # per-head RMSNorm on q and k (qwen3, olmo2, gemma3)
+    tie_word_embeddings: bool = False
+    embedding_scale: float = 1.0        # gemma multiplies embeddings by sqrt(hidden)
+    parallel_residual: bool = False     # gpt-neox / phi-2 style x + attn(ln(x)) + mlp(ln(x))
+    shared_input_norm: bool = False     # with parallel_residual: one norm feeds both branches
+    post_attention_norm: bool = False   # gemma2/3: extra norms after attention and after the MLP
+    post_mlp_norm: bool = False
+    query_pre_attn_scalar: float = 0.0  # gemma2: sm_scale = this ** -0.5
+    attn_logit_softcap: float = 0.0
+    final_logit_softcap: float = 0.0
+    layer_attn_kinds: Optional[List[str]] = None  # per-layer "mha" | "mha_sliding"
+    rope_local_theta: float = 0.0       # gemma3: theta of sliding layers
+    lm_head_bias: bool = False
+    # mixture of experts
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    moe_router: str = "topk_softmax"    # "topk_softmax" (mixtral) | "softmax_topk" (qwen-moe)
+    shared_expert_intermediate_size: int = 0
+    shared_expert_gate: bool = False
+    moe_layer_freq: int = 1
+    first_moe_layer: int = 0
+    expert_parallel: bool = False       # shard experts across ranks instead of their width
+    extra: Dict[str, Any] = dataclasses.field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.num_key_value_heads <= 0:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim <= 0:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.context_window_size <= 0:
+            self.context_window_size = self.max_position_embeddings or 8192
+        if self.prefill_chunk_size <= 0:
+            self.prefill_chunk_size = min(self.context_window_size, 8192)
+        if self.moe_intermediate_size <= 0 and self.num_experts > 0:
+            self.moe_intermediate_size = self.intermediate_size
+
+    @property
+    def rotary_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return r - (r % 2)
+
+    def is_moe_layer(self, layer: int) -> bool:
+        return (self.num_experts > 0 and layer >= self.first_moe_layer
+                and (layer + 1) % max(1, self.moe_layer_freq) == 0)
+
+    def kv_cache_metadata(self) -> Dict[str, int]:
+        tp = max(1, self.tensor_parallel_shards)
+        return {"num_hidden_layers": self.num_hidden_layers,
+                "num_attention_heads": self.num_attention_heads // tp,
+                "num_key_value_heads": max(1, self.num_key_value_heads // tp),
+                "head_dim": self.head_dim}
+
+    def asdict(self) -> Dict[str, Any]:
+        d = dataclasses.asdict(self)
+        d.pop("extra")
+        return d
+
+
+def _get(cfg: Dict[str, Any], *names, default=None):
+    for n in names:
+        if n in cfg and cfg[n] is not None:
+            return cfg[n]
+    return default
+
+
+def _common(cfg: Dict[str, Any], model_type: str) -> Dict[str, Any]:
+    """Fields spelled the same way by most HuggingFace configs."""
+    out = dict(
+        model_type=model_type,
+        hidden_size=_get(cfg, "hidden_size", "n_embd", "d_model", default=4096),
+        intermediate_size=_get(cfg, "intermediate_size", "n_inner", "ffn_dim", default=0) or 0,
+        num_hidden_layers=_get(cfg, "num_hidden_layers", "n_layer", "num_layers", default=32),
+        num_attention_heads=_get(cfg, "num_attention_heads", "n_head", default=32),
+        num_key_value_heads=_get(cfg, "num_key_value_heads", "num_kv_heads", default=0) or 0,
+        head_dim=_get(cfg, "head_dim", default=0) or 0,
+        vocab_size=_get(cfg, "vocab_size", default=32000),
+        rms_norm_eps=_get(cfg, "rms_norm_eps", "layer_norm_eps", "layer_norm_epsilon", "norm_eps",
+                          "norm_epsilon", default=1e-5),
+        rope_theta=float(_get(cfg, "rope_theta", "position_embedding_base", "rotary_emb_base",
+                              default=10000.0)),
+        rope_scaling=_get(cfg, "rope_scaling"),
+        max_position_embeddings=_get(cfg, "max_position_embeddings", "n_positions",
+                                     "max_sequence_length", default=0) or 0,
+        context_window_size=_get(cfg, "context_window_size", default=0) or 0,
+        prefill_chunk_size=_get(cfg, "prefill_chunk_size", default=0) or 0,
+        sliding_window_size=_get(cfg, "sliding_window_size", default=-1),
+        attention_sink_size=_get(cfg, "attention_sink_size", default=-1),
+        tensor_parallel_shards=_get(cfg, "tensor_parallel_shards", default=1),
+        pipeline_parallel_stages=_get(cfg, "pipeline_parallel_stages", default=1),
+        max_batch_size=_get(cfg, "max_batch_size", default=128),
+        tie_word_embeddings=bool(_get(cfg, "tie_word_embeddings", default=False)),
+    )
+    if out["intermediate_size"] == 0:
+        out["intermediate_size"] = 4 * out["hidden_size"]
+    return out
+
+
+def _llama(cfg, mt):
+    d = _common(cfg, mt)
+    d["attention_bias"] = bool(_get(cfg, "attention_bias", default=False))
+    d["attention_out_bias"] = d["attention_bias"]
+    d["mlp_bias"] = bool(_get(cfg, "mlp_bias", default=False))
+    return d
+
+
+def _mistral(cfg, mt):
+    d = _common(cfg, mt)
+    sw = _get(cfg, "sliding_window")
+    if sw and d["sliding_window_size"] in (-1, None) and not d["context_window_size"]:
+        d["sliding_window_size"] = int(sw)
+        d["attention_sink_size"] = max(0, d["attention_sink_size"] or 0) if d["attention_sink_size"] != -1 else 4
+        d["context_window_size"] = -1 if False else 0
+    return d
+
+
+def _qwen2(cfg, mt):
+    d = _common(cfg, mt)
+    d["attention_bias"] = True
+    return d
+
+
+def _qwen3(cfg, mt):
+    d = _common(cfg, mt)
+    d["attention_bias"] = bool(_get(cfg, "attention_bias", default=False))
+    d["qk_norm"] = True
+    return d
+
+
+def _gemma(cfg, mt):
+    d = _common(cfg, mt)
+    d["norm_weight_offset"] = 1.0
+    d["hidden_act"] = "gelu_tanh"
+    d["embedding_scale"] = math.sqrt(d["hidden_size"])
+    d["tie_word_embeddings"] = True
+    if mt in ("gemma2", "gemma3", "gemma3_text"):
+        d["post_attention_norm"] = True
+        d["post_mlp_norm"] = True
+        d["query_pre_attn_scalar"] = float(_get(cfg, "query_pre_attn_scalar", default=0) or 0)
+        d["attn_logit_softcap"] = float(_get(cfg, "attn_logit_softcapping", default=0) or 0)
+        d["final_logit_softcap"] = float(_get(cfg, "final_logit_softcapping", default=0) or 0)
+        sw = _get(cfg, "sliding_window", default=4096)
+        n = d["num_hidden_layers"]
+        if mt == "gemma2":
+            d["layer_attn_kinds"] = ["mha_sliding" if i % 2 == 0 else "mha" for i in range(n)]
+        else:
+            pat = _get(cfg, "sliding_window_pattern", default=6)
+            d["layer_attn_kinds"] = ["mha" if (i + 1) % pat == 0 else "mha_sliding" for i in range(n)]
+            d["qk_norm"] = True
+            d["rope_local_theta"] = float(_get(cfg, "rope_local_base_freq", default=10000.0))
+        d["extra"] = {"layer_sliding_window": int(sw)}
+    return d
+
+
+def _phi3(cfg, mt):
+    d = _common(cfg, mt)
+    return d
+
+
+def _phi(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
+             attention_out_bias=True, mlp_bias=True, parallel_residual=True, shared_input_norm=True,
+             partial_rotary_factor=float(_get(cfg, "partial_rotary_factor", default=0.4)),
+             lm_head_bias=True)
+    return d
+
+
+def _gpt_neox(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", hidden_act="gelu", gated_mlp=False, attention_bias=True,
+             attention_out_bias=True, mlp_bias=True,
+             parallel_residual=bool(_get(cfg, "use_parallel_residual", default=True)),
+             partial_rotary_factor=float(_get(cfg, "rotary_pct", default=0.25)))
+    return d
+
+
+def _gpt2(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
+             attention_out_bias=True, mlp_bias=True, position_embedding="learned",
+             tie_word_embeddings=True)
+    if mt == "gpt_bigcode":
+        d["num_key_value_heads"] = 1 if _get(cfg, "multi_query", default=True) else 0
+    return d
+
+
+def _starcoder2(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
+             attention_out_bias=True, mlp_bias=True)
+    return d
+
+
+def _stablelm(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", attention_bias=bool(_get(cfg, "use_qkv_bias", default=False)),
+             partial_rotary_factor=float(_get(cfg, "partial_rotary_factor", "rope_pct", default=0.25)))
+    return d
+
+
+def _olmo(cfg, mt):
+    d = _common(cfg, mt)
+    if mt == "olmo2":
+        d["qk_norm"] = True
+        d["post_attention_norm"] = True
+        d["post_mlp_norm"] = True
+        d["extra"] = {"no_pre_norm": True}
+    else:
+        d["norm_type"] = "layernorm"
+        d["extra"] = {"norm_no_affine": True}
+    return d
+
+
+def _mixtral(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(num_experts=_get(cfg, "num_local_experts", "num_experts", default=8),
+             num_experts_per_tok=_get(cfg, "num_experts_per_tok", default=2),
+             moe_router="topk_softmax", expert_parallel=bool(_get(cfg, "expert_parallel", default=False)))
+    d["moe_intermediate_size"] = d["intermediate_size"]
+    return d
+
+
+def _qwen_moe(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(num_experts=_get(cfg, "num_experts", default=60),
+             num_experts_per_tok=_get(cfg, "num_experts_per_tok", default=4),
+             moe_intermediate_size=_get(cfg, "moe_intermediate_size", default=1408),
+             norm_topk_prob=bool(_get(cfg, "norm_topk_prob", default=False)),
+             moe_router="softmax_topk",
+             shared_expert_intermediate_size=_get(cfg, "shared_expert_intermediate_size", default=0) or 0,
+             moe_layer_freq=_get(cfg, "decoder_sparse_step", default=1),
+             expert_parallel=bool(_get(cfg, "expert_parallel", default=False)))
+    if mt == "qwen2_moe":
+        d["attention_bias"] = True
+        d["shared_expert_gate"] = True
+    else:
+        d["qk_norm"] = True
+    return d
+
+
+def _nemotron(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", norm_weight_offset=1.0, hidden_act="relu2", gated_mlp=False,
+             partial_rotary_factor=float(_get(cfg, "partial_rotary_factor", "rope_percent", default=0.5)))
+    return d
+
+
+def _cohere(cfg, mt):
+    d = _common(cfg, mt)
+    d.update(norm_type="layernorm", parallel_residual=True, shared_input_norm=True,
+             tie_word_embeddings=True)
+    d["extra"] = {"logit_scale": float(_get(cfg, "logit_scale", default=0.0625)), "norm_no_bias": True}
+    return d
+
+
+_PARSERS = {
+    "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
+    "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
+    "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2,
+    "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
+    "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
+    "internlm": _llama, "internlm2": _llama, "baichuan": _llama, "orion": _llama, "minicpm": _llama,
+    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _llama, "aquila": _llama,
+    "yi": _llama, "tinyllama": _llama,
+}
+
+SUPPORTED_MODEL_TYPES = sorted(_PARSERS)
+
+
+def from_dict(model_type: str, cfg: Dict[str, Any]) -> ModelConfig:
+    """Build a ``ModelConfig`` from a HuggingFace ``config.json`` dict or from the ``model_config``
+    section of ``mlc-chat-config.json`` (both spellings of every field are accepted)."""
+    mt = model_type.replace("-", "_") if model_type not in _PARSERS else model_type
+    if mt not in _PARSERS:
+        raise ValueError(f"Unknown model type {model_type!r}; supported: {SUPPORTED_MODEL_TYPES}")
+    fields = _PARSERS[mt](cfg, mt)
+    known = {f.name for f in dataclasses.fields(ModelConfig)}
+    # explicit structural overrides present in the dict win (round trip of our own asdict())
+    for k, v in cfg.items():
+        if k in known and k not in ("model_type", "extra") and v is not None and k not in fields:
+            fields[k] = v
+    return ModelConfig(**{k: v for k, v in fields.items() if k in known})

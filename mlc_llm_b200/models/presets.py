@@ -1,0 +1,101 @@
+"""Named architecture presets (HuggingFace-style config dicts) used by ``gen_config`` and by the
+random-weight benchmark / test models (reference: ``python/mlc_llm/model/model_preset.py``)."""
+
+MODEL_PRESETS = {
+    # 2-layer model for CPU plumbing tests
+    "tiny-llama": {
+        "model_type": "llama", "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048,
+    },
+    # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
+    "tiny-llama-gpu": {
+        "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+    },
+    "llama-3-8b": {
+        "model_type": "llama", "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+        "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 8192,
+    },
+    "llama-3-70b": {
+        "model_type": "llama", "hidden_size": 8192, "intermediate_size": 28672, "num_hidden_layers": 80,
+        "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+        "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 8192,
+    },
+    # 2-layer Llama-3-shaped draft model for speculative decoding
+    "llama-3-draft-2l": {
+        "model_type": "llama", "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 2,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+        "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 8192,
+    },
+    "llama-2-7b": {
+        "model_type": "llama", "hidden_size": 4096, "intermediate_size": 11008, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 32, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 4096,
+    },
+    "mistral-7b": {
+        "model_type": "mistral", "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "vocab_size": 32000, "rms_norm_eps": 1e-5,
+        "rope_theta": 10000.0, "max_position_embeddings": 32768, "sliding_window": 4096,
+    },
+    "mixtral-8x7b": {
+        "model_type": "mixtral", "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "vocab_size": 32000, "rms_norm_eps": 1e-5,
+        "rope_theta": 1000000.0, "max_position_embeddings": 32768, "num_local_experts": 8,
+        "num_experts_per_tok": 2,
+    },
+    "tiny-mixtral": {
+        "model_type": "mixtral", "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048,
+        "num_local_experts": 4, "num_experts_per_tok": 2,
+    },
+    "qwen2-7b": {
+        "model_type": "qwen2", "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
+        "num_attention_heads": 28, "num_key_value_heads": 4, "vocab_size": 152064, "rms_norm_eps": 1e-6,
+        "rope_theta": 1000000.0, "max_position_embeddings": 32768,
+    },
+    "qwen3-8b": {
+        "model_type": "qwen3", "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 36,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 151936,
+        "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 40960,
+    },
+    "gemma-2b": {
+        "model_type": "gemma", "hidden_size": 2048, "intermediate_size": 16384, "num_hidden_layers": 18,
+        "num_attention_heads": 8, "num_key_value_heads": 1, "head_dim": 256, "vocab_size": 256000,
+        "rms_norm_eps": 1e-6, "max_position_embeddings": 8192,
+    },
+    "gemma2-9b": {
+        "model_type": "gemma2", "hidden_size": 3584, "intermediate_size": 14336, "num_hidden_layers": 42,
+        "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 256, "vocab_size": 256000,
+        "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "query_pre_attn_scalar": 256,
+        "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "sliding_window": 4096,
+    },
+    "phi-3-mini": {
+        "model_type": "phi3", "hidden_size": 3072, "intermediate_size": 8192, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 32, "vocab_size": 32064, "rms_norm_eps": 1e-5,
+        "max_position_embeddings": 4096,
+    },
+    "phi-2": {
+        "model_type": "phi", "hidden_size": 2560, "intermediate_size": 10240, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "vocab_size": 51200, "layer_norm_eps": 1e-5,
+        "max_position_embeddings": 2048, "partial_rotary_factor": 0.4,
+    },
+    "gpt2": {
+        "model_type": "gpt2", "n_embd": 768, "n_layer": 12, "n_head": 12, "vocab_size": 50257,
+        "layer_norm_epsilon": 1e-5, "n_positions": 1024,
+    },
+    "gpt-neox-pythia-1b": {
+        "model_type": "gpt_neox", "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+        "num_attention_heads": 8, "vocab_size": 50304, "layer_norm_eps": 1e-5,
+        "max_position_embeddings": 2048, "rotary_pct": 0.25, "use_parallel_residual": True,
+    },
+    "qwen2-moe-a2.7b": {
+        "model_type": "qwen2_moe", "hidden_size": 2048, "intermediate_size": 5632, "num_hidden_layers": 24,
+        "num_attention_heads": 16, "num_key_value_heads": 16, "vocab_size": 151936, "rms_norm_eps": 1e-6,
+        "num_experts": 60, "num_experts_per_tok": 4, "moe_intermediate_size": 1408,
+        "shared_expert_intermediate_size": 5632, "max_position_embeddings": 8192,
+    },
+}

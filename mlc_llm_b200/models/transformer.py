@@ -1,0 +1,377 @@
+"""Config-driven decoder-only transformer over the paged KV cache.
+
+One implementation serves every dense and mixture-of-experts family in ``models/config.py``; the
+per-family differences (norm type, biases, qk-norm, partial rotary, gated vs plain MLP, parallel
+residual, post-norms, soft-capping, sliding layers, MoE routing) are switches of ``ModelConfig``.
+All heavy math goes through ``mlc_llm_b200.ops`` (sm_100a kernels on GPU, fp32 PyTorch on CPU).
+
+Reference: the Relax modules of ``python/mlc_llm/model/llama/llama_model.py:106-423`` (layer math,
+tensor-parallel sharding, batch_prefill / batch_decode / batch_verify entry points) and
+``model/mixtral/mixtral_model.py:64-168`` (MoE block).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .. import quantization as Q
+from ..ops import LinearWeight
+from .config import ModelConfig
+
+
+@dataclasses.dataclass
+class BatchInfo:
+    """Device-resident index arrays of one forward call (built from the KV manager's plan)."""
+
+    positions: torch.Tensor
+    slots: torch.Tensor
+    q_seq: torch.Tensor
+    q_kvlen: torch.Tensor
+    page_indptr: torch.Tensor
+    page_indices: torch.Tensor
+    q_kvstart: Optional[torch.Tensor] = None
+    tree_mask: Optional[torch.Tensor] = None
+    attn_plan: object = None  # tensor-core attention schedule (GPU only)
+    num_tokens: int = 0
+
+
+class ParamStore:
+    """Named parameters in their run-time form (dense tensors and ``LinearWeight`` objects)."""
+
+    def __init__(self):
+        self.tensors: Dict[str, torch.Tensor] = {}
+        self.linears: Dict[str, LinearWeight] = {}
+
+    def nbytes(self) -> int:
+        total = sum(t.numel() * t.element_size() for t in self.tensors.values())
+        for lw in self.linears.values():
+            total += lw.w.numel() * lw.w.element_size()
+            if lw.scale is not None:
+                total += lw.scale.numel() * lw.scale.element_size()
+            if lw.bias is not None:
+                total += lw.bias.numel() * lw.bias.element_size()
+        return total
+
+
+class DecoderModel:
+    """A (tensor-parallel shard of a) decoder model plus its paged KV cache."""
+
+    def __init__(self, config: ModelConfig, quant: Q.Quantization, params: ParamStore,
+                 device: torch.device, comm=None, layer_range: Optional[range] = None):
+        self.cfg = config
+        self.quant = quant
+        self.p = params
+        self.device = device
+        self.comm = comm  # tensor-parallel communicator (None when world == 1)
+        self.tp = comm.world_size if comm is not None else 1
+        self.dtype = quant.torch_dtype
+        self.hq = config.num_attention_heads // self.tp
+        self.hkv = max(1, config.num_key_value_heads // self.tp)
+        self.d = config.head_dim
+        self.layers = layer_range if layer_range is not None else range(config.num_hidden_layers)
+        self.first_stage = self.layers.start == 0
+        self.last_stage = self.layers.stop == config.num_hidden_layers
+        self.kv_pages: Optional[torch.Tensor] = None
+        self.page = 16
+        self.sm_scale = (config.query_pre_attn_scalar ** -0.5 if config.query_pre_attn_scalar > 0
+                         else self.d ** -0.5)
+        self.inv_freq = None
+        self.inv_freq_local = None
+        if config.position_embedding == "rope":
+            self.inv_freq = ops.reference.rope_inv_freq(config.rotary_dim, config.rope_theta,
+                                                        config.rope_scaling).to(device)
+            if config.rope_local_theta > 0:
+                self.inv_freq_local = ops.reference.rope_inv_freq(
+                    config.rotary_dim, config.rope_local_theta, None).to(device)
+
+    # ------------------------------------------------------------------ KV cache
+    def create_kv_cache(self, num_pages: int, page_size: int = 16) -> None:
+        self.page = page_size
+        n = len(self.layers)
+        self.kv_pages = torch.zeros(n, num_pages, 2, self.hkv, page_size, self.d, dtype=self.kv_dtype,
+                                    device=self.device)
+
+    @property
+    def kv_dtype(self) -> torch.dtype:
+        return self.dtype if self.dtype != torch.float32 or self.device.type == "cpu" else torch.float16
+
+    def kv_bytes_per_token(self) -> int:
+        return 2 * self.hkv * self.d * len(self.layers) * (2 if self.kv_dtype != torch.float32 else 4)
+
+    def copy_pages(self, pairs: torch.Tensor) -> None:
+        """(src, dst) page copies for copy-on-write, applied to every layer."""
+        if pairs.numel() == 0:
+            return
+        src, dst = pairs[0::2].long(), pairs[1::2].long()
+        self.kv_pages[:, dst] = self.kv_pages[:, src]
+
+    def move_tokens(self, moves: torch.Tensor) -> None:
+        """(src_slot, dst_slot) token moves (tree commit), applied to every layer."""
+        if moves.numel() == 0:
+            return
+        src, dst = moves[0::2].long(), moves[1::2].long()
+        sp, so = src // self.page, src % self.page
+        dp, do = dst // self.page, dst % self.page
+        self.kv_pages[:, dp, :, :, do, :] = self.kv_pages[:, sp, :, :, so, :]
+
+    # ------------------------------------------------------------------ pieces
+    def _norm(self, x, name, eps=None):
+        c = self.cfg
+        w = self.p.tensors.get(name + ".weight")
+        if c.norm_type == "layernorm":
+            b = self.p.tensors.get(name + ".bias")
+            if w is None:
+                w = torch.ones(x.shape[-1], dtype=x.dtype, device=x.device)
+            return ops.reference.layernorm(x, w, b, c.rms_norm_eps)
+        return ops.rmsnorm(x, w, c.rms_norm_eps, c.norm_weight_offset)
+
+    def _add_norm(self, delta, residual, name):
+        """residual += delta; returns norm(residual)."""
+        c = self.cfg
+        if c.norm_type == "rms":
+            return ops.add_rmsnorm(delta, residual, self.p.tensors[name + ".weight"], c.rms_norm_eps,
+                                   c.norm_weight_offset)
+        residual.add_(delta)
+        return self._norm(residual, name)
+
+    def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        table = self.p.linears.get("model.embed_tokens") or self.p.tensors["model.embed_tokens.weight"]
+        x = ops.embed(token_ids, table, c.hidden_size, self.dtype, c.embedding_scale)
+        if c.position_embedding == "learned":
+            raise RuntimeError("learned positions are added in forward() where positions are known")
+        return x
+
+    def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        c = self.cfg
+        pre = f"model.layers.{li}.self_attn."
+        qkv = ops.linear(h, self.p.linears[pre + "qkv_proj"])
+        hq, hkv, d = self.hq, self.hkv, self.d
+        if c.qk_norm:
+            t = qkv.shape[0]
+            heads = qkv.view(t, hq + 2 * hkv, d)
+            qn = ops.rmsnorm(heads[:, :hq].reshape(-1, d), self.p.tensors[pre + "q_norm.weight"],
+                             c.rms_norm_eps, c.norm_weight_offset)
+            kn = ops.rmsnorm(heads[:, hq:hq + hkv].reshape(-1, d), self.p.tensors[pre + "k_norm.weight"],
+                             c.rms_norm_eps, c.norm_weight_offset)
+            heads[:, :hq] = qn.view(t, hq, d)
+            heads[:, hq:hq + hkv] = kn.view(t, hkv, d)
+        sliding = c.layer_attn_kinds is not None and c.layer_attn_kinds[li] == "mha_sliding"
+        inv = self.inv_freq_local if (sliding and self.inv_freq_local is not None) else self.inv_freq
+        local = li - self.layers.start
+        ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, inv, hq, hkv, d,
+                        c.rotary_dim if inv is not None else 0, self.page)
+        kvstart = b.q_kvstart
+        if sliding:
+            w = int(c.extra.get("layer_sliding_window", 4096))
+            kvstart = torch.clamp(b.q_kvlen - w, min=0).to(torch.int32)
+        out = ops.paged_attention(qkv[:, : hq * d], self.kv_pages[local], b.q_seq, b.q_kvlen, b.page_indptr,
+                                  b.page_indices, hq, hkv, d, self.page, self.sm_scale, q_kvstart=kvstart,
+                                  sink=max(0, c.attention_sink_size) if kvstart is not None and not sliding else 0,
+                                  tree_mask=b.tree_mask, softcap=c.attn_logit_softcap, plan=b.attn_plan)
+        o = ops.linear(out, self.p.linears[pre + "o_proj"])
+        return o
+
+    def _mlp(self, li: int, h: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        if c.is_moe_layer(li):
+            from .moe import moe_block  # pylint: disable=import-outside-toplevel
+
+            return moe_block(self, li, h)
+        pre = f"model.layers.{li}.mlp."
+        if c.gated_mlp:
+            g = ops.linear(h, self.p.linears[pre + "gate_up_proj"])
+            a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
+        else:
+            u = ops.linear(h, self.p.linears[pre + "up_proj"])
+            if c.hidden_act == "relu2":
+                a = torch.relu(u) ** 2
+            elif c.hidden_act == "gelu":
+                a = torch.nn.functional.gelu(u.float()).to(u.dtype)
+            else:
+                a = torch.nn.functional.gelu(u.float(), approximate="tanh").to(u.dtype)
+        return ops.linear(a, self.p.linears[pre + "down_proj"])
+
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.comm is not None and self.tp > 1:
+            self.comm.all_reduce(x)
+        return x
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        """``x``: embeddings (first stage) or the previous stage's hidden state, ``[T, H]``.
+        Returns the residual stream after this stage's layers (final norm NOT applied)."""
+        c = self.cfg
+        if c.position_embedding == "learned" and self.first_stage:
+            x = x + self.p.tensors["model.embed_positions.weight"][b.positions.long()].to(x.dtype)
+        x = x.contiguous()
+        no_pre_norm = bool(c.extra.get("no_pre_norm"))
+        pending = None  # branch output not yet added to the residual stream
+        for li in self.layers:
+            pre = f"model.layers.{li}."
+            if c.parallel_residual:
+                if pending is not None:
+                    x = x + pending
+                    pending = None
+                h1 = self._norm(x, pre + "input_layernorm")
+                h2 = h1 if c.shared_input_norm else self._norm(x, pre + "post_attention_layernorm")
+                attn = self._attention(li, h1, b)
+                mlp = self._mlp(li, h2)
+                pending = self._reduce(attn + mlp)
+                continue
+            # ---- attention block
+            if no_pre_norm:
+                if pending is not None:
+                    x = x + pending
+                    pending = None
+                h = x
+            elif pending is None:
+                h = self._norm(x, pre + "input_layernorm")
+            else:
+                h = self._add_norm(pending, x, pre + "input_layernorm")
+                pending = None
+            attn = self._reduce(self._attention(li, h, b))
+            if c.post_attention_norm:
+                attn = self._norm(attn, pre + ("post_attention_layernorm" if (c.post_mlp_norm)
+                                               else "post_attention_norm"))
+            # ---- MLP block
+            if no_pre_norm:
+                x = x + attn
+                h = x
+            else:
+                mlp_norm = "pre_feedforward_layernorm" if (c.post_attention_norm and not no_pre_norm) \
+                    else "post_attention_layernorm"
+                h = self._add_norm(attn, x, pre + mlp_norm)
+            mlp = self._reduce(self._mlp(li, h))
+            if c.post_mlp_norm:
+                mlp = self._norm(mlp, pre + "post_feedforward_layernorm")
+            pending = mlp
+        if pending is not None:
+            if self.last_stage and c.norm_type == "rms" and not no_pre_norm:
+                self._final_normed = self._add_norm(pending, x, "model.norm")
+                return x
+            x = x + pending
+        self._final_normed = None
+        return x
+
+    def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor]) -> torch.Tensor:
+        """Final norm + lm_head on the selected rows of the residual stream; fp32 ``[n, V]``."""
+        c = self.cfg
+        normed = getattr(self, "_final_normed", None)
+        if normed is None:
+            src = hidden if rows is None else ops.row_gather(hidden, rows)
+            h = self._norm(src, "model.norm")
+        else:
+            h = normed if rows is None else ops.row_gather(normed, rows)
+        self._final_normed = None
+        head = self.p.linears.get("lm_head")
+        if head is None:
+            emb = self.p.linears.get("model.embed_tokens")
+            if emb is not None and emb.kind == "q4" and h.is_cuda and not emb.device_layout:
+                head = self._tied_head = getattr(self, "_tied_head", None) or emb.to(h.device)
+            else:
+                head = emb if emb is not None else ops.dense_weight(self.p.tensors["model.embed_tokens.weight"])
+        lg = ops.linear(h, head, out_dtype=torch.float32)
+        if "logit_scale" in c.extra:
+            lg = lg * c.extra["logit_scale"]
+        if c.final_logit_softcap > 0:
+            lg = torch.tanh(lg / c.final_logit_softcap) * c.final_logit_softcap
+        return lg
+
+
+# ---------------------------------------------------------------------------- parameter creation
+def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
+    """Full (unsharded) parameter shapes in MLC naming: name -> (shape, kind), kind in
+    {"linear", "embedding", "norm", "bias", "experts", "router", "pos"}."""
+    h, inter = cfg.hidden_size, cfg.intermediate_size
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    specs: Dict[str, tuple] = {"model.embed_tokens.weight": ((cfg.vocab_size, h), "embedding")}
+    if cfg.position_embedding == "learned":
+        specs["model.embed_positions.weight"] = ((cfg.context_window_size, h), "pos")
+    ln = cfg.norm_type == "layernorm" and not cfg.extra.get("norm_no_affine")
+    ln_bias = ln and not cfg.extra.get("norm_no_bias")
+
+    def norm(name, dim=h):
+        if cfg.norm_type == "rms" or ln:
+            specs[name + ".weight"] = ((dim,), "norm")
+        if ln_bias:
+            specs[name + ".bias"] = ((dim,), "bias")
+
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        if not cfg.extra.get("no_pre_norm"):
+            norm(p + "input_layernorm")
+        specs[p + "self_attn.qkv_proj.weight"] = (((hq + 2 * hkv) * d, h), "linear")
+        if cfg.attention_bias:
+            specs[p + "self_attn.qkv_proj.bias"] = (((hq + 2 * hkv) * d,), "bias")
+        specs[p + "self_attn.o_proj.weight"] = ((h, hq * d), "linear")
+        if cfg.attention_out_bias:
+            specs[p + "self_attn.o_proj.bias"] = ((h,), "bias")
+        if cfg.qk_norm:
+            specs[p + "self_attn.q_norm.weight"] = ((d,), "norm")
+            specs[p + "self_attn.k_norm.weight"] = ((d,), "norm")
+        if not (cfg.parallel_residual and cfg.shared_input_norm):
+            norm(p + "post_attention_layernorm")
+        if cfg.post_attention_norm and not cfg.extra.get("no_pre_norm"):
+            norm(p + "pre_feedforward_layernorm")
+        if cfg.post_mlp_norm:
+            norm(p + "post_feedforward_layernorm")
+        if cfg.is_moe_layer(i):
+            e, mi = cfg.num_experts, cfg.moe_intermediate_size
+            specs[p + "moe.gate.weight"] = ((e, h), "router")
+            specs[p + "moe.e1_e3.weight"] = ((e, 2 * mi, h), "experts")
+            specs[p + "moe.e2.weight"] = ((e, h, mi), "experts")
+            if cfg.shared_expert_intermediate_size > 0:
+                si = cfg.shared_expert_intermediate_size
+                specs[p + "moe.shared_expert.gate_up_proj.weight"] = ((2 * si, h), "linear")
+                specs[p + "moe.shared_expert.down_proj.weight"] = ((h, si), "linear")
+                if cfg.shared_expert_gate:
+                    specs[p + "moe.shared_expert_gate.weight"] = ((1, h), "router")
+        elif cfg.gated_mlp:
+            specs[p + "mlp.gate_up_proj.weight"] = ((2 * inter, h), "linear")
+            specs[p + "mlp.down_proj.weight"] = ((h, inter), "linear")
+            if cfg.mlp_bias:
+                specs[p + "mlp.gate_up_proj.bias"] = ((2 * inter,), "bias")
+                specs[p + "mlp.down_proj.bias"] = ((h,), "bias")
+        else:
+            specs[p + "mlp.up_proj.weight"] = ((inter, h), "linear")
+            specs[p + "mlp.down_proj.weight"] = ((h, inter), "linear")
+            if cfg.mlp_bias:
+                specs[p + "mlp.up_proj.bias"] = ((inter,), "bias")
+                specs[p + "mlp.down_proj.bias"] = ((h,), "bias")
+    norm("model.norm")
+    if not cfg.tie_word_embeddings:
+        specs["lm_head.weight"] = ((cfg.vocab_size, h), "linear")
+        if cfg.lm_head_bias:
+            specs["lm_head.bias"] = ((cfg.vocab_size,), "bias")
+    return specs
+
+
+def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
+    """Row (output-feature) index ranges of `name` kept by `rank`; None = replicated / column-sharded.
+    Follows the reference's ShardSingleDim segments (support/tensor_parallel.py:36-97): qkv_proj is
+    split per segment [q, k, v], gate_up_proj per segment [gate, up]."""
+    d = cfg.head_dim
+    if name.endswith("self_attn.qkv_proj"):
+        segs = [cfg.num_attention_heads * d, cfg.num_key_value_heads * d, cfg.num_key_value_heads * d]
+    elif name.endswith("gate_up_proj"):
+        segs = [full_rows // 2, full_rows // 2]
+    elif name.endswith("mlp.up_proj"):
+        segs = [full_rows]
+    else:
+        return None
+    out, off = [], 0
+    for s in segs:
+        per = s // tp
+        out.append((off + rank * per, off + (rank + 1) * per))
+        off += s
+    return out
+
+
+def column_sharded(name: str) -> bool:
+    return name.endswith("self_attn.o_proj") or name.endswith("down_proj")

@@ -77,6 +77,24 @@ def dense_weight(w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Linear
     return LinearWeight("dense", w, None, bias, None, w.shape[0], w.shape[1])
 
 
+_GEMM_SCRATCH = {}
+GEMM_WORKSPACE_BYTES = 32 << 20
+GEMM_COUNTERS = 4096
+
+
+def _gemm_scratch(device: torch.device):
+    """Split-K scratch of the GEMM kernel: fp32 partial sums plus per-tile arrival counters
+    (zero between launches). One per device; launches on one device are stream-ordered."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    sc = _GEMM_SCRATCH.get(key)
+    if sc is None:
+        ws = torch.empty(GEMM_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        cnt = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
+        sc = (ws, cnt)
+        _GEMM_SCRATCH[key] = sc
+    return (ptr(sc[0]), c_ll(GEMM_WORKSPACE_BYTES), ptr(sc[1]), c_int(GEMM_COUNTERS))
+
+
 def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``y = x @ W^T (+ bias)`` for ``x [..., K]``."""
     lead = x.shape[:-1]
@@ -101,7 +119,8 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
         assert lw.device_layout
         rc = lib().mlcb_gemm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m),
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
-                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
+                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
+                             stream_ptr())
     elif lw.kind == "fp8_block" and x2.dtype == torch.bfloat16 and k % 128 == 0:
         from .fp8 import linear_fp8_block  # pylint: disable=import-outside-toplevel
 
@@ -110,7 +129,8 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
         w = lw.dense(x2.dtype)
         rc = lib().mlcb_gemm(ptr(x2), ptr(w), ptr(None), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
                              c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
-                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
+                             c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
+                             stream_ptr())
     check(rc, f"mlcb_gemm(M={m},N={n},K={k},{lw.kind})")
     return y.reshape(*lead, n)
 

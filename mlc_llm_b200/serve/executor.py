@@ -1,0 +1,316 @@
+"""Model executor: the Python side of the native engine's ``ModelBackend``.
+
+One call per scheduling step: the engine hands over the KV manager's index arrays and the sampling
+parameters as NumPy arrays; the executor packs them into one pinned staging buffer, uploads it with
+a single asynchronous copy (and, under tensor parallelism, one broadcast to the other ranks), runs
+the model, processes logits and samples on the device, and reads back only the sampled tokens.
+
+Reference counterparts: ``cpp/serve/model.cc:245-367,455-534,682-768`` (batch prefill / decode /
+verify wrappers), ``cpp/serve/logit_processor.cc:40-458`` and ``cpp/serve/sampler/gpu_sampler.cc``
+(host-side packing for the logit-processing and sampling kernels).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.transformer import BatchInfo, DecoderModel
+
+_INT_KEYS = ("positions", "slots", "q_seq", "q_kvlen", "q_kvstart", "page_indptr", "page_indices",
+             "page_copies", "q_indptr", "seq_lens", "append_lens")
+_S_INT = ("logit_token_index", "top_k", "pen_row", "pen_token", "pen_count", "bias_row", "bias_token",
+          "mask_rows", "mask_bits", "prob_slots")
+_S_FLT = ("temperature", "top_p", "uniform", "penalties", "bias_value")
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StagingBuffer:
+    """Packs many small int32 / float32 arrays into one pinned buffer -> one H2D copy."""
+
+    def __init__(self, device: torch.device, capacity: int = 1 << 16):
+        self.device = device
+        self.capacity = 0
+        self.host = None
+        self.dev = None
+        self._grow(capacity)
+
+    def _grow(self, n: int) -> None:
+        cap = max(n, self.capacity * 2, 1 << 12)
+        pin = self.device.type == "cuda"
+        self.host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(cap, dtype=torch.int32, device=self.device) if pin else self.host
+        self.capacity = cap
+
+    def upload(self, arrays: Dict[str, np.ndarray]) -> Dict[str, torch.Tensor]:
+        total = sum(_pad4(a.size * (2 if a.dtype.itemsize == 8 else 1)) for a in arrays.values())
+        if total > self.capacity:
+            self._grow(total)
+        off = 0
+        layout = []
+        for name, a in arrays.items():
+            words = a.size * (2 if a.dtype.itemsize == 8 else 1)
+            if words:
+                self.host_np[off:off + words] = a.reshape(-1).view(np.int32)
+            layout.append((name, off, words, a.dtype))
+            off += _pad4(words)
+        if self.dev is not self.host and off:
+            self.dev[:off].copy_(self.host[:off], non_blocking=True)
+        self.last_words = off
+        return self.views(layout)
+
+    def views(self, layout) -> Dict[str, torch.Tensor]:
+        out = {}
+        for name, off, words, dt in layout:
+            t = self.dev[off:off + words]
+            if dt == np.float32:
+                t = t.view(torch.float32)
+            elif dt.itemsize == 8:
+                t = t.view(torch.int64)
+            out[name] = t
+        return out
+
+
+class ModelExecutor:
+    """Runs one or more ``DecoderModel`` (main model, optional draft model) for the engine."""
+
+    def __init__(self, models: List[DecoderModel], device: torch.device, comm=None,
+                 max_draft_slots: int = 0):
+        self.models = models
+        self.device = device
+        self.comm = comm
+        self.staging = StagingBuffer(device)
+        self.vocab = models[0].cfg.vocab_size
+        self.draft_probs: Optional[torch.Tensor] = None
+        self.max_draft_slots = max_draft_slots
+        self.embeddings: Dict[int, torch.Tensor] = {}
+        self._next_embed = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.kernel_launch_estimate = 0
+        self.use_tensor_core_attention = device.type == "cuda"
+
+    # ------------------------------------------------------------------ embeddings (multimodal)
+    def hold_embedding(self, emb: torch.Tensor) -> int:
+        h = self._next_embed
+        self._next_embed += 1
+        self.embeddings[h] = emb.to(self.device)
+        return h
+
+    def release_embedding(self, handle: int) -> None:
+        self.embeddings.pop(int(handle), None)
+
+    def reset(self) -> None:
+        self.embeddings.clear()
+
+    def synchronize(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------ plumbing
+    def _batch_info(self, dev: Dict[str, torch.Tensor], plan: dict, model: DecoderModel) -> BatchInfo:
+        b = BatchInfo(
+            positions=dev["positions"], slots=dev["slots"], q_seq=dev["q_seq"], q_kvlen=dev["q_kvlen"],
+            page_indptr=dev["page_indptr"], page_indices=dev["page_indices"],
+            q_kvstart=dev["q_kvstart"] if dev["q_kvstart"].numel() else None,
+            tree_mask=dev["tree_mask"] if dev["tree_mask"].numel() else None,
+            num_tokens=int(dev["positions"].numel()))
+        if self.use_tensor_core_attention and b.tree_mask is None and b.q_kvstart is None \
+                and model.d == 128 and model.page == 16 and model.cfg.layer_attn_kinds is None \
+                and model.cfg.attn_logit_softcap == 0:
+            from ..ops.attention import make_plan  # pylint: disable=import-outside-toplevel
+
+            b.attn_plan = make_plan(plan, model.hq, model.hkv, self.device)
+        return b
+
+    def _pack(self, plan: dict, token_ids: np.ndarray, sp: Optional[dict]) -> Dict[str, np.ndarray]:
+        arrays: Dict[str, np.ndarray] = {"token_ids": np.ascontiguousarray(token_ids, dtype=np.int32)}
+        for k in _INT_KEYS:
+            arrays[k] = np.ascontiguousarray(plan[k], dtype=np.int32)
+        arrays["tree_mask"] = np.ascontiguousarray(plan["tree_mask"], dtype=np.uint64).view(np.int64)
+        if sp is not None:
+            for k in _S_INT:
+                arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.int32)
+            for k in _S_FLT:
+                arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.float32)
+        return arrays
+
+    def _run_model(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor],
+                   embed_handles: Optional[np.ndarray]) -> torch.Tensor:
+        model = self.models[model_id]
+        if dev["page_copies"].numel():
+            model.copy_pages(dev["page_copies"])
+        b = self._batch_info(dev, plan, model)
+        x = model.embed(dev["token_ids"])
+        if embed_handles is not None:
+            idx = np.nonzero(embed_handles >= 0)[0]
+            tok = np.asarray(dev["token_ids"].cpu())
+            for i in idx:
+                x[i] = self.embeddings[int(embed_handles[i])][int(tok[i])].to(x.dtype)
+        return model.forward(x, b)
+
+    def _process_logits(self, logits: torch.Tensor, dev: Dict[str, torch.Tensor], sp: dict) -> None:
+        n = logits.shape[0]
+        if dev["s_bias_row"].numel():
+            ops.apply_logit_bias(logits, dev["s_bias_row"], dev["s_bias_token"], dev["s_bias_value"])
+        if dev["s_pen_row"].numel():
+            ops.apply_penalty(logits, dev["s_pen_row"], dev["s_pen_token"], dev["s_pen_count"],
+                              dev["s_penalties"].view(n, 3))
+        if dev["s_mask_rows"].numel():
+            words = (logits.shape[1] + 31) // 32
+            ops.apply_bitmask(logits, dev["s_mask_rows"], dev["s_mask_bits"].view(-1, words))
+
+    @staticmethod
+    def _is_plain_greedy(sp: dict) -> bool:
+        return (len(sp["temperature"]) > 0 and float(np.max(sp["temperature"])) < 1e-5
+                and sp["num_top_logprobs"] == 0 and len(sp["pen_row"]) == 0 and len(sp["bias_row"]) == 0
+                and len(sp["mask_rows"]) == 0 and len(sp["prob_slots"]) == 0)
+
+    def _ensure_draft_storage(self, max_slot: int) -> None:
+        need = max(max_slot + 1, self.max_draft_slots)
+        if self.draft_probs is None or self.draft_probs.shape[0] < need:
+            new = torch.zeros(need, self.vocab, dtype=torch.float32, device=self.device)
+            if self.draft_probs is not None:
+                new[: self.draft_probs.shape[0]] = self.draft_probs
+            self.draft_probs = new
+
+    # ------------------------------------------------------------------ backend interface
+    def forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
+                       embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
+        n_rows = len(sp["logit_token_index"])
+        arrays = self._pack(plan, token_ids, sp)
+        if self.comm is not None:
+            self.comm.broadcast_step("forward", model_id, arrays,
+                                     {"num_top_logprobs": int(sp["num_top_logprobs"])})
+        dev = self.staging.upload(arrays)
+        self.h2d_bytes += self.staging.last_words * 4
+        hidden = self._run_model(model_id, plan, dev, embed_handles)
+        if n_rows == 0:
+            return None
+        model = self.models[model_id]
+        logits = model.logits(hidden, dev["s_logit_token_index"])
+        if self._is_plain_greedy(sp):
+            tokens = ops.argmax(logits)
+            tok = tokens.cpu().numpy()
+            self.d2h_bytes += tok.nbytes
+            return {"tokens": tok, "probs": np.ones(n_rows, dtype=np.float32)}
+        self._process_logits(logits, dev, sp)
+        probs = ops.softmax_temperature(logits, dev["s_temperature"])
+        if len(sp["prob_slots"]):
+            # draft model: the verifier needs the distribution the token was actually drawn from
+            if float(np.min(sp["top_p"])) < 1.0:
+                ops.renorm_top_p(probs, None, dev["s_top_p"])
+            self._ensure_draft_storage(int(np.max(sp["prob_slots"])))
+            ops.row_scatter(self.draft_probs, dev["s_prob_slots"], probs)
+            ones = torch.ones_like(dev["s_top_p"])
+            tokens, tprobs = ops.sample(probs, None, dev["s_uniform"], ones, None)
+        else:
+            top_k = dev["s_top_k"] if int(np.max(sp["top_k"])) > 0 else None
+            tokens, tprobs = ops.sample(probs, None, dev["s_uniform"], dev["s_top_p"], top_k)
+        out = {}
+        k = int(sp["num_top_logprobs"])
+        if k > 0:
+            _, tp, ti = ops.take_probs(probs, None, tokens if tokens.device == probs.device
+                                       else tokens.to(probs.device), k)
+            out["top_probs"] = tp.reshape(-1).float().cpu().numpy()
+            out["top_tokens"] = ti.reshape(-1).to(torch.int32).cpu().numpy()
+            # logprobs are reported on the unrenormalised distribution
+            sel = probs[torch.arange(n_rows, device=probs.device), tokens.long().to(probs.device)]
+            tprobs = sel
+        out["tokens"] = tokens.to(torch.int32).cpu().numpy()
+        out["probs"] = tprobs.float().cpu().numpy()
+        self.d2h_bytes += out["tokens"].nbytes + out["probs"].nbytes
+        return out
+
+    def forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
+        sp = vp["sampling"]
+        arrays = self._pack(plan, token_ids, sp)
+        if self.comm is not None:
+            self.comm.broadcast_step("forward", model_id, arrays, {"num_top_logprobs": 0})
+        dev = self.staging.upload(arrays)
+        self.h2d_bytes += self.staging.last_words * 4
+        hidden = self._run_model(model_id, plan, dev, None)
+        model = self.models[model_id]
+        logits = model.logits(hidden, dev["s_logit_token_index"])
+        self._process_logits(logits, dev, sp)
+        probs = ops.softmax_temperature(logits, dev["s_temperature"])
+        if float(np.min(sp["top_p"])) < 1.0:
+            ops.renorm_top_p(probs, None, dev["s_top_p"])
+        # flat node table: row r of `probs` is node r; roots carry no draft token
+        node_indptr = np.asarray(vp["node_indptr"])
+        nseq = len(node_indptr) - 1
+        total_rows = probs.shape[0]
+        first_child = np.full(total_rows, -1, dtype=np.int32)
+        next_sibling = np.full(total_rows, -1, dtype=np.int32)
+        draft_tok = np.zeros(total_rows, dtype=np.int32)
+        uniform = np.zeros(total_rows, dtype=np.float32)
+        slot_of_row = np.zeros(total_rows, dtype=np.int32)
+        parent_row = np.full(total_rows, -1, dtype=np.int32)
+        roots = np.zeros(nseq, dtype=np.int32)
+        parents = np.asarray(vp["parents"])
+        row = 0
+        for s in range(nseq):
+            root = row
+            roots[s] = root
+            nb, ne = int(node_indptr[s]), int(node_indptr[s + 1])
+            last_child: Dict[int, int] = {}
+            for j in range(nb, ne):
+                r = root + 1 + (j - nb)
+                p = root if parents[j] < 0 else root + 1 + int(parents[j])
+                parent_row[r] = p
+                if p in last_child:
+                    next_sibling[last_child[p]] = r
+                else:
+                    first_child[p] = r
+                last_child[p] = r
+                draft_tok[r] = vp["draft_tokens"][j]
+                uniform[r] = vp["uniform"][j]
+                slot_of_row[r] = vp["draft_prob_slots"][j]
+            row += 1 + (ne - nb)
+        d = self.device
+        self._ensure_draft_storage(int(slot_of_row.max()) if total_rows else 0)
+        draft_rows = ops.row_gather(self.draft_probs, torch.from_numpy(slot_of_row).to(d))
+        parent_ptr = torch.from_numpy(roots.copy()).to(d)
+        ops.verify_tree(draft_rows, torch.from_numpy(draft_tok).to(d), probs,
+                        torch.from_numpy(first_child).to(d), torch.from_numpy(next_sibling).to(d),
+                        torch.from_numpy(uniform).to(d), parent_ptr)
+        fin_u = torch.from_numpy(np.asarray(vp["final_uniform"], dtype=np.float32)).to(d)
+        tokens, tprobs = ops.sample(probs, parent_ptr, fin_u, torch.ones_like(fin_u), None)
+        last = parent_ptr.cpu().numpy()
+        accepted_indptr = [0]
+        accepted_nodes: List[int] = []
+        for s in range(nseq):
+            path = []
+            r = int(last[s])
+            while r != roots[s]:
+                path.append(r - roots[s] - 1)
+                r = int(parent_row[r])
+            accepted_nodes.extend(reversed(path))
+            accepted_indptr.append(len(accepted_nodes))
+        return {"accepted_indptr": np.asarray(accepted_indptr, dtype=np.int32),
+                "accepted_nodes": np.asarray(accepted_nodes, dtype=np.int32),
+                "final_tokens": tokens.to(torch.int32).cpu().numpy(),
+                "final_probs": tprobs.float().cpu().numpy()}
+
+    def move_kv_tokens(self, model_id: int, moves: np.ndarray) -> None:
+        if self.comm is not None:
+            self.comm.broadcast_step("move", model_id, {"moves": np.ascontiguousarray(moves, dtype=np.int32)}, {})
+        self.models[model_id].move_tokens(torch.from_numpy(np.ascontiguousarray(moves, dtype=np.int32)).to(self.device))
+
+    # ------------------------------------------------------------------ worker side (rank > 0)
+    def worker_step(self, op: str, model_id: int, arrays: Dict[str, np.ndarray], layout) -> None:
+        """Mirror of the rank-0 calls on the other tensor-parallel ranks: same forward, no sampling."""
+        if op == "move":
+            self.models[model_id].move_tokens(torch.from_numpy(arrays["moves"]).to(self.device))
+            return
+        dev = self.staging.upload(arrays)
+        plan = {k: arrays[k] for k in _INT_KEYS}
+        plan["tree_mask"] = arrays["tree_mask"]
+        self._run_model(model_id, plan, dev, None)
