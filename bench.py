@@ -1,0 +1,267 @@
+"""Headline serving benchmark: output tokens/s of continuous-batching generation.
+
+Workload (one "step" = one full pass of it): Llama-3-8B, q4f16_1 weights (random init, N(0, 0.02),
+seeded), 256 requests of 512 uniform-random prompt tokens, 256 output tokens each (EOS ignored),
+16-token KV pages, fp16 KV cache, greedy sampling.  With N > 1 GPUs the model runs tensor-parallel
+over the N ranks (one process per GPU, NCCL); the request count is fixed, so scaling is "strong".
+
+Two numbers are reported:
+* ``value``  -- device-timed (CUDA events on the compute stream, max over ranks) run of the native
+  engine stepped directly through the step-driven ``SyncMLCEngine``;
+* ``e2e``    -- the same workload through the public ``MLCEngine.completions`` API (background engine
+  thread, stream-back thread, detokenisation), wall-clock, including per-step H2D of the step's
+  index arrays from pinned memory and D2H of the sampled tokens.
+
+``--impl reference`` would run the unmodified reference implementation; it cannot be installed in
+this environment (its build needs the TVM / tokenizers-cpp / xgrammar submodules, which are empty
+directories), so that arm prints an ``unavailable`` line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+
+def _reference_arm():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "offline pip install of /root/reference fails at CMake: 3rdparty/tvm, "
+                       "3rdparty/tokenizers-cpp and 3rdparty/xgrammar are empty submodule directories "
+                       "(add_subdirectory has no CMakeLists.txt); apache-tvm-ffi is not in the wheelhouse",
+    }))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    cols = [c.strip() for c in line.split(",")]
+                    if len(cols) < 9:
+                        continue
+                    try:
+                        sm.append(float(cols[1]))
+                        mx.append(float(cols[2]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                          "sw_power_cap"), cols[5:9]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="llama-3-8b")
+    ap.add_argument("--quant", default="q4f16_1")
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return _reference_arm()
+
+    import torch
+
+    from mlc_llm_b200 import parallel
+    from mlc_llm_b200.ops import _lib
+    from mlc_llm_b200.serve.config import EngineConfig
+
+    rank, world, local = parallel.env_world()
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("for --gpus N > 1 launch with torch.distributed.run --nproc-per-node N")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    comm = parallel.Communicator(tp_size=world, pp_size=1) if world > 1 else None
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+
+    model = f"random://{args.model}?quant={args.quant}&seed=0"
+    total_tokens = args.requests * (args.prompt_len + args.output_len)
+    cfg = EngineConfig(mode="server", max_num_sequence=args.requests, prefill_chunk_size=8192,
+                       max_total_sequence_length=total_tokens + 16 * args.requests + 8192,
+                       prefix_cache_mode="disable", gpu_memory_utilization=0.90)
+    rng = np.random.default_rng(1234)
+    gen_cfg = {"max_tokens": args.output_len, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+    vocab_hi = 32000
+
+    def make_prompts():
+        # fresh prompts every pass so no pass benefits from an earlier one
+        return [rng.integers(0, vocab_hi, args.prompt_len).tolist() for _ in range(args.requests)]
+
+    # ------------------------------------------------------------------ worker ranks
+    if rank != 0:
+        from mlc_llm_b200.serve.engine_base import EngineRuntime
+
+        cfg.model = model
+        rt = EngineRuntime(cfg, device, comm=comm)
+        passes = (args.warmup + args.steps) * (1 if args.no_e2e else 2)
+        for _ in range(passes):
+            comm.barrier()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            parallel.worker_loop(rt.executor, comm)
+            end.record()
+            torch.cuda.synchronize()
+            comm.barrier()
+            comm.max_over_ranks(start.elapsed_time(end))
+        comm.destroy()
+        return 0
+
+    # ------------------------------------------------------------------ rank 0
+    from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
+
+    eng = SyncMLCEngine(model, device, engine_config=cfg, comm=comm)
+    lib = _lib.lib()
+    lib.mlcb_launch_count.restype = __import__("ctypes").c_longlong
+
+    def run_pass_device():
+        prompts = make_prompts()
+        if comm is not None:
+            comm.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = lib.mlcb_launch_count()
+        start.record()
+        out_tokens = eng.run_token_workload(prompts, gen_cfg)
+        end.record()
+        torch.cuda.synchronize()
+        if comm is not None:
+            comm.shutdown_workers()
+            comm.barrier()
+        ms = start.elapsed_time(end)
+        if comm is not None:
+            ms = comm.max_over_ranks(ms)
+        _lib.check_status(device)
+        return ms, out_tokens, lib.mlcb_launch_count() - l0
+
+    for _ in range(args.warmup):
+        run_pass_device()
+    sampler = ClockSampler(local)
+    sampler.start()
+    times, toks, launches = [], 0, 0
+    for _ in range(args.steps):
+        ms, n, l = run_pass_device()
+        times.append(ms)
+        toks += n
+        launches += l
+    clocks = sampler.stop()
+    total_ms = sum(times)
+    value = toks / (total_ms / 1e3)
+    steps_per_pass = json.loads(eng.debug_stats())
+    engine_steps = steps_per_pass["num_prefill_steps"] + steps_per_pass["num_decode_steps"]
+
+    # ------------------------------------------------------------------ end to end, public API
+    e2e = None
+    if not args.no_e2e:
+        h2d0, d2h0 = eng.runtime.executor.h2d_bytes, eng.runtime.executor.d2h_bytes
+        steps0 = json.loads(eng.debug_stats())
+        from mlc_llm_b200.serve.engine import MLCEngine
+
+        api = MLCEngine.from_runtime(eng.runtime)
+
+        def run_pass_api():
+            prompts = make_prompts()
+            if comm is not None:
+                comm.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            res = api.generate_many(prompts, gen_cfg)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            if comm is not None:
+                comm.shutdown_workers()
+                comm.barrier()
+                comm.max_over_ranks(0.0)
+            return dt, sum(r["usage"]["completion_tokens"] for r in res)
+
+        for _ in range(args.warmup):
+            run_pass_api()
+        h2d0, d2h0 = eng.runtime.executor.h2d_bytes, eng.runtime.executor.d2h_bytes
+        st0 = api.debug_step_count()
+        dts, etoks = [], 0
+        for _ in range(args.steps):
+            dt, n = run_pass_api()
+            dts.append(dt)
+            etoks += n
+        nsteps = max(1, api.debug_step_count() - st0)
+        e2e = {"value": etoks / sum(dts), "unit": "output tokens/s",
+               "h2d_bytes_per_step": (eng.runtime.executor.h2d_bytes - h2d0) / nsteps,
+               "d2h_bytes_per_step": (eng.runtime.executor.d2h_bytes - d2h0) / nsteps,
+               "engine_steps": nsteps}
+        api.terminate()
+
+    line = {
+        "metric": "output tok/s (device-timed, max over ranks)",
+        "value": value, "unit": "output tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp16 activations, int4-group weights (q4f16_1)"
+        if args.quant == "q4f16_1" else args.quant, "data": "synthetic (uniform-random token ids, random-init weights)",
+        "config": {"model": f"{args.model} {args.quant}", "global_batch": args.requests,
+                   "seq_len": args.prompt_len + args.output_len, "prompt_len": args.prompt_len,
+                   "output_len": args.output_len, "parallelism": f"tp{world}",
+                   "l2": "inputs larger than L2 (weights and KV cache far exceed 126 MB)",
+                   "kv_page": 16, "kv_dtype": "fp16", "sampling": "greedy, ignore_eos"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "engine_steps_per_pass": engine_steps // max(1, args.warmup + args.steps),
+    }
+    print(json.dumps(line))
+    if comm is not None:
+        comm.destroy()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -137,6 +137,7 @@ MLCB_API int mlcb_attn_simt(const void* q, const void* kv_pages, void* out, floa
     attn_simt_kernel<__half><<<grid, 128, 0, stream>>>(a);
   else
     attn_simt_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(a);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -148,5 +149,6 @@ MLCB_API int mlcb_merge_attn(void* o1, float* lse1, const void* o2, const float*
   else
     merge_attn_kernel<__nv_bfloat16>
         <<<rows, 128, 0, stream>>>((__nv_bfloat16*)o1, lse1, (const __nv_bfloat16*)o2, lse2, d);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }

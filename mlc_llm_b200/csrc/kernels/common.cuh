@@ -263,6 +263,13 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // ---------------------------------------------------------------- host helpers
 #define MLCB_API extern "C" __attribute__((visibility("default")))
 
+// Launch accounting: every exported entry point that launches work bumps this counter once per
+// kernel launch it issues, so callers can report how many of this library's kernels ran.
+namespace mlcb {
+extern long long g_launch_count;
+inline void count_launch(int n = 1) { __atomic_fetch_add(&g_launch_count, n, __ATOMIC_RELAXED); }
+}  // namespace mlcb
+
 namespace mlcb {
 // Encodes (and caches) a tiled tensor map. dims/strides are innermost-first; strides in bytes for
 // dims 1..rank-1. Returns nullptr on failure.

@@ -231,6 +231,7 @@ MLCB_API int mlcb_rmsnorm(const void* x, void* residual, const void* w, void* ou
     LAUNCH(__nv_bfloat16)
   }
 #undef LAUNCH
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -246,6 +247,7 @@ MLCB_API int mlcb_act_mul(const void* in, void* out, int tokens, int inter, int 
   else
     act_mul_kernel<__nv_bfloat16>
         <<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total, act);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -263,6 +265,7 @@ MLCB_API int mlcb_rope_append(void* qkv, void* kv_pages, const int* pos, const i
     rope_append_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
         (__nv_bfloat16*)qkv, (__nv_bfloat16*)kv_pages, pos, slot, inv_freq, hq, hkv, d, rot_dim, page,
         attn_factor, status, num_slots);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -276,6 +279,7 @@ MLCB_API int mlcb_embed(const int* ids, const void* table, void* out, int tokens
   else
     embed_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table,
                                                            (__nv_bfloat16*)out, hidden, vocab, scale);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -285,6 +289,7 @@ MLCB_API int mlcb_embed_q4(const int* ids, const void* qw, const void* qs, void*
   if (hidden % 32) return -1;
   embed_q4_kernel<<<tokens, 256, 0, stream>>>(ids, (const uint32_t*)qw, (const __half*)qs,
                                               (__half*)out, hidden, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -294,6 +299,7 @@ MLCB_API int mlcb_row_copy(const void* src, void* dst, const int* idx, int rows,
   if (row_bytes % 16) return -1;
   row_copy_kernel<<<rows, 256, 0, stream>>>((const uint8_t*)src, (uint8_t*)dst, idx, row_bytes,
                                             scatter);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -302,5 +308,6 @@ MLCB_API int mlcb_page_copy(void* pages, const int* src_dst, int pairs, int laye
   if (pairs <= 0) return 0;
   page_copy_kernel<<<pairs * layers, 256, 0, stream>>>((uint8_t*)pages, src_dst, (size_t)page_bytes,
                                                       (size_t)layer_stride, pairs);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }

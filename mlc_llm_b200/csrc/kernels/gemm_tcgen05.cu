@@ -429,6 +429,8 @@ const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, co
   return m;
 }
 
+long long g_launch_count = 0;
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -526,5 +528,8 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
     gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
     gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
+
+MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }

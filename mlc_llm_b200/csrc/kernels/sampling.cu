@@ -389,12 +389,14 @@ MLCB_API int mlcb_logit_bias(float* logits, const int* pos2seq, const int* token
                              int n, int vocab, cudaStream_t stream) {
   if (n <= 0) return 0;
   logit_bias_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, pos2seq, token, bias, n, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_penalty(float* logits, const int* pos2seq, const int* token, const int* cnt,
                           const float* penalties, int n, int vocab, cudaStream_t stream) {
   if (n <= 0) return 0;
   penalty_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, pos2seq, token, cnt, penalties, n, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_bitmask(float* logits, const int* rows, const int* bitmask, int nrows, int vocab,
@@ -402,18 +404,21 @@ MLCB_API int mlcb_bitmask(float* logits, const int* rows, const int* bitmask, in
   if (nrows <= 0) return 0;
   dim3 grid((vocab + 255) / 256, nrows);
   bitmask_kernel<<<grid, 256, 0, stream>>>(logits, rows, bitmask, vocab, (vocab + 31) / 32);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_softmax_temperature(const float* logits, float* probs, const float* temperature,
                                       int n, int vocab, int active_vocab, cudaStream_t stream) {
   if (n <= 0) return 0;
   softmax_temp_kernel<<<n, ROW_THREADS, 0, stream>>>(logits, probs, temperature, vocab, active_vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_argmax(const float* x, int* out, float* out_val, int n, int vocab,
                          cudaStream_t stream) {
   if (n <= 0) return 0;
   argmax_kernel<<<n, ROW_THREADS, 0, stream>>>(x, out, out_val, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_sample(const float* probs, const int* sample_rows, const float* uniform,
@@ -422,12 +427,14 @@ MLCB_API int mlcb_sample(const float* probs, const int* sample_rows, const float
   if (n <= 0) return 0;
   sample_kernel<<<n, ROW_THREADS, 0, stream>>>(probs, sample_rows, uniform, top_p, top_k, out_token,
                                                out_prob, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_renorm_top_p(float* probs, const int* rows, const float* top_p, int n, int vocab,
                                cudaStream_t stream) {
   if (n <= 0) return 0;
   renorm_top_p_kernel<<<n, ROW_THREADS, 0, stream>>>(probs, rows, top_p, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_take_probs(const float* probs, const int* rows, const int* token, float* out_prob,
@@ -437,6 +444,7 @@ MLCB_API int mlcb_take_probs(const float* probs, const int* rows, const int* tok
   if (k > 32) return -1;
   take_probs_kernel<<<n, ROW_THREADS, 0, stream>>>(probs, rows, token, out_prob, topk_prob, topk_idx,
                                                    k, vocab);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 MLCB_API int mlcb_verify_tree(const float* draft_probs, const int* draft_tokens, float* model_probs,
@@ -447,5 +455,6 @@ MLCB_API int mlcb_verify_tree(const float* draft_probs, const int* draft_tokens,
   verify_tree_kernel<<<nbatch, ROW_THREADS, 0, stream>>>(draft_probs, draft_tokens, model_probs,
                                                          first_child, next_sibling, uniform,
                                                          parent_ptr, vocab, max_nodes);
+  count_launch();
   return static_cast<int>(cudaGetLastError());
 }

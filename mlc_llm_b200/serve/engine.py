@@ -65,19 +65,24 @@ class MLCEngineBase:
 
     def __init__(self, kind: str, model: str, device: Union[str, torch.device] = "auto", *,
                  model_lib: Optional[str] = None, mode: Literal["local", "interactive", "server"] = "local",
-                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None):
-        if engine_config is None:
-            engine_config = EngineConfig()
-        if engine_config.model is not None and engine_config.model != model:
-            raise ValueError("engine_config.model conflicts with the model argument")
-        engine_config.model = model
-        if model_lib is not None:
-            engine_config.model_lib = model_lib
-        if engine_config.mode is None:
-            engine_config.mode = mode
+                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None,
+                 runtime: Optional[EngineRuntime] = None):
         self.kind = kind
-        self.trace_recorder = _core.EventTraceRecorder() if enable_tracing else None
-        self.runtime = EngineRuntime(engine_config, device, comm=comm, trace_recorder=self.trace_recorder)
+        if runtime is not None:
+            self.runtime = runtime
+            self.trace_recorder = runtime.trace
+        else:
+            if engine_config is None:
+                engine_config = EngineConfig()
+            if engine_config.model is not None and engine_config.model != model:
+                raise ValueError("engine_config.model conflicts with the model argument")
+            engine_config.model = model
+            if model_lib is not None:
+                engine_config.model_lib = model_lib
+            if engine_config.mode is None:
+                engine_config.mode = mode
+            self.trace_recorder = _core.EventTraceRecorder() if enable_tracing else None
+            self.runtime = EngineRuntime(engine_config, device, comm=comm, trace_recorder=self.trace_recorder)
         self.tokenizer = self.runtime.tokenizer
         self.conv_template = self.runtime.conv_template
         self.model = model
@@ -98,7 +103,19 @@ class MLCEngineBase:
 
     # ---------------------------------------------------------------- native glue
     def _factory(self, engine_config_json: str):
-        return self.runtime.make_core_engine(engine_config_json, None)
+        self._core_engine = self.runtime.make_core_engine(engine_config_json, None)
+        return self._core_engine
+
+    def debug_step_count(self) -> int:
+        """Scheduling steps taken so far (prefill + decode + verify)."""
+        st = json.loads(self._core_engine.debug_stats())
+        return int(st.get("num_prefill_steps", 0) + st.get("num_decode_steps", 0) + st.get("num_verify_steps", 0))
+
+    @classmethod
+    def from_runtime(cls, runtime: EngineRuntime):
+        """Build an engine over an already loaded runtime (weights and KV cache are shared, so the
+        engines must not generate at the same time)."""
+        return cls(runtime.engine_config.model, runtime.device, runtime=runtime)
 
     def _on_outputs(self, outputs: List[dict]) -> None:
         """Runs on the stream-back thread: detokenise and hand each request its items."""
@@ -216,9 +233,10 @@ class AsyncMLCEngine(MLCEngineBase):
 
     def __init__(self, model: str, device: Union[str, torch.device] = "auto", *,
                  model_lib: Optional[str] = None, mode: Literal["local", "interactive", "server"] = "local",
-                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None):
+                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None,
+                 runtime: Optional[EngineRuntime] = None):
         super().__init__("async", model, device, model_lib=model_lib, mode=mode, engine_config=engine_config,
-                         enable_tracing=enable_tracing, comm=comm)
+                         enable_tracing=enable_tracing, comm=comm, runtime=runtime)
         self.chat = _Namespace()
         self.chat.completions = AsyncChatCompletion(self)
         self.completions = AsyncCompletion(self)
@@ -333,9 +351,10 @@ class MLCEngine(MLCEngineBase):
 
     def __init__(self, model: str, device: Union[str, torch.device] = "auto", *,
                  model_lib: Optional[str] = None, mode: Literal["local", "interactive", "server"] = "local",
-                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None):
+                 engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None,
+                 runtime: Optional[EngineRuntime] = None):
         super().__init__("sync", model, device, model_lib=model_lib, mode=mode, engine_config=engine_config,
-                         enable_tracing=enable_tracing, comm=comm)
+                         enable_tracing=enable_tracing, comm=comm, runtime=runtime)
         self.chat = _Namespace()
         self.chat.completions = ChatCompletion(self)
         self.completions = Completion(self)

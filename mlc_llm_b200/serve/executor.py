@@ -187,8 +187,8 @@ class ModelExecutor:
         n_rows = len(sp["logit_token_index"])
         arrays = self._pack(plan, token_ids, sp)
         if self.comm is not None:
-            self.comm.broadcast_step("forward", model_id, arrays,
-                                     {"num_top_logprobs": int(sp["num_top_logprobs"])})
+            self.comm.broadcast_step("forward", model_id,
+                                     {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         hidden = self._run_model(model_id, plan, dev, embed_handles)
@@ -233,7 +233,8 @@ class ModelExecutor:
         sp = vp["sampling"]
         arrays = self._pack(plan, token_ids, sp)
         if self.comm is not None:
-            self.comm.broadcast_step("forward", model_id, arrays, {"num_top_logprobs": 0})
+            self.comm.broadcast_step("forward", model_id,
+                                     {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         hidden = self._run_model(model_id, plan, dev, None)
