@@ -52,6 +52,16 @@ struct GemmParams {
   int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
 };
 
+// Work item `t` walks its K blocks [kb0, kb1) starting at an item-dependent offset. When many
+// CTAs share one token tile (decode: a single M block) they would otherwise all fetch the same
+// activation lines at the same moment and queue up on one L2 slice; the sum over K is order-free.
+__device__ __forceinline__ int rotate_k(int kb, int kb0, int kb1, int t) {
+  const int n = kb1 - kb0;
+  int r = (kb - kb0) + (t * 5) % n;
+  if (r >= n) r -= n;
+  return kb0 + r;
+}
+
 template <typename OutT>
 __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
   reinterpret_cast<OutT*>(y)[idx] = Cvt<OutT>::from_f(v);
@@ -128,11 +138,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             if (!ok) break;
           }
           mbar_expect_tx(&full[s], tx_bytes);
-          tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], kb * BK, mb * p.tn);
+          const int ka = rotate_k(kb, kb0, kb1, t);  // see rotate_k
+          tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], ka * BK, mb * p.tn);
           if (Q4)
-            tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &full[s], kb * (BK / 8), nb * BM);
+            tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &full[s], ka * (BK / 8), nb * BM);
           else
-            tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], kb * BK, nb * BM);
+            tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], ka * BK, nb * BM);
         }
       }
     }
@@ -195,10 +206,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           // the two group scales of this 64-wide K block (issued before the wait to hide latency)
           __half2 sc = __floats2half2_rn(0.f, 0.f);
-          if (n_ok && (kb * 2 + 1) < groups_per_row)
-            sc = *reinterpret_cast<const __half2*>(srow + kb * 2);
-          else if (n_ok && kb * 2 < groups_per_row)
-            sc = __halves2half2(srow[kb * 2], __float2half(0.f));
+          const int ka = rotate_k(kb, kb0, kb1, t);
+          if (n_ok && (ka * 2 + 1) < groups_per_row)
+            sc = *reinterpret_cast<const __half2*>(srow + ka * 2);
+          else if (n_ok && ka * 2 < groups_per_row)
+            sc = __halves2half2(srow[ka * 2], __float2half(0.f));
           ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
           ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
           if (!ok) break;

@@ -95,7 +95,7 @@ class ModelExecutor:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launch_estimate = 0
-        self.use_tensor_core_attention = device.type == "cuda"
+        self.use_tensor_core_attention = False
 
     # ------------------------------------------------------------------ embeddings (multimodal)
     def hold_embedding(self, emb: torch.Tensor) -> int:
