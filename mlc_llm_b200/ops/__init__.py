@@ -244,7 +244,7 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
     out = torch.empty(t, hq * d, dtype=q.dtype, device=q.device)
     lse = torch.empty(t, hq, dtype=torch.float32, device=q.device) if return_lse else None
     if plan is not None and plan.use_tensor_core and tree_mask is None and softcap == 0.0 \
-            and q_kvstart is None and d == 128 and page == 16:
+            and q_kvstart is None and d == 128 and page == 16 and q.dtype in (torch.float16, torch.bfloat16):
         from .attention import attention_tcgen05  # pylint: disable=import-outside-toplevel
 
         attention_tcgen05(q, kv_pages, out, lse, plan, hq, hkv, sm_scale)

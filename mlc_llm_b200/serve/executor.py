@@ -95,7 +95,7 @@ class ModelExecutor:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launch_estimate = 0
-        self.use_tensor_core_attention = False
+        self.use_tensor_core_attention = device.type == "cuda"
 
     # ------------------------------------------------------------------ embeddings (multimodal)
     def hold_embedding(self, emb: torch.Tensor) -> int:
@@ -122,19 +122,30 @@ class ModelExecutor:
             q_kvstart=dev["q_kvstart"] if dev["q_kvstart"].numel() else None,
             tree_mask=dev["tree_mask"] if dev["tree_mask"].numel() else None,
             num_tokens=int(dev["positions"].numel()))
-        if self.use_tensor_core_attention and b.tree_mask is None and b.q_kvstart is None \
-                and model.d == 128 and model.page == 16 and model.cfg.layer_attn_kinds is None \
-                and model.cfg.attn_logit_softcap == 0:
-            from ..ops.attention import make_plan  # pylint: disable=import-outside-toplevel
+        if "tile_seq" in dev and self._tc_attention_ok(model) and b.tree_mask is None \
+                and b.q_kvstart is None:
+            from ..ops.attention import AttentionPlan  # pylint: disable=import-outside-toplevel
 
-            b.attn_plan = make_plan(plan, model.hq, model.hkv, self.device)
+            b.attn_plan = AttentionPlan(dev["tile_seq"], dev["tile_qstart"], dev["tile_ntok"], b.q_kvlen,
+                                        b.page_indptr, b.page_indices, int(dev["tile_seq"].numel()))
         return b
 
-    def _pack(self, plan: dict, token_ids: np.ndarray, sp: Optional[dict]) -> Dict[str, np.ndarray]:
+    def _tc_attention_ok(self, model: DecoderModel) -> bool:
+        return (self.use_tensor_core_attention and model.d == 128 and model.page == 16
+                and model.cfg.layer_attn_kinds is None and model.cfg.attn_logit_softcap == 0
+                and model.kv_dtype in (torch.float16, torch.bfloat16))
+
+    def _pack(self, plan: dict, token_ids: np.ndarray, sp: Optional[dict], model_id: int = 0
+              ) -> Dict[str, np.ndarray]:
         arrays: Dict[str, np.ndarray] = {"token_ids": np.ascontiguousarray(token_ids, dtype=np.int32)}
         for k in _INT_KEYS:
             arrays[k] = np.ascontiguousarray(plan[k], dtype=np.int32)
         arrays["tree_mask"] = np.ascontiguousarray(plan["tree_mask"], dtype=np.uint64).view(np.int64)
+        model = self.models[model_id]
+        if self._tc_attention_ok(model) and arrays["tree_mask"].size == 0 and arrays["q_kvstart"].size == 0:
+            from ..ops.attention import build_tiles  # pylint: disable=import-outside-toplevel
+
+            arrays.update(build_tiles(arrays["q_indptr"], model.hq // model.hkv))
         if sp is not None:
             for k in _S_INT:
                 arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.int32)
@@ -185,7 +196,7 @@ class ModelExecutor:
     def forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
                        embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
         n_rows = len(sp["logit_token_index"])
-        arrays = self._pack(plan, token_ids, sp)
+        arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,
                                      {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})
@@ -231,7 +242,7 @@ class ModelExecutor:
 
     def forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
         sp = vp["sampling"]
-        arrays = self._pack(plan, token_ids, sp)
+        arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,
                                      {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})

@@ -1,6 +1,8 @@
 """CUDA kernels against the fp32 PyTorch oracle (``ops.reference``)."""
 import math
 
+import numpy as np
+
 import pytest
 import torch
 
@@ -239,3 +241,43 @@ def test_logit_edits_and_take_probs_and_verify():
     ops.verify_tree(dp.to(DEV), dt.to(DEV), mpg, fc.to(DEV), ns.to(DEV), u.to(DEV), ppg)
     assert torch.equal(ppg.cpu(), pp_ref)
     _close(mpg, mp_ref, 1e-4, 1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (8, 1), (4, 4), (32, 8)])
+@pytest.mark.parametrize("mode", ["prefill", "decode", "mixed"])
+def test_attention_tcgen05(dtype, hq, hkv, mode):
+    from mlc_llm_b200.ops.attention import AttentionPlan, build_tiles
+
+    torch.manual_seed(11)
+    d, page = 128, 16
+    if mode == "prefill":
+        lens, appended = [70, 200, 33, 129], [70, 200, 33, 129]
+    elif mode == "decode":
+        lens, appended = [1, 17, 64, 65, 300, 128], [1, 1, 1, 1, 1, 1]
+    else:
+        lens, appended = [300, 40, 90], [44, 1, 90]
+    kv, indptr, indices = _mk_paged(len(lens), lens, hkv, d, page, dtype)
+    q_seq, q_kvlen, q_indptr = [], [], [0]
+    for b, (l, a) in enumerate(zip(lens, appended)):
+        for i in range(a):
+            q_seq.append(b)
+            q_kvlen.append(l - a + i + 1)
+        q_indptr.append(len(q_seq))
+    t = len(q_seq)
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d) * 0.7).to(dtype)
+    q_seq = torch.tensor(q_seq, dtype=torch.int32)
+    q_kvlen = torch.tensor(q_kvlen, dtype=torch.int32)
+    scale = d ** -0.5
+    o_ref, lse_ref = ops.paged_attention(qkv[:, : hq * d], kv, q_seq, q_kvlen, indptr, indices, hq, hkv, d,
+                                         page, scale, return_lse=True)
+    tiles = build_tiles(np.asarray(q_indptr), hq // hkv)
+    dev = lambda a: torch.as_tensor(a).to(DEV)
+    plan = AttentionPlan(dev(tiles["tile_seq"]), dev(tiles["tile_qstart"]), dev(tiles["tile_ntok"]),
+                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]))
+    qg = qkv.to(DEV)
+    o, lse = ops.paged_attention(qg[:, : hq * d], kv.to(DEV), q_seq.to(DEV), q_kvlen.to(DEV), indptr.to(DEV),
+                                 indices.to(DEV), hq, hkv, d, page, scale, return_lse=True, plan=plan)
+    ops.check_status(qg.device)
+    _close(o, o_ref, 2e-2, 2e-2)
+    _close(lse, lse_ref, 1e-2, 1e-2)
