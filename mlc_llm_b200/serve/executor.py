@@ -126,8 +126,16 @@ class ModelExecutor:
                 and b.q_kvstart is None:
             from ..ops.attention import AttentionPlan  # pylint: disable=import-outside-toplevel
 
+            from ..ops.attention import choose_splits  # pylint: disable=import-outside-toplevel
+
+            n_dec = int(dev["dec_seq"].numel())
+            max_pages = (int(plan["max_seq_len"]) + 15) // 16
             b.attn_plan = AttentionPlan(dev["tile_seq"], dev["tile_qstart"], dev["tile_ntok"], b.q_kvlen,
-                                        b.page_indptr, b.page_indices, int(dev["tile_seq"].numel()))
+                                        b.page_indptr, b.page_indices, int(dev["tile_seq"].numel()),
+                                        dec_seq=dev["dec_seq"], dec_qstart=dev["dec_qstart"],
+                                        dec_ntok=dev["dec_ntok"], num_dec=n_dec,
+                                        dec_splits=choose_splits(n_dec, model.hkv, max_pages, self.device)
+                                        if n_dec else 1, max_pages=max_pages)
         return b
 
     def _tc_attention_ok(self, model: DecoderModel) -> bool:
@@ -325,4 +333,5 @@ class ModelExecutor:
         dev = self.staging.upload(arrays)
         plan = {k: arrays[k] for k in _INT_KEYS}
         plan["tree_mask"] = arrays["tree_mask"]
+        plan["max_seq_len"] = int(arrays["seq_lens"].max()) if arrays["seq_lens"].size else 0
         self._run_model(model_id, plan, dev, None)

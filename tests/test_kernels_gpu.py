@@ -245,8 +245,9 @@ def test_logit_edits_and_take_probs_and_verify():
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("hq,hkv", [(8, 2), (8, 1), (4, 4), (32, 8)])
-@pytest.mark.parametrize("mode", ["prefill", "decode", "mixed"])
-def test_attention_tcgen05(dtype, hq, hkv, mode):
+@pytest.mark.parametrize("mode,splits", [("prefill", 1), ("decode", 1), ("mixed", 1), ("decode", 3),
+                                         ("verify", 1), ("verify", 2)])
+def test_attention_tcgen05(dtype, hq, hkv, mode, splits):
     from mlc_llm_b200.ops.attention import AttentionPlan, build_tiles
 
     torch.manual_seed(11)
@@ -255,6 +256,8 @@ def test_attention_tcgen05(dtype, hq, hkv, mode):
         lens, appended = [70, 200, 33, 129], [70, 200, 33, 129]
     elif mode == "decode":
         lens, appended = [1, 17, 64, 65, 300, 128], [1, 1, 1, 1, 1, 1]
+    elif mode == "verify":
+        lens, appended = [33, 500, 7, 260], [3, 4, 2, 4]
     else:
         lens, appended = [300, 40, 90], [44, 1, 90]
     kv, indptr, indices = _mk_paged(len(lens), lens, hkv, d, page, dtype)
@@ -274,7 +277,9 @@ def test_attention_tcgen05(dtype, hq, hkv, mode):
     tiles = build_tiles(np.asarray(q_indptr), hq // hkv)
     dev = lambda a: torch.as_tensor(a).to(DEV)
     plan = AttentionPlan(dev(tiles["tile_seq"]), dev(tiles["tile_qstart"]), dev(tiles["tile_ntok"]),
-                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]))
+                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]),
+                         dec_seq=dev(tiles["dec_seq"]), dec_qstart=dev(tiles["dec_qstart"]),
+                         dec_ntok=dev(tiles["dec_ntok"]), num_dec=len(tiles["dec_seq"]), dec_splits=splits)
     qg = qkv.to(DEV)
     o, lse = ops.paged_attention(qg[:, : hq * d], kv.to(DEV), q_seq.to(DEV), q_kvlen.to(DEV), indptr.to(DEV),
                                  indices.to(DEV), hq, hkv, d, page, scale, return_lse=True, plan=plan)
