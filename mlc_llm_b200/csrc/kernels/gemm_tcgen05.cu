@@ -11,8 +11,9 @@
 // small decode batches do not pad to 128 rows. Accumulators live in TMEM (two buffers of 256
 // columns, so the epilogue of one tile overlaps the main loop of the next).
 //
-// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
-// warps 2-5 = dequant, warps 6-9 = epilogue (TMEM -> registers -> global).
+// Roles (352 threads): warp 0 = TMA producer (activations), warp 1 = MMA issuer (+TMEM owner),
+// warps 2-5 = dequant, warps 6-9 = epilogue (TMEM -> registers -> global), warp 10 = TMA producer
+// of the packed weights (q4).
 //
 // Reference counterparts: dense matmul dispatched to cuBLAS (compiler_pass/blas_dispatch.py:15-52)
 // and the fused dequantize+matmul produced by compiler_pass/fuse_dequantize_matmul_ewise.py:9-85
@@ -28,12 +29,13 @@ namespace mlcb {
 constexpr int BM = 128;       // weight rows (output features) per tile == UMMA M
 constexpr int BK = 64;        // K elements per pipeline stage (128 bytes of 16-bit data)
 constexpr int MAX_TN = 256;   // tokens per tile == UMMA N
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;     // activation / expanded-weight ring
+constexpr int RAW_STAGES = 6; // packed-weight ring (q4): deeper, so TMA latency stays off the MMA loop
 constexpr int X_STAGE_BYTES = MAX_TN * BK * 2;   // 32 KiB
 constexpr int W_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int RAW_STAGE_BYTES = BM * (BK / 2);   // 4 KiB of packed nibbles
-constexpr int GEMM_THREADS = 320;
-constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES + RAW_STAGE_BYTES) + 1024 + 512;
+constexpr int GEMM_THREADS = 352;
+constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES) + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 512;
 
 struct GemmParams {
   const void* scale;    // [N, K/32] fp16 (q4 only)
@@ -50,11 +52,12 @@ struct GemmParams {
   int kb_per_split;     // K blocks handled by one work item
   float* workspace;     // [tiles, splits, tn, BM] fp32 partial sums (split-K only)
   int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
+  long long* trace;     // optional: per-role timestamps of CTA 0 (profiling aid, null = off)
 };
 
 // Work item `t` walks its K blocks [kb0, kb1) starting at an item-dependent offset. When many
 // CTAs share one token tile (decode: a single M block) they would otherwise all fetch the same
-// activation lines at the same moment and queue up on one L2 slice; the sum over K is order-free.
+// activation lines at the same moment; the sum over K is order-free.
 __device__ __forceinline__ int rotate_k(int kb, int kb0, int kb1, int t) {
   const int n = kb1 - kb0;
   int r = (kb - kb0) + (t * 5) % n;
@@ -62,10 +65,45 @@ __device__ __forceinline__ int rotate_k(int kb, int kb0, int kb1, int t) {
   return kb0 + r;
 }
 
+// Profiling aid: role `r` records clock64 for event slot `i` (CTA 0 only, when a buffer is given).
+#define GEMM_TRACE(r, i)                                                               \
+  do {                                                                                 \
+    if (p.trace && blockIdx.x == 0 && (i) < 512) p.trace[(r) * 512 + (i)] = clock64(); \
+  } while (0)
+
 template <typename OutT>
 __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
   reinterpret_cast<OutT*>(y)[idx] = Cvt<OutT>::from_f(v);
 }
+
+// Cursor over the (work item, K block) sequence of this CTA; every role advances its own copy.
+// Everything that needs an integer division is computed once per work item.
+struct KCursor {
+  int t, kb, kb0, kb1, ka, nb, mb;
+  __device__ __forceinline__ void init(const GemmParams& p, int total_kb, int num_items) {
+    t = blockIdx.x;
+    set(p, total_kb, num_items);
+  }
+  __device__ __forceinline__ void set(const GemmParams& p, int total_kb, int num_items) {
+    if (t >= num_items) return;
+    const int tile = t / p.splits;
+    kb0 = (t - tile * p.splits) * p.kb_per_split;
+    kb1 = min(total_kb, kb0 + p.kb_per_split);
+    nb = tile % p.num_n_blocks;
+    mb = tile / p.num_n_blocks;
+    kb = kb0;
+    ka = rotate_k(kb0, kb0, kb1, t);  // actual K block loaded at step kb (rotated start)
+  }
+  __device__ __forceinline__ bool valid(int num_items) const { return t < num_items; }
+  __device__ __forceinline__ void next(const GemmParams& p, int total_kb, int num_items) {
+    if (++kb >= kb1) {
+      t += gridDim.x;
+      set(p, total_kb, num_items);
+    } else if (++ka >= kb1) {
+      ka = kb0;
+    }
+  }
+};
 
 template <bool Q4>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -76,14 +114,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                                              ~uintptr_t(1023));
   uint8_t* sx = smem;                                   // STAGES x 32 KiB
   uint8_t* sw = sx + STAGES * X_STAGE_BYTES;            // STAGES x 16 KiB
-  uint8_t* sraw = sw + STAGES * W_STAGE_BYTES;          // STAGES x 4 KiB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sraw + STAGES * RAW_STAGE_BYTES);
-  uint64_t* full = bars;                 // [STAGES] TMA landed
-  uint64_t* empty = bars + STAGES;       // [STAGES] MMA done reading
-  uint64_t* deq_full = bars + 2 * STAGES;  // [STAGES] dequantised tile written
-  uint64_t* acc_full = bars + 3 * STAGES;  // [2]
-  uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint64_t* ep_bar = acc_empty + 2;        // [2] epilogue-group sync for the split-K reduction
+  uint8_t* sraw = sw + STAGES * W_STAGE_BYTES;          // RAW_STAGES x 4 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sraw + RAW_STAGES * RAW_STAGE_BYTES);
+  uint64_t* full = bars;                       // [STAGES] activation (and dense weight) tile landed
+  uint64_t* empty = full + STAGES;             // [STAGES] MMA done reading the stage
+  uint64_t* deq_full = empty + STAGES;         // [STAGES] expanded weight tile written
+  uint64_t* raw_full = deq_full + STAGES;      // [RAW_STAGES] packed weight tile landed
+  uint64_t* raw_empty = raw_full + RAW_STAGES; // [RAW_STAGES] dequant warps done reading it
+  uint64_t* acc_full = raw_empty + RAW_STAGES; // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint64_t* ep_bar = acc_empty + 2;            // [2] epilogue-group sync for the split-K reduction
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ep_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -98,6 +138,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&deq_full[s], 4);
+    }
+    for (int s = 0; s < RAW_STAGES; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 4);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
@@ -117,34 +161,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer: activations
+    // (and the dense weight tile). Ring of STAGES, recycled by the MMA.
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
+      if (!Q4) tma_prefetch_desc(&tmap_w);
+      const uint32_t x_bytes = static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES);
+      KCursor cx;
+      cx.init(p, total_kb, num_tiles);
+      for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
+        const int s = ix % STAGES;
+        if (ix >= STAGES &&
+            !mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
+          break;
+        GEMM_TRACE(0, ix);
+        mbar_expect_tx(&full[s], x_bytes);
+        tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.mb * p.tn);
+        if (!Q4) tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.nb * BM);
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ TMA producer: packed weights
+    // (q4). Ring of RAW_STAGES, recycled by the dequant warps as soon as they hold the nibbles in
+    // registers, so this stream runs ahead of the MMA loop.
+    if (Q4 && lane == 0) {
       tma_prefetch_desc(&tmap_w);
-      uint32_t it = 0;
-      const uint32_t tx_bytes =
-          static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? RAW_STAGE_BYTES : W_STAGE_BYTES);
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int tile = t / p.splits, sp = t % p.splits;
-        const int nb = tile % p.num_n_blocks, mb = tile / p.num_n_blocks;
-        const int kb0 = sp * p.kb_per_split;
-        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (it >= STAGES) {
-            ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
-            if (!ok) break;
-          }
-          mbar_expect_tx(&full[s], tx_bytes);
-          const int ka = rotate_k(kb, kb0, kb1, t);  // see rotate_k
-          tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], ka * BK, mb * p.tn);
-          if (Q4)
-            tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &full[s], ka * (BK / 8), nb * BM);
-          else
-            tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], ka * BK, nb * BM);
-        }
+      KCursor cr;
+      cr.init(p, total_kb, num_tiles);
+      for (uint32_t ir = 0; cr.valid(num_tiles); ++ir, cr.next(p, total_kb, num_tiles)) {
+        const int s = ir % RAW_STAGES;
+        if (ir >= RAW_STAGES &&
+            !mbar_wait(&raw_empty[s], ((ir / RAW_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
+          break;
+        mbar_expect_tx(&raw_full[s], RAW_STAGE_BYTES);
+        tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &raw_full[s], cr.ka * (BK / 8), cr.nb * BM);
       }
     }
   } else if (warp == 1) {
@@ -169,10 +219,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
           if (!ok) break;
+          GEMM_TRACE(1, it);
           if (Q4) {
             ok = mbar_wait(&deq_full[s], ph, abort_flag, p.status, ERR_WAIT_DEQUANT);
             if (!ok) break;
           }
+          GEMM_TRACE(2, it);
           tc_fence_after();
           const uint64_t adesc = umma_smem_desc(smem_u32(sw + s * W_STAGE_BYTES), 16, 1024);
           const uint64_t bdesc = umma_smem_desc(smem_u32(sx + s * X_STAGE_BYTES), 16, 1024);
@@ -182,6 +234,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
           }
           umma_commit(&empty[s]);
+          GEMM_TRACE(3, it);
         }
         if (ok) umma_commit(&acc_full[a]);
       }
@@ -194,29 +247,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const int groups_per_row = p.K / 32;
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int nb = (t / p.splits) % p.num_n_blocks;
-        const int kb0 = (t % p.splits) * p.kb_per_split;
-        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
-        const int n = nb * BM + row;
-        const bool n_ok = n < p.N;
-        const __half* srow = scale + static_cast<size_t>(n_ok ? n : 0) * groups_per_row;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      // group scales of a K block: two fp16 values per row; fetched one iteration ahead so the
+      // global-load latency never sits on the dequant critical path
+      auto load_scale = [&](const KCursor& c) -> __half2 {
+        if (!c.valid(num_tiles)) return __floats2half2_rn(0.f, 0.f);
+        const int nn = c.nb * BM + row;
+        if (nn >= p.N) return __floats2half2_rn(0.f, 0.f);
+        const __half* sr = scale + static_cast<size_t>(nn) * groups_per_row;
+        if (c.ka * 2 + 1 < groups_per_row) return *reinterpret_cast<const __half2*>(sr + c.ka * 2);
+        if (c.ka * 2 < groups_per_row) return __halves2half2(sr[c.ka * 2], __float2half(0.f));
+        return __floats2half2_rn(0.f, 0.f);
+      };
+      KCursor cs;
+      cs.init(p, total_kb, num_tiles);
+      __half2 sc_next = load_scale(cs);
+      for (; cs.valid(num_tiles) && ok; ++it) {
+        {
           const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          // the two group scales of this 64-wide K block (issued before the wait to hide latency)
-          __half2 sc = __floats2half2_rn(0.f, 0.f);
-          const int ka = rotate_k(kb, kb0, kb1, t);
-          if (n_ok && (ka * 2 + 1) < groups_per_row)
-            sc = *reinterpret_cast<const __half2*>(srow + ka * 2);
-          else if (n_ok && ka * 2 < groups_per_row)
-            sc = __halves2half2(srow[ka * 2], __float2half(0.f));
-          ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
+          const int rs = it % RAW_STAGES;
+          const __half2 sc = sc_next;
+          cs.next(p, total_kb, num_tiles);
+          sc_next = load_scale(cs);
+          ok = mbar_wait(&raw_full[rs], (it / RAW_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
           ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
           if (!ok) break;
-          const uint4* raw = reinterpret_cast<const uint4*>(sraw + s * RAW_STAGE_BYTES + row * 32);
+          if (threadIdx.x == 64) GEMM_TRACE(4, it);
+          const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_STAGE_BYTES + row * 32);
           uint4 r0 = raw[0], r1 = raw[1];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[rs]);  // nibbles are in registers: recycle early
           uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+          // the expanded tile may only be overwritten once the MMA that read it has finished
+          if (it >= STAGES) {
+            ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
           uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
@@ -240,10 +306,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&deq_full[s]);
+          if (threadIdx.x == 64) GEMM_TRACE(5, it);
         }
       }
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tile_i = 0;
@@ -256,6 +323,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, ERR_WAIT_MMA);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
+      if (threadIdx.x == 192) GEMM_TRACE(6, tile_i);
       tc_fence_after();
       const int row = q * 32 + lane;     // row inside the tile
       const int n = nb * BM + row;       // output feature of this thread
@@ -328,27 +396,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         continue;
       }
+      // lane = output feature: a warp-wide store covers 32 consecutive features of one token.
+      // Kept free of shared-memory traffic on purpose (the MMA needs that bandwidth when this
+      // epilogue overlaps the next tile's main loop).
+      const int jlim = min(p.tn, p.M - m0);
       for (int c = 0; c < p.tn; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * MAX_TN + c, r);
         tmem_ld_wait();
-        if (n_ok) {
+        if (!n_ok) continue;
+        const int jn = jlim - c;  // valid tokens in this chunk (may be <= 0)
+        const size_t base = static_cast<size_t>(m0 + c) * p.ldy + n;
+        if (p.out_dtype == 0) {
+          __half* y = reinterpret_cast<__half*>(p.y) + base;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int m = m0 + c + j;
-            if (c + j < p.tn && m < p.M) {
-              const float v = __uint_as_float(r[j]) + bias;
-              const size_t idx = static_cast<size_t>(m) * p.ldy + n;
-              if (p.out_dtype == 0) store_out<__half>(p.y, idx, v);
-              else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx, v);
-              else store_out<float>(p.y, idx, v);
-            }
-          }
+          for (int j = 0; j < 32; ++j)
+            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __float2half_rn(__uint_as_float(r[j]) + bias);
+        } else if (p.out_dtype == 1) {
+          __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + base;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __float2bfloat16_rn(__uint_as_float(r[j]) + bias);
+        } else {
+          float* y = reinterpret_cast<float*>(p.y) + base;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __uint_as_float(r[j]) + bias;
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
+      if (threadIdx.x == 192) GEMM_TRACE(7, tile_i);
     }
   }
 
@@ -466,6 +545,10 @@ static int pick_tn(int M) {
 
 using namespace mlcb;
 
+static long long* g_gemm_trace = nullptr;
+// Debug hook: device buffer of 8 x 512 int64 that receives CTA 0's role timestamps (null = off).
+MLCB_API void mlcb_gemm_set_trace(long long* buf) { g_gemm_trace = buf; }
+
 // Returns 0 on success, a negative value for a rejected shape, a positive CUDA error otherwise.
 // x: [M, K] row-major (ldx elements) fp16/bf16.  w: dense [N, K] (same dtype) or, with
 // scale != nullptr, the device-layout packed int4 [N, K/8] uint32 with scale [N, K/32] fp16.
@@ -515,6 +598,7 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
     p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
     p.workspace = workspace;
     p.counters = counters;
+    p.trace = g_gemm_trace;
   }
 
   uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
