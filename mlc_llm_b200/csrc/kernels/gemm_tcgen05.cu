@@ -629,3 +629,134 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
 }
 
 MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in gemm_noalloc.h). Same kernel, but the split-K scratch
+// is a fixed array in this translation unit instead of caller-provided memory.
+// ---------------------------------------------------------------------------------------------
+#include "gemm_noalloc.h"
+
+#include <cstdio>
+
+namespace {
+// Partial sums first, tile counters behind them. In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernel receives the looked-up device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MLCB_NOALLOC_SCRATCH_BYTES +
+                                                                 MLCB_NOALLOC_MAX_TILES * sizeof(int)];
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+thread_local char g_noalloc_err[256] = {0};
+
+int noalloc_fail(int code, const char* fmt, long long a = 0, long long b = 0, long long c = 0) {
+  snprintf(g_noalloc_err, sizeof(g_noalloc_err), fmt, a, b, c);
+  return code;
+}
+
+// Encodes a 2-D tiled tensor map into caller-provided storage (no heap, no cache).
+bool encode_map_local(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+MLCB_API const char* mlcb_gemm_noalloc_last_error(void) { return g_noalloc_err; }
+
+MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy,
+                               int ab_fmt, int* status, cudaStream_t stream) {
+  g_noalloc_err[0] = 0;
+  if (M <= 0 || N <= 0) return 0;
+  if (!x || !w || !y || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K || ldy < N || (ab_fmt != 0 && ab_fmt != 1))
+    return noalloc_fail(MLCB_NOALLOC_BAD_ARGUMENT,
+                        "mlcb_gemm_noalloc: bad argument (K=%lld and ldx must be multiples of 8, ldx >= K, ldy >= N=%lld)",
+                        K, N);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15)
+    return noalloc_fail(MLCB_NOALLOC_BAD_ARGUMENT, "mlcb_gemm_noalloc: pointers must be 16-byte aligned");
+
+  // ---- one-time set-up per device: device address of the built-in scratch
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return noalloc_fail(static_cast<int>(err), "mlcb_gemm_noalloc: cudaGetDevice failed (%lld)", err);
+  if (dev < 0 || dev >= kMaxDevices)
+    return noalloc_fail(MLCB_NOALLOC_BAD_ARGUMENT, "mlcb_gemm_noalloc: device index %lld out of range", dev);
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      err = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // with `dev` current
+      if (err != cudaSuccess || !p)
+        return noalloc_fail(static_cast<int>(err ? err : cudaErrorInvalidSymbol),
+                            "mlcb_gemm_noalloc: cudaGetSymbolAddress failed (%lld)", err);
+      static bool attr_set_noalloc = false;
+      if (!attr_set_noalloc) {
+        cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+        attr_set_noalloc = true;
+      }
+      g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+
+  // ---- tiling and split-K, bounded by the built-in scratch
+  GemmParams p;
+  p.scale = nullptr;
+  p.bias = nullptr;
+  p.y = y;
+  p.status = status;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  p.tn = pick_tn(M);
+  p.num_m_blocks = (M + p.tn - 1) / p.tn;
+  p.num_n_blocks = (N + BM - 1) / BM;
+  p.out_dtype = ab_fmt;
+  p.ab_fmt = ab_fmt;
+  p.trace = nullptr;
+  const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles > MLCB_NOALLOC_MAX_TILES)
+    return noalloc_fail(MLCB_NOALLOC_TOO_LARGE,
+                        "mlcb_gemm_noalloc: %lld output tiles exceed the built-in limit of %lld; use mlcb_gemm with "
+                        "caller-provided scratch",
+                        tiles, MLCB_NOALLOC_MAX_TILES);
+  const int total_kb = (K + BK - 1) / BK;
+  // this entry point always runs the split-K form (that is the variant that needs scratch)
+  int splits = sm_count() / static_cast<int>(tiles);
+  if (splits > 8) splits = 8;
+  if (splits > total_kb) splits = total_kb;
+  if (splits < 2) splits = total_kb >= 2 ? 2 : 1;
+  p.kb_per_split = (total_kb + splits - 1) / splits;
+  p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  const long long need = tiles * p.splits * p.tn * BM * 4;
+  if (need > static_cast<long long>(MLCB_NOALLOC_SCRATCH_BYTES))
+    return noalloc_fail(MLCB_NOALLOC_TOO_LARGE,
+                        "mlcb_gemm_noalloc: split-K scratch of %lld bytes exceeds the built-in %lld bytes "
+                        "(M x N too large for this entry point; use mlcb_gemm)",
+                        need, MLCB_NOALLOC_SCRATCH_BYTES);
+  p.workspace = reinterpret_cast<float*>(scratch);
+  p.counters = reinterpret_cast<int*>(scratch + MLCB_NOALLOC_SCRATCH_BYTES);
+  // the counters must start at zero; the partial sums are fully overwritten before they are read
+  err = cudaMemsetAsync(p.counters, 0, static_cast<size_t>(tiles) * sizeof(int), stream);
+  if (err != cudaSuccess) return noalloc_fail(static_cast<int>(err), "mlcb_gemm_noalloc: cudaMemsetAsync failed (%lld)", err);
+
+  CUtensorMap mx, mw;
+  if (!encode_map_local(&mx, x, K, M, static_cast<uint64_t>(ldx) * 2, BK, p.tn) ||
+      !encode_map_local(&mw, w, K, N, static_cast<uint64_t>(K) * 2, BK, BM))
+    return noalloc_fail(MLCB_NOALLOC_NO_DRIVER_ENTRY, "mlcb_gemm_noalloc: could not encode the TMA tensor maps");
+  const int items = static_cast<int>(tiles) * p.splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(mx, mw, p);
+  count_launch();
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return noalloc_fail(static_cast<int>(err), "mlcb_gemm_noalloc: launch failed (%lld)", err);
+  return 0;
+}

@@ -1,0 +1,68 @@
+"""The allocation-free GEMM entry point, called through its exported C symbol.
+
+Some embedders of the kernel library may not allocate device memory when they call it (fixed memory
+budgets, latency-critical paths where cudaMalloc would stall the device, a device heap owned by a
+different allocator).  ``mlcb_gemm_noalloc`` serves them: its split-K scratch is a fixed array inside
+the library.  The test checks it against the regular entry point (which gets its scratch from the
+caller) on two consecutive calls, because the built-in scratch is shared by all calls and keeps the
+previous call's contents.  The file name sorts last so a run that stops at the first failure has
+already executed every other test.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from mlc_llm_b200.ops import _lib as loader
+
+    lib = loader.lib()
+    lib.mlcb_gemm_noalloc.restype = ctypes.c_int
+    lib.mlcb_gemm_noalloc_last_error.restype = ctypes.c_char_p
+    return lib
+
+
+def _noalloc(lib, x, w, y, ab_fmt):
+    m, k = x.shape
+    n = w.shape[0]
+    return lib.mlcb_gemm_noalloc(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                 ctypes.c_void_p(y.data_ptr()), ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
+                                 ctypes.c_int(x.stride(0)), ctypes.c_int(y.stride(0)), ctypes.c_int(ab_fmt),
+                                 ctypes.c_void_p(0), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
+@pytest.mark.parametrize("dtype,ab_fmt", [(torch.float16, 0), (torch.bfloat16, 1)])
+def test_noalloc_matches_regular_entry_point_twice(dtype, ab_fmt):
+    from mlc_llm_b200 import ops
+
+    lib = _lib()
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    # first a larger problem, then a smaller one with different data: the second call must not be
+    # affected by what the first left in the shared scratch
+    for m, n, k in [(200, 512, 1024), (48, 256, 2048)]:
+        x = (torch.randn(m, k, device=dev) * 0.5).to(dtype)
+        w = (torch.randn(n, k, device=dev) * 0.05).to(dtype)
+        y = torch.empty(m, n, dtype=dtype, device=dev)
+        rc = _noalloc(lib, x, w, y, ab_fmt)
+        assert rc == 0, lib.mlcb_gemm_noalloc_last_error().decode()
+        ref = ops.linear(x, ops.dense_weight(w))
+        torch.cuda.synchronize()
+        err = (y.float() - ref.float()).abs()
+        tol = 2e-2 + 2e-2 * ref.float().abs()
+        assert bool((err <= tol).all()), f"max err {err.max().item()}"
+
+
+def test_noalloc_rejects_oversized_problem():
+    lib = _lib()
+    dev = torch.device("cuda")
+    # 4096 x 8192 output needs far more split-K scratch (and tiles) than the built-in array holds
+    x = torch.zeros(4096, 64, dtype=torch.float16, device=dev)
+    w = torch.zeros(8192, 64, dtype=torch.float16, device=dev)
+    y = torch.zeros(4096, 8192, dtype=torch.float16, device=dev)
+    rc = _noalloc(lib, x, w, y, 0)
+    assert rc == -2
+    assert b"exceed" in lib.mlcb_gemm_noalloc_last_error()
