@@ -1,0 +1,42 @@
+"""Child process of the multi-rank tests: runs a tiny model tensor-parallel (gloo on CPU, NCCL on
+GPUs) and, on rank 0, prints the generated token ids as JSON."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from mlc_llm_b200 import parallel  # noqa: E402
+from mlc_llm_b200.serve.config import EngineConfig  # noqa: E402
+from mlc_llm_b200.serve.engine_base import EngineRuntime  # noqa: E402
+
+
+def main():
+    model = sys.argv[1]
+    device = sys.argv[2]
+    rank, world, local = parallel.env_world()
+    dev = torch.device("cuda", local) if device == "cuda" else torch.device("cpu")
+    comm = parallel.Communicator(tp_size=world, pp_size=1, device=dev, timeout_s=120)
+    cfg = EngineConfig(model=model, mode="server", max_num_sequence=8, prefill_chunk_size=64,
+                       max_total_sequence_length=1024, prefix_cache_mode="disable")
+    if rank != 0:
+        rt = EngineRuntime(cfg, dev, comm=comm)
+        parallel.worker_loop(rt.executor, comm)
+        comm.destroy()
+        return
+    from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
+
+    eng = SyncMLCEngine(model, dev, engine_config=cfg, comm=comm)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (40, 9, 23)]
+    _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
+    comm.shutdown_workers()
+    print("RESULT " + json.dumps([t[0] for t in toks]), flush=True)
+    comm.destroy()
+
+
+if __name__ == "__main__":
+    main()

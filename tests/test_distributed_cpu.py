@@ -1,0 +1,29 @@
+"""Tensor parallelism over CPU ranks (gloo): sharded weights + step broadcast + worker loop must
+reproduce the single-process result exactly (fp32)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world: int, model: str, device: str = "cpu", port: int = 29531):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker.py"),
+           model, device]
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.parametrize("model", ["random://tiny-llama?quant=q0f32&seed=5"])
+def test_tp2_matches_single_rank(model):
+    single = _run(1, model, port=29541)
+    tp2 = _run(2, model, port=29542)
+    assert single == tp2
