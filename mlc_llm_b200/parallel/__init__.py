@@ -56,6 +56,8 @@ class Communicator:
             else:
                 device = torch.device("cpu")
         self.device = device
+        if device.type == "cuda":
+            torch.cuda.set_device(device)  # object collectives stage through the current device
         backend = backend or ("nccl" if device.type == "cuda" else "gloo")
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -107,7 +109,7 @@ class Communicator:
         pages = torch.tensor([int(res["num_pages"])], dtype=torch.int64, device=self._header.device)
         dist.all_reduce(pages, op=dist.ReduceOp.MIN)
         box = [res if self.rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
+        dist.broadcast_object_list(box, src=0, device=self._header.device)
         out = dict(box[0])
         out["num_pages"] = int(pages.item())
         return out

@@ -17,6 +17,12 @@ def _run(world: int, model: str, device: str = "cpu", port: int = 29531):
            model, device]
     env = dict(os.environ, OMP_NUM_THREADS="2")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    if out.returncode != 0:
+        # keep the children's full stderr where a GPU run can pick it up
+        log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
+        if os.path.isdir(log_dir):
+            with open(os.path.join(log_dir, "dist_stderr.log"), "w", encoding="utf-8") as f:
+                f.write(out.stderr)
     assert out.returncode == 0, out.stderr[-3000:]
     line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
