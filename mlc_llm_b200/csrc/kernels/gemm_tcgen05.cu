@@ -53,7 +53,40 @@ struct GemmParams {
   float* workspace;     // [tiles, splits, tn, BM] fp32 partial sums (split-K only)
   int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
   long long* trace;     // optional: per-role timestamps of CTA 0 (profiling aid, null = off)
+  // grouped mode (mixture of experts): X rows [group_offsets[e], group_offsets[e+1]) use the weight
+  // slab e, i.e. rows [e * N, (e + 1) * N) of W (and of the scales). Null = one dense problem.
+  const int* group_offsets;
+  int num_groups;
 };
+
+// Where a tile lives: first weight row, first activation / output row, valid token rows, N block.
+struct TileInfo {
+  int w_row, x_row, m_valid, nb;
+};
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+  TileInfo ti;
+  ti.nb = tile % p.num_n_blocks;
+  const int mbg = tile / p.num_n_blocks;
+  if (!p.group_offsets) {
+    ti.w_row = ti.nb * BM;
+    ti.x_row = mbg * p.tn;
+    ti.m_valid = min(p.tn, p.M - ti.x_row);
+    return ti;
+  }
+  int cum = 0, e = 0, begin = 0, cnt = 0;
+  for (; e < p.num_groups; ++e) {
+    begin = p.group_offsets[e];
+    cnt = p.group_offsets[e + 1] - begin;
+    const int mbs = (cnt + p.tn - 1) / p.tn;
+    if (mbg < cum + mbs) break;
+    cum += mbs;
+  }
+  const int mb = mbg - cum;
+  ti.w_row = e * p.N + ti.nb * BM;
+  ti.x_row = begin + mb * p.tn;
+  ti.m_valid = min(p.tn, cnt - mb * p.tn);
+  return ti;
+}
 
 // Work item `t` walks its K blocks [kb0, kb1) starting at an item-dependent offset. When many
 // CTAs share one token tile (decode: a single M block) they would otherwise all fetch the same
@@ -79,7 +112,8 @@ __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
 // Cursor over the (work item, K block) sequence of this CTA; every role advances its own copy.
 // Everything that needs an integer division is computed once per work item.
 struct KCursor {
-  int t, kb, kb0, kb1, ka, nb, mb;
+  int t, kb, kb0, kb1, ka;
+  TileInfo ti;
   __device__ __forceinline__ void init(const GemmParams& p, int total_kb, int num_items) {
     t = blockIdx.x;
     set(p, total_kb, num_items);
@@ -89,8 +123,7 @@ struct KCursor {
     const int tile = t / p.splits;
     kb0 = (t - tile * p.splits) * p.kb_per_split;
     kb1 = min(total_kb, kb0 + p.kb_per_split);
-    nb = tile % p.num_n_blocks;
-    mb = tile / p.num_n_blocks;
+    ti = decode_tile(p, tile);
     kb = kb0;
     ka = rotate_k(kb0, kb0, kb1, t);  // actual K block loaded at step kb (rotated start)
   }
@@ -129,9 +162,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;  // work items
   const int total_kb = (p.K + BK - 1) / BK;
   __shared__ int last_flag;
+  __shared__ int sh_num_items;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -149,6 +182,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       mbar_init(&ep_bar[a], 4);
     }
     *abort_flag = 0;
+    if (p.group_offsets) {
+      int mbs = 0;
+      for (int e = 0; e < p.num_groups; ++e)
+        mbs += (p.group_offsets[e + 1] - p.group_offsets[e] + p.tn - 1) / p.tn;
+      sh_num_items = mbs * p.num_n_blocks;
+    } else {
+      sh_num_items = p.num_m_blocks * p.num_n_blocks * p.splits;
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -159,6 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int num_tiles = sh_num_items;  // work items
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: activations
@@ -176,8 +218,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           break;
         GEMM_TRACE(0, ix);
         mbar_expect_tx(&full[s], x_bytes);
-        tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.mb * p.tn);
-        if (!Q4) tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.nb * BM);
+        tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_row);
+        if (!Q4) tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.ti.w_row);
       }
     }
   } else if (warp == 10) {
@@ -194,7 +236,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             !mbar_wait(&raw_empty[s], ((ir / RAW_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
           break;
         mbar_expect_tx(&raw_full[s], RAW_STAGE_BYTES);
-        tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &raw_full[s], cr.ka * (BK / 8), cr.nb * BM);
+        tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &raw_full[s], cr.ka * (BK / 8), cr.ti.w_row);
       }
     }
   } else if (warp == 1) {
@@ -251,9 +293,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       // global-load latency never sits on the dequant critical path
       auto load_scale = [&](const KCursor& c) -> __half2 {
         if (!c.valid(num_tiles)) return __floats2half2_rn(0.f, 0.f);
-        const int nn = c.nb * BM + row;
-        if (nn >= p.N) return __floats2half2_rn(0.f, 0.f);
-        const __half* sr = scale + static_cast<size_t>(nn) * groups_per_row;
+        if (c.ti.nb * BM + row >= p.N) return __floats2half2_rn(0.f, 0.f);
+        const __half* sr = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row;
         if (c.ka * 2 + 1 < groups_per_row) return *reinterpret_cast<const __half2*>(sr + c.ka * 2);
         if (c.ka * 2 < groups_per_row) return __halves2half2(sr[c.ka * 2], __float2half(0.f));
         return __floats2half2_rn(0.f, 0.f);
@@ -317,7 +358,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
       const int tile = t / p.splits, sp = t % p.splits;
-      const int nb = tile % p.num_n_blocks, mb = tile / p.num_n_blocks;
+      const TileInfo ti = decode_tile(p, tile);
+      const int nb = ti.nb;
       const int a = tile_i & 1;
       const uint32_t aph = (tile_i >> 1) & 1;
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, ERR_WAIT_MMA);
@@ -333,7 +375,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         bias = p.ab_fmt == 0 ? __half2float(reinterpret_cast<const __half*>(p.bias)[n])
                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
       }
-      const int m0 = mb * p.tn;
+      const int m0 = ti.x_row;
       float* ws_tile = p.workspace + static_cast<size_t>(tile) * p.splits * p.tn * BM;
       if (p.splits > 1) {
         // park this split's partial sums: [split][token][feature] so a warp writes 128 bytes
@@ -370,7 +412,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         if (!ok) break;
         if (last_flag) {
           __threadfence();
-          const int jmax = min(p.tn, p.M - m0);
+          const int jmax = ti.m_valid;
           for (int j0 = 0; j0 < jmax; j0 += 8) {
             float v[8];
 #pragma unroll
@@ -399,7 +441,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       // lane = output feature: a warp-wide store covers 32 consecutive features of one token.
       // Kept free of shared-memory traffic on purpose (the MMA needs that bandwidth when this
       // epilogue overlaps the next tile's main loop).
-      const int jlim = min(p.tn, p.M - m0);
+      const int jlim = ti.m_valid;
       for (int c = 0; c < p.tn; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * MAX_TN + c, r);
@@ -599,6 +641,8 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
     p.workspace = workspace;
     p.counters = counters;
     p.trace = g_gemm_trace;
+    p.group_offsets = nullptr;
+    p.num_groups = 0;
   }
 
   uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -629,6 +673,77 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
 }
 
 MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
+
+// Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of x (expert-major
+// permuted tokens, `total_rows` in all) are multiplied by expert e's weight slab w[e] ([N, K] dense
+// 16-bit, or packed int4 [N, K/8] + scale [N, K/32]); y has the same row order, [total_rows, N].
+// `offsets` is a device array of num_groups + 1 ints; the kernel derives its tile list from it, so
+// no host synchronisation is needed between routing and the expert matmuls.
+MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, void* y, const int* offsets,
+                               int num_groups, int total_rows, int N, int K, int ldx, int ldy, int ab_fmt,
+                               int out_dtype, int* status, cudaStream_t stream) {
+  if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
+  const bool q4 = scale != nullptr;
+  if (K % 8 != 0 || ldx % 8 != 0 || N % BM != 0) return -1;
+  if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    attr_set = true;
+  }
+  GemmParams p;
+  p.scale = scale;
+  p.bias = nullptr;
+  p.y = y;
+  p.status = status;
+  p.M = total_rows;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  // token tile sized for the average expert load (the box of the activation tensor map is fixed)
+  const int avg = (total_rows + num_groups - 1) / num_groups;
+  p.tn = avg >= 192 ? 256 : avg >= 96 ? 128 : avg >= 48 ? 64 : avg >= 24 ? 32 : 16;
+  p.num_m_blocks = 0;
+  p.num_n_blocks = N / BM;
+  p.out_dtype = out_dtype;
+  p.ab_fmt = ab_fmt;
+  p.splits = 1;
+  p.kb_per_split = (K + BK - 1) / BK;
+  p.workspace = nullptr;
+  p.counters = nullptr;
+  p.trace = nullptr;
+  p.group_offsets = offsets;
+  p.num_groups = num_groups;
+  uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(total_rows)};
+  uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
+  uint32_t xb[2] = {BK, static_cast<uint32_t>(p.tn)};
+  const CUtensorMap* mx = get_tensor_map(x, 2, 2, xd, xs, xb, 1);
+  const CUtensorMap* mw;
+  const uint64_t wrows = static_cast<uint64_t>(num_groups) * N;
+  if (q4) {
+    uint64_t wd[2] = {static_cast<uint64_t>(K / 8), wrows};
+    uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
+    uint32_t wb[2] = {BK / 8, BM};
+    mw = get_tensor_map(w, 4, 2, wd, ws, wb, 0);
+  } else {
+    uint64_t wd[2] = {static_cast<uint64_t>(K), wrows};
+    uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
+    uint32_t wb[2] = {BK, BM};
+    mw = get_tensor_map(w, 2, 2, wd, ws, wb, 1);
+  }
+  if (!mx || !mw) return -4;
+  // upper bound of useful CTAs: every expert may add one partial token block
+  const long long max_tiles = (static_cast<long long>(total_rows) / p.tn + num_groups) * p.num_n_blocks;
+  const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
+  if (q4)
+    gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  else
+    gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
 
 // ---------------------------------------------------------------------------------------------
 // Allocation-free entry point (declared in gemm_noalloc.h). Same kernel, but the split-K scratch
@@ -722,6 +837,8 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
   p.out_dtype = ab_fmt;
   p.ab_fmt = ab_fmt;
   p.trace = nullptr;
+  p.group_offsets = nullptr;
+  p.num_groups = 0;
   const long long tiles = static_cast<long long>(p.num_m_blocks) * p.num_n_blocks;
   if (tiles > MLCB_NOALLOC_MAX_TILES)
     return noalloc_fail(MLCB_NOALLOC_TOO_LARGE,

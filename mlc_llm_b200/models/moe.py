@@ -1,0 +1,46 @@
+"""Mixture-of-experts block: router -> expert-major permutation -> grouped GEMMs -> weighted combine.
+
+Reference: ``model/mixtral/mixtral_model.py:64-117`` (softmax-top-k routing, ``e1_e3`` / ``e2`` expert
+matmuls, scatter back and weighted sum) and ``model/qwen2_moe`` / ``qwen3_moe`` (shared expert,
+optional renormalisation).  Under tensor parallelism the experts are sharded on their intermediate
+dimension as in the reference (``mixtral_model.py:144-145``); with ``expert_parallel`` whole experts
+live on different ranks and tokens travel through the all-to-all in ``parallel/expert.py``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+
+def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
+    c = model.cfg
+    pre = f"model.layers.{li}.moe."
+    t, hidden = h.shape
+    k = c.num_experts_per_tok
+    gate_w = model.p.tensors[pre + "gate.weight"]
+    logits = ops.linear(h, ops.dense_weight(gate_w))
+    renorm = c.norm_topk_prob if c.moe_router == "softmax_topk" else True
+    weights, experts = ops.moe_router(logits, k, renorm)
+    w13 = model.p.linears[pre + "e1_e3"]
+    w2 = model.p.linears[pre + "e2"]
+    if c.expert_parallel and model.comm is not None and model.tp > 1:
+        from ..parallel.expert import expert_parallel_ffn  # pylint: disable=import-outside-toplevel
+
+        out = expert_parallel_ffn(model, h, weights, experts, w13, w2)
+    else:
+        offsets, sorted_pos, src_token = ops.moe_permute(experts, c.num_experts)
+        xp = ops.row_gather(h, src_token)
+        h1 = ops.grouped_linear(xp, w13, offsets)
+        a = ops.act_mul(h1, "silu" if c.hidden_act == "silu" else "gelu")
+        y = ops.grouped_linear(a, w2, offsets)
+        out = ops.moe_combine(y, weights, sorted_pos, None)
+    if c.shared_expert_intermediate_size > 0:
+        g = ops.linear(h, model.p.linears[pre + "shared_expert.gate_up_proj"])
+        s = ops.linear(ops.act_mul(g, "silu"), model.p.linears[pre + "shared_expert.down_proj"])
+        if c.shared_expert_gate:
+            sg = ops.linear(h, ops.dense_weight(model.p.tensors[pre + "shared_expert_gate.weight"]))
+            s = (torch.sigmoid(sg.float()) * s.float()).to(s.dtype)
+        out = out + s
+    return out

@@ -52,6 +52,12 @@ MODEL_PRESETS = {
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048,
         "num_local_experts": 4, "num_experts_per_tok": 2,
     },
+    "tiny-mixtral-gpu": {
+        "model_type": "mixtral", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+        "num_local_experts": 8, "num_experts_per_tok": 2,
+    },
     "qwen2-7b": {
         "model_type": "qwen2", "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
         "num_attention_heads": 28, "num_key_value_heads": 4, "vocab_size": 152064, "rms_norm_eps": 1e-6,

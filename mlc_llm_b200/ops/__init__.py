@@ -374,4 +374,92 @@ def row_scatter(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> None
     check(rc, "mlcb_row_copy")
 
 
+# --------------------------------------------------------------------------- mixture of experts
+def moe_router(logits: torch.Tensor, k: int, renorm: bool = True):
+    """Softmax over the experts, top-k, optional renormalisation. Returns (weights fp32 [T, k],
+    expert ids int32 [T, k])."""
+    if not logits.is_cuda:
+        return ref.moe_softmax_topk(logits, k, renorm)
+    t, e = logits.shape
+    w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(t, k, dtype=torch.int32, device=logits.device)
+    lg = logits.contiguous()
+    rc = lib().mlcb_moe_router(ptr(lg), ptr(w), ptr(idx), c_int(t), c_int(e), c_int(k), c_int(0),
+                               c_int(1 if renorm else 0), c_int(DTYPE_CODE[lg.dtype]), stream_ptr())
+    check(rc, "mlcb_moe_router")
+    return w, idx
+
+
+def moe_permute(experts: torch.Tensor, num_experts: int):
+    """Expert-major ordering of the (token, slot) pairs. Returns (offsets int32 [E+1], sorted_pos
+    int32 [T*k] = row of each pair, src_token int32 [T*k] = token feeding each row)."""
+    t, k = experts.shape
+    n = t * k
+    if not experts.is_cuda:
+        flat = experts.reshape(-1).long()
+        order = torch.sort(flat, stable=True).indices
+        sorted_pos = torch.empty(n, dtype=torch.int32)
+        sorted_pos[order] = torch.arange(n, dtype=torch.int32)
+        counts = torch.bincount(flat, minlength=num_experts)
+        offsets = torch.zeros(num_experts + 1, dtype=torch.int32)
+        offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        return offsets, sorted_pos, (order // k).to(torch.int32)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=experts.device)
+    sorted_pos = torch.empty(n, dtype=torch.int32, device=experts.device)
+    src_token = torch.empty(n, dtype=torch.int32, device=experts.device)
+    rc = lib().mlcb_moe_permute(ptr(experts.contiguous()), c_int(n), c_int(k), c_int(num_experts), ptr(offsets),
+                                ptr(sorted_pos), ptr(src_token), stream_ptr())
+    check(rc, "mlcb_moe_permute")
+    return offsets, sorted_pos, src_token
+
+
+def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
+                   out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Rows ``[offsets[e], offsets[e+1])`` of ``x`` times expert ``e``'s weight ``lw.w[e]``."""
+    od = out_dtype or x.dtype
+    e = lw.w.shape[0]
+    n = lw.w.shape[1]
+    if not x.is_cuda:
+        y = torch.zeros(x.shape[0], n, dtype=od)
+        w = lw.dense(torch.float32)
+        off = offsets.tolist()
+        for i in range(e):
+            if off[i + 1] > off[i]:
+                y[off[i]:off[i + 1]] = ref.linear_dense(x[off[i]:off[i + 1]], w[i], None, od)
+        return y
+    rows, k = x.shape
+    y = torch.empty(rows, n, dtype=od, device=x.device)
+    if rows == 0:
+        return y
+    x2 = x if x.stride(-1) == 1 else x.contiguous()
+    q4 = lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and x.dtype == torch.float16 \
+        and k % 64 == 0
+    w = lw.w if (q4 or lw.kind == "dense") else lw.dense(x.dtype)
+    if lw.kind == "q4" and not q4:
+        w = lw.dense(x.dtype)
+    rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(lw.scale) if q4 else ptr(None), ptr(y), ptr(offsets),
+                                 c_int(e), c_int(rows), c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n),
+                                 c_int(DTYPE_CODE[x.dtype]), c_int(DTYPE_CODE[od]), ptr(status_word(x.device)),
+                                 stream_ptr())
+    check(rc, f"mlcb_gemm_grouped(rows={rows},E={e},N={n},K={k})")
+    return y
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, sorted_pos: torch.Tensor,
+                add: Optional[torch.Tensor]) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * y[sorted_pos[t * k + j]] (+ add[t])``."""
+    t, k = weights.shape
+    if not y.is_cuda:
+        rows = y[sorted_pos.long()].float().view(t, k, -1)
+        out = (rows * weights.float().unsqueeze(-1)).sum(1)
+        if add is not None:
+            out = out + add.float()
+        return out.to(y.dtype)
+    out = torch.empty(t, y.shape[1], dtype=y.dtype, device=y.device)
+    rc = lib().mlcb_moe_combine(ptr(y), ptr(weights), ptr(sorted_pos), ptr(add), ptr(out), c_int(t),
+                                c_int(y.shape[1]), c_int(k), c_int(DTYPE_CODE[y.dtype]), stream_ptr())
+    check(rc, "mlcb_moe_combine")
+    return out
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]

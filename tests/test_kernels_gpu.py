@@ -286,3 +286,41 @@ def test_attention_tcgen05(dtype, hq, hkv, mode, splits):
     ops.check_status(qg.device)
     _close(o, o_ref, 2e-2, 2e-2)
     _close(lse, lse_ref, 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1"])
+@pytest.mark.parametrize("tokens", [1, 37, 700])
+def test_moe_block_kernels(quant_name, tokens):
+    torch.manual_seed(21)
+    e, k, hidden, inter = 8, 2, 256, 512
+    quant = Q.get(quant_name)
+    x = (torch.randn(tokens, hidden) * 0.5).half()
+    gate = (torch.randn(tokens, e)).half()
+    w13 = (torch.randn(e, 2 * inter, hidden) * 0.05).half()
+    w2 = (torch.randn(e, hidden, inter) * 0.05).half()
+
+    def mk(w):
+        if quant.kind == "no-quant":
+            return ops.LinearWeight("dense", w, None, None, None, w.shape[1], w.shape[2])
+        qw, qs = Q.group_quantize(w, quant)
+        return ops.LinearWeight("q4", qw, qs, None, quant, w.shape[1], w.shape[2])
+
+    l13, l2 = mk(w13), mk(w2)
+
+    def run(dev):
+        xx, gg = x.to(dev), gate.to(dev)
+        a13, a2 = l13.to(dev), l2.to(dev)
+        wts, idx = ops.moe_router(gg, k, True)
+        off, spos, src = ops.moe_permute(idx, e)
+        xp = ops.row_gather(xx, src)
+        h1 = ops.grouped_linear(xp, a13, off)
+        y = ops.grouped_linear(ops.act_mul(h1), a2, off)
+        return ops.moe_combine(y, wts, spos, None), wts, idx, off
+
+    o_cpu, w_cpu, i_cpu, off_cpu = run("cpu")
+    o_gpu, w_gpu, i_gpu, off_gpu = run(DEV)
+    ops.check_status(torch.device(DEV))
+    assert torch.equal(i_cpu.cpu(), i_gpu.cpu())
+    assert torch.equal(off_cpu.cpu(), off_gpu.cpu())
+    _close(w_gpu, w_cpu, 1e-3, 1e-5)
+    _close(o_gpu, o_cpu, 3e-2, 3e-2)
