@@ -18,7 +18,7 @@ class ErrorResponse(BaseModel):
 
 def create_error_response(status_code: HTTPStatus, message: str) -> fastapi.responses.JSONResponse:
     return fastapi.responses.JSONResponse(
-        ErrorResponse(message=message, code=status_code.value).model_dump_json(by_alias=True),
+        ErrorResponse(message=message, code=status_code.value).model_dump(by_alias=True),
         status_code=status_code.value,
     )
 

@@ -68,6 +68,7 @@ class MLCEngineBase:
                  engine_config: Optional[EngineConfig] = None, enable_tracing: bool = False, comm=None,
                  runtime: Optional[EngineRuntime] = None):
         self.kind = kind
+        self._workers = None
         if runtime is not None:
             self.runtime = runtime
             self.trace_recorder = runtime.trace
@@ -82,6 +83,14 @@ class MLCEngineBase:
             if engine_config.mode is None:
                 engine_config.mode = mode
             self.trace_recorder = _core.EventTraceRecorder() if enable_tracing else None
+            tp = int(engine_config.tensor_parallel_shards or 1)
+            pp = int(engine_config.pipeline_parallel_stages or 1)
+            if comm is None and tp * pp > 1:
+                from ..parallel import launcher  # pylint: disable=import-outside-toplevel
+
+                self._workers = launcher.launch(engine_config, engine_base.detect_device(device), tp, pp)
+                comm = self._workers.comm
+                device = comm.device
             self.runtime = EngineRuntime(engine_config, device, comm=comm, trace_recorder=self.trace_recorder)
         self.tokenizer = self.runtime.tokenizer
         self.conv_template = self.runtime.conv_template
@@ -175,7 +184,10 @@ class MLCEngineBase:
                 native_inputs.append(("embed", handle, int(emb.shape[0])))
             else:
                 native_inputs.append(item)
-        self._threaded.add_request(request_id, native_inputs, json.dumps(gen_cfg))
+        try:
+            self._threaded.add_request(request_id, native_inputs, json.dumps(gen_cfg))
+        except (ValueError, RuntimeError) as err:
+            raise BadRequestError(str(err)) from err
 
     # ---------------------------------------------------------------- public management API
     def terminate(self) -> None:
@@ -185,6 +197,9 @@ class MLCEngineBase:
         self._threaded.exit_background_loop()
         for t in self._threads:
             t.join(timeout=10)
+        workers = getattr(self, "_workers", None)
+        if workers is not None:
+            workers.shutdown()
 
     def __del__(self):
         try:

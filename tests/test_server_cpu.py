@@ -1,0 +1,81 @@
+"""REST server over a tiny random model on CPU: OpenAI endpoints, SSE framing, metrics, debug."""
+import json
+import socket
+
+import pytest
+import requests
+
+from mlc_llm_b200.serve.server import PopenServer
+
+MODEL = "random://tiny-llama?quant=q0f32&seed=3"
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.fixture(scope="module")
+def server():
+    srv = PopenServer(MODEL, "cpu", mode="local", port=_port(), enable_debug=True, enable_tracing=True,
+                      api_key="sekret")
+    srv.start(timeout=180)
+    yield srv
+    srv.terminate()
+
+
+H = {"Authorization": "Bearer sekret"}
+
+
+def test_models_and_auth(server):
+    r = requests.get(server.base_url + "/v1/models", headers=H, timeout=30)
+    assert r.status_code == 200 and r.json()["data"][0]["id"] == MODEL
+    assert requests.get(server.base_url + "/v1/models", timeout=30).status_code == 401
+
+
+def test_completion_and_usage(server):
+    body = {"model": MODEL, "prompt": [5, 6, 7, 8, 9], "max_tokens": 6, "temperature": 0.0,
+            "debug_config": {"ignore_eos": True}}
+    r = requests.post(server.base_url + "/v1/completions", json=body, headers=H, timeout=120)
+    assert r.status_code == 200, r.text
+    out = r.json()
+    assert out["object"] == "text_completion"
+    assert out["usage"]["prompt_tokens"] == 5 and out["usage"]["completion_tokens"] == 6
+    assert out["choices"][0]["finish_reason"] == "length"
+    # same request again is deterministic
+    r2 = requests.post(server.base_url + "/v1/completions", json=body, headers=H, timeout=120)
+    assert r2.json()["choices"][0]["text"] == out["choices"][0]["text"]
+
+
+def test_chat_stream_sse(server):
+    body = {"model": MODEL, "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 5,
+            "stream": True, "stream_options": {"include_usage": True}, "n": 2, "seed": 1}
+    with requests.post(server.base_url + "/v1/chat/completions", json=body, headers=H, stream=True,
+                       timeout=120) as r:
+        assert r.status_code == 200
+        assert r.headers["content-type"].startswith("text/event-stream")
+        lines = [ln.decode() for ln in r.iter_lines() if ln]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(ln[len("data: "):]) for ln in lines[:-1]]
+    assert all(c["object"] == "chat.completion.chunk" for c in chunks)
+    finished = {ch["index"] for c in chunks for ch in c["choices"] if ch["finish_reason"]}
+    assert finished == {0, 1}
+    assert chunks[-1]["usage"]["completion_tokens"] > 0 and chunks[-1]["choices"] == []
+
+
+def test_bad_request_is_400(server):
+    body = {"model": MODEL, "messages": [{"role": "user", "content": "x"}], "max_tokens": 4, "temperature": -1}
+    r = requests.post(server.base_url + "/v1/chat/completions", json=body, headers=H, timeout=60)
+    assert r.status_code in (400, 422)
+
+
+def test_metrics_and_debug(server):
+    r = requests.get(server.base_url + "/metrics", timeout=30)
+    assert r.status_code == 200 and "prefill_tokens_sum" in r.text
+    r = requests.post(server.base_url + "/debug/dump_event_trace", json={"model": MODEL}, timeout=30)
+    assert r.status_code == 200 and isinstance(r.json(), (list, dict))
+    r = requests.post(server.base_url + "/debug/dump_engine_metrics", json={"model": MODEL}, timeout=30)
+    assert r.status_code == 200 and "engine_prefill_time_sum" in r.json()
+    r = requests.post(server.base_url + "/debug/reset_engine", json={"model": MODEL}, timeout=30)
+    assert r.status_code == 200
