@@ -1,0 +1,63 @@
+"""``convert_weight``: HuggingFace checkpoint -> quantised tensor cache (reference:
+``python/mlc_llm/interface/convert_weight.py:32-216``).  Tensors are renamed / fused, quantised one
+at a time on ``device`` (the GPU when present) and streamed into ``params_shard_*.bin``."""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import quantization as Q
+from ..loader import huggingface_loader
+from ..loader.tensor_cache import dump_tensor_cache
+from ..models import config as model_config
+from ..models.loader import export_params
+from ..support.auto_config import detect_config, detect_device, detect_model_type, detect_weight
+
+
+def convert_weight(config: str, quantization: str, model_type: str = "auto", device: str = "auto",
+                   source: str = "auto", source_format: str = "auto", output: str = ".",
+                   lora_adapter: Optional[str] = None, verbose: bool = True,
+                   encode_format: str = "f32-to-bf16") -> dict:
+    if lora_adapter is not None:
+        raise ValueError("merging LoRA adapters is not supported by this build")
+    config_path, hf = detect_config(config)
+    mt = detect_model_type(model_type, hf)
+    quant = Q.get(quantization)
+    cfg = model_config.from_dict(mt, hf)
+    dev = detect_device(device)
+    src_dir, _fmt = detect_weight(source, config_path, source_format)
+    os.makedirs(output, exist_ok=True)
+    stats = {"params": 0, "bytes": 0}
+
+    def on_device():
+        for name, t in huggingface_loader.iter_mlc_params(src_dir, cfg):
+            yield name, t.to(dev)
+
+    def records():
+        for name, t in export_params(cfg, quant, on_device()):
+            t = t.cpu()
+            stats["bytes"] += t.numel() * t.element_size()
+            if not (name.endswith("q_scale") or name.endswith("weight_scale_inv")):
+                per_word = 32 // quant.bits if name.endswith("q_weight") and quant.kind == "group-quant" else 1
+                stats["params"] += t.numel() * per_word
+            if verbose:
+                print(f"[convert_weight] {name} {tuple(t.shape)} {t.dtype}")
+            yield name, t
+
+    doc = dump_tensor_cache(records(), output, encode_format=encode_format)
+    total_params, total_bytes = stats["params"], stats["bytes"]
+    bits = total_bytes * 8.0 / max(1, total_params)
+    doc["metadata"].update({"ParamSize": sum(len(s["records"]) for s in doc["records"]),
+                            "ParamBytes": float(total_bytes), "BitsPerParam": bits})
+    import json  # pylint: disable=import-outside-toplevel
+
+    with open(os.path.join(output, "tensor-cache.json"), "w", encoding="utf-8") as f:
+        json.dump(doc, f, indent=2)
+    if verbose:
+        print(f"[convert_weight] {total_params / 1e9:.3f} B parameters, {total_bytes / 2**30:.3f} GiB, "
+              f"{bits:.3f} bits per parameter -> {output}")
+    _ = torch
+    return {"params": total_params, "bytes": total_bytes, "bits_per_param": bits}

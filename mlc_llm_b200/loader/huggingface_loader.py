@@ -1,0 +1,342 @@
+"""Read HuggingFace checkpoints (safetensors or torch ``.bin`` shards) and rename / fuse their
+tensors into this framework's parameter set.
+
+Reference: ``python/mlc_llm/loader/huggingface_loader.py:26-228`` (lazy shard loading ordered for
+file locality, quantise while loading) and ``loader/standard_loader.py:23-152`` (q/k/v concatenated
+on axis 0 into ``qkv_proj``; gate/up concatenated into ``gate_up_proj``) plus the per-model
+``*_loader.py`` files.  Here one table per naming family produces, for every destination tensor, the
+source names and the function that combines them.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict, Iterator, List, Optional, Tuple
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.transformer import param_specs
+
+Combine = Callable[[List[torch.Tensor]], torch.Tensor]
+
+
+def _cat0(ts: List[torch.Tensor]) -> torch.Tensor:
+    return torch.cat(ts, dim=0)
+
+
+def _first(ts: List[torch.Tensor]) -> torch.Tensor:
+    return ts[0]
+
+
+def _t(ts: List[torch.Tensor]) -> torch.Tensor:
+    return ts[0].t().contiguous()
+
+
+class Mapping:
+    """destination name -> (source names, combine)."""
+
+    def __init__(self) -> None:
+        self.items: Dict[str, Tuple[List[str], Combine]] = {}
+
+    def add(self, dst: str, srcs: List[str], fn: Combine = _first) -> None:
+        self.items[dst] = (srcs, fn)
+
+
+# ------------------------------------------------------------------------------------ family tables
+def _llama_like(cfg: ModelConfig, m: Mapping, *, prefix: str = "model.", attn: str = "self_attn",
+                q="q_proj", k="k_proj", v="v_proj", o="o_proj", mlp="mlp", gate="gate_proj", up="up_proj",
+                down="down_proj", in_norm="input_layernorm", post_norm="post_attention_layernorm",
+                final_norm="norm", embed="embed_tokens", head="lm_head") -> None:
+    specs = param_specs(cfg)
+
+    def has(name: str) -> bool:
+        return name in specs
+
+    m.add("model.embed_tokens.weight", [f"{prefix}{embed}.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, d = f"{prefix}layers.{i}.", f"model.layers.{i}."
+        for suffix in ("weight", "bias"):
+            if has(d + f"self_attn.qkv_proj.{suffix}"):
+                m.add(d + f"self_attn.qkv_proj.{suffix}",
+                      [f"{s}{attn}.{q}.{suffix}", f"{s}{attn}.{k}.{suffix}", f"{s}{attn}.{v}.{suffix}"], _cat0)
+            if has(d + f"self_attn.o_proj.{suffix}"):
+                m.add(d + f"self_attn.o_proj.{suffix}", [f"{s}{attn}.{o}.{suffix}"])
+            if has(d + f"input_layernorm.{suffix}"):
+                m.add(d + f"input_layernorm.{suffix}", [f"{s}{in_norm}.{suffix}"])
+            if has(d + f"post_attention_layernorm.{suffix}"):
+                m.add(d + f"post_attention_layernorm.{suffix}", [f"{s}{post_norm}.{suffix}"])
+            if has(d + f"pre_feedforward_layernorm.{suffix}"):
+                m.add(d + f"pre_feedforward_layernorm.{suffix}", [f"{s}pre_feedforward_layernorm.{suffix}"])
+            if has(d + f"post_feedforward_layernorm.{suffix}"):
+                m.add(d + f"post_feedforward_layernorm.{suffix}", [f"{s}post_feedforward_layernorm.{suffix}"])
+            if has(d + f"mlp.gate_up_proj.{suffix}"):
+                m.add(d + f"mlp.gate_up_proj.{suffix}", [f"{s}{mlp}.{gate}.{suffix}", f"{s}{mlp}.{up}.{suffix}"], _cat0)
+            if has(d + f"mlp.up_proj.{suffix}"):
+                m.add(d + f"mlp.up_proj.{suffix}", [f"{s}{mlp}.{up}.{suffix}"])
+            if has(d + f"mlp.down_proj.{suffix}"):
+                m.add(d + f"mlp.down_proj.{suffix}", [f"{s}{mlp}.{down}.{suffix}"])
+        if cfg.qk_norm:
+            m.add(d + "self_attn.q_norm.weight", [f"{s}{attn}.q_norm.weight"])
+            m.add(d + "self_attn.k_norm.weight", [f"{s}{attn}.k_norm.weight"])
+    for suffix in ("weight", "bias"):
+        if has(f"model.norm.{suffix}"):
+            m.add(f"model.norm.{suffix}", [f"{prefix}{final_norm}.{suffix}"])
+    if has("lm_head.weight"):
+        m.add("lm_head.weight", [f"{head}.weight"])
+    if has("lm_head.bias"):
+        m.add("lm_head.bias", [f"{head}.bias"])
+
+
+def _moe_layers(cfg: ModelConfig, m: Mapping, style: str) -> None:
+    """Stack per-expert HF matrices into ``e1_e3`` [E, 2I, H] (gate rows then up rows) and ``e2``
+    [E, H, I] (reference: ``model/mixtral/mixtral_loader.py``, ``qwen2_moe_loader.py``)."""
+    e = cfg.num_experts
+
+    def stack13(ts: List[torch.Tensor]) -> torch.Tensor:
+        return torch.stack([torch.cat([ts[2 * j], ts[2 * j + 1]], dim=0) for j in range(e)], dim=0)
+
+    def stack(ts: List[torch.Tensor]) -> torch.Tensor:
+        return torch.stack(ts, dim=0)
+
+    for i in range(cfg.num_hidden_layers):
+        if not cfg.is_moe_layer(i):
+            continue
+        d = f"model.layers.{i}.moe."
+        if style == "mixtral":
+            s = f"model.layers.{i}.block_sparse_moe."
+            g, u, dn = "w1", "w3", "w2"
+            m.add(d + "gate.weight", [s + "gate.weight"])
+        else:
+            s = f"model.layers.{i}.mlp."
+            g, u, dn = "gate_proj", "up_proj", "down_proj"
+            m.add(d + "gate.weight", [s + "gate.weight"])
+        srcs13 = []
+        for j in range(e):
+            srcs13 += [f"{s}experts.{j}.{g}.weight", f"{s}experts.{j}.{u}.weight"]
+        m.add(d + "e1_e3.weight", srcs13, stack13)
+        m.add(d + "e2.weight", [f"{s}experts.{j}.{dn}.weight" for j in range(e)], stack)
+        if cfg.shared_expert_intermediate_size > 0:
+            m.add(d + "shared_expert.gate_up_proj.weight",
+                  [s + "shared_expert.gate_proj.weight", s + "shared_expert.up_proj.weight"], _cat0)
+            m.add(d + "shared_expert.down_proj.weight", [s + "shared_expert.down_proj.weight"])
+            if cfg.shared_expert_gate:
+                m.add(d + "shared_expert_gate.weight", [s + "shared_expert_gate.weight"])
+
+
+def _phi3(cfg: ModelConfig, m: Mapping) -> None:
+    _llama_like(cfg, m)
+    for i in range(cfg.num_hidden_layers):
+        m.add(f"model.layers.{i}.self_attn.qkv_proj.weight", [f"model.layers.{i}.self_attn.qkv_proj.weight"])
+        m.add(f"model.layers.{i}.mlp.gate_up_proj.weight", [f"model.layers.{i}.mlp.gate_up_proj.weight"])
+
+
+def _gpt2(cfg: ModelConfig, m: Mapping) -> None:
+    """GPT-2 stores Conv1D weights as [in, out]; they are transposed here (reference:
+    ``model/gpt2/gpt2_loader.py``)."""
+    pre = "transformer." if cfg.extra.get("hf_prefix", True) else ""
+    m.add("model.embed_tokens.weight", [pre + "wte.weight"])
+    m.add("model.embed_positions.weight", [pre + "wpe.weight"])
+    conv1d = cfg.model_type == "gpt2"
+    tw = _t if conv1d else _first
+    for i in range(cfg.num_hidden_layers):
+        s, d = f"{pre}h.{i}.", f"model.layers.{i}."
+        m.add(d + "input_layernorm.weight", [s + "ln_1.weight"])
+        m.add(d + "input_layernorm.bias", [s + "ln_1.bias"])
+        m.add(d + "self_attn.qkv_proj.weight", [s + "attn.c_attn.weight"], tw)
+        m.add(d + "self_attn.qkv_proj.bias", [s + "attn.c_attn.bias"])
+        m.add(d + "self_attn.o_proj.weight", [s + "attn.c_proj.weight"], tw)
+        m.add(d + "self_attn.o_proj.bias", [s + "attn.c_proj.bias"])
+        m.add(d + "post_attention_layernorm.weight", [s + "ln_2.weight"])
+        m.add(d + "post_attention_layernorm.bias", [s + "ln_2.bias"])
+        m.add(d + "mlp.up_proj.weight", [s + "mlp.c_fc.weight"], tw)
+        m.add(d + "mlp.up_proj.bias", [s + "mlp.c_fc.bias"])
+        m.add(d + "mlp.down_proj.weight", [s + "mlp.c_proj.weight"], tw)
+        m.add(d + "mlp.down_proj.bias", [s + "mlp.c_proj.bias"])
+    m.add("model.norm.weight", [pre + "ln_f.weight"])
+    m.add("model.norm.bias", [pre + "ln_f.bias"])
+
+
+def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
+    """GPT-NeoX interleaves q, k, v per head inside ``query_key_value`` ([heads, 3, d, hidden]); they
+    are regrouped into [q; k; v] (reference: ``model/gpt_neox/gpt_neox_loader.py``)."""
+    hq, d = cfg.num_attention_heads, cfg.head_dim
+
+    def regroup_w(ts):
+        w = ts[0].view(hq, 3, d, -1)
+        return torch.cat([w[:, 0].reshape(hq * d, -1), w[:, 1].reshape(hq * d, -1), w[:, 2].reshape(hq * d, -1)], 0)
+
+    def regroup_b(ts):
+        b = ts[0].view(hq, 3, d)
+        return torch.cat([b[:, 0].reshape(-1), b[:, 1].reshape(-1), b[:, 2].reshape(-1)], 0)
+
+    m.add("model.embed_tokens.weight", ["gpt_neox.embed_in.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, dd = f"gpt_neox.layers.{i}.", f"model.layers.{i}."
+        for suffix in ("weight", "bias"):
+            m.add(dd + f"input_layernorm.{suffix}", [s + f"input_layernorm.{suffix}"])
+            m.add(dd + f"post_attention_layernorm.{suffix}", [s + f"post_attention_layernorm.{suffix}"])
+            m.add(dd + f"self_attn.o_proj.{suffix}", [s + f"attention.dense.{suffix}"])
+            m.add(dd + f"mlp.up_proj.{suffix}", [s + f"mlp.dense_h_to_4h.{suffix}"])
+            m.add(dd + f"mlp.down_proj.{suffix}", [s + f"mlp.dense_4h_to_h.{suffix}"])
+        m.add(dd + "self_attn.qkv_proj.weight", [s + "attention.query_key_value.weight"], regroup_w)
+        m.add(dd + "self_attn.qkv_proj.bias", [s + "attention.query_key_value.bias"], regroup_b)
+    m.add("model.norm.weight", ["gpt_neox.final_layer_norm.weight"])
+    m.add("model.norm.bias", ["gpt_neox.final_layer_norm.bias"])
+    m.add("lm_head.weight", ["embed_out.weight"])
+
+
+def _phi(cfg: ModelConfig, m: Mapping) -> None:
+    _llama_like(cfg, m, mlp="mlp", up="fc1", down="fc2", final_norm="final_layernorm")
+    for i in range(cfg.num_hidden_layers):
+        for suffix in ("weight", "bias"):
+            m.add(f"model.layers.{i}.self_attn.o_proj.{suffix}", [f"model.layers.{i}.self_attn.dense.{suffix}"])
+
+
+def _internlm2(cfg: ModelConfig, m: Mapping) -> None:
+    """InternLM2 packs ``wqkv`` per KV group as [groups, q_per_group + 2, d, hidden] (reference:
+    ``model/internlm2/internlm2_loader.py``)."""
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per = hq // hkv
+
+    def regroup(ts):
+        w = ts[0].view(hkv, per + 2, d, -1)
+        q = w[:, :per].reshape(hq * d, -1)
+        k = w[:, per].reshape(hkv * d, -1)
+        v = w[:, per + 1].reshape(hkv * d, -1)
+        return torch.cat([q, k, v], 0)
+
+    m.add("model.embed_tokens.weight", ["model.tok_embeddings.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, dd = f"model.layers.{i}.", f"model.layers.{i}."
+        m.add(dd + "input_layernorm.weight", [s + "attention_norm.weight"])
+        m.add(dd + "post_attention_layernorm.weight", [s + "ffn_norm.weight"])
+        m.add(dd + "self_attn.qkv_proj.weight", [s + "attention.wqkv.weight"], regroup)
+        m.add(dd + "self_attn.o_proj.weight", [s + "attention.wo.weight"])
+        m.add(dd + "mlp.gate_up_proj.weight", [s + "feed_forward.w1.weight", s + "feed_forward.w3.weight"], _cat0)
+        m.add(dd + "mlp.down_proj.weight", [s + "feed_forward.w2.weight"])
+    m.add("model.norm.weight", ["model.norm.weight"])
+    m.add("lm_head.weight", ["output.weight"])
+
+
+def _baichuan(cfg: ModelConfig, m: Mapping) -> None:
+    _llama_like(cfg, m)
+    for i in range(cfg.num_hidden_layers):
+        m.add(f"model.layers.{i}.self_attn.qkv_proj.weight", [f"model.layers.{i}.self_attn.W_pack.weight"])
+
+
+def build_mapping(cfg: ModelConfig) -> Mapping:
+    m = Mapping()
+    mt = cfg.model_type
+    if mt in ("gpt2", "gpt_bigcode"):
+        _gpt2(cfg, m)
+    elif mt == "gpt_neox":
+        _gpt_neox(cfg, m)
+    elif mt == "phi3":
+        _phi3(cfg, m)
+    elif mt in ("phi", "phi-msft"):
+        _phi(cfg, m)
+    elif mt == "internlm2":
+        _internlm2(cfg, m)
+    elif mt == "baichuan":
+        _baichuan(cfg, m)
+    elif mt == "starcoder2":
+        _llama_like(cfg, m, up="c_fc", down="c_proj")
+    elif mt == "mixtral":
+        _llama_like(cfg, m)
+        _moe_layers(cfg, m, "mixtral")
+    elif mt in ("qwen2_moe", "qwen3_moe"):
+        _llama_like(cfg, m)
+        _moe_layers(cfg, m, "qwen")
+    else:
+        _llama_like(cfg, m)
+    # drop destinations the architecture does not have (e.g. dense MLP names on MoE layers)
+    specs = param_specs(cfg)
+    m.items = {k: v for k, v in m.items.items() if k in specs}
+    missing = [k for k in specs if k not in m.items]
+    if missing:
+        raise ValueError(f"no HuggingFace source known for parameters {missing[:5]} of model type {mt}")
+    return m
+
+
+# ------------------------------------------------------------------------------------ tensor source
+class HFCheckpoint:
+    """Name -> tensor view over the shards of a HuggingFace checkpoint directory; one shard is open
+    at a time."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self.name_to_file: Dict[str, str] = {}
+        st_index = os.path.join(path, "model.safetensors.index.json")
+        pt_index = os.path.join(path, "pytorch_model.bin.index.json")
+        if os.path.isfile(st_index):
+            self.name_to_file = dict(json.load(open(st_index, encoding="utf-8"))["weight_map"])
+        elif os.path.isfile(os.path.join(path, "model.safetensors")):
+            from safetensors import safe_open  # pylint: disable=import-outside-toplevel
+
+            with safe_open(os.path.join(path, "model.safetensors"), "pt") as f:
+                self.name_to_file = {k: "model.safetensors" for k in f.keys()}
+        elif os.path.isfile(pt_index):
+            self.name_to_file = dict(json.load(open(pt_index, encoding="utf-8"))["weight_map"])
+        elif os.path.isfile(os.path.join(path, "pytorch_model.bin")):
+            sd = torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu", weights_only=True)
+            self.name_to_file = {k: "pytorch_model.bin" for k in sd}
+            self._open_file, self._open = "pytorch_model.bin", sd
+        else:
+            raise FileNotFoundError(f"no safetensors or torch checkpoint found under {path}")
+        if not hasattr(self, "_open_file"):
+            self._open_file: Optional[str] = None
+            self._open = None
+
+    def _load_file(self, fname: str) -> None:
+        if self._open_file == fname:
+            return
+        full = os.path.join(self.path, fname)
+        if fname.endswith(".safetensors"):
+            from safetensors.torch import load_file  # pylint: disable=import-outside-toplevel
+
+            self._open = load_file(full)
+        else:
+            self._open = torch.load(full, map_location="cpu", weights_only=True)
+        self._open_file = fname
+
+    def resolve(self, name: str) -> Optional[str]:
+        """Checkpoints differ in whether names carry the ``model.`` / ``transformer.`` prefix."""
+        if name in self.name_to_file:
+            return name
+        for alt in (name.removeprefix("model."), "model." + name, name.removeprefix("transformer."),
+                    "transformer." + name, "model.language_model." + name.removeprefix("model."),
+                    "language_model." + name):
+            if alt in self.name_to_file:
+                return alt
+        return None
+
+    def get(self, name: str) -> torch.Tensor:
+        real = self.resolve(name)
+        if real is None:
+            raise KeyError(name)
+        self._load_file(self.name_to_file[real])
+        return self._open[real]
+
+
+def iter_mlc_params(path: str, cfg: ModelConfig) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Yield (destination name, full-precision tensor), ordered so that tensors sharing a shard file
+    are produced together."""
+    ckpt = HFCheckpoint(path)
+    mapping = build_mapping(cfg)
+    tied_head = None
+
+    def file_key(item):
+        srcs = item[1][0]
+        real = ckpt.resolve(srcs[0])
+        return (ckpt.name_to_file.get(real, "~") if real else "~", item[0])
+
+    for dst, (srcs, fn) in sorted(mapping.items.items(), key=file_key):
+        if dst == "lm_head.weight" and ckpt.resolve(srcs[0]) is None:
+            tied_head = dst  # checkpoint ties the head to the embedding without saying so
+            continue
+        yield dst, fn([ckpt.get(s) for s in srcs])
+    if tied_head is not None:
+        emb_src = mapping.items["model.embed_tokens.weight"][0][0]
+        yield tied_head, ckpt.get(emb_src)

@@ -115,6 +115,15 @@ def _get(cfg: Dict[str, Any], *names, default=None):
 
 def _common(cfg: Dict[str, Any], model_type: str) -> Dict[str, Any]:
     """Fields spelled the same way by most HuggingFace configs."""
+    rp = cfg.get("rope_parameters")
+    if isinstance(rp, dict):  # newer transformers nest the rotary settings
+        cfg = dict(cfg)
+        if "rope_theta" in rp and cfg.get("rope_theta") is None:
+            cfg["rope_theta"] = rp["rope_theta"]
+        if rp.get("rope_type", "default") != "default" and cfg.get("rope_scaling") is None:
+            cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+        if "partial_rotary_factor" in rp and cfg.get("partial_rotary_factor") is None:
+            cfg["partial_rotary_factor"] = rp["partial_rotary_factor"]
     out = dict(
         model_type=model_type,
         hidden_size=_get(cfg, "hidden_size", "n_embd", "d_model", default=4096),
@@ -254,7 +263,7 @@ def _olmo(cfg, mt):
         d["qk_norm"] = True
         d["post_attention_norm"] = True
         d["post_mlp_norm"] = True
-        d["extra"] = {"no_pre_norm": True}
+        d["extra"] = {"no_pre_norm": True, "qk_norm_full": True}
     else:
         d["norm_type"] = "layernorm"
         d["extra"] = {"norm_no_affine": True}
@@ -272,7 +281,7 @@ def _mixtral(cfg, mt):
 
 def _qwen_moe(cfg, mt):
     d = _common(cfg, mt)
-    d.update(num_experts=_get(cfg, "num_experts", default=60),
+    d.update(num_experts=_get(cfg, "num_experts", "num_local_experts", default=60),
              num_experts_per_tok=_get(cfg, "num_experts_per_tok", default=4),
              moe_intermediate_size=_get(cfg, "moe_intermediate_size", default=1408),
              norm_topk_prob=bool(_get(cfg, "norm_topk_prob", default=False)),

@@ -292,3 +292,28 @@ def export_params(cfg: ModelConfig, quant: Q.Quantization, named_full: Iterator[
                 yield base + ".q_scale", sc
                 continue
         yield name, w.to(quant.torch_dtype)
+
+
+def load_hf_params(hf_dir: str, cfg: ModelConfig, quant: Q.Quantization, device: torch.device,
+                   tp: int = 1, rank: int = 0, layers: Optional[range] = None) -> ParamStore:
+    """Build the run-time parameters straight from a HuggingFace checkpoint, quantising on the fly
+    (the in-memory form of ``convert_weight`` followed by ``load_params``)."""
+    from ..loader.huggingface_loader import iter_mlc_params  # pylint: disable=import-outside-toplevel
+
+    layers = layers if layers is not None else range(cfg.num_hidden_layers)
+    specs = param_specs(cfg)
+    store = ParamStore()
+    biases: Dict[str, torch.Tensor] = {}
+    ep = cfg.expert_parallel and tp > 1
+    for name, w in iter_mlc_params(hf_dir, cfg):
+        if not _wanted(name, cfg, layers):
+            continue
+        kind = specs[name][1]
+        w = _shard_dense(name, w.to(device if device.type == "cuda" else "cpu"), kind, cfg, tp, rank, ep)
+        _store(store, name, kind, w, quant, device, biases)
+    for base, b in biases.items():
+        if base in store.linears:
+            store.linears[base].bias = b
+        else:
+            store.tensors[base + ".bias"] = b
+    return store

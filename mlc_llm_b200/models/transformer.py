@@ -143,16 +143,23 @@ class DecoderModel:
         c = self.cfg
         table = self.p.linears.get("model.embed_tokens") or self.p.tensors["model.embed_tokens.weight"]
         x = ops.embed(token_ids, table, c.hidden_size, self.dtype, c.embedding_scale)
-        if c.position_embedding == "learned":
-            raise RuntimeError("learned positions are added in forward() where positions are known")
-        return x
+        return x  # learned positions are added in forward(), where positions are known
 
     def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
         c = self.cfg
         pre = f"model.layers.{li}.self_attn."
         qkv = ops.linear(h, self.p.linears[pre + "qkv_proj"])
         hq, hkv, d = self.hq, self.hkv, self.d
-        if c.qk_norm:
+        if c.qk_norm and c.extra.get("qk_norm_full"):
+            # OLMo-2 normalises the whole q / k projection, not each head
+            if self.tp > 1:
+                raise NotImplementedError("full-width q/k norm is not supported with tensor parallelism")
+            nq, nk = hq * d, hkv * d
+            qkv[:, :nq] = ops.rmsnorm(qkv[:, :nq].contiguous(), self.p.tensors[pre + "q_norm.weight"],
+                                      c.rms_norm_eps, c.norm_weight_offset)
+            qkv[:, nq:nq + nk] = ops.rmsnorm(qkv[:, nq:nq + nk].contiguous(), self.p.tensors[pre + "k_norm.weight"],
+                                             c.rms_norm_eps, c.norm_weight_offset)
+        elif c.qk_norm:
             t = qkv.shape[0]
             heads = qkv.view(t, hq + 2 * hkv, d)
             qn = ops.rmsnorm(heads[:, :hq].reshape(-1, d), self.p.tensors[pre + "q_norm.weight"],
@@ -313,8 +320,9 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
         if cfg.attention_out_bias:
             specs[p + "self_attn.o_proj.bias"] = ((h,), "bias")
         if cfg.qk_norm:
-            specs[p + "self_attn.q_norm.weight"] = ((d,), "norm")
-            specs[p + "self_attn.k_norm.weight"] = ((d,), "norm")
+            full = bool(cfg.extra.get("qk_norm_full"))
+            specs[p + "self_attn.q_norm.weight"] = ((hq * d if full else d,), "norm")
+            specs[p + "self_attn.k_norm.weight"] = ((hkv * d if full else d,), "norm")
         if not (cfg.parallel_residual and cfg.shared_input_norm):
             norm(p + "post_attention_layernorm")
         if cfg.post_attention_norm and not cfg.extra.get("no_pre_norm"):

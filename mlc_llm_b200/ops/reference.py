@@ -98,8 +98,9 @@ def rope_append(qkv: torch.Tensor, kv_pages: torch.Tensor, pos: torch.Tensor, sl
         half = rot_dim // 2
         qk = heads[:, : hq + hkv, :rot_dim].float()
         a, b = qk[..., :half], qk[..., half:]
-        heads[:, : hq + hkv, :half] = (a * cos - b * sin).to(qkv.dtype)
-        heads[:, : hq + hkv, half:rot_dim] = (b * cos + a * sin).to(qkv.dtype)
+        lo, hi = a * cos - b * sin, b * cos + a * sin  # both before writing: qk aliases heads in fp32
+        heads[:, : hq + hkv, :half] = lo.to(qkv.dtype)
+        heads[:, : hq + hkv, half:rot_dim] = hi.to(qkv.dtype)
     valid = slot >= 0
     if valid.any():
         sl = slot[valid].long()
