@@ -47,6 +47,7 @@ class ModelInfo:
     model_path: Optional[str]
     chat_config: Dict[str, Any]
     random_seed: Optional[int] = None  # set for "random://" models
+    hf_weights: bool = False  # model_path is an unconverted HuggingFace checkpoint
 
 
 def _random_model_chat_config(spec: str) -> Tuple[Dict[str, Any], int]:
@@ -96,6 +97,8 @@ def resolve_model(model: str) -> ModelInfo:
     if os.path.isfile(model_path):
         model_path = os.path.dirname(model_path)
     cfg_path = os.path.join(model_path, "mlc-chat-config.json")
+    if not os.path.exists(cfg_path) and os.path.exists(os.path.join(model_path, "config.json")):
+        return _resolve_hf_checkpoint(model, model_path)
     if not os.path.exists(cfg_path):
         raise FileNotFoundError(f"Cannot find mlc-chat-config.json under {model_path}")
     with open(cfg_path, encoding="utf-8") as f:
@@ -103,6 +106,38 @@ def resolve_model(model: str) -> ModelInfo:
     for k, v in MLC_CHAT_SYSTEM_DEFAULT.items():
         chat.setdefault(k, v)
     return ModelInfo(model, model_path, chat)
+
+
+_DEFAULT_CONV = {"llama": "llama-2", "mistral": "mistral_default", "mixtral": "mistral_default",
+                 "qwen2": "qwen2", "qwen3": "qwen3", "qwen2_moe": "qwen2", "qwen3_moe": "qwen3",
+                 "gemma": "gemma_instruction", "gemma2": "gemma_instruction", "gemma3": "gemma3_instruction",
+                 "phi3": "phi-3", "phi": "phi-2", "gpt2": "gpt2", "gpt_bigcode": "gpt_bigcode"}
+
+
+def _resolve_hf_checkpoint(model: str, model_path: str) -> ModelInfo:
+    """Serve an unconverted HuggingFace directory: the chat config is generated in memory
+    (``gen_config`` defaults; quantisation from ``MLC_JIT_QUANTIZATION`` or the checkpoint dtype) and
+    weights are quantised while loading — the counterpart of the reference's JIT path
+    (``serve/engine_base.py:155-175``, ``interface/jit.py``)."""
+    import tempfile  # pylint: disable=import-outside-toplevel
+
+    from ..interface.gen_config import gen_config  # pylint: disable=import-outside-toplevel
+
+    with open(os.path.join(model_path, "config.json"), encoding="utf-8") as f:
+        hf = json.load(f)
+    dtype = str(hf.get("torch_dtype", hf.get("dtype", "float16")))
+    quant = os.environ.get("MLC_JIT_QUANTIZATION") or {"bfloat16": "q0bf16", "float32": "q0f32"}.get(dtype, "q0f16")
+    mt = hf.get("model_type", "llama")
+    conv = os.environ.get("MLC_JIT_CONV_TEMPLATE") or _DEFAULT_CONV.get(mt, "LM")
+    if "llama" == mt and int(hf.get("vocab_size", 0)) > 100000:
+        conv = "llama-3"
+    with tempfile.TemporaryDirectory() as tmp:
+        path = gen_config(model_path, "auto", quant, conv, None, None, None, None, None, None, None, 128, tmp)
+        with open(path, encoding="utf-8") as f:
+            chat = json.load(f)
+    for k, v in MLC_CHAT_SYSTEM_DEFAULT.items():
+        chat.setdefault(k, v)
+    return ModelInfo(model, model_path, chat, None, True)
 
 
 def conversation_of(chat_config: Dict[str, Any]) -> Conversation:
@@ -248,6 +283,8 @@ class EngineRuntime:
             layers = range(part[pp_rank], part[pp_rank + 1]) if mi == 0 else range(mcfg.num_hidden_layers)
             if info.random_seed is not None:
                 store = model_loader.random_params(mcfg, quant, info.random_seed, self.device, tp, tp_rank, layers)
+            elif info.hf_weights:
+                store = model_loader.load_hf_params(info.model_path, mcfg, quant, self.device, tp, tp_rank, layers)
             else:
                 store = model_loader.load_params(info.model_path, mcfg, quant, self.device, tp, tp_rank, layers)
             model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)

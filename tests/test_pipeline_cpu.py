@@ -1,0 +1,131 @@
+"""Offline pipeline on CPU: HuggingFace checkpoint -> gen_config -> convert_weight -> engine, checked
+against ``transformers`` greedy generation; plus compile metadata, chat REPL and the direct
+(unconverted) HuggingFace path."""
+import json
+import os
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+tokenizers = pytest.importorskip("tokenizers")
+
+from mlc_llm_b200.cli import compile as cli_compile  # noqa: E402
+from mlc_llm_b200.cli import convert_weight as cli_convert  # noqa: E402
+from mlc_llm_b200.cli import gen_config as cli_gen  # noqa: E402
+from mlc_llm_b200.interface.chat import ChatState  # noqa: E402
+from mlc_llm_b200.loader.tensor_cache import TensorCache  # noqa: E402
+from mlc_llm_b200.serve.config import EngineConfig  # noqa: E402
+from mlc_llm_b200.serve.engine import MLCEngine  # noqa: E402
+
+CORPUS = ["the quick brown fox jumps over the lazy dog", "hello world, this is a tiny tokenizer",
+          "serving large language models on fast hardware", "what is the capital of France?",
+          "numbers 0 1 2 3 4 5 6 7 8 9 and symbols !?.,;:"] * 4
+
+
+@pytest.fixture(scope="module")
+def hf_dir(tmp_path_factory):
+    d = tmp_path_factory.mktemp("hf")
+    tok = tokenizers.Tokenizer(tokenizers.models.BPE(unk_token=None))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    trainer = tokenizers.trainers.BpeTrainer(vocab_size=300, special_tokens=["<s>", "</s>", "<unk>"],
+                                             initial_alphabet=tokenizers.pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(CORPUS, trainer)
+    tok.save(str(d / "tokenizer.json"))
+    vocab = tok.get_vocab_size()
+    torch.manual_seed(1)
+    cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, vocab_size=vocab,
+                                   max_position_embeddings=256, bos_token_id=0, eos_token_id=1)
+    model = transformers.LlamaForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():  # larger weights -> confident argmax, stable under quantisation checks
+            p.mul_(8.0) if p.dim() > 1 else None
+    model.save_pretrained(d, safe_serialization=True)
+    return str(d), model, tok
+
+
+def test_gen_config_convert_and_generate(hf_dir, tmp_path):
+    src, hf_model, tok = hf_dir
+    out = str(tmp_path / "mlc")
+    cli_gen.main([src, "--quantization", "q0f32", "--conv-template", "LM", "--output", out])
+    chat = json.load(open(os.path.join(out, "mlc-chat-config.json")))
+    assert chat["model_type"] == "llama" and chat["quantization"] == "q0f32"
+    assert "tokenizer.json" in chat["tokenizer_files"] and os.path.exists(os.path.join(out, "tokenizer.json"))
+    assert chat["conv_template"]["name"] == "LM" and chat["vocab_size"] == tok.get_vocab_size()
+    from mlc_llm_b200.interface.convert_weight import convert_weight
+    convert_weight(src, "q0f32", output=out, verbose=False, encode_format="raw")
+    cache = TensorCache(out, verify_md5=True)
+    assert "model.layers.0.self_attn.qkv_proj.weight" in cache.names()
+    assert cache.metadata["ParamSize"] == len(cache.names())
+    engine = MLCEngine(out, "cpu", engine_config=EngineConfig(mode="local"))
+    try:
+        prompt = tok.encode("the quick brown fox").ids
+        want = hf_model.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False,
+                                 eos_token_id=None, pad_token_id=0)[0, len(prompt):].tolist()
+        resp = engine.completions.create(prompt=prompt, max_tokens=8, temperature=0.0,
+                                         debug_config={"ignore_eos": True})
+        assert resp.choices[0].text == tok.decode(want)
+        # text prompt goes through the real tokenizer and gives the same continuation
+        resp2 = engine.completions.create(prompt="the quick brown fox", max_tokens=8, temperature=0.0,
+                                          debug_config={"ignore_eos": True})
+        prefix = list(engine.conv_template.system_prefix_token_ids or [])
+        want2 = hf_model.generate(torch.tensor([prefix + prompt]), max_new_tokens=8, do_sample=False,
+                                  eos_token_id=None, pad_token_id=0)[0, len(prefix) + len(prompt):].tolist()
+        assert resp2.choices[0].text == tok.decode(want2)
+        assert resp2.usage.prompt_tokens == len(prefix) + len(prompt)
+        # chat REPL over the same engine
+        lines = []
+        state = ChatState(engine, write=lines.append)
+        assert state.handle("/set temperature=0;max_tokens=4")
+        assert state.handle("hello world")
+        assert len(state.history) == 2 and state.history[1]["role"] == "assistant"
+        assert state.handle("/stats") and "completion_tokens: 4" in "".join(lines)
+        assert state.handle("/reset") and not state.history
+        assert not state.handle("/exit")
+    finally:
+        engine.terminate()
+
+
+def test_quantized_convert_and_compile_metadata(hf_dir, tmp_path):
+    src, _, _ = hf_dir
+    out = str(tmp_path / "mlc-q4")
+    cli_gen.main([src, "--quantization", "q4f16_1", "--conv-template", "LM", "--output", out,
+                  "--context-window-size", "128"])
+    cli_convert.main([src, "--quantization", "q4f16_1", "--output", out, "--device", "cpu"])
+    cache = TensorCache(out)
+    names = cache.names()
+    assert "model.layers.1.mlp.gate_up_proj.q_weight" in names and "model.layers.1.mlp.gate_up_proj.q_scale" in names
+    qw = cache.get("model.layers.1.mlp.gate_up_proj.q_weight")
+    assert qw.shape == (256, 64 // 8)
+    assert 4.0 < cache.metadata["BitsPerParam"] < 6.5
+    lib = str(tmp_path / "lib.json")
+    cli_compile.main([out, "--output", lib])
+    meta = json.load(open(lib))
+    assert meta["quantization"] == "q4f16_1" and meta["context_window_size"] == 128
+    assert meta["kv_cache"]["num_key_value_heads"] == 2
+    engine = MLCEngine(out, "cpu", model_lib=lib, engine_config=EngineConfig(mode="local"))
+    try:
+        r = engine.chat.completions.create(messages=[{"role": "user", "content": "hello"}], max_tokens=5)
+        assert r.usage.completion_tokens <= 5 and r.choices[0].message.role == "assistant"
+    finally:
+        engine.terminate()
+
+
+def test_serve_unconverted_hf_directory(hf_dir):
+    src, hf_model, tok = hf_dir
+    os.environ["MLC_JIT_QUANTIZATION"] = "q0f32"
+    try:
+        engine = MLCEngine(src, "cpu", engine_config=EngineConfig(mode="local"))
+    finally:
+        del os.environ["MLC_JIT_QUANTIZATION"]
+    try:
+        prompt = tok.encode("hello world").ids
+        want = hf_model.generate(torch.tensor([prompt]), max_new_tokens=6, do_sample=False,
+                                 eos_token_id=None, pad_token_id=0)[0, len(prompt):].tolist()
+        resp = engine.completions.create(prompt=prompt, max_tokens=6, temperature=0.0,
+                                         debug_config={"ignore_eos": True})
+        assert resp.choices[0].text == tok.decode(want)
+    finally:
+        engine.terminate()
