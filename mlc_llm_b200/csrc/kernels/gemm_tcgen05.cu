@@ -34,8 +34,12 @@ constexpr int RAW_STAGES = 6; // packed-weight ring (q4): deeper, so TMA latency
 constexpr int X_STAGE_BYTES = MAX_TN * BK * 2;   // 32 KiB
 constexpr int W_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int RAW_STAGE_BYTES = BM * (BK / 2);   // 4 KiB of packed nibbles
-constexpr int GEMM_THREADS = 352;
-constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES) + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 512;
+constexpr int GEMM_THREADS = 352;      // dense kernel: warps 0-10
+constexpr int GEMM_THREADS_Q4 = 480;   // int4 kernel: plus a second dequant group, warps 11-14
+constexpr int SCALE_DEPTH = 8;                   // group scales are fetched this many K blocks ahead
+constexpr int SCALE_STAGE_BYTES = BM * 4;        // two fp16 scales per weight row and K block
+constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES) + RAW_STAGES * RAW_STAGE_BYTES +
+                          SCALE_DEPTH * SCALE_STAGE_BYTES + 1024 + 512;
 
 struct GemmParams {
   const void* scale;    // [N, K/32] fp16 (q4 only)
@@ -139,7 +143,7 @@ struct KCursor {
 };
 
 template <bool Q4>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(Q4 ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -148,7 +152,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   uint8_t* sx = smem;                                   // STAGES x 32 KiB
   uint8_t* sw = sx + STAGES * X_STAGE_BYTES;            // STAGES x 16 KiB
   uint8_t* sraw = sw + STAGES * W_STAGE_BYTES;          // RAW_STAGES x 4 KiB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sraw + RAW_STAGES * RAW_STAGE_BYTES);
+  uint8_t* sscale = sraw + RAW_STAGES * RAW_STAGE_BYTES;  // SCALE_DEPTH x 512 B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sscale + SCALE_DEPTH * SCALE_STAGE_BYTES);
   uint64_t* full = bars;                       // [STAGES] activation (and dense weight) tile landed
   uint64_t* empty = full + STAGES;             // [STAGES] MMA done reading the stage
   uint64_t* deq_full = empty + STAGES;         // [STAGES] expanded weight tile written
@@ -163,7 +168,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_kb = (p.K + BK - 1) / BK;
-  __shared__ int last_flag;
+  if (threadIdx.x == 0) GEMM_TRACE(7, 510);
   __shared__ int sh_num_items;
 
   if (threadIdx.x == 0) {
@@ -281,74 +286,93 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         if (ok) umma_commit(&acc_full[a]);
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 6 || warp >= 11) {
     // ------------------------------------------------------------ dequant warps (q4 only)
+    // Two groups of four warps (2-5 and 11-14) take alternate K blocks. One iteration is a chain of
+    // long-latency steps (barrier polls, shared loads, the proxy fence), about twice the time the
+    // tensor core needs for the block, so two chains in flight keep it fed.
     if (Q4) {
-      const int row = (warp - 2) * 32 + lane;  // 0..127 inside the tile
+      const int grp = warp >= 11 ? 1 : 0;
+      const int row = (warp - (grp ? 11 : 2)) * 32 + lane;  // 0..127 inside the tile
       const __half* scale = reinterpret_cast<const __half*>(p.scale);
       const int groups_per_row = p.K / 32;
-      uint32_t it = 0;
       bool ok = true;
-      // group scales of a K block: two fp16 values per row; fetched one iteration ahead so the
-      // global-load latency never sits on the dequant critical path
-      auto load_scale = [&](const KCursor& c) -> __half2 {
-        if (!c.valid(num_tiles)) return __floats2half2_rn(0.f, 0.f);
-        if (c.ti.nb * BM + row >= p.N) return __floats2half2_rn(0.f, 0.f);
-        const __half* sr = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row;
-        if (c.ka * 2 + 1 < groups_per_row) return *reinterpret_cast<const __half2*>(sr + c.ka * 2);
-        if (c.ka * 2 < groups_per_row) return __halves2half2(sr[c.ka * 2], __float2half(0.f));
-        return __floats2half2_rn(0.f, 0.f);
-      };
-      KCursor cs;
-      cs.init(p, total_kb, num_tiles);
-      __half2 sc_next = load_scale(cs);
-      for (; cs.valid(num_tiles) && ok; ++it) {
-        {
-          const int s = it % STAGES;
-          const int rs = it % RAW_STAGES;
-          const __half2 sc = sc_next;
-          cs.next(p, total_kb, num_tiles);
-          sc_next = load_scale(cs);
-          ok = mbar_wait(&raw_full[rs], (it / RAW_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
-          ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
-          if (!ok) break;
-          if (threadIdx.x == 64) GEMM_TRACE(4, it);
-          const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_STAGE_BYTES + row * 32);
-          uint4 r0 = raw[0], r1 = raw[1];
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&raw_empty[rs]);  // nibbles are in registers: recycle early
-          uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-          // the expanded tile may only be overwritten once the MMA that read it has finished
-          if (it >= STAGES) {
-            ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-          }
-          uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
-            const __half2 s2 = __half2half2(sv);
-            // 0x6400 | q is the fp16 value 1024 + q; subtracting 1031 is exact, so the product
-            // (q - 7) * s is rounded once
-            const __half2 off = __float2half2_rn(1031.f);
-            const uint32_t x = words[w];
-            uint32_t h[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              // device layout: nibble pair (2j, 2j+1) sits at bits [4j, 4j+4) and [16+4j, 20+4j)
-              uint32_t v = ((x >> (4 * j)) & 0x000f000fu) | 0x64006400u;
-              __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v), off), s2);
-              h[j] = *reinterpret_cast<uint32_t*>(&hv);
-            }
-            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
-                make_uint4(h[0], h[1], h[2], h[3]);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&deq_full[s]);
-          if (threadIdx.x == 64) GEMM_TRACE(5, it);
+      // Group scales of a K block: two fp16 values per row, copied into shared memory
+      // SCALE_DEPTH blocks ahead with cp.async (one commit group per own iteration).
+      const uint32_t my_scale = smem_u32(sscale) + row * 4;
+      auto fetch_scale = [&](const KCursor& c, uint32_t slot) {
+        const uint32_t dst = my_scale + slot * SCALE_STAGE_BYTES;
+        const bool live = c.valid(num_tiles) && (c.ti.nb * BM + row < p.N) && (c.ka * 2 + 1 < groups_per_row);
+        if (live) {
+          const __half* src = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row + c.ka * 2;
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+        } else {
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+      auto advance2 = [&](KCursor& c) {
+        if (c.valid(num_tiles)) c.next(p, total_kb, num_tiles);
+        if (c.valid(num_tiles)) c.next(p, total_kb, num_tiles);
+      };
+      KCursor cs, cp;
+      cs.init(p, total_kb, num_tiles);
+      if (grp && cs.valid(num_tiles)) cs.next(p, total_kb, num_tiles);
+      cp = cs;
+      for (int i = 0; i < SCALE_DEPTH / 2; ++i) {
+        fetch_scale(cp, grp + 2 * i);
+        advance2(cp);
+      }
+      for (uint32_t it = grp; cs.valid(num_tiles) && ok; it += 2) {
+        const int s = it % STAGES;
+        const int rs = it % RAW_STAGES;
+        const uint32_t slot = it % SCALE_DEPTH;
+        asm volatile("cp.async.wait_group %0;" ::"n"(SCALE_DEPTH / 2 - 1) : "memory");
+        uint32_t sc_bits;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc_bits) : "r"(my_scale + slot * SCALE_STAGE_BYTES) : "memory");
+        const __half2 sc = *reinterpret_cast<__half2*>(&sc_bits);
+        advance2(cs);
+        ok = mbar_wait(&raw_full[rs], (it / RAW_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
+        ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
+        if (!ok) break;
+        if (threadIdx.x == 64) GEMM_TRACE(4, it);
+        const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_STAGE_BYTES + row * 32);
+        uint4 r0 = raw[0], r1 = raw[1];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);  // nibbles are in registers: recycle early
+        uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        // the expanded tile may only be overwritten once the MMA that read it has finished
+        if (it >= STAGES) {
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
+          const __half2 s2 = __half2half2(sv);
+          // 0x6400 | q is the fp16 value 1024 + q; subtracting 1031 is exact, so the product
+          // (q - 7) * s is rounded once
+          const __half2 off = __float2half2_rn(1031.f);
+          const uint32_t x = words[w];
+          uint32_t h[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // device layout: nibble pair (2j, 2j+1) sits at bits [4j, 4j+4) and [16+4j, 20+4j)
+            uint32_t v = ((x >> (4 * j)) & 0x000f000fu) | 0x64006400u;
+            __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v), off), s2);
+            h[j] = *reinterpret_cast<uint32_t*>(&hv);
+          }
+          *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
+              make_uint4(h[0], h[1], h[2], h[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&deq_full[s]);
+        if (threadIdx.x == 64) GEMM_TRACE(5, it);
+        fetch_scale(cp, slot);  // refill the slot consumed above
+        advance2(cp);
       }
     }
   } else if (warp < 10) {
@@ -391,49 +415,113 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[a]);
-        // the last split to arrive for this tile performs the reduction
+        // Every split reduces its own share of the tile's tokens once all partial sums are parked,
+        // so the reduction runs on `splits` SMs at once. The counter's low half counts arrivals,
+        // its high half counts finished reducers; the last reducer zeroes it for the next launch.
+        // (Each CTA owns at most one split item, so waiting here cannot starve a sibling.)
         __threadfence();
         __syncwarp();
-        // bounded group syncs over mbarriers (one arrival per epilogue warp)
         if (lane == 0) mbar_arrive(&ep_bar[0]);
-        ok = mbar_wait(&ep_bar[0], tile_i & 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+        ok = mbar_wait(&ep_bar[0], 0, abort_flag, p.status, ERR_WAIT_EPILOGUE);  // two phases per tile
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (warp == 6 && lane == 0) {
-          const int prev = atomicAdd(&p.counters[tile], 1);
-          last_flag = (prev == p.splits - 1);
-          if (last_flag) p.counters[tile] = 0;
-          __threadfence_block();
+        if (warp == 6) {
+          int seen = 0;
+          if (lane == 0) {
+            atomicAdd(&p.counters[tile], 1);
+            const unsigned long long t_start = global_timer_ns();
+            uint32_t spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+              if ((seen & 0xffff) >= p.splits || *abort_flag) break;
+              if ((++spins & 0x3f) == 0 && global_timer_ns() - t_start > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, ERR_WAIT_EPILOGUE);
+                break;
+              }
+            }
+          }
+          __syncwarp();
         }
-        __syncwarp();
         if (lane == 0) mbar_arrive(&ep_bar[1]);
         ok = mbar_wait(&ep_bar[1], tile_i & 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+        ok = ok && (*abort_flag == 0);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (last_flag) {
+        {
           __threadfence();
+          // this split's share of the valid tokens; thread = (token slot, 4 consecutive features)
           const int jmax = ti.m_valid;
-          for (int j0 = 0; j0 < jmax; j0 += 8) {
-            float v[8];
+          const int per = (jmax + p.splits - 1) / p.splits;
+          const int j_begin = sp * per;
+          const int j_end = min(jmax, j_begin + per);
+          const int f4 = lane * 4;                 // feature offset inside the tile
+          const int n4 = nb * BM + f4;             // first output feature of this thread
+          float b4[4] = {0.f, 0.f, 0.f, 0.f};
+          if (p.bias) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = bias;
+            for (int u = 0; u < 4; ++u)
+              if (n4 + u < p.N)
+                b4[u] = p.ab_fmt == 0 ? __half2float(reinterpret_cast<const __half*>(p.bias)[n4 + u])
+                                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n4 + u]);
+          }
+          const int ew = warp - 6;                 // epilogue warp 0..3
+          for (int j0 = j_begin + ew; j0 < j_end; j0 += 16) {
+            float4 acc[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = make_float4(b4[0], b4[1], b4[2], b4[3]);
             for (int s2 = 0; s2 < p.splits; ++s2) {
-              const float* src = ws_tile + (static_cast<size_t>(s2) * p.tn + j0) * BM + row;
+              const float* src = ws_tile + (static_cast<size_t>(s2) * p.tn) * BM + f4;
+              float4 v[4];
 #pragma unroll
-              for (int u = 0; u < 8; ++u)
-                if (j0 + u < jmax) v[u] += __ldcg(src + u * BM);
+              for (int u = 0; u < 4; ++u) {
+                const int j = j0 + 4 * u;
+                v[u] = j < j_end ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(j) * BM))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+              }
             }
-            if (n_ok) {
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                if (j0 + u < jmax) {
-                  const size_t idx = static_cast<size_t>(m0 + j0 + u) * p.ldy + n;
-                  if (p.out_dtype == 0) store_out<__half>(p.y, idx, v[u]);
-                  else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx, v[u]);
-                  else store_out<float>(p.y, idx, v[u]);
+            for (int u = 0; u < 4; ++u) {
+              const int j = j0 + 4 * u;
+              if (j >= j_end) continue;
+              const size_t idx = static_cast<size_t>(m0 + j) * p.ldy + n4;
+              const float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+              if (n4 + 3 < p.N && (p.ldy & 3) == 0) {
+                if (p.out_dtype == 0) {
+                  __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
+                  uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.y) + idx) = pk;
+                } else if (p.out_dtype == 1) {
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+                  uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + idx) = pk;
+                } else {
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + idx) = acc[u];
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (n4 + e >= p.N) continue;
+                  if (p.out_dtype == 0) store_out<__half>(p.y, idx + e, o[e]);
+                  else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx + e, o[e]);
+                  else store_out<float>(p.y, idx + e, o[e]);
                 }
               }
             }
+          }
+          // retire: the last reducer of the tile zeroes the counter
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ep_bar[0]);
+          ok = mbar_wait(&ep_bar[0], 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (warp == 6 && lane == 0) {
+            const int prev = atomicAdd(&p.counters[tile], 0x10000);
+            if ((prev >> 16) == p.splits - 1) p.counters[tile] = 0;
           }
         }
         continue;
@@ -479,6 +567,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+  if (threadIdx.x == 0) GEMM_TRACE(7, 511);
 }
 
 // ---------------------------------------------------------------- host side
@@ -665,7 +754,7 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
   int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (q4)
-    gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<true><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
     gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
@@ -738,7 +827,7 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
   const long long max_tiles = (static_cast<long long>(total_rows) / p.tn + num_groups) * p.num_n_blocks;
   const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
   if (q4)
-    gemm_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<true><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
     gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
