@@ -116,6 +116,39 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- cross-GPU flags
+// Flags that peers write carry a call number (epoch); a reader waits until the flag has reached its
+// own epoch (signed difference, so wrap-around is harmless). System-scope release / acquire.
+__device__ __forceinline__ void flag_store_release_sys(int* flag, int value) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+__device__ __forceinline__ int flag_load_acquire_sys(const int* flag) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+// Bounded wait for `*flag - epoch >= 0`.
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int epoch, volatile int* abort_flag,
+                                             int* status, int code) {
+  if (flag_load_acquire_sys(flag) - epoch >= 0) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (flag_load_acquire_sys(flag) - epoch >= 0) return true;
+    if ((++spins & 0xf) == 0) {
+      if (abort_flag && *abort_flag) return false;
+      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (abort_flag) *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
 
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {

@@ -61,6 +61,24 @@ struct GemmParams {
   // slab e, i.e. rows [e * N, (e + 1) * N) of W (and of the scales). Null = one dense problem.
   const int* group_offsets;
   int num_groups;
+  // ---- tensor-parallel fusion (see the "fused collectives" section below); all off when zero/null
+  // Reduce-scatter epilogue: output rows go to the rank that owns them instead of to `y`.
+  int rs_world, rs_rank;
+  int rs_rows;                       // rows owned by each rank (multiple of 32)
+  int rs_epoch;                      // call number; flags carry it, so nothing is reset
+  // peer address tables live in device memory (dynamic indexing of kernel parameters would force
+  // a local copy of the whole parameter block)
+  const unsigned long long* rs_recv; // [world] per rank: receive buffer [world][rs_rows][N], output dtype
+  const unsigned long long* rs_flag; // [world] per rank: int flags [rs_rows / 32][world]
+  int* rs_count;                     // local: arrivals per 32-row chunk of the whole batch, zeroed by the last one
+  void* rs_residual;                 // local: residual rows owned by this rank [rs_rows, N] (updated in place)
+  const void* rs_norm_w;             // RMSNorm weight [N]
+  float rs_eps, rs_w_offset;
+  const unsigned long long* ag_xn;   // [world] per rank: gathered normalised activations [world * rs_rows, N]
+  const unsigned long long* ag_flag; // [world] per rank: int flags [world * rs_rows / 8], one per 8-row group
+  // All-gather prologue: token rows of X become readable once their 8-row group flag reaches ag_epoch.
+  const int* ag_wait;
+  int ag_epoch;
 };
 
 // Where a tile lives: first weight row, first activation / output row, valid token rows, N block.
@@ -111,6 +129,114 @@ __device__ __forceinline__ int rotate_k(int kb, int kb0, int kb1, int t) {
 template <typename OutT>
 __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
   reinterpret_cast<OutT*>(y)[idx] = Cvt<OutT>::from_f(v);
+}
+
+// Byte address of output row `t` (feature 0). With the reduce-scatter epilogue the row lives in
+// the receive buffer of the rank that owns it, in the slot of the sending rank.
+__device__ __forceinline__ char* out_row_ptr(const GemmParams& p, int t, int esize) {
+  if (p.rs_world == 0) return reinterpret_cast<char*>(p.y) + static_cast<size_t>(t) * p.ldy * esize;
+  const int owner = t / p.rs_rows;
+  const int local = t - owner * p.rs_rows;
+  return reinterpret_cast<char*>(p.rs_recv[owner]) +
+         (static_cast<size_t>(p.rs_rank) * p.rs_rows + local) * p.N * esize;
+}
+
+// One epilogue warp has stored its part of the 32-token chunk `chunk` (global chunk index) of one
+// feature tile. The last of the `expected` arrivals on this GPU tells the owner of those rows that
+// this rank's partial sums for the chunk are complete.
+__device__ __forceinline__ void rs_signal_chunk(const GemmParams& p, int chunk, int expected, int lane) {
+  __threadfence_system();
+  __syncwarp();
+  if (lane == 0) {
+    const int prev = atomicAdd(&p.rs_count[chunk], 1);
+    if (prev == expected - 1) {
+      p.rs_count[chunk] = 0;
+      __threadfence_system();
+      const int t = chunk * 32;
+      const int owner = t / p.rs_rows;
+      const int local_chunk = (t - owner * p.rs_rows) >> 5;
+      flag_store_release_sys(reinterpret_cast<int*>(p.rs_flag[owner]) + local_chunk * p.rs_world + p.rs_rank,
+                             p.rs_epoch);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
+  const int valid = max(0, min(p.rs_rows, p.M - p.rs_rank * p.rs_rows));
+  const int ngroups = (valid + 7) >> 3;
+  const int nvec = p.N >> 3;  // 16-byte vectors per row
+  const int* my_flags = reinterpret_cast<const int*>(p.rs_flag[p.rs_rank]);
+  const char* my_recv = reinterpret_cast<const char*>(p.rs_recv[p.rs_rank]);
+  T* residual = reinterpret_cast<T*>(p.rs_residual);
+  const T* nw = reinterpret_cast<const T*>(p.rs_norm_w);
+  for (int g = blockIdx.x; g < ngroups; g += gridDim.x) {
+    if (warp < 8) {
+      const int row = g * 8 + warp;
+      bool ok = row < valid;
+      if (ok) {
+        const int chunk = row >> 5;
+        bool got = true;
+        if (lane < p.rs_world)
+          got = flag_wait_ge(my_flags + chunk * p.rs_world + lane, p.rs_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+        ok = __all_sync(0xffffffffu, got);
+      }
+      if (ok) {
+        T* res_row = residual + static_cast<size_t>(row) * p.N;
+        float ss = 0.f;
+        for (int v = lane; v < nvec; v += 32) {
+          uint4 rv = *reinterpret_cast<const uint4*>(res_row + v * 8);
+          const T* rh = reinterpret_cast<const T*>(&rv);
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = Cvt<T>::to_f(rh[e]);
+          for (int src = 0; src < p.rs_world; ++src) {
+            const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(
+                my_recv + ((static_cast<size_t>(src) * p.rs_rows + row) * p.N + v * 8) * sizeof(T)));
+            const T* ph = reinterpret_cast<const T*>(&pv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += Cvt<T>::to_f(ph[e]);
+          }
+          uint4 ov;
+          T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            oh[e] = Cvt<T>::from_f(acc[e]);
+            const float r = Cvt<T>::to_f(oh[e]);  // the norm sees the rounded residual
+            ss += r * r;
+          }
+          *reinterpret_cast<uint4*>(res_row + v * 8) = ov;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / static_cast<float>(p.N) + p.rs_eps);
+        const size_t grow = static_cast<size_t>(p.rs_rank) * p.rs_rows + row;  // row in the gathered batch
+        for (int v = lane; v < nvec; v += 32) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(res_row + v * 8);
+          const uint4 wv = *reinterpret_cast<const uint4*>(nw + v * 8);
+          const T* rh = reinterpret_cast<const T*>(&rv);
+          const T* wh = reinterpret_cast<const T*>(&wv);
+          uint4 ov;
+          T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            oh[e] = Cvt<T>::from_f(Cvt<T>::to_f(rh[e]) * inv * (Cvt<T>::to_f(wh[e]) + p.rs_w_offset));
+          for (int dst = 0; dst < p.rs_world; ++dst)
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.ag_xn[dst]) + (grow * p.N + v * 8) * sizeof(T)) = ov;
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x < p.rs_world && g * 8 < valid)
+        flag_store_release_sys(reinterpret_cast<int*>(p.ag_flag[threadIdx.x]) + ((p.rs_rank * p.rs_rows) >> 3) + g,
+                               p.rs_epoch);
+    }
+  }
+}
+
+__device__ __forceinline__ void rs_tail(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
+  if (p.out_dtype == 0) rs_tail_rows<__half>(p, warp, lane, abort_flag);
+  else rs_tail_rows<__nv_bfloat16>(p, warp, lane, abort_flag);
 }
 
 // Cursor over the (work item, K block) sequence of this CTA; every role advances its own copy.
@@ -213,14 +339,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       if (!Q4) tma_prefetch_desc(&tmap_w);
-      const uint32_t x_bytes = static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES);
-      KCursor cx;
-      cx.init(p, total_kb, num_tiles);
-      for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
-        const int s = ix % STAGES;
-        if (ix >= STAGES &&
-            !mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
-          break;
+    }
+    const uint32_t x_bytes = static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES);
+    KCursor cx;
+    cx.init(p, total_kb, num_tiles);
+    int gathered_row = -1;  // token tile whose rows are known to have arrived
+    for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
+      const int s = ix % STAGES;
+      bool ok = true;
+      if (lane == 0 && ix >= STAGES)
+        ok = mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
+      if (p.ag_wait && cx.ti.x_row != gathered_row) {
+        // rows of this token tile are pushed by their owners' kernels; one lane per 8-row group
+        const int g0 = cx.ti.x_row >> 3;
+        const int ng = (cx.ti.m_valid + 7) >> 3;
+        if (lane < ng) ok = ok && flag_wait_ge(p.ag_wait + g0 + lane, p.ag_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+        gathered_row = cx.ti.x_row;
+        fence_proxy_async_all();  // peer stores (generic proxy) -> TMA reads (async proxy)
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) {
         GEMM_TRACE(0, ix);
         mbar_expect_tx(&full[s], x_bytes);
         tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_row);
@@ -452,8 +591,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           __threadfence();
           // this split's share of the valid tokens; thread = (token slot, 4 consecutive features)
           const int jmax = ti.m_valid;
-          const int per = (jmax + p.splits - 1) / p.splits;
-          const int j_begin = sp * per;
+          int per = (jmax + p.splits - 1) / p.splits;
+          if (p.rs_world) per = (per + 31) & ~31;  // whole 32-token chunks, so each chunk has one reducer
+          const int j_begin = min(jmax, sp * per);
           const int j_end = min(jmax, j_begin + per);
           const int f4 = lane * 4;                 // feature offset inside the tile
           const int n4 = nb * BM + f4;             // first output feature of this thread
@@ -488,31 +628,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             for (int u = 0; u < 4; ++u) {
               const int j = j0 + 4 * u;
               if (j >= j_end) continue;
-              const size_t idx = static_cast<size_t>(m0 + j) * p.ldy + n4;
+              const int esize = p.out_dtype == 2 ? 4 : 2;
+              char* rowp = out_row_ptr(p, m0 + j, esize);
               const float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
               if (n4 + 3 < p.N && (p.ldy & 3) == 0) {
                 if (p.out_dtype == 0) {
                   __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
                   uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                  *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.y) + idx) = pk;
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(rowp) + n4) = pk;
                 } else if (p.out_dtype == 1) {
                   __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
                   uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                  *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + idx) = pk;
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(rowp) + n4) = pk;
                 } else {
-                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + idx) = acc[u];
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(rowp) + n4) = acc[u];
                 }
               } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   if (n4 + e >= p.N) continue;
-                  if (p.out_dtype == 0) store_out<__half>(p.y, idx + e, o[e]);
-                  else if (p.out_dtype == 1) store_out<__nv_bfloat16>(p.y, idx + e, o[e]);
-                  else store_out<float>(p.y, idx + e, o[e]);
+                  if (p.out_dtype == 0) store_out<__half>(rowp, n4 + e, o[e]);
+                  else if (p.out_dtype == 1) store_out<__nv_bfloat16>(rowp, n4 + e, o[e]);
+                  else store_out<float>(rowp, n4 + e, o[e]);
                 }
               }
             }
           }
+          if (p.rs_world)
+            for (int c = j_begin; c < j_end; c += 32) rs_signal_chunk(p, (m0 + c) >> 5, p.num_n_blocks * 4, lane);
           // retire: the last reducer of the tile zeroes the counter
           __syncwarp();
           if (lane == 0) mbar_arrive(&ep_bar[0]);
@@ -536,24 +679,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         tmem_ld_wait();
         if (!n_ok) continue;
         const int jn = jlim - c;  // valid tokens in this chunk (may be <= 0)
-        const size_t base = static_cast<size_t>(m0 + c) * p.ldy + n;
+        if (jn <= 0) continue;
+        // a 32-token chunk never straddles two owners (rs_rows and the tile origin are multiples of 32)
+        char* rowp = out_row_ptr(p, m0 + c, p.out_dtype == 2 ? 4 : 2);
+        const size_t ldy = p.rs_world ? static_cast<size_t>(p.N) : static_cast<size_t>(p.ldy);
         if (p.out_dtype == 0) {
-          __half* y = reinterpret_cast<__half*>(p.y) + base;
+          __half* y = reinterpret_cast<__half*>(rowp) + n;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __float2half_rn(__uint_as_float(r[j]) + bias);
+            if (j < jn) y[static_cast<size_t>(j) * ldy] = __float2half_rn(__uint_as_float(r[j]) + bias);
         } else if (p.out_dtype == 1) {
-          __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + base;
+          __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(rowp) + n;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __float2bfloat16_rn(__uint_as_float(r[j]) + bias);
+            if (j < jn) y[static_cast<size_t>(j) * ldy] = __float2bfloat16_rn(__uint_as_float(r[j]) + bias);
         } else {
-          float* y = reinterpret_cast<float*>(p.y) + base;
+          float* y = reinterpret_cast<float*>(rowp) + n;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (j < jn) y[static_cast<size_t>(j) * p.ldy] = __uint_as_float(r[j]) + bias;
+            if (j < jn) y[static_cast<size_t>(j) * ldy] = __uint_as_float(r[j]) + bias;
         }
       }
+      if (p.rs_world)
+        for (int c = 0; c < jlim; c += 32) rs_signal_chunk(p, (m0 + c) >> 5, p.num_n_blocks * 4, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
@@ -568,6 +716,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0) GEMM_TRACE(7, 511);
+
+  // ------------------------------------------------------------ fused collectives: tail
+  // Reduce-scatter + residual + RMSNorm + all-gather for the rows this rank owns. The main loop
+  // above pushed this rank's partial sums to the owners; here each CTA takes 8-row groups of the
+  // owned rows (one warp per row), waits for every rank's partial sums of the row's 32-row chunk,
+  // adds them to the residual stream (kept only on the owner), normalises, and writes the
+  // normalised row into every rank's gather buffer, followed by the group's flag.
+  if (p.rs_world && *abort_flag == 0) rs_tail(p, warp, lane, abort_flag);
 }
 
 // ---------------------------------------------------------------- host side
@@ -683,11 +839,30 @@ MLCB_API void mlcb_gemm_set_trace(long long* buf) { g_gemm_trace = buf; }
 // Returns 0 on success, a negative value for a rejected shape, a positive CUDA error otherwise.
 // x: [M, K] row-major (ldx elements) fp16/bf16.  w: dense [N, K] (same dtype) or, with
 // scale != nullptr, the device-layout packed int4 [N, K/8] uint32 with scale [N, K/32] fp16.
-MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const void* bias, void* y,
+// Arguments of the fused tensor-parallel forms (mirrored by a ctypes structure on the Python side).
+struct MlcbFusedArgs {
+  int rs_world, rs_rank, rs_rows, rs_epoch;
+  const unsigned long long* rs_recv;  // device arrays of `rs_world` peer addresses
+  const unsigned long long* rs_flag;
+  void* rs_count;
+  void* rs_residual;
+  const void* rs_norm_w;
+  float rs_eps, rs_w_offset;
+  const unsigned long long* ag_xn;
+  const unsigned long long* ag_flag;
+  const void* ag_wait;
+  int ag_epoch, reserved;
+};
+
+static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
                        int* status, float* workspace, long long workspace_bytes, int* counters,
-                       int num_counters, cudaStream_t stream) {
+                       int num_counters, cudaStream_t stream, const MlcbFusedArgs* f) {
   if (M <= 0 || N <= 0) return 0;
+  const bool rs = f && f->rs_world > 0;
+  if (rs && (f->rs_world > 8 || f->rs_rows % 32 != 0 || N % 8 != 0 || out_dtype > 1 ||
+             static_cast<long long>(f->rs_rows) * f->rs_world < M))
+    return -5;
   const bool q4 = scale != nullptr;
   if (K % 8 != 0 || ldx % 8 != 0) return -1;
   if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
@@ -698,7 +873,7 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
     cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     attr_set = true;
   }
-  GemmParams p;
+  GemmParams p = {};
   p.scale = scale;
   p.bias = bias;
   p.y = y;
@@ -708,10 +883,28 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
   p.K = K;
   p.ldy = ldy;
   p.tn = pick_tn(M);
+  if (rs) p.tn = (p.tn + 31) & ~31;  // 32-token chunks must not straddle tiles
   p.num_m_blocks = (M + p.tn - 1) / p.tn;
   p.num_n_blocks = (N + BM - 1) / BM;
   p.out_dtype = out_dtype;
   p.ab_fmt = ab_fmt;
+  if (f) {
+    p.rs_world = f->rs_world;
+    p.rs_rank = f->rs_rank;
+    p.rs_rows = f->rs_rows;
+    p.rs_epoch = f->rs_epoch;
+    p.rs_recv = f->rs_recv;
+    p.rs_flag = f->rs_flag;
+    p.ag_xn = f->ag_xn;
+    p.ag_flag = f->ag_flag;
+    p.rs_count = static_cast<int*>(f->rs_count);
+    p.rs_residual = f->rs_residual;
+    p.rs_norm_w = f->rs_norm_w;
+    p.rs_eps = f->rs_eps;
+    p.rs_w_offset = f->rs_w_offset;
+    p.ag_wait = static_cast<const int*>(f->ag_wait);
+    p.ag_epoch = f->ag_epoch;
+  }
   // split-K when the output tiles alone cannot fill the GPU (decode-sized M with a narrow N)
   {
     const int tiles = p.num_m_blocks * p.num_n_blocks;
@@ -761,6 +954,46 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
   return static_cast<int>(cudaGetLastError());
 }
 
+MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const void* bias, void* y,
+                       int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
+                       int* status, float* workspace, long long workspace_bytes, int* counters,
+                       int num_counters, cudaStream_t stream) {
+  return gemm_launch(x, w, scale, bias, y, M, N, K, ldx, ldy, ab_fmt, out_dtype, status, workspace,
+                     workspace_bytes, counters, num_counters, stream, nullptr);
+}
+
+// Tensor-parallel forms of the same kernel (one launch each, collective included):
+//  * reduce-scatter form (f->rs_world > 0): this rank's partial products go straight from the
+//    epilogue into the receive buffers of the ranks that own the rows (peer stores over NVLink,
+//    overlapping the remaining tiles); the kernel's tail then sums the partial sums of the rows it
+//    owns, adds the residual, applies RMSNorm and writes the normalised rows to every rank.
+//    `y` is unused.  Replaces GEMM + all-reduce + add + RMSNorm (reference:
+//    model/llama/llama_model.py:211-214 with compiler_pass/fuse_add_norm.py).
+//  * all-gather form (f->ag_wait != null): `x` is this rank's gather buffer; the activation
+//    producer waits per 8-row group for the owners' pushes, so the GEMM starts on the rows that
+//    have arrived while the rest is still in flight.
+// All peer accesses are plain loads / stores from this kernel; no TMA touches peer memory.
+MLCB_API int mlcb_gemm_fused(const void* x, const void* w, const void* scale, const void* bias, void* y,
+                             int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
+                             int* status, float* workspace, long long workspace_bytes, int* counters,
+                             int num_counters, const MlcbFusedArgs* f, cudaStream_t stream) {
+  return gemm_launch(x, w, scale, bias, y, M, N, K, ldx, ldy, ab_fmt, out_dtype, status, workspace,
+                     workspace_bytes, counters, num_counters, stream, f);
+}
+
+// Bounded wait until the gather flags of rows [0, rows) have reached `epoch` (for consumers of a
+// gather buffer that are not this library's GEMM, e.g. the row gather before the LM head).
+__global__ void flag_wait_kernel(const int* flags, int groups, int epoch, int* status) {
+  for (int g = threadIdx.x; g < groups; g += blockDim.x)
+    flag_wait_ge(flags + g, epoch, nullptr, status, ERR_WAIT_PEER);
+}
+MLCB_API int mlcb_flag_wait(const int* flags, int rows, int epoch, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  flag_wait_kernel<<<1, 256, 0, stream>>>(flags, (rows + 7) / 8, epoch, status);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
 MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
 
 // Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of x (expert-major
@@ -782,7 +1015,7 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
     cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     attr_set = true;
   }
-  GemmParams p;
+  GemmParams p = {};
   p.scale = scale;
   p.bias = nullptr;
   p.y = y;
@@ -911,7 +1144,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
   }
 
   // ---- tiling and split-K, bounded by the built-in scratch
-  GemmParams p;
+  GemmParams p = {};
   p.scale = nullptr;
   p.bias = nullptr;
   p.y = y;

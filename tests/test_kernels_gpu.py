@@ -324,3 +324,47 @@ def test_moe_block_kernels(quant_name, tokens):
     assert torch.equal(off_cpu.cpu(), off_gpu.cpu())
     _close(w_gpu, w_cpu, 1e-3, 1e-5)
     _close(o_gpu, o_cpu, 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
+@pytest.mark.parametrize("tokens,k", [(256, 2048), (37, 512), (1000, 1024)])
+def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
+    """World size 1 runs the fused reduce-scatter / all-gather kernels in their degenerate form: the
+    pushes go to this GPU's own buffers, so one GPU checks the epilogue addressing, the flags, the
+    tail (residual add + RMSNorm) and the gather wait against the unfused ops."""
+    from mlc_llm_b200.parallel.fused import FusedCollectives
+
+    torch.manual_seed(5)
+    hidden, inter = 512, 1536
+    quant = Q.get(quant_name)
+    dt = quant.torch_dtype
+    x = (torch.randn(tokens, k) * 0.5).to(dt).to(DEV)
+    res0 = (torch.randn(tokens, hidden) * 0.5).to(dt).to(DEV)
+    nw = (1 + 0.1 * torch.randn(hidden)).to(dt).to(DEV)
+    w_o = (torch.randn(hidden, k) * 0.05).to(dt)
+    w_up = (torch.randn(inter, hidden) * 0.05).to(dt)
+
+    def mk(w):
+        if quant.kind == "no-quant":
+            return ops.LinearWeight("dense", w, None, None, None, w.shape[0], w.shape[1]).to(DEV)
+        qw, qs = Q.group_quantize(w, quant)
+        return ops.LinearWeight("q4", qw, qs, None, quant, w.shape[0], w.shape[1]).to(DEV)
+
+    l_o, l_up = mk(w_o), mk(w_up)
+    fc = FusedCollectives(hidden, dt, 1024, torch.device(DEV))
+    for rep in range(3):  # several epochs over the same buffers
+        fc.begin(tokens)
+        fc.scatter_residual(res0)
+        fc.gemm_rs_norm(x, l_o, nw, 1e-5)
+        y = fc.gemm_ag(l_up)
+        xn = fc.wait_gather().clone()
+        ops.check_status(torch.device(DEV))
+        # unfused oracle with the same kernels
+        res = res0.clone()
+        o = ops.linear(x, l_o)
+        want_xn = ops.add_rmsnorm(o, res, nw, 1e-5)
+        want_y = ops.linear(want_xn, l_up)
+        tol = 3e-2 if dt == torch.bfloat16 else 4e-3
+        _close(fc.residual[:tokens], res, tol, tol)
+        _close(xn, want_xn, tol, tol)
+        _close(y, want_y, 10 * tol, 10 * tol)
