@@ -146,9 +146,15 @@ class DecoderModel:
         return x  # learned positions are added in forward(), where positions are known
 
     def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
-        c = self.cfg
         pre = f"model.layers.{li}.self_attn."
         qkv = ops.linear(h, self.p.linears[pre + "qkv_proj"])
+        return ops.linear(self._attention_core(li, qkv, b), self.p.linears[pre + "o_proj"])
+
+    def _attention_core(self, li: int, qkv: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        """q/k norms, RoPE + KV append and paged attention on a fused ``qkv`` projection; returns
+        the attention context ``[T, hq * d]`` (input of ``o_proj``)."""
+        c = self.cfg
+        pre = f"model.layers.{li}.self_attn."
         hq, hkv, d = self.hq, self.hkv, self.d
         if c.qk_norm and c.extra.get("qk_norm_full"):
             # OLMo-2 normalises the whole q / k projection, not each head
@@ -181,8 +187,7 @@ class DecoderModel:
                                   b.page_indices, hq, hkv, d, self.page, self.sm_scale, q_kvstart=kvstart,
                                   sink=max(0, c.attention_sink_size) if kvstart is not None and not sliding else 0,
                                   tree_mask=b.tree_mask, softcap=c.attn_logit_softcap, plan=b.attn_plan)
-        o = ops.linear(out, self.p.linears[pre + "o_proj"])
-        return o
+        return out.reshape(out.shape[0], hq * d)
 
     def _mlp(self, li: int, h: torch.Tensor) -> torch.Tensor:
         c = self.cfg
@@ -209,11 +214,57 @@ class DecoderModel:
             self.comm.all_reduce(x)
         return x
 
+    # ------------------------------------------------------------------ fused tensor parallelism
+    def enable_fused(self, fused) -> bool:
+        """Use the fused GEMM+collective kernels (``parallel.fused.FusedCollectives``) when the
+        architecture has the plain pre-norm RMSNorm block structure they implement; otherwise the
+        model keeps the NCCL all-reduce path. Returns whether the fused path is on."""
+        c = self.cfg
+        plain = (c.norm_type == "rms" and not c.parallel_residual and not c.post_attention_norm
+                 and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
+                 and c.gated_mlp and c.position_embedding != "learned"
+                 and self.first_stage and self.last_stage and self.dtype in (torch.float16, torch.bfloat16))
+        self.fused = fused if plain else None
+        return self.fused is not None
+
+    def _forward_fused(self, x: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        """Forward with the residual stream scattered over the ranks (each keeps the rows it owns).
+        Per layer: qkv (all-gather form) -> attention -> o_proj (reduce-scatter form, + residual +
+        post-attention norm) -> gate_up (all-gather form) -> activation -> down_proj (reduce-scatter
+        form, + residual + next layer's input norm, or the final norm). Returns the final normalised
+        hidden states of all rows."""
+        c, f = self.cfg, self.fused
+        f.begin(x.shape[0])
+        x = x.contiguous()
+        f.scatter_residual(x)
+        layers = list(self.layers)
+        h = self._norm(x, f"model.layers.{layers[0]}.input_layernorm")
+        for pos, li in enumerate(layers):
+            pre = f"model.layers.{li}."
+            if pos == 0:
+                qkv = ops.linear(h, self.p.linears[pre + "self_attn.qkv_proj"])
+            else:
+                qkv = f.gemm_ag(self.p.linears[pre + "self_attn.qkv_proj"])
+            ctx = self._attention_core(li, qkv, b)
+            f.gemm_rs_norm(ctx, self.p.linears[pre + "self_attn.o_proj"],
+                           self.p.tensors[pre + "post_attention_layernorm.weight"], c.rms_norm_eps,
+                           c.norm_weight_offset)
+            g = f.gemm_ag(self.p.linears[pre + "mlp.gate_up_proj"])
+            a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
+            nxt = f"model.layers.{layers[pos + 1]}.input_layernorm" if pos + 1 < len(layers) else "model.norm"
+            f.gemm_rs_norm(a, self.p.linears[pre + "mlp.down_proj"], self.p.tensors[nxt + ".weight"],
+                           c.rms_norm_eps, c.norm_weight_offset)
+        out = f.wait_gather()
+        self._final_normed = out
+        return out
+
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, b: BatchInfo) -> torch.Tensor:
         """``x``: embeddings (first stage) or the previous stage's hidden state, ``[T, H]``.
         Returns the residual stream after this stage's layers (final norm NOT applied)."""
         c = self.cfg
+        if getattr(self, "fused", None) is not None and x.is_cuda and x.shape[0] > 0:
+            return self._forward_fused(x, b)
         if c.position_embedding == "learned" and self.first_stage:
             x = x + self.p.tensors["model.embed_positions.weight"][b.positions.long()].to(x.dtype)
         x = x.contiguous()

@@ -7,7 +7,7 @@ disaggregation path allocates (``cpp/serve/engine.cc:410-425``) and the CUDA-IPC
 custom all-reduce (``compiler_pass/pipeline.py:185-189``).
 
 Only plain loads / stores / reductions from kernels of this package touch peer pointers; peer
-memory is never handed to library kernels and never read through TMA multicast.
+memory is never handed to library kernels and never read through TMA.
 """
 
 from __future__ import annotations

@@ -316,6 +316,18 @@ class EngineRuntime:
             m.create_kv_cache(n_pages, 16)
             self.num_pages.append(n_pages)
         full = json.loads(self.complete_config_json)
+        self.fused_tp = False
+        if tp > 1 and self.device.type == "cuda" and os.environ.get("MLCB_FUSED_TP", "1") != "0":
+            # fused GEMM+collective kernels over symmetric peer buffers (main model only)
+            from ..parallel.fused import FusedCollectives  # pylint: disable=import-outside-toplevel
+
+            main_model = self.models[0]
+            if main_model.cfg.norm_type == "rms" and main_model.dtype in (torch.float16, torch.bfloat16):
+                max_tokens = max(int(full.get("prefill_chunk_size") or 2048),
+                                 int(full["max_num_sequence"]) * ((full.get("spec_draft_length") or 0) + 1))
+                fused = FusedCollectives(main_model.cfg.hidden_size, main_model.dtype, max_tokens, self.device,
+                                         group=comm.tp_group, world_size=tp)
+                self.fused_tp = main_model.enable_fused(fused)
         slots = int(full["max_num_sequence"]) * 2 * ((full.get("spec_draft_length") or 4) + 1) \
             if full.get("speculative_mode", "disable") != "disable" else 0
         self.executor = ModelExecutor(self.models, self.device, comm, max_draft_slots=slots)

@@ -34,6 +34,10 @@ def main():
     prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (40, 9, 23)]
     _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
     comm.shutdown_workers()
+    rt = eng.runtime
+    print("FLAGS " + json.dumps({"fused_tp": bool(getattr(rt, "fused_tp", False)),
+                                 "fused_launches": int(rt.models[0].fused.launches) if getattr(rt.models[0], "fused", None) else 0}),
+          flush=True)
     print("RESULT " + json.dumps([t[0] for t in toks]), flush=True)
     comm.destroy()
 

@@ -11,11 +11,12 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world: int, model: str, device: str = "cpu", port: int = 29531):
+def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_env=None, want_flags=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker.py"),
            model, device]
     env = dict(os.environ, OMP_NUM_THREADS="2")
+    env.update(extra_env or {})
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     if out.returncode != 0:
         # keep the children's full stderr where a GPU run can pick it up
@@ -25,7 +26,11 @@ def _run(world: int, model: str, device: str = "cpu", port: int = 29531):
                 f.write(out.stderr)
     assert out.returncode == 0, out.stderr[-3000:]
     line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
-    return json.loads(line[len("RESULT "):])
+    result = json.loads(line[len("RESULT "):])
+    if want_flags:
+        flags = [l for l in out.stdout.splitlines() if l.startswith("FLAGS ")][-1]
+        return result, json.loads(flags[len("FLAGS "):])
+    return result
 
 
 @pytest.mark.parametrize("model", ["random://tiny-llama?quant=q0f32&seed=5"])

@@ -15,3 +15,17 @@ def test_tp2_nccl_matches_single_gpu():
     tp2 = _run(2, model, "cuda", port=29552)
     agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(single, tp2)])
     assert agree >= 0.7, (single, tp2)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("quant", ["q4f16_1", "q0f16"])
+def test_tp2_fused_collectives_match_nccl_path(quant):
+    """The fused GEMM+reduce-scatter / all-gather+GEMM kernels over peer memory against the same
+    model on the NCCL all-reduce path."""
+    model = f"random://tiny-llama-gpu?quant={quant}&seed=5"
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    nccl, f0 = _run(2, model, "cuda", port=29553, extra_env=dict(env, MLCB_FUSED_TP="0"), want_flags=True)
+    fused, f1 = _run(2, model, "cuda", port=29554, extra_env=dict(env, MLCB_FUSED_TP="1"), want_flags=True)
+    assert not f0["fused_tp"] and f1["fused_tp"] and f1["fused_launches"] > 0
+    agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(nccl, fused)])
+    assert agree >= 0.7, (nccl, fused)
