@@ -141,13 +141,16 @@ __device__ __forceinline__ char* out_row_ptr(const GemmParams& p, int t, int esi
          (static_cast<size_t>(p.rs_rank) * p.rs_rows + local) * p.N * esize;
 }
 
-// One epilogue warp has stored its part of the 32-token chunk `chunk` (global chunk index) of one
-// feature tile. The last of the `expected` arrivals on this GPU tells the owner of those rows that
-// this rank's partial sums for the chunk are complete.
-__device__ __forceinline__ void rs_signal_chunk(const GemmParams& p, int chunk, int expected, int lane) {
+// One epilogue warp has stored its part of the 32-token chunks [first_chunk, first_chunk + nchunks)
+// (global chunk indices, nchunks <= 32) of one feature tile. One system-scope fence covers all of the
+// warp's stores; lanes then count one arrival per chunk, and the last of the `expected` arrivals on
+// this GPU tells the owner of those rows that this rank's partial sums for the chunk are complete.
+__device__ __forceinline__ void rs_signal_chunks(const GemmParams& p, int first_chunk, int nchunks,
+                                                 int expected, int lane) {
   __threadfence_system();
   __syncwarp();
-  if (lane == 0) {
+  if (lane < nchunks) {
+    const int chunk = first_chunk + lane;
     const int prev = atomicAdd(&p.rs_count[chunk], 1);
     if (prev == expected - 1) {
       p.rs_count[chunk] = 0;
@@ -159,13 +162,16 @@ __device__ __forceinline__ void rs_signal_chunk(const GemmParams& p, int chunk, 
                              p.rs_epoch);
     }
   }
+  __syncwarp();
 }
 
 template <typename T>
 __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
+  constexpr int VU = 4;  // 16-byte vectors in flight per operand and lane
   const int valid = max(0, min(p.rs_rows, p.M - p.rs_rank * p.rs_rows));
   const int ngroups = (valid + 7) >> 3;
   const int nvec = p.N >> 3;  // 16-byte vectors per row
+  const int world = p.rs_world;
   const int* my_flags = reinterpret_cast<const int*>(p.rs_flag[p.rs_rank]);
   const char* my_recv = reinterpret_cast<const char*>(p.rs_recv[p.rs_rank]);
   T* residual = reinterpret_cast<T*>(p.rs_residual);
@@ -177,57 +183,91 @@ __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int 
       if (ok) {
         const int chunk = row >> 5;
         bool got = true;
-        if (lane < p.rs_world)
-          got = flag_wait_ge(my_flags + chunk * p.rs_world + lane, p.rs_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+        if (lane < world)
+          got = flag_wait_ge(my_flags + chunk * world + lane, p.rs_epoch, abort_flag, p.status, ERR_WAIT_PEER);
         ok = __all_sync(0xffffffffu, got);
       }
       if (ok) {
         T* res_row = residual + static_cast<size_t>(row) * p.N;
         float ss = 0.f;
-        for (int v = lane; v < nvec; v += 32) {
-          uint4 rv = *reinterpret_cast<const uint4*>(res_row + v * 8);
-          const T* rh = reinterpret_cast<const T*>(&rv);
-          float acc[8];
+        for (int v0 = lane; v0 < nvec; v0 += 32 * VU) {
+          uint4 rv[VU];
+          float acc[VU][8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = Cvt<T>::to_f(rh[e]);
-          for (int src = 0; src < p.rs_world; ++src) {
-            const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(
-                my_recv + ((static_cast<size_t>(src) * p.rs_rows + row) * p.N + v * 8) * sizeof(T)));
-            const T* ph = reinterpret_cast<const T*>(&pv);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] += Cvt<T>::to_f(ph[e]);
+          for (int u = 0; u < VU; ++u) {
+            const int v = v0 + 32 * u;
+            rv[u] = v < nvec ? *reinterpret_cast<const uint4*>(res_row + v * 8) : make_uint4(0, 0, 0, 0);
           }
-          uint4 ov;
-          T* oh = reinterpret_cast<T*>(&ov);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            oh[e] = Cvt<T>::from_f(acc[e]);
-            const float r = Cvt<T>::to_f(oh[e]);  // the norm sees the rounded residual
-            ss += r * r;
+          for (int u = 0; u < VU; ++u) {
+            const T* rh = reinterpret_cast<const T*>(&rv[u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[u][e] = Cvt<T>::to_f(rh[e]);
           }
-          *reinterpret_cast<uint4*>(res_row + v * 8) = ov;
+          for (int src = 0; src < world; ++src) {
+            uint4 pv[VU];
+#pragma unroll
+            for (int u = 0; u < VU; ++u) {
+              const int v = v0 + 32 * u;
+              pv[u] = v < nvec ? __ldcg(reinterpret_cast<const uint4*>(
+                                     my_recv + ((static_cast<size_t>(src) * p.rs_rows + row) * p.N + v * 8) * sizeof(T)))
+                               : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < VU; ++u) {
+              const T* ph = reinterpret_cast<const T*>(&pv[u]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[u][e] += Cvt<T>::to_f(ph[e]);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < VU; ++u) {
+            const int v = v0 + 32 * u;
+            if (v >= nvec) continue;
+            uint4 ov;
+            T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              oh[e] = Cvt<T>::from_f(acc[u][e]);
+              const float r = Cvt<T>::to_f(oh[e]);  // the norm sees the rounded residual
+              ss += r * r;
+            }
+            *reinterpret_cast<uint4*>(res_row + v * 8) = ov;
+          }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         const float inv = rsqrtf(ss / static_cast<float>(p.N) + p.rs_eps);
         const size_t grow = static_cast<size_t>(p.rs_rank) * p.rs_rows + row;  // row in the gathered batch
-        for (int v = lane; v < nvec; v += 32) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(res_row + v * 8);
-          const uint4 wv = *reinterpret_cast<const uint4*>(nw + v * 8);
-          const T* rh = reinterpret_cast<const T*>(&rv);
-          const T* wh = reinterpret_cast<const T*>(&wv);
-          uint4 ov;
-          T* oh = reinterpret_cast<T*>(&ov);
+        for (int v0 = lane; v0 < nvec; v0 += 32 * VU) {
+          uint4 rv[VU], wv[VU];
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            oh[e] = Cvt<T>::from_f(Cvt<T>::to_f(rh[e]) * inv * (Cvt<T>::to_f(wh[e]) + p.rs_w_offset));
-          for (int dst = 0; dst < p.rs_world; ++dst)
-            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.ag_xn[dst]) + (grow * p.N + v * 8) * sizeof(T)) = ov;
+          for (int u = 0; u < VU; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < nvec) {
+              rv[u] = *reinterpret_cast<const uint4*>(res_row + v * 8);
+              wv[u] = *reinterpret_cast<const uint4*>(nw + v * 8);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < VU; ++u) {
+            const int v = v0 + 32 * u;
+            if (v >= nvec) continue;
+            const T* rh = reinterpret_cast<const T*>(&rv[u]);
+            const T* wh = reinterpret_cast<const T*>(&wv[u]);
+            uint4 ov;
+            T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              oh[e] = Cvt<T>::from_f(Cvt<T>::to_f(rh[e]) * inv * (Cvt<T>::to_f(wh[e]) + p.rs_w_offset));
+            for (int dst = 0; dst < world; ++dst)
+              *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.ag_xn[dst]) + (grow * p.N + v * 8) * sizeof(T)) = ov;
+          }
         }
       }
       __threadfence_system();
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (threadIdx.x < p.rs_world && g * 8 < valid)
+      if (threadIdx.x < world && g * 8 < valid)
         flag_store_release_sys(reinterpret_cast<int*>(p.ag_flag[threadIdx.x]) + ((p.rs_rank * p.rs_rows) >> 3) + g,
                                p.rs_epoch);
     }
@@ -344,22 +384,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     KCursor cx;
     cx.init(p, total_kb, num_tiles);
     int gathered_row = -1;  // token tile whose rows are known to have arrived
+    bool failed = false;    // no early exit: the lanes meet again at every token-tile change
     for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
       const int s = ix % STAGES;
-      bool ok = true;
-      if (lane == 0 && ix >= STAGES)
-        ok = mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
+      if (lane == 0 && ix >= STAGES && !failed)
+        failed = !mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
       if (p.ag_wait && cx.ti.x_row != gathered_row) {
         // rows of this token tile are pushed by their owners' kernels; one lane per 8-row group
         const int g0 = cx.ti.x_row >> 3;
         const int ng = (cx.ti.m_valid + 7) >> 3;
-        if (lane < ng) ok = ok && flag_wait_ge(p.ag_wait + g0 + lane, p.ag_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+        if (lane < ng && *abort_flag == 0)
+          flag_wait_ge(p.ag_wait + g0 + lane, p.ag_epoch, abort_flag, p.status, ERR_WAIT_PEER);
         gathered_row = cx.ti.x_row;
+        __syncwarp();
         fence_proxy_async_all();  // peer stores (generic proxy) -> TMA reads (async proxy)
+        if (*abort_flag) failed = true;
       }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (lane == 0) {
+      if (lane == 0 && !failed) {
         GEMM_TRACE(0, ix);
         mbar_expect_tx(&full[s], x_bytes);
         tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_row);
@@ -654,8 +695,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
               }
             }
           }
-          if (p.rs_world)
-            for (int c = j_begin; c < j_end; c += 32) rs_signal_chunk(p, (m0 + c) >> 5, p.num_n_blocks * 4, lane);
+          if (p.rs_world && j_end > j_begin)
+            rs_signal_chunks(p, (m0 + j_begin) >> 5, (j_end - j_begin + 31) >> 5, p.num_n_blocks * 4, lane);
           // retire: the last reducer of the tile zeroes the counter
           __syncwarp();
           if (lane == 0) mbar_arrive(&ep_bar[0]);
@@ -700,8 +741,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             if (j < jn) y[static_cast<size_t>(j) * ldy] = __uint_as_float(r[j]) + bias;
         }
       }
-      if (p.rs_world)
-        for (int c = 0; c < jlim; c += 32) rs_signal_chunk(p, (m0 + c) >> 5, p.num_n_blocks * 4, lane);
+      if (p.rs_world && jlim > 0) rs_signal_chunks(p, m0 >> 5, (jlim + 31) >> 5, p.num_n_blocks * 4, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
