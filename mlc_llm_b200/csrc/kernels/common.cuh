@@ -25,6 +25,7 @@ enum ErrCode : int {
   ERR_WAIT_PEER = 5,
   ERR_BAD_INDEX = 6,
   ERR_WAIT_DEQUANT = 7,
+  ERR_CAPACITY = 8,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -61,6 +61,10 @@ struct GemmParams {
   // slab e, i.e. rows [e * N, (e + 1) * N) of W (and of the scales). Null = one dense problem.
   const int* group_offsets;
   int num_groups;
+  // Explicit group table (expert-parallel receive layout): when group_count is set, group e covers
+  // rows [group_offsets[e], group_offsets[e] + group_count[e]) and uses weight slab group_slab[e].
+  const int* group_count;
+  const int* group_slab;
   // ---- tensor-parallel fusion (see the "fused collectives" section below); all off when zero/null
   // Reduce-scatter epilogue: output rows go to the rank that owns them instead of to `y`.
   int rs_world, rs_rank;
@@ -98,13 +102,14 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   int cum = 0, e = 0, begin = 0, cnt = 0;
   for (; e < p.num_groups; ++e) {
     begin = p.group_offsets[e];
-    cnt = p.group_offsets[e + 1] - begin;
+    cnt = p.group_count ? p.group_count[e] : p.group_offsets[e + 1] - begin;
     const int mbs = (cnt + p.tn - 1) / p.tn;
     if (mbg < cum + mbs) break;
     cum += mbs;
   }
   const int mb = mbg - cum;
-  ti.w_row = e * p.N + ti.nb * BM;
+  const int slab = p.group_slab ? p.group_slab[e] : e;
+  ti.w_row = slab * p.N + ti.nb * BM;
   ti.x_row = begin + mb * p.tn;
   ti.m_valid = min(p.tn, cnt - mb * p.tn);
   return ti;
@@ -355,8 +360,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     *abort_flag = 0;
     if (p.group_offsets) {
       int mbs = 0;
-      for (int e = 0; e < p.num_groups; ++e)
-        mbs += (p.group_offsets[e + 1] - p.group_offsets[e] + p.tn - 1) / p.tn;
+      for (int e = 0; e < p.num_groups; ++e) {
+        const int cnt = p.group_count ? p.group_count[e] : p.group_offsets[e + 1] - p.group_offsets[e];
+        mbs += (cnt + p.tn - 1) / p.tn;
+      }
       sh_num_items = mbs * p.num_n_blocks;
     } else {
       sh_num_items = p.num_m_blocks * p.num_n_blocks * p.splits;
@@ -1041,8 +1048,9 @@ MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
 // 16-bit, or packed int4 [N, K/8] + scale [N, K/32]); y has the same row order, [total_rows, N].
 // `offsets` is a device array of num_groups + 1 ints; the kernel derives its tile list from it, so
 // no host synchronisation is needed between routing and the expert matmuls.
-MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, void* y, const int* offsets,
-                               int num_groups, int total_rows, int N, int K, int ldx, int ldy, int ab_fmt,
+static int gemm_grouped_launch(const void* x, const void* w, const void* scale, void* y, const int* offsets,
+                               const int* group_count, const int* group_slab, int num_groups, int num_slabs,
+                               int total_rows, int rows_hint, int N, int K, int ldx, int ldy, int ab_fmt,
                                int out_dtype, int* status, cudaStream_t stream) {
   if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
   const bool q4 = scale != nullptr;
@@ -1065,7 +1073,7 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
   p.K = K;
   p.ldy = ldy;
   // token tile sized for the average expert load (the box of the activation tensor map is fixed)
-  const int avg = (total_rows + num_groups - 1) / num_groups;
+  const int avg = (rows_hint + num_groups - 1) / num_groups;
   p.tn = avg >= 192 ? 256 : avg >= 96 ? 128 : avg >= 48 ? 64 : avg >= 24 ? 32 : 16;
   p.num_m_blocks = 0;
   p.num_n_blocks = N / BM;
@@ -1078,12 +1086,14 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
   p.trace = nullptr;
   p.group_offsets = offsets;
   p.num_groups = num_groups;
+  p.group_count = group_count;
+  p.group_slab = group_slab;
   uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(total_rows)};
   uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
   uint32_t xb[2] = {BK, static_cast<uint32_t>(p.tn)};
   const CUtensorMap* mx = get_tensor_map(x, 2, 2, xd, xs, xb, 1);
   const CUtensorMap* mw;
-  const uint64_t wrows = static_cast<uint64_t>(num_groups) * N;
+  const uint64_t wrows = static_cast<uint64_t>(num_slabs) * N;
   if (q4) {
     uint64_t wd[2] = {static_cast<uint64_t>(K / 8), wrows};
     uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
@@ -1097,7 +1107,7 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
   }
   if (!mx || !mw) return -4;
   // upper bound of useful CTAs: every expert may add one partial token block
-  const long long max_tiles = (static_cast<long long>(total_rows) / p.tn + num_groups) * p.num_n_blocks;
+  const long long max_tiles = (static_cast<long long>(rows_hint) / p.tn + num_groups) * p.num_n_blocks;
   const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
   if (q4)
     gemm_kernel<true><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
@@ -1105,6 +1115,27 @@ MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, 
     gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, void* y, const int* offsets,
+                               int num_groups, int total_rows, int N, int K, int ldx, int ldy, int ab_fmt,
+                               int out_dtype, int* status, cudaStream_t stream) {
+  return gemm_grouped_launch(x, w, scale, y, offsets, nullptr, nullptr, num_groups, num_groups, total_rows,
+                             total_rows, N, K, ldx, ldy, ab_fmt, out_dtype, status, stream);
+}
+
+// Grouped GEMM over an explicit group table (device arrays of num_groups ints each): group g covers
+// rows [group_begin[g], group_begin[g] + group_count[g]) of x / y and uses weight slab group_slab[g]
+// out of num_slabs. `buffer_rows` is the height of x / y, `rows_hint` the expected number of live
+// rows (sizes the token tile and the grid; any value is safe). Used by the expert-parallel path,
+// whose receive buffer holds one expert-major region per sending rank.
+MLCB_API int mlcb_gemm_grouped_table(const void* x, const void* w, const void* scale, void* y,
+                                     const int* group_begin, const int* group_count, const int* group_slab,
+                                     int num_groups, int num_slabs, int buffer_rows, int rows_hint, int N, int K,
+                                     int ldx, int ldy, int ab_fmt, int out_dtype, int* status, cudaStream_t stream) {
+  return gemm_grouped_launch(x, w, scale, y, group_begin, group_count, group_slab, num_groups, num_slabs,
+                             buffer_rows, rows_hint > 0 ? rows_hint : 1, N, K, ldx, ldy, ab_fmt, out_dtype, status,
+                             stream);
 }
 
 // ---------------------------------------------------------------------------------------------

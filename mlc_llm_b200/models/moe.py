@@ -29,6 +29,7 @@ def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
         from ..parallel.expert import expert_parallel_ffn  # pylint: disable=import-outside-toplevel
 
         out = expert_parallel_ffn(model, h, weights, experts, w13, w2)
+        model._mlp_complete = True  # every expert ran whole on some rank: nothing to all-reduce
     else:
         offsets, sorted_pos, src_token = ops.moe_permute(experts, c.num_experts)
         xp = ops.row_gather(h, src_token)
@@ -42,5 +43,7 @@ def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
         if c.shared_expert_gate:
             sg = ops.linear(h, ops.dense_weight(model.p.tensors[pre + "shared_expert_gate.weight"]))
             s = (torch.sigmoid(sg.float()) * s.float()).to(s.dtype)
+        if getattr(model, "_mlp_complete", False):
+            s = model._reduce(s)  # the shared expert stays sharded over its width
         out = out + s
     return out

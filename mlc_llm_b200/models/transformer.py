@@ -281,6 +281,7 @@ class DecoderModel:
                 attn = self._attention(li, h1, b)
                 mlp = self._mlp(li, h2)
                 pending = self._reduce(attn + mlp)
+                self._mlp_complete = False
                 continue
             # ---- attention block
             if no_pre_norm:
@@ -305,7 +306,11 @@ class DecoderModel:
                 mlp_norm = "pre_feedforward_layernorm" if (c.post_attention_norm and not no_pre_norm) \
                     else "post_attention_layernorm"
                 h = self._add_norm(attn, x, pre + mlp_norm)
-            mlp = self._reduce(self._mlp(li, h))
+            mlp = self._mlp(li, h)
+            if getattr(self, "_mlp_complete", False):
+                self._mlp_complete = False
+            else:
+                mlp = self._reduce(mlp)
             if c.post_mlp_norm:
                 mlp = self._norm(mlp, pre + "post_feedforward_layernorm")
             pending = mlp

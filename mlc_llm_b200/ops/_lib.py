@@ -67,6 +67,7 @@ def check_status(device: torch.device) -> None:
             5: "wait for a peer GPU timed out",
             6: "index out of range",
             7: "wait for dequantised tile timed out",
+            8: "a fixed-capacity exchange buffer overflowed",
         }
         raise KernelError(f"device status {code}: {names.get(code, 'unknown')}")
 

@@ -1,0 +1,197 @@
+"""Expert parallelism for mixture-of-experts layers: all-to-all token dispatch and result combine over
+symmetric peer buffers (kernels in ``csrc/kernels/moe_ep.cu``), expert matmuls on the table-driven
+grouped tcgen05 GEMM.
+
+Every rank owns ``E / world`` whole experts and a contiguous slice of the batch's tokens.  One layer:
+
+1. ``moe_permute`` orders this rank's (token, slot) pairs by expert (hence by destination rank);
+2. ``mlcb_ep_dispatch`` writes each pair's hidden row into the destination's receive region, plus the
+   per-expert counts and the pair ids, then raises this rank's flag at every destination;
+3. ``mlcb_ep_build_groups`` (receiver) waits for all senders and builds the GEMM's group table;
+4. two grouped GEMMs with the activation in between run on the received rows;
+5. ``mlcb_ep_combine_send`` returns each output row to its pair's slot at the token's home rank;
+6. the home rank waits for all expert ranks and takes the weighted sum over the k slots.
+
+The token slices are finally concatenated with one NCCL all-gather, because the attention that follows
+is tensor parallel and wants every token on every rank.
+
+The reference shards experts over their width instead (``model/mixtral/mixtral_model.py:144-145``)
+and has no all-to-all; that layout remains available (``expert_parallel=False``) and is the numerics
+oracle for this path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops._lib import DTYPE_CODE, check, lib, ptr, status_word, stream_ptr
+from .symm import LocalBuffer, SymmetricBuffer
+
+
+class EpArgs(ctypes.Structure):
+    """Mirror of ``MlcbEpArgs``."""
+
+    _fields_ = [
+        ("world", ctypes.c_int), ("rank", ctypes.c_int), ("e_local", ctypes.c_int), ("k", ctypes.c_int),
+        ("hidden", ctypes.c_int), ("cap", ctypes.c_int), ("epoch", ctypes.c_int), ("pairs", ctypes.c_int),
+        ("disp_x", ctypes.c_void_p), ("disp_meta", ctypes.c_void_p), ("disp_pair", ctypes.c_void_p),
+        ("disp_flag", ctypes.c_void_p), ("comb_y", ctypes.c_void_p), ("comb_flag", ctypes.c_void_p),
+        ("done_counter", ctypes.c_void_p), ("status", ctypes.c_void_p),
+    ]
+
+
+def _up(v: int, m: int = 256) -> int:
+    return (v + m - 1) // m * m
+
+
+class ExpertParallel:
+    """Buffers and launch sequence of the expert-parallel FFN for one process group."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden: int, dtype: torch.dtype, max_tokens: int,
+                 device: torch.device, group=None, world_size: int = 1):
+        assert dtype in (torch.float16, torch.bfloat16)
+        world = max(1, world_size)
+        if num_experts % world:
+            raise ValueError(f"{num_experts} experts cannot be split over {world} ranks")
+        self.E, self.k, self.hidden, self.dtype, self.device = num_experts, top_k, hidden, dtype, device
+        self.e_local = num_experts // world
+        self.tokens_cap = -(-max_tokens // world)          # tokens of one rank's slice
+        self.cap = _up(self.tokens_cap * top_k, 32)        # rows one sender may route to one receiver
+        es = 2
+        x_bytes = _up(world * self.cap * hidden * es)
+        meta_bytes = _up(world * (self.e_local + 1) * 4)
+        pair_bytes = _up(world * self.cap * 4)
+        comb_bytes = _up(self.tokens_cap * top_k * hidden * es)
+        # two parities of every data region, one set of flags
+        self.off = {}
+        cur = 0
+        for name, size in (("x0", x_bytes), ("x1", x_bytes), ("meta0", meta_bytes), ("meta1", meta_bytes),
+                           ("pair0", pair_bytes), ("pair1", pair_bytes), ("comb0", comb_bytes),
+                           ("comb1", comb_bytes), ("dflag", 256), ("cflag", 256)):
+            self.off[name] = cur
+            cur += size
+        self.buf = SymmetricBuffer(cur, group, device) if world > 1 else LocalBuffer(cur, device)
+        self.world, self.rank, self.group = self.buf.world_size, self.buf.rank, group
+        names = ["x0", "x1", "meta0", "meta1", "pair0", "pair1", "comb0", "comb1", "dflag", "cflag"]
+        table = torch.zeros(len(names), 8, dtype=torch.int64)
+        for i, n in enumerate(names):
+            for r in range(self.world):
+                table[i, r] = self.buf.peer_ptr(r, self.off[n])
+        self.table = table.to(device)
+        self.row = {n: i for i, n in enumerate(names)}
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        g = self.world * self.e_local
+        self.group_begin = torch.zeros(g, dtype=torch.int32, device=device)
+        self.group_count = torch.zeros(g, dtype=torch.int32, device=device)
+        self.group_slab = torch.zeros(g, dtype=torch.int32, device=device)
+        self.rows_of_src = torch.zeros(8, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.launches = 0
+
+    def token_slice(self, tokens: int) -> range:
+        per = -(-tokens // self.world)
+        lo = min(tokens, self.rank * per)
+        return range(lo, min(tokens, lo + per))
+
+    def _args(self, pairs: int) -> EpArgs:
+        par = self.epoch & 1
+        a = EpArgs()
+        a.world, a.rank, a.e_local, a.k = self.world, self.rank, self.e_local, self.k
+        a.hidden, a.cap, a.epoch, a.pairs = self.hidden, self.cap, self.epoch, pairs
+        a.disp_x = self.table[self.row[f"x{par}"]].data_ptr()
+        a.disp_meta = self.table[self.row[f"meta{par}"]].data_ptr()
+        a.disp_pair = self.table[self.row[f"pair{par}"]].data_ptr()
+        a.disp_flag = self.table[self.row["dflag"]].data_ptr()
+        a.comb_y = self.table[self.row[f"comb{par}"]].data_ptr()
+        a.comb_flag = self.table[self.row["cflag"]].data_ptr()
+        a.done_counter = self.done.data_ptr()
+        a.status = status_word(self.device).data_ptr()
+        return a
+
+    def ffn(self, x: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor, w13, w2,
+            act: str = "silu") -> torch.Tensor:
+        """Expert FFN of this rank's token slice ``x [t, hidden]`` with routing ``weights / experts
+        [t, k]``; ``w13 / w2`` hold this rank's ``e_local`` experts. Returns ``[t, hidden]``."""
+        t = x.shape[0]
+        if t > self.tokens_cap:
+            raise ValueError(f"{t} tokens exceed the expert-parallel buffers ({self.tokens_cap} per rank)")
+        self.epoch += 1
+        par = self.epoch & 1
+        pairs = t * self.k
+        a = self._args(pairs)
+        dt = DTYPE_CODE[x.dtype]
+        x = x.contiguous()
+        if pairs:
+            offsets, sorted_pos, _ = ops.moe_permute(experts.contiguous(), self.E)
+        else:
+            offsets = torch.zeros(self.E + 1, dtype=torch.int32, device=self.device)
+            sorted_pos = torch.zeros(1, dtype=torch.int32, device=self.device)
+            experts = torch.zeros(1, self.k, dtype=torch.int32, device=self.device)
+        rc = lib().mlcb_ep_dispatch(ptr(x), ptr(experts), ptr(sorted_pos), ptr(offsets), ctypes.byref(a),
+                                    ctypes.c_int(dt), stream_ptr())
+        check(rc, "mlcb_ep_dispatch")
+        a.done_counter = self.done[1:].data_ptr()
+        rc = lib().mlcb_ep_build_groups(ctypes.byref(a), ptr(self.group_begin), ptr(self.group_count),
+                                        ptr(self.group_slab), ptr(self.rows_of_src), stream_ptr())
+        check(rc, "mlcb_ep_build_groups")
+        rows = self.world * self.cap
+        recv = self.buf.view(self.off[f"x{par}"], (rows, self.hidden), self.dtype)
+        # expected live rows: every rank routes about 1/world of its pairs here
+        hint = max(1, self.tokens_cap * self.k)
+        h1 = self._grouped(recv, w13, rows, hint)
+        y = self._grouped(ops.act_mul(h1, act), w2, rows, hint)
+        a.done_counter = self.done[2:].data_ptr()
+        rc = lib().mlcb_ep_combine_send(ptr(y), ptr(self.rows_of_src), ctypes.byref(a), ctypes.c_int(dt),
+                                        stream_ptr())
+        check(rc, "mlcb_ep_combine_send")
+        flags = self.buf.peer_ptr(self.rank, self.off["cflag"])
+        rc = lib().mlcb_ep_wait_flags(ctypes.c_void_p(flags), ctypes.c_int(self.world), ctypes.c_int(self.epoch),
+                                      ptr(status_word(self.device)), stream_ptr())
+        check(rc, "mlcb_ep_wait_flags")
+        self.launches += 6
+        if not pairs:
+            return torch.zeros(0, self.hidden, dtype=self.dtype, device=self.device)
+        comb = self.buf.view(self.off[f"comb{par}"], (self.tokens_cap * self.k, self.hidden), self.dtype)[:pairs]
+        ident = torch.arange(pairs, dtype=torch.int32, device=self.device)
+        return ops.moe_combine(comb, weights.contiguous(), ident, None)
+
+    def _grouped(self, x: torch.Tensor, lw, rows: int, hint: int) -> torch.Tensor:
+        n, k = lw.w.shape[1], x.shape[1]
+        q4 = lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and \
+            x.dtype == torch.float16 and k % 64 == 0
+        w = lw.w if (q4 or lw.kind == "dense") else lw.dense(x.dtype)
+        y = torch.empty(rows, n, dtype=x.dtype, device=x.device)
+        rc = lib().mlcb_gemm_grouped_table(
+            ptr(x), ptr(w), ptr(lw.scale) if q4 else ptr(None), ptr(y), ptr(self.group_begin),
+            ptr(self.group_count), ptr(self.group_slab), ctypes.c_int(self.world * self.e_local),
+            ctypes.c_int(self.e_local), ctypes.c_int(rows), ctypes.c_int(hint), ctypes.c_int(n), ctypes.c_int(k),
+            ctypes.c_int(x.stride(0)), ctypes.c_int(n), ctypes.c_int(DTYPE_CODE[x.dtype]),
+            ctypes.c_int(DTYPE_CODE[x.dtype]), ptr(status_word(x.device)), stream_ptr())
+        check(rc, "mlcb_gemm_grouped_table")
+        return y
+
+
+def expert_parallel_ffn(model, h: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor, w13, w2
+                        ) -> torch.Tensor:
+    """MoE FFN of all tokens ``h [T, hidden]`` (replicated on the ranks): each rank handles its token
+    slice through the all-to-all exchange, then the slices are all-gathered."""
+    ep: Optional[ExpertParallel] = getattr(model, "ep", None)
+    if ep is None:
+        raise RuntimeError("expert parallelism was requested but its buffers were not created")
+    t = h.shape[0]
+    sl = ep.token_slice(t)
+    act = "silu" if model.cfg.hidden_act == "silu" else "gelu"
+    out = ep.ffn(h[sl.start: sl.stop], weights[sl.start: sl.stop], experts[sl.start: sl.stop], w13, w2, act)
+    if ep.world == 1:
+        return out
+    per = -(-t // ep.world)
+    padded = torch.zeros(per, h.shape[1], dtype=h.dtype, device=h.device)
+    padded[: out.shape[0]] = out
+    gathered = torch.empty(per * ep.world, h.shape[1], dtype=h.dtype, device=h.device)
+    dist.all_gather_into_tensor(gathered, padded, group=ep.group)
+    return gathered[:t]

@@ -328,6 +328,14 @@ class EngineRuntime:
                 fused = FusedCollectives(main_model.cfg.hidden_size, main_model.dtype, max_tokens, self.device,
                                          group=comm.tp_group, world_size=tp)
                 self.fused_tp = main_model.enable_fused(fused)
+        for m in self.models:
+            if m.cfg.expert_parallel and m.cfg.num_experts > 0 and tp > 1 and self.device.type == "cuda":
+                from ..parallel.expert import ExpertParallel  # pylint: disable=import-outside-toplevel
+
+                max_tokens = max(int(full.get("prefill_chunk_size") or 2048),
+                                 int(full["max_num_sequence"]) * ((full.get("spec_draft_length") or 0) + 1))
+                m.ep = ExpertParallel(m.cfg.num_experts, m.cfg.num_experts_per_tok, m.cfg.hidden_size, m.dtype,
+                                      max_tokens, self.device, group=comm.tp_group, world_size=tp)
         slots = int(full["max_num_sequence"]) * 2 * ((full.get("spec_draft_length") or 4) + 1) \
             if full.get("speculative_mode", "disable") != "disable" else 0
         self.executor = ModelExecutor(self.models, self.device, comm, max_draft_slots=slots)

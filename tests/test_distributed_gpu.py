@@ -29,3 +29,15 @@ def test_tp2_fused_collectives_match_nccl_path(quant):
     assert not f0["fused_tp"] and f1["fused_tp"] and f1["fused_launches"] > 0
     agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(nccl, fused)])
     assert agree >= 0.7, (nccl, fused)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep2_all_to_all_matches_tensor_parallel_moe():
+    """Mixtral-style MoE with experts distributed over the ranks (all-to-all dispatch / combine over
+    peer memory) against the same model with width-sharded experts and NCCL all-reduce."""
+    env = {"NCCL_NVLS_ENABLE": "0", "MLCB_FUSED_TP": "0"}
+    base = "random://tiny-mixtral-gpu?quant=q0f16&seed=7"
+    tp = _run(2, base, "cuda", port=29555, extra_env=env)
+    ep = _run(2, base + "&expert_parallel=true", "cuda", port=29556, extra_env=env)
+    agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(tp, ep)])
+    assert agree >= 0.7, (tp, ep)

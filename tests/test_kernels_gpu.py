@@ -368,3 +368,38 @@ def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
         _close(fc.residual[:tokens], res, tol, tol)
         _close(xn, want_xn, tol, tol)
         _close(y, want_y, 10 * tol, 10 * tol)
+
+
+@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
+@pytest.mark.parametrize("tokens", [1, 37, 300])
+def test_expert_parallel_exchange_single_rank(quant_name, tokens):
+    """World size 1 runs dispatch -> group table -> grouped GEMMs -> combine through this GPU's own
+    exchange buffers; the result must equal the local (permute + grouped GEMM) MoE path."""
+    from mlc_llm_b200.parallel.expert import ExpertParallel
+
+    torch.manual_seed(9)
+    e, k, hidden, inter = 8, 2, 256, 512
+    quant = Q.get(quant_name)
+    dt = quant.torch_dtype
+    x = (torch.randn(tokens, hidden) * 0.5).to(dt).to(DEV)
+    gate = torch.randn(tokens, e).to(dt).to(DEV)
+    w13 = (torch.randn(e, 2 * inter, hidden) * 0.05).to(dt)
+    w2 = (torch.randn(e, hidden, inter) * 0.05).to(dt)
+
+    def mk(w):
+        if quant.kind == "no-quant":
+            return ops.LinearWeight("dense", w, None, None, None, w.shape[1], w.shape[2]).to(DEV)
+        qw, qs = Q.group_quantize(w, quant)
+        return ops.LinearWeight("q4", qw, qs, None, quant, w.shape[1], w.shape[2]).to(DEV)
+
+    l13, l2 = mk(w13), mk(w2)
+    wts, idx = ops.moe_router(gate, k, True)
+    off, spos, src = ops.moe_permute(idx, e)
+    h1 = ops.grouped_linear(ops.row_gather(x, src), l13, off)
+    want = ops.moe_combine(ops.grouped_linear(ops.act_mul(h1), l2, off), wts, spos, None)
+    ep = ExpertParallel(e, k, hidden, dt, 512, torch.device(DEV))
+    for _ in range(3):
+        got = ep.ffn(x, wts, idx, l13, l2)
+        ops.check_status(torch.device(DEV))
+        tol = 3e-2 if dt == torch.bfloat16 else 4e-3
+        _close(got, want, tol, tol)
