@@ -68,7 +68,7 @@ class DecoderModel:
         self.p = params
         self.device = device
         self.comm = comm  # tensor-parallel communicator (None when world == 1)
-        self.tp = comm.world_size if comm is not None else 1
+        self.tp = getattr(comm, "tp_size", None) or (comm.world_size if comm is not None else 1)
         self.dtype = quant.torch_dtype
         self.hq = config.num_attention_heads // self.tp
         self.hkv = max(1, config.num_key_value_heads // self.tp)

@@ -92,6 +92,26 @@ class Communicator:
             self.launches += 1
         return x
 
+    # ---------------------------------------------------------------- pipeline stages (NCCL p2p)
+    def send_to_next_stage(self, x: torch.Tensor) -> None:
+        """Hidden state to the same tensor-parallel rank of the next stage (reference:
+        ``runtime.disco.send_to_next_group``, ``compiler_pass/pipeline_parallel_rewrite.py:105-200``).
+        NCCL p2p is stream-ordered, so the sender moves on to its next work immediately."""
+        dist.send(x.contiguous(), dst=self.rank + self.tp_size)
+        self.launches += 1
+
+    def recv_from_prev_stage(self, x: torch.Tensor) -> None:
+        dist.recv(x, src=self.rank - self.tp_size)
+        self.launches += 1
+
+    def send_logits_to_rank0(self, logits: torch.Tensor) -> None:
+        dist.send(logits.contiguous(), dst=0)
+        self.launches += 1
+
+    def recv_logits_from_last_stage(self, logits: torch.Tensor) -> None:
+        dist.recv(logits, src=(self.pp_size - 1) * self.tp_size)
+        self.launches += 1
+
     def barrier(self) -> None:
         if self.world_size > 1:
             dist.barrier()

@@ -167,13 +167,36 @@ class ModelExecutor:
         if dev["page_copies"].numel():
             model.copy_pages(dev["page_copies"])
         b = self._batch_info(dev, plan, model)
-        x = model.embed(dev["token_ids"])
-        if embed_handles is not None:
-            idx = np.nonzero(embed_handles >= 0)[0]
-            tok = np.asarray(dev["token_ids"].cpu())
-            for i in idx:
-                x[i] = self.embeddings[int(embed_handles[i])][int(tok[i])].to(x.dtype)
-        return model.forward(x, b)
+        staged = self._pipeline(model_id)
+        if staged and not model.first_stage:
+            # hidden state of the previous pipeline stage (same tensor-parallel rank)
+            x = torch.empty(b.num_tokens, model.cfg.hidden_size, dtype=model.dtype, device=self.device)
+            self.comm.recv_from_prev_stage(x)
+        else:
+            x = model.embed(dev["token_ids"])
+            if embed_handles is not None:
+                idx = np.nonzero(embed_handles >= 0)[0]
+                tok = np.asarray(dev["token_ids"].cpu())
+                for i in idx:
+                    x[i] = self.embeddings[int(embed_handles[i])][int(tok[i])].to(x.dtype)
+        h = model.forward(x, b)
+        if staged and not model.last_stage:
+            self.comm.send_to_next_stage(h)
+        return h
+
+    def _pipeline(self, model_id: int) -> bool:
+        return self.comm is not None and self.comm.pp_size > 1 and model_id == 0
+
+    def _logits(self, model_id: int, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """Logits of the selected rows on the rank that hosts the engine. With pipeline stages the
+        last stage computes them and returns them to rank 0 (reference: ``SendFromLastGroupToWorker0``,
+        ``cpp/multi_gpu/builtin.cc:27-87``)."""
+        model = self.models[model_id]
+        if not self._pipeline(model_id):
+            return model.logits(hidden, rows)
+        out = torch.empty(int(rows.numel()), model.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        self.comm.recv_logits_from_last_stage(out)
+        return out
 
     def _process_logits(self, logits: torch.Tensor, dev: Dict[str, torch.Tensor], sp: dict) -> None:
         n = logits.shape[0]
@@ -207,14 +230,15 @@ class ModelExecutor:
         arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,
-                                     {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})
+                                     {k: v for k, v in arrays.items()
+                                      if not k.startswith("s_") or k == "s_logit_token_index"}, {})
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         hidden = self._run_model(model_id, plan, dev, embed_handles)
         if n_rows == 0:
             return None
         model = self.models[model_id]
-        logits = model.logits(hidden, dev["s_logit_token_index"])
+        logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
         if self._is_plain_greedy(sp):
             tokens = ops.argmax(logits)
             tok = tokens.cpu().numpy()
@@ -253,12 +277,12 @@ class ModelExecutor:
         arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,
-                                     {k: v for k, v in arrays.items() if not k.startswith("s_")}, {})
+                                     {k: v for k, v in arrays.items()
+                                      if not k.startswith("s_") or k == "s_logit_token_index"}, {})
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         hidden = self._run_model(model_id, plan, dev, None)
-        model = self.models[model_id]
-        logits = model.logits(hidden, dev["s_logit_token_index"])
+        logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
         self._process_logits(logits, dev, sp)
         probs = ops.softmax_temperature(logits, dev["s_temperature"])
         if float(np.min(sp["top_p"])) < 1.0:
@@ -334,4 +358,8 @@ class ModelExecutor:
         plan = {k: arrays[k] for k in _INT_KEYS}
         plan["tree_mask"] = arrays["tree_mask"]
         plan["max_seq_len"] = int(arrays["seq_lens"].max()) if arrays["seq_lens"].size else 0
-        self._run_model(model_id, plan, dev, None)
+        hidden = self._run_model(model_id, plan, dev, None)
+        model = self.models[model_id]
+        if self._pipeline(model_id) and model.last_stage and self.comm.tp_rank == 0 \
+                and "s_logit_token_index" in dev and dev["s_logit_token_index"].numel():
+            self.comm.send_logits_to_rank0(model.logits(hidden, dev["s_logit_token_index"]))

@@ -19,9 +19,11 @@ def main():
     device = sys.argv[2]
     rank, world, local = parallel.env_world()
     dev = torch.device("cuda", local) if device == "cuda" else torch.device("cpu")
-    comm = parallel.Communicator(tp_size=world, pp_size=1, device=dev, timeout_s=120)
+    pp = int(os.environ.get("MLCB_TEST_PP", "1"))
+    comm = parallel.Communicator(tp_size=world // pp, pp_size=pp, device=dev, timeout_s=120)
     cfg = EngineConfig(model=model, mode="server", max_num_sequence=8, prefill_chunk_size=64,
-                       max_total_sequence_length=1024, prefix_cache_mode="disable")
+                       max_total_sequence_length=1024, prefix_cache_mode="disable",
+                       tensor_parallel_shards=world // pp, pipeline_parallel_stages=pp)
     if rank != 0:
         rt = EngineRuntime(cfg, dev, comm=comm)
         parallel.worker_loop(rt.executor, comm)

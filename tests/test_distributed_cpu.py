@@ -38,3 +38,12 @@ def test_tp2_matches_single_rank(model):
     single = _run(1, model, port=29541)
     tp2 = _run(2, model, port=29542)
     assert single == tp2
+
+
+def test_pp2_matches_single_rank():
+    """Two pipeline stages over gloo p2p: stage 0 sends the hidden state on, the last stage returns
+    the logits to rank 0; greedy tokens equal the single-process run exactly (fp32)."""
+    model = "random://tiny-llama?quant=q0f32&seed=5"
+    single = _run(1, model, port=29543)
+    pp2 = _run(2, model, port=29544, extra_env={"MLCB_TEST_PP": "2"})
+    assert single == pp2

@@ -41,3 +41,13 @@ def test_ep2_all_to_all_matches_tensor_parallel_moe():
     ep = _run(2, base + "&expert_parallel=true", "cuda", port=29556, extra_env=env)
     agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(tp, ep)])
     assert agree >= 0.7, (tp, ep)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pp2_nccl_p2p_matches_single_gpu():
+    """Two pipeline stages on two GPUs: hidden states and logits travel over NCCL send / recv."""
+    model = "random://tiny-llama-gpu?quant=q0f16&seed=5"
+    single = _run(1, model, "cuda", port=29557)
+    pp2 = _run(2, model, "cuda", port=29558, extra_env={"MLCB_TEST_PP": "2", "NCCL_NVLS_ENABLE": "0"})
+    agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(single, pp2)])
+    assert agree >= 0.9, (single, pp2)
