@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the hot kernels, reported against measured peaks.
 
-``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|attn_decode|attn_prefill|all] [--small]``
+``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|attn_decode|attn_prefill|rope|norm|sampling|moe|all] [--small]``
 
 Timing follows the usual hygiene: warm-up, CUDA events on the launching stream, and a buffer larger
 than L2 written between timed launches so every launch starts cold.  ``--small`` shrinks the
@@ -85,6 +85,68 @@ def bench_gemm(small: bool, q4: bool):
     return out
 
 
+def bench_misc(which: str, small: bool):
+    """Memory-bound helpers: RoPE + KV append, add+RMSNorm, sampling; and the MoE grouped GEMM."""
+    dev = torch.device("cuda")
+    hbm, tf, how = _peaks()
+    out = []
+
+    def rec(name, med, byt, flops=0.0, **extra):
+        roof = max(byt / (hbm * 1e9), flops / (tf * 1e12)) * 1e3
+        r = {"kernel": name, "ms_median": round(med, 4), "gbs": round(byt / med / 1e6, 1),
+             "tflops": round(flops / med / 1e9, 1), "frac_of_roofline": round(roof / med, 3), "peaks": how}
+        r.update(extra)
+        print(json.dumps(r), flush=True)
+        out.append(r)
+
+    flush = torch.zeros(160 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
+    if which in ("rope", "all"):
+        t, hq, hkv, d = (8192 if small else 65536), 32, 8, 128
+        qkv = (torch.randn(t, (hq + 2 * hkv) * d, device=dev) * 0.5).half()
+        pages = t // 16 + 1
+        kv = torch.zeros(pages, 2, hkv, 16, d, dtype=torch.float16, device=dev)
+        pos = torch.arange(t, dtype=torch.int32, device=dev) % 4096
+        slot = torch.arange(t, dtype=torch.int32, device=dev)
+        inv = ops.reference.rope_inv_freq(d, 5e5).to(dev)
+        med, _ = _time(lambda: ops.rope_append(qkv, kv, pos, slot, inv, hq, hkv, d, d, 16), flush=flush)
+        # q and k are read and rewritten, v is read, k and v are written to their pages
+        byt = t * d * 2 * (2 * (hq + hkv) + hkv + 2 * hkv)
+        rec("rope_append", med, byt, tokens=t)
+    if which in ("norm", "all"):
+        t, h = (8192 if small else 65536), 4096
+        x = torch.randn(t, h, device=dev).half()
+        res = torch.randn(t, h, device=dev).half()
+        w = torch.ones(h, device=dev).half()
+        med, _ = _time(lambda: ops.add_rmsnorm(x, res, w, 1e-5), flush=flush)
+        rec("add_rmsnorm", med, t * h * 2 * 4, tokens=t)
+    if which in ("sampling", "all"):
+        n, v = (64 if small else 256), 128256
+        logits = torch.randn(n, v, device=dev)
+        temp = torch.full((n,), 0.8, device=dev)
+        u = torch.rand(n, device=dev)
+        top_p = torch.full((n,), 0.9, device=dev)
+        top_k = torch.full((n,), 50, dtype=torch.int32, device=dev)
+        med, _ = _time(lambda: ops.softmax_temperature(logits, temp), flush=flush)
+        rec("softmax_temperature", med, n * v * 4 * 2, rows=n)
+        probs = ops.softmax_temperature(logits, temp)
+        med, _ = _time(lambda: ops.sample(probs, None, u, top_p, top_k), flush=flush)
+        rec("sample_top_p_top_k", med, n * v * 4, rows=n)
+    if which in ("moe", "all"):
+        e, k, h, inter = 8, 2, 4096, 14336
+        t = 1024 if small else 8192
+        x = (torch.randn(t, h, device=dev) * 0.5).half()
+        gate = torch.randn(t, e, device=dev).half()
+        w13 = ops.LinearWeight("dense", (torch.randn(e, 2 * inter, h, device=dev) * 0.02).half(), None, None,
+                               None, 2 * inter, h)
+        wts, idx = ops.moe_router(gate, k, True)
+        off, spos, src = ops.moe_permute(idx, e)
+        xp = ops.row_gather(x, src)
+        med, _ = _time(lambda: ops.grouped_linear(xp, w13, off), flush=flush)
+        rec("moe_grouped_gemm", med, e * 2 * inter * h * 2 + t * k * (h + 2 * inter) * 2,
+            2.0 * t * k * 2 * inter * h, tokens=t, experts=e, top_k=k)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("which", nargs="?", default="all")
@@ -103,6 +165,8 @@ def main(argv=None):
             res += bench_attention(args.which, args.small)
         except ImportError:
             pass
+    if args.which in ("rope", "norm", "sampling", "moe", "all"):
+        res += bench_misc(args.which, args.small)
     if args.out:
         with open(args.out, "w", encoding="utf-8") as f:
             json.dump(res, f, indent=1)

@@ -1,0 +1,4 @@
+"""Request routing over several server processes."""
+from .router import Router
+
+__all__ = ["Router"]

@@ -4,6 +4,7 @@ the REST tests."""
 
 from __future__ import annotations
 
+import dataclasses
 import os
 import subprocess
 import sys
@@ -11,6 +12,12 @@ import time
 from typing import Dict, List, Optional
 
 import requests
+
+
+_OVERRIDE_KEYS = {"max_num_sequence", "max_total_sequence_length", "max_single_sequence_length",
+                  "prefill_chunk_size", "sliding_window_size", "attention_sink_size", "max_history_size",
+                  "gpu_memory_utilization", "spec_draft_length", "spec_tree_width",
+                  "prefix_cache_max_num_recycling_seqs", "tensor_parallel_shards", "pipeline_parallel_stages", "opt"}
 
 
 class PopenServer:  # pylint: disable=too-many-instance-attributes
@@ -48,12 +55,12 @@ class PopenServer:  # pylint: disable=too-many-instance-attributes
             cmd += ["--api-key", self.api_key]
         overrides = []
         if self.engine_config is not None:
-            for key, value in self.engine_config.asdict().items():
+            for key, value in dataclasses.asdict(self.engine_config).items():
                 if value is None or key in ("model", "model_lib", "mode", "additional_models", "verbose"):
                     continue
                 if key in ("speculative_mode", "prefix_cache_mode", "prefill_mode"):
                     cmd += ["--" + key.replace("_", "-"), str(value)]
-                else:
+                elif key in _OVERRIDE_KEYS:
                     overrides.append(f"{key}={value}")
         if self.tensor_parallel_shards is not None:
             overrides.append(f"tensor_parallel_shards={self.tensor_parallel_shards}")
