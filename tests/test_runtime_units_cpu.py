@@ -1,0 +1,326 @@
+"""Unit tests of the native runtime pieces and the artifact code (no model, no GPU)."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from mlc_llm_b200 import _core
+from mlc_llm_b200 import quantization as Q
+from mlc_llm_b200.conversation_template import ConvTemplateRegistry
+from mlc_llm_b200.loader.tensor_cache import TensorCache, dump_tensor_cache
+from mlc_llm_b200.protocol import openai_api_protocol as openai
+from mlc_llm_b200.protocol.conversation_protocol import Conversation
+from mlc_llm_b200.tokenizers import StopStrHandler, TextStreamer, Tokenizer
+
+
+# ------------------------------------------------------------------ KV manager
+def test_kv_manager_append_fork_cow_popn():
+    kv = _core.KVManager(32, 16, 8)
+    kv.add_sequence(0)
+    plan = kv.begin_forward([0], [20])
+    assert list(plan["positions"]) == list(range(20))
+    assert kv.sequence_length(0) == 20 and len(kv.sequence_pages(0)) == 2
+    slots = np.asarray(plan["slots"])
+    pages = kv.sequence_pages(0)
+    assert list(slots[:16] // 16) == [pages[0]] * 16 and list(slots[16:] // 16) == [pages[1]] * 4
+    # fork shares the full pages; the partial last page gets a private copy, emitted with the next plan
+    free_before = kv.num_available_pages()
+    kv.fork_sequence(0, 1)
+    child_pages = kv.sequence_pages(1)
+    assert child_pages[0] == pages[0] and child_pages[1] != pages[1]
+    assert kv.num_available_pages() == free_before - 1
+    plan = kv.begin_forward([1], [1])
+    copies = np.asarray(plan["page_copies"]).reshape(-1, 2)
+    assert copies.tolist() == [[pages[1], child_pages[1]]]
+    assert kv.sequence_length(1) == 21 and kv.sequence_length(0) == 20
+    # the parent keeps appending into its own page without a copy
+    plan = kv.begin_forward([0], [1])
+    assert len(plan["page_copies"]) == 0
+    kv.popn(1, 6)
+    assert kv.sequence_length(1) == 15 and len(kv.sequence_pages(1)) == 1
+    kv.remove_sequence(1)
+    kv.remove_sequence(0)
+    assert kv.num_available_pages() == 32 and kv.num_sequences() == 0
+
+
+def test_kv_manager_batch_plan_layout_and_exhaustion():
+    kv = _core.KVManager(4, 16, 8)
+    for i in range(2):
+        kv.add_sequence(i)
+    plan = kv.begin_forward([0, 1], [3, 18])
+    assert list(plan["q_indptr"]) == [0, 3, 21]
+    assert list(plan["q_seq"]) == [0] * 3 + [1] * 18
+    assert list(plan["q_kvlen"])[:3] == [1, 2, 3] and list(plan["q_kvlen"])[-1] == 18
+    assert list(plan["page_indptr"]) == [0, 1, 3]
+    assert kv.num_available_pages() == 1
+    assert kv.pages_needed(0, 13) == 0 and kv.pages_needed(0, 14) == 1 and kv.pages_needed(1, 15) == 1
+    with pytest.raises(Exception):
+        kv.begin_forward([0, 1], [40, 40])
+
+
+def test_kv_manager_tree_append_and_commit():
+    kv = _core.KVManager(16, 16, 4)
+    kv.add_sequence(0)
+    kv.begin_forward([0], [5])
+    # verify step: root + chain of 3 draft tokens, all appended speculatively
+    plan = kv.begin_forward([0], [4], tree_parents=[-1, 0, 1, 2])
+    assert list(plan["positions"]) == [5, 6, 7, 8]
+    assert len(plan["tree_mask"]) == 4
+    # keep root + the first two draft nodes
+    moves = kv.commit_tree_nodes(0, 4, [0, 1, 2])
+    assert kv.sequence_length(0) == 8 and list(moves) == []  # a chain prefix is already in place
+    # branching tree: root, two children of the root, a grandchild under the second child
+    plan = kv.begin_forward([0], [4], tree_parents=[-1, 0, 0, 2])
+    assert list(plan["positions"]) == [8, 9, 9, 10]
+    moves = kv.commit_tree_nodes(0, 4, [0, 2, 3])
+    assert kv.sequence_length(0) == 11
+    # accepted nodes 2 and 3 sat in slots 2 and 3 of the append and move down to slots 1 and 2
+    assert len(moves) == 4
+
+
+def test_kv_manager_sliding_window_releases_pages():
+    kv = _core.KVManager(64, 16, 4)
+    kv.add_sequence(0)
+    kv.enable_sliding_window(0, 32, 4)
+    for _ in range(10):
+        plan = kv.begin_forward([0], [16])
+    assert kv.sequence_length(0) == 160
+    live = [p for p in kv.sequence_pages(0) if p >= 0]
+    assert len(live) <= 5 and kv.num_available_pages() >= 64 - 5  # sink page + window pages, not 10
+    assert len(plan["q_kvstart"]) == 16
+
+
+# ------------------------------------------------------------------ prefix cache
+def test_prefix_cache_reuse_fork_and_recycle():
+    removed = []
+    pc = _core.PrefixCache(True, 2, removed.append)
+    m = pc.insert_sequence(0, list(range(100)))
+    assert m.prefilled_offset == 0 and m.forked_seq_id == -1 and m.reused_seq_id == -1
+    pc.extend_sequence(0, list(range(100)))  # tokens enter the tree once they are prefilled
+    # same prefix, different tail: fork from the live sequence
+    tail = list(range(60)) + [7, 7, 7]
+    m = pc.insert_sequence(1, tail)
+    assert m.forked_seq_id == 0 and m.prefilled_offset == 60
+    pc.extend_sequence(1, tail[60:])
+    pc.recycle_sequence(0, True)
+    assert pc.num_recycling() == 1 and not removed
+    # a recycled sequence matching >= 90% of its length is reused as is (tail popped)
+    reuse = list(range(95)) + [1, 2]
+    m = pc.insert_sequence(2, reuse)
+    assert m.reused_seq_id == 0 and m.reused_seq_pop_last_tokens == 5 and m.prefilled_offset == 95
+    assert pc.num_recycling() == 0
+    pc.extend_sequence(0, reuse[95:])  # the caller keeps using the reused id
+    # recycling beyond the limit evicts the least recently used
+    for sid in (0, 1):
+        pc.recycle_sequence(sid, True)
+    pc.insert_sequence(3, [900, 901])
+    pc.extend_sequence(3, [900, 901])
+    pc.recycle_sequence(3, True)
+    assert pc.num_recycling() == 2 and len(removed) == 1
+    assert pc.try_free_memory() and len(removed) == 2
+
+
+def test_prefix_cache_disabled_never_matches():
+    pc = _core.PrefixCache(False, 0, None)
+    pc.insert_sequence(0, [1, 2, 3])
+    m = pc.insert_sequence(1, [1, 2, 3])
+    assert m.prefilled_offset == 0 and m.forked_seq_id == -1
+
+
+# ------------------------------------------------------------------ configs
+def test_generation_config_validation_and_defaults():
+    g = _core.GenerationConfig.from_json(json.dumps({"temperature": 0.5, "top_p": 0.9, "n": 2, "max_tokens": 7}))
+    d = json.loads(g.as_json())
+    assert d["temperature"] == 0.5 and d["n"] == 2 and g.max_tokens == 7
+    defaults = json.dumps({"temperature": 0.3, "top_p": 0.8, "repetition_penalty": 1.1})
+    d = json.loads(_core.GenerationConfig.from_json("{}", defaults).as_json())
+    assert d["temperature"] == pytest.approx(0.3) and d["top_p"] == pytest.approx(0.8)
+    for bad in ({"temperature": -1}, {"top_p": 1.5}, {"frequency_penalty": 3}, {"n": 0}, {"top_logprobs": 9},
+                {"logit_bias": {"5": 200}}, {"repetition_penalty": 0}):
+        with pytest.raises(Exception):
+            _core.GenerationConfig.from_json(json.dumps(bad))
+
+
+def test_engine_config_inference_modes():
+    model = {"params_bytes": 4 << 30, "num_layers": 32, "num_qo_heads": 32, "num_kv_heads": 8, "head_dim": 128,
+             "vocab_size": 128256, "context_window_size": 8192, "prefill_chunk_size": 8192, "max_batch_size": 128}
+    out = {}
+    for mode in ("local", "interactive", "server"):
+        r = _core.infer_capacity(json.dumps({"mode": mode}), [model], 180 << 30)
+        out[mode] = json.loads(r["config_json"])
+        assert r["num_pages"] * 16 >= out[mode]["max_total_sequence_length"]
+        assert abs(r["kv_bytes_per_token"] - 2 * 32 * 8 * 128 * 2) < 4  # KV rows + page-table bookkeeping
+    assert out["interactive"]["max_num_sequence"] == 1
+    assert out["local"]["max_num_sequence"] == 4
+    assert out["server"]["max_num_sequence"] >= 128
+    assert out["server"]["max_total_sequence_length"] > out["local"]["max_total_sequence_length"]
+    # explicit values are kept; impossible requests are rejected
+    r = _core.infer_capacity(json.dumps({"mode": "server", "max_num_sequence": 9, "max_total_sequence_length": 4096}),
+                             [model], 180 << 30)
+    c = json.loads(r["config_json"])
+    assert c["max_num_sequence"] == 9 and c["max_total_sequence_length"] == 4096
+    with pytest.raises(Exception):
+        _core.infer_capacity(json.dumps({"mode": "server"}), [model], 2 << 30)
+    rt = json.loads(_core.engine_config_roundtrip(json.dumps({"mode": "server", "prefix_cache_mode": "disable",
+                                                              "speculative_mode": "small_draft"})))
+    assert rt["prefix_cache_mode"] == "disable" and rt["speculative_mode"] == "small_draft"
+
+
+# ------------------------------------------------------------------ CPU sampler
+def test_cpu_sampler_top_p_and_verify():
+    p = np.asarray([0.5, 0.3, 0.15, 0.05], dtype=np.float32)
+    assert _core.cpu_sample_top_p(p, 1.0, 0.0)[0] == 0
+    assert _core.cpu_sample_top_p(p, 1.0, 0.79)[0] == 1
+    assert _core.cpu_sample_top_p(p, 1.0, 0.99)[0] == 3
+    # top_p 0.6 keeps {0, 1}: renormalised 0.625 / 0.375
+    tok, prob = _core.cpu_sample_top_p(p, 0.6, 0.7)
+    assert tok == 1 and prob == pytest.approx(0.3, abs=1e-5)  # reported on the unrenormalised distribution
+    q = p.copy()
+    _core.cpu_renormalize_top_p(q, 0.6)
+    assert q[2] == 0 and q[3] == 0 and q.sum() == pytest.approx(1.0)
+    # chain verification: draft token accepted when u < min(1, p/q), else resample from max(p - q, 0)
+    model = np.asarray([[0.1, 0.9, 0.0], [0.6, 0.2, 0.2], [0.3, 0.3, 0.4]], dtype=np.float32)
+    draft = np.asarray([[0.5, 0.5, 0.0], [0.1, 0.8, 0.1]], dtype=np.float32)
+    accepted, final = _core.cpu_verify_chain(model.copy(), draft, [1, 1], [0.5, 0.9], 0.0)
+    assert accepted == 1          # second draft token: p/q = 0.25 < 0.9 -> rejected
+    assert final == 0             # residual max(p - q, 0) = [0.5, 0, 0.1] -> u = 0 picks token 0
+    accepted, final = _core.cpu_verify_chain(model.copy(), draft, [1, 1], [0.5, 0.1], 0.99)
+    assert accepted == 2 and final == 2  # all accepted: bonus token from the last row
+
+
+# ------------------------------------------------------------------ tokenizer glue
+def test_text_streamer_handles_split_utf8_and_stop_strings():
+    tok = Tokenizer.synthetic(1000)
+    ids = tok.encode("héllo wörld ✓ done")
+    st = TextStreamer(tok)
+    pieces = [st.put([i]) for i in ids] + [st.finish()]
+    assert "".join(pieces) == tok.decode(ids)
+    assert all("�" not in p for p in pieces[:-1])
+    handler = StopStrHandler(["wör"], tok)
+    out = []
+    for i in ids:
+        out.extend(handler.put(i))
+        if handler.stop_triggered:
+            break
+    assert handler.stop_triggered
+    assert tok.decode(out) == "héllo "
+
+
+def test_tokenizer_info_detection():
+    info = json.loads(_core.detect_tokenizer_info(json.dumps(
+        {"decoder": {"type": "ByteLevel"}, "normalizer": None, "model": {"type": "BPE"}})))
+    assert info["token_postproc_method"] == "byte_level"
+    info = json.loads(_core.detect_tokenizer_info(json.dumps(
+        {"decoder": {"type": "Sequence", "decoders": [{"type": "Replace"}, {"type": "ByteFallback"}]},
+         "normalizer": {"type": "Prepend", "prepend": "▁"}, "model": {"type": "BPE"}})))
+    assert info["token_postproc_method"] == "byte_fallback" and info["prepend_space_in_encode"]
+    assert _core.post_process_token("<0x41>", "byte_fallback") == b"A"
+    assert _core.post_process_token("▁hi", "byte_fallback") == b" hi"
+    assert _core.post_process_token("Ġhi", "byte_level") == b" hi"
+
+
+# ------------------------------------------------------------------ event trace
+def test_event_trace_recorder_chrome_json():
+    rec = _core.EventTraceRecorder()
+    rec.add_event("req-1", "start prefill")
+    rec.add_event("req-1", "finish prefill")
+    rec.add_event_batch(["req-1", "req-2"], "decode")
+    events = json.loads(rec.dump_json())
+    names = [e["name"] for e in events]
+    assert len(events) == 4 and "decode" in "".join(names)
+    assert all({"ts", "ph", "pid"} <= set(e) for e in events)
+    # a start/finish pair becomes a begin/end pair on the request's own track
+    phases = [e["ph"] for e in events if e["name"].endswith("prefill")]
+    assert phases == ["B", "E"]
+    rec.clear()
+    assert json.loads(rec.dump_json()) == []
+
+
+# ------------------------------------------------------------------ conversation templates
+def test_conversation_templates_python_and_native_agree():
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "Hi"},
+            {"role": "assistant", "content": "Hello."}, {"role": "user", "content": "Bye"}]
+    for name in ("llama-3", "chatml", "llama-2", "mistral_default", "gemma_instruction", "phi-3", "qwen2",
+                 "deepseek", "LM"):
+        conv = ConvTemplateRegistry.get_conv_template(name)
+        assert conv is not None, name
+        c = Conversation.from_json_dict(conv.to_json_dict())
+        c.messages = []
+        for m in msgs:
+            if m["role"] == "system":
+                c.system_message = m["content"]
+            else:
+                c.messages.append((m["role"], m["content"]))
+        c.messages.append(("assistant", None))
+        py = "".join(p for p in c.as_prompt() if isinstance(p, str))
+        native = _core.conv_template_render(json.dumps(conv.to_json_dict()), json.dumps(msgs))
+        assert py == native, name
+    llama3 = ConvTemplateRegistry.get_conv_template("llama-3")
+    out = _core.conv_template_render(json.dumps(llama3.to_json_dict()), json.dumps(msgs[1:2]))
+    assert out.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n") and "Hi<|eot_id|>" in out
+    assert len(ConvTemplateRegistry.names()) >= 45
+
+
+# ------------------------------------------------------------------ protocol
+def test_openai_protocol_validation():
+    req = openai.ChatCompletionRequest(messages=[{"role": "user", "content": "x"}], logprobs=True, top_logprobs=3)
+    assert req.top_logprobs == 3
+    with pytest.raises(Exception):
+        openai.ChatCompletionRequest(messages=[{"role": "user", "content": "x"}], top_logprobs=3)  # needs logprobs
+    with pytest.raises(Exception):
+        openai.ChatCompletionRequest(messages=[{"role": "user", "content": "x"}], logprobs=True, top_logprobs=30)
+    with pytest.raises(Exception):
+        openai.ChatCompletionRequest(messages=[{"role": "system", "content": "a"}, {"role": "system", "content": "b"},
+                                               {"role": "user", "content": "x"}]).check_message_validity()
+    r = openai.CompletionRequest(prompt=[1, 2, 3], response_format={"type": "json_object", "schema": "{}"})
+    assert r.response_format.json_schema == "{}"
+    with pytest.raises(Exception):
+        openai.CompletionRequest(prompt="x", response_format={"type": "yaml"})
+
+
+# ------------------------------------------------------------------ artifacts
+@pytest.mark.parametrize("name", ["q4f16_1", "q4f16_0", "q3f16_1", "q4bf16_1", "q4f32_1"])
+def test_group_quantization_round_trip(name):
+    q = Q.get(name)
+    torch.manual_seed(0)
+    w = torch.randn(64, 160) * 0.1
+    qw, qs = Q.group_quantize(w, q)
+    assert qw.dtype == torch.int32 and qw.shape[0] == 64
+    back = Q.group_dequantize(qw, qs, q, k=160).float()
+    step = w.abs().amax() / q.max_int
+    assert (back - w).abs().max() <= step * 0.6 + 1e-3
+    if q.bits == 4 and q.group_size == 32:
+        assert qw.shape[1] == 160 // 8 and qs.shape == (64, 5)
+        # device nibble order is a pure permutation of the packed words
+        assert torch.equal(Q.from_device_layout_q4(Q.to_device_layout_q4(qw)), qw)
+
+
+def test_fp8_block_scale_round_trip():
+    w = torch.randn(256, 384) * 0.05
+    qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
+    assert qw.dtype == torch.float8_e4m3fn and sc.shape == (2, 3)
+    back = Q.fp8_block_dequantize(qw, sc, (128, 128)).float()
+    assert (back - w).abs().max() < 0.07 * w.abs().max()
+
+
+def test_tensor_cache_round_trip_and_md5(tmp_path):
+    torch.manual_seed(1)
+    tensors = {"a.weight": torch.randn(300, 70).half(), "b.q_weight": torch.randint(-2**31, 2**31 - 1, (64, 9), dtype=torch.int64).to(torch.int32),
+               "c.scale": torch.randn(7).bfloat16(), "d.bias": torch.randn(33), "e.fp8": torch.randn(16, 16).to(torch.float8_e4m3fn)}
+    doc = dump_tensor_cache(iter(tensors.items()), str(tmp_path), shard_bytes=32 * 1024)
+    assert len(doc["records"]) >= 2 and doc["metadata"]["ParamSize"] == sum(t.numel() for t in tensors.values())
+    cache = TensorCache(str(tmp_path), verify_md5=True)
+    got = dict(iter(cache))
+    assert set(got) == set(tensors)
+    for k in ("a.weight", "b.q_weight", "c.scale"):
+        assert torch.equal(got[k], tensors[k])
+    assert torch.equal(got["e.fp8"].view(torch.uint8), tensors["e.fp8"].view(torch.uint8))
+    # float32 is stored as its upper 16 bits ("f32-to-bf16") and widened on load
+    assert torch.equal(got["d.bias"], tensors["d.bias"].view(torch.int32).bitwise_and(-65536).view(torch.float32))
+    shard = tmp_path / doc["records"][0]["dataPath"]
+    data = bytearray(shard.read_bytes())
+    data[0] ^= 0xFF
+    shard.write_bytes(bytes(data))
+    with pytest.raises(ValueError):
+        list(TensorCache(str(tmp_path), verify_md5=True))
