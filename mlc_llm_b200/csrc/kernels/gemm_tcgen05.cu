@@ -313,10 +313,18 @@ struct KCursor {
   }
 };
 
-template <bool Q4>
-__global__ void __launch_bounds__(Q4 ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
+// WF: weight format. 0 = dense 16-bit, 1 = int4 groups of 32 (q4f16_1), 2 = fp8 e4m3 with one fp32
+// scale per 128 x 128 block (weights expanded to the activation dtype on the way to the tensor core).
+template <int WF>
+__global__ void __launch_bounds__(WF ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const GemmParams p) {
+  constexpr bool Q4 = WF != 0;  // "has a dequant stage"
+  constexpr int RAW_BYTES = WF == 2 ? BM * BK : RAW_STAGE_BYTES;            // packed tile of one K block
+  // Ring depth in the same space, kept even: the two dequant groups take alternate K blocks, so with an
+  // even depth every slot belongs to one group, which then observes every phase of the slot's barriers
+  // (a waiter that skipped a phase could mistake an older completion for the one it needs).
+  constexpr int RAW_N = (RAW_STAGES * RAW_STAGE_BYTES / RAW_BYTES) & ~1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -423,12 +431,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       KCursor cr;
       cr.init(p, total_kb, num_tiles);
       for (uint32_t ir = 0; cr.valid(num_tiles); ++ir, cr.next(p, total_kb, num_tiles)) {
-        const int s = ir % RAW_STAGES;
-        if (ir >= RAW_STAGES &&
-            !mbar_wait(&raw_empty[s], ((ir / RAW_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
+        const int s = ir % RAW_N;
+        if (ir >= RAW_N &&
+            !mbar_wait(&raw_empty[s], ((ir / RAW_N) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
           break;
-        mbar_expect_tx(&raw_full[s], RAW_STAGE_BYTES);
-        tma_load_2d(sraw + s * RAW_STAGE_BYTES, &tmap_w, &raw_full[s], cr.ka * (BK / 8), cr.ti.w_row);
+        mbar_expect_tx(&raw_full[s], RAW_BYTES);
+        tma_load_2d(sraw + s * RAW_BYTES, &tmap_w, &raw_full[s], WF == 2 ? cr.ka * BK : cr.ka * (BK / 8),
+                    cr.ti.w_row);
       }
     }
   } else if (warp == 1) {
@@ -489,9 +498,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       const uint32_t my_scale = smem_u32(sscale) + row * 4;
       auto fetch_scale = [&](const KCursor& c, uint32_t slot) {
         const uint32_t dst = my_scale + slot * SCALE_STAGE_BYTES;
-        const bool live = c.valid(num_tiles) && (c.ti.nb * BM + row < p.N) && (c.ka * 2 + 1 < groups_per_row);
+        const bool live = c.valid(num_tiles) && (c.ti.nb * BM + row < p.N) &&
+                          (WF == 2 || c.ka * 2 + 1 < groups_per_row);
         if (live) {
-          const __half* src = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row + c.ka * 2;
+          const void* src;
+          if (WF == 2)  // one fp32 scale per 128 x 128 block: the same word for every row of the tile
+            src = reinterpret_cast<const float*>(p.scale) +
+                  static_cast<size_t>(c.ti.w_row / 128) * ((p.K + 127) / 128) + (c.ka >> 1);
+          else
+            src = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row + c.ka * 2;
           asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
         } else {
           asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
@@ -512,22 +527,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       }
       for (uint32_t it = grp; cs.valid(num_tiles) && ok; it += 2) {
         const int s = it % STAGES;
-        const int rs = it % RAW_STAGES;
+        const int rs = it % RAW_N;
         const uint32_t slot = it % SCALE_DEPTH;
         asm volatile("cp.async.wait_group %0;" ::"n"(SCALE_DEPTH / 2 - 1) : "memory");
         uint32_t sc_bits;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc_bits) : "r"(my_scale + slot * SCALE_STAGE_BYTES) : "memory");
         const __half2 sc = *reinterpret_cast<__half2*>(&sc_bits);
         advance2(cs);
-        ok = mbar_wait(&raw_full[rs], (it / RAW_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
+        ok = mbar_wait(&raw_full[rs], (it / RAW_N) & 1, abort_flag, p.status, ERR_WAIT_TMA);
         ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
         if (!ok) break;
         if (threadIdx.x == 64) GEMM_TRACE(4, it);
-        const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_STAGE_BYTES + row * 32);
-        uint4 r0 = raw[0], r1 = raw[1];
+        constexpr int RAW_ROW = RAW_BYTES / BM;  // 32 bytes of nibbles or 64 bytes of fp8 per row
+        const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_BYTES + row * RAW_ROW);
+        uint32_t words[RAW_ROW / 4];
+#pragma unroll
+        for (int i = 0; i < RAW_ROW / 16; ++i) {
+          const uint4 r = raw[i];
+          words[4 * i] = r.x; words[4 * i + 1] = r.y; words[4 * i + 2] = r.z; words[4 * i + 3] = r.w;
+        }
+        // The packed values are in registers: recycle the slot early. Its next writer is the TMA
+        // engine (async proxy) while these reads went through the generic proxy, so a proxy fence
+        // must order them before the release (without it the refill was seen overtaking the reads).
+        fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);  // nibbles are in registers: recycle early
-        uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
         // the expanded tile may only be overwritten once the MMA that read it has finished
         if (it >= STAGES) {
           ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
@@ -535,6 +559,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           if (!ok) break;
         }
         uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
+        if constexpr (WF == 2) {
+          const float fs = __uint_as_float(sc_bits);
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {  // 8 fp8 values -> one 16-byte chunk of the expanded row
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t pair = (words[2 * w + (j >> 1)] >> (16 * (j & 1))) & 0xffffu;
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair), __NV_E4M3);
+              float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+              f.x *= fs;
+              f.y *= fs;
+              if (p.ab_fmt == 0) {
+                const __half2 o = __float22half2_rn(f);
+                h[j] = *reinterpret_cast<const uint32_t*>(&o);
+              } else {
+                const __nv_bfloat162 o = __float22bfloat162_rn(f);
+                h[j] = *reinterpret_cast<const uint32_t*>(&o);
+              }
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+          }
+        } else {
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
           const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
@@ -553,6 +600,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           }
           *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
               make_uint4(h[0], h[1], h[2], h[3]);
+        }
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -904,20 +952,23 @@ struct MlcbFusedArgs {
 static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
                        int* status, float* workspace, long long workspace_bytes, int* counters,
-                       int num_counters, cudaStream_t stream, const MlcbFusedArgs* f) {
+                       int num_counters, cudaStream_t stream, const MlcbFusedArgs* f, int wf_hint = 0) {
   if (M <= 0 || N <= 0) return 0;
   const bool rs = f && f->rs_world > 0;
   if (rs && (f->rs_world > 8 || f->rs_rows % 32 != 0 || N % 8 != 0 || out_dtype > 1 ||
              static_cast<long long>(f->rs_rows) * f->rs_world < M))
     return -5;
-  const bool q4 = scale != nullptr;
+  const int wf = scale == nullptr ? 0 : ((wf_hint == 2 || (f && f->reserved == 2)) ? 2 : 1);
+  const bool q4 = wf == 1;
   if (K % 8 != 0 || ldx % 8 != 0) return -1;
   if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
+  if (wf == 2 && K % 64 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     attr_set = true;
   }
   GemmParams p = {};
@@ -984,6 +1035,11 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
     uint32_t wb[2] = {BK / 8, BM};
     mw = get_tensor_map(w, 4, 2, wd, ws, wb, 0);
+  } else if (wf == 2) {
+    uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t ws[1] = {static_cast<uint64_t>(K)};
+    uint32_t wb[2] = {BK, BM};
+    mw = get_tensor_map(w, 1, 2, wd, ws, wb, 0);
   } else {
     uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -994,9 +1050,11 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (q4)
-    gemm_kernel<true><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<1><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  else if (wf == 2)
+    gemm_kernel<2><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
-    gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -1007,6 +1065,19 @@ MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const vo
                        int num_counters, cudaStream_t stream) {
   return gemm_launch(x, w, scale, bias, y, M, N, K, ldx, ldy, ab_fmt, out_dtype, status, workspace,
                      workspace_bytes, counters, num_counters, stream, nullptr);
+}
+
+// Weights in fp8 e4m3 [N, K] with one fp32 scale per 128 x 128 block (`scale_inv` [ceil(N/128),
+// ceil(K/128)], the "weight_scale_inv" tensor of block-scaled fp8 checkpoints); activations and the
+// tensor-core math stay 16-bit. Reference: quantization/block_scale_quantization.py with the
+// CUTLASS / Triton fp8 group GEMMs (op/cutlass.py, op/triton.py).
+MLCB_API int mlcb_gemm_fp8(const void* x, const void* w, const void* scale_inv, const void* bias, void* y,
+                           int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype, int* status,
+                           float* workspace, long long workspace_bytes, int* counters, int num_counters,
+                           cudaStream_t stream) {
+  if (!scale_inv) return -2;
+  return gemm_launch(x, w, scale_inv, bias, y, M, N, K, ldx, ldy, ab_fmt, out_dtype, status, workspace,
+                     workspace_bytes, counters, num_counters, stream, nullptr, 2);
 }
 
 // Tensor-parallel forms of the same kernel (one launch each, collective included):
@@ -1059,8 +1130,8 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     attr_set = true;
   }
   GemmParams p = {};
@@ -1110,9 +1181,9 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   const long long max_tiles = (static_cast<long long>(rows_hint) / p.tn + num_groups) * p.num_n_blocks;
   const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
   if (q4)
-    gemm_kernel<true><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<1><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
-    gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -1206,7 +1277,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
                             "mlcb_gemm_noalloc: cudaGetSymbolAddress failed (%lld)", err);
       static bool attr_set_noalloc = false;
       if (!attr_set_noalloc) {
-        cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+        cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
         attr_set_noalloc = true;
       }
       g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
@@ -1264,7 +1335,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
     return noalloc_fail(MLCB_NOALLOC_NO_DRIVER_ENTRY, "mlcb_gemm_noalloc: could not encode the TMA tensor maps");
   const int items = static_cast<int>(tiles) * p.splits;
   const int grid = items < sm_count() ? items : sm_count();
-  gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(mx, mw, p);
+  gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(mx, mw, p);
   count_launch();
   err = cudaGetLastError();
   if (err != cudaSuccess) return noalloc_fail(static_cast<int>(err), "mlcb_gemm_noalloc: launch failed (%lld)", err);

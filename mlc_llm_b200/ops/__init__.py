@@ -121,7 +121,7 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
                              stream_ptr())
-    elif lw.kind == "fp8_block" and x2.dtype == torch.bfloat16 and k % 128 == 0:
+    elif lw.kind == "fp8_block" and k % 64 == 0 and lw.w.dtype == torch.float8_e4m3fn:
         from .fp8 import linear_fp8_block  # pylint: disable=import-outside-toplevel
 
         return linear_fp8_block(x2, lw, od).reshape(*lead, n)

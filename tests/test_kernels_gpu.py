@@ -403,3 +403,19 @@ def test_expert_parallel_exchange_single_rank(quant_name, tokens):
         ops.check_status(torch.device(DEV))
         tol = 3e-2 if dt == torch.bfloat16 else 4e-3
         _close(got, want, tol, tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (33, 384, 512), (256, 1024, 4096), (700, 512, 1024)])
+def test_fp8_block_scale_linear(dtype, m, n, k):
+    torch.manual_seed(3)
+    w = torch.randn(n, k) * 0.05
+    qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
+    quant = Q.get("fp8_e4m3fn_bf16_block_scale")
+    x = (torch.randn(m, k) * 0.5).to(dtype)
+    lw = ops.LinearWeight("fp8_block", qw.to(DEV), sc.float().to(DEV), None, quant, n, k)
+    y = ops.linear(x.to(DEV), lw)
+    ops.check_status(torch.device(DEV))
+    want = x.float() @ Q.fp8_block_dequantize(qw, sc, (128, 128)).float().t()
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    _close(y, want, tol, tol * want.abs().max().item())
