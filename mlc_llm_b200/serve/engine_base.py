@@ -317,7 +317,11 @@ class EngineRuntime:
             self.num_pages.append(n_pages)
         full = json.loads(self.complete_config_json)
         self.fused_tp = False
-        if tp > 1 and self.device.type == "cuda" and os.environ.get("MLCB_FUSED_TP", "1") != "0":
+        # MLCB_FUSED_TP: "1" = always, "0" = never, default "auto" = where the fused kernels measured at or
+        # above the NCCL path (2 ranks); with more ranks NCCL's in-switch reduction currently wins.
+        fused_mode = os.environ.get("MLCB_FUSED_TP", "auto")
+        use_fused = fused_mode == "1" or (fused_mode == "auto" and tp == 2)
+        if tp > 1 and self.device.type == "cuda" and use_fused:
             # fused GEMM+collective kernels over symmetric peer buffers (main model only)
             from ..parallel.fused import FusedCollectives  # pylint: disable=import-outside-toplevel
 
