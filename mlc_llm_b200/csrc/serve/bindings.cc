@@ -7,6 +7,7 @@
 #include "config.h"
 #include "conv_template.h"
 #include "engine.h"
+#include "json_ffi_engine.h"
 #include "kv_manager.h"
 #include "metrics.h"
 #include "prefix_cache.h"
@@ -503,6 +504,36 @@ PYBIND11_MODULE(_core, m) {
       .def("debug_stats", &Engine::DebugStats)
       .def("config_json", [](Engine& e) { return e.Config().AsJSON().dump(); })
       .def("set_stream_callback", [](Engine& e, py::object cb) { e.SetStreamCallback(WrapCallback(cb)); });
+
+  py::class_<JsonFFIEngine>(m, "JsonFFIEngine")
+      .def(py::init([](py::object factory, std::shared_ptr<Tokenizer> tokenizer, const std::string& conv_json,
+                       const std::string& model_name, py::object callback) {
+             auto holder = std::make_shared<py::object>(std::move(factory));
+             ThreadedEngine::EngineFactory fn = [holder](const std::string& cfg, StreamCallback cb) {
+               py::gil_scoped_acquire gil;
+               py::object eng = (*holder)(cfg);
+               Engine* raw = eng.cast<Engine*>();
+               raw->SetStreamCallback(cb);
+               return std::unique_ptr<Engine>(new ProxyEngine(std::move(eng), raw));
+             };
+             auto cb_holder = std::make_shared<py::object>(std::move(callback));
+             JsonFFIEngine::JSONCallback cb = [cb_holder](const std::string& chunks_json) {
+               py::gil_scoped_acquire gil;
+               (*cb_holder)(chunks_json);
+             };
+             return new JsonFFIEngine(fn, std::move(tokenizer), conv_json, model_name, cb);
+           }))
+      .def("chat_completion", &JsonFFIEngine::ChatCompletion, py::call_guard<py::gil_scoped_release>())
+      .def("abort", &JsonFFIEngine::Abort, py::call_guard<py::gil_scoped_release>())
+      .def("get_last_error", &JsonFFIEngine::GetLastError)
+      .def("reload", &JsonFFIEngine::Reload, py::call_guard<py::gil_scoped_release>())
+      .def("unload", &JsonFFIEngine::Unload, py::call_guard<py::gil_scoped_release>())
+      .def("reset", &JsonFFIEngine::Reset, py::call_guard<py::gil_scoped_release>())
+      .def("run_background_loop", &JsonFFIEngine::RunBackgroundLoop, py::call_guard<py::gil_scoped_release>())
+      .def("run_background_stream_back_loop", &JsonFFIEngine::RunBackgroundStreamBackLoop,
+           py::call_guard<py::gil_scoped_release>())
+      .def("exit_background_loop", &JsonFFIEngine::ExitBackgroundLoop, py::call_guard<py::gil_scoped_release>())
+      .def("json_metrics", &JsonFFIEngine::JSONMetrics);
 
   py::class_<ThreadedEngine>(m, "ThreadedEngine")
       .def(py::init([](py::object factory, py::object frontend_callback) {

@@ -208,3 +208,32 @@ def test_request_validation_errors():
         assert ok.usage.completion_tokens <= 2
     finally:
         eng.terminate()
+
+
+def test_json_ffi_engine_matches_python_engine():
+    """The native JSON front end (template + tokenizer + detokenizer in C++) gives the same text as
+    the Python protocol path."""
+    from mlc_llm_b200.json_ffi import JSONFFIEngine
+
+    msgs = [{"role": "user", "content": "hello there"}]
+    ffi = JSONFFIEngine(MODEL, "cpu", engine_config=EngineConfig(mode="local"))
+    try:
+        chunks = list(ffi.chat.completions.create(messages=msgs, max_tokens=8, temperature=0.0,
+                                                  stream_options={"include_usage": True}))
+        text = "".join(ch.delta.content or "" for c in chunks for ch in c.choices)
+        assert chunks[-1].usage is not None and chunks[-1].usage.completion_tokens <= 8
+        assert any(ch.finish_reason for c in chunks for ch in c.choices)
+        with pytest.raises(ValueError):
+            list(ffi.chat.completions.create(messages=msgs, max_tokens=4, temperature=-3))
+        ffi._test_reset()
+        again = "".join(ch.delta.content or "" for c in ffi.chat.completions.create(
+            messages=msgs, max_tokens=8, temperature=0.0) for ch in c.choices)
+        assert again == text
+    finally:
+        ffi.terminate()
+    py = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(mode="local"))
+    try:
+        r = py.chat.completions.create(messages=msgs, max_tokens=8, temperature=0.0)
+        assert r.choices[0].message.content == text
+    finally:
+        py.terminate()
