@@ -204,9 +204,50 @@ __global__ void page_copy_kernel(uint8_t* __restrict__ pages, const int* __restr
   for (size_t v = threadIdx.x; v < page_bytes / 16; v += blockDim.x) dp[v] = sp[v];
 }
 
+// Copies the KV rows of individual token slots from one paged pool to another (the other pool may
+// live on a peer GPU: prefill -> decode hand-off of disaggregated serving). Pools are
+// [layers][pages][2][hkv][page][row_bytes]; one warp moves one (token, layer, k|v, head) row.
+__global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                    const int* __restrict__ src_slots, const int* __restrict__ dst_slots,
+                                    int n, int layers, size_t src_layer_stride, size_t dst_layer_stride, int hkv,
+                                    int page, int row_bytes) {
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(n) * layers * 2 * hkv;
+  if (warp >= total) return;
+  const int h = static_cast<int>(warp % hkv);
+  const int kv = static_cast<int>((warp / hkv) % 2);
+  const int l = static_cast<int>((warp / (2 * hkv)) % layers);
+  const int i = static_cast<int>(warp / (static_cast<long long>(2) * hkv * layers));
+  const int ss = src_slots[i], ds = dst_slots[i];
+  const size_t head_bytes = static_cast<size_t>(page) * row_bytes;
+  const size_t so = l * src_layer_stride + ((static_cast<size_t>(ss / page) * 2 + kv) * hkv + h) * head_bytes +
+                    static_cast<size_t>(ss % page) * row_bytes;
+  const size_t dof = l * dst_layer_stride + ((static_cast<size_t>(ds / page) * 2 + kv) * hkv + h) * head_bytes +
+                     static_cast<size_t>(ds % page) * row_bytes;
+  const uint4* sp = reinterpret_cast<const uint4*>(src + so);
+  uint4* dp = reinterpret_cast<uint4*>(dst + dof);
+  for (int v = lane; v < row_bytes / 16; v += 32) dp[v] = sp[v];
+}
+
 }  // namespace mlcb
 
 using namespace mlcb;
+
+// Strides in bytes; row_bytes = head_dim * element size (multiple of 16).
+MLCB_API int mlcb_kv_slot_copy(const void* src, void* dst, const int* src_slots, const int* dst_slots, int n,
+                               int layers, long long src_layer_stride, long long dst_layer_stride, int hkv,
+                               int page, int row_bytes, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (row_bytes % 16) return -1;
+  const long long warps = static_cast<long long>(n) * layers * 2 * hkv;
+  const long long blocks = (warps + 7) / 8;
+  kv_slot_copy_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), src_slots, dst_slots, n, layers,
+      static_cast<size_t>(src_layer_stride), static_cast<size_t>(dst_layer_stride), hkv, page, row_bytes);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
 
 // dtype: 0 fp16, 1 bf16
 MLCB_API int mlcb_rmsnorm(const void* x, void* residual, const void* w, void* out, int tokens,

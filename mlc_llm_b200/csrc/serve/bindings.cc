@@ -121,6 +121,14 @@ class PyModelBackend : public ModelBackend {
     py::gil_scoped_acquire gil;
     impl_.attr("move_kv_tokens")(model_id, ToArray(moves));
   }
+  void ApplyPageCopies(int model_id, const std::vector<int32_t>& copies) override {
+    py::gil_scoped_acquire gil;
+    impl_.attr("apply_page_copies")(model_id, ToArray(copies));
+  }
+  void SendKV(int model_id, const std::vector<int32_t>& src_slots, const std::string& metadata) override {
+    py::gil_scoped_acquire gil;
+    impl_.attr("send_kv")(model_id, ToArray(src_slots), metadata);
+  }
   void Synchronize() override {
     py::gil_scoped_acquire gil;
     if (py::hasattr(impl_, "synchronize")) impl_.attr("synchronize")();

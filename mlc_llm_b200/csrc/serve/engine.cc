@@ -150,6 +150,19 @@ class EngineImpl : public Engine {
       Emit({std::move(out)});
       return;
     }
+    const DisaggConfig& dc = req.cfg.debug_config.disagg_config;
+    if (dc.kind == DisaggRequestKind::kStartGeneration && TakeOverReservedRequest(rs.get())) return;
+    if (dc.kind == DisaggRequestKind::kRemoteSend) {
+      // prefill [0, end) only; the single sampled token is discarded by the caller
+      int64_t end = dc.kv_window_end.value_or(-1);
+      if (end < 0) end += req.prompt_tokens;
+      end = std::max<int64_t>(1, std::min<int64_t>(end, req.prompt_tokens));
+      TruncateInputs(&req.inputs, end);
+      req.prompt_tokens = end;
+      req.cfg.max_tokens = 1;
+      req.cfg.n = 1;
+      req.cfg.debug_config.ignore_eos = true;
+    }
     if (states_.count(req.id)) throw std::runtime_error("duplicate request id " + req.id);
     const int n = req.cfg.n;
     const int num_entries = n == 1 ? 1 : n + 1;
@@ -187,7 +200,153 @@ class EngineImpl : public Engine {
     }
     RequestState* raw = rs.get();
     states_[req.id] = std::move(rs);
+    if (dc.kind == DisaggRequestKind::kPrepareReceive) {
+      PrepareReceive(raw);
+      return;
+    }
     waiting_.push_back(raw);
+  }
+
+  // ---------------------------------------------------------------- disaggregated serving
+  // (reference: engine_actions/disagg_prepare_recv.cc, disagg_remote_send.cc and the
+  // start-generation handling of new_request_prefill.cc)
+  static void TruncateInputs(std::vector<InputItem>* inputs, int64_t keep) {
+    int64_t left = keep;
+    std::vector<InputItem> out;
+    for (auto& in : *inputs) {
+      if (left <= 0) break;
+      if (in.kind != 0) throw std::runtime_error("disaggregated requests take token inputs only");
+      InputItem it = in;
+      if (static_cast<int64_t>(it.tokens.size()) > left) it.tokens.resize(left);
+      left -= static_cast<int64_t>(it.tokens.size());
+      out.push_back(std::move(it));
+    }
+    *inputs = std::move(out);
+  }
+
+  static std::vector<int32_t> AllTokens(const Request& req) {
+    std::vector<int32_t> t;
+    for (auto& in : req.inputs) t.insert(t.end(), in.tokens.begin(), in.tokens.end());
+    return t;
+  }
+
+  // Decode side, step 1: match the prompt against the prefix cache, reserve KV entries for
+  // [matched, end) and report where a sender may write them. The request then waits (outside the
+  // scheduling queues) for its start-generation step.
+  void PrepareReceive(RequestState* rs) {
+    Request& req = rs->request;
+    const DisaggConfig& dc = req.cfg.debug_config.disagg_config;
+    try {
+      if (req.cfg.n != 1) throw std::runtime_error("disaggregated requests must have n == 1");
+      if (kv_.size() != 1) throw std::runtime_error("disaggregated serving does not combine with draft models");
+      if (cfg_.sliding_window_size > 0) throw std::runtime_error("disaggregated serving needs a full KV cache");
+      int64_t end = dc.kv_window_end.value_or(-1);
+      if (end < 0) end += req.prompt_tokens;
+      end = std::max<int64_t>(0, std::min<int64_t>(end, req.prompt_tokens - 1));  // the last token stays local
+      std::vector<int32_t> tokens = AllTokens(req);
+      RequestStateEntry& e = rs->entries[0];
+      ModelState& ms = e.mstates[0];
+      // match on the part that will be received
+      ms.inputs.clear();
+      InputItem head;
+      head.tokens.assign(tokens.begin(), tokens.begin() + end);
+      if (end > 0) ms.inputs.push_back(std::move(head));
+      if (NumActiveSequences() + 1 > cfg_.max_num_sequence) throw std::runtime_error("too many sequences");
+      MatchPrefixAndCreateSequence({rs, 0});
+      const int64_t matched = ms.num_prefilled_tokens;
+      const int64_t need = end - matched;
+      ForwardPlan plan;
+      if (need > 0) {
+        if (!EnsurePages(kv_[0]->PagesNeeded(ms.internal_id, need) + 1))
+          throw std::runtime_error("not enough KV memory to receive the request");
+        plan = kv_[0]->BeginForward({ms.internal_id}, {static_cast<int32_t>(need)});
+        if (!plan.page_copies.empty()) backend_->ApplyPageCopies(0, plan.page_copies);
+      }
+      rs->disagg_reserved_end = end;
+      rs->disagg_matched = matched;
+      e.status = EntryStatus::kAlive;  // holds a sequence; not schedulable until start-generation
+      ms.inputs.clear();
+      json::Array slots;
+      for (int32_t sl : plan.slots) slots.push_back(Value(static_cast<int64_t>(sl)));
+      Object meta;
+      meta["slots"] = Value(std::move(slots));
+      meta["begin"] = matched;
+      meta["end"] = end;
+      Object disagg;
+      disagg["kv_append_metadata"] = Value(Value(std::move(meta)).dump());
+      disagg["prefix_matched_length"] = matched;
+      RequestStreamOutput out;
+      out.request_id = req.id;
+      out.group_delta_token_ids.resize(1);
+      out.group_delta_logprob_json_strs.resize(1);
+      out.group_finish_reason = {"stop"};
+      out.group_extra_prefix_string = {""};
+      Value usage = rs->metrics.AsUsageJSON(true);
+      usage.as_object()["extra"].as_object()["disagg"] = Value(Value(std::move(disagg)).dump());
+      out.request_final_usage_json_str = usage.dump();
+      Emit({std::move(out)});
+    } catch (...) {
+      for (auto& e : rs->entries) ReleaseEntry(e, /*recycle=*/false);
+      states_.erase(req.id);
+      throw;
+    }
+  }
+
+  // Decode side, step 3: the KV of [0, begin) has arrived; prefill the rest locally and decode.
+  // Returns false when no reservation exists for this id (the request then runs as a normal one).
+  bool TakeOverReservedRequest(RequestState* incoming) {
+    auto it = states_.find(incoming->request.id);
+    if (it == states_.end() || it->second->disagg_reserved_end < 0) return false;
+    RequestState* rs = it->second.get();
+    const DisaggConfig& dc = incoming->request.cfg.debug_config.disagg_config;
+    const int64_t begin = dc.kv_window_begin.value_or(rs->disagg_reserved_end);
+    if (begin != rs->disagg_reserved_end)
+      throw std::runtime_error("start-generation position does not match the reserved KV range");
+    std::vector<int32_t> tokens = AllTokens(incoming->request);
+    if (static_cast<int64_t>(tokens.size()) <= begin) throw std::runtime_error("nothing left to prefill");
+    rs->request.cfg = incoming->request.cfg;
+    rs->request.cfg.debug_config.disagg_config = DisaggConfig();
+    rs->request.inputs = incoming->request.inputs;
+    rs->request.prompt_tokens = static_cast<int64_t>(tokens.size());
+    rs->metrics = RequestMetrics();
+    rs->metrics.prompt_tokens = rs->request.prompt_tokens;
+    rs->metrics.add_time = NowSeconds();
+    RequestStateEntry& e = rs->entries[0];
+    ModelState& ms = e.mstates[0];
+    e.stop_handler = std::make_unique<StopStrHandler>(rs->request.cfg.stop_strs, tok_);
+    if (rs->request.cfg.seed >= 0) e.rng.seed(static_cast<uint64_t>(rs->request.cfg.seed));
+    // received tokens become part of the cached prefix of this sequence
+    if (prefix_cache_.HasSequence(ms.internal_id) && begin > rs->disagg_matched) {
+      std::vector<int32_t> got(tokens.begin() + rs->disagg_matched, tokens.begin() + begin);
+      prefix_cache_.ExtendSequence(ms.internal_id, got);
+      prefix_cache_.CommitSequenceExtention();
+    }
+    ms.prefilled_tokens.assign(tokens.begin(), tokens.begin() + begin);
+    ms.num_prefilled_tokens = begin;
+    ms.inputs.clear();
+    InputItem rest;
+    rest.tokens.assign(tokens.begin() + begin, tokens.end());
+    ms.inputs.push_back(std::move(rest));
+    rs->disagg_reserved_end = -1;
+    rs->num_unfinished = 1;
+    running_.push_back(rs);  // it already owns a KV sequence: a running request with inputs left
+    return true;
+  }
+
+  // Prefill side: after [0, end) is computed, copy the KV of [begin, end) to the receiver.
+  void SendKVOfFinishedEntry(RequestState* rs, RequestStateEntry& e) {
+    const DisaggConfig& dc = rs->request.cfg.debug_config.disagg_config;
+    const int64_t id = e.mstates[0].internal_id;
+    if (id < 0 || !kv_[0]->Has(id)) return;
+    const int64_t end = rs->request.prompt_tokens;
+    const int64_t begin = std::max<int64_t>(0, std::min<int64_t>(dc.kv_window_begin.value_or(0), end));
+    if (begin >= end) return;
+    std::vector<int32_t> pages = kv_[0]->SequencePages(id);
+    const int64_t page = cfg_.kv_cache_page_size;
+    std::vector<int32_t> slots;
+    for (int64_t pos = begin; pos < end; ++pos)
+      slots.push_back(static_cast<int32_t>(pages[pos / page] * page + pos % page));
+    backend_->SendKV(0, slots, dc.kv_append_metadata);
   }
 
   void AbortRequest(const std::string& request_id) override {
@@ -1037,6 +1196,8 @@ class EngineImpl : public Engine {
         if (!finish.empty()) {
           any = true;
           out.group_finish_reason[g] = finish;
+          if (req.cfg.debug_config.disagg_config.kind == DisaggRequestKind::kRemoteSend)
+            SendKVOfFinishedEntry(rs, e);
           FinishEntry(rs, e, finish);
           // the KV may hold tokens past the finish point (speculation): trim, then recycle
           ReleaseEntry(e, /*recycle=*/true);

@@ -13,6 +13,7 @@
 // post-processing action_commons.cc:177-331, draft/verify batch_draft.cc / batch_verify.cc),
 // cpp/serve/request_state.cc:175-263 (finish rules) and cpp/serve/threaded_engine.cc:31-401.
 #pragma once
+#include <stdexcept>
 #include <atomic>
 #include <condition_variable>
 #include <deque>
@@ -123,6 +124,15 @@ class ModelBackend {
                                      const VerifyParams& verify) = 0;
   // Applies (src_slot, dst_slot) token moves in the KV pages of `model_id` (tree commit).
   virtual void MoveKVTokens(int model_id, const std::vector<int32_t>& moves) = 0;
+  // Applies (src_page, dst_page) copies outside a forward call (KV reserved for a remote sender).
+  virtual void ApplyPageCopies(int /*model_id*/, const std::vector<int32_t>& /*copies*/) {
+    throw std::runtime_error("this backend cannot reserve KV for disaggregated serving");
+  }
+  // Copies the KV entries at `src_slots` of `model_id` into the receiver described by `metadata`
+  // (opaque payload produced by the receiving engine's prepare-receive step). Blocks until done.
+  virtual void SendKV(int /*model_id*/, const std::vector<int32_t>& /*src_slots*/, const std::string& /*metadata*/) {
+    throw std::runtime_error("this backend cannot send KV to a remote engine");
+  }
   virtual void Synchronize() {}
   virtual void ReleaseEmbedding(int64_t /*handle*/) {}
   virtual void Reset() {}
@@ -181,6 +191,10 @@ struct RequestState {
   RequestMetrics metrics;
   bool prefill_done = false;
   int num_unfinished = 0;
+  // disaggregated serving: KV for positions [.., disagg_reserved_end) is reserved / being received
+  // and the request waits for its start-generation step (-1: not such a request)
+  int64_t disagg_reserved_end = -1;
+  int64_t disagg_matched = 0;
 };
 
 // ------------------------------------------------------------------ engine

@@ -61,8 +61,14 @@ class Router:  # pylint: disable=too-many-instance-attributes
             def start(i: int) -> None:
                 gpu_ids = list(range(self.device_id_starts[i], self.device_id_starts[i + 1])) \
                     if device.startswith("cuda") else None
+                server_device = device
+                if router_mode == "disagg" and device.startswith("cuda"):
+                    # the prefill engine maps the decode engine's KV pool through CUDA IPC, so every
+                    # endpoint must see all GPUs: select the device by index instead of masking
+                    gpu_ids = None
+                    server_device = f"cuda:{self.device_id_starts[i]}"
                 srv = PopenServer(
-                    model, device, model_lib=model_lib, mode="server", host=hosts[i], port=ports[i],
+                    model, server_device, model_lib=model_lib, mode="server", host=hosts[i], port=ports[i],
                     enable_debug=True, gpu_ids=gpu_ids,
                     tensor_parallel_shards=num_gpus[i] if num_gpus[i] > 1 else None,
                     engine_config=EngineConfig(prefix_cache_mode="radix" if enable_prefix_cache else "disable",

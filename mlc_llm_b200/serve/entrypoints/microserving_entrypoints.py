@@ -37,6 +37,20 @@ def _as_completion(request, disagg: DisaggConfig) -> CompletionRequest:
     return base
 
 
+def prep_recv_response(engine, response) -> PrepRecvResponse:
+    """Wrap the engine's slot reservation with a handle of its KV pool, so the prefill engine knows
+    where (which device memory) and at which slots to write."""
+    import base64  # pylint: disable=import-outside-toplevel
+
+    extra = json.loads(response.usage.extra["disagg"]) if response.usage and response.usage.extra and \
+        "disagg" in response.usage.extra else {}
+    reservation = json.loads(extra.get("kv_append_metadata") or "{}")
+    payload = {"pool": engine.runtime.executor.kv_export(0), "slots": reservation.get("slots", []),
+               "begin": reservation.get("begin", 0), "end": reservation.get("end", 0)}
+    return PrepRecvResponse(kv_append_metadata=base64.b64encode(json.dumps(payload).encode()).decode("ascii"),
+                            prefix_matched_length=int(extra.get("prefix_matched_length", 0)))
+
+
 @app.post("/microserving/prep_recv")
 async def prep_recv(request: PrepRecvRequest):
     engine = ServerContext.current().get_engine(request.model)
@@ -47,10 +61,7 @@ async def prep_recv(request: PrepRecvRequest):
     completion.stream = False
     request_id = engine_base.create_request_id("cmpl", request.user)
     response = await engine._gather_completion(completion, request_id)  # pylint: disable=protected-access
-    extra = json.loads(response.usage.extra["disagg"]) if response.usage and response.usage.extra and \
-        "disagg" in response.usage.extra else {}
-    return PrepRecvResponse(kv_append_metadata=extra.get("kv_append_metadata", ""),
-                            prefix_matched_length=int(extra.get("prefix_matched_length", 0)))
+    return prep_recv_response(engine, response)
 
 
 @app.post("/microserving/remote_send")

@@ -12,6 +12,9 @@ verify wrappers), ``cpp/serve/logit_processor.cc:40-458`` and ``cpp/serve/sample
 
 from __future__ import annotations
 
+import json
+import os
+
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -25,6 +28,10 @@ _INT_KEYS = ("positions", "slots", "q_seq", "q_kvlen", "q_kvstart", "page_indptr
 _S_INT = ("logit_token_index", "top_k", "pen_row", "pen_token", "pen_count", "bias_row", "bias_token",
           "mask_rows", "mask_bits", "prob_slots")
 _S_FLT = ("temperature", "top_p", "uniform", "penalties", "bias_value")
+
+
+# KV pools exported by engines of this process (disaggregated serving inside one process)
+_LOCAL_KV_POOLS: Dict[str, torch.Tensor] = {}
 
 
 def _pad4(n: int) -> int:
@@ -347,6 +354,82 @@ class ModelExecutor:
         if self.comm is not None:
             self.comm.broadcast_step("move", model_id, {"moves": np.ascontiguousarray(moves, dtype=np.int32)}, {})
         self.models[model_id].move_tokens(torch.from_numpy(np.ascontiguousarray(moves, dtype=np.int32)).to(self.device))
+
+    # ------------------------------------------------------------------ disaggregated serving
+    def apply_page_copies(self, model_id: int, copies: np.ndarray) -> None:
+        """Copy-on-write page copies of a KV reservation that is not followed by a forward call."""
+        if self.comm is not None and self.comm.world_size > 1:
+            raise RuntimeError("disaggregated serving supports single-GPU endpoints only")
+        pairs = torch.from_numpy(np.ascontiguousarray(copies, dtype=np.int32)).to(self.device)
+        self.models[model_id].copy_pages(pairs)
+
+    def kv_export(self, model_id: int = 0) -> str:
+        """Opaque description of this engine's KV pool that a peer engine can write into: an
+        in-process registry key (engines sharing a process, CPU tests) plus, on GPUs, a CUDA IPC
+        handle of the pool (engines in different processes of one NVLink box)."""
+        import base64  # pylint: disable=import-outside-toplevel
+        import pickle  # pylint: disable=import-outside-toplevel
+        import uuid  # pylint: disable=import-outside-toplevel
+
+        pool = self.models[model_id].kv_pages
+        key = getattr(self, "_kv_export_key", None)
+        if key is None:
+            key = self._kv_export_key = uuid.uuid4().hex
+            _LOCAL_KV_POOLS[key] = pool
+        desc = {"key": key, "pid": os.getpid(), "shape": list(pool.shape), "dtype": str(pool.dtype)}
+        if pool.is_cuda:
+            from torch.multiprocessing.reductions import reduce_tensor  # pylint: disable=import-outside-toplevel
+
+            fn, args = reduce_tensor(pool)
+            desc["ipc"] = base64.b64encode(pickle.dumps((fn, args))).decode("ascii")
+        return base64.b64encode(json.dumps(desc).encode()).decode("ascii")
+
+    def _peer_pool(self, desc: dict) -> torch.Tensor:
+        if desc["pid"] == os.getpid() and desc["key"] in _LOCAL_KV_POOLS:
+            return _LOCAL_KV_POOLS[desc["key"]]
+        cache = self.__dict__.setdefault("_peer_pools", {})
+        if desc["key"] not in cache:
+            import base64  # pylint: disable=import-outside-toplevel
+            import pickle  # pylint: disable=import-outside-toplevel
+
+            if "ipc" not in desc:
+                raise RuntimeError("the receiving engine did not export a device memory handle")
+            fn, args = pickle.loads(base64.b64decode(desc["ipc"]))
+            cache[desc["key"]] = fn(*args)  # maps the peer's pool (cudaIpcOpenMemHandle)
+        return cache[desc["key"]]
+
+    def send_kv(self, model_id: int, src_slots: np.ndarray, metadata: str) -> None:
+        """Prefill side of the hand-off: copy the KV rows at ``src_slots`` into the receiver's slots.
+        ``metadata`` = base64 JSON {"pool": <kv_export of the receiver>, "slots": [...]}."""
+        import base64  # pylint: disable=import-outside-toplevel
+
+        meta = json.loads(base64.b64decode(metadata))
+        pool_desc = json.loads(base64.b64decode(meta["pool"]))
+        dst_slots = np.asarray(meta["slots"], dtype=np.int32)
+        src_slots = np.ascontiguousarray(src_slots, dtype=np.int32)
+        if len(dst_slots) != len(src_slots):
+            raise RuntimeError(f"KV hand-off size mismatch: {len(src_slots)} rows to send, {len(dst_slots)} reserved")
+        src = self.models[model_id].kv_pages
+        dst = self._peer_pool(pool_desc)
+        if list(dst.shape[2:]) != list(src.shape[2:]) or dst.shape[0] != src.shape[0] or dst.dtype != src.dtype:
+            raise RuntimeError("the two engines do not hold the same model / KV layout")
+        page = src.shape[4]
+        if not src.is_cuda:
+            s, d = torch.from_numpy(src_slots).long(), torch.from_numpy(dst_slots).long()
+            dst[:, d // page, :, :, d % page, :] = src[:, s // page, :, :, s % page, :]
+            return
+        from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
+        import ctypes  # pylint: disable=import-outside-toplevel
+
+        ss = torch.from_numpy(src_slots).to(self.device)
+        ds = torch.from_numpy(dst_slots).to(self.device)
+        es = src.element_size()
+        rc = lib().mlcb_kv_slot_copy(
+            ptr(src), ctypes.c_void_p(dst.data_ptr()), ptr(ss), ptr(ds), ctypes.c_int(len(src_slots)),
+            ctypes.c_int(src.shape[0]), ctypes.c_longlong(src.stride(0) * es), ctypes.c_longlong(dst.stride(0) * es),
+            ctypes.c_int(src.shape[3]), ctypes.c_int(page), ctypes.c_int(src.shape[5] * es), stream_ptr())
+        check(rc, "mlcb_kv_slot_copy")
+        torch.cuda.synchronize(self.device)  # the receiver may start as soon as this call returns
 
     # ------------------------------------------------------------------ worker side (rank > 0)
     def worker_step(self, op: str, model_id: int, arrays: Dict[str, np.ndarray], layout) -> None:

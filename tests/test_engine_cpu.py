@@ -237,3 +237,49 @@ def test_json_ffi_engine_matches_python_engine():
         assert r.choices[0].message.content == text
     finally:
         py.terminate()
+
+
+def test_disaggregated_prefill_decode_hand_off():
+    """Two engines of one process act as prefill (P) and decode (D) endpoints: D reserves KV and
+    reports its prefix-cache hit, P prefills and copies the KV rows into D's pool, D prefills only the
+    last prompt token and decodes. The output must equal a plain run, and D must not recompute."""
+    from mlc_llm_b200.serve.entrypoints.microserving_entrypoints import prep_recv_response
+
+    cfg = dict(mode="server", max_num_sequence=4, max_total_sequence_length=1024, prefill_chunk_size=64)
+    plain = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    p_eng = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    d_eng = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    try:
+        prompt = _prompts(1, 70, 71, seed=41)[0]
+        want = plain.completions.create(prompt=prompt, max_tokens=10, temperature=0.0,
+                                        debug_config={"ignore_eos": True})
+
+        def run(prompt, rid):
+            prep = d_eng.completions.create(prompt=prompt, max_tokens=1, request_id=rid, debug_config={
+                "disagg_config": {"kind": "prepare_receive", "kv_window_begin": 0, "kv_window_end": -1}})
+            meta = prep_recv_response(d_eng, prep)
+            end = len(prompt) - 1
+            assert meta.prefix_matched_length <= end
+            if meta.prefix_matched_length < end:
+                p_eng.completions.create(prompt=prompt, max_tokens=1, request_id=rid, debug_config={
+                    "disagg_config": {"kind": "remote_send", "kv_window_begin": meta.prefix_matched_length,
+                                      "kv_window_end": end, "kv_append_metadata": meta.kv_append_metadata,
+                                      "dst_group_offset": 0}})
+            before = d_eng.metrics()["prefill_tokens_sum"]
+            out = d_eng.completions.create(prompt=prompt, max_tokens=10, temperature=0.0, request_id=rid,
+                                           debug_config={"ignore_eos": True, "disagg_config": {
+                                               "kind": "start_generation", "kv_window_begin": end}})
+            return out, meta.prefix_matched_length, d_eng.metrics()["prefill_tokens_sum"] - before
+
+        got, matched, d_prefilled = run(prompt, "disagg-1")
+        assert got.choices[0].text == want.choices[0].text and matched == 0
+        assert d_prefilled == 1 and got.usage.prompt_tokens == len(prompt)   # D computed only the last token
+        # a second request sharing 64 tokens hits D's prefix cache: P sends only the remainder
+        prompt2 = prompt[:64] + _prompts(1, 12, 13, seed=42)[0]
+        want2 = plain.completions.create(prompt=prompt2, max_tokens=10, temperature=0.0,
+                                         debug_config={"ignore_eos": True})
+        got2, matched2, _ = run(prompt2, "disagg-2")
+        assert got2.choices[0].text == want2.choices[0].text and matched2 >= 48
+    finally:
+        for e in (plain, p_eng, d_eng):
+            e.terminate()
