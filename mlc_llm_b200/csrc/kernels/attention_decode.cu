@@ -373,11 +373,10 @@ MLCB_API int mlcb_attn_decode(const void* q, const void* kv_pages, void* out, fl
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
        reinterpret_cast<uintptr_t>(kv_pages)) & 15)
     return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};
+  if (first_use_on_device(attr_set)) {
     cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
     cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
-    attr_set = true;
   }
   uint64_t dims[2] = {128, static_cast<uint64_t>(num_pages) * 2 * hkv * 16};
   uint64_t strides[1] = {256};

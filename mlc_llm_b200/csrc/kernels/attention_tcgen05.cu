@@ -397,10 +397,9 @@ MLCB_API int mlcb_attn_tc(const void* q, const void* kv_pages, void* out, float*
        reinterpret_cast<uintptr_t>(kv_pages)) & 15)
     return -3;
   if ((q_stride * 2) % 16) return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};
+  if (first_use_on_device(attr_set)) {
     cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    attr_set = true;
   }
   uint64_t dims[2] = {ATT_D, static_cast<uint64_t>(num_pages) * 2 * hkv * ATT_PAGE};
   uint64_t strides[1] = {ATT_D * 2};

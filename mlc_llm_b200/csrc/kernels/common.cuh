@@ -312,4 +312,14 @@ const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, co
                                   const uint64_t* strides_bytes, const uint32_t* box, int swizzle_128,
                                   int is_fp8 = 0);
 int sm_count();
+// True the first time it is called on each device with the same flag array (function attributes such as
+// the dynamic shared-memory limit are per device).
+inline bool first_use_on_device(bool (&flags)[64]) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (flags[dev]) return false;
+  flags[dev] = true;
+  return true;
+}
 }  // namespace mlcb

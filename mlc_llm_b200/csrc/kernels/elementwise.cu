@@ -234,6 +234,26 @@ __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __
 
 using namespace mlcb;
 
+// Lets kernels running on `device` dereference memory of `peer` (both in this process's view).
+// Returns 0 when access is (already) enabled.
+MLCB_API int mlcb_enable_peer_access(int device, int peer) {
+  if (device == peer) return 0;
+  int can = 0;
+  cudaError_t err = cudaDeviceCanAccessPeer(&can, device, peer);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (!can) return -1;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device);
+  err = cudaDeviceEnablePeerAccess(peer, 0);
+  cudaSetDevice(prev);
+  if (err == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return 0;
+  }
+  return static_cast<int>(err);
+}
+
 // Strides in bytes; row_bytes = head_dim * element size (multiple of 16).
 MLCB_API int mlcb_kv_slot_copy(const void* src, void* dst, const int* src_slots, const int* dst_slots, int n,
                                int layers, long long src_layer_stride, long long dst_layer_stride, int hkv,

@@ -905,14 +905,15 @@ const CUtensorMap* get_tensor_map(const void* base, int elem_bytes, int rank, co
 long long g_launch_count = 0;
 
 int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+  static int n[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (n[dev] == 0) {
+    cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (n[dev] <= 0) n[dev] = 148;
   }
-  return n;
+  return n[dev];
 }
 
 static int pick_tn(int M) {
@@ -964,12 +965,11 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
   if (wf == 2 && K % 64 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};
+  if (first_use_on_device(attr_set)) {
     cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     cudaFuncSetAttribute(gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    attr_set = true;
   }
   GemmParams p = {};
   p.scale = scale;
@@ -1128,11 +1128,11 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   if (K % 8 != 0 || ldx % 8 != 0 || N % BM != 0) return -1;
   if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};
+  if (first_use_on_device(attr_set)) {
     cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    attr_set = true;
+    cudaFuncSetAttribute(gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
   }
   GemmParams p = {};
   p.scale = scale;
@@ -1275,11 +1275,8 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
       if (err != cudaSuccess || !p)
         return noalloc_fail(static_cast<int>(err ? err : cudaErrorInvalidSymbol),
                             "mlcb_gemm_noalloc: cudaGetSymbolAddress failed (%lld)", err);
-      static bool attr_set_noalloc = false;
-      if (!attr_set_noalloc) {
-        cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-        attr_set_noalloc = true;
-      }
+      // once per device (this block runs once per device): the attribute is per device
+      cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
       g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
     }
     scratch = g_noalloc_ptr[dev];

@@ -219,6 +219,8 @@ class EngineRuntime:
     def __init__(self, engine_config: EngineConfig, device: Union[str, torch.device] = "auto",
                  comm=None, trace_recorder=None):
         self.device = detect_device(device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
         self.comm = comm
         self.trace = trace_recorder
         cfg = engine_config

@@ -105,6 +105,12 @@ class ModelExecutor:
         self.use_tensor_core_attention = device.type == "cuda"
 
     # ------------------------------------------------------------------ embeddings (multimodal)
+    def _enter(self) -> None:
+        """Kernels launch on the calling thread's current CUDA device; the engine drives this object
+        from its own threads, whose current device starts at 0."""
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+
     def hold_embedding(self, emb: torch.Tensor) -> int:
         h = self._next_embed
         self._next_embed += 1
@@ -233,6 +239,7 @@ class ModelExecutor:
     # ------------------------------------------------------------------ backend interface
     def forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
                        embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
+        self._enter()
         n_rows = len(sp["logit_token_index"])
         arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
@@ -280,6 +287,7 @@ class ModelExecutor:
         return out
 
     def forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
+        self._enter()
         sp = vp["sampling"]
         arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
@@ -351,6 +359,7 @@ class ModelExecutor:
                 "final_probs": tprobs.float().cpu().numpy()}
 
     def move_kv_tokens(self, model_id: int, moves: np.ndarray) -> None:
+        self._enter()
         if self.comm is not None:
             self.comm.broadcast_step("move", model_id, {"moves": np.ascontiguousarray(moves, dtype=np.int32)}, {})
         self.models[model_id].move_tokens(torch.from_numpy(np.ascontiguousarray(moves, dtype=np.int32)).to(self.device))
@@ -358,6 +367,7 @@ class ModelExecutor:
     # ------------------------------------------------------------------ disaggregated serving
     def apply_page_copies(self, model_id: int, copies: np.ndarray) -> None:
         """Copy-on-write page copies of a KV reservation that is not followed by a forward call."""
+        self._enter()
         if self.comm is not None and self.comm.world_size > 1:
             raise RuntimeError("disaggregated serving supports single-GPU endpoints only")
         pairs = torch.from_numpy(np.ascontiguousarray(copies, dtype=np.int32)).to(self.device)
@@ -401,6 +411,7 @@ class ModelExecutor:
     def send_kv(self, model_id: int, src_slots: np.ndarray, metadata: str) -> None:
         """Prefill side of the hand-off: copy the KV rows at ``src_slots`` into the receiver's slots.
         ``metadata`` = base64 JSON {"pool": <kv_export of the receiver>, "slots": [...]}."""
+        self._enter()
         import base64  # pylint: disable=import-outside-toplevel
 
         meta = json.loads(base64.b64decode(metadata))
@@ -421,6 +432,9 @@ class ModelExecutor:
         from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
         import ctypes  # pylint: disable=import-outside-toplevel
 
+        if dst.device != src.device:
+            rc = lib().mlcb_enable_peer_access(ctypes.c_int(src.device.index), ctypes.c_int(dst.device.index))
+            check(rc, f"peer access from GPU {src.device.index} to GPU {dst.device.index}")
         ss = torch.from_numpy(src_slots).to(self.device)
         ds = torch.from_numpy(dst_slots).to(self.device)
         es = src.element_size()
@@ -434,6 +448,7 @@ class ModelExecutor:
     # ------------------------------------------------------------------ worker side (rank > 0)
     def worker_step(self, op: str, model_id: int, arrays: Dict[str, np.ndarray], layout) -> None:
         """Mirror of the rank-0 calls on the other tensor-parallel ranks: same forward, no sampling."""
+        self._enter()
         if op == "move":
             self.models[model_id].move_tokens(torch.from_numpy(arrays["moves"]).to(self.device))
             return
