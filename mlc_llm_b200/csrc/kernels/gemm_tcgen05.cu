@@ -20,6 +20,7 @@
 // from quantization/group_quantization.py:390-440.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -83,20 +84,37 @@ struct GemmParams {
   // All-gather prologue: token rows of X become readable once their 8-row group flag reaches ag_epoch.
   const int* ag_wait;
   int ag_epoch;
+  // CTA pairs (cta_group::2): two CTAs of a cluster share each UMMA; see gemm_kernel<.., true>.
+  int pair;
 };
 
 // Where a tile lives: first weight row, first activation / output row, valid token rows, N block.
 struct TileInfo {
   int w_row, x_row, m_valid, nb;
+  int tile;        // linear (token block, feature block) index: split-K workspace / counter slot
+  int x_load_row;  // first activation row this CTA loads (second half of the token tile for the peer CTA)
+  bool dummy;      // pair mode, odd feature-block count: this CTA's half has no output
 };
-__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+__device__ __forceinline__ int work_id(const GemmParams& p) { return p.pair ? blockIdx.x >> 1 : blockIdx.x; }
+__device__ __forceinline__ int work_stride(const GemmParams& p) { return p.pair ? gridDim.x >> 1 : gridDim.x; }
+__device__ __forceinline__ int feature_blocks_per_item(const GemmParams& p) {
+  return p.pair ? (p.num_n_blocks + 1) >> 1 : p.num_n_blocks;
+}
+
+// `unit` counts (token block, feature block) tiles, or (token block, pair of feature blocks) in pair mode.
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int unit) {
   TileInfo ti;
-  ti.nb = tile % p.num_n_blocks;
-  const int mbg = tile / p.num_n_blocks;
+  const int per = feature_blocks_per_item(p);
+  const int mbg = unit / per;
+  ti.nb = unit - mbg * per;
+  if (p.pair) ti.nb = 2 * ti.nb + static_cast<int>(cluster_ctarank());
+  ti.dummy = ti.nb >= p.num_n_blocks;
+  ti.tile = mbg * p.num_n_blocks + ti.nb;
   if (!p.group_offsets) {
     ti.w_row = ti.nb * BM;
     ti.x_row = mbg * p.tn;
     ti.m_valid = min(p.tn, p.M - ti.x_row);
+    ti.x_load_row = ti.x_row + (p.pair ? static_cast<int>(cluster_ctarank()) * (p.tn >> 1) : 0);
     return ti;
   }
   int cum = 0, e = 0, begin = 0, cnt = 0;
@@ -112,6 +130,7 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   ti.w_row = slab * p.N + ti.nb * BM;
   ti.x_row = begin + mb * p.tn;
   ti.m_valid = min(p.tn, cnt - mb * p.tn);
+  ti.x_load_row = ti.x_row + (p.pair ? static_cast<int>(cluster_ctarank()) * (p.tn >> 1) : 0);
   return ti;
 }
 
@@ -290,7 +309,7 @@ struct KCursor {
   int t, kb, kb0, kb1, ka;
   TileInfo ti;
   __device__ __forceinline__ void init(const GemmParams& p, int total_kb, int num_items) {
-    t = blockIdx.x;
+    t = work_id(p);
     set(p, total_kb, num_items);
   }
   __device__ __forceinline__ void set(const GemmParams& p, int total_kb, int num_items) {
@@ -305,7 +324,7 @@ struct KCursor {
   __device__ __forceinline__ bool valid(int num_items) const { return t < num_items; }
   __device__ __forceinline__ void next(const GemmParams& p, int total_kb, int num_items) {
     if (++kb >= kb1) {
-      t += gridDim.x;
+      t += work_stride(p);
       set(p, total_kb, num_items);
     } else if (++ka >= kb1) {
       ka = kb0;
@@ -315,11 +334,18 @@ struct KCursor {
 
 // WF: weight format. 0 = dense 16-bit, 1 = int4 groups of 32 (q4f16_1), 2 = fp8 e4m3 with one fp32
 // scale per 128 x 128 block (weights expanded to the activation dtype on the way to the tensor core).
-template <int WF>
+// TWO: CTA pairs. Launched as clusters of two; the pair computes 256 output features x TN tokens per
+// UMMA (cta_group::2): each CTA loads its own 128-feature weight tile and HALF of the token tile, so a
+// stage is 32 KiB instead of 48 and the ring is six deep; the leader (cluster rank 0) waits for both
+// CTAs' tiles on its barriers, issues the MMAs, and its commits arrive on both CTAs' barriers.
+template <int WF, bool TWO>
 __global__ void __launch_bounds__(WF ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const GemmParams p) {
   constexpr bool Q4 = WF != 0;  // "has a dequant stage"
+  constexpr int NST = TWO ? 6 : STAGES;                                  // ring depth
+  constexpr int XSB = TWO ? X_STAGE_BYTES / 2 : X_STAGE_BYTES;           // activation bytes per stage
+  const uint32_t rank = TWO ? cluster_ctarank() : 0;                     // 0 = leader
   constexpr int RAW_BYTES = WF == 2 ? BM * BK : RAW_STAGE_BYTES;            // packed tile of one K block
   // Ring depth in the same space, kept even: the two dequant groups take alternate K blocks, so with an
   // even depth every slot belongs to one group, which then observes every phase of the slot's barriers
@@ -328,15 +354,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sx = smem;                                   // STAGES x 32 KiB
-  uint8_t* sw = sx + STAGES * X_STAGE_BYTES;            // STAGES x 16 KiB
-  uint8_t* sraw = sw + STAGES * W_STAGE_BYTES;          // RAW_STAGES x 4 KiB
+  uint8_t* sx = smem;                                   // NST x XSB (4 x 32 KiB or 6 x 16 KiB)
+  uint8_t* sw = sx + NST * XSB;                         // NST x 16 KiB
+  uint8_t* sraw = sw + NST * W_STAGE_BYTES;             // RAW_STAGES x 4 KiB
   uint8_t* sscale = sraw + RAW_STAGES * RAW_STAGE_BYTES;  // SCALE_DEPTH x 512 B
   uint64_t* bars = reinterpret_cast<uint64_t*>(sscale + SCALE_DEPTH * SCALE_STAGE_BYTES);
-  uint64_t* full = bars;                       // [STAGES] activation (and dense weight) tile landed
-  uint64_t* empty = full + STAGES;             // [STAGES] MMA done reading the stage
-  uint64_t* deq_full = empty + STAGES;         // [STAGES] expanded weight tile written
-  uint64_t* raw_full = deq_full + STAGES;      // [RAW_STAGES] packed weight tile landed
+  uint64_t* full = bars;                       // [NST] activation (and dense weight) tile landed
+  uint64_t* empty = full + NST;                // [NST] MMA done reading the stage
+  uint64_t* deq_full = empty + NST;            // [NST] expanded weight tile written
+  uint64_t* raw_full = deq_full + NST;         // [RAW_STAGES] packed weight tile landed
   uint64_t* raw_empty = raw_full + RAW_STAGES; // [RAW_STAGES] dequant warps done reading it
   uint64_t* acc_full = raw_empty + RAW_STAGES; // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
@@ -351,10 +377,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   __shared__ int sh_num_items;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    // pair mode: the leader's barriers also collect the peer CTA's arrivals
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&deq_full[s], 4);
+      mbar_init(&deq_full[s], TWO ? 8 : 4);
     }
     for (int s = 0; s < RAW_STAGES; ++s) {
       mbar_init(&raw_full[s], 1);
@@ -362,7 +389,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], TWO ? 8 : 4);
       mbar_init(&ep_bar[a], 4);
     }
     *abort_flag = 0;
@@ -372,18 +399,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int cnt = p.group_count ? p.group_count[e] : p.group_offsets[e + 1] - p.group_offsets[e];
         mbs += (cnt + p.tn - 1) / p.tn;
       }
-      sh_num_items = mbs * p.num_n_blocks;
+      sh_num_items = mbs * feature_blocks_per_item(p);
     } else {
-      sh_num_items = p.num_m_blocks * p.num_n_blocks * p.splits;
+      sh_num_items = p.num_m_blocks * feature_blocks_per_item(p) * p.splits;
     }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (TWO) {
+      tmem_alloc_pair(tmem_slot, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // both CTAs' barriers and TMEM exist before anyone signals the peer
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_tiles = sh_num_items;  // work items
@@ -395,19 +428,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tma_prefetch_desc(&tmap_x);
       if (!Q4) tma_prefetch_desc(&tmap_w);
     }
-    const uint32_t x_bytes = static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES);
+    // bytes credited to full[s]: in pair mode the leader's barrier counts both CTAs' tiles
+    const uint32_t x_bytes = TWO ? 2u * (static_cast<uint32_t>(p.tn >> 1) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES))
+                                 : static_cast<uint32_t>(p.tn) * BK * 2 + (Q4 ? 0 : W_STAGE_BYTES);
     KCursor cx;
     cx.init(p, total_kb, num_tiles);
     int gathered_row = -1;  // token tile whose rows are known to have arrived
     bool failed = false;    // no early exit: the lanes meet again at every token-tile change
     for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
-      const int s = ix % STAGES;
-      if (lane == 0 && ix >= STAGES && !failed)
-        failed = !mbar_wait(&empty[s], ((ix / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
+      const int s = ix % NST;
+      if (lane == 0 && ix >= NST && !failed)
+        failed = !mbar_wait(&empty[s], ((ix / NST) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
       if (p.ag_wait && cx.ti.x_row != gathered_row) {
         // rows of this token tile are pushed by their owners' kernels; one lane per 8-row group
-        const int g0 = cx.ti.x_row >> 3;
-        const int ng = (cx.ti.m_valid + 7) >> 3;
+        // (in pair mode each CTA waits for the half it loads)
+        const int g0 = cx.ti.x_load_row >> 3;
+        const int my_rows = TWO ? max(0, min(p.tn >> 1, cx.ti.x_row + cx.ti.m_valid - cx.ti.x_load_row))
+                                : cx.ti.m_valid;
+        const int ng = (my_rows + 7) >> 3;
         if (lane < ng && *abort_flag == 0)
           flag_wait_ge(p.ag_wait + g0 + lane, p.ag_epoch, abort_flag, p.status, ERR_WAIT_PEER);
         gathered_row = cx.ti.x_row;
@@ -417,9 +455,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       }
       if (lane == 0 && !failed) {
         GEMM_TRACE(0, ix);
-        mbar_expect_tx(&full[s], x_bytes);
-        tma_load_2d(sx + s * X_STAGE_BYTES, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_row);
-        if (!Q4) tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.ti.w_row);
+        if (TWO) {
+          if (rank == 0) mbar_expect_tx(&full[s], x_bytes);
+          tma_load_2d_pair(sx + s * XSB, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_load_row);
+          if (!Q4) tma_load_2d_pair(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.ti.w_row);
+        } else {
+          mbar_expect_tx(&full[s], x_bytes);
+          tma_load_2d(sx + s * XSB, &tmap_x, &full[s], cx.ka * BK, cx.ti.x_row);
+          if (!Q4) tma_load_2d(sw + s * W_STAGE_BYTES, &tmap_w, &full[s], cx.ka * BK, cx.ti.w_row);
+        }
       }
     }
   } else if (warp == 10) {
@@ -442,15 +486,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(p.ab_fmt, BM, p.tn, 0, 0);
+    // (pair mode: the leader CTA issues for both; the peer's warp only owns its half of the TMEM)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(p.ab_fmt, TWO ? 2 * BM : BM, p.tn, 0, 0);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+      auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
+        return TWO ? mbar_wait_cluster(bar, parity, abort_flag, p.status, code)
+                   : mbar_wait(bar, parity, abort_flag, p.status, code);
+      };
+      for (int t = work_id(p); t < num_tiles && ok; t += work_stride(p), ++tile_i) {
         const int a = tile_i & 1;
         const uint32_t aph = (tile_i >> 1) & 1;
         if (tile_i >= 2) {
-          ok = mbar_wait(&acc_empty[a], aph ^ 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+          ok = wait_bar(&acc_empty[a], aph ^ 1, ERR_WAIT_EPILOGUE);
           if (!ok) break;
         }
         tc_fence_after();
@@ -458,28 +507,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int kb0 = (t % p.splits) * p.kb_per_split;
         const int kb1 = min(total_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&full[s], ph, abort_flag, p.status, ERR_WAIT_TMA);
+          const int s = it % NST;
+          const uint32_t ph = (it / NST) & 1;
+          ok = wait_bar(&full[s], ph, ERR_WAIT_TMA);
           if (!ok) break;
           GEMM_TRACE(1, it);
           if (Q4) {
-            ok = mbar_wait(&deq_full[s], ph, abort_flag, p.status, ERR_WAIT_DEQUANT);
+            ok = wait_bar(&deq_full[s], ph, ERR_WAIT_DEQUANT);
             if (!ok) break;
           }
           GEMM_TRACE(2, it);
           tc_fence_after();
           const uint64_t adesc = umma_smem_desc(smem_u32(sw + s * W_STAGE_BYTES), 16, 1024);
-          const uint64_t bdesc = umma_smem_desc(smem_u32(sx + s * X_STAGE_BYTES), 16, 1024);
+          const uint64_t bdesc = umma_smem_desc(smem_u32(sx + s * XSB), 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             // advancing 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
-            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
+            if (TWO) umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
+            else umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
           }
-          umma_commit(&empty[s]);
+          if (TWO) umma_commit_pair(&empty[s]);
+          else umma_commit(&empty[s]);
           GEMM_TRACE(3, it);
         }
-        if (ok) umma_commit(&acc_full[a]);
+        if (ok) {
+          if (TWO) umma_commit_pair(&acc_full[a]);
+          else umma_commit(&acc_full[a]);
+        }
       }
     }
   } else if (warp < 6 || warp >= 11) {
@@ -526,7 +580,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         advance2(cp);
       }
       for (uint32_t it = grp; cs.valid(num_tiles) && ok; it += 2) {
-        const int s = it % STAGES;
+        const int s = it % NST;
         const int rs = it % RAW_N;
         const uint32_t slot = it % SCALE_DEPTH;
         asm volatile("cp.async.wait_group %0;" ::"n"(SCALE_DEPTH / 2 - 1) : "memory");
@@ -553,8 +607,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
         // the expanded tile may only be overwritten once the MMA that read it has finished
-        if (it >= STAGES) {
-          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
+        if (it >= NST) {
+          ok = mbar_wait(&empty[s], ((it / NST) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
@@ -604,7 +658,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&deq_full[s]);
+        if (lane == 0) {
+          // pair mode: the leader's barrier counts the dequant warps of both CTAs
+          if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&deq_full[s]), 0));
+          else mbar_arrive(&deq_full[s]);
+        }
         if (threadIdx.x == 64) GEMM_TRACE(5, it);
         fetch_scale(cp, slot);  // refill the slot consumed above
         advance2(cp);
@@ -615,9 +673,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
-      const int tile = t / p.splits, sp = t % p.splits;
-      const TileInfo ti = decode_tile(p, tile);
+    // the accumulator buffer goes back to the MMA issuer: the leader's barrier in pair mode
+    auto release_acc = [&](int a) {
+      if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[a]), 0));
+      else mbar_arrive(&acc_empty[a]);
+    };
+    for (int t = work_id(p); t < num_tiles && ok; t += work_stride(p), ++tile_i) {
+      const int sp = t % p.splits;
+      const TileInfo ti = decode_tile(p, t / p.splits);
+      const int tile = ti.tile;
       const int nb = ti.nb;
       const int a = tile_i & 1;
       const uint32_t aph = (tile_i >> 1) & 1;
@@ -626,6 +690,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       if (!ok) break;
       if (threadIdx.x == 192) GEMM_TRACE(6, tile_i);
       tc_fence_after();
+      if (ti.dummy) {  // odd feature-block count: this half of the pair tile has no output
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) release_acc(a);
+        continue;
+      }
       const int row = q * 32 + lane;     // row inside the tile
       const int n = nb * BM + row;       // output feature of this thread
       const bool n_ok = n < p.N;
@@ -649,7 +719,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[a]);
+        if (lane == 0) release_acc(a);
         // Every split reduces its own share of the tile's tokens once all partial sums are parked,
         // so the reduction runs on `splits` SMs at once. The counter's low half counts arrivals,
         // its high half counts finished reducers; the last reducer zeroes it for the next launch.
@@ -799,16 +869,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       if (p.rs_world && jlim > 0) rs_signal_chunks(p, m0 >> 5, (jlim + 31) >> 5, p.num_n_blocks * 4, lane);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[a]);
+      if (lane == 0) release_acc(a);
       if (threadIdx.x == 192) GEMM_TRACE(7, tile_i);
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // the peer's shared memory and TMEM stay valid until both are done
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (TWO) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0) GEMM_TRACE(7, 511);
 
@@ -950,6 +1022,17 @@ struct MlcbFusedArgs {
   int ag_epoch, reserved;
 };
 
+// CTA-pair kernels are opt-in through MLCB_GEMM_PAIR=1 (read once) or mlcb_gemm_set_pair_mode.
+static int g_pair_mode = -1;
+static bool pair_mode_enabled() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("MLCB_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pair_mode == 1;
+}
+MLCB_API void mlcb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+
 static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
                        int* status, float* workspace, long long workspace_bytes, int* counters,
@@ -967,9 +1050,12 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set[64] = {};
   if (first_use_on_device(attr_set)) {
-    cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
   }
   GemmParams p = {};
   p.scale = scale;
@@ -982,6 +1068,11 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   p.ldy = ldy;
   p.tn = pick_tn(M);
   if (rs) p.tn = (p.tn + 31) & ~31;  // 32-token chunks must not straddle tiles
+  // CTA pairs: each CTA loads half of the token tile, so the tile must split into two halves of whole
+  // swizzle atoms; tiny batches stay on the single-CTA kernel.
+  const bool pair = pair_mode_enabled() && M > 32;
+  if (pair) p.tn = (p.tn + 31) & ~31;
+  p.pair = pair ? 1 : 0;
   p.num_m_blocks = (M + p.tn - 1) / p.tn;
   p.num_n_blocks = (N + BM - 1) / BM;
   p.out_dtype = out_dtype;
@@ -1008,8 +1099,11 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     const int tiles = p.num_m_blocks * p.num_n_blocks;
     const int total_kb = (K + BK - 1) / BK;
     int splits = 1;
-    if (workspace && counters && tiles * 2 <= sm_count() && tiles <= num_counters) {
-      splits = sm_count() / tiles;
+    // work items that exist without splitting, and the CTAs (or CTA pairs) that can take one each
+    const int units = pair ? p.num_m_blocks * ((p.num_n_blocks + 1) / 2) : tiles;
+    const int workers = pair ? sm_count() / 2 : sm_count();
+    if (workspace && counters && units * 2 <= workers && tiles <= num_counters) {
+      splits = workers / units;
       if (splits > 8) splits = 8;
       if (splits > total_kb / 4) splits = total_kb / 4;
       if (splits < 1) splits = 1;
@@ -1027,7 +1121,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
 
   uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
   uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
-  uint32_t xb[2] = {BK, static_cast<uint32_t>(p.tn)};
+  uint32_t xb[2] = {BK, static_cast<uint32_t>(pair ? p.tn / 2 : p.tn)};
   const CUtensorMap* mx = get_tensor_map(x, 2, 2, xd, xs, xb, 1);
   const CUtensorMap* mw;
   if (q4) {
@@ -1047,14 +1141,36 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     mw = get_tensor_map(w, 2, 2, wd, ws, wb, 1);
   }
   if (!mx || !mw) return -4;
+  if (pair) {
+    const int items = p.num_m_blocks * ((p.num_n_blocks + 1) / 2) * p.splits;
+    const int pairs = items < sm_count() / 2 ? items : sm_count() / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err;
+    if (q4) err = cudaLaunchKernelEx(&cfg, gemm_kernel<1, true>, *mx, *mw, p);
+    else if (wf == 2) err = cudaLaunchKernelEx(&cfg, gemm_kernel<2, true>, *mx, *mw, p);
+    else err = cudaLaunchKernelEx(&cfg, gemm_kernel<0, true>, *mx, *mw, p);
+    count_launch();
+    return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
+  }
   int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (q4)
-    gemm_kernel<1><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else if (wf == 2)
-    gemm_kernel<2><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<2, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
-    gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<0, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -1130,9 +1246,9 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set[64] = {};
   if (first_use_on_device(attr_set)) {
-    cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    cudaFuncSetAttribute(gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
   }
   GemmParams p = {};
   p.scale = scale;
@@ -1181,9 +1297,9 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   const long long max_tiles = (static_cast<long long>(rows_hint) / p.tn + num_groups) * p.num_n_blocks;
   const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
   if (q4)
-    gemm_kernel<1><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
-    gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
+    gemm_kernel<0, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
@@ -1276,7 +1392,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
         return noalloc_fail(static_cast<int>(err ? err : cudaErrorInvalidSymbol),
                             "mlcb_gemm_noalloc: cudaGetSymbolAddress failed (%lld)", err);
       // once per device (this block runs once per device): the attribute is per device
-      cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+      cudaFuncSetAttribute(gemm_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
       g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
     }
     scratch = g_noalloc_ptr[dev];
@@ -1332,7 +1448,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
     return noalloc_fail(MLCB_NOALLOC_NO_DRIVER_ENTRY, "mlcb_gemm_noalloc: could not encode the TMA tensor maps");
   const int items = static_cast<int>(tiles) * p.splits;
   const int grid = items < sm_count() ? items : sm_count();
-  gemm_kernel<0><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(mx, mw, p);
+  gemm_kernel<0, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(mx, mw, p);
   count_launch();
   err = cudaGetLastError();
   if (err != cudaSuccess) return noalloc_fail(static_cast<int>(err), "mlcb_gemm_noalloc: launch failed (%lld)", err);

@@ -419,3 +419,36 @@ def test_fp8_block_scale_linear(dtype, m, n, k):
     want = x.float() @ Q.fp8_block_dequantize(qw, sc, (128, 128)).float().t()
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
     _close(y, want, tol, tol * want.abs().max().item())
+
+
+@pytest.fixture
+def pair_mode():
+    """CTA-pair (cta_group::2) form of the GEMM kernel for the duration of a test."""
+    from mlc_llm_b200.ops._lib import lib
+    lib().mlcb_gemm_set_pair_mode(1)
+    yield
+    lib().mlcb_gemm_set_pair_mode(0)
+
+
+@pytest.mark.parametrize("quant_name", ["q0f16", "q0bf16", "q4f16_1"])
+@pytest.mark.parametrize("m,n,k", [(64, 256, 512), (256, 512, 4096), (256, 384, 1024), (300, 1152, 2048),
+                                   (2048, 1024, 1024), (1000, 640, 512)])
+def test_gemm_cta_pair_mode(pair_mode, quant_name, m, n, k):
+    torch.manual_seed(11)
+    quant = Q.get(quant_name)
+    dt = quant.torch_dtype
+    w = (torch.randn(n, k) * 0.05).to(dt)
+    x = (torch.randn(m, k) * 0.5).to(dt)
+    if quant.kind == "no-quant":
+        lw = ops.LinearWeight("dense", w, None, None, None, n, k).to(DEV)
+        wref = w.float()
+    else:
+        qw, qs = Q.group_quantize(w, quant)
+        lw = ops.LinearWeight("q4", qw, qs, None, quant, n, k).to(DEV)
+        wref = Q.group_dequantize(qw, qs, quant, k=k).float()
+    for _ in range(2):
+        y = ops.linear(x.to(DEV), lw)
+        ops.check_status(torch.device(DEV))
+        want = x.float() @ wref.t()
+        tol = 2e-2 if dt == torch.bfloat16 else 3e-3
+        _close(y, want, tol, tol * want.abs().max().item())
