@@ -1022,16 +1022,19 @@ struct MlcbFusedArgs {
   int ag_epoch, reserved;
 };
 
-// CTA-pair kernels are opt-in through MLCB_GEMM_PAIR=1 (read once) or mlcb_gemm_set_pair_mode.
-static int g_pair_mode = -1;
-static bool pair_mode_enabled() {
+// CTA-pair kernels: MLCB_GEMM_PAIR = "0" never, "1" every weight format, unset = dense 16-bit weights
+// only (measured: +5..18 % on dense shapes; with a dequant stage the leader has to wait for both CTAs'
+// expanded tiles every K block and the pair form is slower than two independent CTAs).
+static int g_pair_mode = -1;  // -1 unread, 0 off, 1 all formats, 2 dense only
+static bool pair_mode_enabled(int wf) {
   if (g_pair_mode < 0) {
     const char* e = getenv("MLCB_GEMM_PAIR");
-    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+    g_pair_mode = !e ? 2 : (e[0] == '1' ? 1 : 0);
   }
-  return g_pair_mode == 1;
+  return g_pair_mode == 1 || (g_pair_mode == 2 && wf == 0);
 }
-MLCB_API void mlcb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+// Test hook: 1 = every format, 0 = off, 2 = default policy.
+MLCB_API void mlcb_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 
 static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
@@ -1070,7 +1073,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   if (rs) p.tn = (p.tn + 31) & ~31;  // 32-token chunks must not straddle tiles
   // CTA pairs: each CTA loads half of the token tile, so the tile must split into two halves of whole
   // swizzle atoms; tiny batches stay on the single-CTA kernel.
-  const bool pair = pair_mode_enabled() && M > 32;
+  const bool pair = pair_mode_enabled(wf) && M > 32;
   if (pair) p.tn = (p.tn + 31) & ~31;
   p.pair = pair ? 1 : 0;
   p.num_m_blocks = (M + p.tn - 1) / p.tn;

@@ -427,7 +427,7 @@ def pair_mode():
     from mlc_llm_b200.ops._lib import lib
     lib().mlcb_gemm_set_pair_mode(1)
     yield
-    lib().mlcb_gemm_set_pair_mode(0)
+    lib().mlcb_gemm_set_pair_mode(2)
 
 
 @pytest.mark.parametrize("quant_name", ["q0f16", "q0bf16", "q4f16_1"])
