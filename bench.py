@@ -212,6 +212,8 @@ def main(argv=None) -> int:
 
         api = MLCEngine.from_runtime(eng.runtime)
 
+        lat = []  # per-request server-side latencies (engine metrics: ttft_s, decode_tokens_per_s)
+
         def run_pass_api():
             prompts = make_prompts()
             if comm is not None:
@@ -225,6 +227,7 @@ def main(argv=None) -> int:
                 comm.shutdown_workers()
                 comm.barrier()
                 comm.max_over_ranks(0.0)
+            lat.extend((r["usage"].get("extra") or {}) for r in res)
             return dt, sum(r["usage"]["completion_tokens"] for r in res)
 
         for _ in range(args.warmup):
@@ -232,6 +235,7 @@ def main(argv=None) -> int:
         h2d0, d2h0 = eng.runtime.executor.h2d_bytes, eng.runtime.executor.d2h_bytes
         st0 = api.debug_step_count()
         dts, etoks = [], 0
+        lat.clear()
         for _ in range(args.steps):
             dt, n = run_pass_api()
             dts.append(dt)
@@ -241,6 +245,12 @@ def main(argv=None) -> int:
                "h2d_bytes_per_step": (eng.runtime.executor.h2d_bytes - h2d0) / nsteps,
                "d2h_bytes_per_step": (eng.runtime.executor.d2h_bytes - d2h0) / nsteps,
                "engine_steps": nsteps}
+        ttft = sorted(x["ttft_s"] for x in lat if "ttft_s" in x)
+        tpot = sorted(1.0 / x["decode_tokens_per_s"] for x in lat if x.get("decode_tokens_per_s"))
+        if ttft:
+            e2e["p50_ttft_s"] = ttft[len(ttft) // 2]
+        if tpot:
+            e2e["p50_tpot_s"] = tpot[len(tpot) // 2]
         api.terminate()
 
     line = {

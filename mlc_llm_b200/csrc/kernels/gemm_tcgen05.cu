@@ -600,12 +600,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           const uint4 r = raw[i];
           words[4 * i] = r.x; words[4 * i + 1] = r.y; words[4 * i + 2] = r.z; words[4 * i + 3] = r.w;
         }
-        // The packed values are in registers: recycle the slot early. Its next writer is the TMA
-        // engine (async proxy) while these reads went through the generic proxy, so a proxy fence
-        // must order them before the release (without it the refill was seen overtaking the reads).
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        // The packed slot is released further down, behind the proxy fence that also publishes the
+        // expanded tile: its next writer is the TMA engine (async proxy) while these reads went through
+        // the generic proxy, and without a fence in between the refill was seen overtaking the reads.
         // the expanded tile may only be overwritten once the MMA that read it has finished
         if (it >= NST) {
           ok = mbar_wait(&empty[s], ((it / NST) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
@@ -658,6 +655,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         fence_proxy_async_smem();
         __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
         if (lane == 0) {
           // pair mode: the leader's barrier counts the dequant warps of both CTAs
           if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&deq_full[s]), 0));
