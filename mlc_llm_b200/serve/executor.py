@@ -12,6 +12,7 @@ verify wrappers), ``cpp/serve/logit_processor.cc:40-458`` and ``cpp/serve/sample
 
 from __future__ import annotations
 
+import ctypes
 import json
 import os
 
@@ -50,6 +51,7 @@ class StagingBuffer:
 
     def _grow(self, n: int) -> None:
         cap = max(n, self.capacity * 2, 1 << 12)
+        self.generation = getattr(self, "generation", 0) + 1  # device addresses change: drop CUDA graphs
         pin = self.device.type == "cuda"
         self.host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
         self.host_np = self.host.numpy()
@@ -62,7 +64,13 @@ class StagingBuffer:
             self._grow(total)
         off = 0
         layout = []
-        for name, a in arrays.items():
+        # Fixed-size forward arrays first, the page list (the one array that grows from step to step
+        # at a constant batch) next, sampling arrays last: the device address of every array a
+        # captured forward reads then depends on the batch shape only.
+        order = [k for k in arrays if not k.startswith("s_") and k != "page_indices"]
+        order += [k for k in arrays if k == "page_indices"] + [k for k in arrays if k.startswith("s_")]
+        for name in order:
+            a = arrays[name]
             words = a.size * (2 if a.dtype.itemsize == 8 else 1)
             if words:
                 self.host_np[off:off + words] = a.reshape(-1).view(np.int32)
@@ -103,6 +111,12 @@ class ModelExecutor:
         self.d2h_bytes = 0
         self.kernel_launch_estimate = 0
         self.use_tensor_core_attention = device.type == "cuda"
+        # CUDA graphs of decode-shaped forwards, keyed by the batch shape (MLCB_CUDA_GRAPH=0 disables)
+        self.use_graphs = device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
+        self._graphs: Dict[tuple, dict] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
+        self.graph_launches = 0
 
     # ------------------------------------------------------------------ embeddings (multimodal)
     def _enter(self) -> None:
@@ -179,6 +193,60 @@ class ModelExecutor:
         model = self.models[model_id]
         if dev["page_copies"].numel():
             model.copy_pages(dev["page_copies"])
+        if self._graph_ok(model_id, dev, embed_handles):
+            return self._run_graph(model_id, plan, dev)
+        return self._run_eager(model_id, plan, dev, embed_handles)
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _graph_ok(self, model_id: int, dev: Dict[str, torch.Tensor], embed_handles) -> bool:
+        """Pure decode-shaped steps (every sequence appends a few tokens through the decode attention
+        kernel, no tree, no window, no copy-on-write) of a single-stage model on the NCCL or
+        single-GPU path: everything the forward launches then depends on the batch shape only."""
+        model = self.models[model_id]
+        return (self.use_graphs and embed_handles is None and not self._pipeline(model_id)
+                and getattr(model, "fused", None) is None and getattr(model, "ep", None) is None
+                and "dec_seq" in dev and dev["dec_seq"].numel() > 0 and dev["tile_seq"].numel() == 0
+                and dev["page_copies"].numel() == 0 and dev["tree_mask"].numel() == 0
+                and dev["q_kvstart"].numel() == 0 and self._tc_attention_ok(model))
+
+    def _run_graph(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor]) -> torch.Tensor:
+        from ..ops.attention import choose_splits  # pylint: disable=import-outside-toplevel
+
+        model = self.models[model_id]
+        max_pages = (int(plan["max_seq_len"]) + 15) // 16
+        splits = choose_splits(int(dev["dec_seq"].numel()), model.hkv, max_pages, self.device)
+        shape = tuple((k, int(v.numel())) for k, v in dev.items() if not k.startswith("s_") and k != "page_indices")
+        key = (model_id, self.staging.generation, splits, shape)
+        entry = self._graphs.get(key)
+        if entry is None:
+            # first sight of a shape: run it eagerly (lazy one-time set-up must not happen under capture;
+            # every rank takes the same decision from the same broadcast arrays)
+            if len(self._graphs) >= 32:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = {"graph": None}
+            return self._run_eager(model_id, plan, dev, None)
+        if entry["graph"] is None:
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            from ..ops._lib import lib  # pylint: disable=import-outside-toplevel
+
+            lib().mlcb_launch_count.restype = ctypes.c_longlong
+            before = lib().mlcb_launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                hidden = self._run_eager(model_id, plan, dev, None)
+                normed = getattr(model, "_final_normed", None)
+            entry.update(graph=graph, hidden=hidden, normed=normed, launches=int(lib().mlcb_launch_count() - before))
+        entry["graph"].replay()
+        self.graph_replays += 1
+        self.graph_launches += entry["launches"]  # kernels a replay launches (the C counter sees captures only)
+        model._final_normed = entry["normed"]  # pylint: disable=protected-access
+        return entry["hidden"]
+
+    def _run_eager(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor],
+                   embed_handles: Optional[np.ndarray]) -> torch.Tensor:
+        model = self.models[model_id]
         b = self._batch_info(dev, plan, model)
         staged = self._pipeline(model_id)
         if staged and not model.first_stage:
