@@ -112,7 +112,10 @@ class ModelExecutor:
         self.kernel_launch_estimate = 0
         self.use_tensor_core_attention = device.type == "cuda"
         # CUDA graphs of decode-shaped forwards, keyed by the batch shape (MLCB_CUDA_GRAPH=0 disables)
-        self.use_graphs = device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
+        # Single-process engines only: a forward with NCCL collectives inside did not complete under
+        # capture in a two-rank run, so multi-rank engines stay on eager launches.
+        self.use_graphs = (device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
+                           and (comm is None or comm.world_size == 1))
         self._graphs: Dict[tuple, dict] = {}
         self._graph_pool = None
         self.graph_replays = 0
