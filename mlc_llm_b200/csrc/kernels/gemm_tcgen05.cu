@@ -71,6 +71,10 @@ struct GemmParams {
   int rs_world, rs_rank;
   int rs_rows;                       // rows owned by each rank (multiple of 32)
   int rs_epoch;                      // call number; flags carry it, so nothing is reset
+  // When set, the call number is `*epoch_base + rs_epoch` (and `*epoch_base + ag_epoch`): the base
+  // lives in device memory and advances once per forward, so a captured CUDA graph of a forward can
+  // be replayed with fresh call numbers.
+  const int* epoch_base;
   // peer address tables live in device memory (dynamic indexing of kernel parameters would force
   // a local copy of the whole parameter block)
   const unsigned long long* rs_recv; // [world] per rank: receive buffer [world][rs_rows][N], output dtype
@@ -95,6 +99,12 @@ struct TileInfo {
   int x_load_row;  // first activation row this CTA loads (second half of the token tile for the peer CTA)
   bool dummy;      // pair mode, odd feature-block count: this CTA's half has no output
 };
+__device__ __forceinline__ int rs_epoch_of(const GemmParams& p) {
+  return p.rs_epoch + (p.epoch_base ? __ldg(p.epoch_base) : 0);
+}
+__device__ __forceinline__ int ag_epoch_of(const GemmParams& p) {
+  return p.ag_epoch + (p.epoch_base ? __ldg(p.epoch_base) : 0);
+}
 __device__ __forceinline__ int work_id(const GemmParams& p) { return p.pair ? blockIdx.x >> 1 : blockIdx.x; }
 __device__ __forceinline__ int work_stride(const GemmParams& p) { return p.pair ? gridDim.x >> 1 : gridDim.x; }
 __device__ __forceinline__ int feature_blocks_per_item(const GemmParams& p) {
@@ -183,7 +193,7 @@ __device__ __forceinline__ void rs_signal_chunks(const GemmParams& p, int first_
       const int owner = t / p.rs_rows;
       const int local_chunk = (t - owner * p.rs_rows) >> 5;
       flag_store_release_sys(reinterpret_cast<int*>(p.rs_flag[owner]) + local_chunk * p.rs_world + p.rs_rank,
-                             p.rs_epoch);
+                             rs_epoch_of(p));
     }
   }
   __syncwarp();
@@ -200,6 +210,7 @@ __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int 
   const char* my_recv = reinterpret_cast<const char*>(p.rs_recv[p.rs_rank]);
   T* residual = reinterpret_cast<T*>(p.rs_residual);
   const T* nw = reinterpret_cast<const T*>(p.rs_norm_w);
+  const int epoch = rs_epoch_of(p);
   for (int g = blockIdx.x; g < ngroups; g += gridDim.x) {
     if (warp < 8) {
       const int row = g * 8 + warp;
@@ -208,7 +219,7 @@ __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int 
         const int chunk = row >> 5;
         bool got = true;
         if (lane < world)
-          got = flag_wait_ge(my_flags + chunk * world + lane, p.rs_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+          got = flag_wait_ge(my_flags + chunk * world + lane, epoch, abort_flag, p.status, ERR_WAIT_PEER);
         ok = __all_sync(0xffffffffu, got);
       }
       if (ok) {
@@ -293,7 +304,7 @@ __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int 
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (threadIdx.x < world && g * 8 < valid)
         flag_store_release_sys(reinterpret_cast<int*>(p.ag_flag[threadIdx.x]) + ((p.rs_rank * p.rs_rows) >> 3) + g,
-                               p.rs_epoch);
+                               epoch);
     }
   }
 }
@@ -447,7 +458,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                                 : cx.ti.m_valid;
         const int ng = (my_rows + 7) >> 3;
         if (lane < ng && *abort_flag == 0)
-          flag_wait_ge(p.ag_wait + g0 + lane, p.ag_epoch, abort_flag, p.status, ERR_WAIT_PEER);
+          flag_wait_ge(p.ag_wait + g0 + lane, ag_epoch_of(p), abort_flag, p.status, ERR_WAIT_PEER);
         gathered_row = cx.ti.x_row;
         __syncwarp();
         fence_proxy_async_all();  // peer stores (generic proxy) -> TMA reads (async proxy)
@@ -1018,6 +1029,7 @@ struct MlcbFusedArgs {
   const unsigned long long* ag_flag;
   const void* ag_wait;
   int ag_epoch, reserved;
+  const int* epoch_base;  // optional device word added to rs_epoch / ag_epoch (CUDA-graph replays)
 };
 
 // CTA-pair kernels: MLCB_GEMM_PAIR = "0" never, "1" every weight format, unset = dense 16-bit weights
@@ -1094,6 +1106,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     p.rs_w_offset = f->rs_w_offset;
     p.ag_wait = static_cast<const int*>(f->ag_wait);
     p.ag_epoch = f->ag_epoch;
+    p.epoch_base = f->epoch_base;
   }
   // split-K when the output tiles alone cannot fill the GPU (decode-sized M with a narrow N)
   {
@@ -1218,13 +1231,24 @@ MLCB_API int mlcb_gemm_fused(const void* x, const void* w, const void* scale, co
 
 // Bounded wait until the gather flags of rows [0, rows) have reached `epoch` (for consumers of a
 // gather buffer that are not this library's GEMM, e.g. the row gather before the LM head).
-__global__ void flag_wait_kernel(const int* flags, int groups, int epoch, int* status) {
+__global__ void flag_wait_kernel(const int* flags, int groups, int epoch, const int* epoch_base, int* status) {
+  if (epoch_base) epoch += __ldg(epoch_base);
   for (int g = threadIdx.x; g < groups; g += blockDim.x)
     flag_wait_ge(flags + g, epoch, nullptr, status, ERR_WAIT_PEER);
 }
-MLCB_API int mlcb_flag_wait(const int* flags, int rows, int epoch, int* status, cudaStream_t stream) {
+MLCB_API int mlcb_flag_wait(const int* flags, int rows, int epoch, const int* epoch_base, int* status,
+                            cudaStream_t stream) {
   if (rows <= 0) return 0;
-  flag_wait_kernel<<<1, 256, 0, stream>>>(flags, (rows + 7) / 8, epoch, status);
+  flag_wait_kernel<<<1, 256, 0, stream>>>(flags, (rows + 7) / 8, epoch, epoch_base, status);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+// `*word += delta` in stream order: advances the device-resident call-number base of the fused
+// collectives at the end of a forward (captured into the forward's CUDA graph).
+__global__ void epoch_add_kernel(int* word, int delta) { *word += delta; }
+MLCB_API int mlcb_epoch_add(int* word, int delta, cudaStream_t stream) {
+  epoch_add_kernel<<<1, 1, 0, stream>>>(word, delta);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -255,6 +255,7 @@ class DecoderModel:
             f.gemm_rs_norm(a, self.p.linears[pre + "mlp.down_proj"], self.p.tensors[nxt + ".weight"],
                            c.rms_norm_eps, c.norm_weight_offset)
         out = f.wait_gather()
+        f.end()
         self._final_normed = out
         return out
 

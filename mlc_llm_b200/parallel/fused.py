@@ -1,7 +1,10 @@
 """Fused tensor-parallel collectives: the host side of ``mlcb_gemm_fused``.
 
 One object per tensor-parallel group owns the symmetric peer buffers and the call counter (epoch)
-that the kernels' flags carry:
+that the kernels' flags carry.  The counter is kept in device memory as a per-forward base plus the
+call's index inside the forward (a launch argument): a forward that was captured into a CUDA graph
+replays with fresh call numbers because only the base changes (``mlcb_epoch_add`` at the end of the
+forward is part of the graph).  Ranks stay in step because all of them run the same forwards.
 
 * ``gemm_rs_norm``  row-parallel GEMM (``o_proj`` / ``down_proj``) whose epilogue pushes partial sums
   to the rows' owners and whose tail does reduce + residual add + RMSNorm + all-gather of the
@@ -40,6 +43,7 @@ class FusedArgs(ctypes.Structure):
         ("rs_eps", ctypes.c_float), ("rs_w_offset", ctypes.c_float),
         ("ag_xn", ctypes.c_void_p), ("ag_flag", ctypes.c_void_p),
         ("ag_wait", ctypes.c_void_p), ("ag_epoch", ctypes.c_int), ("reserved", ctypes.c_int),
+        ("epoch_base", ctypes.c_void_p),
     ]
 
 
@@ -83,7 +87,9 @@ class FusedCollectives:
         self.table = table.to(device)
         self.rs_count = torch.zeros(world * self.rows_cap // 32 + 8, dtype=torch.int32, device=device)
         self.residual = torch.zeros(self.rows_cap, hidden, dtype=dtype, device=device)
-        self.epoch = 0
+        self.epoch_dev = torch.zeros(4, dtype=torch.int32, device=device)  # [0]: base of the call numbers
+        self.base = 0        # host mirror of epoch_dev[0] once every queued forward has run
+        self.call = 0        # reduce-scatter calls since begin()
         self.rows = self.rows_cap
         self.tokens = 0
         self.launches = 0
@@ -91,11 +97,30 @@ class FusedCollectives:
     # ------------------------------------------------------------------ per-forward state
     def begin(self, tokens: int) -> None:
         """Fix the row partition of this forward call (every rank passes the same token count)."""
+        self.end()
         if tokens > self.rows_cap * self.world:
             raise ValueError(f"{tokens} tokens exceed the fused-collective buffers "
                              f"({self.rows_cap * self.world}); raise prefill_chunk_size-based capacity")
         self.tokens = tokens
         self.rows = _round_up(-(-tokens // self.world), 32)
+
+    def end(self) -> None:
+        """Close a forward: the device-side base moves past the call numbers it used."""
+        if self.call:
+            rc = lib().mlcb_epoch_add(ptr(self.epoch_dev), ctypes.c_int(self.call), stream_ptr())
+            check(rc, "mlcb_epoch_add")
+            self.base += self.call
+            self.call = 0
+            self.launches += 1
+
+    def note_replay(self, calls: int) -> None:
+        """A captured forward with ``calls`` reduce-scatter launches was replayed."""
+        self.base += calls
+
+    @property
+    def epoch(self) -> int:
+        """Number of the latest reduce-scatter call."""
+        return self.base + self.call
 
     def owned(self) -> range:
         lo = min(self.tokens, self.rank * self.rows)
@@ -138,9 +163,12 @@ class FusedCollectives:
         assert x.shape[0] == self.tokens and x.is_contiguous()
         n = lw.out_features or lw.w.shape[0]
         assert n == self.hidden
-        self.epoch += 1
+        self.call += 1
         a = FusedArgs()
-        a.rs_world, a.rs_rank, a.rs_rows, a.rs_epoch = self.world, self.rank, self.rows, self.epoch
+        a.rs_world, a.rs_rank, a.rs_rows, a.rs_epoch = self.world, self.rank, self.rows, self.call
+        a.epoch_base = self.epoch_dev.data_ptr()
+        # the receive buffer alternates with the call number; a captured forward keeps the parity it
+        # was captured with, which holds as long as every forward makes an even number of these calls
         a.rs_recv = self.table[self.epoch & 1].data_ptr()
         a.rs_flag = self.table[2].data_ptr()
         a.rs_count = self.rs_count.data_ptr()
@@ -161,13 +189,15 @@ class FusedCollectives:
         od = out_dtype or x.dtype
         y = torch.empty(self.tokens, n, dtype=od, device=self.device)
         a = FusedArgs()
-        a.ag_wait, a.ag_epoch = self._ag_flags_ptr(), self.epoch
+        a.ag_wait, a.ag_epoch = self._ag_flags_ptr(), self.call
+        a.epoch_base = self.epoch_dev.data_ptr()
         self._launch(x, lw, y, n, od, a, bias=lw.bias is not None)
         return y
 
     def wait_gather(self) -> torch.Tensor:
         """Make the gather buffer safe to read for any later kernel on this stream."""
         rc = lib().mlcb_flag_wait(ctypes.c_void_p(self._ag_flags_ptr()), ctypes.c_int(self.tokens),
-                                  ctypes.c_int(self.epoch), ptr(status_word(self.device)), stream_ptr())
+                                  ctypes.c_int(self.call), ptr(self.epoch_dev), ptr(status_word(self.device)),
+                                  stream_ptr())
         check(rc, "mlcb_flag_wait")
         return self.xn()

@@ -323,7 +323,8 @@ class EngineRuntime:
         # above the NCCL path (2 ranks); with more ranks NCCL's in-switch reduction currently wins.
         fused_mode = os.environ.get("MLCB_FUSED_TP", "auto")
         use_fused = fused_mode == "1" or (fused_mode == "auto" and tp == 2)
-        if tp > 1 and self.device.type == "cuda" and use_fused:
+        # "1" on a single GPU runs the same kernels with one rank (peer tables point at local memory)
+        if (tp > 1 or fused_mode == "1") and self.device.type == "cuda" and use_fused:
             # fused GEMM+collective kernels over symmetric peer buffers (main model only)
             from ..parallel.fused import FusedCollectives  # pylint: disable=import-outside-toplevel
 
@@ -332,7 +333,7 @@ class EngineRuntime:
                 max_tokens = max(int(full.get("prefill_chunk_size") or 2048),
                                  int(full["max_num_sequence"]) * ((full.get("spec_draft_length") or 0) + 1))
                 fused = FusedCollectives(main_model.cfg.hidden_size, main_model.dtype, max_tokens, self.device,
-                                         group=comm.tp_group, world_size=tp)
+                                         group=comm.tp_group if tp > 1 else None, world_size=tp)
                 self.fused_tp = main_model.enable_fused(fused)
         for m in self.models:
             if m.cfg.expert_parallel and m.cfg.num_experts > 0 and tp > 1 and self.device.type == "cuda":

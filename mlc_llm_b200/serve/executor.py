@@ -112,10 +112,11 @@ class ModelExecutor:
         self.kernel_launch_estimate = 0
         self.use_tensor_core_attention = device.type == "cuda"
         # CUDA graphs of decode-shaped forwards, keyed by the batch shape (MLCB_CUDA_GRAPH=0 disables)
-        # Single-process engines only: a forward with NCCL collectives inside did not complete under
-        # capture in a two-rank run, so multi-rank engines stay on eager launches.
+        # Default for single-process engines only: a forward with NCCL collectives inside did not
+        # complete under capture in a two-rank run.  MLCB_CUDA_GRAPH=1 (explicit) also captures the
+        # fused tensor-parallel forward of multi-rank engines, which holds no NCCL call.
         self.use_graphs = (device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
-                           and (comm is None or comm.world_size == 1))
+                           and (comm is None or comm.world_size == 1 or os.environ.get("MLCB_CUDA_GRAPH") == "1"))
         self._graphs: Dict[tuple, dict] = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -203,11 +204,16 @@ class ModelExecutor:
     # ------------------------------------------------------------------ CUDA graphs
     def _graph_ok(self, model_id: int, dev: Dict[str, torch.Tensor], embed_handles) -> bool:
         """Pure decode-shaped steps (every sequence appends a few tokens through the decode attention
-        kernel, no tree, no window, no copy-on-write) of a single-stage model on the NCCL or
-        single-GPU path: everything the forward launches then depends on the batch shape only."""
+        kernel, no tree, no window, no copy-on-write) of a single-stage model: everything the forward
+        launches then depends on the batch shape only.  Across ranks only the fused tensor-parallel
+        forward is captured: its collectives are this library's kernels over peer memory (call numbers
+        come from device memory), so the graph holds no NCCL call."""
         model = self.models[model_id]
+        multi = self.comm is not None and self.comm.world_size > 1
+        if multi and getattr(model, "fused", None) is None:
+            return False
         return (self.use_graphs and embed_handles is None and not self._pipeline(model_id)
-                and getattr(model, "fused", None) is None and getattr(model, "ep", None) is None
+                and getattr(model, "ep", None) is None
                 and "dec_seq" in dev and dev["dec_seq"].numel() > 0 and dev["tile_seq"].numel() == 0
                 and dev["page_copies"].numel() == 0 and dev["tree_mask"].numel() == 0
                 and dev["q_kvstart"].numel() == 0 and self._tc_attention_ok(model))
@@ -237,11 +243,24 @@ class ModelExecutor:
 
             lib().mlcb_launch_count.restype = ctypes.c_longlong
             before = lib().mlcb_launch_count()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            fused = getattr(model, "fused", None)
+            base = fused.base if fused is not None else 0
+            multi = self.comm is not None and self.comm.world_size > 1
+            with torch.cuda.graph(graph, pool=self._graph_pool,
+                                  capture_error_mode="thread_local" if multi else "global"):
                 hidden = self._run_eager(model_id, plan, dev, None)
                 normed = getattr(model, "_final_normed", None)
-            entry.update(graph=graph, hidden=hidden, normed=normed, launches=int(lib().mlcb_launch_count() - before))
+            calls = 0
+            if fused is not None:
+                # nothing ran during capture: the call-number base moves when the graph is replayed
+                calls, fused.base = fused.base - base, base
+                if calls % 2:
+                    raise RuntimeError("a captured fused forward must make an even number of reduce-scatter calls")
+            entry.update(graph=graph, hidden=hidden, normed=normed, fused_calls=calls,
+                         launches=int(lib().mlcb_launch_count() - before))
         entry["graph"].replay()
+        if entry.get("fused_calls"):
+            model.fused.note_replay(entry["fused_calls"])
         self.graph_replays += 1
         self.graph_launches += entry["launches"]  # kernels a replay launches (the C counter sees captures only)
         model._final_normed = entry["normed"]  # pylint: disable=protected-access
