@@ -189,6 +189,8 @@ def main(argv=None) -> int:
 
     for _ in range(args.warmup):
         run_pass_device()
+    host0 = dict(eng.runtime.executor.host_times)
+    wall0 = time.perf_counter()
     sampler = ClockSampler(local)
     sampler.start()
     times, toks, launches = [], 0, 0
@@ -198,6 +200,12 @@ def main(argv=None) -> int:
         toks += n
         launches += l
     clocks = sampler.stop()
+    # where rank 0's host time went per engine step (ms): executor phases, and the rest of the loop
+    # (native engine step, plan building, output handling) as "engine_other"
+    host1 = eng.runtime.executor.host_times
+    calls = max(1.0, host1["calls"] - host0["calls"])
+    host_ms = {k: round((host1[k] - host0[k]) * 1e3 / calls, 3) for k in host1 if k != "calls"}
+    host_ms["engine_other"] = round((time.perf_counter() - wall0) * 1e3 / calls - sum(host_ms.values()), 3)
     total_ms = sum(times)
     value = toks / (total_ms / 1e3)
     steps_per_pass = json.loads(eng.debug_stats())
@@ -266,6 +274,7 @@ def main(argv=None) -> int:
                    "kv_page": 16, "kv_dtype": "fp16", "sampling": "greedy, ignore_eos"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "engine_steps_per_pass": engine_steps // max(1, args.warmup + args.steps),
+        "host_ms_per_engine_step": host_ms,
     }
     print(json.dumps(line))
     if comm is not None:

@@ -19,6 +19,8 @@ from __future__ import annotations
 import datetime
 import os
 import pickle
+import sys
+import time
 from typing import Dict, List, Optional, Tuple
 
 import numpy as np
@@ -212,11 +214,22 @@ _ID_NAME = dict(enumerate(_ARRAY_NAMES))
 
 def worker_loop(executor, comm: Communicator) -> None:
     """Body of every rank other than 0: mirror rank 0's model calls until told to stop."""
+    report = os.environ.get("MLCB_STEP_TIMES") == "1"
+    recv_s = step_s = 0.0
+    steps = 0
     while True:
+        t0 = time.perf_counter()
         op, model_id, arrays = comm.receive_step()
+        t1 = time.perf_counter()
         if op == "shutdown":
+            if report and steps:
+                print(f"[rank {comm.rank}] {steps} steps: receive {recv_s * 1e3 / steps:.3f} ms/step, "
+                      f"launch {step_s * 1e3 / steps:.3f} ms/step", file=sys.stderr, flush=True)
             return
         if op == "reset":
             executor.reset()
             continue
         executor.worker_step(op, model_id, arrays, None)
+        recv_s += t1 - t0
+        step_s += time.perf_counter() - t1
+        steps += 1

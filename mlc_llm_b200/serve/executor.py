@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import json
 import os
+import time
 
 from typing import Dict, List, Optional
 
@@ -120,6 +121,9 @@ class ModelExecutor:
         self._graphs: Dict[tuple, dict] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        # wall-clock seconds the host spent per phase of forward_sample (profiling aid)
+        self.host_times: Dict[str, float] = {"pack": 0.0, "broadcast": 0.0, "upload": 0.0, "forward": 0.0,
+                                             "logits_sample": 0.0, "readback": 0.0, "calls": 0.0}
         self.graph_launches = 0
 
     # ------------------------------------------------------------------ embeddings (multimodal)
@@ -330,22 +334,36 @@ class ModelExecutor:
     def forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
                        embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
         self._enter()
+        ht, clock = self.host_times, time.perf_counter
+        t0 = clock()
         n_rows = len(sp["logit_token_index"])
         arrays = self._pack(plan, token_ids, sp, model_id)
+        t1 = clock()
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,
                                      {k: v for k, v in arrays.items()
                                       if not k.startswith("s_") or k == "s_logit_token_index"}, {})
+        t2 = clock()
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
+        t3 = clock()
         hidden = self._run_model(model_id, plan, dev, embed_handles)
+        t4 = clock()
+        ht["pack"] += t1 - t0
+        ht["broadcast"] += t2 - t1
+        ht["upload"] += t3 - t2
+        ht["forward"] += t4 - t3
+        ht["calls"] += 1
         if n_rows == 0:
             return None
         model = self.models[model_id]
         logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
         if self._is_plain_greedy(sp):
             tokens = ops.argmax(logits)
+            t5 = clock()
             tok = tokens.cpu().numpy()
+            ht["logits_sample"] += t5 - t4
+            ht["readback"] += clock() - t5
             self.d2h_bytes += tok.nbytes
             return {"tokens": tok, "probs": np.ones(n_rows, dtype=np.float32)}
         self._process_logits(logits, dev, sp)

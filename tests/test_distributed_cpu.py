@@ -11,13 +11,13 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_env=None, want_flags=False):
+def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_env=None, want_flags=False, timeout=600):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker.py"),
            model, device]
     env = dict(os.environ, OMP_NUM_THREADS="2")
     env.update(extra_env or {})
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     if out.returncode != 0:
         # keep the children's full stderr where a GPU run can pick it up
         log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")

@@ -32,6 +32,21 @@ def test_tp2_fused_collectives_match_nccl_path(quant):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_fused_forward_replayed_from_cuda_graphs():
+    """Both ranks capture the fused forward of a decode shape and replay it; the kernels' call numbers
+    come from device memory, so the replays exchange rows exactly like the eager launches do."""
+    model = "random://tiny-llama-gpu?quant=q4f16_1&seed=5"
+    env = {"NCCL_NVLS_ENABLE": "0", "MLCB_FUSED_TP": "1"}
+    eager, f0 = _run(2, model, "cuda", port=29559, extra_env=dict(env, MLCB_CUDA_GRAPH="0"), want_flags=True,
+                     timeout=180)
+    graph, f1 = _run(2, model, "cuda", port=29560, extra_env=dict(env, MLCB_CUDA_GRAPH="1"), want_flags=True,
+                     timeout=180)
+    assert f0["graph_replays"] == 0 and f1["graph_replays"] > 0 and f1["fused_tp"]
+    agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(eager, graph)])
+    assert agree >= 0.9, (eager, graph)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_ep2_all_to_all_matches_tensor_parallel_moe():
     """Mixtral-style MoE with experts distributed over the ranks (all-to-all dispatch / combine over
     peer memory) against the same model with width-sharded experts and NCCL all-reduce."""
