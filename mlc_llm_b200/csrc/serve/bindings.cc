@@ -374,6 +374,11 @@ PYBIND11_MODULE(_core, m) {
       .def(py::init(&MakeTokenizer), py::arg("vocab"), py::arg("info_json"), py::arg("encode") = py::none(),
            py::arg("special_token_ids") = std::vector<int32_t>())
       .def("encode", &Tokenizer::Encode)
+      .def("encode_no_prepend_space", &Tokenizer::EncodeNoPrependSpace)
+      .def("prefix_token_mask", [](const Tokenizer& t) {
+        const std::vector<bool>& m = t.PrefixTokenMask();
+        return std::vector<int>(m.begin(), m.end());
+      })
       .def("decode", [](const Tokenizer& t, const std::vector<int32_t>& ids) { return t.Decode(ids); })
       .def("token_bytes", [](const Tokenizer& t, int32_t id) { return py::bytes(t.TokenBytes(id)); })
       .def("vocab_size", &Tokenizer::VocabSize)

@@ -380,6 +380,7 @@ class EngineImpl : public Engine {
 
   void Step() override {
     touched_.clear();
+    StepJumpForward();
     bool did = StepPrefill();
     if (!did) {
       if (spec_) did = StepSpecDecode();
@@ -804,7 +805,9 @@ class EngineImpl : public Engine {
         }
         ms.num_prefilled_tokens += it.take;
         ms.prefilled_tokens.insert(ms.prefilled_tokens.end(), fed.begin(), fed.end());
-        it.ref.rs->metrics.prefill_tokens += it.take;
+        const int64_t forced = std::min<int64_t>(it.take, ms.jump_forward_inputs);
+        ms.jump_forward_inputs -= forced;
+        it.ref.rs->metrics.prefill_tokens += it.take - forced;
         if (prefix_cache_.HasSequence(ms.internal_id)) prefix_cache_.ExtendSequence(ms.internal_id, fed);
       }
       if (it.completes) {
@@ -907,6 +910,115 @@ class EngineImpl : public Engine {
     metrics_.engine_decode_time_sum += dt;
     metrics_.UpdateDecodeTimeByBatchSize(static_cast<int>(ready.size()), dt);
     return true;
+  }
+
+  // ---------------------------------------------------------------- jump-forward decoding
+  // When the grammar leaves only one way to continue (a JSON key, punctuation, ...), that text is
+  // appended without running the model for each of its tokens (reference:
+  // cpp/serve/engine_actions/batch_jumpforward.cc).  The tail of the output is re-tokenised together
+  // with the forced text, because the natural tokenisation may merge across the seam: tokens that no
+  // longer fit are rolled back (KV, grammar, prefix cache) and the new ones are committed.  The
+  // committed-but-not-yet-computed tokens then become inputs of the sequence, so the next prefill
+  // step computes their KV in one pass and samples the token that follows.
+  static constexpr int kMaxRollbackTokens = 10;
+  static constexpr int kJumpForwardPagesPerRequest = 10;
+
+  void StepJumpForward() {
+    if (!grammar_ || spec_ || kv_.size() > 1 || !tok_) return;
+    std::vector<EntryRef> ready = ReadyToDecode();
+    if (ready.empty()) return;
+    bool any_grammar = false;
+    for (auto& r : ready) any_grammar |= r.e().grammar_handle >= 0;
+    if (!any_grammar) return;
+    const double t0 = NowSeconds();
+    // keep headroom for the forced text of every running request, as the reference does
+    if (static_cast<int64_t>(ready.size()) * kJumpForwardPagesPerRequest > kv_[0]->NumAvailablePages() &&
+        !EnsurePages(static_cast<int64_t>(ready.size()) * kJumpForwardPagesPerRequest))
+      return;
+    for (EntryRef r : ready) {
+      RequestStateEntry& e = r.e();
+      const GenerationConfig& g = r.rs->request.cfg;
+      if (e.grammar_handle < 0 || g.logprobs ||
+          g.debug_config.grammar_execution_mode != GrammarExecutionMode::kJumpForward)
+        continue;
+      if (grammar_->IsTerminated(e.grammar_handle)) continue;
+      const std::string forced = grammar_->FindJumpForwardString(e.grammar_handle);
+      if (forced.empty()) continue;
+      JumpForward(r, forced);
+    }
+    metrics_.engine_jump_forward_time_sum += NowSeconds() - t0;
+  }
+
+  void JumpForward(EntryRef r, const std::string& forced) {
+    RequestStateEntry& e = r.e();
+    ModelState& ms = e.mstates[0];
+    const int64_t n = static_cast<int64_t>(e.committed_tokens.size());
+    // ---- re-tokenise the last few tokens together with the forced text
+    const int64_t past_begin = std::max<int64_t>(0, n - kMaxRollbackTokens);
+    std::vector<int32_t> past;
+    std::string past_text;
+    for (int64_t i = past_begin; i < n; ++i) {
+      past.push_back(e.committed_tokens[i].token);
+      past_text += tok_->TokenBytes(e.committed_tokens[i].token);
+    }
+    std::vector<int32_t> fresh = tok_->EncodeNoPrependSpace(past_text + forced);
+    if (fresh.empty()) return;
+    std::string delta_text = forced;
+    // a last token that is a prefix of another token would likely be re-merged by the next decode
+    // step; leave it (and its text) to the model
+    const std::vector<bool>& prefix_mask = tok_->PrefixTokenMask();
+    if (fresh.back() >= 0 && fresh.back() < static_cast<int32_t>(prefix_mask.size()) && prefix_mask[fresh.back()]) {
+      const std::string& last = tok_->TokenBytes(fresh.back());
+      if (last.size() >= forced.size()) return;
+      delta_text.resize(delta_text.size() - last.size());
+      fresh.pop_back();
+    }
+    size_t same = 0;
+    while (same < past.size() && same < fresh.size() && past[same] == fresh[same]) ++same;
+    const int64_t rollback = static_cast<int64_t>(past.size() - same);
+    std::vector<int32_t> added(fresh.begin() + static_cast<std::ptrdiff_t>(same), fresh.end());
+    if (rollback == 0 && added.empty()) return;
+
+    // ---- stream output: text already handed out stays valid (the new tokens spell the same text plus
+    // the forced part), so only the forced part is sent, as a string, and the new tokens are skipped
+    if (rollback > n - e.next_callback_token_pos) {
+      for (int64_t i = e.next_callback_token_pos; i < n; ++i)
+        e.extra_prefix_string += tok_->TokenBytes(e.committed_tokens[i].token);
+      e.extra_prefix_string += delta_text;
+      e.next_callback_token_pos = n - rollback + static_cast<int64_t>(added.size());
+    }
+    // ---- roll back: grammar, token bookkeeping, prefix cache, KV
+    if (rollback > 0) {
+      grammar_->Rollback(e.grammar_handle, static_cast<int>(rollback));
+      for (int64_t i = n - rollback; i < n; ++i) {
+        auto it = e.appeared_token_ids.find(e.committed_tokens[i].token);
+        if (it != e.appeared_token_ids.end() && --it->second <= 0) e.appeared_token_ids.erase(it);
+      }
+      e.committed_tokens.resize(n - rollback);
+      r.rs->metrics.completion_tokens -= rollback;
+      // the KV holds every committed token but the last one
+      const int64_t kv_rollback = rollback - 1;
+      if (kv_rollback > 0) {
+        const int64_t cached = std::max<int64_t>(0, ms.cached_committed_tokens - (n - rollback));
+        if (cached > 0 && prefix_cache_.HasSequence(ms.internal_id)) {
+          prefix_cache_.RollBackSequence(ms.internal_id, cached);
+          ms.cached_committed_tokens -= cached;
+        }
+        kv_[0]->PopN(ms.internal_id, kv_rollback);
+      }
+    }
+    const int64_t in_kv = std::min<int64_t>(n - 1, n - rollback);  // committed tokens whose KV exists
+    for (int32_t t : added) CommitToken(r, SampleResult{t, 1.f, {}});
+    r.rs->metrics.jump_forward_tokens += std::max<int64_t>(0, static_cast<int64_t>(added.size()) - rollback);
+    // ---- the tokens without KV become inputs; the next prefill step computes them and samples on
+    InputItem item;
+    for (int64_t i = in_kv; i < static_cast<int64_t>(e.committed_tokens.size()); ++i)
+      item.tokens.push_back(e.committed_tokens[i].token);
+    ms.jump_forward_inputs = static_cast<int64_t>(item.tokens.size());
+    ms.inputs.push_back(std::move(item));
+    // those tokens reach the prefix cache as prefilled inputs
+    ms.cached_committed_tokens = static_cast<int64_t>(e.committed_tokens.size());
+    Touch(r.rs);
   }
 
   // ---------------------------------------------------------------- speculative decoding
@@ -1184,13 +1296,20 @@ class EngineImpl : public Engine {
         // feed the prefix cache with tokens whose KV now exists (all committed but the last)
         {
           ModelState& ms = e.mstates[0];
-          const int64_t with_kv = static_cast<int64_t>(e.committed_tokens.size()) - 1;
+          int64_t without_kv = 0;  // forced tokens still waiting as inputs, else the last sampled token
+          for (auto& in : ms.inputs) without_kv += in.Length();
+          const int64_t with_kv = static_cast<int64_t>(e.committed_tokens.size()) - std::max<int64_t>(1, without_kv);
           if (prefix_cache_.HasSequence(ms.internal_id) && with_kv > ms.cached_committed_tokens && finish.empty()) {
             std::vector<int32_t> toks;
             for (int64_t j = ms.cached_committed_tokens; j < with_kv; ++j) toks.push_back(e.committed_tokens[j].token);
             prefix_cache_.ExtendSequence(ms.internal_id, toks);
             ms.cached_committed_tokens = with_kv;
           }
+        }
+        if (!e.extra_prefix_string.empty()) {
+          out.group_extra_prefix_string[g] = std::move(e.extra_prefix_string);
+          e.extra_prefix_string.clear();
+          any = true;
         }
         if (!delta.empty()) any = true;
         if (!finish.empty()) {

@@ -165,6 +165,7 @@ struct ModelState {
   std::vector<int32_t> draft_slots;
   std::vector<int32_t> draft_parents;
   int64_t num_tokens_for_next_decode = 0;
+  int64_t jump_forward_inputs = 0;          // pending inputs that are grammar-forced output tokens
 };
 
 struct RequestStateEntry {

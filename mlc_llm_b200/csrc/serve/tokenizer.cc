@@ -153,6 +153,35 @@ std::vector<int32_t> Tokenizer::Encode(const std::string& text) const {
   return encode_(text);
 }
 
+std::vector<int32_t> Tokenizer::EncodeNoPrependSpace(const std::string& text) const {
+  if (!info_.prepend_space_in_encode) return Encode(text);
+  // a sentinel byte takes the prepended space; everything up to and including it is dropped
+  std::vector<int32_t> ids = Encode(std::string("\x01") + text);
+  for (size_t i = 0; i < ids.size(); ++i) {
+    const std::string& bytes = TokenBytes(ids[i]);
+    if (!bytes.empty() && bytes.back() == '\x01') {
+      ids.erase(ids.begin(), ids.begin() + static_cast<std::ptrdiff_t>(i) + 1);
+      return ids;
+    }
+  }
+  return Encode(text);  // the sentinel did not survive as a token of its own
+}
+
+const std::vector<bool>& Tokenizer::PrefixTokenMask() const {
+  if (!prefix_mask_.empty() || table_.empty()) return prefix_mask_;
+  std::vector<bool> mask(table_.size(), false);
+  std::vector<int32_t> order(table_.size());
+  for (size_t i = 0; i < order.size(); ++i) order[i] = static_cast<int32_t>(i);
+  std::sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return table_[a] < table_[b]; });
+  for (size_t i = 0; i + 1 < order.size(); ++i) {
+    const std::string& cur = table_[order[i]];
+    const std::string& nxt = table_[order[i + 1]];
+    if (cur.size() <= nxt.size() && nxt.compare(0, cur.size(), cur) == 0) mask[order[i]] = true;
+  }
+  prefix_mask_ = std::move(mask);
+  return prefix_mask_;
+}
+
 const std::string& Tokenizer::TokenBytes(int32_t id) const {
   if (id < 0 || id >= static_cast<int32_t>(table_.size())) return empty_;
   return table_[id];

@@ -35,6 +35,12 @@ class Tokenizer {
             std::vector<int32_t> special_token_ids = {});
 
   std::vector<int32_t> Encode(const std::string& text) const;
+  // Encodes a continuation of earlier text: tokenizers that put a space in front of every input
+  // (SentencePiece-style) are kept from doing so here (reference: cpp/tokenizers/tokenizers.cc:78-90).
+  std::vector<int32_t> EncodeNoPrependSpace(const std::string& text) const;
+  // [id] = the token's bytes are a prefix of another token's bytes (such a token is likely to be
+  // re-merged by the next decode step; reference: cpp/tokenizers/tokenizers.cc:104-131).
+  const std::vector<bool>& PrefixTokenMask() const;
   std::string Decode(const std::vector<int32_t>& ids) const;  // whole-text decode
   const std::string& TokenBytes(int32_t id) const;
   int64_t VocabSize() const { return static_cast<int64_t>(table_.size()); }
@@ -52,6 +58,7 @@ class Tokenizer {
   std::vector<bool> special_;
   std::unordered_map<std::string, int32_t> raw_index_;
   std::string empty_;
+  mutable std::vector<bool> prefix_mask_;
 };
 
 class TextStreamer {

@@ -150,6 +150,9 @@ class MLCEngineBase:
                 if sink.done[i]:
                     continue
                 text = sink.streamers[i].put(ids) if ids else ""
+                if extra and fr != "error":
+                    # grammar-forced text (jump-forward decoding) arrives as a string, before the ids
+                    text = extra + text
                 if fr is not None:
                     text += sink.streamers[i].finish()
                     sink.done[i] = True

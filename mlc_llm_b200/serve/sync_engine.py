@@ -94,6 +94,8 @@ class SyncMLCEngine:
             self.add_request(rid, [toks], g)
         index = {rid: i for i, rid in enumerate(ids)}
         tokens: List[List[List[int]]] = [[[] for _ in range(int(g.get("n", 1)))] for g in cfgs]
+        streamers = [[TextStreamer(self.tokenizer) for _ in req] for req in tokens]
+        texts = [["" for _ in req] for req in tokens]
         while not self.empty():
             self.step()
             for out in self.take_outputs():
@@ -102,7 +104,15 @@ class SyncMLCEngine:
                     continue
                 for c, delta in enumerate(out["group_delta_token_ids"]):
                     tokens[i][c].extend(delta)
-        texts = [[self.tokenizer.decode(t) for t in req] for req in tokens]
+                    # grammar-forced text (jump-forward decoding) is delivered as a string, not as ids
+                    extra = out["group_extra_prefix_string"][c]
+                    if extra and out["group_finish_reason"][c] != "error":
+                        texts[i][c] += extra
+                    if delta:
+                        texts[i][c] += streamers[i][c].put(delta)
+        for i, req in enumerate(texts):
+            for c in range(len(req)):
+                req[c] += streamers[i][c].finish()
         return texts, tokens
 
     def run_token_workload(self, prompts: List[List[int]], generation_config: Dict[str, Any]) -> int:

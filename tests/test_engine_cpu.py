@@ -283,3 +283,28 @@ def test_disaggregated_prefill_decode_hand_off():
     finally:
         for e in (plain, p_eng, d_eng):
             e.terminate()
+
+
+def test_json_mode_jump_forward_skips_decode_steps_and_keeps_the_text():
+    """Grammar-constrained output with and without jump-forward decoding: the forced parts of the JSON
+    (keys, punctuation) are appended without a decode step each, several requests at once, and the
+    text is what token-by-token constrained decoding produces (greedy)."""
+    pytest.importorskip("xgrammar")
+    schema = json.dumps({"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                                                           "tags": {"type": "array", "items": {"type": "string"}}},
+                         "required": ["name", "age", "tags"]})
+    prompts = _prompts(3, seed=3)
+    out = {}
+    for mode in ("constraint", "jump_forward"):
+        eng = _engine(prefix_cache_mode="radix")
+        cfg = {"max_tokens": 48, "temperature": 0.0, "response_format": {"type": "json_object", "schema": schema},
+               "debug_config": {"grammar_execution_mode": mode}}
+        texts, toks = eng.generate(prompts, cfg)
+        stats = json.loads(eng.debug_stats())
+        out[mode] = ([t[0] for t in texts], stats["num_decode_steps"], stats["num_prefill_steps"])
+        assert all(t[0].startswith("{") for t in texts)
+        # the sequences' KV was returned: nothing leaks through the roll-back / re-prefill path
+        assert stats["num_running"] == 0
+    assert out["jump_forward"][0] == out["constraint"][0]
+    assert out["jump_forward"][1] < out["constraint"][1]
+    assert out["jump_forward"][2] > out["constraint"][2]

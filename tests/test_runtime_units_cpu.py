@@ -220,6 +220,35 @@ def test_tokenizer_info_detection():
     assert _core.post_process_token("Ġhi", "byte_level") == b" hi"
 
 
+def test_tokenizer_continuation_encode_and_prefix_mask():
+    """Helpers of jump-forward decoding: encoding a continuation without the SentencePiece-style
+    leading space, and the mask of tokens that are prefixes of other tokens."""
+    vocab = ["<unk>", "<0x01>", "▁", "a", "ab", "▁ab", "c", "abc"]
+
+    def encode(text):  # greedy longest match over the post-processed bytes, space prepended
+        table = {"\x01": 1, " ": 2, "a": 3, "ab": 4, " ab": 5, "c": 6, "abc": 7}
+        text = " " + text
+        out = []
+        while text:
+            for n in range(len(text), 0, -1):
+                if text[:n] in table:
+                    out.append(table[text[:n]])
+                    text = text[n:]
+                    break
+            else:
+                text = text[1:]
+        return out
+
+    info = {"token_postproc_method": "byte_fallback", "prepend_space_in_encode": True,
+            "strip_space_in_decode": False}
+    tok = _core.Tokenizer(vocab, json.dumps(info), encode, [])
+    assert tok.encode("ab") == [5]                    # " ab"
+    assert tok.encode_no_prepend_space("abc") == [7]  # no leading space this time
+    mask = tok.prefix_token_mask()
+    assert mask[3] and mask[4] and not mask[7] and not mask[6]  # "a" < "ab" < "abc"; "c", "abc" are not
+    assert mask[2]                                    # " " is a prefix of " ab"
+
+
 # ------------------------------------------------------------------ event trace
 def test_event_trace_recorder_chrome_json():
     rec = _core.EventTraceRecorder()
