@@ -120,6 +120,46 @@ def dump_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str,
     return doc
 
 
+def update_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str,
+                        encode_format: str = "f32-to-bf16") -> Dict:
+    """Add (or replace) tensors in the tensor cache under ``out_dir`` without rewriting its existing
+    shards: the new tensors go to one extra shard file and records of the same name in older shards are
+    dropped from the index.  Creates the cache when there is none."""
+    index = os.path.join(out_dir, "tensor-cache.json")
+    if not os.path.isfile(index):
+        return dump_tensor_cache(params, out_dir, encode_format=encode_format)
+    with open(index, encoding="utf-8") as f:
+        doc = json.load(f)
+    items = list(params)
+    names = {n for n, _ in items}
+    buf = bytearray()
+    records: List[Dict] = []
+    for name, t in items:
+        fmt = "raw"
+        if t.dtype == torch.float32 and encode_format == "f32-to-bf16":
+            raw = (t.detach().cpu().contiguous().numpy().view(np.uint32) >> 16).astype(np.uint16).tobytes()
+            fmt = "f32-to-bf16"
+        else:
+            raw = _to_bytes(t)
+        records.append({"name": name, "shape": list(t.shape), "dtype": dtype_name(t), "format": fmt,
+                        "nbytes": len(raw), "byteOffset": len(buf)})
+        buf += raw
+    for shard in doc["records"]:
+        shard["records"] = [r for r in shard["records"] if r["name"] not in names]
+    used = {s["dataPath"] for s in doc["records"]}
+    k = 0
+    while f"params_shard_extra_{k}.bin" in used:
+        k += 1
+    path = f"params_shard_extra_{k}.bin"
+    with open(os.path.join(out_dir, path), "wb") as f:
+        f.write(buf)
+    doc["records"].append({"dataPath": path, "format": "raw-shard", "nbytes": len(buf), "records": records,
+                           "md5sum": hashlib.md5(buf).hexdigest()})
+    with open(index, "w", encoding="utf-8") as f:
+        json.dump(doc, f, indent=2)
+    return doc
+
+
 class TensorCache:
     """Lazy reader: iterates shard by shard so peak host memory is one shard file."""
 

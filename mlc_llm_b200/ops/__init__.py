@@ -95,10 +95,22 @@ def _gemm_scratch(device: torch.device):
     return (ptr(sc[0]), c_ll(GEMM_WORKSPACE_BYTES), ptr(sc[1]), c_int(GEMM_COUNTERS))
 
 
+_LINEAR_OBSERVER = None
+
+
+def set_linear_observer(fn) -> None:
+    """Install ``fn(weight, activations [M, K])`` to be called before every :func:`linear` (None removes
+    it).  Used by calibration to record activation statistics; not meant for the serving path."""
+    global _LINEAR_OBSERVER  # pylint: disable=global-statement
+    _LINEAR_OBSERVER = fn
+
+
 def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``y = x @ W^T (+ bias)`` for ``x [..., K]``."""
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
+    if _LINEAR_OBSERVER is not None and x2.shape[0] > 0:
+        _LINEAR_OBSERVER(lw, x2)
     od = out_dtype or x.dtype
     if not x.is_cuda:
         w = lw.dense(torch.float32)
