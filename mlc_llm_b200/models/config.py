@@ -312,6 +312,30 @@ def _cohere(cfg, mt):
     return d
 
 
+def _eagle(cfg, mt):
+    """EAGLE draft head: Llama blocks fed with ``fc([embedding ; target feature])``; no final norm and no
+    LM head of its own (reference: ``python/mlc_llm/model/eagle/eagle_model.py``)."""
+    d = _llama(cfg, mt)
+    d["tie_word_embeddings"] = True  # no lm_head parameter: logits come from the target model's head
+    d.setdefault("extra", {})
+    d["extra"] = dict(d["extra"], eagle=True, eagle_fc_bias=bool(_get(cfg, "bias", default=True)))
+    return d
+
+
+def _medusa(cfg, mt):
+    """Medusa heads: ``medusa_num_heads`` stacks of ``medusa_num_layers`` residual SiLU blocks and a
+    vocabulary projection, all reading the target's last hidden state (reference:
+    ``python/mlc_llm/model/medusa/medusa_model.py``).  There are no decoder layers and no KV cache."""
+    h = int(_get(cfg, "hidden_size"))
+    return dict(model_type=mt, hidden_size=h, intermediate_size=h, num_hidden_layers=0,
+                num_attention_heads=1, num_key_value_heads=1, head_dim=64,
+                vocab_size=int(_get(cfg, "vocab_size")), context_window_size=1 << 20,
+                prefill_chunk_size=int(_get(cfg, "prefill_chunk_size", default=-1) or -1),
+                tie_word_embeddings=True,
+                extra={"medusa": {"num_heads": int(_get(cfg, "medusa_num_heads")),
+                                  "num_layers": int(_get(cfg, "medusa_num_layers", default=1))}})
+
+
 _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
@@ -319,7 +343,8 @@ _PARSERS = {
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _llama, "internlm2": _llama, "baichuan": _llama, "orion": _llama, "minicpm": _llama,
-    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _llama, "aquila": _llama,
+    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _eagle, "medusa": _medusa,
+    "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,
 }
 

@@ -8,6 +8,16 @@ MODEL_PRESETS = {
         "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048,
     },
+    # speculative draft heads sized for tiny-llama: a one-block EAGLE head and three Medusa heads
+    "tiny-eagle": {
+        "model_type": "eagle", "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 1,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048, "bias": True,
+    },
+    "tiny-medusa": {
+        "model_type": "medusa", "hidden_size": 256, "vocab_size": 32000, "medusa_num_heads": 3,
+        "medusa_num_layers": 1,
+    },
     # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
     "tiny-llama-gpu": {
         "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,

@@ -291,7 +291,8 @@ class DecoderModel:
                     pending = None
                 h = x
             elif pending is None:
-                h = self._norm(x, pre + "input_layernorm")
+                # the first block of an EAGLE head reads the fused input as it is
+                h = x if (c.extra.get("eagle") and li == 0) else self._norm(x, pre + "input_layernorm")
             else:
                 h = self._add_norm(pending, x, pre + "input_layernorm")
                 pending = None
@@ -316,12 +317,51 @@ class DecoderModel:
                 mlp = self._norm(mlp, pre + "post_feedforward_layernorm")
             pending = mlp
         if pending is not None:
-            if self.last_stage and c.norm_type == "rms" and not no_pre_norm:
+            if self.last_stage and c.norm_type == "rms" and not no_pre_norm and not c.extra.get("eagle"):
                 self._final_normed = self._add_norm(pending, x, "model.norm")
                 return x
             x = x + pending
         self._final_normed = None
         return x
+
+    # ------------------------------------------------------------------ speculative draft heads
+    def final_features(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Final-normed hidden states of all rows of the latest forward (the "features" that EAGLE and
+        Medusa heads consume); must be called before :meth:`logits` consumes the cached tensor."""
+        normed = getattr(self, "_final_normed", None)
+        return normed if normed is not None else self._norm(hidden, "model.norm")
+
+    def head_logits(self, features: torch.Tensor) -> torch.Tensor:
+        """LM head alone (no norm) on feature rows; fp32 ``[n, V]``.  EAGLE heads borrow the target
+        model's vocabulary projection this way (reference: ``cpp/serve/model.cc`` ``GetLogits``)."""
+        c = self.cfg
+        head = self.p.linears.get("lm_head")
+        if head is None:
+            emb = self.p.linears.get("model.embed_tokens")
+            if emb is not None and emb.kind == "q4" and features.is_cuda and not emb.device_layout:
+                head = self._tied_head = getattr(self, "_tied_head", None) or emb.to(features.device)
+            else:
+                head = emb if emb is not None else ops.dense_weight(self.p.tensors["model.embed_tokens.weight"])
+        lg = ops.linear(features.contiguous(), head, out_dtype=torch.float32)
+        if "logit_scale" in c.extra:
+            lg = lg * c.extra["logit_scale"]
+        if c.final_logit_softcap > 0:
+            lg = torch.tanh(lg / c.final_logit_softcap) * c.final_logit_softcap
+        return lg
+
+    def fuse_embed_hidden(self, embed: torch.Tensor, features: torch.Tensor) -> torch.Tensor:
+        """EAGLE input: ``fc([token embedding ; feature of the previous position])``."""
+        x = torch.cat([embed, features.to(embed.dtype)], dim=-1).contiguous()
+        return ops.linear(x, self.p.linears["model.fc"])
+
+    def medusa_logits(self, features: torch.Tensor, head: int) -> torch.Tensor:
+        """Logits of Medusa head ``head`` on feature rows ``[n, H]``; fp32 ``[n, V]``."""
+        m = self.cfg.extra["medusa"]
+        x = features.to(self.dtype).contiguous()
+        for j in range(int(m["num_layers"])):
+            y = ops.linear(x, self.p.linears[f"medusa_head.{head}.{j}.linear"])
+            x = x + torch.nn.functional.silu(y.float()).to(x.dtype)
+        return ops.linear(x, self.p.linears[f"medusa_head.{head}.{int(m['num_layers'])}"], out_dtype=torch.float32)
 
     def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Final norm + lm_head on the selected rows of the residual stream; fp32 ``[n, V]``."""
@@ -354,7 +394,21 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
     {"linear", "embedding", "norm", "bias", "experts", "router", "pos"}."""
     h, inter = cfg.hidden_size, cfg.intermediate_size
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    medusa = cfg.extra.get("medusa")
+    if medusa:
+        specs = {}
+        for i in range(int(medusa["num_heads"])):
+            for j in range(int(medusa["num_layers"])):
+                specs[f"medusa_head.{i}.{j}.linear.weight"] = ((h, h), "linear")
+                specs[f"medusa_head.{i}.{j}.linear.bias"] = ((h,), "bias")
+            specs[f"medusa_head.{i}.{int(medusa['num_layers'])}.weight"] = ((cfg.vocab_size, h), "linear")
+        return specs
+    eagle = bool(cfg.extra.get("eagle"))
     specs: Dict[str, tuple] = {"model.embed_tokens.weight": ((cfg.vocab_size, h), "embedding")}
+    if eagle:
+        specs["model.fc.weight"] = ((h, 2 * h), "linear")
+        if cfg.extra.get("eagle_fc_bias", True):
+            specs["model.fc.bias"] = ((h,), "bias")
     if cfg.position_embedding == "learned":
         specs["model.embed_positions.weight"] = ((cfg.context_window_size, h), "pos")
     ln = cfg.norm_type == "layernorm" and not cfg.extra.get("norm_no_affine")
@@ -368,7 +422,7 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
 
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        if not cfg.extra.get("no_pre_norm"):
+        if not cfg.extra.get("no_pre_norm") and not (eagle and i == 0):
             norm(p + "input_layernorm")
         specs[p + "self_attn.qkv_proj.weight"] = (((hq + 2 * hkv) * d, h), "linear")
         if cfg.attention_bias:
@@ -409,7 +463,8 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
             if cfg.mlp_bias:
                 specs[p + "mlp.up_proj.bias"] = ((inter,), "bias")
                 specs[p + "mlp.down_proj.bias"] = ((h,), "bias")
-    norm("model.norm")
+    if not eagle:
+        norm("model.norm")
     if not cfg.tie_word_embeddings:
         specs["lm_head.weight"] = ((cfg.vocab_size, h), "linear")
         if cfg.lm_head_bias:

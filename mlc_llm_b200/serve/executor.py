@@ -12,6 +12,7 @@ verify wrappers), ``cpp/serve/logit_processor.cc:40-458`` and ``cpp/serve/sample
 
 from __future__ import annotations
 
+import collections
 import ctypes
 import json
 import os
@@ -38,6 +39,63 @@ _LOCAL_KV_POOLS: Dict[str, torch.Tensor] = {}
 
 def _pad4(n: int) -> int:
     return (n + 3) & ~3
+
+
+class FeatureStore:
+    """Target-model features (final-normed hidden states) of the positions that a speculative draft
+    head (EAGLE, Medusa) has not consumed yet, per sequence, plus the head's own latest prediction.
+
+    The draft head reads the feature of position ``p - 1`` together with the token at position ``p``
+    (reference: ``cpp/serve/engine_actions/eagle_new_request_prefill.cc`` and ``eagle_batch_draft.cc``
+    move the same rows through the draft-token workspace).  While the target has computed that position
+    the true feature is used; beyond it, the head continues from its own previous output.
+    """
+
+    CAP_ROWS = 512    # per sequence: older rows are dropped (the head then sees zeros for them)
+    CAP_SEQS = 4096   # sequences remembered; the least recently written go first
+
+    def __init__(self):
+        self.rows: "collections.OrderedDict[int, tuple]" = collections.OrderedDict()
+        self.pred: Dict[int, tuple] = {}
+
+    def put(self, seq: int, start: int, feats: torch.Tensor) -> None:
+        """Rows for positions ``start ..``; anything stored from ``start`` on is replaced."""
+        feats = feats.detach().clone()
+        cur = self.rows.pop(seq, None)
+        if cur is not None:
+            s0, t = cur
+            if s0 <= start <= s0 + t.shape[0]:
+                feats = torch.cat([t[: start - s0], feats])
+                start = s0
+        if feats.shape[0] > self.CAP_ROWS:
+            start += feats.shape[0] - self.CAP_ROWS
+            feats = feats[-self.CAP_ROWS:]
+        self.rows[seq] = (start, feats)
+        self.pred.pop(seq, None)
+        while len(self.rows) > self.CAP_SEQS:
+            old, _ = self.rows.popitem(last=False)
+            self.pred.pop(old, None)
+
+    def end(self, seq: int) -> int:
+        """One past the last position whose true feature is known (0: none)."""
+        cur = self.rows.get(seq)
+        return 0 if cur is None else cur[0] + cur[1].shape[0]
+
+    def span(self, seq: int):
+        cur = self.rows.get(seq)
+        return (0, None) if cur is None else cur
+
+    def trim(self, seq: int, keep_from: int) -> None:
+        cur = self.rows.get(seq)
+        if cur is not None and keep_from > cur[0]:
+            s0, t = cur
+            k = min(keep_from - s0, t.shape[0] - 1)  # always keep the newest row
+            if k > 0:
+                self.rows[seq] = (s0 + k, t[k:])
+
+    def clear(self) -> None:
+        self.rows.clear()
+        self.pred.clear()
 
 
 class StagingBuffer:
@@ -112,15 +170,24 @@ class ModelExecutor:
         self.d2h_bytes = 0
         self.kernel_launch_estimate = 0
         self.use_tensor_core_attention = device.type == "cuda"
-        # CUDA graphs of decode-shaped forwards, keyed by the batch shape (MLCB_CUDA_GRAPH=0 disables)
-        # Default for single-process engines only: a forward with NCCL collectives inside did not
-        # complete under capture in a two-rank run.  MLCB_CUDA_GRAPH=1 (explicit) also captures the
-        # fused tensor-parallel forward of multi-rank engines, which holds no NCCL call.
-        self.use_graphs = (device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
-                           and (comm is None or comm.world_size == 1 or os.environ.get("MLCB_CUDA_GRAPH") == "1"))
+        # CUDA graphs of decode-shaped forwards, keyed by the batch shape (MLCB_CUDA_GRAPH=0 disables).
+        # Multi-rank engines capture only the fused tensor-parallel forward, whose collectives are this
+        # library's kernels over peer memory (see _graph_ok): a forward with NCCL collectives inside did
+        # not complete under capture in a two-rank run and stays on eager launches.
+        self.use_graphs = device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
         self._graphs: Dict[tuple, dict] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        # speculative draft heads fed with the target's features: model id -> "eagle" | "medusa"
+        self.spec_heads: Dict[int, str] = {}
+        for mi, m in enumerate(models):
+            if mi > 0 and m.cfg.extra.get("eagle"):
+                self.spec_heads[mi] = "eagle"
+            elif mi > 0 and m.cfg.extra.get("medusa"):
+                self.spec_heads[mi] = "medusa"
+        if self.spec_heads and comm is not None and comm.world_size > 1:
+            raise NotImplementedError("EAGLE / Medusa draft heads run on single-process engines only")
+        self.features = FeatureStore()
         # wall-clock seconds the host spent per phase of forward_sample (profiling aid)
         self.host_times: Dict[str, float] = {"pack": 0.0, "broadcast": 0.0, "upload": 0.0, "forward": 0.0,
                                              "logits_sample": 0.0, "readback": 0.0, "calls": 0.0}
@@ -144,6 +211,7 @@ class ModelExecutor:
 
     def reset(self) -> None:
         self.embeddings.clear()
+        self.features.clear()
 
     def synchronize(self) -> None:
         if self.device.type == "cuda":
@@ -347,6 +415,11 @@ class ModelExecutor:
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         t3 = clock()
+        if model_id in self.spec_heads:
+            logits = self._forward_spec_head(model_id, plan, dev, n_rows)
+            if logits is None:
+                return None
+            return self._sample(logits, dev, sp, n_rows)
         hidden = self._run_model(model_id, plan, dev, embed_handles)
         t4 = clock()
         ht["pack"] += t1 - t0
@@ -354,9 +427,10 @@ class ModelExecutor:
         ht["upload"] += t3 - t2
         ht["forward"] += t4 - t3
         ht["calls"] += 1
+        if self.spec_heads and model_id == 0:
+            self._remember_features(plan, self.models[0].final_features(hidden), None)
         if n_rows == 0:
             return None
-        model = self.models[model_id]
         logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
         if self._is_plain_greedy(sp):
             tokens = ops.argmax(logits)
@@ -366,6 +440,10 @@ class ModelExecutor:
             ht["readback"] += clock() - t5
             self.d2h_bytes += tok.nbytes
             return {"tokens": tok, "probs": np.ones(n_rows, dtype=np.float32)}
+        return self._sample(logits, dev, sp, n_rows)
+
+    def _sample(self, logits: torch.Tensor, dev: Dict[str, torch.Tensor], sp: dict, n_rows: int) -> dict:
+        """Logit processing, softmax, sampling and read-back of one row per entry of ``sp``."""
         self._process_logits(logits, dev, sp)
         probs = ops.softmax_temperature(logits, dev["s_temperature"])
         if len(sp["prob_slots"]):
@@ -394,6 +472,86 @@ class ModelExecutor:
         self.d2h_bytes += out["tokens"].nbytes + out["probs"].nbytes
         return out
 
+    # ------------------------------------------------------------------ EAGLE / Medusa draft heads
+    def _remember_features(self, plan: dict, feats: torch.Tensor, rows_of_seq: Optional[List[List[int]]]) -> None:
+        """Store the target's features of this forward: all rows of every sequence (prefill, decode), or
+        only ``rows_of_seq[i]`` (verification: the root and the accepted nodes, which sit at consecutive
+        positions)."""
+        qi = np.asarray(plan["q_indptr"])
+        pos = np.asarray(plan["positions"])
+        for i, sid in enumerate(np.asarray(plan["seq_ids"]).tolist()):
+            a, b = int(qi[i]), int(qi[i + 1])
+            if b <= a:
+                continue
+            if rows_of_seq is None:
+                self.features.put(int(sid), int(pos[a]), feats[a:b])
+            else:
+                idx = torch.as_tensor(rows_of_seq[i], dtype=torch.long, device=feats.device)
+                self.features.put(int(sid), int(pos[a]), feats.index_select(0, idx))
+
+    def _forward_spec_head(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor], n_rows: int
+                           ) -> Optional[torch.Tensor]:
+        """Forward of a feature-fed draft head over the tokens of ``plan``; returns the logits of the
+        sample rows (None when the call only advances the head's state, i.e. its prefill)."""
+        kind = self.spec_heads[model_id]
+        head, target = self.models[model_id], self.models[0]
+        qi = np.asarray(plan["q_indptr"])
+        pos = np.asarray(plan["positions"])
+        ids = [int(x) for x in np.asarray(plan["seq_ids"]).tolist()]
+        hsz = target.cfg.hidden_size
+        if kind == "medusa":
+            # no state of its own: draft round r uses head r on the newest true feature
+            if n_rows == 0:
+                return None
+            heads = int(head.cfg.extra["medusa"]["num_heads"])
+            feats = torch.zeros(len(ids), hsz, dtype=target.dtype, device=self.device)
+            which = np.zeros(len(ids), dtype=np.int64)
+            for i, sid in enumerate(ids):
+                s0, t = self.features.span(sid)
+                if t is not None:
+                    feats[i] = t[-1]
+                    which[i] = min(max(int(pos[int(qi[i + 1]) - 1]) - (s0 + t.shape[0]), 0), heads - 1)
+            logits = torch.empty(len(ids), head.cfg.vocab_size, dtype=torch.float32, device=self.device)
+            for j in sorted(set(which.tolist())):
+                sel = torch.as_tensor(np.nonzero(which == j)[0], dtype=torch.long, device=self.device)
+                logits[sel] = head.medusa_logits(feats.index_select(0, sel), int(j))
+            return logits
+        # ---- EAGLE: token at position p is fused with the feature of position p - 1
+        if dev["page_copies"].numel():
+            head.copy_pages(dev["page_copies"])
+        x = head.embed(dev["token_ids"])
+        prev = torch.zeros(x.shape[0], hsz, dtype=x.dtype, device=self.device)
+        all_true = []
+        for i, sid in enumerate(ids):
+            a, b = int(qi[i]), int(qi[i + 1])
+            if b <= a:
+                all_true.append(False)
+                continue
+            s0, t = self.features.span(sid)
+            first = int(pos[a]) - 1            # feature position wanted by row a
+            covered = 0
+            if t is not None:
+                lo, hi = max(first, s0), min(first + (b - a), s0 + t.shape[0])
+                if hi > lo:
+                    prev[a + (lo - first): a + (hi - first)] = t[lo - s0: hi - s0].to(x.dtype)
+                    covered = hi - lo
+            own = self.features.pred.get(sid)
+            if own is not None and first <= own[0] < first + (b - a) and (t is None or own[0] >= s0 + t.shape[0]):
+                prev[a + (own[0] - first)] = own[1].to(x.dtype)
+            all_true.append(covered == b - a)
+        x = head.fuse_embed_hidden(x, prev)
+        h = head.forward(x, self._batch_info(dev, plan, head))
+        for i, sid in enumerate(ids):
+            a, b = int(qi[i]), int(qi[i + 1])
+            if b <= a:
+                continue
+            if all_true[i]:
+                self.features.trim(sid, int(pos[b - 1]) - 1)
+            self.features.pred[sid] = (int(pos[b - 1]), h[b - 1].detach().clone())
+        if n_rows == 0:
+            return None
+        return target.head_logits(ops.row_gather(h, dev["s_logit_token_index"]))
+
     def forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
         self._enter()
         sp = vp["sampling"]
@@ -405,6 +563,7 @@ class ModelExecutor:
         dev = self.staging.upload(arrays)
         self.h2d_bytes += self.staging.last_words * 4
         hidden = self._run_model(model_id, plan, dev, None)
+        feats = self.models[0].final_features(hidden) if (self.spec_heads and model_id == 0) else None
         logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
         self._process_logits(logits, dev, sp)
         probs = ops.softmax_temperature(logits, dev["s_temperature"])
@@ -461,6 +620,12 @@ class ModelExecutor:
                 r = int(parent_row[r])
             accepted_nodes.extend(reversed(path))
             accepted_indptr.append(len(accepted_nodes))
+        if feats is not None:
+            # the draft head continues from the true features of the root and of the accepted nodes
+            qi = np.asarray(plan["q_indptr"])
+            keep = [[int(qi[s_])] + [int(qi[s_]) + 1 + n for n in accepted_nodes[accepted_indptr[s_]:accepted_indptr[s_ + 1]]]
+                    for s_ in range(nseq)]
+            self._remember_features(plan, feats, keep)
         return {"accepted_indptr": np.asarray(accepted_indptr, dtype=np.int32),
                 "accepted_nodes": np.asarray(accepted_nodes, dtype=np.int32),
                 "final_tokens": tokens.to(torch.int32).cpu().numpy(),
