@@ -100,6 +100,8 @@ class EngineImpl : public Engine {
       if (v.is_object()) default_gen_ = GenerationConfig::DefaultsFromModelConfig(v.as_object());
     }
     spec_ = cfg_.speculative_mode != SpeculativeMode::kDisable && models_.size() > 1;
+    feature_fed_draft_ = cfg_.speculative_mode == SpeculativeMode::kEagle ||
+                         cfg_.speculative_mode == SpeculativeMode::kMedusa;
     if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * 2 * (MaxDraftLength() + 1));
     std::random_device rd;
     seed_rng_.seed(rd());
@@ -1183,8 +1185,11 @@ class EngineImpl : public Engine {
       for (int j = beg; j < end; ++j) keep.push_back(vo.accepted_nodes[j] + 1);
       std::vector<int32_t> moves = kv_[0]->CommitTreeNodes(e.mstates[0].internal_id, k + 1, keep);
       if (!moves.empty()) backend_->MoveKVTokens(0, moves);
-      // draft KV holds [.., last committed, d_0 .. d_{k-2}]; keep the accepted part
-      const int draft_valid = std::min(accepted, k - 1);
+      // draft KV holds [.., last committed, d_0 .. d_{k-2}]; keep the accepted part.  A feature-fed head
+      // (EAGLE) computed those entries from its own predicted features: all of them are dropped and
+      // the next draft phase recomputes the accepted tokens from the target's true features
+      // (reference: cpp/serve/engine_actions/eagle_batch_verify.cc).
+      const int draft_valid = feature_fed_draft_ ? 0 : std::min(accepted, k - 1);
       if (k - 1 - draft_valid > 0) kv_[1]->PopN(ds.internal_id, k - 1 - draft_valid);
       for (int j = beg; j < end; ++j) {
         CommitToken(r, ds.draft_tokens[vo.accepted_nodes[j]]);
@@ -1359,6 +1364,7 @@ class EngineImpl : public Engine {
   EngineMetrics metrics_;
   std::mt19937_64 seed_rng_;
   bool spec_ = false;
+  bool feature_fed_draft_ = false;  // EAGLE / Medusa: the draft head consumes the target's hidden states
   int64_t num_prefill_steps_ = 0, num_decode_steps_ = 0, num_verify_steps_ = 0, num_preemptions_ = 0;
 };
 

@@ -249,6 +249,16 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
     elif mt in ("qwen2_moe", "qwen3_moe"):
         _llama_like(cfg, m)
         _moe_layers(cfg, m, "qwen")
+    elif mt == "eagle":
+        # EAGLE checkpoints name their tensors without the "model." prefix; the resolver tries both
+        _llama_like(cfg, m)
+        m.add("model.fc.weight", ["fc.weight"])
+        if cfg.extra.get("eagle_fc_bias", True):
+            m.add("model.fc.bias", ["fc.bias"])
+    elif mt == "medusa":
+        # same names on both sides (reference: model/medusa/medusa_loader.py, standard loader)
+        for name in param_specs(cfg):
+            m.add(name, [name])
     else:
         _llama_like(cfg, m)
     # drop destinations the architecture does not have (e.g. dense MLP names on MoE layers)

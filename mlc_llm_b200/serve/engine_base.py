@@ -308,6 +308,10 @@ class EngineRuntime:
             total = min(psutil.virtual_memory().available, 16 << 30)
         ec = json.loads(cfg.asjson())
         ec.setdefault("mode", "local")
+        if ec.get("speculative_mode") == "medusa" and len(self.models) > 1 and self.models[1].cfg.extra.get("medusa"):
+            # one draft token per Medusa head
+            heads = int(self.models[1].cfg.extra["medusa"]["num_heads"])
+            ec["spec_draft_length"] = min(int(ec.get("spec_draft_length") or heads), heads)
         res = _core.infer_capacity(json.dumps(ec), infos, int(total))
         if comm is not None and comm.world_size > 1:
             res = comm.agree_on_capacity(res)

@@ -1,0 +1,178 @@
+"""EAGLE and Medusa speculative modes on CPU: greedy output equals plain decoding, and the draft heads
+are fed the target model's true features of the right positions."""
+import numpy as np
+import pytest
+import torch
+
+from mlc_llm_b200.serve.config import EngineConfig
+from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
+
+MODEL = "random://tiny-llama?quant=q0f32&seed=11"
+HEADS = {"eagle": "random://tiny-eagle?quant=q0f32&seed=3", "medusa": "random://tiny-medusa?quant=q0f32&seed=4"}
+GREEDY = {"temperature": 0.0, "debug_config": {"ignore_eos": True}, "max_tokens": 10}
+
+
+def _engine(mode=None, chunk=32):
+    kw = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=chunk,
+              prefix_cache_mode="disable")
+    if mode:
+        kw.update(speculative_mode=mode, spec_draft_length=3, additional_models=[HEADS[mode]])
+    return SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+
+
+def _prompts(n, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(10, 31000, int(rng.integers(20, 60))).tolist() for _ in range(n)]
+
+
+def _reference_features(tokens):
+    """Final-normed hidden states of every position of ``tokens``, from one plain prefill pass."""
+    eng = _engine(chunk=256)
+    model = eng.runtime.models[0]
+    seen = []
+    orig = model.logits
+
+    def logits(hidden, rows):
+        seen.append(model.final_features(hidden).detach().clone())
+        return orig(hidden, rows)
+
+    model.logits = logits
+    eng.generate([tokens], dict(GREEDY, max_tokens=1))
+    return seen[0]
+
+
+@pytest.mark.parametrize("mode", ["eagle", "medusa"])
+def test_greedy_output_equals_plain_decoding(mode):
+    prompts = _prompts(4)
+    _, want = _engine().generate(prompts, GREEDY)
+    eng = _engine(mode)
+    _, got = eng.generate(prompts, GREEDY)
+    assert [t[0] for t in got] == [t[0] for t in want]
+    import json
+
+    stats = json.loads(eng.debug_stats())
+    assert stats["num_verify_steps"] > 0 and stats["num_running"] == 0
+
+
+def test_eagle_head_reads_true_features_of_the_previous_position():
+    prompt = _prompts(1, seed=5)[0][:45] + _prompts(1, seed=6)[0][:5]   # > one prefill chunk of 32
+    eng = _engine("eagle")
+    ex = eng.runtime.executor
+    head = eng.runtime.models[1]
+    events = []
+    orig_fuse, orig_head, orig_verify = head.fuse_embed_hidden, ex._forward_spec_head, ex.forward_verify
+
+    def fuse(embed, feats):
+        events[-1]["prev"] = feats.detach().clone()
+        return orig_fuse(embed, feats)
+
+    def spec_head(model_id, plan, dev, n_rows):
+        events.append({"kind": "head", "pos": np.asarray(plan["positions"]).copy(), "sampling": n_rows > 0})
+        return orig_head(model_id, plan, dev, n_rows)
+
+    def verify(*a, **k):
+        events.append({"kind": "verify"})
+        return orig_verify(*a, **k)
+
+    head.fuse_embed_hidden, ex._forward_spec_head, ex.forward_verify = fuse, spec_head, verify
+    _, toks = eng.generate([prompt], GREEDY)
+    full = prompt + toks[0][0]
+    ref = _reference_features(full[:-1] + [1])[: len(full) - 1]
+    checked_prefill = checked_round0 = 0
+    prev_kind = "start"
+    for ev in events:
+        if ev["kind"] == "head":
+            first_after_target_pass = prev_kind in ("start", "verify", "prefill")
+            if not ev["sampling"] or first_after_target_pass:
+                # prefill of the head, or the first draft round after a target pass: every row pairs its
+                # token with the target's feature of the position before it (zeros before position 0)
+                for row, p in enumerate(ev["pos"].tolist()):
+                    want = ref[p - 1] if p > 0 else torch.zeros_like(ref[0])
+                    assert torch.allclose(ev["prev"][row], want, atol=2e-4), (p, ev["sampling"])
+                    if ev["sampling"]:
+                        checked_round0 += 1
+                    else:
+                        checked_prefill += 1
+            prev_kind = "head" if ev["sampling"] else "prefill"
+        else:
+            prev_kind = "verify"
+    assert checked_prefill >= len(prompt) and checked_round0 >= 3
+
+
+def test_medusa_round_r_uses_head_r_on_the_newest_true_feature():
+    prompt = _prompts(1, seed=7)[0][:40]
+    eng = _engine("medusa")
+    ex = eng.runtime.executor
+    head = eng.runtime.models[1]
+    events = []
+    orig_logits, orig_head, orig_verify = head.medusa_logits, ex._forward_spec_head, ex.forward_verify
+
+    def medusa_logits(feats, which):
+        events[-1].update(feats=feats.detach().clone(), head=which)
+        return orig_logits(feats, which)
+
+    def spec_head(model_id, plan, dev, n_rows):
+        if n_rows:
+            events.append({"kind": "head", "last_pos": int(np.asarray(plan["positions"])[-1])})
+        return orig_head(model_id, plan, dev, n_rows)
+
+    def verify(*a, **k):
+        events.append({"kind": "verify"})
+        return orig_verify(*a, **k)
+
+    head.medusa_logits, ex._forward_spec_head, ex.forward_verify = medusa_logits, spec_head, verify
+    _, toks = eng.generate([prompt], GREEDY)
+    full = prompt + toks[0][0]
+    ref = _reference_features(full[:-1] + [1])[: len(full) - 1]
+    rnd, base, n = 0, None, 0
+    for ev in events:
+        if ev["kind"] == "verify":
+            rnd = 0
+            continue
+        if rnd == 0:
+            base = ev["last_pos"]  # position of the last committed token
+        assert ev["head"] == rnd and ev["last_pos"] == base + rnd
+        assert torch.allclose(ev["feats"][0], ref[base - 1], atol=2e-4)
+        rnd += 1
+        n += 1
+    assert n >= 6
+
+
+def test_eagle_and_medusa_checkpoints_load_from_huggingface_names(tmp_path):
+    from safetensors.torch import save_file
+
+    from mlc_llm_b200 import quantization as Q
+    from mlc_llm_b200.models import config as mc
+    from mlc_llm_b200.models import loader
+    from mlc_llm_b200.models.presets import MODEL_PRESETS
+
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, generator=g) * 0.05
+    # ---- EAGLE: tensors without the "model." prefix, separate q / k / v and gate / up, fc with bias
+    cfg = mc.from_dict("eagle", dict(MODEL_PRESETS["tiny-eagle"]))
+    h, d, hq, hkv, inter = 256, 64, 4, 2, 688
+    sd = {"embed_tokens.weight": rnd(32000, h), "fc.weight": rnd(h, 2 * h), "fc.bias": rnd(h),
+          "layers.0.self_attn.q_proj.weight": rnd(hq * d, h), "layers.0.self_attn.k_proj.weight": rnd(hkv * d, h),
+          "layers.0.self_attn.v_proj.weight": rnd(hkv * d, h), "layers.0.self_attn.o_proj.weight": rnd(h, hq * d),
+          "layers.0.mlp.gate_proj.weight": rnd(inter, h), "layers.0.mlp.up_proj.weight": rnd(inter, h),
+          "layers.0.mlp.down_proj.weight": rnd(h, inter), "layers.0.post_attention_layernorm.weight": rnd(h)}
+    (tmp_path / "eagle").mkdir()
+    save_file(sd, str(tmp_path / "eagle" / "model.safetensors"))
+    store = loader.load_hf_params(str(tmp_path / "eagle"), cfg, Q.get("q0f32"), torch.device("cpu"))
+    assert torch.equal(store.linears["model.fc"].w, sd["fc.weight"])
+    assert torch.equal(store.linears["model.fc"].bias, sd["fc.bias"])
+    qkv = torch.cat([sd[f"layers.0.self_attn.{n}_proj.weight"] for n in "qkv"])
+    assert torch.equal(store.linears["model.layers.0.self_attn.qkv_proj"].w, qkv)
+    assert "model.layers.0.input_layernorm.weight" not in store.tensors  # the first block has none
+    # ---- Medusa: names are kept
+    mcfg = mc.from_dict("medusa", dict(MODEL_PRESETS["tiny-medusa"]))
+    msd = {}
+    for i in range(3):
+        msd[f"medusa_head.{i}.0.linear.weight"] = rnd(h, h)
+        msd[f"medusa_head.{i}.0.linear.bias"] = rnd(h)
+        msd[f"medusa_head.{i}.1.weight"] = rnd(32000, h)
+    (tmp_path / "medusa").mkdir()
+    save_file(msd, str(tmp_path / "medusa" / "model.safetensors"))
+    mstore = loader.load_hf_params(str(tmp_path / "medusa"), mcfg, Q.get("q0f32"), torch.device("cpu"))
+    assert torch.equal(mstore.linears["medusa_head.2.1"].w, msd["medusa_head.2.1.weight"])
+    assert torch.equal(mstore.linears["medusa_head.1.0.linear"].bias, msd["medusa_head.1.0.linear.bias"])
