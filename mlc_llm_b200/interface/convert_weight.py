@@ -21,8 +21,6 @@ def convert_weight(config: str, quantization: str, model_type: str = "auto", dev
                    source: str = "auto", source_format: str = "auto", output: str = ".",
                    lora_adapter: Optional[str] = None, verbose: bool = True,
                    encode_format: str = "f32-to-bf16") -> dict:
-    if lora_adapter is not None:
-        raise ValueError("merging LoRA adapters is not supported by this build")
     config_path, hf = detect_config(config)
     mt = detect_model_type(model_type, hf)
     quant = Q.get(quantization)
@@ -33,7 +31,7 @@ def convert_weight(config: str, quantization: str, model_type: str = "auto", dev
     stats = {"params": 0, "bytes": 0}
 
     def on_device():
-        for name, t in huggingface_loader.iter_mlc_params(src_dir, cfg):
+        for name, t in huggingface_loader.iter_mlc_params(src_dir, cfg, lora_adapter):
             yield name, t.to(dev)
 
     def records():
@@ -46,6 +44,15 @@ def convert_weight(config: str, quantization: str, model_type: str = "auto", dev
             if verbose:
                 print(f"[convert_weight] {name} {tuple(t.shape)} {t.dtype}")
             yield name, t
+        if cfg.extra.get("vision"):
+            # the vision tower and projector stay unquantised, under their checkpoint names
+            from ..models.vision import load_hf_vision_params  # pylint: disable=import-outside-toplevel
+
+            for name, t in load_hf_vision_params(src_dir, cfg.extra["vision"], cfg.hidden_size).items():
+                t = t.to(torch.float32 if quant.torch_dtype == torch.float32 else torch.float16)
+                stats["bytes"] += t.numel() * t.element_size()
+                stats["params"] += t.numel()
+                yield name, t
 
     doc = dump_tensor_cache(records(), output, encode_format=encode_format)
     total_params, total_bytes = stats["params"], stats["bytes"]

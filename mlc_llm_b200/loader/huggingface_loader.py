@@ -275,9 +275,12 @@ class HFCheckpoint:
     """Name -> tensor view over the shards of a HuggingFace checkpoint directory; one shard is open
     at a time."""
 
-    def __init__(self, path: str):
+    def __init__(self, path: str, lora_adapter: Optional[str] = None):
         self.path = path
         self.name_to_file: Dict[str, str] = {}
+        self.lora: Dict[str, Tuple[torch.Tensor, torch.Tensor, float]] = {}
+        if lora_adapter is not None:
+            self.lora = load_lora_adapter(lora_adapter)
         st_index = os.path.join(path, "model.safetensors.index.json")
         pt_index = os.path.join(path, "pytorch_model.bin.index.json")
         if os.path.isfile(st_index):
@@ -317,23 +320,81 @@ class HFCheckpoint:
             return name
         for alt in (name.removeprefix("model."), "model." + name, name.removeprefix("transformer."),
                     "transformer." + name, "model.language_model." + name.removeprefix("model."),
-                    "language_model." + name):
+                    "language_model." + name, "model.language_model." + name):
             if alt in self.name_to_file:
                 return alt
+        return None
+
+    def _lora_delta(self, real: str) -> Optional[torch.Tensor]:
+        if not self.lora or not real.endswith(".weight"):
+            return None
+        module = real[: -len(".weight")]
+        for cand in (module, module.removeprefix("model."), "model." + module):
+            if cand in self.lora:
+                a, b, scale = self.lora[cand]
+                return (b.float() @ a.float()) * scale
         return None
 
     def get(self, name: str) -> torch.Tensor:
         real = self.resolve(name)
         if real is None:
             raise KeyError(name)
+        delta = self._lora_delta(real)
+        if delta is not None:
+            self._load_file(self.name_to_file[real])
+            w = self._open[real]
+            return (w.float() + delta).to(w.dtype)
         self._load_file(self.name_to_file[real])
         return self._open[real]
 
 
-def iter_mlc_params(path: str, cfg: ModelConfig) -> Iterator[Tuple[str, torch.Tensor]]:
+def load_lora_adapter(adapter_dir: str) -> Dict[str, Tuple[torch.Tensor, torch.Tensor, float]]:
+    """Read a PEFT-format LoRA adapter directory (``adapter_config.json`` + ``adapter_model.safetensors``
+    or ``adapter_model.bin``): module path -> ``(A [r, in], B [out, r], scale)`` with
+    ``scale = lora_alpha / r`` (``/ sqrt(r)`` for rank-stabilised adapters).  Merging is
+    ``W += scale * B @ A``, which is what the reference obtains from ``peft``'s ``merge_and_unload``
+    (``python/mlc_llm/interface/convert_weight.py:68-98``)."""
+    cfg_path = os.path.join(adapter_dir, "adapter_config.json")
+    if not os.path.isfile(cfg_path):
+        raise ValueError(f"LoRA adapter directory does not exist or has no adapter_config.json: {adapter_dir}")
+    acfg = json.load(open(cfg_path, encoding="utf-8"))
+    st = os.path.join(adapter_dir, "adapter_model.safetensors")
+    if os.path.isfile(st):
+        from safetensors.torch import load_file  # pylint: disable=import-outside-toplevel
+
+        sd = load_file(st)
+    else:
+        sd = torch.load(os.path.join(adapter_dir, "adapter_model.bin"), map_location="cpu", weights_only=True)
+    r_default = int(acfg.get("r", 8))
+    alpha_default = float(acfg.get("lora_alpha", r_default))
+    out: Dict[str, Tuple[torch.Tensor, torch.Tensor, float]] = {}
+    for key, a in sd.items():
+        if ".lora_A" not in key:
+            continue
+        module = key.split(".lora_A")[0]
+        b_key = key.replace(".lora_A", ".lora_B")
+        if b_key not in sd:
+            raise ValueError(f"adapter tensor {key} has no lora_B partner")
+        short = module.removeprefix("base_model.model.")
+        leaf = short.rsplit(".", 1)[-1]
+        r = int((acfg.get("rank_pattern") or {}).get(leaf, a.shape[0]))
+        alpha = float((acfg.get("alpha_pattern") or {}).get(leaf, alpha_default))
+        scale = alpha / (r ** 0.5) if acfg.get("use_rslora") else alpha / r
+        w_a, w_b = a, sd[b_key]
+        if acfg.get("fan_in_fan_out"):
+            w_a, w_b = w_b.t(), w_a.t()
+        out[short] = (w_a, w_b, scale)
+    if not out:
+        raise ValueError(f"no lora_A / lora_B tensors found under {adapter_dir}")
+    return out
+
+
+def iter_mlc_params(path: str, cfg: ModelConfig, lora_adapter: Optional[str] = None
+                    ) -> Iterator[Tuple[str, torch.Tensor]]:
     """Yield (destination name, full-precision tensor), ordered so that tensors sharing a shard file
-    are produced together."""
-    ckpt = HFCheckpoint(path)
+    are produced together.  With ``lora_adapter`` the adapter's low-rank updates are merged into the
+    tensors they target before any fusing or quantisation."""
+    ckpt = HFCheckpoint(path, lora_adapter)
     mapping = build_mapping(cfg)
     tied_head = None
 

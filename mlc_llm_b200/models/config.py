@@ -336,6 +336,39 @@ def _medusa(cfg, mt):
                                   "num_layers": int(_get(cfg, "medusa_num_layers", default=1))}})
 
 
+def _llava(cfg, mt):
+    """LLaVA: a Llama / Mistral language model plus a CLIP vision tower whose projected patch features
+    replace the image placeholder in the prompt (reference: ``python/mlc_llm/model/llava/llava_model.py``)."""
+    text = dict(cfg.get("text_config") or {})
+    text_type = text.get("model_type", "llama")
+    if text_type not in ("llama", "mistral"):
+        raise ValueError(f"LLaVA with a {text_type!r} language model is not supported")
+    for k in ("context_window_size", "prefill_chunk_size", "sliding_window_size", "attention_sink_size",
+              "tensor_parallel_shards", "pipeline_parallel_stages", "max_batch_size"):
+        if k in cfg and k not in text:
+            text[k] = cfg[k]
+    text.setdefault("vocab_size", cfg.get("vocab_size", 32064))
+    d = _PARSERS[text_type](text, text_type)
+    d["model_type"] = mt
+    vision = dict(cfg.get("vision_config") or {})
+    vision.setdefault("hidden_size", 1024)
+    vision.setdefault("intermediate_size", 4096)
+    vision.setdefault("num_hidden_layers", 24)
+    vision.setdefault("num_attention_heads", 16)
+    vision.setdefault("image_size", 336)
+    vision.setdefault("patch_size", 14)
+    vision.setdefault("hidden_act", "quick_gelu")
+    vision.setdefault("layer_norm_eps", 1e-5)
+    extra = dict(d.get("extra") or {})
+    extra["vision"] = vision
+    extra["vision_feature_layer"] = int(cfg.get("vision_feature_layer", -2))
+    extra["vision_feature_select_strategy"] = cfg.get("vision_feature_select_strategy", "default")
+    extra["projector_hidden_act"] = cfg.get("projector_hidden_act", "gelu")
+    extra["image_token_index"] = int(cfg.get("image_token_index", cfg.get("image_token_id", 32000)))
+    d["extra"] = extra
+    return d
+
+
 _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
@@ -343,7 +376,7 @@ _PARSERS = {
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _llama, "internlm2": _llama, "baichuan": _llama, "orion": _llama, "minicpm": _llama,
-    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _eagle, "medusa": _medusa,
+    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
     "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,
 }

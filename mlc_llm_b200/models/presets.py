@@ -18,6 +18,19 @@ MODEL_PRESETS = {
         "model_type": "medusa", "hidden_size": 256, "vocab_size": 32000, "medusa_num_heads": 3,
         "medusa_num_layers": 1,
     },
+    # tiny-llama with a 2-block CLIP tower: 28 x 28 images, four 14 x 14 patches
+    "tiny-llava": {
+        "model_type": "llava", "image_token_index": 31999, "vision_feature_layer": -2,
+        "vision_feature_select_strategy": "default", "projector_hidden_act": "gelu",
+        "text_config": {
+            "model_type": "llama", "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 2,
+            "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
+            "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 2048,
+        },
+        "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+                          "num_attention_heads": 4, "image_size": 28, "patch_size": 14,
+                          "hidden_act": "quick_gelu", "layer_norm_eps": 1e-5},
+    },
     # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
     "tiny-llama-gpu": {
         "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,

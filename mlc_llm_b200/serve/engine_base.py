@@ -266,6 +266,29 @@ class EngineRuntime:
             mc["pipeline_parallel_stages"] = cfg.pipeline_parallel_stages
         return model_config.from_dict(chat["model_type"], mc)
 
+    def _attach_vision_tower(self, model: DecoderModel, info: ModelInfo, mcfg) -> None:
+        """Image inputs: the CLIP tower + projector produce the prompt rows of an image
+        (``model.image_embed(pixels)``; reference: ``cpp/serve/model.cc`` ``ImageEmbed``)."""
+        from ..models import vision as V  # pylint: disable=import-outside-toplevel
+
+        vis = mcfg.extra["vision"]
+        if info.random_seed is not None:
+            params = V.VisionTower.random_params(vis, mcfg.hidden_size, info.random_seed + 101)
+        elif info.hf_weights:
+            params = V.load_hf_vision_params(info.model_path, vis, mcfg.hidden_size)
+        else:
+            from ..loader.tensor_cache import TensorCache  # pylint: disable=import-outside-toplevel
+
+            cache = TensorCache(info.model_path)
+            params = {n: cache.get(n) for n in V.VisionTower.param_shapes(vis, mcfg.hidden_size)}
+        dtype = model.dtype if self.device.type == "cuda" else torch.float32
+        tower = V.VisionTower(vis, params, self.device, dtype,
+                              feature_layer=int(mcfg.extra.get("vision_feature_layer", -2)),
+                              select=mcfg.extra.get("vision_feature_select_strategy", "default"),
+                              projector_act=mcfg.extra.get("projector_hidden_act", "gelu"))
+        model.vision_tower = tower
+        model.image_embed = lambda pixels: tower.embed(pixels).to(model.dtype)
+
     def _build_models(self) -> None:
         cfg = self.engine_config
         comm = self.comm
@@ -290,6 +313,8 @@ class EngineRuntime:
             else:
                 store = model_loader.load_params(info.model_path, mcfg, quant, self.device, tp, tp_rank, layers)
             model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
+            if mi == 0 and mcfg.extra.get("vision"):
+                self._attach_vision_tower(model, info, mcfg)
             self.models.append(model)
             infos.append({
                 "params_bytes": store.nbytes(), "num_layers": mcfg.num_hidden_layers,

@@ -129,3 +129,39 @@ def test_serve_unconverted_hf_directory(hf_dir):
         assert resp.choices[0].text == tok.decode(want)
     finally:
         engine.terminate()
+
+
+def test_convert_weight_merges_a_lora_adapter(hf_dir, tmp_path):
+    """``--lora-adapter``: the PEFT-format low-rank updates are merged (W += alpha / r * B @ A) into the
+    tensors they target before q / k / v fusing; everything else is untouched."""
+    from safetensors.torch import save_file
+
+    src, hf_model, _ = hf_dir
+    adapter = tmp_path / "adapter"
+    adapter.mkdir()
+    g = torch.Generator().manual_seed(3)
+    r, alpha = 4, 8.0
+    a_q, b_q = torch.randn(r, 64, generator=g) * 0.1, torch.randn(64, r, generator=g) * 0.1
+    a_d, b_d = torch.randn(r, 128, generator=g) * 0.1, torch.randn(64, r, generator=g) * 0.1
+    save_file({"base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight": a_q,
+               "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight": b_q,
+               "base_model.model.model.layers.1.mlp.down_proj.lora_A.weight": a_d,
+               "base_model.model.model.layers.1.mlp.down_proj.lora_B.weight": b_d},
+              str(adapter / "adapter_model.safetensors"))
+    (adapter / "adapter_config.json").write_text(json.dumps(
+        {"peft_type": "LORA", "r": r, "lora_alpha": alpha, "target_modules": ["q_proj", "down_proj"]}))
+    out = str(tmp_path / "merged")
+    cli_convert.main([src, "--quantization", "q0f32", "--output", out, "--lora-adapter", str(adapter)])
+    cache = TensorCache(out)
+    sd = hf_model.state_dict()
+    scale = alpha / r
+    qkv = cache.get("model.layers.0.self_attn.qkv_proj.weight").float()
+    want_q = sd["model.layers.0.self_attn.q_proj.weight"] + scale * (b_q @ a_q)
+    assert torch.allclose(qkv[:64], want_q, atol=2e-2, rtol=1e-2)        # bf16 storage
+    assert torch.allclose(qkv[64:96], sd["model.layers.0.self_attn.k_proj.weight"], atol=2e-2, rtol=1e-2)
+    assert not torch.allclose(qkv[:64], sd["model.layers.0.self_attn.q_proj.weight"], atol=2e-2, rtol=1e-2)
+    down = cache.get("model.layers.1.mlp.down_proj.weight").float()
+    assert torch.allclose(down, sd["model.layers.1.mlp.down_proj.weight"] + scale * (b_d @ a_d), atol=2e-2,
+                          rtol=1e-2)
+    down0 = cache.get("model.layers.0.mlp.down_proj.weight").float()
+    assert torch.allclose(down0, sd["model.layers.0.mlp.down_proj.weight"], atol=2e-2, rtol=1e-2)
