@@ -158,6 +158,35 @@ def _gpt2(cfg: ModelConfig, m: Mapping) -> None:
     m.add("model.norm.bias", [pre + "ln_f.bias"])
 
 
+def _gptj(cfg: ModelConfig, m: Mapping) -> None:
+    """GPT-J rotates interleaved pairs (2i, 2i + 1); the kernels rotate (i, i + rotary_dim / 2).  Attention
+    scores do not change when q and k are permuted the same way, so the rows of ``q_proj`` / ``k_proj``
+    are reordered per head to [even rotary dims, odd rotary dims, the rest]."""
+    hq, d, rot = cfg.num_attention_heads, cfg.head_dim, cfg.rotary_dim
+    idx = torch.tensor(list(range(0, rot, 2)) + list(range(1, rot, 2)) + list(range(rot, d)))
+
+    def qkv(ts):
+        q, k, v = ts
+        perm = lambda w: w.view(hq, d, -1).index_select(1, idx).reshape(hq * d, -1)
+        return torch.cat([perm(q), perm(k), v], 0)
+
+    m.add("model.embed_tokens.weight", ["transformer.wte.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, dd = f"transformer.h.{i}.", f"model.layers.{i}."
+        m.add(dd + "input_layernorm.weight", [s + "ln_1.weight"])
+        m.add(dd + "input_layernorm.bias", [s + "ln_1.bias"])
+        m.add(dd + "self_attn.qkv_proj.weight",
+              [s + "attn.q_proj.weight", s + "attn.k_proj.weight", s + "attn.v_proj.weight"], qkv)
+        m.add(dd + "self_attn.o_proj.weight", [s + "attn.out_proj.weight"])
+        for suffix in ("weight", "bias"):
+            m.add(dd + f"mlp.up_proj.{suffix}", [s + f"mlp.fc_in.{suffix}"])
+            m.add(dd + f"mlp.down_proj.{suffix}", [s + f"mlp.fc_out.{suffix}"])
+    m.add("model.norm.weight", ["transformer.ln_f.weight"])
+    m.add("model.norm.bias", ["transformer.ln_f.bias"])
+    m.add("lm_head.weight", ["lm_head.weight"])
+    m.add("lm_head.bias", ["lm_head.bias"])
+
+
 def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
     """GPT-NeoX interleaves q, k, v per head inside ``query_key_value`` ([heads, 3, d, hidden]); they
     are regrouped into [q; k; v] (reference: ``model/gpt_neox/gpt_neox_loader.py``)."""
@@ -233,6 +262,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gpt2(cfg, m)
     elif mt == "gpt_neox":
         _gpt_neox(cfg, m)
+    elif mt in ("gptj", "gpt_j"):
+        _gptj(cfg, m)
     elif mt == "phi3":
         _phi3(cfg, m)
     elif mt in ("phi", "phi-msft"):

@@ -233,6 +233,19 @@ def _gpt_neox(cfg, mt):
     return d
 
 
+def _gptj(cfg, mt):
+    """GPT-J: one LayerNorm feeds attention and MLP in parallel, rotary embedding on the first
+    ``rotary_dim`` dimensions of every head (reference: ``python/mlc_llm/model/gpt_j/gpt_j_model.py``).
+    The checkpoint's interleaved rotary layout is converted to the half-split one when weights load."""
+    d = _common(cfg, mt)
+    head_dim = d["hidden_size"] // d["num_attention_heads"]
+    rot = int(_get(cfg, "rotary_dim", default=head_dim) or head_dim)
+    d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=False,
+             attention_out_bias=False, mlp_bias=True, parallel_residual=True, shared_input_norm=True,
+             partial_rotary_factor=rot / head_dim, lm_head_bias=True, tie_word_embeddings=False)
+    return d
+
+
 def _gpt2(cfg, mt):
     d = _common(cfg, mt)
     d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
@@ -372,7 +385,8 @@ def _llava(cfg, mt):
 _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
-    "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2,
+    "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
+    "gpt_j": _gptj,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _llama, "internlm2": _llama, "baichuan": _llama, "orion": _llama, "minicpm": _llama,

@@ -127,6 +127,8 @@ class DecoderModel:
             b = self.p.tensors.get(name + ".bias")
             if w is None:
                 w = torch.ones(x.shape[-1], dtype=x.dtype, device=x.device)
+            elif c.norm_weight_offset:
+                w = w + c.norm_weight_offset  # "LayerNorm1P": the stored weight is the deviation from one
             return ops.reference.layernorm(x, w, b, c.rms_norm_eps)
         return ops.rmsnorm(x, w, c.rms_norm_eps, c.norm_weight_offset)
 

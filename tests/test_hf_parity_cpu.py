@@ -28,6 +28,12 @@ CASES = {
     "gpt_neox": ("GPTNeoXConfig", dict(hidden_size=64, intermediate_size=256, num_hidden_layers=2,
                                        num_attention_heads=4, vocab_size=160, max_position_embeddings=128,
                                        rotary_pct=0.25)),
+    "gptj": ("GPTJConfig", dict(n_embd=64, n_layer=2, n_head=4, vocab_size=160, n_positions=128, rotary_dim=8)),
+    "nemotron": ("NemotronConfig", dict(BASE, head_dim=16)),
+    "olmo": ("OlmoConfig", dict(BASE)),
+    "gpt_bigcode": ("GPTBigCodeConfig", dict(n_embd=64, n_layer=2, n_head=4, vocab_size=160, n_positions=128,
+                                             multi_query=True)),
+    "gemma3_text": ("Gemma3TextConfig", dict(BASE, head_dim=16, query_pre_attn_scalar=16, sliding_window=4096)),
     "mixtral": ("MixtralConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                          shared_expert_intermediate_size=80, decoder_sparse_step=1,
