@@ -162,6 +162,32 @@ def _llama(cfg, mt):
     return d
 
 
+def _minicpm(cfg, mt):
+    """MiniCPM: Llama blocks with scaled embeddings, residual branches scaled by
+    ``scale_depth / sqrt(num_layers)`` and hidden states divided by ``hidden / dim_model_base`` before the
+    head (reference: ``python/mlc_llm/model/minicpm/minicpm_model.py:300-314,355-372,386``)."""
+    d = _llama(cfg, mt)
+    layers = int(d["num_hidden_layers"])
+    d["embedding_scale"] = float(_get(cfg, "scale_emb", default=1))
+    width = max(1, int(d["hidden_size"]) // int(_get(cfg, "dim_model_base", default=d["hidden_size"])))
+    d["extra"] = {"residual_scale": float(_get(cfg, "scale_depth", default=1.0)) / math.sqrt(layers),
+                  "logit_scale": 1.0 / width}
+    return d
+
+
+def _internlm(cfg, mt):
+    d = _llama(cfg, mt)
+    if "bias" in cfg and "attention_bias" not in cfg:  # InternLM spells the q/k/v/o bias switch "bias"
+        d["attention_bias"] = d["attention_out_bias"] = bool(cfg["bias"])
+    return d
+
+
+def _orion(cfg, mt):
+    d = _llama(cfg, mt)
+    d["norm_type"] = "layernorm"  # reference: python/mlc_llm/model/orion/orion_model.py:149-150,195
+    return d
+
+
 def _mistral(cfg, mt):
     d = _common(cfg, mt)
     sw = _get(cfg, "sliding_window")
@@ -389,7 +415,7 @@ _PARSERS = {
     "gpt_j": _gptj,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
-    "internlm": _llama, "internlm2": _llama, "baichuan": _llama, "orion": _llama, "minicpm": _llama,
+    "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,
     "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
     "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,

@@ -224,7 +224,7 @@ class DecoderModel:
         c = self.cfg
         plain = (c.norm_type == "rms" and not c.parallel_residual and not c.post_attention_norm
                  and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
-                 and c.gated_mlp and c.position_embedding != "learned"
+                 and c.gated_mlp and c.position_embedding != "learned" and "residual_scale" not in c.extra
                  and self.first_stage and self.last_stage and self.dtype in (torch.float16, torch.bfloat16))
         self.fused = fused if plain else None
         return self.fused is not None
@@ -272,6 +272,7 @@ class DecoderModel:
             x = x + self.p.tensors["model.embed_positions.weight"][b.positions.long()].to(x.dtype)
         x = x.contiguous()
         no_pre_norm = bool(c.extra.get("no_pre_norm"))
+        rs = float(c.extra.get("residual_scale", 1.0))  # MiniCPM scales every residual branch
         pending = None  # branch output not yet added to the residual stream
         for li in self.layers:
             pre = f"model.layers.{li}."
@@ -299,6 +300,8 @@ class DecoderModel:
                 h = self._add_norm(pending, x, pre + "input_layernorm")
                 pending = None
             attn = self._reduce(self._attention(li, h, b))
+            if rs != 1.0:
+                attn = attn * rs
             if c.post_attention_norm:
                 attn = self._norm(attn, pre + ("post_attention_layernorm" if (c.post_mlp_norm)
                                                else "post_attention_norm"))
@@ -315,6 +318,8 @@ class DecoderModel:
                 self._mlp_complete = False
             else:
                 mlp = self._reduce(mlp)
+            if rs != 1.0:
+                mlp = mlp * rs
             if c.post_mlp_norm:
                 mlp = self._norm(mlp, pre + "post_feedforward_layernorm")
             pending = mlp

@@ -1,0 +1,59 @@
+"""Architecture switches that have no HuggingFace counterpart installed: checked through algebraic
+identities against the plain Llama forward."""
+import math
+
+import numpy as np
+import torch
+
+from mlc_llm_b200 import _core
+from mlc_llm_b200 import quantization as Q
+from mlc_llm_b200.models import config as mc
+from mlc_llm_b200.models import loader
+from mlc_llm_b200.models.transformer import BatchInfo, DecoderModel
+
+BASE = dict(hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, vocab_size=160, max_position_embeddings=128, rms_norm_eps=1e-5)
+
+
+def _logits(model, toks):
+    model.create_kv_cache(8, 16)
+    kv = _core.KVManager(8, 16, 2)
+    kv.add_sequence(0)
+    plan = kv.begin_forward([0], [len(toks)])
+    t = lambda k: torch.from_numpy(np.asarray(plan[k])).to(torch.int32)
+    b = BatchInfo(positions=t("positions"), slots=t("slots"), q_seq=t("q_seq"), q_kvlen=t("q_kvlen"),
+                  page_indptr=t("page_indptr"), page_indices=t("page_indices"), num_tokens=len(toks))
+    h = model.forward(model.embed(torch.tensor(toks, dtype=torch.int32)), b)
+    return model.logits(h, None).float()
+
+
+def test_minicpm_scaling_equals_llama_with_rescaled_weights():
+    """embedding x scale_emb, residual branches x scale_depth / sqrt(L), hidden / (hidden / dim_model_base)
+    before the head: the same function as a Llama whose embedding, o_proj / down_proj and lm_head
+    weights carry those factors."""
+    quant = Q.get("q0f32")
+    cpm = mc.from_dict("minicpm", dict(BASE, scale_emb=12, scale_depth=1.4, dim_model_base=16))
+    assert cpm.embedding_scale == 12 and math.isclose(cpm.extra["residual_scale"], 1.4 / math.sqrt(2))
+    assert math.isclose(cpm.extra["logit_scale"], 1 / 4)
+    llama = mc.from_dict("llama", dict(BASE))
+    store = loader.random_params(cpm, quant, 7, torch.device("cpu"), std=0.2)
+    ref_store = loader.random_params(llama, quant, 7, torch.device("cpu"), std=0.2)
+    rs = cpm.extra["residual_scale"]
+    ref_store.tensors["model.embed_tokens.weight"] = ref_store.tensors["model.embed_tokens.weight"] * 12
+    for i in range(2):
+        for name in (f"model.layers.{i}.self_attn.o_proj", f"model.layers.{i}.mlp.down_proj"):
+            ref_store.linears[name].w = ref_store.linears[name].w * rs
+    ref_store.linears["lm_head"].w = ref_store.linears["lm_head"].w / 4
+    toks = [3, 17, 42, 99, 5, 8]
+    got = _logits(DecoderModel(cpm, quant, store, torch.device("cpu")), toks)
+    want = _logits(DecoderModel(llama, quant, ref_store, torch.device("cpu")), toks)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), (got - want).abs().max()
+    plain = _logits(DecoderModel(llama, quant, loader.random_params(llama, quant, 7, torch.device("cpu"), std=0.2),
+                                 torch.device("cpu")), toks)
+    assert not torch.allclose(got, plain, atol=1e-2)
+
+
+def test_internlm_bias_and_orion_layernorm_switches():
+    assert mc.from_dict("internlm", dict(BASE, bias=True)).attention_bias
+    assert not mc.from_dict("internlm", dict(BASE, bias=False)).attention_bias
+    assert mc.from_dict("orion", dict(BASE)).norm_type == "layernorm"
