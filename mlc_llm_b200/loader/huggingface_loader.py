@@ -118,9 +118,10 @@ def _moe_layers(cfg: ModelConfig, m: Mapping, style: str) -> None:
         m.add(d + "e1_e3.weight", srcs13, stack13)
         m.add(d + "e2.weight", [f"{s}experts.{j}.{dn}.weight" for j in range(e)], stack)
         if cfg.shared_expert_intermediate_size > 0:
+            se = "shared_experts" if style == "deepseek" else "shared_expert"
             m.add(d + "shared_expert.gate_up_proj.weight",
-                  [s + "shared_expert.gate_proj.weight", s + "shared_expert.up_proj.weight"], _cat0)
-            m.add(d + "shared_expert.down_proj.weight", [s + "shared_expert.down_proj.weight"])
+                  [s + se + ".gate_proj.weight", s + se + ".up_proj.weight"], _cat0)
+            m.add(d + "shared_expert.down_proj.weight", [s + se + ".down_proj.weight"])
             if cfg.shared_expert_gate:
                 m.add(d + "shared_expert_gate.weight", [s + "shared_expert_gate.weight"])
 
@@ -185,6 +186,39 @@ def _gptj(cfg: ModelConfig, m: Mapping) -> None:
     m.add("model.norm.bias", ["transformer.ln_f.bias"])
     m.add("lm_head.weight", ["lm_head.weight"])
     m.add("lm_head.bias", ["lm_head.bias"])
+
+
+def _deepseek_v2(cfg: ModelConfig, m: Mapping) -> None:
+    """Multi-head latent attention tensors.  The checkpoint rotates interleaved pairs of the rotary part
+    and puts it last in every head; the kernels rotate half-split pairs of the first ``rotary_dim``
+    dimensions, so the rotary rows are de-interleaved and moved to the front of every q head, and
+    de-interleaved in place in ``kv_a_proj_with_mqa`` (a permutation shared by q and k leaves the scores
+    unchanged)."""
+    mla = cfg.extra["mla"]
+    hq, nope, rope, rank = cfg.num_attention_heads, mla["qk_nope_head_dim"], mla["qk_rope_head_dim"], mla["kv_lora_rank"]
+    deint = list(range(0, rope, 2)) + list(range(1, rope, 2))
+    q_idx = torch.tensor([nope + j for j in deint] + list(range(nope)))
+    kv_idx = torch.tensor(list(range(rank)) + [rank + j for j in deint])
+
+    def q_rows(ts):
+        w = ts[0]
+        return w.view(hq, nope + rope, -1).index_select(1, q_idx).reshape(hq * (nope + rope), -1)
+
+    _llama_like(cfg, m)
+    for i in range(cfg.num_hidden_layers):
+        s = d = f"model.layers.{i}.self_attn."
+        if mla.get("q_lora_rank"):
+            m.add(d + "q_a_proj.weight", [s + "q_a_proj.weight"])
+            m.add(d + "q_a_layernorm.weight", [s + "q_a_layernorm.weight"])
+            m.add(d + "q_b_proj.weight", [s + "q_b_proj.weight"], q_rows)
+        else:
+            m.add(d + "q_proj.weight", [s + "q_proj.weight"], q_rows)
+        m.add(d + "kv_a_proj_with_mqa.weight", [s + "kv_a_proj_with_mqa.weight"],
+              lambda ts: ts[0].index_select(0, kv_idx))
+        m.add(d + "kv_a_layernorm.weight", [s + "kv_a_layernorm.weight"])
+        m.add(d + "kv_b_proj.weight", [s + "kv_b_proj.weight"])
+        m.add(d + "o_proj.weight", [s + "o_proj.weight"])
+    _moe_layers(cfg, m, "deepseek")
 
 
 def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
@@ -280,6 +314,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
     elif mt in ("qwen2_moe", "qwen3_moe"):
         _llama_like(cfg, m)
         _moe_layers(cfg, m, "qwen")
+    elif mt == "deepseek_v2":
+        _deepseek_v2(cfg, m)
     elif mt == "eagle":
         # EAGLE checkpoints name their tensors without the "model." prefix; the resolver tries both
         _llama_like(cfg, m)

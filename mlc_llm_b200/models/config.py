@@ -336,6 +336,40 @@ def _qwen_moe(cfg, mt):
     return d
 
 
+def _deepseek_v2(cfg, mt):
+    """DeepSeek-V2: multi-head latent attention (queries and keys are a no-position part plus a rotary
+    part shared by all heads; keys / values are expanded from a low-rank latent) and a mixture of
+    experts with shared experts and group-limited routing (reference:
+    ``python/mlc_llm/model/deepseek_v2/deepseek_v2_model.py``).  Here every head's q / k is laid out as
+    [rotary | no-position] and values are padded to that width, so the paged attention kernels see a
+    plain multi-head problem; the latent is expanded before it is cached."""
+    d = _common(cfg, mt)
+    nope = int(_get(cfg, "qk_nope_head_dim", default=128))
+    rope = int(_get(cfg, "qk_rope_head_dim", default=64))
+    d["head_dim"] = nope + rope
+    d["num_key_value_heads"] = d["num_attention_heads"]
+    d["partial_rotary_factor"] = rope / (nope + rope)
+    scaling = d.get("rope_scaling")
+    if isinstance(scaling, dict) and scaling.get("rope_type", scaling.get("type", "default")) not in ("default", "linear"):
+        raise ValueError("DeepSeek-V2 rotary scaling other than linear is not supported")
+    routed = int(_get(cfg, "n_routed_experts", default=0) or 0)
+    shared = int(_get(cfg, "n_shared_experts", default=0) or 0)
+    moe_inter = int(_get(cfg, "moe_intermediate_size", default=1407))
+    d.update(num_experts=routed, num_experts_per_tok=int(_get(cfg, "num_experts_per_tok", default=6) or 0),
+             moe_intermediate_size=moe_inter, norm_topk_prob=bool(_get(cfg, "norm_topk_prob", default=False)),
+             moe_router="softmax_topk", shared_expert_intermediate_size=moe_inter * shared,
+             first_moe_layer=int(_get(cfg, "first_k_dense_replace", default=0)),
+             moe_layer_freq=int(_get(cfg, "moe_layer_freq", default=1)))
+    d["extra"] = {"mla": {"q_lora_rank": _get(cfg, "q_lora_rank"), "kv_lora_rank": int(_get(cfg, "kv_lora_rank", default=512)),
+                          "qk_nope_head_dim": nope, "qk_rope_head_dim": rope,
+                          "v_head_dim": int(_get(cfg, "v_head_dim", default=128))},
+                  "routed_scaling_factor": float(_get(cfg, "routed_scaling_factor", default=1.0)),
+                  "topk_method": _get(cfg, "topk_method", default="greedy"),
+                  "n_group": int(_get(cfg, "n_group", default=1) or 1),
+                  "topk_group": int(_get(cfg, "topk_group", default=1) or 1)}
+    return d
+
+
 def _nemotron(cfg, mt):
     d = _common(cfg, mt)
     d.update(norm_type="layernorm", norm_weight_offset=1.0, hidden_act="relu2", gated_mlp=False,
@@ -416,7 +450,7 @@ _PARSERS = {
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,
-    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
+    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "deepseek_v2": _deepseek_v2, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
     "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,
 }

@@ -14,6 +14,20 @@ import torch
 from .. import ops
 
 
+def _group_limited_router(logits: torch.Tensor, k: int, n_group: int, topk_group: int, renorm: bool):
+    """DeepSeek-V2 routing: softmax over all experts, keep the ``topk_group`` expert groups with the
+    best single score, then the top ``k`` experts inside them (reference: ``op/moe_misc.py:238-368``)."""
+    t, e = logits.shape
+    probs = torch.softmax(logits.float(), dim=-1)
+    group_best = probs.view(t, n_group, e // n_group).max(dim=-1).values
+    keep = torch.zeros_like(group_best).scatter_(1, torch.topk(group_best, topk_group, dim=-1).indices, 1.0)
+    masked = probs.masked_fill(keep.unsqueeze(-1).expand(t, n_group, e // n_group).reshape(t, e) == 0, 0.0)
+    w, idx = torch.topk(masked, k, dim=-1)
+    if renorm:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w.to(logits.dtype if logits.dtype != torch.float32 else torch.float32), idx.to(torch.int32)
+
+
 def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
     c = model.cfg
     pre = f"model.layers.{li}.moe."
@@ -22,7 +36,13 @@ def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
     gate_w = model.p.tensors[pre + "gate.weight"]
     logits = ops.linear(h, ops.dense_weight(gate_w))
     renorm = c.norm_topk_prob if c.moe_router == "softmax_topk" else True
-    weights, experts = ops.moe_router(logits, k, renorm)
+    if c.extra.get("topk_method") == "group_limited_greedy" and c.extra.get("n_group", 1) > 1:
+        weights, experts = _group_limited_router(logits, k, c.extra["n_group"], c.extra["topk_group"], renorm)
+    else:
+        weights, experts = ops.moe_router(logits, k, renorm)
+    scale = float(c.extra.get("routed_scaling_factor", 1.0))
+    if scale != 1.0:
+        weights = weights * scale
     w13 = model.p.linears[pre + "e1_e3"]
     w2 = model.p.linears[pre + "e2"]
     if c.expert_parallel and model.comm is not None and model.tp > 1:

@@ -147,7 +147,36 @@ class DecoderModel:
         x = ops.embed(token_ids, table, c.hidden_size, self.dtype, c.embedding_scale)
         return x  # learned positions are added in forward(), where positions are known
 
+    def _attention_mla(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        """Multi-head latent attention with the latent expanded before caching: q / k heads are
+        [rotary | no-position] (the rotary key part is shared by all heads), values are zero-padded to
+        the q / k width, and the paged kernels run an ordinary multi-head problem."""
+        c, m = self.cfg, self.cfg.extra["mla"]
+        if self.tp > 1:
+            raise NotImplementedError("multi-head latent attention is not sharded across ranks yet")
+        pre = f"model.layers.{li}.self_attn."
+        t = h.shape[0]
+        hq, d = self.hq, self.d
+        nope, rope, vd, rank = m["qk_nope_head_dim"], m["qk_rope_head_dim"], m["v_head_dim"], m["kv_lora_rank"]
+        if m.get("q_lora_rank"):
+            qa = ops.linear(h, self.p.linears[pre + "q_a_proj"])
+            qa = ops.rmsnorm(qa, self.p.tensors[pre + "q_a_layernorm.weight"], c.rms_norm_eps, 0.0)
+            q = ops.linear(qa, self.p.linears[pre + "q_b_proj"])
+        else:
+            q = ops.linear(h, self.p.linears[pre + "q_proj"])
+        ckv = ops.linear(h, self.p.linears[pre + "kv_a_proj_with_mqa"])
+        latent = ops.rmsnorm(ckv[:, :rank].contiguous(), self.p.tensors[pre + "kv_a_layernorm.weight"],
+                             c.rms_norm_eps, 0.0)
+        kv = ops.linear(latent, self.p.linears[pre + "kv_b_proj"]).view(t, hq, nope + vd)
+        k = torch.cat([ckv[:, rank:].unsqueeze(1).expand(t, hq, rope), kv[..., :nope]], dim=-1)
+        v = torch.nn.functional.pad(kv[..., nope:], (0, d - vd))
+        qkv = torch.cat([q.view(t, hq, d), k, v], dim=1).reshape(t, 3 * hq * d).contiguous()
+        ctx = self._attention_core(li, qkv, b).view(t, hq, d)[..., :vd].reshape(t, hq * vd).contiguous()
+        return ops.linear(ctx, self.p.linears[pre + "o_proj"])
+
     def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        if self.cfg.extra.get("mla"):
+            return self._attention_mla(li, h, b)
         pre = f"model.layers.{li}.self_attn."
         qkv = ops.linear(h, self.p.linears[pre + "qkv_proj"])
         return ops.linear(self._attention_core(li, qkv, b), self.p.linears[pre + "o_proj"])
@@ -225,6 +254,7 @@ class DecoderModel:
         plain = (c.norm_type == "rms" and not c.parallel_residual and not c.post_attention_norm
                  and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
                  and c.gated_mlp and c.position_embedding != "learned" and "residual_scale" not in c.extra
+                 and "mla" not in c.extra
                  and self.first_stage and self.last_stage and self.dtype in (torch.float16, torch.bfloat16))
         self.fused = fused if plain else None
         return self.fused is not None
@@ -431,10 +461,25 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
         p = f"model.layers.{i}."
         if not cfg.extra.get("no_pre_norm") and not (eagle and i == 0):
             norm(p + "input_layernorm")
-        specs[p + "self_attn.qkv_proj.weight"] = (((hq + 2 * hkv) * d, h), "linear")
-        if cfg.attention_bias:
-            specs[p + "self_attn.qkv_proj.bias"] = (((hq + 2 * hkv) * d,), "bias")
-        specs[p + "self_attn.o_proj.weight"] = ((h, hq * d), "linear")
+        mla = cfg.extra.get("mla")
+        if mla:
+            qk = mla["qk_nope_head_dim"] + mla["qk_rope_head_dim"]
+            if mla.get("q_lora_rank"):
+                specs[p + "self_attn.q_a_proj.weight"] = ((mla["q_lora_rank"], h), "linear")
+                specs[p + "self_attn.q_a_layernorm.weight"] = ((mla["q_lora_rank"],), "norm")
+                specs[p + "self_attn.q_b_proj.weight"] = ((hq * qk, mla["q_lora_rank"]), "linear")
+            else:
+                specs[p + "self_attn.q_proj.weight"] = ((hq * qk, h), "linear")
+            specs[p + "self_attn.kv_a_proj_with_mqa.weight"] = ((mla["kv_lora_rank"] + mla["qk_rope_head_dim"], h), "linear")
+            specs[p + "self_attn.kv_a_layernorm.weight"] = ((mla["kv_lora_rank"],), "norm")
+            specs[p + "self_attn.kv_b_proj.weight"] = ((hq * (mla["qk_nope_head_dim"] + mla["v_head_dim"]),
+                                                        mla["kv_lora_rank"]), "linear")
+            specs[p + "self_attn.o_proj.weight"] = ((h, hq * mla["v_head_dim"]), "linear")
+        else:
+            specs[p + "self_attn.qkv_proj.weight"] = (((hq + 2 * hkv) * d, h), "linear")
+            if cfg.attention_bias:
+                specs[p + "self_attn.qkv_proj.bias"] = (((hq + 2 * hkv) * d,), "bias")
+            specs[p + "self_attn.o_proj.weight"] = ((h, hq * d), "linear")
         if cfg.attention_out_bias:
             specs[p + "self_attn.o_proj.bias"] = ((h,), "bias")
         if cfg.qk_norm:

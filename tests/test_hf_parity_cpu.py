@@ -34,6 +34,12 @@ CASES = {
     "gpt_bigcode": ("GPTBigCodeConfig", dict(n_embd=64, n_layer=2, n_head=4, vocab_size=160, n_positions=128,
                                              multi_query=True)),
     "gemma3_text": ("Gemma3TextConfig", dict(BASE, head_dim=16, query_pre_attn_scalar=16, sliding_window=4096)),
+    "deepseek_v2": ("DeepseekV2Config", dict(
+        hidden_size=64, intermediate_size=112, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+        vocab_size=160, max_position_embeddings=128, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16,
+        qk_rope_head_dim=16, v_head_dim=16, head_dim=16, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=3,
+        moe_intermediate_size=24, first_k_dense_replace=1, topk_method="greedy", n_group=4,
+        topk_group=2, routed_scaling_factor=1.5, norm_topk_prob=False)),
     "mixtral": ("MixtralConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                          shared_expert_intermediate_size=80, decoder_sparse_step=1,
