@@ -206,19 +206,28 @@ Request MakeRequest(const std::string& id, const py::list& inputs, const Generat
   return r;
 }
 
-py::dict OutputToDict(const RequestStreamOutput& o) {
-  py::dict d;
-  d["request_id"] = o.request_id;
-  d["group_delta_token_ids"] = o.group_delta_token_ids;
-  d["group_delta_logprob_json_strs"] = o.group_delta_logprob_json_strs;
-  py::list fr;
-  for (auto& s : o.group_finish_reason) fr.append(s.empty() ? py::object(py::none()) : py::object(py::str(s)));
-  d["group_finish_reason"] = fr;
-  d["group_extra_prefix_string"] = o.group_extra_prefix_string;
-  d["request_final_usage_json_str"] =
-      o.request_final_usage_json_str.empty() ? py::object(py::none()) : py::object(py::str(o.request_final_usage_json_str));
-  return d;
+// One field of a stream output as a Python object. Outputs cross into Python as thin wrappers and are
+// converted field by field on access: a decode step of a large batch emits hundreds of them, and most
+// consumers read one or two fields.
+py::object OutputField(const RequestStreamOutput& o, const std::string& key) {
+  if (key == "request_id") return py::str(o.request_id);
+  if (key == "group_delta_token_ids") return py::cast(o.group_delta_token_ids);
+  if (key == "group_delta_logprob_json_strs") return py::cast(o.group_delta_logprob_json_strs);
+  if (key == "group_finish_reason") {
+    py::list fr;
+    for (auto& s : o.group_finish_reason) fr.append(s.empty() ? py::object(py::none()) : py::object(py::str(s)));
+    return std::move(fr);
+  }
+  if (key == "group_extra_prefix_string") return py::cast(o.group_extra_prefix_string);
+  if (key == "request_final_usage_json_str")
+    return o.request_final_usage_json_str.empty() ? py::object(py::none())
+                                                  : py::object(py::str(o.request_final_usage_json_str));
+  throw py::key_error(key);
 }
+
+const char* const kOutputKeys[] = {"request_id", "group_delta_token_ids", "group_delta_logprob_json_strs",
+                                   "group_finish_reason", "group_extra_prefix_string",
+                                   "request_final_usage_json_str"};
 
 StreamCallback WrapCallback(py::object fn) {
   if (fn.is_none()) return nullptr;
@@ -226,7 +235,7 @@ StreamCallback WrapCallback(py::object fn) {
   return [holder](std::vector<RequestStreamOutput> outs) {
     py::gil_scoped_acquire gil;
     py::list lst;
-    for (auto& o : outs) lst.append(OutputToDict(o));
+    for (auto& o : outs) lst.append(py::cast(std::move(o)));
     (*holder)(lst);
   };
 }
@@ -287,6 +296,30 @@ class ProxyEngine : public Engine {
 }  // namespace
 
 PYBIND11_MODULE(_core, m) {
+  // ---------------------------------------------------------------- stream outputs (dict-like, lazy)
+  py::class_<RequestStreamOutput>(m, "StreamOutput")
+      .def("__getitem__", [](const RequestStreamOutput& o, const std::string& key) { return OutputField(o, key); })
+      .def("__contains__", [](const RequestStreamOutput&, const std::string& key) {
+        for (const char* k : kOutputKeys)
+          if (key == k) return true;
+        return false;
+      })
+      .def("get", [](const RequestStreamOutput& o, const std::string& key, py::object dflt) {
+        for (const char* k : kOutputKeys)
+          if (key == k) return OutputField(o, key);
+        return dflt;
+      }, py::arg("key"), py::arg("default") = py::none())
+      .def("keys", []() {
+        py::list out;
+        for (const char* k : kOutputKeys) out.append(py::str(k));
+        return out;
+      })
+      .def("asdict", [](const RequestStreamOutput& o) {
+        py::dict d;
+        for (const char* k : kOutputKeys) d[py::str(k)] = OutputField(o, k);
+        return d;
+      });
+
   m.doc() = "Native serving runtime of mlc_llm_b200";
 
   // ---------------------------------------------------------------- radix tree / prefix cache

@@ -124,6 +124,14 @@ class EngineImpl : public Engine {
     o["kv_available_pages"] = kv_[0]->NumAvailablePages();
     o["kv_total_sequence_length"] = kv_[0]->TotalSequenceLength();
     o["prefix_cache_recycling"] = prefix_cache_.NumRecycling();
+    // host seconds spent per phase of decode steps (profiling aid)
+    Object t;
+    t["assemble"] = t_assemble_;
+    t["plan"] = t_plan_;
+    t["backend"] = t_backend_;
+    t["commit"] = t_commit_;
+    t["postprocess"] = t_post_;
+    o["decode_host_seconds"] = Value(std::move(t));
     return Value(std::move(o)).dump();
   }
 
@@ -388,7 +396,11 @@ class EngineImpl : public Engine {
       if (spec_) did = StepSpecDecode();
       else did = StepDecode();
     }
-    if (did) PostProcess();
+    if (did) {
+      const double t0 = NowSeconds();
+      PostProcess();
+      t_post_ += NowSeconds() - t0;
+    }
   }
 
  private:
@@ -900,12 +912,19 @@ class EngineImpl : public Engine {
       token_ids.push_back(e.committed_tokens.back().token);
       AddSampleRow(&sp, ready[i], static_cast<int32_t>(i));
     }
+    const double ta = NowSeconds();
     ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens);
+    const double tb = NowSeconds();
     SampleOutput out = backend_->ForwardSample(0, plan, token_ids, embed_handles, sp);
+    const double tc = NowSeconds();
     for (size_t i = 0; i < ready.size(); ++i) {
       ready[i].rs->metrics.decode_tokens += 1;
       CommitToken(ready[i], RowResult(out, static_cast<int>(i), sp.num_top_logprobs, ready[i].rs->request.cfg));
     }
+    t_assemble_ += ta - t0;
+    t_plan_ += tb - ta;
+    t_backend_ += tc - tb;
+    t_commit_ += NowSeconds() - tc;
     TraceBatch(ready, "finish decode");
     ++num_decode_steps_;
     const double dt = NowSeconds() - t0;
@@ -1363,6 +1382,7 @@ class EngineImpl : public Engine {
   SlotManager draft_slots_;
   EngineMetrics metrics_;
   std::mt19937_64 seed_rng_;
+  double t_assemble_ = 0, t_plan_ = 0, t_backend_ = 0, t_commit_ = 0, t_post_ = 0;
   bool spec_ = false;
   bool feature_fed_draft_ = false;  // EAGLE / Medusa: the draft head consumes the target's hidden states
   int64_t num_prefill_steps_ = 0, num_decode_steps_ = 0, num_verify_steps_ = 0, num_preemptions_ = 0;

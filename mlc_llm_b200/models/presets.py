@@ -31,6 +31,17 @@ MODEL_PRESETS = {
                           "num_attention_heads": 4, "image_size": 28, "patch_size": 14,
                           "hidden_act": "quick_gelu", "layer_norm_eps": 1e-5},
     },
+    # 3-layer DeepSeek-V2-shaped model: latent attention (128 + 64 wide heads), one dense layer, then
+    # layers with 8 routed experts (4 groups) and 2 shared experts
+    "tiny-deepseek-v2": {
+        "model_type": "deepseek_v2", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 3,
+        "num_attention_heads": 4, "num_key_value_heads": 4, "vocab_size": 32000, "rms_norm_eps": 1e-6,
+        "rope_theta": 10000.0, "max_position_embeddings": 4096, "q_lora_rank": None, "kv_lora_rank": 128,
+        "qk_nope_head_dim": 128, "qk_rope_head_dim": 64, "v_head_dim": 128, "n_routed_experts": 8,
+        "n_shared_experts": 2, "num_experts_per_tok": 2, "moe_intermediate_size": 256,
+        "first_k_dense_replace": 1, "topk_method": "group_limited_greedy", "n_group": 4, "topk_group": 2,
+        "routed_scaling_factor": 1.0, "norm_topk_prob": False,
+    },
     # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
     "tiny-llama-gpu": {
         "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
