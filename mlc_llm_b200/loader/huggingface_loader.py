@@ -221,6 +221,58 @@ def _deepseek_v2(cfg: ModelConfig, m: Mapping) -> None:
     _moe_layers(cfg, m, "deepseek")
 
 
+def _deinterleave_rows(cfg: ModelConfig, heads: int):
+    """Row permutation of a [heads * d, ...] projection that turns interleaved rotary pairs (2i, 2i + 1)
+    of the first ``rotary_dim`` dimensions of every head into half-split pairs (i, i + rotary_dim / 2)."""
+    d, rot = cfg.head_dim, cfg.rotary_dim
+    idx = torch.tensor(list(range(0, rot, 2)) + list(range(1, rot, 2)) + list(range(rot, d)))
+
+    def perm(w: torch.Tensor) -> torch.Tensor:
+        return w.reshape(heads, d, -1).index_select(1, idx).reshape(w.shape)
+
+    return perm
+
+
+def _glm(cfg: ModelConfig, m: Mapping) -> None:
+    """HuggingFace ``glm``: Llama names with a fused ``gate_up_proj``; rotary rows de-interleaved."""
+    pq, pk = _deinterleave_rows(cfg, cfg.num_attention_heads), _deinterleave_rows(cfg, cfg.num_key_value_heads)
+    _llama_like(cfg, m)
+    for i in range(cfg.num_hidden_layers):
+        s = d = f"model.layers.{i}."
+        for suffix in ("weight", "bias"):
+            m.add(d + f"self_attn.qkv_proj.{suffix}",
+                  [s + f"self_attn.q_proj.{suffix}", s + f"self_attn.k_proj.{suffix}", s + f"self_attn.v_proj.{suffix}"],
+                  lambda ts: torch.cat([pq(ts[0]), pk(ts[1]), ts[2]], 0))
+        m.add(d + "mlp.gate_up_proj.weight", [s + "mlp.gate_up_proj.weight"])
+
+
+def _chatglm(cfg: ModelConfig, m: Mapping) -> None:
+    """ChatGLM3 checkpoints: ``query_key_value`` is [q; k; v] and ``dense_h_to_4h`` is [gate; up]
+    (reference: ``python/mlc_llm/model/chatglm3/chatglm3_loader.py``)."""
+    hq, hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    pq, pk = _deinterleave_rows(cfg, hq), _deinterleave_rows(cfg, hkv)
+
+    def qkv(ts):
+        w = ts[0]
+        q, k, v = w[: hq * hd], w[hq * hd: (hq + hkv) * hd], w[(hq + hkv) * hd:]
+        return torch.cat([pq(q), pk(k), v], 0)
+
+    pre = "transformer.encoder."
+    m.add("model.embed_tokens.weight", ["transformer.embedding.word_embeddings.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, d = f"{pre}layers.{i}.", f"model.layers.{i}."
+        m.add(d + "input_layernorm.weight", [s + "input_layernorm.weight"])
+        m.add(d + "post_attention_layernorm.weight", [s + "post_attention_layernorm.weight"])
+        m.add(d + "self_attn.qkv_proj.weight", [s + "self_attention.query_key_value.weight"], qkv)
+        if cfg.attention_bias:
+            m.add(d + "self_attn.qkv_proj.bias", [s + "self_attention.query_key_value.bias"], qkv)
+        m.add(d + "self_attn.o_proj.weight", [s + "self_attention.dense.weight"])
+        m.add(d + "mlp.gate_up_proj.weight", [s + "mlp.dense_h_to_4h.weight"])
+        m.add(d + "mlp.down_proj.weight", [s + "mlp.dense_4h_to_h.weight"])
+    m.add("model.norm.weight", [pre + "final_layernorm.weight"])
+    m.add("lm_head.weight", ["transformer.output_layer.weight"])
+
+
 def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
     """GPT-NeoX interleaves q, k, v per head inside ``query_key_value`` ([heads, 3, d, hidden]); they
     are regrouped into [q; k; v] (reference: ``model/gpt_neox/gpt_neox_loader.py``)."""
@@ -298,6 +350,10 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gpt_neox(cfg, m)
     elif mt in ("gptj", "gpt_j"):
         _gptj(cfg, m)
+    elif mt == "glm":
+        _glm(cfg, m)
+    elif mt == "chatglm":
+        _chatglm(cfg, m)
     elif mt == "phi3":
         _phi3(cfg, m)
     elif mt in ("phi", "phi-msft"):

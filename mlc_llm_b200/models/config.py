@@ -272,6 +272,31 @@ def _gptj(cfg, mt):
     return d
 
 
+def _glm(cfg, mt):
+    """GLM-4 (HuggingFace ``glm``) and ChatGLM3: RMSNorm Llama-style blocks with q/k/v bias and rotary
+    embedding on the first half of every head, stored interleaved in the checkpoint (reference:
+    ``python/mlc_llm/model/chatglm3/chatglm3_model.py``)."""
+    if mt == "chatglm":
+        cfg = dict(cfg)
+        ren = {"num_layers": "num_hidden_layers", "multi_query_group_num": "num_key_value_heads",
+               "kv_channels": "head_dim", "ffn_hidden_size": "intermediate_size",
+               "layernorm_epsilon": "rms_norm_eps", "padded_vocab_size": "vocab_size",
+               "seq_length": "max_position_embeddings"}
+        for old, new in ren.items():
+            if old in cfg and new not in cfg:
+                cfg[new] = cfg[old]
+        if not cfg.get("multi_query_attention", True):
+            cfg["num_key_value_heads"] = cfg["num_attention_heads"]
+        cfg.setdefault("rope_theta", 10000.0 * float(cfg.get("rope_ratio", 1.0)))
+        cfg.setdefault("attention_bias", bool(cfg.get("add_qkv_bias", True)))
+    d = _common(cfg, mt)
+    d["attention_bias"] = bool(_get(cfg, "attention_bias", default=True))
+    d["attention_out_bias"] = False
+    d["partial_rotary_factor"] = float(_get(cfg, "partial_rotary_factor", default=0.5))
+    d["extra"] = {"rope_interleaved_in_checkpoint": True}
+    return d
+
+
 def _gpt2(cfg, mt):
     d = _common(cfg, mt)
     d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
@@ -446,7 +471,7 @@ _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
-    "gpt_j": _gptj,
+    "gpt_j": _gptj, "glm": _glm, "chatglm": _glm,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,

@@ -40,6 +40,7 @@ CASES = {
         qk_rope_head_dim=16, v_head_dim=16, head_dim=16, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=3,
         moe_intermediate_size=24, first_k_dense_replace=1, topk_method="greedy", n_group=4,
         topk_group=2, routed_scaling_factor=1.5, norm_topk_prob=False)),
+    "glm": ("GlmConfig", dict(BASE, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)),
     "mixtral": ("MixtralConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                          shared_expert_intermediate_size=80, decoder_sparse_step=1,

@@ -57,3 +57,54 @@ def test_internlm_bias_and_orion_layernorm_switches():
     assert mc.from_dict("internlm", dict(BASE, bias=True)).attention_bias
     assert not mc.from_dict("internlm", dict(BASE, bias=False)).attention_bias
     assert mc.from_dict("orion", dict(BASE)).norm_type == "layernorm"
+
+
+def test_chatglm3_checkpoint_layout_equals_glm(tmp_path):
+    """A ChatGLM3-format checkpoint (fused ``query_key_value`` / ``dense_h_to_4h``, its own config keys)
+    built from the tensors of a HuggingFace ``glm`` model must give the same logits as that model."""
+    import json
+
+    import pytest
+    from safetensors.torch import save_file
+
+    transformers = pytest.importorskip("transformers")
+    if not hasattr(transformers, "GlmConfig"):
+        pytest.skip("transformers has no GLM")
+    torch.manual_seed(0)
+    hf_cfg = transformers.GlmConfig(hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, vocab_size=160, head_dim=16,
+                                    max_position_embeddings=128, partial_rotary_factor=0.5, attention_bias=True,
+                                    pad_token_id=0)
+    hf = transformers.AutoModelForCausalLM.from_config(hf_cfg).float().eval()
+    (tmp_path / "glm").mkdir()
+    hf.save_pretrained(tmp_path / "glm", safe_serialization=True)
+    sd = hf.state_dict()
+    out = {"transformer.embedding.word_embeddings.weight": sd["model.embed_tokens.weight"],
+           "transformer.encoder.final_layernorm.weight": sd["model.norm.weight"],
+           "transformer.output_layer.weight": sd["lm_head.weight"]}
+    for i in range(2):
+        s, d = f"model.layers.{i}.", f"transformer.encoder.layers.{i}."
+        out[d + "input_layernorm.weight"] = sd[s + "input_layernorm.weight"]
+        out[d + "post_attention_layernorm.weight"] = sd[s + "post_attention_layernorm.weight"]
+        for suffix in ("weight", "bias"):
+            out[d + f"self_attention.query_key_value.{suffix}"] = torch.cat(
+                [sd[s + f"self_attn.{n}_proj.{suffix}"] for n in "qkv"])
+        out[d + "self_attention.dense.weight"] = sd[s + "self_attn.o_proj.weight"]
+        out[d + "mlp.dense_h_to_4h.weight"] = sd[s + "mlp.gate_up_proj.weight"]
+        out[d + "mlp.dense_4h_to_h.weight"] = sd[s + "mlp.down_proj.weight"]
+    (tmp_path / "chatglm").mkdir()
+    save_file({k: v.contiguous().clone() for k, v in out.items()}, str(tmp_path / "chatglm" / "model.safetensors"))
+    chat_cfg = dict(model_type="chatglm", hidden_size=64, num_layers=2, num_attention_heads=4,
+                    multi_query_attention=True, multi_query_group_num=2, kv_channels=16, ffn_hidden_size=112,
+                    layernorm_epsilon=hf_cfg.rms_norm_eps, padded_vocab_size=160, seq_length=128,
+                    add_qkv_bias=True, rope_ratio=1.0)
+    quant = Q.get("q0f32")
+    toks = [3, 17, 42, 99, 5, 8, 120]
+    glm_cfg = mc.from_dict("glm", json.load(open(tmp_path / "glm" / "config.json")))
+    want = _logits(DecoderModel(glm_cfg, quant, loader.load_hf_params(str(tmp_path / "glm"), glm_cfg, quant,
+                                                                      torch.device("cpu")), torch.device("cpu")), toks)
+    cfg = mc.from_dict("chatglm", chat_cfg)
+    assert cfg.num_key_value_heads == 2 and cfg.head_dim == 16 and cfg.rotary_dim == 8 and cfg.attention_bias
+    got = _logits(DecoderModel(cfg, quant, loader.load_hf_params(str(tmp_path / "chatglm"), cfg, quant,
+                                                                 torch.device("cpu")), torch.device("cpu")), toks)
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
