@@ -273,6 +273,23 @@ def _chatglm(cfg: ModelConfig, m: Mapping) -> None:
     m.add("lm_head.weight", ["transformer.output_layer.weight"])
 
 
+def _qwen(cfg: ModelConfig, m: Mapping) -> None:
+    """First-generation Qwen: GPT-2 style names, fused ``c_attn``; the MLP computes
+    ``c_proj(w1(x) * silu(w2(x)))``, so ``w2`` is the gate (reference: ``model/qwen/qwen_loader.py``)."""
+    m.add("model.embed_tokens.weight", ["transformer.wte.weight"])
+    for i in range(cfg.num_hidden_layers):
+        s, d = f"transformer.h.{i}.", f"model.layers.{i}."
+        m.add(d + "input_layernorm.weight", [s + "ln_1.weight"])
+        m.add(d + "post_attention_layernorm.weight", [s + "ln_2.weight"])
+        m.add(d + "self_attn.qkv_proj.weight", [s + "attn.c_attn.weight"])
+        m.add(d + "self_attn.qkv_proj.bias", [s + "attn.c_attn.bias"])
+        m.add(d + "self_attn.o_proj.weight", [s + "attn.c_proj.weight"])
+        m.add(d + "mlp.gate_up_proj.weight", [s + "mlp.w2.weight", s + "mlp.w1.weight"], _cat0)
+        m.add(d + "mlp.down_proj.weight", [s + "mlp.c_proj.weight"])
+    m.add("model.norm.weight", ["transformer.ln_f.weight"])
+    m.add("lm_head.weight", ["lm_head.weight"])
+
+
 def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
     """GPT-NeoX interleaves q, k, v per head inside ``query_key_value`` ([heads, 3, d, hidden]); they
     are regrouped into [q; k; v] (reference: ``model/gpt_neox/gpt_neox_loader.py``)."""
@@ -350,6 +367,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gpt_neox(cfg, m)
     elif mt in ("gptj", "gpt_j"):
         _gptj(cfg, m)
+    elif mt == "qwen":
+        _qwen(cfg, m)
     elif mt == "glm":
         _glm(cfg, m)
     elif mt == "chatglm":

@@ -198,6 +198,22 @@ def _mistral(cfg, mt):
     return d
 
 
+def _qwen(cfg, mt):
+    """Qwen (first generation): Llama math with a q/k/v bias; ``intermediate_size`` in its config counts
+    gate and up together (reference: ``python/mlc_llm/model/qwen/qwen_model.py:118-134``)."""
+    cfg = dict(cfg)
+    if "kv_channels" in cfg and "head_dim" not in cfg:
+        cfg["head_dim"] = cfg["kv_channels"]
+    cfg.setdefault("rms_norm_eps", cfg.get("layer_norm_epsilon", 1e-6))
+    cfg.setdefault("rope_theta", cfg.get("rotary_emb_base", 10000.0))
+    cfg.setdefault("max_position_embeddings", cfg.get("seq_length", 8192))
+    d = _common(cfg, mt)
+    d["intermediate_size"] = int(d["intermediate_size"]) // 2
+    d["attention_bias"] = True
+    d["attention_out_bias"] = False
+    return d
+
+
 def _qwen2(cfg, mt):
     d = _common(cfg, mt)
     d["attention_bias"] = True
@@ -468,7 +484,7 @@ def _llava(cfg, mt):
 
 
 _PARSERS = {
-    "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen2": _qwen2, "qwen3": _qwen3,
+    "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
     "gpt_j": _gptj, "glm": _glm, "chatglm": _glm,

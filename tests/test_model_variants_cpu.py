@@ -108,3 +108,50 @@ def test_chatglm3_checkpoint_layout_equals_glm(tmp_path):
     got = _logits(DecoderModel(cfg, quant, loader.load_hf_params(str(tmp_path / "chatglm"), cfg, quant,
                                                                  torch.device("cpu")), torch.device("cpu")), toks)
     assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+
+
+def test_qwen1_checkpoint_layout_equals_qwen2(tmp_path):
+    """First-generation Qwen checkpoint names (``c_attn``, ``w1`` / ``w2``, doubled ``intermediate_size``)
+    built from a HuggingFace Qwen2 model (same math: q/k/v bias, SwiGLU) give the same logits."""
+    import json
+
+    import pytest
+    from safetensors.torch import save_file
+
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hf_cfg = transformers.Qwen2Config(hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=4, vocab_size=160,
+                                      max_position_embeddings=128, tie_word_embeddings=False)
+    hf = transformers.AutoModelForCausalLM.from_config(hf_cfg).float().eval()
+    (tmp_path / "q2").mkdir()
+    hf.save_pretrained(tmp_path / "q2", safe_serialization=True)
+    sd = hf.state_dict()
+    out = {"transformer.wte.weight": sd["model.embed_tokens.weight"], "transformer.ln_f.weight": sd["model.norm.weight"],
+           "lm_head.weight": sd["lm_head.weight"]}
+    for i in range(2):
+        s, d = f"model.layers.{i}.", f"transformer.h.{i}."
+        out[d + "ln_1.weight"] = sd[s + "input_layernorm.weight"]
+        out[d + "ln_2.weight"] = sd[s + "post_attention_layernorm.weight"]
+        for suffix in ("weight", "bias"):
+            out[d + f"attn.c_attn.{suffix}"] = torch.cat([sd[s + f"self_attn.{n}_proj.{suffix}"] for n in "qkv"])
+        out[d + "attn.c_proj.weight"] = sd[s + "self_attn.o_proj.weight"]
+        out[d + "mlp.w1.weight"] = sd[s + "mlp.up_proj.weight"]
+        out[d + "mlp.w2.weight"] = sd[s + "mlp.gate_proj.weight"]
+        out[d + "mlp.c_proj.weight"] = sd[s + "mlp.down_proj.weight"]
+    (tmp_path / "q1").mkdir()
+    save_file({k: v.contiguous().clone() for k, v in out.items()}, str(tmp_path / "q1" / "model.safetensors"))
+    q1_cfg = dict(model_type="qwen", hidden_size=64, num_hidden_layers=2, num_attention_heads=4, kv_channels=16,
+                  intermediate_size=224, layer_norm_epsilon=hf_cfg.rms_norm_eps, vocab_size=160, seq_length=128,
+                  rotary_emb_base=json.load(open(tmp_path / "q2" / "config.json")).get("rope_theta", 10000.0))
+    quant = Q.get("q0f32")
+    toks = [3, 17, 42, 99, 5, 8, 120]
+    c2 = mc.from_dict("qwen2", json.load(open(tmp_path / "q2" / "config.json")))
+    c1 = mc.from_dict("qwen", q1_cfg)
+    c1.rope_theta = c2.rope_theta
+    assert c1.intermediate_size == 112 and c1.attention_bias
+    want = _logits(DecoderModel(c2, quant, loader.load_hf_params(str(tmp_path / "q2"), c2, quant, torch.device("cpu")),
+                                torch.device("cpu")), toks)
+    got = _logits(DecoderModel(c1, quant, loader.load_hf_params(str(tmp_path / "q1"), c1, quant, torch.device("cpu")),
+                               torch.device("cpu")), toks)
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
