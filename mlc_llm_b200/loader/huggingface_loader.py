@@ -391,6 +391,9 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _moe_layers(cfg, m, "qwen")
     elif mt == "deepseek_v2":
         _deepseek_v2(cfg, m)
+    elif mt == "deepseek":
+        _llama_like(cfg, m)
+        _moe_layers(cfg, m, "deepseek")
     elif mt == "eagle":
         # EAGLE checkpoints name their tensors without the "model." prefix; the resolver tries both
         _llama_like(cfg, m)

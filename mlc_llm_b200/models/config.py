@@ -90,8 +90,10 @@ class ModelConfig:
         return r - (r % 2)
 
     def is_moe_layer(self, layer: int) -> bool:
+        # Qwen counts sparse layers as (layer + 1) % step == 0, DeepSeek as layer % freq == 0
+        phase = int(self.extra.get("moe_layer_phase", 1))
         return (self.num_experts > 0 and layer >= self.first_moe_layer
-                and (layer + 1) % max(1, self.moe_layer_freq) == 0)
+                and (layer + phase) % max(1, self.moe_layer_freq) == 0)
 
     def kv_cache_metadata(self) -> Dict[str, int]:
         tp = max(1, self.tensor_parallel_shards)
@@ -377,6 +379,29 @@ def _qwen_moe(cfg, mt):
     return d
 
 
+def _deepseek_moe_fields(cfg, d):
+    routed = int(_get(cfg, "n_routed_experts", default=0) or 0)
+    shared = int(_get(cfg, "n_shared_experts", default=0) or 0)
+    moe_inter = int(_get(cfg, "moe_intermediate_size", default=1407))
+    d.update(num_experts=routed, num_experts_per_tok=int(_get(cfg, "num_experts_per_tok", default=6) or 0),
+             moe_intermediate_size=moe_inter, norm_topk_prob=bool(_get(cfg, "norm_topk_prob", default=False)),
+             moe_router="softmax_topk", shared_expert_intermediate_size=moe_inter * shared,
+             first_moe_layer=int(_get(cfg, "first_k_dense_replace", default=0)),
+             moe_layer_freq=int(_get(cfg, "moe_layer_freq", default=1)))
+    return {"routed_scaling_factor": float(_get(cfg, "routed_scaling_factor", default=1.0)),
+            "topk_method": _get(cfg, "topk_method", default="greedy"),
+            "n_group": int(_get(cfg, "n_group", default=1) or 1),
+            "topk_group": int(_get(cfg, "topk_group", default=1) or 1), "moe_layer_phase": 0}
+
+
+def _deepseek(cfg, mt):
+    """DeepSeek-MoE (first generation): Llama attention, dense first layers, then routed + shared experts
+    (reference: ``python/mlc_llm/model/deepseek/deepseek_model.py:171-208,248-254``)."""
+    d = _llama(cfg, mt)
+    d["extra"] = _deepseek_moe_fields(cfg, d)
+    return d
+
+
 def _deepseek_v2(cfg, mt):
     """DeepSeek-V2: multi-head latent attention (queries and keys are a no-position part plus a rotary
     part shared by all heads; keys / values are expanded from a low-rank latent) and a mixture of
@@ -393,21 +418,11 @@ def _deepseek_v2(cfg, mt):
     scaling = d.get("rope_scaling")
     if isinstance(scaling, dict) and scaling.get("rope_type", scaling.get("type", "default")) not in ("default", "linear"):
         raise ValueError("DeepSeek-V2 rotary scaling other than linear is not supported")
-    routed = int(_get(cfg, "n_routed_experts", default=0) or 0)
-    shared = int(_get(cfg, "n_shared_experts", default=0) or 0)
-    moe_inter = int(_get(cfg, "moe_intermediate_size", default=1407))
-    d.update(num_experts=routed, num_experts_per_tok=int(_get(cfg, "num_experts_per_tok", default=6) or 0),
-             moe_intermediate_size=moe_inter, norm_topk_prob=bool(_get(cfg, "norm_topk_prob", default=False)),
-             moe_router="softmax_topk", shared_expert_intermediate_size=moe_inter * shared,
-             first_moe_layer=int(_get(cfg, "first_k_dense_replace", default=0)),
-             moe_layer_freq=int(_get(cfg, "moe_layer_freq", default=1)))
-    d["extra"] = {"mla": {"q_lora_rank": _get(cfg, "q_lora_rank"), "kv_lora_rank": int(_get(cfg, "kv_lora_rank", default=512)),
-                          "qk_nope_head_dim": nope, "qk_rope_head_dim": rope,
-                          "v_head_dim": int(_get(cfg, "v_head_dim", default=128))},
-                  "routed_scaling_factor": float(_get(cfg, "routed_scaling_factor", default=1.0)),
-                  "topk_method": _get(cfg, "topk_method", default="greedy"),
-                  "n_group": int(_get(cfg, "n_group", default=1) or 1),
-                  "topk_group": int(_get(cfg, "topk_group", default=1) or 1)}
+    extra = _deepseek_moe_fields(cfg, d)
+    extra["mla"] = {"q_lora_rank": _get(cfg, "q_lora_rank"), "kv_lora_rank": int(_get(cfg, "kv_lora_rank", default=512)),
+                    "qk_nope_head_dim": nope, "qk_rope_head_dim": rope,
+                    "v_head_dim": int(_get(cfg, "v_head_dim", default=128))}
+    d["extra"] = extra
     return d
 
 
@@ -491,7 +506,7 @@ _PARSERS = {
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,
-    "deepseek": _llama, "nemotron": _nemotron, "cohere": _cohere, "deepseek_v2": _deepseek_v2, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
+    "deepseek": _deepseek, "nemotron": _nemotron, "cohere": _cohere, "deepseek_v2": _deepseek_v2, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
     "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,
 }
