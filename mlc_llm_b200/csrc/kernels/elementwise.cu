@@ -230,9 +230,71 @@ __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __
   for (int v = lane; v < row_bytes / 16; v += 32) dp[v] = sp[v];
 }
 
+// RWKV-5 recurrence (reference: python/mlc_llm/model/rwkv5/rwkv5_model.py:64-123). One CTA per
+// (head, sequence); thread i owns row i of the head's matrix state (value dimension i, all key dimensions)
+// in registers and walks the sequence's tokens in order:
+//   out_t[i] = sum_k r_t[k] * (u[k] * k_t[k] * v_t[i] + S[i][k]);   S[i][k] = S[i][k] * w[k] + k_t[k] * v_t[i]
+// r, k, v, out: [tokens, heads, H] fp32.  w, u: [heads, H].  The state of sequence s for this layer starts at
+// state_base[s] + layer_offset floats and is [heads, H, H].
+template <int H>
+__global__ void __launch_bounds__(H) wkv5_kernel(const float* __restrict__ r, const float* __restrict__ k,
+                                                  const float* __restrict__ v, const float* __restrict__ w,
+                                                  const float* __restrict__ u, const long long* __restrict__ state_base,
+                                                  long long layer_offset, const int* __restrict__ q_indptr,
+                                                  float* __restrict__ out, int heads, int total_tokens) {
+  __shared__ float sh_r[H], sh_k[H], sh_w[H], sh_u[H];
+  const int h = blockIdx.x, seq = blockIdx.y, i = threadIdx.x;
+  const int t0 = q_indptr[seq], t1 = q_indptr[seq + 1];
+  if (t0 < 0 || t1 > total_tokens || t0 >= t1) return;
+  float* state = reinterpret_cast<float*>(state_base[seq]) + layer_offset +
+                 (static_cast<size_t>(h) * H + i) * H;
+  float s[H];
+#pragma unroll
+  for (int j = 0; j < H; ++j) s[j] = state[j];
+  sh_w[i] = w[h * H + i];
+  sh_u[i] = u[h * H + i];
+  for (int t = t0; t < t1; ++t) {
+    const size_t base = (static_cast<size_t>(t) * heads + h) * H;
+    __syncthreads();
+    sh_r[i] = r[base + i];
+    sh_k[i] = k[base + i];
+    __syncthreads();
+    const float vi = v[base + i];
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < H; ++j) {
+      const float x = sh_k[j] * vi;
+      acc += sh_r[j] * (sh_u[j] * x + s[j]);
+      s[j] = s[j] * sh_w[j] + x;
+    }
+    out[base + i] = acc;
+  }
+#pragma unroll
+  for (int j = 0; j < H; ++j) state[j] = s[j];
+}
+
 }  // namespace mlcb
 
 using namespace mlcb;
+
+// head_size 32 or 64 (every released RWKV-5 uses 64); other sizes return -1 and the caller falls back.
+MLCB_API int mlcb_wkv5(const float* r, const float* k, const float* v, const float* w, const float* u,
+                       const long long* state_base, long long layer_offset, const int* q_indptr, float* out,
+                       int num_seqs, int heads, int head_size, int total_tokens, cudaStream_t stream) {
+  if (num_seqs <= 0 || total_tokens <= 0) return 0;
+  if (heads <= 0 || num_seqs > 65535) return -1;
+  dim3 grid(heads, num_seqs);
+  if (head_size == 64)
+    wkv5_kernel<64><<<grid, 64, 0, stream>>>(r, k, v, w, u, state_base, layer_offset, q_indptr, out, heads,
+                                             total_tokens);
+  else if (head_size == 32)
+    wkv5_kernel<32><<<grid, 32, 0, stream>>>(r, k, v, w, u, state_base, layer_offset, q_indptr, out, heads,
+                                             total_tokens);
+  else
+    return -1;
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
 
 // Lets kernels running on `device` dereference memory of `peer` (both in this process's view).
 // Returns 0 when access is (already) enabled.

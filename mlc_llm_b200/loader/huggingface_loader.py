@@ -290,6 +290,21 @@ def _qwen(cfg: ModelConfig, m: Mapping) -> None:
     m.add("lm_head.weight", ["lm_head.weight"])
 
 
+def _rwkv5(cfg: ModelConfig, m: Mapping) -> None:
+    """RWKV-5 checkpoints: ``rwkv.`` prefix, ``time_mix_*`` stored as [1, 1, hidden], ``time_decay`` stored
+    before the double exponential (reference: ``model/rwkv5/rwkv5_loader.py:41-52``)."""
+    for name, (shape, _kind) in param_specs(cfg).items():
+        src = "rwkv." + name[len("model."):] if name.startswith("model.") else name
+        if name.endswith("time_decay"):
+            m.add(name, [src], lambda ts: torch.exp(-torch.exp(ts[0].float())).reshape(cfg.hidden_size // cfg.head_dim, cfg.head_dim))
+        elif "time_mix_" in name:
+            m.add(name, [src], lambda ts: ts[0].reshape(-1))
+        elif name.endswith("time_faaaa"):
+            m.add(name, [src], lambda ts: ts[0].float().reshape(cfg.hidden_size // cfg.head_dim, cfg.head_dim))
+        else:
+            m.add(name, [src])
+
+
 def _gpt_neox(cfg: ModelConfig, m: Mapping) -> None:
     """GPT-NeoX interleaves q, k, v per head inside ``query_key_value`` ([heads, 3, d, hidden]); they
     are regrouped into [q; k; v] (reference: ``model/gpt_neox/gpt_neox_loader.py``)."""
@@ -369,6 +384,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gptj(cfg, m)
     elif mt == "qwen":
         _qwen(cfg, m)
+    elif mt == "rwkv5":
+        _rwkv5(cfg, m)
     elif mt == "glm":
         _glm(cfg, m)
     elif mt == "chatglm":

@@ -315,6 +315,23 @@ def _glm(cfg, mt):
     return d
 
 
+def _rwkv5(cfg, mt):
+    """RWKV-5: recurrent blocks, no attention (reference: ``python/mlc_llm/model/rwkv5/rwkv5_model.py``)."""
+    hidden = int(_get(cfg, "hidden_size"))
+    head = int(_get(cfg, "head_size", default=64))
+    inter = _get(cfg, "intermediate_size")
+    if not inter:
+        inter = int((hidden * 3.5)) // 32 * 32
+    return dict(model_type=mt, hidden_size=hidden, intermediate_size=int(inter),
+                num_hidden_layers=int(_get(cfg, "num_hidden_layers")), num_attention_heads=hidden // head,
+                num_key_value_heads=hidden // head, head_dim=head, vocab_size=int(_get(cfg, "vocab_size")),
+                rms_norm_eps=float(_get(cfg, "layer_norm_epsilon", default=1e-5)), norm_type="layernorm",
+                position_embedding="none", context_window_size=int(_get(cfg, "context_window_size", default=0) or 0) or -1,
+                prefill_chunk_size=int(_get(cfg, "prefill_chunk_size", default=0) or 0),
+                max_batch_size=int(_get(cfg, "max_batch_size", default=128)),
+                extra={"rwkv": 5, "rescale_every": int(_get(cfg, "rescale_every", default=0) or 0)})
+
+
 def _gpt2(cfg, mt):
     d = _common(cfg, mt)
     d.update(norm_type="layernorm", hidden_act="gelu_tanh", gated_mlp=False, attention_bias=True,
@@ -502,7 +519,7 @@ _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
-    "gpt_j": _gptj, "glm": _glm, "chatglm": _glm,
+    "gpt_j": _gptj, "glm": _glm, "chatglm": _glm, "rwkv5": _rwkv5,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,

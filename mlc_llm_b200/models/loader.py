@@ -124,6 +124,8 @@ def _store(store: ParamStore, name: str, kind: str, w: torch.Tensor, quant: Q.Qu
         biases[base] = w.to(quant.torch_dtype).to(device)
     elif kind == "router":
         store.tensors[name] = w.to(quant.torch_dtype).to(device)
+    elif kind == "f32":
+        store.tensors[name] = w.float().to(device)
     else:
         store.tensors[name] = w.to(quant.torch_dtype).to(device)
 
@@ -145,6 +147,11 @@ def random_params(cfg: ModelConfig, quant: Q.Quantization, seed: int, device: to
             w = torch.full(shape, 1.0 - cfg.norm_weight_offset)
         elif kind == "bias":
             w = torch.zeros(shape)
+        elif "time_mix_" in name or name.endswith("time_decay"):
+            # interpolation weights and decays of recurrent blocks live in (0, 1)
+            g = torch.Generator(device=gen_device)
+            g.manual_seed((seed * 1000003 + idx * 7919) % (2 ** 63 - 1))
+            w = torch.rand(shape, generator=g, device=gen_device, dtype=torch.float32) * 0.7 + 0.25
         else:
             g = torch.Generator(device=gen_device)
             g.manual_seed((seed * 1000003 + idx * 7919) % (2 ** 63 - 1))
@@ -253,6 +260,8 @@ def load_params(model_dir: str, cfg: ModelConfig, quant: Q.Quantization, device:
                                                t.shape[-2], t.shape[-1]).to(device)
         elif kind == "bias":
             biases[base] = t.to(quant.torch_dtype).to(device)
+        elif kind == "f32":
+            store.tensors[name] = t.float().to(device)
         else:
             store.tensors[name] = t.to(quant.torch_dtype).to(device)
     # fp8 block-scale pairs

@@ -42,6 +42,10 @@ MODEL_PRESETS = {
         "first_k_dense_replace": 1, "topk_method": "group_limited_greedy", "n_group": 4, "topk_group": 2,
         "routed_scaling_factor": 1.0, "norm_topk_prob": False,
     },
+    "tiny-rwkv5": {
+        "model_type": "rwkv5", "hidden_size": 128, "num_hidden_layers": 2, "head_size": 32, "vocab_size": 32000,
+        "layer_norm_epsilon": 1e-5, "rescale_every": 0,
+    },
     # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
     "tiny-llama-gpu": {
         "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,

@@ -440,6 +440,32 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
                 specs[f"medusa_head.{i}.{j}.linear.bias"] = ((h,), "bias")
             specs[f"medusa_head.{i}.{int(medusa['num_layers'])}.weight"] = ((cfg.vocab_size, h), "linear")
         return specs
+    if cfg.extra.get("rwkv"):
+        specs = {"model.embeddings.weight": ((cfg.vocab_size, h), "pos"),
+                 "model.ln_out.weight": ((h,), "norm"), "model.ln_out.bias": ((h,), "bias"),
+                 "head.weight": ((cfg.vocab_size, h), "linear")}
+        nh, hs = h // cfg.head_dim, cfg.head_dim
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.blocks.{i}."
+            for ln in (["pre_ln"] if i == 0 else []) + ["ln1", "ln2"]:
+                specs[p + ln + ".weight"] = ((h,), "norm")
+                specs[p + ln + ".bias"] = ((h,), "bias")
+            a = p + "attention."
+            specs[a + "time_decay"] = ((nh, hs), "f32")   # already exp(-exp(.)) of the checkpoint value
+            specs[a + "time_faaaa"] = ((nh, hs), "f32")
+            for n_ in ("gate", "key", "value", "receptance"):
+                specs[a + f"time_mix_{n_}"] = ((h,), "pos")
+                specs[a + n_ + ".weight"] = ((h, h), "linear")
+            specs[a + "output.weight"] = ((h, h), "linear")
+            specs[a + "ln_x.weight"] = ((h,), "norm")
+            specs[a + "ln_x.bias"] = ((h,), "bias")
+            f = p + "feed_forward."
+            specs[f + "time_mix_key"] = ((h,), "pos")
+            specs[f + "time_mix_receptance"] = ((h,), "pos")
+            specs[f + "key.weight"] = ((inter, h), "linear")
+            specs[f + "receptance.weight"] = ((h, h), "linear")
+            specs[f + "value.weight"] = ((h, inter), "linear")
+        return specs
     eagle = bool(cfg.extra.get("eagle"))
     specs: Dict[str, tuple] = {"model.embed_tokens.weight": ((cfg.vocab_size, h), "embedding")}
     if eagle:

@@ -312,7 +312,15 @@ class EngineRuntime:
                 store = model_loader.load_hf_params(info.model_path, mcfg, quant, self.device, tp, tp_rank, layers)
             else:
                 store = model_loader.load_params(info.model_path, mcfg, quant, self.device, tp, tp_rank, layers)
-            model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
+            if mcfg.extra.get("rwkv"):
+                from ..models.rwkv import RwkvModel  # pylint: disable=import-outside-toplevel
+
+                if tp > 1 or pp > 1 or len(self.models_info) > 1:
+                    raise ValueError("recurrent-state models run on one GPU, without a draft model")
+                model = RwkvModel(mcfg, quant, store, self.device, None, layers)
+                cfg.prefix_cache_mode = "disable"  # a recurrent state cannot be shared or rolled back
+            else:
+                model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
             if mi == 0 and mcfg.extra.get("vision"):
                 self._attach_vision_tower(model, info, mcfg)
             self.models.append(model)

@@ -225,6 +225,14 @@ class ModelExecutor:
             q_kvstart=dev["q_kvstart"] if dev["q_kvstart"].numel() else None,
             tree_mask=dev["tree_mask"] if dev["tree_mask"].numel() else None,
             num_tokens=int(dev["positions"].numel()))
+        if getattr(model, "stateful", False):
+            # recurrent models select their state by sequence id and need the chunk boundaries on the host
+            qi = np.asarray(plan["q_indptr"])
+            pos = np.asarray(plan["positions"])
+            b.seq_ids = np.asarray(plan["seq_ids"])
+            b.q_indptr = qi
+            b.start_positions = np.asarray([int(pos[qi[i]]) if qi[i + 1] > qi[i] else 0
+                                            for i in range(len(qi) - 1)])
         if "tile_seq" in dev and self._tc_attention_ok(model) and b.tree_mask is None \
                 and b.q_kvstart is None:
             from ..ops.attention import AttentionPlan  # pylint: disable=import-outside-toplevel
@@ -285,7 +293,7 @@ class ModelExecutor:
         if multi and getattr(model, "fused", None) is None:
             return False
         return (self.use_graphs and embed_handles is None and not self._pipeline(model_id)
-                and getattr(model, "ep", None) is None
+                and getattr(model, "ep", None) is None and not getattr(model, "stateful", False)
                 and "dec_seq" in dev and dev["dec_seq"].numel() > 0 and dev["tile_seq"].numel() == 0
                 and dev["page_copies"].numel() == 0 and dev["tree_mask"].numel() == 0
                 and dev["q_kvstart"].numel() == 0 and self._tc_attention_ok(model))

@@ -452,3 +452,30 @@ def test_gemm_cta_pair_mode(pair_mode, quant_name, m, n, k):
         want = x.float() @ wref.t()
         tol = 2e-2 if dt == torch.bfloat16 else 3e-3
         _close(y, want, tol, tol * want.abs().max().item())
+
+
+@pytest.mark.parametrize("head_size", [64, 32])
+def test_wkv5_recurrence_kernel(head_size):
+    """RWKV-5 recurrence: one launch over three sequences of different lengths (one of them continuing
+    from a non-zero state) against the per-token fp32 loop."""
+    from mlc_llm_b200.models.rwkv import wkv5, wkv5_batch
+
+    torch.manual_seed(0)
+    n, layers, pos = 3, 2, 1
+    lens = [5, 1, 17]
+    qi = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    t_all = int(qi[-1])
+    r, k, v = (torch.randn(t_all, n, head_size) * 0.5 for _ in range(3))
+    w = torch.rand(n, head_size) * 0.7 + 0.25
+    u = torch.randn(n, head_size) * 0.3
+    states = [torch.randn(layers, n, head_size, head_size) * (0.2 if i == 2 else 0.0) for i in range(3)]
+    want_states = [s.clone() for s in states]
+    want = torch.cat([wkv5(r[qi[i]:qi[i + 1]], k[qi[i]:qi[i + 1]], v[qi[i]:qi[i + 1]], w, u, want_states[i][pos])
+                      for i in range(3)])
+    dev_states = [s.cuda() for s in states]
+    got = wkv5_batch(r.cuda(), k.cuda(), v.cuda(), w.cuda(), u.cuda(), dev_states, pos, qi)
+    torch.cuda.synchronize()
+    assert torch.allclose(got.cpu(), want, atol=1e-4, rtol=1e-4), (got.cpu() - want).abs().max()
+    for a, b in zip(dev_states, want_states):
+        assert torch.allclose(a.cpu(), b, atol=1e-4, rtol=1e-4)
+        assert torch.equal(a[0].cpu(), b[0])  # the other layer's rows are untouched
