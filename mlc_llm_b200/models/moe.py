@@ -25,7 +25,7 @@ def _group_limited_router(logits: torch.Tensor, k: int, n_group: int, topk_group
     w, idx = torch.topk(masked, k, dim=-1)
     if renorm:
         w = w / w.sum(dim=-1, keepdim=True)
-    return w.to(logits.dtype if logits.dtype != torch.float32 else torch.float32), idx.to(torch.int32)
+    return w.float().contiguous(), idx.to(torch.int32).contiguous()  # fp32 weights, like ops.moe_router
 
 
 def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:

@@ -468,6 +468,8 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, sorted_pos: torch.Tensor
             out = out + add.float()
         return out.to(y.dtype)
     out = torch.empty(t, y.shape[1], dtype=y.dtype, device=y.device)
+    if weights.dtype != torch.float32 or not weights.is_contiguous():
+        weights = weights.float().contiguous()  # the kernel reads fp32 routing weights
     rc = lib().mlcb_moe_combine(ptr(y), ptr(weights), ptr(sorted_pos), ptr(add), ptr(out), c_int(t),
                                 c_int(y.shape[1]), c_int(k), c_int(DTYPE_CODE[y.dtype]), stream_ptr())
     check(rc, "mlcb_moe_combine")
