@@ -1,0 +1,141 @@
+// Memory-bound matrix-vector product for int4-group weights (q4f16_1) and one to four tokens: the
+// single-stream decode case, where the tensor-core kernel's dequantise-to-shared-memory stage, not
+// HBM, sets the pace.  Reference behaviour: the fused dequantize + GEMV schedule that dlight gives
+// ``fuse_dequantize_matmul_ewise`` outputs at batch 1 (python/mlc_llm/compiler_pass/
+// fuse_dequantize_matmul_ewise.py:9-85, low_batch_specialization.py).
+//
+// One warp owns R = 4 consecutive output rows.  A lane takes one 32-weight group of each row per
+// step: a 16-byte load of packed nibbles per row, one fp16 scale per row, and the 32 activations of
+// that group for every token (64 bytes per token, shared by the four rows and, through L1, by the
+// other warps).  Weights are expanded with the 0x6400 trick (1024 + q is exact in fp16), multiplied
+// with the activations in half2 four products at a time, and accumulated in fp32.  No shared memory,
+// no barriers.
+//
+// Weight layout: the device nibble order of the tensor-core kernel (word w of a row holds elements
+// 8w .. 8w+7; pair (2j, 2j+1) at bits [4j, 4j+4) and [16+4j, 20+4j)).
+#include "common.cuh"
+
+namespace mlcb {
+
+constexpr int GEMV_ROWS = 4;    // rows per warp
+constexpr int GEMV_WARPS = 8;   // warps per CTA
+
+template <typename TO, int MMAX>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+    gemv_q4_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w, const __half* __restrict__ scale,
+                   const __half* __restrict__ bias, TO* __restrict__ y, int m_count, int N, int K, int ldx,
+                   int ldy) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_ROWS;
+  if (row0 >= N) return;
+  const int groups = K >> 5;            // 32-weight groups (= 16-byte chunks of nibbles) per row
+  const size_t words_per_row = static_cast<size_t>(K) >> 3;
+  float acc[GEMV_ROWS][MMAX];
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) acc[r][m] = 0.f;
+  const __half2 off = __float2half2_rn(1031.f);
+  for (int g = lane; g < groups; g += 32) {
+    uint4 q[GEMV_ROWS];
+    float s[GEMV_ROWS];
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const int row = row0 + r;
+      if (row < N) {
+        q[r] = __ldg(reinterpret_cast<const uint4*>(w + row * words_per_row) + g);
+        s[r] = __half2float(__ldg(scale + static_cast<size_t>(row) * groups + g));
+      } else {
+        q[r] = make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);  // q - 7 == 0
+        s[r] = 0.f;
+      }
+    }
+    __half2 xv[MMAX][16];
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      if (m < m_count) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * ldx + (g << 5));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 t = __ldg(xp + i);
+          xv[m][4 * i] = *reinterpret_cast<const __half2*>(&t.x);
+          xv[m][4 * i + 1] = *reinterpret_cast<const __half2*>(&t.y);
+          xv[m][4 * i + 2] = *reinterpret_cast<const __half2*>(&t.z);
+          xv[m][4 * i + 3] = *reinterpret_cast<const __half2*>(&t.w);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xv[m][i] = __float2half2_rn(0.f);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const uint32_t words[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        __half2 hv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t v = ((words[wd] >> (4 * j)) & 0x000f000fu) | 0x64006400u;
+          hv[j] = __hsub2(*reinterpret_cast<__half2*>(&v), off);  // (q - 7), exact
+        }
+#pragma unroll
+        for (int m = 0; m < MMAX; ++m) {
+          __half2 p = __hmul2(hv[0], xv[m][4 * wd]);
+          p = __hfma2(hv[1], xv[m][4 * wd + 1], p);
+          p = __hfma2(hv[2], xv[m][4 * wd + 2], p);
+          p = __hfma2(hv[3], xv[m][4 * wd + 3], p);
+          const float2 f = __half22float2(p);
+          acc[r][m] += s[r] * (f.x + f.y);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      const int row = row0 + r;
+      if (lane == 0 && row < N && m < m_count) {
+        if (bias) v += __half2float(bias[row]);
+        y[static_cast<size_t>(m) * ldy + row] = Cvt<TO>::from_f(v);
+      }
+    }
+}
+
+}  // namespace mlcb
+
+using namespace mlcb;
+
+// x: [M, K] fp16 (row stride ldx, 16-byte aligned rows), w: packed int4 [N, K/8] in the device nibble
+// order, scale: [N, K/32] fp16, y: [M, N] (row stride ldy) fp16 (out_dtype 0) or fp32 (out_dtype 2).
+// Returns -1 for shapes it does not take (M > 4, K not a multiple of 32, misaligned rows); the caller
+// then uses the tensor-core kernel.
+MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const void* bias, void* y, int M,
+                          int N, int K, int ldx, int ldy, int out_dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 4 || K <= 0 || K % 32 != 0 || ldx % 8 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -1;
+  if (out_dtype != 0 && out_dtype != 2) return -1;
+  const int rows_per_cta = GEMV_WARPS * GEMV_ROWS;
+  const int grid = (N + rows_per_cta - 1) / rows_per_cta;
+#define GEMV_LAUNCH(TO, MM)                                                                             \
+  gemv_q4_kernel<TO, MM><<<grid, GEMV_WARPS * 32, 0, stream>>>(                                         \
+      static_cast<const __half*>(x), static_cast<const uint32_t*>(w), static_cast<const __half*>(scale), \
+      static_cast<const __half*>(bias), static_cast<TO*>(y), M, N, K, ldx, ldy)
+  if (out_dtype == 0) {
+    if (M == 1) GEMV_LAUNCH(__half, 1);
+    else if (M == 2) GEMV_LAUNCH(__half, 2);
+    else GEMV_LAUNCH(__half, 4);
+  } else {
+    if (M == 1) GEMV_LAUNCH(float, 1);
+    else if (M == 2) GEMV_LAUNCH(float, 2);
+    else GEMV_LAUNCH(float, 4);
+  }
+#undef GEMV_LAUNCH
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}

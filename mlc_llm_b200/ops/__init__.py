@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import dataclasses
+import os
 from typing import Optional
 
 import torch
@@ -96,6 +97,7 @@ def _gemm_scratch(device: torch.device):
 
 
 _LINEAR_OBSERVER = None
+_GEMV_Q4 = os.environ.get("MLCB_GEMV_Q4", "1") != "0"
 
 
 def set_linear_observer(fn) -> None:
@@ -129,6 +131,15 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
     if lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and x2.dtype == torch.float16 \
             and k % 64 == 0:
         assert lw.device_layout
+        if m <= 4 and od in (torch.float16, torch.float32) and _GEMV_Q4:
+            # one to four tokens: the memory-bound CUDA-core kernel beats the tensor-core one, whose
+            # dequantise stage is sized for wide token tiles
+            rc = lib().mlcb_gemv_q4(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
+                                    c_int(k), c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[od]), stream_ptr())
+            if rc == 0:
+                return y.reshape(*lead, n)
+            if rc > 0:
+                check(rc, f"mlcb_gemv_q4(M={m},N={n},K={k})")
         rc = lib().mlcb_gemm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m),
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),

@@ -479,3 +479,26 @@ def test_wkv5_recurrence_kernel(head_size):
     for a, b in zip(dev_states, want_states):
         assert torch.allclose(a.cpu(), b, atol=1e-4, rtol=1e-4)
         assert torch.equal(a[0].cpu(), b[0])  # the other layer's rows are untouched
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 14336), (77, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype):
+    """One to four tokens against q4f16_1 weights take the CUDA-core GEMV; rows that are not a multiple
+    of the 32 rows of a CTA, a K that leaves lanes idle, bias, fp32 output."""
+    torch.manual_seed(m * 1000 + n + k)
+    quant = Q.get("q4f16_1")
+    w = torch.randn(n, k) * 0.05
+    qw, qs = Q.group_quantize(w.half(), quant)
+    wd = Q.group_dequantize(qw, qs, quant, k=k, out_dtype=torch.float32)
+    bias = (torch.randn(n) * 0.1).half()
+    lw = ops.LinearWeight("q4", qw, qs, bias, quant, n, k, False).to("cuda")
+    x = (torch.randn(m, k) * 0.5).half()
+    want = x.float() @ wd.t() + bias.float()
+    assert ops._GEMV_Q4
+    got = ops.linear(x.cuda(), lw, out_dtype=out_dtype)
+    ops.check_status(torch.device("cuda"))
+    assert got.dtype == out_dtype and got.shape == (m, n)
+    err = (got.float().cpu() - want).abs().max()
+    assert err < 2e-2 * max(1.0, float(want.abs().max())), err
