@@ -236,7 +236,8 @@ __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __
 //   out_t[i] = sum_k r_t[k] * (u[k] * k_t[k] * v_t[i] + S[i][k]);   S[i][k] = S[i][k] * w[k] + k_t[k] * v_t[i]
 // r, k, v, out: [tokens, heads, H] fp32.  w, u: [heads, H].  The state of sequence s for this layer starts at
 // state_base[s] + layer_offset floats and is [heads, H, H].
-template <int H>
+// PER_TOKEN: the decay `w` is [tokens, heads, H] (RWKV-6, data-dependent) instead of [heads, H].
+template <int H, bool PER_TOKEN>
 __global__ void __launch_bounds__(H) wkv5_kernel(const float* __restrict__ r, const float* __restrict__ k,
                                                   const float* __restrict__ v, const float* __restrict__ w,
                                                   const float* __restrict__ u, const long long* __restrict__ state_base,
@@ -251,13 +252,14 @@ __global__ void __launch_bounds__(H) wkv5_kernel(const float* __restrict__ r, co
   float s[H];
 #pragma unroll
   for (int j = 0; j < H; ++j) s[j] = state[j];
-  sh_w[i] = w[h * H + i];
+  if (!PER_TOKEN) sh_w[i] = w[h * H + i];
   sh_u[i] = u[h * H + i];
   for (int t = t0; t < t1; ++t) {
     const size_t base = (static_cast<size_t>(t) * heads + h) * H;
     __syncthreads();
     sh_r[i] = r[base + i];
     sh_k[i] = k[base + i];
+    if (PER_TOKEN) sh_w[i] = w[base + i];
     __syncthreads();
     const float vi = v[base + i];
     float acc = 0.f;
@@ -280,18 +282,24 @@ using namespace mlcb;
 // head_size 32 or 64 (every released RWKV-5 uses 64); other sizes return -1 and the caller falls back.
 MLCB_API int mlcb_wkv5(const float* r, const float* k, const float* v, const float* w, const float* u,
                        const long long* state_base, long long layer_offset, const int* q_indptr, float* out,
-                       int num_seqs, int heads, int head_size, int total_tokens, cudaStream_t stream) {
+                       int num_seqs, int heads, int head_size, int total_tokens, int w_per_token,
+                       cudaStream_t stream) {
   if (num_seqs <= 0 || total_tokens <= 0) return 0;
   if (heads <= 0 || num_seqs > 65535) return -1;
   dim3 grid(heads, num_seqs);
-  if (head_size == 64)
-    wkv5_kernel<64><<<grid, 64, 0, stream>>>(r, k, v, w, u, state_base, layer_offset, q_indptr, out, heads,
-                                             total_tokens);
-  else if (head_size == 32)
-    wkv5_kernel<32><<<grid, 32, 0, stream>>>(r, k, v, w, u, state_base, layer_offset, q_indptr, out, heads,
-                                             total_tokens);
-  else
+#define WKV_LAUNCH(HS, PT)                                                                                   \
+  wkv5_kernel<HS, PT><<<grid, HS, 0, stream>>>(r, k, v, w, u, state_base, layer_offset, q_indptr, out, heads, \
+                                               total_tokens)
+  if (head_size == 64) {
+    if (w_per_token) WKV_LAUNCH(64, true);
+    else WKV_LAUNCH(64, false);
+  } else if (head_size == 32) {
+    if (w_per_token) WKV_LAUNCH(32, true);
+    else WKV_LAUNCH(32, false);
+  } else {
     return -1;
+  }
+#undef WKV_LAUNCH
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -291,16 +291,24 @@ def _qwen(cfg: ModelConfig, m: Mapping) -> None:
 
 
 def _rwkv5(cfg: ModelConfig, m: Mapping) -> None:
-    """RWKV-5 checkpoints: ``rwkv.`` prefix, ``time_mix_*`` stored as [1, 1, hidden], ``time_decay`` stored
-    before the double exponential (reference: ``model/rwkv5/rwkv5_loader.py:41-52``)."""
+    """RWKV-5 / RWKV-6 checkpoints: ``rwkv.`` prefix, mixing weights stored as [1, 1, hidden]; RWKV-5's
+    ``time_decay`` is stored before the double exponential; with ``rescale_every`` the output projections of
+    block i are divided by 2 ** (i // rescale_every), matching the halving of the activations in the forward
+    (reference: ``model/rwkv5/rwkv5_loader.py:41-52``, ``model/rwkv6/rwkv6_loader.py:38-55``)."""
+    v6 = int(cfg.extra["rwkv"]) == 6
+    nh, hs = cfg.hidden_size // cfg.head_dim, cfg.head_dim
+    rescale = int(cfg.extra.get("rescale_every", 0))
     for name, (shape, _kind) in param_specs(cfg).items():
         src = "rwkv." + name[len("model."):] if name.startswith("model.") else name
-        if name.endswith("time_decay"):
-            m.add(name, [src], lambda ts: torch.exp(-torch.exp(ts[0].float())).reshape(cfg.hidden_size // cfg.head_dim, cfg.head_dim))
-        elif "time_mix_" in name:
-            m.add(name, [src], lambda ts: ts[0].reshape(-1))
+        if name.endswith("time_decay") and not v6:
+            m.add(name, [src], lambda ts: torch.exp(-torch.exp(ts[0].float())).reshape(nh, hs))
         elif name.endswith("time_faaaa"):
-            m.add(name, [src], lambda ts: ts[0].float().reshape(cfg.hidden_size // cfg.head_dim, cfg.head_dim))
+            m.add(name, [src], lambda ts: ts[0].float().reshape(nh, hs))
+        elif "time_mix_" in name or name.endswith("time_decay") or ("time_maa_" in name and len(shape) == 1):
+            m.add(name, [src], lambda ts: ts[0].reshape(-1))
+        elif rescale > 0 and (name.endswith("feed_forward.value.weight") or name.endswith("attention.output.weight")):
+            block = int(name.split(".")[2])
+            m.add(name, [src], lambda ts, t=block // rescale: ts[0] / (2 ** t))
         else:
             m.add(name, [src])
 
@@ -384,7 +392,7 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gptj(cfg, m)
     elif mt == "qwen":
         _qwen(cfg, m)
-    elif mt == "rwkv5":
+    elif mt in ("rwkv5", "rwkv6"):
         _rwkv5(cfg, m)
     elif mt == "glm":
         _glm(cfg, m)

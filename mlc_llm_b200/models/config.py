@@ -329,7 +329,11 @@ def _rwkv5(cfg, mt):
                 position_embedding="none", context_window_size=int(_get(cfg, "context_window_size", default=0) or 0) or -1,
                 prefill_chunk_size=int(_get(cfg, "prefill_chunk_size", default=0) or 0),
                 max_batch_size=int(_get(cfg, "max_batch_size", default=128)),
-                extra={"rwkv": 5, "rescale_every": int(_get(cfg, "rescale_every", default=0) or 0)})
+                extra={"rwkv": 6 if mt == "rwkv6" else 5,
+                       "rescale_every": int(_get(cfg, "rescale_every", default=0) or 0),
+                       # widths of RWKV-6's low-rank corrections (reference: rwkv6_model.py:203-209)
+                       "time_mix_extra_dim": 64 if hidden == 4096 else 32,
+                       "time_decay_extra_dim": 128 if hidden == 4096 else 64})
 
 
 def _gpt2(cfg, mt):
@@ -519,7 +523,7 @@ _PARSERS = {
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
-    "gpt_j": _gptj, "glm": _glm, "chatglm": _glm, "rwkv5": _rwkv5,
+    "gpt_j": _gptj, "glm": _glm, "chatglm": _glm, "rwkv5": _rwkv5, "rwkv6": _rwkv5,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
     "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,

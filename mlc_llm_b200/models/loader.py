@@ -147,7 +147,8 @@ def random_params(cfg: ModelConfig, quant: Q.Quantization, seed: int, device: to
             w = torch.full(shape, 1.0 - cfg.norm_weight_offset)
         elif kind == "bias":
             w = torch.zeros(shape)
-        elif "time_mix_" in name or name.endswith("time_decay"):
+        elif "time_mix_" in name or (name.endswith("time_decay") and len(shape) == 2) or \
+                ("time_maa_" in name and len(shape) == 1):
             # interpolation weights and decays of recurrent blocks live in (0, 1)
             g = torch.Generator(device=gen_device)
             g.manual_seed((seed * 1000003 + idx * 7919) % (2 ** 63 - 1))

@@ -46,6 +46,10 @@ MODEL_PRESETS = {
         "model_type": "rwkv5", "hidden_size": 128, "num_hidden_layers": 2, "head_size": 32, "vocab_size": 32000,
         "layer_norm_epsilon": 1e-5, "rescale_every": 0,
     },
+    "tiny-rwkv6": {
+        "model_type": "rwkv6", "hidden_size": 128, "num_hidden_layers": 2, "head_size": 32, "vocab_size": 32000,
+        "layer_norm_epsilon": 1e-5, "rescale_every": 0,
+    },
     # GPU-friendly small model (head_dim 128, dimensions multiples of 128)
     "tiny-llama-gpu": {
         "model_type": "llama", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,

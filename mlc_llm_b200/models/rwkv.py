@@ -1,4 +1,4 @@
-"""RWKV-5 ("Eagle"): a recurrent model whose per-sequence state replaces the KV cache.
+"""RWKV-5 ("Eagle") and RWKV-6 ("Finch"): recurrent models whose per-sequence state replaces the KV cache.
 
 Reference: ``python/mlc_llm/model/rwkv5/rwkv5_model.py`` (time-mix block with a per-head matrix state
 updated by the ``wkv5`` recurrence ``:64-123``, channel-mix block ``:150-175``, token shift against the
@@ -16,7 +16,9 @@ The recurrence itself runs as one pass over the tokens of each sequence in fp32:
     out_t[i] = sum_k r_t[k] * (u[k] * k_t[k] * v_t[i] + S[i, k])
     S[i, k]  = S[i, k] * w[k] + k_t[k] * v_t[i]
 
-with ``w = exp(-exp(time_decay))`` and ``u = time_faaaa`` per head.
+with ``w = exp(-exp(time_decay))`` and ``u = time_faaaa`` per head.  RWKV-6
+(``python/mlc_llm/model/rwkv6/rwkv6_model.py``) keeps the recurrence and makes two things depend on the
+token: the token-shift mixing weights get low-rank corrections, and the decay ``w`` is computed per token.
 """
 
 from __future__ import annotations
@@ -36,14 +38,15 @@ STATE_CAP = 4096  # sequences whose state is remembered; the least recently used
 
 def wkv5(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
          state: torch.Tensor) -> torch.Tensor:
-    """One sequence: ``r, k, v [T, N, H]`` fp32, ``w, u [N, H]``, ``state [N, H(value), H(key)]`` updated in
-    place; returns ``[T, N, H]``."""
+    """One sequence: ``r, k, v [T, N, H]`` fp32, ``u [N, H]``, decay ``w [N, H]`` (RWKV-5) or ``[T, N, H]``
+    (RWKV-6, one decay per token), ``state [N, H(value), H(key)]`` updated in place; returns ``[T, N, H]``."""
     t_len = r.shape[0]
     out = torch.empty_like(r)
     for t in range(t_len):
         kv = v[t].unsqueeze(-1) * k[t].unsqueeze(-2)                      # [N, Hv, Hk]
         out[t] = ((u.unsqueeze(-2) * kv + state) * r[t].unsqueeze(-2)).sum(-1)
-        state.mul_(w.unsqueeze(-2)).add_(kv)
+        wt = w[t] if w.dim() == 3 else w
+        state.mul_(wt.unsqueeze(-2)).add_(kv)
     return out
 
 
@@ -67,13 +70,13 @@ def wkv5_batch(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tenso
         rc = lib().mlcb_wkv5(ptr(r.contiguous()), ptr(k.contiguous()), ptr(v.contiguous()), ptr(w.contiguous()),
                              ptr(u.contiguous()), ptr(base), ctypes.c_longlong(layer_offset), ptr(qi), ptr(out),
                              ctypes.c_int(len(kv_states)), ctypes.c_int(n), ctypes.c_int(hs), ctypes.c_int(t_all),
-                             stream_ptr())
+                             ctypes.c_int(1 if w.dim() == 3 else 0), stream_ptr())
         check(rc, "mlcb_wkv5")
         return out
     for i, st in enumerate(kv_states):
         s, e = int(q_indptr[i]), int(q_indptr[i + 1])
         if e > s:
-            out[s:e] = wkv5(r[s:e], k[s:e], v[s:e], w, u, st[layer_pos])
+            out[s:e] = wkv5(r[s:e], k[s:e], v[s:e], w[s:e] if w.dim() == 3 else w, u, st[layer_pos])
     return out
 
 
@@ -144,6 +147,7 @@ class RwkvModel(DecoderModel):
         lasts = torch.as_tensor([int(qi[i + 1]) - 1 for i in live], dtype=torch.long, device=x.device)
         hs, n = c.head_dim, self.heads
         t_all = x.shape[0]
+        v6 = int(c.extra.get("rwkv", 5)) == 6
         # chunk boundaries of the sequences that have tokens in this step (they are contiguous in x)
         live_indptr = np.asarray([int(qi[i]) for i in live] + [int(qi[live[-1] + 1]) if live else 0], dtype=np.int32)
         for pos, li in enumerate(self.layers):
@@ -155,12 +159,30 @@ class RwkvModel(DecoderModel):
             prev = torch.stack([states[i]["att_x"][pos] for i in live])
             sx = self._shift(h, prev, qi, firsts)
             a = pre + "attention."
-            mix = lambda name: h * self.p.tensors[a + name] + sx * (1.0 - self.p.tensors[a + name])
-            r = ops.linear(mix("time_mix_receptance"), self.p.linears[a + "receptance"]).float().view(t_all, n, hs)
-            k = ops.linear(mix("time_mix_key"), self.p.linears[a + "key"]).float().view(t_all, n, hs)
-            v = ops.linear(mix("time_mix_value"), self.p.linears[a + "value"]).float().view(t_all, n, hs)
-            g = F.silu(ops.linear(mix("time_mix_gate"), self.p.linears[a + "gate"]).float())
-            w = self.p.tensors[a + "time_decay"].float()
+            if v6:
+                # data-dependent interpolation: five low-rank corrections of the mixing weights, and a
+                # per-token decay (reference: python/mlc_llm/model/rwkv6/rwkv6_model.py:236-272)
+                tp = self.p.tensors
+                dx = sx - h
+                xxx = torch.tanh((h + dx * tp[a + "time_maa_x"]).float() @ tp[a + "time_maa_w1"].float())
+                xxx = xxx.view(t_all, 5, -1).transpose(0, 1)                       # [5, T, D]
+                m5 = torch.bmm(xxx, tp[a + "time_maa_w2"].float()).to(h.dtype)      # [5, T, hidden]
+                mixed = lambda j, name: h + dx * (tp[a + name] + m5[j])
+                xw, xk, xv, xr, xg = (mixed(0, "time_maa_w"), mixed(1, "time_maa_k"), mixed(2, "time_maa_v"),
+                                      mixed(3, "time_maa_r"), mixed(4, "time_maa_g"))
+                dec = tp[a + "time_decay"].float().view(1, n, hs) + (
+                    torch.tanh(xw.float() @ tp[a + "time_decay_w1"].float()) @ tp[a + "time_decay_w2"].float()
+                ).view(t_all, n, hs)
+                w = torch.exp(-torch.exp(dec)).contiguous()
+            else:
+                mix = lambda name: h * self.p.tensors[a + name] + sx * (1.0 - self.p.tensors[a + name])
+                xr, xk, xv, xg = (mix("time_mix_receptance"), mix("time_mix_key"), mix("time_mix_value"),
+                                  mix("time_mix_gate"))
+                w = self.p.tensors[a + "time_decay"].float()
+            r = ops.linear(xr, self.p.linears[a + "receptance"]).float().view(t_all, n, hs)
+            k = ops.linear(xk, self.p.linears[a + "key"]).float().view(t_all, n, hs)
+            v = ops.linear(xv, self.p.linears[a + "value"]).float().view(t_all, n, hs)
+            g = F.silu(ops.linear(xg, self.p.linears[a + "gate"]).float())
             u = self.p.tensors[a + "time_faaaa"].float()
             out = wkv5_batch(r, k, v, w, u, [states[i]["kv"] for i in live], pos, live_indptr)
             newest = h.index_select(0, lasts)
@@ -174,8 +196,12 @@ class RwkvModel(DecoderModel):
             prev = torch.stack([states[i]["ffn_x"][pos] for i in live])
             sx = self._shift(h, prev, qi, firsts)
             f = pre + "feed_forward."
-            xk = h * self.p.tensors[f + "time_mix_key"] + sx * (1.0 - self.p.tensors[f + "time_mix_key"])
-            xr = h * self.p.tensors[f + "time_mix_receptance"] + sx * (1.0 - self.p.tensors[f + "time_mix_receptance"])
+            if v6:
+                xk = h + (sx - h) * self.p.tensors[f + "time_maa_k"]
+                xr = h + (sx - h) * self.p.tensors[f + "time_maa_r"]
+            else:
+                xk = h * self.p.tensors[f + "time_mix_key"] + sx * (1.0 - self.p.tensors[f + "time_mix_key"])
+                xr = h * self.p.tensors[f + "time_mix_receptance"] + sx * (1.0 - self.p.tensors[f + "time_mix_receptance"])
             newest = h.index_select(0, lasts)
             for j, i in enumerate(live):
                 states[i]["ffn_x"][pos] = newest[j]

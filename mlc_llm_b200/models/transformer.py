@@ -451,17 +451,33 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
                 specs[p + ln + ".weight"] = ((h,), "norm")
                 specs[p + ln + ".bias"] = ((h,), "bias")
             a = p + "attention."
-            specs[a + "time_decay"] = ((nh, hs), "f32")   # already exp(-exp(.)) of the checkpoint value
+            v6 = int(cfg.extra["rwkv"]) == 6
             specs[a + "time_faaaa"] = ((nh, hs), "f32")
+            if v6:
+                dm, dd = int(cfg.extra["time_mix_extra_dim"]), int(cfg.extra["time_decay_extra_dim"])
+                specs[a + "time_decay"] = ((h,), "f32")       # raw; the decay is computed per token
+                for n_ in "xwkvrg":
+                    specs[a + f"time_maa_{n_}"] = ((h,), "pos")
+                specs[a + "time_maa_w1"] = ((h, 5 * dm), "f32")
+                specs[a + "time_maa_w2"] = ((5, dm, h), "f32")
+                specs[a + "time_decay_w1"] = ((h, dd), "f32")
+                specs[a + "time_decay_w2"] = ((dd, h), "f32")
+            else:
+                specs[a + "time_decay"] = ((nh, hs), "f32")   # already exp(-exp(.)) of the checkpoint value
             for n_ in ("gate", "key", "value", "receptance"):
-                specs[a + f"time_mix_{n_}"] = ((h,), "pos")
+                if not v6:
+                    specs[a + f"time_mix_{n_}"] = ((h,), "pos")
                 specs[a + n_ + ".weight"] = ((h, h), "linear")
             specs[a + "output.weight"] = ((h, h), "linear")
             specs[a + "ln_x.weight"] = ((h,), "norm")
             specs[a + "ln_x.bias"] = ((h,), "bias")
             f = p + "feed_forward."
-            specs[f + "time_mix_key"] = ((h,), "pos")
-            specs[f + "time_mix_receptance"] = ((h,), "pos")
+            if v6:
+                specs[f + "time_maa_k"] = ((h,), "pos")
+                specs[f + "time_maa_r"] = ((h,), "pos")
+            else:
+                specs[f + "time_mix_key"] = ((h,), "pos")
+                specs[f + "time_mix_receptance"] = ((h,), "pos")
             specs[f + "key.weight"] = ((inter, h), "linear")
             specs[f + "receptance.weight"] = ((h, h), "linear")
             specs[f + "value.weight"] = ((h, inter), "linear")

@@ -454,10 +454,11 @@ def test_gemm_cta_pair_mode(pair_mode, quant_name, m, n, k):
         _close(y, want, tol, tol * want.abs().max().item())
 
 
+@pytest.mark.parametrize("per_token_decay", [False, True])
 @pytest.mark.parametrize("head_size", [64, 32])
-def test_wkv5_recurrence_kernel(head_size):
-    """RWKV-5 recurrence: one launch over three sequences of different lengths (one of them continuing
-    from a non-zero state) against the per-token fp32 loop."""
+def test_wkv5_recurrence_kernel(head_size, per_token_decay):
+    """RWKV-5 / RWKV-6 recurrence: one launch over three sequences of different lengths (one of them
+    continuing from a non-zero state) against the per-token fp32 loop; RWKV-6 has one decay per token."""
     from mlc_llm_b200.models.rwkv import wkv5, wkv5_batch
 
     torch.manual_seed(0)
@@ -466,11 +467,12 @@ def test_wkv5_recurrence_kernel(head_size):
     qi = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     t_all = int(qi[-1])
     r, k, v = (torch.randn(t_all, n, head_size) * 0.5 for _ in range(3))
-    w = torch.rand(n, head_size) * 0.7 + 0.25
+    w = torch.rand(*((t_all,) if per_token_decay else ()), n, head_size) * 0.7 + 0.25
     u = torch.randn(n, head_size) * 0.3
     states = [torch.randn(layers, n, head_size, head_size) * (0.2 if i == 2 else 0.0) for i in range(3)]
     want_states = [s.clone() for s in states]
-    want = torch.cat([wkv5(r[qi[i]:qi[i + 1]], k[qi[i]:qi[i + 1]], v[qi[i]:qi[i + 1]], w, u, want_states[i][pos])
+    want = torch.cat([wkv5(r[qi[i]:qi[i + 1]], k[qi[i]:qi[i + 1]], v[qi[i]:qi[i + 1]],
+                           w[qi[i]:qi[i + 1]] if per_token_decay else w, u, want_states[i][pos])
                       for i in range(3)])
     dev_states = [s.cuda() for s in states]
     got = wkv5_batch(r.cuda(), k.cuda(), v.cuda(), w.cuda(), u.cuda(), dev_states, pos, qi)

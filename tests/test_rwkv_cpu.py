@@ -16,9 +16,9 @@ from mlc_llm_b200.serve.config import EngineConfig
 from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
 
 
-def _model(seed=3):
-    hf = dict(MODEL_PRESETS["tiny-rwkv5"])
-    cfg = mc.from_dict("rwkv5", hf)
+def _model(seed=3, preset="tiny-rwkv5"):
+    hf = dict(MODEL_PRESETS[preset])
+    cfg = mc.from_dict(hf["model_type"], hf)
     quant = Q.get("q0f32")
     m = RwkvModel(cfg, quant, loader.random_params(cfg, quant, seed, torch.device("cpu"), std=0.1),
                   torch.device("cpu"))
@@ -51,13 +51,25 @@ def _naive_logits(m, tokens):
                 x = ln(x, pre + "pre_ln")
             h = ln(x, pre + "ln1")
             a = pre + "attention."
-            mix = lambda name: h * p.tensors[a + name] + att_x[li] * (1 - p.tensors[a + name])
-            r = (p.linears[a + "receptance"].w @ mix("time_mix_receptance")).view(n, hs)
-            k = (p.linears[a + "key"].w @ mix("time_mix_key")).view(n, hs)
-            v = (p.linears[a + "value"].w @ mix("time_mix_value")).view(n, hs)
-            g = F.silu(p.linears[a + "gate"].w @ mix("time_mix_gate"))
+            v6 = c.extra["rwkv"] == 6
+            if v6:
+                t_ = p.tensors
+                dx = att_x[li] - h
+                low = torch.tanh((h + dx * t_[a + "time_maa_x"]) @ t_[a + "time_maa_w1"]).view(5, -1)
+                corr = [low[j] @ t_[a + "time_maa_w2"][j] for j in range(5)]
+                xw, xk_, xv_, xr_, xg_ = (h + dx * (t_[a + f"time_maa_{nm}"] + corr[j]) for j, nm in enumerate("wkvrg"))
+                w = torch.exp(-torch.exp(t_[a + "time_decay"].view(n, hs) + (
+                    torch.tanh(xw @ t_[a + "time_decay_w1"]) @ t_[a + "time_decay_w2"]).view(n, hs)))
+            else:
+                mix = lambda name: h * p.tensors[a + name] + att_x[li] * (1 - p.tensors[a + name])
+                xr_, xk_, xv_, xg_ = mix("time_mix_receptance"), mix("time_mix_key"), mix("time_mix_value"), mix("time_mix_gate")
+                w = p.tensors[a + "time_decay"]
+            r = (p.linears[a + "receptance"].w @ xr_).view(n, hs)
+            k = (p.linears[a + "key"].w @ xk_).view(n, hs)
+            v = (p.linears[a + "value"].w @ xv_).view(n, hs)
+            g = F.silu(p.linears[a + "gate"].w @ xg_)
             att_x[li] = h
-            w, u = p.tensors[a + "time_decay"], p.tensors[a + "time_faaaa"]
+            u = p.tensors[a + "time_faaaa"]
             out = torch.zeros(n, hs)
             for hd in range(n):
                 for i in range(hs):
@@ -69,8 +81,12 @@ def _naive_logits(m, tokens):
             x = x + p.linears[a + "output"].w @ (out * g)
             h = ln(x, pre + "ln2")
             f = pre + "feed_forward."
-            xk = h * p.tensors[f + "time_mix_key"] + ffn_x[li] * (1 - p.tensors[f + "time_mix_key"])
-            xr = h * p.tensors[f + "time_mix_receptance"] + ffn_x[li] * (1 - p.tensors[f + "time_mix_receptance"])
+            if v6:
+                xk = h + (ffn_x[li] - h) * p.tensors[f + "time_maa_k"]
+                xr = h + (ffn_x[li] - h) * p.tensors[f + "time_maa_r"]
+            else:
+                xk = h * p.tensors[f + "time_mix_key"] + ffn_x[li] * (1 - p.tensors[f + "time_mix_key"])
+                xr = h * p.tensors[f + "time_mix_receptance"] + ffn_x[li] * (1 - p.tensors[f + "time_mix_receptance"])
             ffn_x[li] = h
             rr = torch.sigmoid(p.linears[f + "receptance"].w @ xr)
             kk2 = torch.square(torch.relu(p.linears[f + "key"].w @ xk))
@@ -79,8 +95,12 @@ def _naive_logits(m, tokens):
     return torch.stack(outs)
 
 
-def test_batched_chunked_forward_equals_naive_recurrence():
-    m = _model()
+import pytest
+
+
+@pytest.mark.parametrize("preset", ["tiny-rwkv5", "tiny-rwkv6"])
+def test_batched_chunked_forward_equals_naive_recurrence(preset):
+    m = _model(preset=preset)
     rng = np.random.default_rng(0)
     seq_a, seq_b = rng.integers(0, 32000, 7).tolist(), rng.integers(0, 32000, 5).tolist()
     want_a, want_b = _naive_logits(m, seq_a), _naive_logits(m, seq_b)
@@ -96,8 +116,9 @@ def test_batched_chunked_forward_equals_naive_recurrence():
     assert torch.allclose(m.logits(h, None), want_b, atol=1e-4)
 
 
-def test_engine_generates_with_recurrent_state():
-    eng = SyncMLCEngine("random://tiny-rwkv5?quant=q0f32&seed=4", "cpu",
+@pytest.mark.parametrize("preset", ["tiny-rwkv5", "tiny-rwkv6"])
+def test_engine_generates_with_recurrent_state(preset):
+    eng = SyncMLCEngine(f"random://{preset}?quant=q0f32&seed=4", "cpu",
                         engine_config=EngineConfig(mode="server", max_num_sequence=4, prefill_chunk_size=16,
                                                    max_total_sequence_length=1024))
     assert json.loads(eng.runtime.complete_config_json)["prefix_cache_mode"] == "disable"
