@@ -486,7 +486,7 @@ def test_wkv5_recurrence_kernel(head_size, per_token_decay):
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 14336), (77, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
-def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype):
+def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype, monkeypatch):
     """One to four tokens against q4f16_1 weights take the CUDA-core GEMV; rows that are not a multiple
     of the 32 rows of a CTA, a K that leaves lanes idle, bias, fp32 output."""
     torch.manual_seed(m * 1000 + n + k)
@@ -498,7 +498,7 @@ def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype):
     lw = ops.LinearWeight("q4", qw, qs, bias, quant, n, k, False).to("cuda")
     x = (torch.randn(m, k) * 0.5).half()
     want = x.float() @ wd.t() + bias.float()
-    assert ops._GEMV_Q4
+    monkeypatch.setattr(ops, "_GEMV_Q4", True)
     got = ops.linear(x.cuda(), lw, out_dtype=out_dtype)
     ops.check_status(torch.device("cuda"))
     assert got.dtype == out_dtype and got.shape == (m, n)
