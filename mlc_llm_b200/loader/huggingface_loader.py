@@ -273,6 +273,27 @@ def _chatglm(cfg: ModelConfig, m: Mapping) -> None:
     m.add("lm_head.weight", ["transformer.output_layer.weight"])
 
 
+def _llama4(cfg: ModelConfig, m: Mapping) -> None:
+    """Llama-4: ``feed_forward`` instead of ``mlp``; experts stored as [E, hidden, 2 * inter] / [E, inter, hidden]
+    (input-major), transposed here to the [E, out, in] form of the grouped GEMM; interleaved rotary rows
+    de-interleaved (reference: ``model/llama4/llama4_loader.py``)."""
+    pq, pk = _deinterleave_rows(cfg, cfg.num_attention_heads), _deinterleave_rows(cfg, cfg.num_key_value_heads)
+    _llama_like(cfg, m, mlp="feed_forward")
+    for i in range(cfg.num_hidden_layers):
+        s, d = f"model.layers.{i}.", f"model.layers.{i}."
+        m.add(d + "self_attn.qkv_proj.weight",
+              [s + "self_attn.q_proj.weight", s + "self_attn.k_proj.weight", s + "self_attn.v_proj.weight"],
+              lambda ts: torch.cat([pq(ts[0]), pk(ts[1]), ts[2]], 0))
+        if cfg.is_moe_layer(i):
+            f = s + "feed_forward."
+            m.add(d + "moe.gate.weight", [f + "router.weight"])
+            m.add(d + "moe.e1_e3.weight", [f + "experts.gate_up_proj"], lambda ts: ts[0].transpose(1, 2).contiguous())
+            m.add(d + "moe.e2.weight", [f + "experts.down_proj"], lambda ts: ts[0].transpose(1, 2).contiguous())
+            m.add(d + "moe.shared_expert.gate_up_proj.weight",
+                  [f + "shared_expert.gate_proj.weight", f + "shared_expert.up_proj.weight"], _cat0)
+            m.add(d + "moe.shared_expert.down_proj.weight", [f + "shared_expert.down_proj.weight"])
+
+
 def _qwen(cfg: ModelConfig, m: Mapping) -> None:
     """First-generation Qwen: GPT-2 style names, fused ``c_attn``; the MLP computes
     ``c_proj(w1(x) * silu(w2(x)))``, so ``w2`` is the gate (reference: ``model/qwen/qwen_loader.py``)."""
@@ -390,6 +411,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _gpt_neox(cfg, m)
     elif mt in ("gptj", "gpt_j"):
         _gptj(cfg, m)
+    elif mt in ("llama4", "llama4_text"):
+        _llama4(cfg, m)
     elif mt == "qwen":
         _qwen(cfg, m)
     elif mt in ("rwkv5", "rwkv6"):

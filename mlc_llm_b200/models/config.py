@@ -91,6 +91,8 @@ class ModelConfig:
 
     def is_moe_layer(self, layer: int) -> bool:
         # Qwen counts sparse layers as (layer + 1) % step == 0, DeepSeek as layer % freq == 0
+        if "moe_layers" in self.extra:  # explicit list (Llama-4)
+            return self.num_experts > 0 and layer in self.extra["moe_layers"]
         phase = int(self.extra.get("moe_layer_phase", 1))
         return (self.num_experts > 0 and layer >= self.first_moe_layer
                 and (layer + phase) % max(1, self.moe_layer_freq) == 0)
@@ -161,6 +163,40 @@ def _llama(cfg, mt):
     d["attention_bias"] = bool(_get(cfg, "attention_bias", default=False))
     d["attention_out_bias"] = d["attention_bias"]
     d["mlp_bias"] = bool(_get(cfg, "mlp_bias", default=False))
+    return d
+
+
+def _llama4(cfg, mt):
+    """Llama-4 text model: rotary layers with chunked attention and weightless q / k L2 norm, interleaved
+    with position-free layers whose queries are scaled by a temperature that grows with the position;
+    mixture-of-experts layers route on the top logit, scale the expert *input* by its sigmoid and add a shared
+    expert (reference: ``python/mlc_llm/model/llama4/llama4_model.py``)."""
+    if isinstance(cfg.get("text_config"), dict):
+        outer, cfg = cfg, dict(cfg["text_config"])
+        for k in ("context_window_size", "prefill_chunk_size", "tensor_parallel_shards", "max_batch_size"):
+            if k in outer and k not in cfg:
+                cfg[k] = outer[k]
+    d = _llama(cfg, mt)
+    layers = int(d["num_hidden_layers"])
+    expert_inter = int(_get(cfg, "intermediate_size", default=8192))
+    d["intermediate_size"] = int(_get(cfg, "intermediate_size_mlp", default=16384))
+    use_rope = _get(cfg, "no_rope_layers") or [int((i + 1) % 4 != 0) for i in range(layers)]
+    step = int(_get(cfg, "interleave_moe_layer_step", default=1))
+    moe_layers = _get(cfg, "moe_layers")
+    if moe_layers is None:
+        moe_layers = list(range(step - 1, layers, step))
+    chunk = int(_get(cfg, "attention_chunk_size", default=8192) or 0)
+    d.update(num_experts=int(_get(cfg, "num_local_experts", default=16)),
+             num_experts_per_tok=int(_get(cfg, "num_experts_per_tok", default=1)),
+             moe_intermediate_size=expert_inter, shared_expert_intermediate_size=expert_inter,
+             moe_router="llama4_sigmoid",
+             layer_attn_kinds=["mha_chunked" if r else "mha_nope" for r in use_rope])
+    d["extra"] = {"moe_layers": [int(x) for x in moe_layers],
+                  "llama4": {"use_qk_norm": bool(_get(cfg, "use_qk_norm", default=True)),
+                             "attn_temperature_tuning": bool(_get(cfg, "attn_temperature_tuning", default=True)),
+                             "floor_scale": float(_get(cfg, "floor_scale", default=8192)),
+                             "attn_scale": float(_get(cfg, "attn_scale", default=0.1)),
+                             "attention_chunk_size": chunk}}
     return d
 
 
@@ -526,7 +562,7 @@ _PARSERS = {
     "gpt_j": _gptj, "glm": _glm, "chatglm": _glm, "rwkv5": _rwkv5, "rwkv6": _rwkv5,
     "gpt_bigcode": _gpt2, "starcoder2": _starcoder2, "stablelm": _stablelm, "stablelm_epoch": _stablelm,
     "olmo": _olmo, "olmo2": _olmo, "mixtral": _mixtral, "qwen2_moe": _qwen_moe, "qwen3_moe": _qwen_moe,
-    "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,
+    "llama4": _llama4, "llama4_text": _llama4, "internlm": _internlm, "internlm2": _llama, "baichuan": _llama, "orion": _orion, "minicpm": _minicpm,
     "deepseek": _deepseek, "nemotron": _nemotron, "cohere": _cohere, "deepseek_v2": _deepseek_v2, "eagle": _eagle, "medusa": _medusa, "llava": _llava,
     "aquila": _llama,
     "yi": _llama, "tinyllama": _llama,

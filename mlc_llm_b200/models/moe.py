@@ -28,6 +28,30 @@ def _group_limited_router(logits: torch.Tensor, k: int, n_group: int, topk_group
     return w.float().contiguous(), idx.to(torch.int32).contiguous()  # fp32 weights, like ops.moe_router
 
 
+def _llama4_moe(model, li: int, h: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+    """Llama-4 routing: top-k over the raw logits; the *input* of each chosen expert is scaled by the sigmoid of
+    its logit, the expert outputs are summed unweighted, and a shared expert is added (reference:
+    ``python/mlc_llm/model/llama4/llama4_model.py:363-410``)."""
+    c = model.cfg
+    if c.expert_parallel and model.comm is not None and model.tp > 1:
+        raise NotImplementedError("expert parallelism is not available for the Llama-4 router")
+    pre = f"model.layers.{li}.moe."
+    t, k = h.shape[0], c.num_experts_per_tok
+    top_v, idx = torch.topk(logits.float(), k, dim=-1)
+    scores = torch.sigmoid(top_v)                                         # [T, k]
+    experts = idx.to(torch.int32).contiguous()
+    offsets, sorted_pos, src_token = ops.moe_permute(experts, c.num_experts)
+    row_scale = torch.empty(t * k, dtype=torch.float32, device=h.device)
+    row_scale[sorted_pos.long()] = scores.reshape(-1)
+    xp = (ops.row_gather(h, src_token).float() * row_scale.unsqueeze(-1)).to(h.dtype)
+    h1 = ops.grouped_linear(xp, model.p.linears[pre + "e1_e3"], offsets)
+    y = ops.grouped_linear(ops.act_mul(h1, "silu"), model.p.linears[pre + "e2"], offsets)
+    ones = torch.ones(t, k, dtype=torch.float32, device=h.device)
+    out = ops.moe_combine(y, ones, sorted_pos, None)
+    g = ops.linear(h, model.p.linears[pre + "shared_expert.gate_up_proj"])
+    return out + ops.linear(ops.act_mul(g, "silu"), model.p.linears[pre + "shared_expert.down_proj"])
+
+
 def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
     c = model.cfg
     pre = f"model.layers.{li}.moe."
@@ -35,6 +59,8 @@ def moe_block(model, li: int, h: torch.Tensor) -> torch.Tensor:
     k = c.num_experts_per_tok
     gate_w = model.p.tensors[pre + "gate.weight"]
     logits = ops.linear(h, ops.dense_weight(gate_w))
+    if c.moe_router == "llama4_sigmoid":
+        return _llama4_moe(model, li, h, logits)
     renorm = c.norm_topk_prob if c.moe_router == "softmax_topk" else True
     if c.extra.get("topk_method") == "group_limited_greedy" and c.extra.get("n_group", 1) > 1:
         weights, experts = _group_limited_router(logits, k, c.extra["n_group"], c.extra["topk_group"], renorm)

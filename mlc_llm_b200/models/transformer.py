@@ -205,18 +205,48 @@ class DecoderModel:
                              c.rms_norm_eps, c.norm_weight_offset)
             heads[:, :hq] = qn.view(t, hq, d)
             heads[:, hq:hq + hkv] = kn.view(t, hkv, d)
-        sliding = c.layer_attn_kinds is not None and c.layer_attn_kinds[li] == "mha_sliding"
+        kind = c.layer_attn_kinds[li] if c.layer_attn_kinds is not None else None
+        sliding = kind == "mha_sliding"
         inv = self.inv_freq_local if (sliding and self.inv_freq_local is not None) else self.inv_freq
         local = li - self.layers.start
-        ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, inv, hq, hkv, d,
-                        c.rotary_dim if inv is not None else 0, self.page)
         kvstart = b.q_kvstart
+        l4 = c.extra.get("llama4")
+        if l4 is not None:
+            t = qkv.shape[0]
+            heads = qkv.view(t, hq + 2 * hkv, d)
+            if kind == "mha_nope":
+                # position-free layer: no rotation; queries are scaled by a temperature that grows with
+                # the position (llama4_model.py: attn_temperature_tuning)
+                ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, None, hq, hkv, d, 0, self.page)
+                if l4["attn_temperature_tuning"]:
+                    pos = b.positions.float()
+                    scale = torch.log1p(torch.floor((pos + 1.0) / l4["floor_scale"])) * l4["attn_scale"] + 1.0
+                    heads[:, :hq] = (heads[:, :hq].float() * scale.view(t, 1, 1)).to(qkv.dtype)
+            else:
+                if l4["use_qk_norm"]:
+                    # rotate without appending, L2-normalise q and k per head (no weight), then append
+                    ops.rope_append(qkv, self.kv_pages[local], b.positions, torch.full_like(b.slots, -1), inv,
+                                    hq, hkv, d, c.rotary_dim, self.page)
+                    qk = heads[:, : hq + hkv].float()
+                    qk = qk * torch.rsqrt(qk.pow(2).mean(-1, keepdim=True) + c.rms_norm_eps)
+                    heads[:, : hq + hkv] = qk.to(qkv.dtype)
+                    ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, None, hq, hkv, d, 0, self.page)
+                else:
+                    ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, inv, hq, hkv, d,
+                                    c.rotary_dim, self.page)
+                chunk = int(l4["attention_chunk_size"])
+                if chunk > 0:  # a token attends inside its own chunk of positions only
+                    kvstart = (torch.div(b.q_kvlen - 1, chunk, rounding_mode="floor") * chunk).to(torch.int32)
+        else:
+            ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, inv, hq, hkv, d,
+                            c.rotary_dim if inv is not None else 0, self.page)
         if sliding:
             w = int(c.extra.get("layer_sliding_window", 4096))
             kvstart = torch.clamp(b.q_kvlen - w, min=0).to(torch.int32)
         out = ops.paged_attention(qkv[:, : hq * d], self.kv_pages[local], b.q_seq, b.q_kvlen, b.page_indptr,
                                   b.page_indices, hq, hkv, d, self.page, self.sm_scale, q_kvstart=kvstart,
-                                  sink=max(0, c.attention_sink_size) if kvstart is not None and not sliding else 0,
+                                  sink=max(0, c.attention_sink_size) if kvstart is not None and not sliding
+                                  and l4 is None else 0,
                                   tree_mask=b.tree_mask, softcap=c.attn_logit_softcap, plan=b.attn_plan)
         return out.reshape(out.shape[0], hq * d)
 
@@ -254,7 +284,7 @@ class DecoderModel:
         plain = (c.norm_type == "rms" and not c.parallel_residual and not c.post_attention_norm
                  and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
                  and c.gated_mlp and c.position_embedding != "learned" and "residual_scale" not in c.extra
-                 and "mla" not in c.extra
+                 and "mla" not in c.extra and "llama4" not in c.extra
                  and self.first_stage and self.last_stage and self.dtype in (torch.float16, torch.bfloat16))
         self.fused = fused if plain else None
         return self.fused is not None

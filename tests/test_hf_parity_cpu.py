@@ -41,6 +41,11 @@ CASES = {
         moe_intermediate_size=24, first_k_dense_replace=1, topk_method="greedy", n_group=4,
         topk_group=2, routed_scaling_factor=1.5, norm_topk_prob=False)),
     "glm": ("GlmConfig", dict(BASE, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)),
+    "llama4_text": ("Llama4TextConfig", dict(
+        hidden_size=64, intermediate_size=48, intermediate_size_mlp=112, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, vocab_size=160, max_position_embeddings=128, num_local_experts=4,
+        num_experts_per_tok=1, interleave_moe_layer_step=2, use_qk_norm=True, attn_temperature_tuning=True,
+        floor_scale=8, attn_scale=0.1, attention_chunk_size=8, rope_theta=10000.0, pad_token_id=0)),
     "mixtral": ("MixtralConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
     "qwen2_moe": ("Qwen2MoeConfig", dict(BASE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                          shared_expert_intermediate_size=80, decoder_sparse_step=1,
