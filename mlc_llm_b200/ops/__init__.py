@@ -97,7 +97,7 @@ def _gemm_scratch(device: torch.device):
 
 
 _LINEAR_OBSERVER = None
-_GEMV_Q4 = os.environ.get("MLCB_GEMV_Q4", "0") != "0"
+_GEMV_Q4 = os.environ.get("MLCB_GEMV_Q4", "1") != "0"
 
 
 def set_linear_observer(fn) -> None:

@@ -79,3 +79,46 @@ def test_metrics_and_debug(server):
     assert r.status_code == 200 and "engine_prefill_time_sum" in r.json()
     r = requests.post(server.base_url + "/debug/reset_engine", json={"model": MODEL}, timeout=30)
     assert r.status_code == 200
+
+
+def test_json_mode_over_rest(server):
+    """response_format with a JSON schema: the grammar constrains decoding (jump-forward by default) and
+    the usage block reports the forced tokens."""
+    schema = json.dumps({"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]})
+    body = {"model": MODEL, "messages": [{"role": "user", "content": "say yes"}], "max_tokens": 24,
+            "temperature": 0.0, "response_format": {"type": "json_object", "schema": schema}}
+    r = requests.post(server.base_url + "/v1/chat/completions", json=body, headers=H, timeout=120)
+    assert r.status_code == 200, r.text
+    out = r.json()
+    text = out["choices"][0]["message"]["content"]
+    assert text.lstrip().startswith("{")   # the grammar admits white space after the brace
+    if out["choices"][0]["finish_reason"] == "stop":
+        assert json.loads(text)["ok"] in (True, False)
+    assert "jump_forward_tokens" in out["usage"]["extra"]
+
+
+def test_image_request_over_rest():
+    """A LLaVA-type model behind the REST server takes `image_url` content parts (data URLs)."""
+    import base64
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    model = "random://tiny-llava?quant=q0f32&seed=2"
+    srv = PopenServer(model, "cpu", mode="local", port=_port())
+    srv.start(timeout=180)
+    try:
+        img = Image.fromarray((np.random.default_rng(0).random((30, 30, 3)) * 255).astype(np.uint8))
+        buf = io.BytesIO()
+        img.save(buf, format="PNG")
+        url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+        mk = lambda content: {"model": model, "messages": [{"role": "user", "content": content}],
+                              "max_tokens": 4, "temperature": 0.0}
+        plain = requests.post(srv.base_url + "/v1/chat/completions", json=mk("describe"), timeout=120).json()
+        with_img = requests.post(srv.base_url + "/v1/chat/completions", timeout=120, json=mk(
+            [{"type": "text", "text": "describe"}, {"type": "image_url", "image_url": {"url": url}}])).json()
+        assert with_img["usage"]["prompt_tokens"] == plain["usage"]["prompt_tokens"] + 4 + 1
+        assert with_img["usage"]["completion_tokens"] == 4
+    finally:
+        srv.terminate()
