@@ -103,8 +103,17 @@ def bench_gemv_q4(small: bool):
         qs = (torch.rand(n, k // 32, device=dev) * 0.01).half()
         lw = ops.LinearWeight("q4", qw, qs, None, quant, n, k, device_layout=True)
         byt = n * k // 2 + n * (k // 32) * 2 + m * k * 2 + m * n * 2
-        for name, flag in (("gemv_q4", True), ("gemm_q4_tensor_core", False)):
+        try:
+            set_form = ops.lib().mlcb_gemv_set_form
+            variants = (("gemv_q4_split_k", True, 2), ("gemv_q4_row_per_warp", True, 1),
+                        ("gemm_q4_tensor_core", False, 0))
+        except AttributeError:  # library built before the second form existed
+            set_form = None
+            variants = (("gemv_q4", True, 0), ("gemm_q4_tensor_core", False, 0))
+        for name, flag, form in variants:
             ops._GEMV_Q4 = flag  # pylint: disable=protected-access
+            if set_form is not None and form:
+                set_form(form)
             med, best = _time(lambda: ops.linear(x, lw), flush=flush)
             ops.check_status(dev)
             rec = {"kernel": name, "M": m, "N": n, "K": k, "ms_median": round(med, 4), "ms_best": round(best, 4),
@@ -113,6 +122,8 @@ def bench_gemv_q4(small: bool):
             print(json.dumps(rec), flush=True)
             out.append(rec)
         ops._GEMV_Q4 = True  # pylint: disable=protected-access
+        if set_form is not None:
+            set_form(2)
     return out
 
 

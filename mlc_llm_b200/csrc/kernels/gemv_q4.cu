@@ -106,9 +106,142 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
     }
 }
 
+// Second form: KS warps of a CTA share each group of four rows and split K between them (narrow layers
+// have too few rows to fill the GPU with one warp per row group), and the loads of the next step are
+// issued before the arithmetic of the current one (PREFETCH; only where the registers allow, M <= 2).
+template <typename TO, int MMAX, int KS, bool PREFETCH>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+    gemv_q4_split_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w,
+                         const __half* __restrict__ scale, const __half* __restrict__ bias, TO* __restrict__ y,
+                         int m_count, int N, int K, int ldx, int ldy) {
+  __shared__ float partial[GEMV_WARPS][GEMV_ROWS][MMAX];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int GROUPS_PER_CTA = GEMV_WARPS / KS;     // row groups per CTA
+  const int rg = warp / KS, ks = warp % KS;           // row group inside the CTA, K slice of this warp
+  const int row0 = (blockIdx.x * GROUPS_PER_CTA + rg) * GEMV_ROWS;
+  const int groups = K >> 5;
+  const size_t words_per_row = static_cast<size_t>(K) >> 3;
+  float acc[GEMV_ROWS][MMAX];
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) acc[r][m] = 0.f;
+  const __half2 off = __float2half2_rn(1031.f);
+
+  uint4 q[GEMV_ROWS], qn[GEMV_ROWS];
+  float s[GEMV_ROWS], sn[GEMV_ROWS];
+  uint4 xr[MMAX][4], xn[MMAX][4];
+  auto load = [&](int g, uint4 (&qq)[GEMV_ROWS], float (&ss)[GEMV_ROWS], uint4 (&xx)[MMAX][4]) {
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const int row = row0 + r;
+      if (row < N && g < groups) {
+        qq[r] = __ldg(reinterpret_cast<const uint4*>(w + row * words_per_row) + g);
+        ss[r] = __half2float(__ldg(scale + static_cast<size_t>(row) * groups + g));
+      } else {
+        qq[r] = make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+        ss[r] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      if (m < m_count && g < groups) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * ldx + (g << 5));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xx[m][i] = __ldg(xp + i);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xx[m][i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  auto compute = [&](const uint4 (&qq)[GEMV_ROWS], const float (&ss)[GEMV_ROWS], const uint4 (&xx)[MMAX][4]) {
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const uint32_t words[4] = {qq[r].x, qq[r].y, qq[r].z, qq[r].w};
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        __half2 hv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t v = ((words[wd] >> (4 * j)) & 0x000f000fu) | 0x64006400u;
+          hv[j] = __hsub2(*reinterpret_cast<__half2*>(&v), off);
+        }
+#pragma unroll
+        for (int m = 0; m < MMAX; ++m) {
+          const uint32_t xw[4] = {xx[m][wd].x, xx[m][wd].y, xx[m][wd].z, xx[m][wd].w};
+          __half2 p = __hmul2(hv[0], *reinterpret_cast<const __half2*>(&xw[0]));
+          p = __hfma2(hv[1], *reinterpret_cast<const __half2*>(&xw[1]), p);
+          p = __hfma2(hv[2], *reinterpret_cast<const __half2*>(&xw[2]), p);
+          p = __hfma2(hv[3], *reinterpret_cast<const __half2*>(&xw[3]), p);
+          const float2 f = __half22float2(p);
+          acc[r][m] += ss[r] * (f.x + f.y);
+        }
+      }
+    }
+  };
+  const int step = 32 * KS;
+  int g = ks * 32 + lane;
+  if (row0 < N) {
+    if (PREFETCH) {
+      load(g, q, s, xr);
+      while (g < groups) {
+        load(g + step, qn, sn, xn);   // past the end: zero weights, no memory access
+        compute(q, s, xr);
+#pragma unroll
+        for (int r = 0; r < GEMV_ROWS; ++r) { q[r] = qn[r]; s[r] = sn[r]; }
+#pragma unroll
+        for (int m = 0; m < MMAX; ++m)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) xr[m][i] = xn[m][i];
+        g += step;
+      }
+    } else {
+      for (; g < groups; g += step) {
+        load(g, q, s, xr);
+        compute(q, s, xr);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MMAX; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) partial[warp][r][m] = v;
+    }
+  __syncthreads();
+  // one thread per (row group, row, token) adds the K slices
+  const int items = GROUPS_PER_CTA * GEMV_ROWS * MMAX;
+  for (int i = threadIdx.x; i < items; i += blockDim.x) {
+    const int g2 = i / (GEMV_ROWS * MMAX), r = (i / MMAX) % GEMV_ROWS, m = i % MMAX;
+    const int row = (blockIdx.x * GROUPS_PER_CTA + g2) * GEMV_ROWS + r;
+    if (row < N && m < m_count) {
+      float v = 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < KS; ++k2) v += partial[g2 * KS + k2][r][m];
+      if (bias) v += __half2float(bias[row]);
+      y[static_cast<size_t>(m) * ldy + row] = Cvt<TO>::from_f(v);
+    }
+  }
+}
+
 }  // namespace mlcb
 
 using namespace mlcb;
+
+static int g_gemv_form = -1;  // -1 unread; 1 = one warp per row group; 2 = K split across warps + prefetch
+static int gemv_form() {
+  if (g_gemv_form < 0) {
+    const char* e = getenv("MLCB_GEMV_FORM");
+    g_gemv_form = (e && e[0] == '1') ? 1 : 2;
+  }
+  return g_gemv_form;
+}
+// Test / benchmark hook.
+MLCB_API void mlcb_gemv_set_form(int form) { g_gemv_form = form; }
 
 // x: [M, K] fp16 (row stride ldx, 16-byte aligned rows), w: packed int4 [N, K/8] in the device nibble
 // order, scale: [N, K/32] fp16, y: [M, N] (row stride ldy) fp16 (out_dtype 0) or fp32 (out_dtype 2).
@@ -120,6 +253,41 @@ MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const
   if (M > 4 || K <= 0 || K % 32 != 0 || ldx % 8 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -1;
   if (out_dtype != 0 && out_dtype != 2) return -1;
+  if (gemv_form() == 2) {
+    // K slices per row group: enough warps to cover the SMs several times over, at least one step each
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long row_groups = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+    int ks = 1;
+    while (ks < GEMV_WARPS && row_groups * ks < static_cast<long long>(sms) * 32 && (K >> 5) >= 32 * ks * 2) ks *= 2;
+    const int groups_per_cta = GEMV_WARPS / ks;
+    const int grid2 = static_cast<int>((row_groups + groups_per_cta - 1) / groups_per_cta);
+#define GEMV_SPLIT(TO, MM, KS, PF)                                                                          \
+  gemv_q4_split_kernel<TO, MM, KS, PF><<<grid2, GEMV_WARPS * 32, 0, stream>>>(                               \
+      static_cast<const __half*>(x), static_cast<const uint32_t*>(w), static_cast<const __half*>(scale),     \
+      static_cast<const __half*>(bias), static_cast<TO*>(y), M, N, K, ldx, ldy)
+#define GEMV_SPLIT_KS(TO, MM, PF)                                     \
+  do {                                                                \
+    if (ks == 1) GEMV_SPLIT(TO, MM, 1, PF);                           \
+    else if (ks == 2) GEMV_SPLIT(TO, MM, 2, PF);                      \
+    else if (ks == 4) GEMV_SPLIT(TO, MM, 4, PF);                      \
+    else GEMV_SPLIT(TO, MM, 8, PF);                                   \
+  } while (0)
+    if (out_dtype == 0) {
+      if (M == 1) GEMV_SPLIT_KS(__half, 1, true);
+      else if (M == 2) GEMV_SPLIT_KS(__half, 2, true);
+      else GEMV_SPLIT_KS(__half, 4, false);
+    } else {
+      if (M == 1) GEMV_SPLIT_KS(float, 1, true);
+      else if (M == 2) GEMV_SPLIT_KS(float, 2, true);
+      else GEMV_SPLIT_KS(float, 4, false);
+    }
+#undef GEMV_SPLIT_KS
+#undef GEMV_SPLIT
+    count_launch();
+    return static_cast<int>(cudaGetLastError());
+  }
   const int rows_per_cta = GEMV_WARPS * GEMV_ROWS;
   const int grid = (N + rows_per_cta - 1) / rows_per_cta;
 #define GEMV_LAUNCH(TO, MM)                                                                             \

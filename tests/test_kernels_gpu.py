@@ -483,10 +483,11 @@ def test_wkv5_recurrence_kernel(head_size, per_token_decay):
         assert torch.equal(a[0].cpu(), b[0])  # the other layer's rows are untouched
 
 
+@pytest.mark.parametrize("form", [1, 2])
 @pytest.mark.parametrize("m", [1, 2, 3, 4])
-@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 14336), (77, 128)])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 14336), (77, 128), (28672, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
-def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype, monkeypatch):
+def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype, form, monkeypatch):
     """One to four tokens against q4f16_1 weights take the CUDA-core GEMV; rows that are not a multiple
     of the 32 rows of a CTA, a K that leaves lanes idle, bias, fp32 output."""
     torch.manual_seed(m * 1000 + n + k)
@@ -499,7 +500,11 @@ def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype, monkeypatch):
     x = (torch.randn(m, k) * 0.5).half()
     want = x.float() @ wd.t() + bias.float()
     monkeypatch.setattr(ops, "_GEMV_Q4", True)
-    got = ops.linear(x.cuda(), lw, out_dtype=out_dtype)
+    ops.lib().mlcb_gemv_set_form(form)   # 1: one warp per four rows; 2: K split across warps + prefetch
+    try:
+        got = ops.linear(x.cuda(), lw, out_dtype=out_dtype)
+    finally:
+        ops.lib().mlcb_gemv_set_form(2)
     ops.check_status(torch.device("cuda"))
     assert got.dtype == out_dtype and got.shape == (m, n)
     err = (got.float().cpu() - want).abs().max()
