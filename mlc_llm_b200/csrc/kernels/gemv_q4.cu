@@ -20,6 +20,26 @@ namespace mlcb {
 constexpr int GEMV_ROWS = 4;    // rows per warp
 constexpr int GEMV_WARPS = 8;   // warps per CTA
 
+// Eight weights of one packed word -> four half2 values (q - 7), in element order.  Pairs 0 and 2 sit in
+// the low nibble of each half-word (of the word, and of the word shifted right by 8): 0x6400 | q is
+// 1024 + q.  Pairs 1 and 3 sit one nibble higher: 0x6400 | (q << 4) is 1024 + 16 q, and one fused
+// multiply-add (x 1/16, - 71) brings it to q - 7.  One shift, four logic ops and four arithmetic ops
+// per word; every step is exact in fp16.
+__device__ __forceinline__ void unpack8_q4(uint32_t wv, __half2 (&hv)[4]) {
+  const __half2 off = __float2half2_rn(1031.f);
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  const __half2 off_hi = __float2half2_rn(-71.f);
+  const uint32_t w8 = wv >> 8;
+  uint32_t a = (wv & 0x000f000fu) | 0x64006400u;
+  uint32_t b = (wv & 0x00f000f0u) | 0x64006400u;
+  uint32_t c = (w8 & 0x000f000fu) | 0x64006400u;
+  uint32_t d = (w8 & 0x00f000f0u) | 0x64006400u;
+  hv[0] = __hsub2(*reinterpret_cast<__half2*>(&a), off);
+  hv[1] = __hfma2(*reinterpret_cast<__half2*>(&b), sixteenth, off_hi);
+  hv[2] = __hsub2(*reinterpret_cast<__half2*>(&c), off);
+  hv[3] = __hfma2(*reinterpret_cast<__half2*>(&d), sixteenth, off_hi);
+}
+
 template <typename TO, int MMAX>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
     gemv_q4_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w, const __half* __restrict__ scale,
@@ -72,19 +92,20 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
     for (int r = 0; r < GEMV_ROWS; ++r) {
       const uint32_t words[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
 #pragma unroll
-      for (int wd = 0; wd < 4; ++wd) {
-        __half2 hv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t v = ((words[wd] >> (4 * j)) & 0x000f000fu) | 0x64006400u;
-          hv[j] = __hsub2(*reinterpret_cast<__half2*>(&v), off);  // (q - 7), exact
-        }
+      for (int wd = 0; wd < 4; wd += 2) {   // two words (16 weights) per trip to fp32
+        __half2 ha[4], hb[4];
+        unpack8_q4(words[wd], ha);
+        unpack8_q4(words[wd + 1], hb);
 #pragma unroll
         for (int m = 0; m < MMAX; ++m) {
-          __half2 p = __hmul2(hv[0], xv[m][4 * wd]);
-          p = __hfma2(hv[1], xv[m][4 * wd + 1], p);
-          p = __hfma2(hv[2], xv[m][4 * wd + 2], p);
-          p = __hfma2(hv[3], xv[m][4 * wd + 3], p);
+          __half2 p = __hmul2(ha[0], xv[m][4 * wd]);
+          p = __hfma2(ha[1], xv[m][4 * wd + 1], p);
+          p = __hfma2(ha[2], xv[m][4 * wd + 2], p);
+          p = __hfma2(ha[3], xv[m][4 * wd + 3], p);
+          p = __hfma2(hb[0], xv[m][4 * wd + 4], p);
+          p = __hfma2(hb[1], xv[m][4 * wd + 5], p);
+          p = __hfma2(hb[2], xv[m][4 * wd + 6], p);
+          p = __hfma2(hb[3], xv[m][4 * wd + 7], p);
           const float2 f = __half22float2(p);
           acc[r][m] += s[r] * (f.x + f.y);
         }
@@ -108,7 +129,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
 
 // Second form: KS warps of a CTA share each group of four rows and split K between them (narrow layers
 // have too few rows to fill the GPU with one warp per row group), and the loads of the next step are
-// issued before the arithmetic of the current one (PREFETCH; only where the registers allow, M <= 2).
+// issued before the arithmetic of the current one (PREFETCH; measured slower than relying on occupancy:
+// 119 us vs 100 us on the 128256 x 4096 LM head, so the launcher does not select it).
 template <typename TO, int MMAX, int KS, bool PREFETCH>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
     gemv_q4_split_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w,
@@ -160,20 +182,22 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
     for (int r = 0; r < GEMV_ROWS; ++r) {
       const uint32_t words[4] = {qq[r].x, qq[r].y, qq[r].z, qq[r].w};
 #pragma unroll
-      for (int wd = 0; wd < 4; ++wd) {
-        __half2 hv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t v = ((words[wd] >> (4 * j)) & 0x000f000fu) | 0x64006400u;
-          hv[j] = __hsub2(*reinterpret_cast<__half2*>(&v), off);
-        }
+      for (int wd = 0; wd < 4; wd += 2) {
+        __half2 ha[4], hb[4];
+        unpack8_q4(words[wd], ha);
+        unpack8_q4(words[wd + 1], hb);
 #pragma unroll
         for (int m = 0; m < MMAX; ++m) {
-          const uint32_t xw[4] = {xx[m][wd].x, xx[m][wd].y, xx[m][wd].z, xx[m][wd].w};
-          __half2 p = __hmul2(hv[0], *reinterpret_cast<const __half2*>(&xw[0]));
-          p = __hfma2(hv[1], *reinterpret_cast<const __half2*>(&xw[1]), p);
-          p = __hfma2(hv[2], *reinterpret_cast<const __half2*>(&xw[2]), p);
-          p = __hfma2(hv[3], *reinterpret_cast<const __half2*>(&xw[3]), p);
+          const uint32_t xa[4] = {xx[m][wd].x, xx[m][wd].y, xx[m][wd].z, xx[m][wd].w};
+          const uint32_t xb[4] = {xx[m][wd + 1].x, xx[m][wd + 1].y, xx[m][wd + 1].z, xx[m][wd + 1].w};
+          __half2 p = __hmul2(ha[0], *reinterpret_cast<const __half2*>(&xa[0]));
+          p = __hfma2(ha[1], *reinterpret_cast<const __half2*>(&xa[1]), p);
+          p = __hfma2(ha[2], *reinterpret_cast<const __half2*>(&xa[2]), p);
+          p = __hfma2(ha[3], *reinterpret_cast<const __half2*>(&xa[3]), p);
+          p = __hfma2(hb[0], *reinterpret_cast<const __half2*>(&xb[0]), p);
+          p = __hfma2(hb[1], *reinterpret_cast<const __half2*>(&xb[1]), p);
+          p = __hfma2(hb[2], *reinterpret_cast<const __half2*>(&xb[2]), p);
+          p = __hfma2(hb[3], *reinterpret_cast<const __half2*>(&xb[3]), p);
           const float2 f = __half22float2(p);
           acc[r][m] += ss[r] * (f.x + f.y);
         }
@@ -275,12 +299,12 @@ MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const
     else GEMV_SPLIT(TO, MM, 8, PF);                                   \
   } while (0)
     if (out_dtype == 0) {
-      if (M == 1) GEMV_SPLIT_KS(__half, 1, true);
-      else if (M == 2) GEMV_SPLIT_KS(__half, 2, true);
+      if (M == 1) GEMV_SPLIT_KS(__half, 1, false);
+      else if (M == 2) GEMV_SPLIT_KS(__half, 2, false);
       else GEMV_SPLIT_KS(__half, 4, false);
     } else {
-      if (M == 1) GEMV_SPLIT_KS(float, 1, true);
-      else if (M == 2) GEMV_SPLIT_KS(float, 2, true);
+      if (M == 1) GEMV_SPLIT_KS(float, 1, false);
+      else if (M == 2) GEMV_SPLIT_KS(float, 2, false);
       else GEMV_SPLIT_KS(float, 4, false);
     }
 #undef GEMV_SPLIT_KS
