@@ -359,7 +359,9 @@ verify_tree_kernel(const float* __restrict__ draft_probs, const int* __restrict_
     const float q = draft_probs[static_cast<size_t>(child) * vocab + tok];
     const float u = uniform[child];
     __syncthreads();
-    if (p >= u * q) {
+    // p > 0: a candidate the draft distribution gives no mass (a lower-ranked child of a draft tree under
+    // greedy sampling has q == 0) must not pass on 0 >= 0
+    if (p > 0.f && p >= u * q) {
       parent = child;
       child = first_child[child];
     } else {

@@ -102,7 +102,7 @@ class EngineImpl : public Engine {
     spec_ = cfg_.speculative_mode != SpeculativeMode::kDisable && models_.size() > 1;
     feature_fed_draft_ = cfg_.speculative_mode == SpeculativeMode::kEagle ||
                          cfg_.speculative_mode == SpeculativeMode::kMedusa;
-    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * 2 * (MaxDraftLength() + 1));
+    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * DraftSlotsPerSequence());
     std::random_device rd;
     seed_rng_.seed(rd());
   }
@@ -383,7 +383,7 @@ class EngineImpl : public Engine {
     prefix_cache_.Reset();
     for (auto& kv : kv_) kv->Clear();
     ids_.Reset();
-    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * 2 * (MaxDraftLength() + 1));
+    if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * DraftSlotsPerSequence());
     metrics_.Reset();
     if (backend_) backend_->Reset();
   }
@@ -406,6 +406,17 @@ class EngineImpl : public Engine {
  private:
   // ---------------------------------------------------------------- helpers
   int MaxDraftLength() const { return cfg_.spec_draft_length > 0 ? cfg_.spec_draft_length : 4; }
+  // Distribution slots one sequence can hold at once: a chain needs one per draft token; a tree one per
+  // node that gets children (1 + w + ... + w^(k-1)).
+  int DraftSlotsPerSequence() const {
+    const int k = MaxDraftLength();
+    int rows = 1, level = 1;
+    for (int d = 1; d < k; ++d) {
+      level *= std::max(1, cfg_.spec_tree_width);
+      rows += level;
+    }
+    return std::max(2 * (k + 1), rows + 1);
+  }
 
   void Trace(const std::string& id, const std::string& ev) {
     if (trace_) trace_->AddEvent(id, ev);
@@ -1096,17 +1107,104 @@ class EngineImpl : public Engine {
     backend_->ForwardSample(1, plan, token_ids, embed_handles, none);
   }
 
+  // Draft tree (spec_tree_width > 1; reference: cpp/serve/engine_actions/batch_draft.cc:150-290): every
+  // round gives each leaf `width` children, the most probable tokens of the draft model after that leaf;
+  // the children share the slot that holds the leaf's distribution.  Round 0 feeds the tokens the draft
+  // model has not seen and grows the first level; each later round feeds the whole tree built so far as
+  // one chunk (the tree mask covers a chunk, so earlier levels are recomputed rather than left in the
+  // KV, which keeps siblings invisible to each other) and grows its leaves.
+  void DraftTree(const std::vector<EntryRef>& ready, int k, int width, std::vector<int64_t>* spec_kv) {
+    std::vector<int> level_begin(ready.size(), 0);  // first node of the deepest level, per sequence
+    for (int round = 0; round < k; ++round) {
+      std::vector<int64_t> seq_ids;
+      std::vector<int32_t> lens, token_ids, tree_parents;
+      SampleParams sp;
+      std::vector<std::pair<size_t, int>> row_owner;  // (sequence, node that the row's distribution follows; -1 = root)
+      int32_t off = 0;
+      for (size_t i = 0; i < ready.size(); ++i) {
+        EntryRef r = ready[i];
+        RequestStateEntry& e = r.e();
+        ModelState& ds = e.mstates[1];
+        if (!kv_[1]->Has(ds.internal_id)) kv_[1]->AddSequence(ds.internal_id);
+        seq_ids.push_back(ds.internal_id);
+        if (round == 0) {
+          const int64_t total = r.rs->request.prompt_tokens + static_cast<int64_t>(e.committed_tokens.size());
+          int64_t lag = total - kv_[1]->SequenceLength(ds.internal_id);
+          if (lag > static_cast<int64_t>(e.committed_tokens.size()))
+            throw std::runtime_error("Engine: draft model KV lags behind the prompt");
+          for (int64_t j = static_cast<int64_t>(e.committed_tokens.size()) - lag;
+               j < static_cast<int64_t>(e.committed_tokens.size()); ++j) {
+            token_ids.push_back(e.committed_tokens[j].token);
+            tree_parents.push_back(static_cast<int32_t>(j - (static_cast<int64_t>(e.committed_tokens.size()) - lag)) - 1);
+          }
+          lens.push_back(static_cast<int32_t>(lag));
+          off += static_cast<int32_t>(lag);
+          AddSampleRow(&sp, r, off - 1);
+          row_owner.emplace_back(i, -1);
+        } else {
+          // drop the previous round's speculative entries, then feed the whole tree
+          if ((*spec_kv)[i] > 0) kv_[1]->PopN(ds.internal_id, (*spec_kv)[i]);
+          const int nodes = static_cast<int>(ds.draft_tokens.size());
+          for (int j = 0; j < nodes; ++j) {
+            token_ids.push_back(ds.draft_tokens[j].token);
+            tree_parents.push_back(ds.draft_parents[j]);  // -1: hangs under the last committed token
+          }
+          lens.push_back(nodes);
+          (*spec_kv)[i] = nodes;
+          for (int j = level_begin[i]; j < nodes; ++j) {
+            AddSampleRow(&sp, r, off + j);
+            row_owner.emplace_back(i, j);
+          }
+          off += nodes;
+        }
+      }
+      if (round == 0) std::fill(spec_kv->begin(), spec_kv->end(), 0);
+      for (size_t row = 0; row < row_owner.size(); ++row) {
+        const int slot = draft_slots_.Alloc();
+        sp.prob_slots.push_back(slot);
+      }
+      sp.num_top_logprobs = std::max(sp.num_top_logprobs, width);
+      std::vector<int64_t> embed_handles(token_ids.size(), -1);
+      ForwardPlan plan = round == 0 ? kv_[1]->BeginForward(seq_ids, lens)
+                                    : kv_[1]->BeginForward(seq_ids, lens, &tree_parents);
+      SampleOutput out = backend_->ForwardSample(1, plan, token_ids, embed_handles, sp);
+      const int num_top = sp.num_top_logprobs;
+      for (size_t i = 0; i < ready.size(); ++i) level_begin[i] = static_cast<int>(ready[i].e().mstates[1].draft_tokens.size());
+      for (size_t row = 0; row < row_owner.size(); ++row) {
+        ModelState& ds = ready[row_owner[row].first].e().mstates[1];
+        for (int c = 0; c < width; ++c) {
+          SampleResult s;
+          s.token = out.top_tokens[row * num_top + c];
+          s.prob = out.top_probs[row * num_top + c];
+          ds.draft_tokens.push_back(s);
+          ds.draft_slots.push_back(sp.prob_slots[row]);
+          ds.draft_parents.push_back(row_owner[row].second);
+        }
+      }
+    }
+  }
+
   bool StepSpecDecode() {
     std::vector<EntryRef> ready = ReadyToDecode();
     if (ready.empty()) return false;
     const int k = DraftLengthFor(static_cast<int>(ready.size()));
     if (k == 0) return StepDecode();
-    if (!FitDecodeBatch(&ready, k + 1)) return false;
+    int64_t max_nodes = k;  // chain; a tree of width w has w + w^2 + ... + w^k nodes
+    if (!feature_fed_draft_ && cfg_.spec_tree_width > 1) {
+      max_nodes = 0;
+      int64_t level = 1;
+      for (int d = 0; d < k; ++d) {
+        level *= cfg_.spec_tree_width;
+        max_nodes += level;
+      }
+      if (max_nodes > 63) throw std::runtime_error("Engine: spec_tree_width ^ spec_draft_length exceeds the 63-node draft tree limit");
+    }
+    if (!FitDecodeBatch(&ready, max_nodes + 1)) return false;
     if (static_cast<int64_t>(ready.size()) > cfg_.max_num_sequence) ready.resize(cfg_.max_num_sequence);
     // the draft model needs the same room
     {
       int64_t need = 0;
-      for (auto& r : ready) need += kv_[1]->PagesNeeded(r.e().mstates[1].internal_id, k + 8);
+      for (auto& r : ready) need += kv_[1]->PagesNeeded(r.e().mstates[1].internal_id, max_nodes + 8);
       if (kv_[1]->NumAvailablePages() < need) return StepDecode();
     }
     const int64_t prompt_extra = 0;
@@ -1114,7 +1212,11 @@ class EngineImpl : public Engine {
     // ---- draft phase: k rounds of the small model
     double t0 = NowSeconds();
     TraceBatch(ready, "start draft");
-    for (int round = 0; round < k; ++round) {
+    const int width = feature_fed_draft_ ? 1 : std::max(1, cfg_.spec_tree_width);
+    // speculative entries each sequence leaves in the draft model's KV (dropped after verification)
+    std::vector<int64_t> spec_kv(ready.size(), k - 1);
+    if (width > 1) DraftTree(ready, k, width, &spec_kv);
+    for (int round = 0; round < (width > 1 ? 0 : k); ++round) {
       std::vector<int64_t> seq_ids;
       std::vector<int32_t> lens, token_ids;
       SampleParams sp;
@@ -1172,24 +1274,26 @@ class EngineImpl : public Engine {
     for (auto& r : ready) {
       RequestStateEntry& e = r.e();
       ModelState& ds = e.mstates[1];
+      const int nodes = static_cast<int>(ds.draft_tokens.size());  // k for a chain, more for a tree
       seq_ids.push_back(e.mstates[0].internal_id);
-      lens.push_back(k + 1);
+      lens.push_back(nodes + 1);
       token_ids.push_back(e.committed_tokens.back().token);
       tree_parents.push_back(-1);
       // row for the root (distribution after the last committed token)
       AddSampleRow(&vp.sampling, r, off);
-      for (int j = 0; j < k; ++j) {
+      for (int j = 0; j < nodes; ++j) {
         token_ids.push_back(ds.draft_tokens[j].token);
-        tree_parents.push_back(j);  // chunk-local: node j+1 hangs under node j (root is node 0)
+        // chunk-local: the root is entry 0, node j is entry j + 1 and hangs under its parent's entry
+        tree_parents.push_back(ds.draft_parents[j] + 1);
         vp.draft_tokens.push_back(ds.draft_tokens[j].token);
         vp.draft_prob_slots.push_back(ds.draft_slots[j]);
-        vp.parents.push_back(j - 1);
+        vp.parents.push_back(ds.draft_parents[j]);
         vp.uniform.push_back(static_cast<float>(e.NextUniform()));
         AddSampleRow(&vp.sampling, r, off + 1 + j);
       }
       vp.node_indptr.push_back(static_cast<int32_t>(vp.draft_tokens.size()));
       vp.final_uniform.push_back(static_cast<float>(e.NextUniform()));
-      off += k + 1;
+      off += nodes + 1;
     }
     ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens, &tree_parents);
     VerifyOutput vo = backend_->ForwardVerify(0, plan, token_ids, vp);
@@ -1202,14 +1306,17 @@ class EngineImpl : public Engine {
       // KV: node 0 (the last committed token) is always kept; accepted draft nodes follow
       std::vector<int32_t> keep{0};
       for (int j = beg; j < end; ++j) keep.push_back(vo.accepted_nodes[j] + 1);
-      std::vector<int32_t> moves = kv_[0]->CommitTreeNodes(e.mstates[0].internal_id, k + 1, keep);
+      const int nodes = static_cast<int>(ds.draft_tokens.size());
+      std::vector<int32_t> moves = kv_[0]->CommitTreeNodes(e.mstates[0].internal_id, nodes + 1, keep);
       if (!moves.empty()) backend_->MoveKVTokens(0, moves);
       // draft KV holds [.., last committed, d_0 .. d_{k-2}]; keep the accepted part.  A feature-fed head
       // (EAGLE) computed those entries from its own predicted features: all of them are dropped and
       // the next draft phase recomputes the accepted tokens from the target's true features
       // (reference: cpp/serve/engine_actions/eagle_batch_verify.cc).
-      const int draft_valid = feature_fed_draft_ ? 0 : std::min(accepted, k - 1);
-      if (k - 1 - draft_valid > 0) kv_[1]->PopN(ds.internal_id, k - 1 - draft_valid);
+      // With a draft tree the speculative entries are dropped as well: their order in the draft KV is
+      // the tree's, not the accepted path's.
+      const int64_t draft_valid = (feature_fed_draft_ || width > 1) ? 0 : std::min<int64_t>(accepted, k - 1);
+      if (spec_kv[i] - draft_valid > 0) kv_[1]->PopN(ds.internal_id, spec_kv[i] - draft_valid);
       for (int j = beg; j < end; ++j) {
         CommitToken(r, ds.draft_tokens[vo.accepted_nodes[j]]);
       }
@@ -1219,6 +1326,9 @@ class EngineImpl : public Engine {
       CommitToken(r, fin);
       r.rs->metrics.decode_tokens += accepted + 1;
       metrics_.spec_decode.Update(k, accepted);
+      // siblings of a draft tree share their parent's slot: free every slot once
+      std::sort(ds.draft_slots.begin(), ds.draft_slots.end());
+      ds.draft_slots.erase(std::unique(ds.draft_slots.begin(), ds.draft_slots.end()), ds.draft_slots.end());
       for (int s : ds.draft_slots) draft_slots_.Free(s);
       ds.draft_slots.clear();
       ds.draft_tokens.clear();

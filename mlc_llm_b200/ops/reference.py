@@ -268,8 +268,8 @@ def take_probs(probs, rows, token, k):
 
 def verify_tree(draft_probs, draft_tokens, model_probs, first_child, next_sibling, uniform,
                 parent_ptr) -> None:
-    """op/batch_spec_verify.py:8-175: accept a child when p >= u * q, otherwise replace the parent
-    distribution by normalise(max(p - q, 0)) and try the next sibling."""
+    """op/batch_spec_verify.py:8-175: accept a child when p >= u * q (and p > 0), otherwise replace the
+    parent distribution by normalise(max(p - q, 0)) and try the next sibling."""
     for b in range(parent_ptr.shape[0]):
         parent = int(parent_ptr[b])
         child = int(first_child[parent])
@@ -277,7 +277,7 @@ def verify_tree(draft_probs, draft_tokens, model_probs, first_child, next_siblin
             tok = int(draft_tokens[child])
             p = float(model_probs[parent, tok])
             qv = float(draft_probs[child, tok])
-            if p >= float(uniform[child]) * qv:
+            if p > 0.0 and p >= float(uniform[child]) * qv:  # p > 0: see the kernel's note on q == 0
                 parent, child = child, int(first_child[child])
             else:
                 r = torch.clamp(model_probs[parent] - draft_probs[child], min=0)

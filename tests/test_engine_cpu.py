@@ -308,3 +308,52 @@ def test_json_mode_jump_forward_skips_decode_steps_and_keeps_the_text():
     assert out["jump_forward"][0] == out["constraint"][0]
     assert out["jump_forward"][1] < out["constraint"][1]
     assert out["jump_forward"][2] > out["constraint"][2]
+
+
+def test_speculative_decoding_with_draft_trees(reference_outputs):
+    """spec_tree_width > 1: every draft round gives each leaf several children; verification walks the
+    tree.  Greedy output stays the target model's, also when lower-ranked children carry no draft
+    probability; an identical draft model has its first child accepted at every level."""
+    prompts, want = reference_outputs
+    for draft, width, length in (("random://tiny-llama?quant=q0f32&seed=12&num_hidden_layers=1", 2, 3),
+                                 (MODEL, 2, 3), (MODEL, 3, 2)):
+        cfg = EngineConfig(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64,
+                           prefix_cache_mode="disable", speculative_mode="small_draft", spec_draft_length=length,
+                           spec_tree_width=width, additional_models=[draft])
+        eng = SyncMLCEngine(MODEL, "cpu", engine_config=cfg)
+        _, toks = eng.generate(prompts[:4], dict(GREEDY, max_tokens=12))
+        assert [t[0] for t in toks] == want[:4], (draft, width, length)
+        stats = json.loads(eng.debug_stats())
+        assert stats["num_running"] == 0
+        if draft == MODEL:
+            assert stats["num_verify_steps"] <= -(-11 // (length + 1)) + 1
+    # sampling (temperature > 0) runs through the same path
+    cfg = EngineConfig(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64,
+                       prefix_cache_mode="disable", speculative_mode="small_draft", spec_draft_length=2,
+                       spec_tree_width=2, additional_models=[MODEL])
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=cfg)
+    _, toks = eng.generate(prompts[:2], {"max_tokens": 10, "temperature": 0.8, "top_p": 0.95, "seed": 3,
+                                         "debug_config": {"ignore_eos": True}})
+    assert all(len(t[0]) == 10 for t in toks)
+
+
+def test_verify_tree_rejects_candidates_without_probability():
+    """A child whose token has zero probability under both distributions must not be accepted (0 >= 0)."""
+    import torch
+
+    from mlc_llm_b200.ops import reference as ref
+
+    vocab = 6
+    model = torch.zeros(3, vocab)
+    model[0, 4] = 1.0            # after the root the target wants token 4
+    draft = torch.zeros(3, vocab)
+    draft[1, 2] = 1.0            # both children share the draft distribution: all mass on token 2
+    draft[2, 2] = 1.0
+    tokens = torch.tensor([0, 2, 3])          # row 1: token 2 (draft argmax), row 2: token 3 (q == 0, p == 0)
+    first_child = torch.tensor([1, -1, -1])
+    next_sibling = torch.tensor([-1, 2, -1])
+    uniform = torch.tensor([0.0, 0.5, 0.5])
+    parent = torch.tensor([0])
+    ref.verify_tree(draft, tokens, model, first_child, next_sibling, uniform, parent)
+    assert int(parent[0]) == 0   # nothing accepted; the residual stays on token 4
+    assert float(model[0, 4]) == 1.0
