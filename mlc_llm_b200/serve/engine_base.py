@@ -357,9 +357,9 @@ class EngineRuntime:
         full = json.loads(self.complete_config_json)
         self.fused_tp = False
         # MLCB_FUSED_TP: "1" = always, "0" = never, default "auto" = where the fused kernels, replayed
-        # from CUDA graphs, measured above the NCCL path (2 and 4 ranks).
+        # from CUDA graphs, measured above the NCCL path (2, 4 and 8 ranks).
         fused_mode = os.environ.get("MLCB_FUSED_TP", "auto")
-        use_fused = fused_mode == "1" or (fused_mode == "auto" and tp in (2, 4))
+        use_fused = fused_mode == "1" or (fused_mode == "auto" and tp in (2, 4, 8))
         # "1" on a single GPU runs the same kernels with one rank (peer tables point at local memory)
         if (tp > 1 or fused_mode == "1") and self.device.type == "cuda" and use_fused:
             # fused GEMM+collective kernels over symmetric peer buffers (main model only)
