@@ -9,7 +9,9 @@ from __future__ import annotations
 
 import asyncio
 import json
+import os
 import queue
+import sys
 import threading
 from typing import Any, AsyncGenerator, Dict, Iterator, List, Literal, Optional, Union
 
@@ -104,6 +106,13 @@ class MLCEngineBase:
             threading.Thread(target=self._threaded.run_background_stream_back_loop, daemon=True,
                              name="mlc-stream-back"),
         ]
+        # The engine loop and the stream-back loop both run Python (kernel launches, per-request delivery).
+        # With CPython's default 5 ms switch interval a burst of deliveries can hold the interpreter lock
+        # for its whole length while the engine loop waits to launch the next step; a shorter interval
+        # bounds that wait (MLCB_SWITCH_INTERVAL_S, default 0.0005; 0 leaves the interpreter's setting).
+        interval = float(os.environ.get("MLCB_SWITCH_INTERVAL_S", "0.0005"))
+        if interval > 0 and sys.getswitchinterval() > interval:
+            sys.setswitchinterval(interval)
         for t in self._threads:
             t.start()
         self._threaded.reload(self.runtime.complete_config_json)
