@@ -7,6 +7,7 @@ SUBCOMMANDS = {
     "compile": "compile", "convert_weight": "convert_weight", "gen_config": "gen_config", "chat": "chat",
     "serve": "serve", "package": "package", "calibrate": "calibrate", "router": "router", "bench": None,
     "worker": "worker", "check_device": "check_device", "model_metadata": "model_metadata",
+    "delivery": "delivery",
 }
 
 

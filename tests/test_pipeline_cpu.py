@@ -165,3 +165,31 @@ def test_convert_weight_merges_a_lora_adapter(hf_dir, tmp_path):
                           rtol=1e-2)
     down0 = cache.get("model.layers.0.mlp.down_proj.weight").float()
     assert torch.allclose(down0, sd["model.layers.0.mlp.down_proj.weight"], atol=2e-2, rtol=1e-2)
+
+
+def test_delivery_runs_only_what_the_log_lacks(hf_dir, tmp_path):
+    """Continuous delivery: every (model, quantisation) pair of the spec that the log does not list is
+    converted; a second run has nothing left to do; a changed conversation template only redoes the config."""
+    from mlc_llm_b200.cli import delivery
+
+    src, _, _ = hf_dir
+    spec = {"tasks": [{"model_id": "tiny", "model": src, "conv_template": "LM", "quantization": ["q0f32"],
+                       "overrides": {"q4f16_1": {"context_window_size": 128}}}],
+            "default_quantization": ["q4f16_1"]}
+    spec_path, log_path, out = tmp_path / "spec.json", tmp_path / "log.json", tmp_path / "out"
+    spec_path.write_text(json.dumps(spec))
+    delivery.main(["--spec", str(spec_path), "--log", str(log_path), "--output", str(out)])
+    dirs = sorted(os.listdir(out))
+    assert dirs == ["tiny-q0f32-MLC", "tiny-q4f16_1-MLC"]
+    chat = json.load(open(out / "tiny-q4f16_1-MLC" / "mlc-chat-config.json"))
+    assert chat["context_window_size"] == 128 and chat["quantization"] == "q4f16_1"
+    assert "model.layers.0.self_attn.qkv_proj.q_weight" in TensorCache(str(out / "tiny-q4f16_1-MLC")).names()
+    log = json.load(open(log_path))
+    assert sorted(t["quantization"] for t in log["tasks"]) == ["q0f32", "q4f16_1"]
+    diff = delivery.generate_model_delivery_diff(delivery.ModelDeliveryList.from_json(spec),
+                                                 delivery.get_current_log(str(log_path)))
+    assert diff.tasks == []
+    spec["tasks"][0]["conv_template"] = "chatml"
+    diff = delivery.generate_model_delivery_diff(delivery.ModelDeliveryList.from_json(spec),
+                                                 delivery.get_current_log(str(log_path)))
+    assert len(diff.tasks) == 2 and all(t.gen_config_only for t in diff.tasks)
