@@ -219,6 +219,7 @@ py::object OutputField(const RequestStreamOutput& o, const std::string& key) {
     return std::move(fr);
   }
   if (key == "group_extra_prefix_string") return py::cast(o.group_extra_prefix_string);
+  if (key == "text_is_final") return py::bool_(o.text_is_final);
   if (key == "request_final_usage_json_str")
     return o.request_final_usage_json_str.empty() ? py::object(py::none())
                                                   : py::object(py::str(o.request_final_usage_json_str));
@@ -227,7 +228,7 @@ py::object OutputField(const RequestStreamOutput& o, const std::string& key) {
 
 const char* const kOutputKeys[] = {"request_id", "group_delta_token_ids", "group_delta_logprob_json_strs",
                                    "group_finish_reason", "group_extra_prefix_string",
-                                   "request_final_usage_json_str"};
+                                   "request_final_usage_json_str", "text_is_final"};
 
 StreamCallback WrapCallback(py::object fn) {
   if (fn.is_none()) return nullptr;
@@ -606,6 +607,11 @@ PYBIND11_MODULE(_core, m) {
              e.AddRequest(std::move(r));
            })
       .def("abort_request", &ThreadedEngine::AbortRequest, py::call_guard<py::gil_scoped_release>())
+      .def("accumulate_outputs",
+           [](ThreadedEngine& e, const std::string& id, int n, std::shared_ptr<Tokenizer> tok) {
+             e.AccumulateOutputs(id, n, std::move(tok));
+           },
+           py::arg("request_id"), py::arg("num_choices"), py::arg("tokenizer"))
       .def("run_background_loop", &ThreadedEngine::RunBackgroundLoop, py::call_guard<py::gil_scoped_release>())
       .def("run_background_stream_back_loop", &ThreadedEngine::RunBackgroundStreamBackLoop,
            py::call_guard<py::gil_scoped_release>())

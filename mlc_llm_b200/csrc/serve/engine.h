@@ -64,6 +64,9 @@ struct RequestStreamOutput {
   std::vector<std::vector<std::string>> group_delta_logprob_json_strs;
   std::vector<std::string> group_finish_reason;  // "" while running
   std::vector<std::string> group_extra_prefix_string;
+  // Set on the single, merged output of a request registered with ThreadedEngine::AccumulateOutputs:
+  // group_extra_prefix_string then holds each choice's complete, already detokenised text.
+  bool text_is_final = false;
   std::string request_final_usage_json_str;      // non-empty on the last output of the request
 };
 
@@ -250,6 +253,10 @@ class ThreadedEngine {
   void Reset();                                         // blocks
   void AddRequest(Request request);
   void AbortRequest(const std::string& request_id);
+  // Non-streaming consumers: keep this request's per-step outputs in the stream-back thread (tokens,
+  // logprobs, detokenised text) and hand the frontend one merged output when the request is done,
+  // instead of one callback per request and step. Call before AddRequest.
+  void AccumulateOutputs(const std::string& request_id, int num_choices, std::shared_ptr<const Tokenizer> tokenizer);
   void RunBackgroundLoop();             // call on a dedicated thread
   void RunBackgroundStreamBackLoop();   // call on a dedicated thread
   void ExitBackgroundLoop();
@@ -288,6 +295,16 @@ class ThreadedEngine {
   std::condition_variable sb_cv_;
   std::vector<RequestStreamOutput> sb_queue_;
   std::atomic<bool> sb_waiting_{false};
+  struct OutputAccumulator {
+    RequestStreamOutput merged;
+    std::vector<TextStreamer> streamers;
+    std::vector<bool> finished;
+  };
+  std::mutex acc_mu_;
+  std::unordered_map<std::string, OutputAccumulator> acc_;
+  // Folds `out` into its request's accumulator. Returns true when `out` should go to the frontend (it
+  // was not an accumulated request, or it now carries the merged, final result).
+  bool Accumulate(RequestStreamOutput* out);
   std::atomic<int64_t> pending_outputs_{0};
 };
 

@@ -202,8 +202,68 @@ void ThreadedEngine::RunBackgroundStreamBackLoop() {
       local.swap(sb_queue_);
     }
     if (exit_.load()) break;
-    if (!local.empty() && frontend_callback_) frontend_callback_(std::move(local));
+    std::vector<RequestStreamOutput> forward;
+    forward.reserve(local.size());
+    for (auto& out : local)
+      if (Accumulate(&out)) forward.push_back(std::move(out));
+    if (!forward.empty() && frontend_callback_) frontend_callback_(std::move(forward));
   }
+}
+
+void ThreadedEngine::AccumulateOutputs(const std::string& request_id, int num_choices,
+                                       std::shared_ptr<const Tokenizer> tokenizer) {
+  OutputAccumulator acc;
+  const int n = std::max(1, num_choices);
+  acc.merged.request_id = request_id;
+  acc.merged.group_delta_token_ids.resize(n);
+  acc.merged.group_delta_logprob_json_strs.resize(n);
+  acc.merged.group_finish_reason.assign(n, "");
+  acc.merged.group_extra_prefix_string.assign(n, "");
+  acc.merged.text_is_final = true;
+  for (int i = 0; i < n; ++i) acc.streamers.emplace_back(tokenizer);
+  acc.finished.assign(n, false);
+  std::lock_guard<std::mutex> lock(acc_mu_);
+  acc_[request_id] = std::move(acc);
+}
+
+bool ThreadedEngine::Accumulate(RequestStreamOutput* out) {
+  std::lock_guard<std::mutex> lock(acc_mu_);
+  auto it = acc_.find(out->request_id);
+  if (it == acc_.end()) return true;
+  OutputAccumulator& acc = it->second;
+  const size_t n = acc.streamers.size();
+  bool error = false;
+  for (size_t i = 0; i < n && i < out->group_delta_token_ids.size(); ++i) {
+    if (acc.finished[i]) continue;
+    const std::string& reason = i < out->group_finish_reason.size() ? out->group_finish_reason[i] : std::string();
+    if (reason == "error") {
+      error = true;
+      break;
+    }
+    std::string& text = acc.merged.group_extra_prefix_string[i];
+    if (i < out->group_extra_prefix_string.size()) text += out->group_extra_prefix_string[i];
+    const std::vector<int32_t>& ids = out->group_delta_token_ids[i];
+    if (!ids.empty()) {
+      text += acc.streamers[i].Put(ids);
+      acc.merged.group_delta_token_ids[i].insert(acc.merged.group_delta_token_ids[i].end(), ids.begin(), ids.end());
+    }
+    if (i < out->group_delta_logprob_json_strs.size())
+      for (auto& s : out->group_delta_logprob_json_strs[i]) acc.merged.group_delta_logprob_json_strs[i].push_back(s);
+    if (!reason.empty()) {
+      text += acc.streamers[i].Finish();
+      acc.merged.group_finish_reason[i] = reason;
+      acc.finished[i] = true;
+    }
+  }
+  if (error) {  // pass the error through as it is
+    acc_.erase(it);
+    return true;
+  }
+  if (out->request_final_usage_json_str.empty()) return false;
+  acc.merged.request_final_usage_json_str = out->request_final_usage_json_str;
+  *out = std::move(acc.merged);
+  acc_.erase(it);
+  return true;
 }
 
 void ThreadedEngine::ExitBackgroundLoop() {

@@ -152,11 +152,18 @@ class MLCEngineBase:
                 continue
             items = []
             usage = out["request_final_usage_json_str"]
+            final_text = out["text_is_final"]
             for i, (ids, lps, fr, extra) in enumerate(zip(out["group_delta_token_ids"],
                                                            out["group_delta_logprob_json_strs"],
                                                            out["group_finish_reason"],
                                                            out["group_extra_prefix_string"])):
                 if sink.done[i]:
+                    continue
+                if final_text:
+                    # merged result of a request accumulated in the native stream-back thread: `extra` is
+                    # the complete, already detokenised text of the choice
+                    sink.done[i] = True
+                    items.append(_StreamItem(i, extra, lps, fr, None))
                     continue
                 text = sink.streamers[i].put(ids) if ids else ""
                 if extra and fr != "error":
@@ -414,31 +421,41 @@ class MLCEngine(MLCEngineBase):
     def generate_many(self, prompts: List[List[int]], gen_cfg: Dict[str, Any]) -> List[Dict[str, Any]]:
         """Batch helper: submit token-id prompts together, wait for all, return per-request
         ``{"text", "finish_reason", "usage"}``. Used by offline evaluation and the benchmark."""
-        q: "queue.Queue" = queue.Queue()
+        # Results are filled in by the stream-back thread itself; this thread only sleeps until the last
+        # request has reported its usage, so it does not compete with the engine loop for the interpreter.
+        results = [{"text": "", "finish_reason": None, "usage": None} for _ in prompts]
+        done = threading.Event()
+        state = {"remaining": len(prompts)}
+
+        def collect(items, i):
+            res = results[i]
+            for it in items:
+                if it.usage_json is not None:
+                    res["usage"] = json.loads(it.usage_json)
+                    state["remaining"] -= 1
+                else:
+                    res["text"] += it.delta_text
+                    if it.finish_reason is not None:
+                        res["finish_reason"] = it.finish_reason
+                        if it.finish_reason == "error":
+                            state["remaining"] -= 1
+            if state["remaining"] <= 0:
+                done.set()
+
         ids = []
         for i, p in enumerate(prompts):
             rid = engine_base.create_request_id("batch", None)
             ids.append(rid)
-            self._register(rid, 1, lambda items, i=i: q.put((i, items)))
-        results = [{"text": "", "finish_reason": None, "usage": None} for _ in prompts]
+            self._register(rid, 1, lambda items, i=i: collect(items, i))
         try:
             import numpy as np  # pylint: disable=import-outside-toplevel
 
             for rid, p in zip(ids, prompts):
+                # nobody streams these: let the native stream-back thread gather each request's outputs
+                self._threaded.accumulate_outputs(rid, 1, self.tokenizer.handle)
                 self._submit(rid, [np.asarray(p, dtype=np.int32)], gen_cfg)
-            remaining = len(prompts)
-            while remaining:
-                i, items = q.get()
-                for it in items:
-                    if it.usage_json is not None:
-                        results[i]["usage"] = json.loads(it.usage_json)
-                        remaining -= 1
-                    else:
-                        results[i]["text"] += it.delta_text
-                        if it.finish_reason is not None:
-                            results[i]["finish_reason"] = it.finish_reason
-                            if it.finish_reason == "error":
-                                remaining -= 1
+            if prompts:
+                done.wait()
         finally:
             for rid in ids:
                 self._unregister(rid)

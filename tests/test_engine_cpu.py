@@ -357,3 +357,30 @@ def test_verify_tree_rejects_candidates_without_probability():
     ref.verify_tree(draft, tokens, model, first_child, next_sibling, uniform, parent)
     assert int(parent[0]) == 0   # nothing accepted; the residual stays on token 4
     assert float(model[0, 4]) == 1.0
+
+
+def test_generate_many_gathers_outputs_natively():
+    """``generate_many`` lets the native stream-back thread gather each request's outputs (tokens,
+    detokenised text, grammar-forced text in order) and delivers one merged result per request; the text
+    equals what the streaming API returns."""
+    eng = MLCEngine(MODEL, "cpu", mode="server",
+                    engine_config=EngineConfig(max_num_sequence=8, prefill_chunk_size=64, max_total_sequence_length=2048))
+    try:
+        prompts = _prompts(5, seed=9)
+        cfg = dict(GREEDY, max_tokens=9)
+        res = eng.generate_many(prompts, cfg)
+        assert [r["finish_reason"] for r in res] == ["length"] * 5
+        assert all(r["usage"]["completion_tokens"] == 9 for r in res)
+        for p, r in zip(prompts[:2], res[:2]):
+            one = eng.completions.create(prompt=p, max_tokens=9, temperature=0.0, debug_config={"ignore_eos": True})
+            assert one.choices[0].text == r["text"]
+        # JSON mode: forced text arrives as strings between token runs; the merged text keeps the order
+        schema = json.dumps({"type": "object", "properties": {"name": {"type": "string"}}, "required": ["name"]})
+        jcfg = {"max_tokens": 24, "temperature": 0.0, "response_format": {"type": "json_object", "schema": schema}}
+        merged = eng.generate_many(prompts[:2], jcfg)
+        for p, r in zip(prompts[:2], merged):
+            one = eng.completions.create(prompt=p, **jcfg)
+            assert one.choices[0].text == r["text"]
+        assert eng.generate_many([], cfg) == []
+    finally:
+        eng.terminate()
