@@ -64,6 +64,9 @@ void ThreadedEngine::AbortRequest(const std::string& request_id) {
     queue_.push_back({Kind::kAbortRequest, nullptr, request_id});
   }
   cv_.notify_one();
+  // an aborted request produces no final output: drop what the stream-back thread gathered for it
+  std::lock_guard<std::mutex> lock(acc_mu_);
+  acc_.erase(request_id);
 }
 
 void ThreadedEngine::HandleReload(const std::string& cfg) {

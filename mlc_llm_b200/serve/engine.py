@@ -282,8 +282,8 @@ class AsyncMLCEngine(MLCEngineBase):
         return EngineMetrics(self._metrics_json())
 
     # ---------------------------------------------------------------- generation core
-    async def _generate(self, inputs: List[Any], gen_cfg: Dict[str, Any], request_id: str
-                        ) -> AsyncGenerator[List[_StreamItem], None]:
+    async def _generate(self, inputs: List[Any], gen_cfg: Dict[str, Any], request_id: str,
+                        accumulate: bool = False) -> AsyncGenerator[List[_StreamItem], None]:
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
 
@@ -293,6 +293,8 @@ class AsyncMLCEngine(MLCEngineBase):
         n = int(gen_cfg.get("n", 1))
         self._register(request_id, n, deliver)
         try:
+            if accumulate:  # non-streaming caller: one merged delivery at the end
+                self._threaded.accumulate_outputs(request_id, n, self.tokenizer.handle)
             self._submit(request_id, inputs, gen_cfg)
             finished = False
             while not finished:
@@ -346,7 +348,7 @@ class AsyncMLCEngine(MLCEngineBase):
         inputs, gen, use_fn, _ = engine_base.process_chat_completion_request(
             request, request_id, self.runtime, self.max_input_sequence_length)
         acc = _Accumulator(request.n)
-        async for items in self._generate(inputs, gen, request_id):
+        async for items in self._generate(inputs, gen, request_id, accumulate=True):
             acc.add(items)
         return acc.chat_response(request_id, self.model, use_fn)
 
@@ -354,7 +356,7 @@ class AsyncMLCEngine(MLCEngineBase):
         inputs, gen, _, echo = engine_base.process_completion_request(
             request, request_id, self.runtime, self.max_input_sequence_length)
         acc = _Accumulator(request.n, echo)
-        async for items in self._generate(inputs, gen, request_id):
+        async for items in self._generate(inputs, gen, request_id, accumulate=True):
             acc.add(items)
         return acc.completion_response(request_id, self.model)
 
@@ -399,12 +401,14 @@ class MLCEngine(MLCEngineBase):
     def metrics(self) -> EngineMetrics:
         return EngineMetrics(self._metrics_json())
 
-    def _generate(self, inputs: List[Any], gen_cfg: Dict[str, Any], request_id: str
-                  ) -> Iterator[List[_StreamItem]]:
+    def _generate(self, inputs: List[Any], gen_cfg: Dict[str, Any], request_id: str,
+                  accumulate: bool = False) -> Iterator[List[_StreamItem]]:
         q: "queue.Queue[List[_StreamItem]]" = queue.Queue()
         n = int(gen_cfg.get("n", 1))
         self._register(request_id, n, q.put)
         try:
+            if accumulate:  # non-streaming caller: one merged delivery at the end
+                self._threaded.accumulate_outputs(request_id, n, self.tokenizer.handle)
             self._submit(request_id, inputs, gen_cfg)
             finished = False
             while not finished:
@@ -469,7 +473,7 @@ class MLCEngine(MLCEngineBase):
         inputs, gen, use_fn, _ = engine_base.process_chat_completion_request(
             request, rid, self.runtime, self.max_input_sequence_length)
         acc = _Accumulator(request.n)
-        for items in self._generate(inputs, gen, rid):
+        for items in self._generate(inputs, gen, rid, accumulate=True):
             acc.add(items)
         return acc.chat_response(rid, self.model, use_fn)
 
@@ -481,7 +485,7 @@ class MLCEngine(MLCEngineBase):
         inputs, gen, _, echo = engine_base.process_completion_request(
             request, rid, self.runtime, self.max_input_sequence_length)
         acc = _Accumulator(request.n, echo)
-        for items in self._generate(inputs, gen, rid):
+        for items in self._generate(inputs, gen, rid, accumulate=True):
             acc.add(items)
         return acc.completion_response(rid, self.model)
 
