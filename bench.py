@@ -34,7 +34,7 @@ import numpy as np
 def _reference_arm():
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "offline pip install of /root/reference fails at CMake: 3rdparty/tvm, "
+        "unavailable": "offline pip install of the reference fails at CMake: 3rdparty/tvm, "
                        "3rdparty/tokenizers-cpp and 3rdparty/xgrammar are empty submodule directories "
                        "(add_subdirectory has no CMakeLists.txt); apache-tvm-ffi is not in the wheelhouse",
     }))

@@ -20,8 +20,8 @@ def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_e
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     if out.returncode != 0:
         # keep the children's full stderr where a GPU run can pick it up
-        log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
-        if os.path.isdir(log_dir):
+        log_dir = os.environ.get("MLCB_TEST_LOG_DIR", "")
+        if log_dir and os.path.isdir(log_dir):
             with open(os.path.join(log_dir, "dist_stderr.log"), "w", encoding="utf-8") as f:
                 f.write(out.stderr)
     assert out.returncode == 0, out.stderr[-3000:]
