@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the hot kernels, reported against measured peaks.
 
-``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|gemv_q4|attn_decode|attn_prefill|rope|norm|sampling|moe|all] [--small]``
+``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|gemv_q4|lowm_q4|attn_decode|attn_prefill|rope|norm|sampling|moe|all] [--small]``
 
 Timing follows the usual hygiene: warm-up, CUDA events on the launching stream, and a buffer larger
 than L2 written between timed launches so every launch starts cold.  ``--small`` shrinks the
@@ -127,6 +127,37 @@ def bench_gemv_q4(small: bool):
     return out
 
 
+def bench_lowm_q4(small: bool):
+    """Five to sixteen tokens against int4-group weights: the warp-level MMA form (``mlcb_gemm_q4_lowm``) and the
+    tcgen05 kernel on the same shapes."""
+    dev = torch.device("cuda")
+    hbm, _tf, how = _peaks()
+    flush = torch.zeros(160 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
+    shapes = [(8, 6144, 4096), (8, 28672, 4096), (8, 4096, 14336), (16, 28672, 4096), (16, 4096, 14336)]
+    if small:
+        shapes = [(8, 28672, 4096)]
+    quant = Q.get("q4f16_1")
+    out = []
+    for m, n, k in shapes:
+        x = (torch.randn(m, k, device=dev) * 0.5).half()
+        qw = torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int64, device=dev).to(torch.int32)
+        qs = (torch.rand(n, k // 32, device=dev) * 0.01).half()
+        lw = ops.LinearWeight("q4", qw, qs, None, quant, n, k, device_layout=True)
+        byt = n * k // 2 + n * (k // 32) * 2 + m * k * 2 + m * n * 2
+        saved = ops._LOWM_Q4  # pylint: disable=protected-access
+        for name, flag in (("gemm_q4_lowm_mma", True), ("gemm_q4_tensor_core", False)):
+            ops._LOWM_Q4 = flag  # pylint: disable=protected-access
+            med, best = _time(lambda: ops.linear(x, lw), flush=flush)
+            ops.check_status(dev)
+            rec = {"kernel": name, "M": m, "N": n, "K": k, "ms_median": round(med, 4), "ms_best": round(best, 4),
+                   "gbs": round(byt / med / 1e6, 1), "frac_of_roofline": round(byt / (hbm * 1e9) * 1e3 / med, 3),
+                   "peaks": how}
+            print(json.dumps(rec), flush=True)
+            out.append(rec)
+        ops._LOWM_Q4 = saved  # pylint: disable=protected-access
+    return out
+
+
 def bench_misc(which: str, small: bool):
     """Memory-bound helpers: RoPE + KV append, add+RMSNorm, sampling; and the MoE grouped GEMM."""
     dev = torch.device("cuda")
@@ -200,6 +231,8 @@ def main(argv=None):
         res += bench_gemm(args.small, q4=False)
     if args.which in ("gemv_q4", "all"):
         bench_gemv_q4(args.small)
+    if args.which in ("lowm_q4", "all"):
+        bench_lowm_q4(args.small)
     if args.which in ("gemm_q4", "all"):
         res += bench_gemm(args.small, q4=True)
     if args.which in ("attn_decode", "attn_prefill", "all"):

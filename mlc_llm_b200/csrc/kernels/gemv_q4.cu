@@ -331,3 +331,157 @@ MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Five to sixteen tokens: warp-level tensor-core form.  The tcgen05 kernel expands weights through shared
+// memory at a rate sized for 256-token tiles, so for a handful of tokens it takes as long as for 256; here the
+// nibbles are expanded in registers straight into the A fragments of mma.sync.m16n8k16 (weights are A,
+// 16 output rows x 16 k; activations are B, 16 k x 8 tokens; fp32 accumulators).
+//
+// Fragment layout (PTX ISA, m16n8k16, .f16): with g = lane / 4 and t = lane % 4,
+//   A regs: {row g, k 2t..2t+1}, {row g+8, k 2t..2t+1}, {row g, k 2t+8..2t+9}, {row g+8, k 2t+8..2t+9}
+//   B regs: {k 2t..2t+1, token g}, {k 2t+8..2t+9, token g}
+//   C regs: {row g, tokens 2t, 2t+1}, {row g+8, tokens 2t, 2t+1}
+// In the device nibble order a packed word holds eight consecutive k with the pair (2j, 2j+1) at bits
+// [4j, 4j+4) and [16+4j, 20+4j), so the A register for k 2t..2t+1 of a 16-k block is pair j = t of the block's
+// first word and the one for k 2t+8..2t+9 is pair t of its second word: one shift, one mask-or, one subtract.
+// A lane reads the 16 bytes (32 k, one scale group) of its two rows per step; the four lanes of a row read
+// the same bytes.  The group scale is applied to the group's partial accumulator in fp32.
+namespace mlcb {
+
+__device__ __forceinline__ uint32_t unpack_pair_q4(uint32_t word, int shift) {
+  uint32_t v = ((word >> shift) & 0x000f000fu) | 0x64006400u;
+  const __half2 off = __float2half2_rn(1031.f);
+  __half2 h = __hsub2(*reinterpret_cast<__half2*>(&v), off);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int MMV_WARPS = 8;
+
+// NT token tiles of eight (1: up to 8 tokens, 2: up to 16); KS warps share a 16-row group and split K.
+template <typename TO, int NT, int KS>
+__global__ void __launch_bounds__(MMV_WARPS * 32)
+    gemm_q4_lowm_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w, const __half* __restrict__ scale,
+                        const __half* __restrict__ bias, TO* __restrict__ y, int m_count, int N, int K, int ldx,
+                        int ldy) {
+  __shared__ float partial[MMV_WARPS][16][NT * 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  constexpr int GROUPS_PER_CTA = MMV_WARPS / KS;
+  const int rg = warp / KS, ks = warp % KS;
+  const int row0 = (blockIdx.x * GROUPS_PER_CTA + rg) * 16;
+  const int groups = K >> 5;                               // 32-k scale groups per row
+  const size_t words_per_row = static_cast<size_t>(K) >> 3;
+  const int ra = row0 + g, rb = row0 + g + 8;              // this lane's two rows
+  const bool va = ra < N, vb = rb < N;
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+  const int shift = 4 * t;
+  if (row0 < N) {
+    for (int gi = ks; gi < groups; gi += KS) {
+      const uint4 qa = va ? __ldg(reinterpret_cast<const uint4*>(w + ra * words_per_row) + gi)
+                          : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+      const uint4 qb = vb ? __ldg(reinterpret_cast<const uint4*>(w + rb * words_per_row) + gi)
+                          : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+      const float sa = va ? __half2float(__ldg(scale + static_cast<size_t>(ra) * groups + gi)) : 0.f;
+      const float sb = vb ? __half2float(__ldg(scale + static_cast<size_t>(rb) * groups + gi)) : 0.f;
+      // two 16-k blocks of this 32-k group: words (x, y) and (z, w)
+      const uint32_t a_lo[4] = {unpack_pair_q4(qa.x, shift), unpack_pair_q4(qb.x, shift),
+                                unpack_pair_q4(qa.y, shift), unpack_pair_q4(qb.y, shift)};
+      const uint32_t a_hi[4] = {unpack_pair_q4(qa.z, shift), unpack_pair_q4(qb.z, shift),
+                                unpack_pair_q4(qa.w, shift), unpack_pair_q4(qb.w, shift)};
+      const int k0 = gi << 5;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int tok = n * 8 + g;
+        uint32_t b[4] = {0u, 0u, 0u, 0u};
+        if (tok < m_count) {
+          const __half* xp = x + static_cast<size_t>(tok) * ldx + k0 + 2 * t;
+          b[0] = __ldg(reinterpret_cast<const uint32_t*>(xp));        // k0 + 2t, +1
+          b[1] = __ldg(reinterpret_cast<const uint32_t*>(xp + 8));    // k0 + 2t + 8, +9
+          b[2] = __ldg(reinterpret_cast<const uint32_t*>(xp + 16));   // second block
+          b[3] = __ldg(reinterpret_cast<const uint32_t*>(xp + 24));
+        }
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_m16n8k16(c, a_lo, b[0], b[1]);
+        mma_m16n8k16(c, a_hi, b[2], b[3]);
+        acc[n][0] += sa * c[0];
+        acc[n][1] += sa * c[1];
+        acc[n][2] += sb * c[2];
+        acc[n][3] += sb * c[3];
+      }
+    }
+  }
+  // C layout: regs 0,1 = (row g, tokens 2t, 2t+1); regs 2,3 = (row g+8, same tokens)
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    partial[warp][g][n * 8 + 2 * t] = acc[n][0];
+    partial[warp][g][n * 8 + 2 * t + 1] = acc[n][1];
+    partial[warp][g + 8][n * 8 + 2 * t] = acc[n][2];
+    partial[warp][g + 8][n * 8 + 2 * t + 1] = acc[n][3];
+  }
+  __syncthreads();
+  const int items = GROUPS_PER_CTA * 16 * NT * 8;
+  for (int i = threadIdx.x; i < items; i += blockDim.x) {
+    const int tok = i % (NT * 8), r = (i / (NT * 8)) % 16, g2 = i / (NT * 8 * 16);
+    const int row = (blockIdx.x * GROUPS_PER_CTA + g2) * 16 + r;
+    if (row < N && tok < m_count) {
+      float v = 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < KS; ++k2) v += partial[g2 * KS + k2][r][tok];
+      if (bias) v += __half2float(bias[row]);
+      y[static_cast<size_t>(tok) * ldy + row] = Cvt<TO>::from_f(v);
+    }
+  }
+}
+
+}  // namespace mlcb
+
+// Same contract as mlcb_gemv_q4 for 1 <= M <= 16 (K a multiple of 32, rows of x 16-byte aligned).
+MLCB_API int mlcb_gemm_q4_lowm(const void* x, const void* w, const void* scale, const void* bias, void* y, int M,
+                               int N, int K, int ldx, int ldy, int out_dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -1;
+  if (out_dtype != 0 && out_dtype != 2) return -1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long row_groups = (N + 15) / 16;
+  int ks = 1;
+  while (ks < MMV_WARPS && row_groups * ks < static_cast<long long>(sms) * 24 && (K >> 5) >= ks * 8) ks *= 2;
+  const int groups_per_cta = MMV_WARPS / ks;
+  const int grid = static_cast<int>((row_groups + groups_per_cta - 1) / groups_per_cta);
+#define LOWM_LAUNCH(TO, NT, KS)                                                                            \
+  mlcb::gemm_q4_lowm_kernel<TO, NT, KS><<<grid, mlcb::MMV_WARPS * 32, 0, stream>>>(                         \
+      static_cast<const __half*>(x), static_cast<const uint32_t*>(w), static_cast<const __half*>(scale),    \
+      static_cast<const __half*>(bias), static_cast<TO*>(y), M, N, K, ldx, ldy)
+#define LOWM_KS(TO, NT)                                \
+  do {                                                 \
+    if (ks == 1) LOWM_LAUNCH(TO, NT, 1);               \
+    else if (ks == 2) LOWM_LAUNCH(TO, NT, 2);          \
+    else if (ks == 4) LOWM_LAUNCH(TO, NT, 4);          \
+    else LOWM_LAUNCH(TO, NT, 8);                       \
+  } while (0)
+  if (out_dtype == 0) {
+    if (M <= 8) LOWM_KS(__half, 1);
+    else LOWM_KS(__half, 2);
+  } else {
+    if (M <= 8) LOWM_KS(float, 1);
+    else LOWM_KS(float, 2);
+  }
+#undef LOWM_KS
+#undef LOWM_LAUNCH
+  mlcb::count_launch();
+  return static_cast<int>(cudaGetLastError());
+}

@@ -98,6 +98,7 @@ def _gemm_scratch(device: torch.device):
 
 _LINEAR_OBSERVER = None
 _GEMV_Q4 = os.environ.get("MLCB_GEMV_Q4", "1") != "0"
+_LOWM_Q4 = os.environ.get("MLCB_LOWM_Q4", "0") != "0"
 
 
 def set_linear_observer(fn) -> None:
@@ -140,6 +141,14 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
                 return y.reshape(*lead, n)
             if rc > 0:
                 check(rc, f"mlcb_gemv_q4(M={m},N={n},K={k})")
+        elif m <= 16 and od in (torch.float16, torch.float32) and _LOWM_Q4:
+            # five to sixteen tokens: nibbles expanded in registers into warp-level MMA fragments
+            rc = lib().mlcb_gemm_q4_lowm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
+                                         c_int(k), c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[od]), stream_ptr())
+            if rc == 0:
+                return y.reshape(*lead, n)
+            if rc > 0:
+                check(rc, f"mlcb_gemm_q4_lowm(M={m},N={n},K={k})")
         rc = lib().mlcb_gemm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m),
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),

@@ -509,3 +509,25 @@ def test_gemv_q4_matches_dequantised_matmul(m, n, k, out_dtype, form, monkeypatc
     assert got.dtype == out_dtype and got.shape == (m, n)
     err = (got.float().cpu() - want).abs().max()
     assert err < 2e-2 * max(1.0, float(want.abs().max())), err
+
+
+@pytest.mark.parametrize("m", [5, 8, 9, 13, 16])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 14336), (77, 128), (28672, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_gemm_q4_low_token_counts_matches_dequantised_matmul(m, n, k, out_dtype, monkeypatch):
+    """Five to sixteen tokens against q4f16_1 weights: nibbles expanded in registers into mma.sync fragments."""
+    torch.manual_seed(m * 1000 + n + k)
+    quant = Q.get("q4f16_1")
+    w = torch.randn(n, k) * 0.05
+    qw, qs = Q.group_quantize(w.half(), quant)
+    wd = Q.group_dequantize(qw, qs, quant, k=k, out_dtype=torch.float32)
+    bias = (torch.randn(n) * 0.1).half()
+    lw = ops.LinearWeight("q4", qw, qs, bias, quant, n, k, False).to("cuda")
+    x = (torch.randn(m, k) * 0.5).half()
+    want = x.float() @ wd.t() + bias.float()
+    monkeypatch.setattr(ops, "_LOWM_Q4", True)
+    got = ops.linear(x.cuda(), lw, out_dtype=out_dtype)
+    ops.check_status(torch.device("cuda"))
+    assert got.dtype == out_dtype and got.shape == (m, n)
+    err = (got.float().cpu() - want).abs().max()
+    assert err < 2e-2 * max(1.0, float(want.abs().max())), err
