@@ -178,6 +178,10 @@ void ThreadedEngine::RunBackgroundLoop() {
         }
         // fail every in-flight request rather than spinning on a broken step
         engine_->AbortAllRequests();
+        {
+          std::lock_guard<std::mutex> lock(acc_mu_);
+          acc_.clear();  // their gathered outputs will never be completed
+        }
         RequestStreamOutput out;
         out.request_id = "";
         out.group_finish_reason = {"error"};

@@ -20,12 +20,27 @@ def main():
     rank, world, local = parallel.env_world()
     dev = torch.device("cuda", local) if device == "cuda" else torch.device("cpu")
     pp = int(os.environ.get("MLCB_TEST_PP", "1"))
-    comm = parallel.Communicator(tp_size=world // pp, pp_size=pp, device=dev, timeout_s=120)
+    comm = parallel.Communicator(tp_size=world // pp, pp_size=pp, device=dev,
+                                 timeout_s=int(os.environ.get("MLCB_TEST_COMM_TIMEOUT_S", "120")))
     cfg = EngineConfig(model=model, mode="server", max_num_sequence=8, prefill_chunk_size=64,
                        max_total_sequence_length=1024, prefix_cache_mode="disable",
                        tensor_parallel_shards=world // pp, pipeline_parallel_stages=pp)
+    exit_after = int(os.environ.get("MLCB_TEST_WORKER_EXIT_AFTER", "0"))
     if rank != 0:
         rt = EngineRuntime(cfg, dev, comm=comm)
+        if exit_after:
+            # failure injection on the host: this rank leaves between two steps, with nothing in flight
+            steps = {"n": 0}
+            orig = rt.executor.worker_step
+
+            def counted(*a, **k):
+                out = orig(*a, **k)
+                steps["n"] += 1
+                if steps["n"] >= exit_after:
+                    os._exit(0)
+                return out
+
+            rt.executor.worker_step = counted
         parallel.worker_loop(rt.executor, comm)
         comm.destroy()
         return
@@ -34,7 +49,13 @@ def main():
     eng = SyncMLCEngine(model, dev, engine_config=cfg, comm=comm)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (40, 9, 23)]
-    _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
+    try:
+        _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
+    except Exception as err:  # pylint: disable=broad-except
+        if not exit_after:
+            raise
+        print("FAILURE " + json.dumps({"rank": rank, "error": str(err)[:300]}), flush=True)
+        os._exit(0)
     comm.shutdown_workers()
     rt = eng.runtime
     print("FLAGS " + json.dumps({"fused_tp": bool(getattr(rt, "fused_tp", False)),

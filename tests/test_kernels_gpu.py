@@ -531,3 +531,30 @@ def test_gemm_q4_low_token_counts_matches_dequantised_matmul(m, n, k, out_dtype,
     assert got.dtype == out_dtype and got.shape == (m, n)
     err = (got.float().cpu() - want).abs().max()
     assert err < 2e-2 * max(1.0, float(want.abs().max())), err
+
+
+def test_bounded_device_wait_reports_through_the_status_word():
+    """A cross-GPU flag that nobody raises: the waiting kernel gives up after its time limit (about two
+    seconds), records the reason in the device status word and returns; the context stays usable."""
+    import ctypes
+    import time
+
+    from mlc_llm_b200.ops import _lib
+
+    dev = torch.device("cuda")
+    _lib.check_status(dev)                      # start from a clean word
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)   # call number 0 everywhere
+    base = torch.zeros(1, dtype=torch.int32, device=dev)
+    t0 = time.time()
+    rc = _lib.lib().mlcb_flag_wait(_lib.ptr(flags), ctypes.c_int(16), ctypes.c_int(1), _lib.ptr(base),
+                                   _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 10.0, waited          # it did wait, and it did stop
+    with pytest.raises(_lib.KernelError, match="peer GPU"):
+        _lib.check_status(dev)
+    _lib.check_status(dev)                      # reading the status cleared it
+    x = torch.randn(8, 64, device=dev, dtype=torch.float16)
+    y = ops.rmsnorm(x, torch.ones(64, device=dev, dtype=torch.float16), 1e-5, 0.0)
+    assert torch.isfinite(y).all()
