@@ -178,6 +178,7 @@ class ModelExecutor:
         self._graphs: Dict[tuple, dict] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        self._nvtx = device.type == "cuda" and os.environ.get("MLCB_NVTX", "0") == "1"
         # speculative draft heads fed with the target's features: model id -> "eagle" | "medusa"
         self.spec_heads: Dict[int, str] = {}
         for mi, m in enumerate(models):
@@ -409,6 +410,17 @@ class ModelExecutor:
     # ------------------------------------------------------------------ backend interface
     def forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
                        embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
+        if not self._nvtx:
+            return self._forward_sample(model_id, plan, token_ids, embed_handles, sp)
+        # NVTX range per model call (reference: NVTXScopedRange around every action, cpp/serve/model.cc:88,262)
+        torch.cuda.nvtx.range_push(f"forward_sample model={model_id} tokens={len(token_ids)} rows={len(sp['logit_token_index'])}")
+        try:
+            return self._forward_sample(model_id, plan, token_ids, embed_handles, sp)
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+    def _forward_sample(self, model_id: int, plan: dict, token_ids: np.ndarray,
+                        embed_handles: Optional[np.ndarray], sp: dict) -> Optional[dict]:
         self._enter()
         ht, clock = self.host_times, time.perf_counter
         t0 = clock()
@@ -561,6 +573,15 @@ class ModelExecutor:
         return target.head_logits(ops.row_gather(h, dev["s_logit_token_index"]))
 
     def forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
+        if self._nvtx:
+            torch.cuda.nvtx.range_push(f"forward_verify model={model_id} tokens={len(token_ids)}")
+            try:
+                return self._forward_verify(model_id, plan, token_ids, vp)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return self._forward_verify(model_id, plan, token_ids, vp)
+
+    def _forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
         self._enter()
         sp = vp["sampling"]
         arrays = self._pack(plan, token_ids, sp, model_id)
