@@ -319,6 +319,7 @@ class EngineRuntime:
                     raise ValueError("recurrent-state models run on one GPU, without a draft model")
                 model = RwkvModel(mcfg, quant, store, self.device, None, layers)
                 cfg.prefix_cache_mode = "disable"  # a recurrent state cannot be shared or rolled back
+                cfg.kv_state_kind = "rnn_state"
             else:
                 model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
             if mi == 0 and mcfg.extra.get("vision"):
