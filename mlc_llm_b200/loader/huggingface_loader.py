@@ -421,7 +421,7 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _glm(cfg, m)
     elif mt == "chatglm":
         _chatglm(cfg, m)
-    elif mt == "phi3":
+    elif mt in ("phi3", "phi3_v", "phi3v"):
         _phi3(cfg, m)
     elif mt in ("phi", "phi-msft"):
         _phi(cfg, m)

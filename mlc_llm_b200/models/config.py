@@ -555,7 +555,34 @@ def _llava(cfg, mt):
     return d
 
 
+def _phi3v(cfg, mt):
+    """Phi-3-vision: the Phi-3 language model plus a CLIP tower read through the high-definition tiling
+    and 2x2 patch merge (reference: ``python/mlc_llm/model/phi3v/phi3v_model.py``). The vision geometry
+    comes from ``vision_config`` when present, else from the CLIP ViT-L/14-336 defaults the HuggingFace
+    config implies through ``img_processor``."""
+    d = _phi3(cfg, "phi3")
+    d["model_type"] = mt
+    vision = dict(cfg.get("vision_config") or {})
+    proc = cfg.get("img_processor") or {}
+    vision.setdefault("hidden_size", int(proc.get("image_dim_out", 1024)))
+    vision.setdefault("intermediate_size", 4 * vision["hidden_size"])
+    vision.setdefault("num_hidden_layers", 24)
+    vision.setdefault("num_attention_heads", 16)
+    vision.setdefault("image_size", 336)
+    vision.setdefault("patch_size", 14)
+    vision.setdefault("hidden_act", "quick_gelu")
+    vision.setdefault("layer_norm_eps", 1e-5)
+    vision.setdefault("hd_num", int(cfg.get("hd_num", 4)))
+    vision["kind"] = "phi3v"
+    extra = dict(d.get("extra") or {})
+    extra["vision"] = vision
+    extra["vision_feature_layer"] = int((proc.get("layer_idx", -2)))
+    d["extra"] = extra
+    return d
+
+
 _PARSERS = {
+    "phi3_v": _phi3v, "phi3v": _phi3v,
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,

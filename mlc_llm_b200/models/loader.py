@@ -46,7 +46,7 @@ def layer_partition(cfg: ModelConfig) -> list:
 
 
 def _wanted(name: str, cfg: ModelConfig, layers: range) -> bool:
-    if name.startswith(("vision_tower.", "multi_modal_projector.")) or name.endswith(".q_calibration_scale"):
+    if name.startswith(("vision_tower.", "multi_modal_projector.", "model.vision_embed_tokens.")) or name.endswith(".q_calibration_scale"):
         return False  # read by the vision tower / kept as calibration metadata, not by the decoder
     if name.startswith("model.layers."):
         li = int(name.split(".")[2])

@@ -31,6 +31,16 @@ MODEL_PRESETS = {
                           "num_attention_heads": 4, "image_size": 28, "patch_size": 14,
                           "hidden_act": "quick_gelu", "layer_norm_eps": 1e-5},
     },
+    # Phi-3-vision-shaped model: fused qkv / gate_up language model, CLIP tower read through the
+    # high-definition tiling (28-pixel tiles of 2x2 patches, so each tile merges into one feature)
+    "tiny-phi3v": {
+        "model_type": "phi3_v", "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 4, "vocab_size": 32064, "rms_norm_eps": 1e-5,
+        "rope_theta": 10000.0, "max_position_embeddings": 4096,
+        "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+                          "num_attention_heads": 4, "image_size": 56, "patch_size": 14,
+                          "hidden_act": "quick_gelu", "layer_norm_eps": 1e-5, "hd_num": 4},
+    },
     # 3-layer DeepSeek-V2-shaped model: latent attention (128 + 64 wide heads), one dense layer, then
     # layers with 8 routed experts (4 groups) and 2 shared experts
     "tiny-deepseek-v2": {

@@ -272,17 +272,18 @@ class EngineRuntime:
         from ..models import vision as V  # pylint: disable=import-outside-toplevel
 
         vis = mcfg.extra["vision"]
+        tower_cls = V.tower_class(vis)
         if info.random_seed is not None:
-            params = V.VisionTower.random_params(vis, mcfg.hidden_size, info.random_seed + 101)
+            params = tower_cls.random_params(vis, mcfg.hidden_size, info.random_seed + 101)
         elif info.hf_weights:
             params = V.load_hf_vision_params(info.model_path, vis, mcfg.hidden_size)
         else:
             from ..loader.tensor_cache import TensorCache  # pylint: disable=import-outside-toplevel
 
             cache = TensorCache(info.model_path)
-            params = {n: cache.get(n) for n in V.VisionTower.param_shapes(vis, mcfg.hidden_size)}
+            params = {n: cache.get(n) for n in tower_cls.param_shapes(vis, mcfg.hidden_size)}
         dtype = model.dtype if self.device.type == "cuda" else torch.float32
-        tower = V.VisionTower(vis, params, self.device, dtype,
+        tower = tower_cls(vis, params, self.device, dtype,
                               feature_layer=int(mcfg.extra.get("vision_feature_layer", -2)),
                               select=mcfg.extra.get("vision_feature_select_strategy", "default"),
                               projector_act=mcfg.extra.get("projector_hidden_act", "gelu"))
