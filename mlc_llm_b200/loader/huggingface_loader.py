@@ -396,6 +396,32 @@ def _internlm2(cfg: ModelConfig, m: Mapping) -> None:
     m.add("lm_head.weight", ["output.weight"])
 
 
+def _qwen35(cfg: ModelConfig, m: Mapping) -> None:
+    """Qwen3.5: ``q_proj`` holds, per head, the query rows followed by the output-gate rows; the four input
+    projections of a linear-attention layer are stacked into two matrices and the depthwise convolution
+    loses its singleton channel axis (reference: ``python/mlc_llm/model/qwen35/qwen35_loader.py``)."""
+    hq, d = cfg.num_attention_heads, cfg.head_dim
+    _llama_like(cfg, m)
+
+    def split_q(part: int):
+        return lambda w: w.reshape(hq, 2, d, -1)[:, part].reshape(hq * d, -1)
+
+    for i in range(cfg.num_hidden_layers):
+        s = dst = f"model.layers.{i}."
+        if cfg.layer_attn_kinds[i] == "linear":
+            la = s + "linear_attn."
+            m.add(dst + "linear_attn.in_proj_qkvz.weight", [la + "in_proj_qkv.weight", la + "in_proj_z.weight"], _cat0)
+            m.add(dst + "linear_attn.in_proj_ba.weight", [la + "in_proj_b.weight", la + "in_proj_a.weight"], _cat0)
+            m.add(dst + "linear_attn.conv1d.weight", [la + "conv1d.weight"], lambda ts: ts[0].reshape(ts[0].shape[0], -1))
+            for n in ("dt_bias", "A_log", "norm.weight", "out_proj.weight"):
+                m.add(dst + "linear_attn." + n, [la + n])
+        else:
+            a = s + "self_attn."
+            m.add(dst + "self_attn.qkv_proj.weight", [a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight"],
+                  lambda ts: torch.cat([split_q(0)(ts[0]), ts[1], ts[2]], 0))
+            m.add(dst + "self_attn.gate_proj.weight", [a + "q_proj.weight"], lambda ts: split_q(1)(ts[0]).contiguous())
+
+
 def _baichuan(cfg: ModelConfig, m: Mapping) -> None:
     _llama_like(cfg, m)
     for i in range(cfg.num_hidden_layers):
@@ -421,6 +447,8 @@ def build_mapping(cfg: ModelConfig) -> Mapping:
         _glm(cfg, m)
     elif mt == "chatglm":
         _chatglm(cfg, m)
+    elif mt in ("qwen3_5", "qwen3_5_text", "qwen35"):
+        _qwen35(cfg, m)
     elif mt in ("phi3", "phi3_v", "phi3v"):
         _phi3(cfg, m)
     elif mt in ("phi", "phi-msft"):

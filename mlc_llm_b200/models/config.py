@@ -555,6 +555,47 @@ def _llava(cfg, mt):
     return d
 
 
+def _qwen35(cfg, mt):
+    """Qwen3.5 hybrid: three of every four layers mix tokens with a gated delta-rule recurrence
+    (``linear_attention``: short causal convolution, per-head decay, one [key_dim, value_dim] state per
+    head), the fourth with softmax attention whose output is gated by a sigmoid of a second query-sized
+    projection; RMS norms store the deviation from one and a quarter of each head is rotated
+    (reference: ``python/mlc_llm/model/qwen35/qwen35_model.py``)."""
+    if isinstance(cfg.get("text_config"), dict):
+        outer, cfg = cfg, dict(cfg["text_config"])
+        for k in ("context_window_size", "prefill_chunk_size", "tensor_parallel_shards", "max_batch_size"):
+            if k in outer and k not in cfg:
+                cfg[k] = outer[k]
+    cfg = dict(cfg)
+    cfg.setdefault("head_dim", 256)
+    rp = cfg.get("rope_parameters") if isinstance(cfg.get("rope_parameters"), dict) else {}
+    if cfg.get("partial_rotary_factor") is None:
+        cfg["partial_rotary_factor"] = rp.get("partial_rotary_factor", 0.25)
+    if cfg.get("rope_theta") is None:
+        cfg["rope_theta"] = rp.get("rope_theta", 10000000)
+    cfg["rope_parameters"] = None  # the sectioned (multimodal) rotary layout equals the plain one for text
+    cfg["rope_scaling"] = None
+    d = _common(cfg, mt)
+    d["attention_bias"] = bool(_get(cfg, "attention_bias", default=False))
+    d["qk_norm"] = True
+    d["norm_weight_offset"] = 1.0
+    d["partial_rotary_factor"] = float(cfg["partial_rotary_factor"])
+    n = int(d["num_hidden_layers"])
+    interval = int(_get(cfg, "full_attention_interval", default=4))
+    types = _get(cfg, "layer_types") or ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
+                                          for i in range(n)]
+    d["layer_attn_kinds"] = ["mha" if t == "full_attention" else "linear" for t in types]
+    extra = dict(d.get("extra") or {})
+    extra["gdn"] = {"key_head_dim": int(_get(cfg, "linear_key_head_dim", default=128)),
+                    "value_head_dim": int(_get(cfg, "linear_value_head_dim", default=128)),
+                    "num_key_heads": int(_get(cfg, "linear_num_key_heads", default=16)),
+                    "num_value_heads": int(_get(cfg, "linear_num_value_heads", default=16)),
+                    "conv_kernel": int(_get(cfg, "linear_conv_kernel_dim", default=4))}
+    extra["attn_output_gate"] = True
+    d["extra"] = extra
+    return d
+
+
 def _phi3v(cfg, mt):
     """Phi-3-vision: the Phi-3 language model plus a CLIP tower read through the high-definition tiling
     and 2x2 patch merge (reference: ``python/mlc_llm/model/phi3v/phi3v_model.py``). The vision geometry
@@ -582,7 +623,7 @@ def _phi3v(cfg, mt):
 
 
 _PARSERS = {
-    "phi3_v": _phi3v, "phi3v": _phi3v,
+    "phi3_v": _phi3v, "phi3v": _phi3v, "qwen3_5": _qwen35, "qwen3_5_text": _qwen35, "qwen35": _qwen35,
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,

@@ -31,6 +31,15 @@ MODEL_PRESETS = {
                           "num_attention_heads": 4, "image_size": 28, "patch_size": 14,
                           "hidden_act": "quick_gelu", "layer_norm_eps": 1e-5},
     },
+    # Qwen3.5-shaped hybrid: three gated delta-rule layers, then one gated softmax-attention layer
+    "tiny-qwen35": {
+        "model_type": "qwen3_5_text", "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 4,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 32000,
+        "rms_norm_eps": 1e-6, "rope_theta": 10000000.0, "partial_rotary_factor": 0.25,
+        "max_position_embeddings": 4096, "linear_key_head_dim": 32, "linear_value_head_dim": 32,
+        "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_conv_kernel_dim": 4,
+        "full_attention_interval": 4,
+    },
     # Phi-3-vision-shaped model: fused qkv / gate_up language model, CLIP tower read through the
     # high-definition tiling (28-pixel tiles of 2x2 patches, so each tile merges into one feature)
     "tiny-phi3v": {

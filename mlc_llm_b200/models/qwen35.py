@@ -1,0 +1,196 @@
+"""Qwen3.5 hybrid decoder: gated delta-rule ("linear attention") layers with a per-sequence recurrent
+state, interleaved with softmax-attention layers on the paged KV cache.
+
+Reference: ``python/mlc_llm/model/qwen35/qwen35_model.py`` (GatedDeltaNet layers holding a convolution
+state and a recurrent state in an RNN-state object next to the paged KV cache of the attention layers).
+
+A linear layer does, per token t and value head h (state ``S`` is ``[key_dim, value_dim]``)::
+
+    [q; k; v] = silu(causal_conv1d([q; k; v] projections, kernel 4))      q, k L2-normalised, q / sqrt(key_dim)
+    g = -exp(A_log) * softplus(a + dt_bias)          beta = sigmoid(b)
+    S  <- S * exp(g)
+    S  <- S + k (x) (beta * (v - S^T k))             # delta rule: move the value stored under k towards v
+    o  = S^T q
+    y  = out_proj( rmsnorm(o) * weight * silu(z) )
+
+An attention layer is Qwen3 attention (per-head q / k RMS norm, a quarter of every head rotated) whose
+context is multiplied by ``sigmoid(gate)``, a second query-sized projection of the layer input.
+
+Only the attention layers own KV pages; the recurrent state lives in two slot tensors indexed by a
+sequence-id map, so a decode step over many sequences is one batched update.
+"""
+
+from __future__ import annotations
+
+import collections
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from .transformer import BatchInfo, DecoderModel
+
+STATE_SLOTS = 256  # sequences whose recurrent state is kept; the least recently used one is dropped
+
+
+def gated_delta_step(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                     g: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    """One token of the recurrence for a batch. ``state`` [B, H, dk, dv] fp32 (updated in place),
+    ``q`` / ``k`` [B, H, dk] (normalised, q scaled), ``v`` [B, H, dv], ``g`` / ``beta`` [B, H].
+    Returns the read-out [B, H, dv]."""
+    state.mul_(g.exp().unsqueeze(-1).unsqueeze(-1))
+    stored = torch.einsum("bhkv,bhk->bhv", state, k)
+    delta = (v - stored) * beta.unsqueeze(-1)
+    state.add_(k.unsqueeze(-1) * delta.unsqueeze(-2))
+    return torch.einsum("bhkv,bhk->bhv", state, q)
+
+
+class Qwen35Model(DecoderModel):
+    """Hybrid model behind the decoder-model interface of the executor."""
+
+    stateful = True  # per-sequence recurrent state: sequences are told apart by id, no CUDA-graph replay
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        c = self.cfg
+        if self.tp > 1:
+            raise NotImplementedError("the gated delta-rule layers are not sharded: run Qwen3.5 on one GPU")
+        g = c.extra["gdn"]
+        self.nk, self.nv = int(g["num_key_heads"]), int(g["num_value_heads"])
+        self.dk, self.dv = int(g["key_head_dim"]), int(g["value_head_dim"])
+        self.kernel = int(g["conv_kernel"])
+        self.key_dim, self.value_dim = self.nk * self.dk, self.nv * self.dv
+        self.conv_dim = 2 * self.key_dim + self.value_dim
+        kinds = c.layer_attn_kinds
+        self.attn_layers = [li for li in self.layers if kinds[li] != "linear"]
+        self.linear_layers = [li for li in self.layers if kinds[li] == "linear"]
+        self._kv_of = {li: i for i, li in enumerate(self.attn_layers)}
+        self._lin_of = {li: i for i, li in enumerate(self.linear_layers)}
+        self.slot_of: "collections.OrderedDict[int, int]" = collections.OrderedDict()
+        self.free_slots: List[int] = list(range(STATE_SLOTS - 1, -1, -1))
+        self.conv_state: Optional[torch.Tensor] = None
+        self.rec_state: Optional[torch.Tensor] = None
+        self._ctx: Optional[dict] = None
+
+    # ------------------------------------------------------------------ caches
+    def create_kv_cache(self, num_pages: int, page_size: int = 16) -> None:
+        self.page = page_size
+        self.kv_pages = torch.zeros(max(1, len(self.attn_layers)), num_pages, 2, self.hkv, page_size, self.d,
+                                    dtype=self.kv_dtype, device=self.device)
+
+    def _kv_layer(self, li: int) -> int:
+        return self._kv_of[li]
+
+    def kv_bytes_per_token(self) -> int:
+        return 2 * self.hkv * self.d * max(1, len(self.attn_layers)) * (2 if self.kv_dtype != torch.float32 else 4)
+
+    def move_tokens(self, moves: torch.Tensor) -> None:
+        if moves.numel():
+            raise NotImplementedError("a recurrent state cannot drop rejected draft tokens")
+
+    def _ensure_state(self) -> None:
+        if self.rec_state is None:
+            n = max(1, len(self.linear_layers))
+            self.conv_state = torch.zeros(n, STATE_SLOTS, self.conv_dim, self.kernel - 1, dtype=torch.float32,
+                                          device=self.device)
+            self.rec_state = torch.zeros(n, STATE_SLOTS, self.nv, self.dk, self.dv, dtype=torch.float32,
+                                         device=self.device)
+
+    def _slot(self, seq_id: int, start_pos: int) -> int:
+        slot = self.slot_of.pop(seq_id, None)
+        if slot is None:
+            if start_pos != 0:
+                raise RuntimeError(f"sequence {seq_id} continues at position {start_pos} without a recurrent "
+                                   "state (forked or reused sequences are not supported for hybrid models)")
+            if not self.free_slots:
+                _, slot = self.slot_of.popitem(last=False)
+            else:
+                slot = self.free_slots.pop()
+        if start_pos == 0:
+            self.conv_state[:, slot] = 0
+            self.rec_state[:, slot] = 0
+        self.slot_of[seq_id] = slot
+        return slot
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        self._ensure_state()
+        qi = np.asarray(b.q_indptr)
+        ids = [int(s) for s in np.asarray(b.seq_ids).tolist()]
+        pos0 = np.asarray(b.start_positions)
+        live = [i for i in range(len(ids)) if qi[i + 1] > qi[i]]
+        slots = [self._slot(ids[i], int(pos0[i])) for i in live]
+        lens = [int(qi[i + 1] - qi[i]) for i in live]
+        starts = [int(qi[i]) for i in live]
+        self._ctx = {"slots": torch.as_tensor(slots, dtype=torch.long, device=x.device), "lens": lens,
+                     "starts": starts, "decode": all(n == 1 for n in lens) and len(live) > 0,
+                     "rows": torch.as_tensor(starts, dtype=torch.long, device=x.device)}
+        return super().forward(x, b)
+
+    def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
+        if li in self._lin_of:
+            return self._gated_delta_net(li, h)
+        pre = f"model.layers.{li}.self_attn."
+        qkv = ops.linear(h, self.p.linears[pre + "qkv_proj"])
+        gate = ops.linear(h, self.p.linears[pre + "gate_proj"])
+        ctx = self._attention_core(li, qkv, b)
+        ctx = (ctx.float() * torch.sigmoid(gate.float())).to(h.dtype)
+        return ops.linear(ctx, self.p.linears[pre + "o_proj"])
+
+    def _gated_delta_net(self, li: int, h: torch.Tensor) -> torch.Tensor:
+        pre = f"model.layers.{li}.linear_attn."
+        t_all = h.shape[0]
+        tp = self.p.tensors
+        ctx = self._ctx
+        layer = self._lin_of[li]
+        proj = ops.linear(h, self.p.linears[pre + "in_proj_qkvz"]).float()
+        mixed, z = proj[:, : self.conv_dim], proj[:, self.conv_dim:]
+        ba = h.float() @ tp[pre + "in_proj_ba.weight"].float().t()
+        beta = torch.sigmoid(ba[:, : self.nv])
+        g = -tp[pre + "A_log"].exp() * F.softplus(ba[:, self.nv:] + tp[pre + "dt_bias"])
+        w = tp[pre + "conv1d.weight"]                                    # [conv_dim, K]
+        slots = ctx["slots"]
+        conv_all = self.conv_state[layer]
+        rec_all = self.rec_state[layer]
+        out = torch.empty(t_all, self.nv, self.dv, dtype=torch.float32, device=h.device)
+        rep = self.nv // self.nk
+
+        def heads(conv_out: torch.Tensor):
+            """Convolved rows [N, conv_dim] -> normalised q, k [N, nv, dk] and v [N, nv, dv]."""
+            q, k, v = torch.split(F.silu(conv_out), [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+            q = q.reshape(-1, self.nk, self.dk)
+            k = k.reshape(-1, self.nk, self.dk)
+            q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * (self.dk ** -0.5)
+            k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+            return q, k, v.reshape(-1, self.nv, self.dv)
+
+        if ctx["decode"]:
+            # one token per sequence: one batched window product and one batched state update
+            rows = ctx["rows"]
+            window = torch.cat([conv_all[slots], mixed[rows].unsqueeze(-1)], dim=-1)   # [B, conv_dim, K]
+            conv_all[slots] = window[:, :, 1:]
+            q, k, v = heads((window * w.unsqueeze(0)).sum(-1))
+            state = rec_all[slots]
+            out[rows] = gated_delta_step(state, q, k, v, g[rows], beta[rows])
+            rec_all[slots] = state
+        else:
+            for j, (start, n) in enumerate(zip(ctx["starts"], ctx["lens"])):
+                slot = slots[j]
+                seq = torch.cat([conv_all[slot], mixed[start:start + n].t()], dim=-1)   # [conv_dim, K - 1 + n]
+                conv_all[slot] = seq[:, -(self.kernel - 1):]
+                conv = F.conv1d(seq.unsqueeze(0), w.unsqueeze(1), groups=self.conv_dim)[0].t()  # [n, conv_dim]
+                q, k, v = heads(conv)
+                state = rec_all[slot].unsqueeze(0).clone()
+                gs, bs = g[start:start + n], beta[start:start + n]
+                for t in range(n):
+                    out[start + t] = gated_delta_step(state, q[t:t + 1], k[t:t + 1], v[t:t + 1],
+                                                      gs[t:t + 1], bs[t:t + 1])[0]
+                rec_all[slot] = state[0]
+        # gated RMS norm over every value head, then the output projection
+        o = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
+        o = o * tp[pre + "norm.weight"].view(1, 1, -1) * F.silu(z.reshape(t_all, self.nv, self.dv))
+        return ops.linear(o.reshape(t_all, self.value_dim).to(h.dtype), self.p.linears[pre + "out_proj"])

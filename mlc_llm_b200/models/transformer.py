@@ -96,6 +96,10 @@ class DecoderModel:
         self.kv_pages = torch.zeros(n, num_pages, 2, self.hkv, page_size, self.d, dtype=self.kv_dtype,
                                     device=self.device)
 
+    def _kv_layer(self, li: int) -> int:
+        """Index of layer ``li`` in ``kv_pages`` (models that cache only some layers override this)."""
+        return li - self.layers.start
+
     @property
     def kv_dtype(self) -> torch.dtype:
         return self.dtype if self.dtype != torch.float32 or self.device.type == "cpu" else torch.float16
@@ -208,7 +212,7 @@ class DecoderModel:
         kind = c.layer_attn_kinds[li] if c.layer_attn_kinds is not None else None
         sliding = kind == "mha_sliding"
         inv = self.inv_freq_local if (sliding and self.inv_freq_local is not None) else self.inv_freq
-        local = li - self.layers.start
+        local = self._kv_layer(li)
         kvstart = b.q_kvstart
         l4 = c.extra.get("llama4")
         if l4 is not None:
@@ -534,6 +538,7 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
         if not cfg.extra.get("no_pre_norm") and not (eagle and i == 0):
             norm(p + "input_layernorm")
         mla = cfg.extra.get("mla")
+        linear_layer = bool(cfg.extra.get("gdn")) and cfg.layer_attn_kinds[i] == "linear"
         if mla:
             qk = mla["qk_nope_head_dim"] + mla["qk_rope_head_dim"]
             if mla.get("q_lora_rank"):
@@ -547,14 +552,29 @@ def param_specs(cfg: ModelConfig) -> Dict[str, tuple]:
             specs[p + "self_attn.kv_b_proj.weight"] = ((hq * (mla["qk_nope_head_dim"] + mla["v_head_dim"]),
                                                         mla["kv_lora_rank"]), "linear")
             specs[p + "self_attn.o_proj.weight"] = ((h, hq * mla["v_head_dim"]), "linear")
+        elif linear_layer:
+            # gated delta-rule mixer: [q; k; v] and the output gate z in one projection, the per-head
+            # write strength / decay inputs (b, a) in a second, unquantised one
+            g = cfg.extra["gdn"]
+            kd, vd = g["num_key_heads"] * g["key_head_dim"], g["num_value_heads"] * g["value_head_dim"]
+            la = p + "linear_attn."
+            specs[la + "in_proj_qkvz.weight"] = ((2 * kd + 2 * vd, h), "linear")
+            specs[la + "in_proj_ba.weight"] = ((2 * g["num_value_heads"], h), "router")
+            specs[la + "conv1d.weight"] = ((2 * kd + vd, g["conv_kernel"]), "f32")
+            specs[la + "dt_bias"] = ((g["num_value_heads"],), "f32")
+            specs[la + "A_log"] = ((g["num_value_heads"],), "f32")
+            specs[la + "norm.weight"] = ((g["value_head_dim"],), "f32")
+            specs[la + "out_proj.weight"] = ((h, vd), "linear")
         else:
             specs[p + "self_attn.qkv_proj.weight"] = (((hq + 2 * hkv) * d, h), "linear")
+            if cfg.extra.get("attn_output_gate"):
+                specs[p + "self_attn.gate_proj.weight"] = ((hq * d, h), "linear")
             if cfg.attention_bias:
                 specs[p + "self_attn.qkv_proj.bias"] = (((hq + 2 * hkv) * d,), "bias")
             specs[p + "self_attn.o_proj.weight"] = ((h, hq * d), "linear")
         if cfg.attention_out_bias:
             specs[p + "self_attn.o_proj.bias"] = ((h,), "bias")
-        if cfg.qk_norm:
+        if cfg.qk_norm and not linear_layer:
             full = bool(cfg.extra.get("qk_norm_full"))
             specs[p + "self_attn.q_norm.weight"] = ((hq * d if full else d,), "norm")
             specs[p + "self_attn.k_norm.weight"] = ((hkv * d if full else d,), "norm")

@@ -321,6 +321,13 @@ class EngineRuntime:
                 model = RwkvModel(mcfg, quant, store, self.device, None, layers)
                 cfg.prefix_cache_mode = "disable"  # a recurrent state cannot be shared or rolled back
                 cfg.kv_state_kind = "rnn_state"
+            elif mcfg.extra.get("gdn"):
+                from ..models.qwen35 import Qwen35Model  # pylint: disable=import-outside-toplevel
+
+                if tp > 1 or pp > 1 or len(self.models_info) > 1:
+                    raise ValueError("hybrid recurrent-state models run on one GPU, without a draft model")
+                model = Qwen35Model(mcfg, quant, store, self.device, None, layers)
+                cfg.prefix_cache_mode = "disable"  # the recurrent half of the state cannot be shared or rolled back
             else:
                 model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
             if mi == 0 and mcfg.extra.get("vision"):
