@@ -155,8 +155,8 @@ def group_dequantize(qw: torch.Tensor, qs: torch.Tensor, q: Quantization, k: Opt
     dt = out_dtype or q.torch_dtype
     deq = (vals.to(torch.float32) - q.max_int).to(dt) * qs.to(dt).unsqueeze(-1)
     deq = deq.reshape(*lead, n, ng * q.group_size)
-    if k is not None:
-        deq = deq[..., :k]
+    if k is not None and k != deq.shape[-1]:
+        deq = deq[..., :k].contiguous()  # kernels read the result through a raw pointer with row stride k
     return deq
 
 

@@ -45,7 +45,7 @@ def test_gemm_dense_bias_fp32_out():
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (7, 256, 128), (64, 512, 4096), (256, 384, 1024),
-                                   (600, 1376, 256)])
+                                   (600, 1376, 256), (24, 256, 688)])  # 688: groups padded, dequantised cold path
 def test_gemm_q4f16(m, n, k):
     torch.manual_seed(2)
     quant = Q.get("q4f16_1")
