@@ -55,7 +55,7 @@ def test_gemm_q4f16(m, n, k):
     x = (torch.randn(m, k) * 0.5).half().to(DEV)
     y = ops.linear(x, lw)
     ops.check_status(x.device)
-    wd = Q.group_dequantize(qw, qs, quant)
+    wd = Q.group_dequantize(qw, qs, quant, k=k)
     yr = ref.linear_dense(x.cpu(), wd)
     _close(y, yr, 2e-2, 2e-2)
 
