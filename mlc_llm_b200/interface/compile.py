@@ -36,7 +36,8 @@ def model_metadata(cfg: model_config.ModelConfig, quant: Q.Quantization) -> Dict
         "attention_sink_size": cfg.attention_sink_size, "prefill_chunk_size": cfg.prefill_chunk_size,
         "max_batch_size": cfg.max_batch_size, "tensor_parallel_shards": cfg.tensor_parallel_shards,
         "pipeline_parallel_stages": cfg.pipeline_parallel_stages,
-        "kv_state_kind": "rnn_state" if cfg.extra.get("rwkv") else ("none" if cfg.extra.get("medusa") else "kv_cache"),
+        "kv_state_kind": "rnn_state" if cfg.extra.get("rwkv") else (
+            "hybrid" if cfg.extra.get("gdn") else ("none" if cfg.extra.get("medusa") else "kv_cache")),
         "kv_cache": cfg.kv_cache_metadata(),
         "params": params, "memory_usage": {"params_bytes": total},
         "target": "sm_100a", "library": "libmlcb200_kernels.so",

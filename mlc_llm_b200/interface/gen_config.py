@@ -41,7 +41,16 @@ def gen_config(config: str, model_type: str, quantization: str, conv_template: s
     cfg = model_config.from_dict(mt, merged)
     if cfg.sliding_window_size and cfg.sliding_window_size > 0:
         cfg.context_window_size = -1
-    mc = cfg.asdict()
+    # the checkpoint's own keys stay in the model section (family parsers read settings such as expert
+    # routing, latent-attention ranks, recurrent-layer geometry or a nested text / vision config from
+    # them when the engine parses the section again); resolved structural fields are written over them
+    resolved = cfg.asdict()
+    mc = {k: v for k, v in merged.items() if k not in ("architectures", "torch_dtype", "dtype", "transformers_version",
+                                                        "id2label", "label2id", "auto_map")}
+    for k, v in resolved.items():
+        if k not in mc or k in overrides or k in ("context_window_size", "sliding_window_size",
+                                                  "prefill_chunk_size", "attention_sink_size"):
+            mc[k] = v
     if disaggregation:
         mc["disaggregation"] = True
     os.makedirs(output, exist_ok=True)

@@ -10,6 +10,10 @@ class BadRequestError(ValueError):
     """Invalid request content; rendered as HTTP 400."""
 
 
+class RequestFailedError(RuntimeError):
+    """The engine could not finish a request (a step raised); rendered as HTTP 500."""
+
+
 class ErrorResponse(BaseModel):
     object: str = "error"
     message: str

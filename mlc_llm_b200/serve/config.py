@@ -29,7 +29,7 @@ class EngineConfig:  # pylint: disable=too-many-instance-attributes
     sliding_window_size: Optional[int] = None
     attention_sink_size: Optional[int] = None
     max_history_size: Optional[int] = None
-    kv_state_kind: Optional[Literal["kv_cache", "rnn_state"]] = None
+    kv_state_kind: Optional[Literal["kv_cache", "rnn_state", "hybrid"]] = None
     speculative_mode: Literal["disable", "small_draft", "eagle", "medusa"] = "disable"
     spec_draft_length: int = 0
     spec_tree_width: int = 1

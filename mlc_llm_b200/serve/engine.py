@@ -143,8 +143,9 @@ class MLCEngineBase:
                 # engine-wide failure: fail every open request
                 with self._sinks_lock:
                     sinks = list(self._sinks.items())
+                why = "".join(out["group_extra_prefix_string"][:1])
                 for _, sink in sinks:
-                    sink.deliver([_StreamItem(i, "", [], "error", None) for i in range(len(sink.streamers))])
+                    sink.deliver([_StreamItem(i, why, [], "error", None) for i in range(len(sink.streamers))])
                 continue
             with self._sinks_lock:
                 sink = self._sinks.get(rid)
@@ -590,6 +591,12 @@ class _Accumulator:
     def completion_response(self, request_id, model) -> openai.CompletionResponse:
         choices = []
         for i, t in enumerate(self.texts):
+            if self.finish[i] == "error":
+                # the completions protocol has no finish reason for a failed request: the error text the
+                # engine put in the stream becomes an exception instead of an empty "stop"
+                from ..protocol.error_protocol import RequestFailedError  # pylint: disable=import-outside-toplevel
+
+                raise RequestFailedError("request failed: " + "".join(t))
             fr = self.finish[i] if self.finish[i] in (None, "stop", "length", "preempt") else "stop"
             choices.append(openai.CompletionResponseChoice(
                 index=i, finish_reason=fr, text="".join(t),

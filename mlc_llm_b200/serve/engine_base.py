@@ -328,6 +328,7 @@ class EngineRuntime:
                     raise ValueError("hybrid recurrent-state models run on one GPU, without a draft model")
                 model = Qwen35Model(mcfg, quant, store, self.device, None, layers)
                 cfg.prefix_cache_mode = "disable"  # the recurrent half of the state cannot be shared or rolled back
+                cfg.kv_state_kind = "hybrid"
             else:
                 model = DecoderModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
             if mi == 0 and mcfg.extra.get("vision"):

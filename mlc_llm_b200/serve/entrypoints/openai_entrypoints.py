@@ -77,6 +77,8 @@ async def request_completion(request: openai.CompletionRequest, raw_request: fas
         return await _await_or_abort(task, raw_request, engine, request_id)
     except error_protocol.BadRequestError as err:
         return error_protocol.create_error_response(HTTPStatus.BAD_REQUEST, message=str(err))
+    except error_protocol.RequestFailedError as err:
+        return error_protocol.create_error_response(HTTPStatus.INTERNAL_SERVER_ERROR, message=str(err))
 
 
 @app.post("/v1/chat/completions")

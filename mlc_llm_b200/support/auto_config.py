@@ -35,7 +35,9 @@ def detect_config(config: str) -> Tuple[str, dict]:
         inner.setdefault("model_type", d["model_type"])
         d = inner
     # multimodal wrappers keep the language model under text_config
-    if "text_config" in d and isinstance(d["text_config"], dict) and "hidden_size" not in d:
+    # (families whose parser reads the wrapper itself -- it also carries their vision section -- keep it)
+    if "text_config" in d and isinstance(d["text_config"], dict) and "hidden_size" not in d \
+            and d.get("model_type") not in ("llava", "llama4", "qwen3_5"):
         merged = dict(d["text_config"])
         merged.setdefault("model_type", d.get("model_type"))
         d = merged

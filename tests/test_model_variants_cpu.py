@@ -3,6 +3,7 @@ identities against the plain Llama forward."""
 import math
 
 import numpy as np
+import pytest
 import torch
 
 from mlc_llm_b200 import _core
@@ -155,3 +156,28 @@ def test_qwen1_checkpoint_layout_equals_qwen2(tmp_path):
     got = _logits(DecoderModel(c1, quant, loader.load_hf_params(str(tmp_path / "q1"), c1, quant, torch.device("cpu")),
                                torch.device("cpu")), toks)
     assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("preset", ["tiny-deepseek-v2", "tiny-llava", "tiny-phi3v", "tiny-qwen35", "tiny-rwkv6",
+                                    "tiny-eagle", "tiny-medusa"])
+def test_gen_config_keeps_what_the_family_parser_needs(preset, tmp_path):
+    """The model section written by gen_config parses back to the same configuration, family-specific
+    settings (latent-attention ranks, vision section, recurrent geometry, draft-head sizes) included."""
+    import json
+    import os
+
+    from mlc_llm_b200.interface.gen_config import gen_config
+    from mlc_llm_b200.models import config as C
+    from mlc_llm_b200.models.presets import MODEL_PRESETS
+
+    src = tmp_path / "src"
+    src.mkdir()
+    json.dump(MODEL_PRESETS[preset], open(src / "config.json", "w"))
+    out = str(tmp_path / "out")
+    gen_config(str(src), "auto", "q0f16", "LM", None, None, None, None, None, None, None, 64, out)
+    chat = json.load(open(os.path.join(out, "mlc-chat-config.json")))
+    again = C.from_dict(chat["model_type"], chat["model_config"])
+    first = C.from_dict(MODEL_PRESETS[preset]["model_type"], dict(MODEL_PRESETS[preset], max_batch_size=64))
+    assert again.extra == first.extra
+    a, b = again.asdict(), first.asdict()
+    assert a == b, {k: (a[k], b[k]) for k in a if a[k] != b[k]}

@@ -135,3 +135,54 @@ def test_qwen35_through_the_engine():
         assert a.usage.completion_tokens == 6
     finally:
         eng.terminate()
+
+
+def test_qwen35_gen_config_convert_and_generate(tmp_path):
+    """HuggingFace checkpoint -> mlc-chat-config + converted weights -> engine; greedy tokens equal
+    ``transformers``' (both the raw artifact and the compile metadata name the hybrid state)."""
+    import os
+
+    import tokenizers
+
+    from mlc_llm_b200.cli import compile as cli_compile
+    from mlc_llm_b200.cli import gen_config as cli_gen
+    from mlc_llm_b200.interface.convert_weight import convert_weight
+    from mlc_llm_b200.serve.config import EngineConfig
+    from mlc_llm_b200.serve.engine import MLCEngine
+
+    if not hasattr(transformers, "Qwen3_5TextConfig"):
+        pytest.skip("transformers has no Qwen3.5")
+    src = tmp_path / "hf"
+    src.mkdir()
+    tok = tokenizers.Tokenizer(tokenizers.models.BPE(unk_token=None))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    trainer = tokenizers.trainers.BpeTrainer(vocab_size=300, special_tokens=["<s>", "</s>"],
+                                             initial_alphabet=tokenizers.pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["the quick brown fox jumps over the lazy dog", "hello world of models"] * 4, trainer)
+    tok.save(str(src / "tokenizer.json"))
+    torch.manual_seed(1)
+    hf_cfg = transformers.Qwen3_5TextConfig(**dict(HF_CFG, vocab_size=tok.get_vocab_size(), bos_token_id=0,
+                                                   eos_token_id=1))
+    hf = transformers.Qwen3_5ForCausalLM(hf_cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.mul_(6.0) if p.dim() > 1 else None
+    hf.save_pretrained(src, safe_serialization=True)
+    out = str(tmp_path / "mlc")
+    cli_gen.main([str(src), "--quantization", "q0f32", "--conv-template", "LM", "--output", out])
+    chat = json.load(open(os.path.join(out, "mlc-chat-config.json")))
+    assert chat["model_type"] in ("qwen3_5_text", "qwen3_5")
+    convert_weight(str(src), "q0f32", output=out, verbose=False, encode_format="raw")
+    lib = str(tmp_path / "lib.json")
+    cli_compile.main([out, "--output", lib])
+    assert json.load(open(lib))["kv_state_kind"] == "hybrid"
+    eng = MLCEngine(out, "cpu", engine_config=EngineConfig(mode="local"))
+    try:
+        prompt = tok.encode("the quick brown fox").ids
+        want = hf.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, eos_token_id=None,
+                           pad_token_id=0)[0, len(prompt):].tolist()
+        resp = eng.completions.create(prompt=prompt, max_tokens=8, temperature=0.0, debug_config={"ignore_eos": True})
+        assert resp.choices[0].text == tok.decode(want), resp
+    finally:
+        eng.terminate()
