@@ -596,6 +596,36 @@ def _qwen35(cfg, mt):
     return d
 
 
+def _qwen2_5_vl(cfg, mt):
+    """Qwen2.5-VL language model: Qwen2 blocks whose rotary frequency bands are dealt to a (time, height,
+    width) position triple (``mrope_section``). For text the three agree, which is plain rotary embedding
+    (reference: ``python/mlc_llm/model/qwen2_5_vl/qwen2_5_vl_model.py``; position triples for prompts with
+    vision grids: ``ops/mrope.py``)."""
+    outer = cfg
+    if isinstance(cfg.get("text_config"), dict):
+        cfg = dict(cfg["text_config"])
+        for k in ("context_window_size", "prefill_chunk_size", "tensor_parallel_shards", "max_batch_size",
+                  "pipeline_parallel_stages", "tie_word_embeddings"):
+            if k in outer and k not in cfg:
+                cfg[k] = outer[k]
+    cfg = dict(cfg)
+    rp = cfg.get("rope_parameters") if isinstance(cfg.get("rope_parameters"), dict) else (cfg.get("rope_scaling") or {})
+    section = rp.get("mrope_section")
+    if cfg.get("rope_theta") is None and "rope_theta" in rp:
+        cfg["rope_theta"] = rp["rope_theta"]
+    cfg["rope_parameters"] = None
+    cfg["rope_scaling"] = None
+    d = _qwen2(cfg, mt)
+    vis = outer.get("vision_config") or {}
+    d["extra"] = {"mrope_section": [int(x) for x in section] if section else None,
+                  "vision_tokens": {"vision_start_token_id": int(outer.get("vision_start_token_id", 151652)),
+                                    "image_token_id": int(outer.get("image_token_id", 151655)),
+                                    "video_token_id": int(outer.get("video_token_id", 151656)),
+                                    "spatial_merge_size": int(vis.get("spatial_merge_size", 2)),
+                                    "tokens_per_second": float(vis.get("tokens_per_second", 2))}}
+    return d
+
+
 def _phi3v(cfg, mt):
     """Phi-3-vision: the Phi-3 language model plus a CLIP tower read through the high-definition tiling
     and 2x2 patch merge (reference: ``python/mlc_llm/model/phi3v/phi3v_model.py``). The vision geometry
@@ -623,7 +653,7 @@ def _phi3v(cfg, mt):
 
 
 _PARSERS = {
-    "phi3_v": _phi3v, "phi3v": _phi3v, "qwen3_5": _qwen35, "qwen3_5_text": _qwen35, "qwen35": _qwen35,
+    "phi3_v": _phi3v, "phi3v": _phi3v, "qwen2_5_vl": _qwen2_5_vl, "qwen2_5_vl_text": _qwen2_5_vl, "qwen3_5": _qwen35, "qwen3_5_text": _qwen35, "qwen35": _qwen35,
     "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,

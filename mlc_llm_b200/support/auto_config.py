@@ -37,7 +37,7 @@ def detect_config(config: str) -> Tuple[str, dict]:
     # multimodal wrappers keep the language model under text_config
     # (families whose parser reads the wrapper itself -- it also carries their vision section -- keep it)
     if "text_config" in d and isinstance(d["text_config"], dict) and "hidden_size" not in d \
-            and d.get("model_type") not in ("llava", "llama4", "qwen3_5"):
+            and d.get("model_type") not in ("llava", "llama4", "qwen3_5", "qwen2_5_vl"):
         merged = dict(d["text_config"])
         merged.setdefault("model_type", d.get("model_type"))
         d = merged
