@@ -33,6 +33,7 @@ from .. import ops
 from .transformer import BatchInfo, DecoderModel
 
 STATE_SLOTS = 256  # sequences whose recurrent state is kept; the least recently used one is dropped
+FIRST_SLOTS = 16   # the slot tensors start this large and double on demand (a slot is megabytes per layer)
 
 
 def gated_delta_step(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -45,6 +46,42 @@ def gated_delta_step(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: t
     delta = (v - stored) * beta.unsqueeze(-1)
     state.add_(k.unsqueeze(-1) * delta.unsqueeze(-2))
     return torch.einsum("bhkv,bhk->bhv", state, q)
+
+
+def gated_delta_chunk(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                      g: torch.Tensor, beta: torch.Tensor, chunk: int = 64) -> torch.Tensor:
+    """The same recurrence for ``n`` consecutive tokens of one sequence, ``chunk`` tokens per step, as
+    matrix products. ``state`` [H, dk, dv] fp32 (updated in place), ``q`` / ``k`` [n, H, dk], ``v`` [n, H, dv],
+    ``g`` / ``beta`` [n, H]; returns [n, H, dv].
+
+    Inside a chunk that starts from state ``S0``, with ``G`` the running sum of ``g`` and ``u_i`` the row
+    written at token i (``S_i = exp(g_i) S_{i-1} + k_i u_i^T``):
+
+        u_i = beta_i * (v_i - exp(G_i) S0^T k_i - sum_{j<i} exp(G_i - G_j) (k_i . k_j) u_j)
+        o_i = exp(G_i) S0^T q_i + sum_{j<=i} exp(G_i - G_j) (q_i . k_j) u_j
+        S_end = exp(G_end) S0 + sum_j exp(G_end - G_j) k_j u_j^T
+
+    The first line is a unit-lower-triangular system in ``u``; every exponent is <= 0.
+    """
+    n = q.shape[0]
+    out = torch.empty(n, v.shape[1], v.shape[2], dtype=torch.float32, device=q.device)
+    for c0 in range(0, n, chunk):
+        c1 = min(n, c0 + chunk)
+        qc, kc, vc = (x[c0:c1].transpose(0, 1).float() for x in (q, k, v))          # [H, C, d]
+        gc, bc = g[c0:c1].t().float(), beta[c0:c1].t().float()                       # [H, C]
+        cum = gc.cumsum(-1)
+        rel = cum.unsqueeze(-1) - cum.unsqueeze(-2)                                   # G_i - G_j
+        lower = torch.ones(c1 - c0, c1 - c0, dtype=torch.bool, device=q.device).tril()
+        decay = torch.where(lower, rel, torch.full_like(rel, float("-inf"))).exp()    # 0 above the diagonal
+        grow = cum.exp().unsqueeze(-1)                                                # exp(G_i)
+        kk = (kc @ kc.transpose(-1, -2)) * decay * bc.unsqueeze(-1)
+        system = torch.eye(c1 - c0, device=q.device) + kk.tril(-1)
+        rhs = bc.unsqueeze(-1) * (vc - grow * (kc @ state))
+        u = torch.linalg.solve_triangular(system, rhs, upper=False, unitriangular=True)
+        out[c0:c1] = (grow * (qc @ state) + ((qc @ kc.transpose(-1, -2)) * decay) @ u).transpose(0, 1)
+        tail = (cum[:, -1:] - cum).exp().unsqueeze(-1)                                # exp(G_end - G_j)
+        state.mul_(cum[:, -1].exp().view(-1, 1, 1)).add_((kc * tail).transpose(-1, -2) @ u)
+    return out
 
 
 class Qwen35Model(DecoderModel):
@@ -69,7 +106,8 @@ class Qwen35Model(DecoderModel):
         self._kv_of = {li: i for i, li in enumerate(self.attn_layers)}
         self._lin_of = {li: i for i, li in enumerate(self.linear_layers)}
         self.slot_of: "collections.OrderedDict[int, int]" = collections.OrderedDict()
-        self.free_slots: List[int] = list(range(STATE_SLOTS - 1, -1, -1))
+        self.free_slots: List[int] = []
+        self.capacity = 0
         self.conv_state: Optional[torch.Tensor] = None
         self.rec_state: Optional[torch.Tensor] = None
         self._ctx: Optional[dict] = None
@@ -90,13 +128,20 @@ class Qwen35Model(DecoderModel):
         if moves.numel():
             raise NotImplementedError("a recurrent state cannot drop rejected draft tokens")
 
+    def _grow_state(self) -> None:
+        """Add slots: 16 at first, then doubling, up to ``STATE_SLOTS``."""
+        n = max(1, len(self.linear_layers))
+        add = FIRST_SLOTS if self.capacity == 0 else min(self.capacity, STATE_SLOTS - self.capacity)
+        conv = torch.zeros(n, add, self.conv_dim, self.kernel - 1, dtype=torch.float32, device=self.device)
+        rec = torch.zeros(n, add, self.nv, self.dk, self.dv, dtype=torch.float32, device=self.device)
+        self.conv_state = conv if self.conv_state is None else torch.cat([self.conv_state, conv], dim=1)
+        self.rec_state = rec if self.rec_state is None else torch.cat([self.rec_state, rec], dim=1)
+        self.free_slots.extend(range(self.capacity + add - 1, self.capacity - 1, -1))
+        self.capacity += add
+
     def _ensure_state(self) -> None:
         if self.rec_state is None:
-            n = max(1, len(self.linear_layers))
-            self.conv_state = torch.zeros(n, STATE_SLOTS, self.conv_dim, self.kernel - 1, dtype=torch.float32,
-                                          device=self.device)
-            self.rec_state = torch.zeros(n, STATE_SLOTS, self.nv, self.dk, self.dv, dtype=torch.float32,
-                                         device=self.device)
+            self._grow_state()
 
     def _slot(self, seq_id: int, start_pos: int) -> int:
         slot = self.slot_of.pop(seq_id, None)
@@ -104,6 +149,8 @@ class Qwen35Model(DecoderModel):
             if start_pos != 0:
                 raise RuntimeError(f"sequence {seq_id} continues at position {start_pos} without a recurrent "
                                    "state (forked or reused sequences are not supported for hybrid models)")
+            if not self.free_slots and self.capacity < STATE_SLOTS:
+                self._grow_state()
             if not self.free_slots:
                 _, slot = self.slot_of.popitem(last=False)
             else:
@@ -184,12 +231,9 @@ class Qwen35Model(DecoderModel):
                 conv_all[slot] = seq[:, -(self.kernel - 1):]
                 conv = F.conv1d(seq.unsqueeze(0), w.unsqueeze(1), groups=self.conv_dim)[0].t()  # [n, conv_dim]
                 q, k, v = heads(conv)
-                state = rec_all[slot].unsqueeze(0).clone()
-                gs, bs = g[start:start + n], beta[start:start + n]
-                for t in range(n):
-                    out[start + t] = gated_delta_step(state, q[t:t + 1], k[t:t + 1], v[t:t + 1],
-                                                      gs[t:t + 1], bs[t:t + 1])[0]
-                rec_all[slot] = state[0]
+                state = rec_all[slot].clone()
+                out[start:start + n] = gated_delta_chunk(state, q, k, v, g[start:start + n], beta[start:start + n])
+                rec_all[slot] = state
         # gated RMS norm over every value head, then the output projection
         o = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
         o = o * tp[pre + "norm.weight"].view(1, 1, -1) * F.silu(z.reshape(t_all, self.nv, self.dv))

@@ -186,3 +186,40 @@ def test_qwen35_gen_config_convert_and_generate(tmp_path):
         assert resp.choices[0].text == tok.decode(want), resp
     finally:
         eng.terminate()
+
+
+def test_chunked_recurrence_equals_the_token_loop():
+    from mlc_llm_b200.models.qwen35 import gated_delta_chunk
+
+    g0 = torch.Generator().manual_seed(0)
+    n, h, dk, dv = 150, 3, 8, 5  # two full chunks and a ragged one
+    q = torch.nn.functional.normalize(torch.randn(n, h, dk, generator=g0), dim=-1) * dk ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(n, h, dk, generator=g0), dim=-1)
+    v = torch.randn(n, h, dv, generator=g0)
+    g = -torch.rand(n, h, generator=g0) * 0.3
+    beta = torch.rand(n, h, generator=g0)
+    s0 = torch.randn(h, dk, dv, generator=g0)
+    loop_state = s0.clone().unsqueeze(0)
+    want = torch.stack([gated_delta_step(loop_state, q[t:t + 1], k[t:t + 1], v[t:t + 1], g[t:t + 1], beta[t:t + 1])[0]
+                        for t in range(n)])
+    state = s0.clone()
+    got = gated_delta_chunk(state, q, k, v, g, beta, chunk=64)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), (got - want).abs().max()
+    assert torch.allclose(state, loop_state[0], atol=1e-4, rtol=1e-4)
+
+
+def test_state_slots_grow_and_recycle(tmp_path, monkeypatch):
+    from mlc_llm_b200.models import qwen35
+
+    monkeypatch.setattr(qwen35, "FIRST_SLOTS", 2)
+    monkeypatch.setattr(qwen35, "STATE_SLOTS", 4)
+    _, model = _build(tmp_path)
+    model._ensure_state()
+    assert model.capacity == 2
+    slots = [model._slot(s, 0) for s in range(4)]
+    assert sorted(slots) == [0, 1, 2, 3] and model.capacity == 4
+    # a fifth sequence takes the slot of the least recently used one; continuing that one is an error
+    assert model._slot(4, 0) == slots[0]
+    with pytest.raises(RuntimeError):
+        model._slot(0, 7)
+    assert model._slot(1, 5) == slots[1]  # a live sequence keeps its slot
