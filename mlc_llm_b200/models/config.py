@@ -128,6 +128,13 @@ def _common(cfg: Dict[str, Any], model_type: str) -> Dict[str, Any]:
             cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
         if "partial_rotary_factor" in rp and cfg.get("partial_rotary_factor") is None:
             cfg["partial_rotary_factor"] = rp["partial_rotary_factor"]
+    if isinstance(cfg.get("rope_scaling"), dict):
+        # stretched-context variants need the trained and the served window next to their factors
+        rs = dict(cfg["rope_scaling"])
+        for key in ("original_max_position_embeddings", "max_position_embeddings"):
+            if rs.get(key) is None and cfg.get(key) is not None:
+                rs[key] = cfg[key]
+        cfg = dict(cfg, rope_scaling=rs)
     out = dict(
         model_type=model_type,
         hidden_size=_get(cfg, "hidden_size", "n_embd", "d_model", default=4096),
@@ -233,6 +240,26 @@ def _mistral(cfg, mt):
         d["sliding_window_size"] = int(sw)
         d["attention_sink_size"] = max(0, d["attention_sink_size"] or 0) if d["attention_sink_size"] != -1 else 4
         d["context_window_size"] = -1 if False else 0
+    return d
+
+
+def _ministral3(cfg, mt):
+    """Ministral 3: Mistral blocks under ``text_config``, YaRN rotary scaling, and queries multiplied by
+    ``1 + beta * ln(1 + floor(position / trained window))`` (reference:
+    ``python/mlc_llm/model/ministral3/ministral3_model.py``)."""
+    if isinstance(cfg.get("text_config"), dict):
+        outer, cfg = cfg, dict(cfg["text_config"])
+        for k in ("context_window_size", "prefill_chunk_size", "sliding_window_size", "attention_sink_size",
+                  "tensor_parallel_shards", "pipeline_parallel_stages", "max_batch_size"):
+            if k in outer and k not in cfg:
+                cfg[k] = outer[k]
+    d = _mistral(cfg, mt)
+    rp = cfg.get("rope_parameters") if isinstance(cfg.get("rope_parameters"), dict) else (cfg.get("rope_scaling") or {})
+    beta = rp.get("llama_4_scaling_beta")
+    if beta:
+        d["extra"] = {"q_pos_scale": {"beta": float(beta),
+                                      "window": int(rp.get("original_max_position_embeddings")
+                                                    or cfg.get("max_position_embeddings") or 1)}}
     return d
 
 
@@ -473,9 +500,13 @@ def _deepseek_v2(cfg, mt):
     d["num_key_value_heads"] = d["num_attention_heads"]
     d["partial_rotary_factor"] = rope / (nope + rope)
     scaling = d.get("rope_scaling")
-    if isinstance(scaling, dict) and scaling.get("rope_type", scaling.get("type", "default")) not in ("default", "linear"):
-        raise ValueError("DeepSeek-V2 rotary scaling other than linear is not supported")
+    kind = scaling.get("rope_type", scaling.get("type", "default")) if isinstance(scaling, dict) else "default"
+    if kind not in ("default", "linear", "yarn"):
+        raise ValueError(f"DeepSeek-V2 rotary scaling {kind!r} is not supported")
     extra = _deepseek_moe_fields(cfg, d)
+    if kind == "yarn" and scaling.get("mscale_all_dim"):
+        factor = float(scaling["factor"])
+        extra["softmax_mscale"] = 1.0 if factor <= 1 else 0.1 * float(scaling["mscale_all_dim"]) * math.log(factor) + 1.0
     extra["mla"] = {"q_lora_rank": _get(cfg, "q_lora_rank"), "kv_lora_rank": int(_get(cfg, "kv_lora_rank", default=512)),
                     "qk_nope_head_dim": nope, "qk_rope_head_dim": rope,
                     "v_head_dim": int(_get(cfg, "v_head_dim", default=128))}
@@ -654,7 +685,7 @@ def _phi3v(cfg, mt):
 
 _PARSERS = {
     "phi3_v": _phi3v, "phi3v": _phi3v, "qwen2_5_vl": _qwen2_5_vl, "qwen2_5_vl_text": _qwen2_5_vl, "qwen3_5": _qwen35, "qwen3_5_text": _qwen35, "qwen35": _qwen35,
-    "llama": _llama, "mistral": _mistral, "ministral3": _mistral, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
+    "llama": _llama, "mistral": _mistral, "ministral3": _ministral3, "qwen": _qwen, "qwen2": _qwen2, "qwen3": _qwen3,
     "gemma": _gemma, "gemma2": _gemma, "gemma3": _gemma, "gemma3_text": _gemma,
     "phi3": _phi3, "phi": _phi, "phi-msft": _phi, "gpt_neox": _gpt_neox, "gpt2": _gpt2, "gptj": _gptj,
     "gpt_j": _gptj, "glm": _glm, "chatglm": _glm, "rwkv5": _rwkv5, "rwkv6": _rwkv5,

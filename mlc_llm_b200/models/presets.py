@@ -166,3 +166,21 @@ MODEL_PRESETS = {
         "shared_expert_intermediate_size": 5632, "max_position_embeddings": 8192,
     },
 }
+
+
+def _public_presets() -> dict:
+    """Architecture hyper-parameters of published checkpoints under the names the reference's
+    ``gen_config`` accepts (``python/mlc_llm/model/model_preset.py``: ``llama2_7b``, ``mistral_7b``,
+    ``phi-3_5`` ...), kept as a data file next to this module."""
+    import json  # pylint: disable=import-outside-toplevel
+    import os  # pylint: disable=import-outside-toplevel
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "public_presets.json")
+    if not os.path.isfile(path):
+        return {}
+    with open(path, encoding="utf-8") as f:
+        return json.load(f)
+
+
+for _name, _cfg in _public_presets().items():
+    MODEL_PRESETS.setdefault(_name, _cfg)

@@ -82,12 +82,17 @@ class DecoderModel:
                          else self.d ** -0.5)
         self.inv_freq = None
         self.inv_freq_local = None
+        self.rope_attn_factor = 1.0
         if config.position_embedding == "rope":
             self.inv_freq = ops.reference.rope_inv_freq(config.rotary_dim, config.rope_theta,
                                                         config.rope_scaling).to(device)
             if config.rope_local_theta > 0:
                 self.inv_freq_local = ops.reference.rope_inv_freq(
                     config.rotary_dim, config.rope_local_theta, None).to(device)
+            self.rope_attn_factor = ops.reference.rope_attention_factor(config.rope_scaling)
+            if config.extra.get("softmax_mscale"):
+                # YaRN checkpoints trained with `mscale_all_dim` fold its square into the softmax scale
+                self.sm_scale *= float(config.extra["softmax_mscale"]) ** 2
 
     # ------------------------------------------------------------------ KV cache
     def create_kv_cache(self, num_pages: int, page_size: int = 16) -> None:
@@ -243,7 +248,14 @@ class DecoderModel:
                     kvstart = (torch.div(b.q_kvlen - 1, chunk, rounding_mode="floor") * chunk).to(torch.int32)
         else:
             ops.rope_append(qkv, self.kv_pages[local], b.positions, b.slots, inv, hq, hkv, d,
-                            c.rotary_dim if inv is not None else 0, self.page)
+                            c.rotary_dim if inv is not None else 0, self.page,
+                            1.0 if inv is self.inv_freq_local else self.rope_attn_factor)
+            qs = c.extra.get("q_pos_scale")
+            if qs:  # queries grow with the logarithm of how many trained windows the position lies beyond
+                t = qkv.shape[0]
+                scale = 1.0 + qs["beta"] * torch.log1p(torch.floor(b.positions.float() / qs["window"]))
+                q = qkv.view(t, hq + 2 * hkv, d)[:, :hq]
+                q.copy_((q.float() * scale.view(t, 1, 1)).to(qkv.dtype))
         if sliding:
             w = int(c.extra.get("layer_sliding_window", 4096))
             kvstart = torch.clamp(b.q_kvlen - w, min=0).to(torch.int32)

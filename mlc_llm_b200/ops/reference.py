@@ -80,7 +80,64 @@ def rope_inv_freq(rot_dim: int, theta: float, scaling: Optional[dict] = None) ->
         inv = scaled
     elif scaling and scaling.get("rope_type", scaling.get("type")) == "linear":
         inv = inv / float(scaling["factor"])
+    elif scaling and scaling.get("rope_type", scaling.get("type")) == "yarn":
+        # YaRN: bands that turn more than beta_fast times inside the original window keep their frequency,
+        # bands that turn less than beta_slow times are slowed by `factor`, a linear ramp in between
+        factor = float(scaling["factor"])
+        orig = float(scaling.get("original_max_position_embeddings") or 0) or 4096.0
+        fast, slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+        def band_of(turns: float) -> float:
+            return rot_dim * math.log(orig / (turns * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = band_of(fast), band_of(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, rot_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rot_dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        inv = (inv / factor) * ramp + inv * (1 - ramp)
+    elif scaling and scaling.get("rope_type", scaling.get("type")) in ("longrope", "su"):
+        # per-band divisors: the long set once the context exceeds the window the model was trained on
+        orig = int(scaling.get("original_max_position_embeddings") or 0)
+        cur = int(scaling.get("max_position_embeddings") or 0)
+        ext = scaling["long_factor"] if (orig and cur > orig) else scaling["short_factor"]
+        inv = inv / torch.tensor(ext, dtype=torch.float64)
+    elif scaling and scaling.get("rope_type", scaling.get("type", "default")) not in ("default", "mrope", None):
+        import logging  # pylint: disable=import-outside-toplevel
+
+        logging.getLogger(__name__).warning("rotary scaling %r is not implemented; plain frequencies are used",
+                                            scaling.get("rope_type", scaling.get("type")))
     return inv.to(torch.float32)
+
+
+def _yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    return 1.0 if factor <= 1 else 0.1 * mscale * math.log(factor) + 1.0
+
+
+def rope_attention_factor(scaling: Optional[dict]) -> float:
+    """Scale applied to cos / sin (hence to q and k) by the rotary variants that stretch the context:
+    YaRN ``0.1 ln(factor) + 1`` (or the ratio of its two ``mscale`` forms), LongRoPE
+    ``sqrt(1 + ln(scale) / ln(original window))``; 1 otherwise."""
+    if not scaling:
+        return 1.0
+    kind = scaling.get("rope_type", scaling.get("type"))
+    if scaling.get("attention_factor") is not None and kind in ("yarn", "longrope", "su"):
+        return float(scaling["attention_factor"])
+    if kind == "yarn":
+        factor = float(scaling["factor"])
+        ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+        if ms and ms_all:
+            return _yarn_mscale(factor, float(ms)) / _yarn_mscale(factor, float(ms_all))
+        return _yarn_mscale(factor)
+    if kind in ("longrope", "su"):
+        orig = int(scaling.get("original_max_position_embeddings") or 0)
+        cur = int(scaling.get("max_position_embeddings") or 0)
+        if not orig or cur <= orig:
+            return 1.0
+        return math.sqrt(1.0 + math.log(cur / orig) / math.log(orig))
+    return 1.0
 
 
 def rope_append(qkv: torch.Tensor, kv_pages: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor,

@@ -58,6 +58,25 @@ CASES = {
     "olmo2": ("Olmo2Config", dict(BASE)),
     "cohere": ("CohereConfig", dict(BASE)),
     "phi": ("PhiConfig", dict(BASE, num_key_value_heads=4)),
+    # stretched-context rotary variants: YaRN (band-wise slow-down + cos/sin scale), LongRoPE (per-band
+    # divisors, long set because the served window exceeds the trained one), YaRN with DeepSeek's softmax scale
+    "llama_yarn": ("LlamaConfig", dict(BASE, rope_parameters={
+        "rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 16, "rope_theta": 10000.0,
+        "beta_fast": 32.0, "beta_slow": 1.0})),
+    "phi3_longrope": ("Phi3Config", dict(BASE, pad_token_id=0, original_max_position_embeddings=16, rope_parameters={
+        "rope_type": "longrope", "rope_theta": 10000.0, "short_factor": [1.0 + 0.05 * i for i in range(8)],
+        "long_factor": [1.5 + 0.25 * i for i in range(8)]})),
+    "ministral3": ("Ministral3Config", dict(BASE, head_dim=16, sliding_window=None, rope_parameters={
+        "rope_type": "yarn", "factor": 16.0, "original_max_position_embeddings": 8, "rope_theta": 10000.0,
+        "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0, "llama_4_scaling_beta": 0.1})),
+    "deepseek_v2_yarn": ("DeepseekV2Config", dict(
+        hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+        vocab_size=160, max_position_embeddings=128, q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16,
+        qk_rope_head_dim=16, v_head_dim=16, head_dim=16, n_routed_experts=4, n_shared_experts=1, num_experts_per_tok=2,
+        moe_intermediate_size=24, first_k_dense_replace=1, topk_method="greedy", n_group=1, topk_group=1,
+        routed_scaling_factor=1.0, norm_topk_prob=False, rope_parameters={
+            "rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 16, "rope_theta": 10000.0,
+            "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 0.707, "mscale_all_dim": 0.707})),
 }
 
 

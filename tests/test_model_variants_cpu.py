@@ -181,3 +181,29 @@ def test_gen_config_keeps_what_the_family_parser_needs(preset, tmp_path):
     assert again.extra == first.extra
     a, b = again.asdict(), first.asdict()
     assert a == b, {k: (a[k], b[k]) for k in a if a[k] != b[k]}
+
+
+def test_public_presets_parse_to_their_published_sizes():
+    """Every named preset of a published checkpoint parses; parameter counts of a few well-known ones."""
+    import math as _math
+
+    from mlc_llm_b200.models.presets import MODEL_PRESETS
+    from mlc_llm_b200.models.transformer import param_specs
+
+    def billions(name):
+        d = MODEL_PRESETS[name]
+        cfg = mc.from_dict(d["model_type"], d)
+        return sum(_math.prod(shape) for shape, _ in param_specs(cfg).values()) / 1e9
+
+    assert abs(billions("llama2_7b") - 6.74) < 0.01
+    assert abs(billions("llama3_1_8b") - 8.03) < 0.01
+    assert abs(billions("mistral_7b") - 7.24) < 0.01
+    assert abs(billions("Mixtral-8x7B-v0.1") - 46.7) < 0.05
+    assert abs(billions("qwen2_7b") - 7.62) < 0.01
+    assert abs(billions("deepseek_v2_lite") - 15.7) < 0.2
+    assert 3.0 < billions("ministral3_3b_2512") < 4.0
+    for name, d in MODEL_PRESETS.items():
+        if d.get("model_type") == "bert":
+            continue  # the embedding encoder has its own configuration class
+        cfg = mc.from_dict(d["model_type"], d)
+        assert cfg.hidden_size > 0 and cfg.num_hidden_layers >= 0, name
