@@ -44,6 +44,19 @@ class LogProbs(BaseModel):
     content: List[LogProbsContent]
 
 
+class CompletionLogProbs(BaseModel):
+    """Log-probabilities in the layout of the legacy completions API (``logprobs=<int>``): parallel lists
+    over the generated tokens (reference: ``protocol/openai_api_protocol.py:47-53``)."""
+
+    text_offset: Optional[List[int]] = None  # offset of each token in the completion text
+    token_logprobs: List[float]
+    tokens: List[str]
+    top_logprobs: List[Dict[str, float]]
+
+
+COMPLETION_MAX_TOP_LOGPROBS = 5
+
+
 class CompletionUsage(BaseModel):
     prompt_tokens: int = 0
     completion_tokens: int = 0
@@ -129,8 +142,11 @@ class CompletionRequest(BaseModel):
     echo: bool = False
     frequency_penalty: Optional[float] = None
     presence_penalty: Optional[float] = None
-    logprobs: bool = False
+    # an integer asks for that many alternatives per token in the legacy layout (``CompletionLogProbs``);
+    # ``true`` with ``top_logprobs`` gives the chat layout
+    logprobs: Union[bool, int, None] = None
     top_logprobs: int = 0
+    legacy_logprobs: bool = Field(default=False, exclude=True)
     logit_bias: Optional[Dict[int, float]] = None
     max_tokens: Optional[int] = None
     n: int = 1
@@ -158,6 +174,14 @@ class CompletionRequest(BaseModel):
 
     @model_validator(mode="after")
     def _consistency(self):
+        if self.logprobs is not None and not isinstance(self.logprobs, bool):
+            if self.logprobs < 0 or self.logprobs > COMPLETION_MAX_TOP_LOGPROBS:
+                raise ValueError(f'"logprobs" must be in range [0, {COMPLETION_MAX_TOP_LOGPROBS}]')
+            object.__setattr__(self, "top_logprobs", int(self.logprobs))
+            object.__setattr__(self, "legacy_logprobs", True)
+            object.__setattr__(self, "logprobs", True)
+        elif self.logprobs is None:
+            object.__setattr__(self, "logprobs", False)
         if self.top_logprobs < 0 or self.top_logprobs > 20:
             raise ValueError('"top_logprobs" must be in [0, 20]')
         if not self.logprobs and self.top_logprobs > 0:
@@ -170,7 +194,7 @@ class CompletionRequest(BaseModel):
 class CompletionResponseChoice(BaseModel):
     finish_reason: Optional[Literal["stop", "length", "preempt"]] = None
     index: int = 0
-    logprobs: Optional[LogProbs] = None
+    logprobs: Optional[Union[CompletionLogProbs, LogProbs]] = None
     text: str
 
 

@@ -342,7 +342,7 @@ class AsyncMLCEngine(MLCEngineBase):
             yield openai.CompletionResponse(id=request_id, model=self.model, choices=[
                 openai.CompletionResponseChoice(index=i, text=echo) for i in range(request.n)])
         async for items in self._generate(inputs, gen, request_id):
-            for c in _completion_stream_chunk(items, request_id, self.model, include_usage):
+            for c in _completion_stream_chunk(items, request_id, self.model, include_usage, request.legacy_logprobs):
                 yield c
 
     async def _gather_chat(self, request, request_id) -> openai.ChatCompletionResponse:
@@ -359,7 +359,7 @@ class AsyncMLCEngine(MLCEngineBase):
         acc = _Accumulator(request.n, echo)
         async for items in self._generate(inputs, gen, request_id, accumulate=True):
             acc.add(items)
-        return acc.completion_response(request_id, self.model)
+        return acc.completion_response(request_id, self.model, request.legacy_logprobs)
 
 
 # ====================================================================== sync engine
@@ -488,7 +488,7 @@ class MLCEngine(MLCEngineBase):
         acc = _Accumulator(request.n, echo)
         for items in self._generate(inputs, gen, rid, accumulate=True):
             acc.add(items)
-        return acc.completion_response(rid, self.model)
+        return acc.completion_response(rid, self.model, request.legacy_logprobs)
 
     def _handle_chat_completion(self, request, request_id) -> Iterator[openai.ChatCompletionStreamResponse]:
         inputs, gen, use_fn, _ = engine_base.process_chat_completion_request(
@@ -505,7 +505,7 @@ class MLCEngine(MLCEngineBase):
             yield openai.CompletionResponse(id=request_id, model=self.model, choices=[
                 openai.CompletionResponseChoice(index=i, text=echo) for i in range(request.n)])
         for items in self._generate(inputs, gen, request_id):
-            yield from _completion_stream_chunk(items, request_id, self.model, include_usage)
+            yield from _completion_stream_chunk(items, request_id, self.model, include_usage, request.legacy_logprobs)
 
 
 # ====================================================================== response assembly
@@ -531,7 +531,8 @@ def _chat_stream_chunk(items, request_id, model, use_fn, include_usage):
     return out
 
 
-def _completion_stream_chunk(items, request_id, model, include_usage):
+def _completion_stream_chunk(items, request_id, model, include_usage, legacy_logprobs=False):
+    parse = engine_base.parse_completion_logprobs if legacy_logprobs else engine_base.parse_logprobs
     choices, out = [], []
     usage_json = None
     for it in items:
@@ -540,7 +541,7 @@ def _completion_stream_chunk(items, request_id, model, include_usage):
             continue
         fr = it.finish_reason if it.finish_reason in (None, "stop", "length", "preempt") else "stop"
         choices.append(openai.CompletionResponseChoice(index=it.index, finish_reason=fr, text=it.delta_text,
-                                                       logprobs=engine_base.parse_logprobs(it.delta_logprob_json_strs)))
+                                                       logprobs=parse(it.delta_logprob_json_strs)))
     if choices:
         out.append(openai.CompletionResponse(id=request_id, choices=choices, model=model))
     if usage_json is not None and include_usage:
@@ -588,7 +589,8 @@ class _Accumulator:
         return openai.ChatCompletionResponse(id=request_id, choices=choices, model=model,
                                              usage=engine_base.parse_usage(self.usage_json))
 
-    def completion_response(self, request_id, model) -> openai.CompletionResponse:
+    def completion_response(self, request_id, model, legacy_logprobs=False) -> openai.CompletionResponse:
+        parse = engine_base.parse_completion_logprobs if legacy_logprobs else engine_base.parse_logprobs
         choices = []
         for i, t in enumerate(self.texts):
             if self.finish[i] == "error":
@@ -600,6 +602,6 @@ class _Accumulator:
             fr = self.finish[i] if self.finish[i] in (None, "stop", "length", "preempt") else "stop"
             choices.append(openai.CompletionResponseChoice(
                 index=i, finish_reason=fr, text="".join(t),
-                logprobs=engine_base.parse_logprobs(self.logprobs[i])))
+                logprobs=parse(self.logprobs[i])))
         return openai.CompletionResponse(id=request_id, choices=choices, model=model,
                                          usage=engine_base.parse_usage(self.usage_json))

@@ -523,6 +523,23 @@ def parse_logprobs(json_strs: Sequence[str]) -> Optional[openai.LogProbs]:
     return openai.LogProbs(content=content)
 
 
+def parse_completion_logprobs(json_strs: Sequence[str]) -> Optional[openai.CompletionLogProbs]:
+    """The same per-token records in the legacy completions layout: parallel lists of token strings, their
+    log-probabilities, a ``{token: logprob}`` dict of alternatives and the offset of every token in the text."""
+    if not json_strs:
+        return None
+    tokens, lps, tops, offsets = [], [], [], []
+    at = 0
+    for s in json_strs:
+        d = json.loads(s)
+        tokens.append(d["token"])
+        lps.append(d["logprob"])
+        tops.append({t["token"]: t["logprob"] for t in d.get("top_logprobs", [])})
+        offsets.append(at)
+        at += len(d["token"])
+    return openai.CompletionLogProbs(text_offset=offsets, token_logprobs=lps, tokens=tokens, top_logprobs=tops)
+
+
 def parse_usage(usage_json: Optional[str], include_extra: bool = True) -> Optional[openai.CompletionUsage]:
     if not usage_json:
         return None

@@ -100,6 +100,15 @@ def test_stop_conditions_and_logprobs():
         assert ch.finish_reason == "length" and base.usage.completion_tokens == 10
         lp = ch.logprobs.content
         assert len(lp) == 10 and all(len(x.top_logprobs) == 3 for x in lp)
+        # the legacy completions layout: ``logprobs=<number of alternatives>`` gives parallel lists
+        legacy = eng.completions.create(prompt=prompt, max_tokens=10, temperature=0.0,
+                                        debug_config={"ignore_eos": True}, logprobs=2).choices[0]
+        assert legacy.text == ch.text
+        ll = legacy.logprobs
+        assert ll.tokens == [x.token for x in lp] and len(ll.token_logprobs) == 10
+        assert all(abs(a - x.logprob) < 1e-5 for a, x in zip(ll.token_logprobs, lp))
+        assert all(len(t) <= 2 and tok in t for t, tok in zip(ll.top_logprobs, ll.tokens))  # greedy: the token is top-1
+        assert ll.text_offset[0] == 0 and ll.text_offset[1] == len(ll.tokens[0])
         assert all(x.logprob <= 0 and abs(x.logprob - x.top_logprobs[0].logprob) < 1e-4 for x in lp)  # greedy = top-1
         # stop string: generation ends before the text that contains it, finish_reason "stop"
         text = ch.text

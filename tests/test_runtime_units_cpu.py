@@ -295,6 +295,13 @@ def test_conversation_templates_python_and_native_agree():
 def test_openai_protocol_validation():
     req = openai.ChatCompletionRequest(messages=[{"role": "user", "content": "x"}], logprobs=True, top_logprobs=3)
     assert req.top_logprobs == 3
+    legacy = openai.CompletionRequest(prompt="x", logprobs=4)       # legacy completions form: a count
+    assert legacy.logprobs is True and legacy.top_logprobs == 4 and legacy.legacy_logprobs
+    plain = openai.CompletionRequest(prompt="x")
+    assert plain.logprobs is False and not plain.legacy_logprobs
+    assert openai.CompletionRequest(prompt="x", logprobs=True, top_logprobs=2).legacy_logprobs is False
+    with pytest.raises(ValueError):
+        openai.CompletionRequest(prompt="x", logprobs=6)             # at most five alternatives
     with pytest.raises(Exception):
         openai.ChatCompletionRequest(messages=[{"role": "user", "content": "x"}], top_logprobs=3)  # needs logprobs
     with pytest.raises(Exception):
