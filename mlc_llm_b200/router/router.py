@@ -95,6 +95,10 @@ class Router:  # pylint: disable=too-many-instance-attributes
         self.servers = []
 
     # ------------------------------------------------------------------ dispatch
+    def translate_request(self, request: openai.CompletionRequest, request_id: str):
+        """The reference's name for ``handle_completion`` (``router/router.py:134``)."""
+        return self.handle_completion(request, request_id)
+
     async def handle_completion(self, request: openai.CompletionRequest, request_id: str
                                 ) -> AsyncGenerator[Optional[openai.CompletionResponse], Any]:
         if isinstance(request.prompt, str):

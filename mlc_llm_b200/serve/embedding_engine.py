@@ -100,11 +100,18 @@ class AsyncEmbeddingEngine:
                 sep_id if sep_id is not None and sep_id >= 0 else None)
 
     # ------------------------------------------------------------------ public API
-    async def embed(self, inputs: Sequence[Union[str, List[int]]]) -> Tuple[List[List[float]], int]:
+    async def async_embed(self, inputs: Sequence[Union[str, List[int]]]) -> Tuple[List[List[float]], int]:
+        """``embed`` on the engine's worker thread, so the event loop stays free
+        (reference: ``serve/embedding_engine.py:184``)."""
         loop = asyncio.get_running_loop()
-        return await loop.run_in_executor(self._executor, self.embed_sync, list(inputs))
+        return await loop.run_in_executor(self._executor, self.embed, list(inputs))
 
     def embed_sync(self, inputs: Sequence[Union[str, List[int]]]) -> Tuple[List[List[float]], int]:
+        return self.embed(inputs)
+
+    def embed(self, inputs: Sequence[Union[str, List[int]]]) -> Tuple[List[List[float]], int]:
+        """Embedding vectors (L2-normalised unless configured otherwise) and the number of input tokens;
+        synchronous (reference: ``serve/embedding_engine.py:165``)."""
         ids = [list(x) if not isinstance(x, str) else self.tokenizer.encode(x) for x in inputs]
         if self.model_type == "encoder":
             vecs = self._embed_encoder(ids)

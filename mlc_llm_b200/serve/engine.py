@@ -263,6 +263,17 @@ class _Namespace:
     pass
 
 
+class Chat(_Namespace):
+    """``engine.chat``: holds ``completions`` (reference: ``serve/engine.py`` ``Chat``)."""
+
+    def __init__(self, completions=None):
+        self.completions = completions
+
+
+class AsyncChat(Chat):
+    """``async_engine.chat`` (reference: ``serve/engine.py`` ``AsyncChat``)."""
+
+
 class AsyncMLCEngine(MLCEngineBase):
     """Asynchronous engine: many concurrent requests from one asyncio loop."""
 
@@ -272,8 +283,7 @@ class AsyncMLCEngine(MLCEngineBase):
                  runtime: Optional[EngineRuntime] = None):
         super().__init__("async", model, device, model_lib=model_lib, mode=mode, engine_config=engine_config,
                          enable_tracing=enable_tracing, comm=comm, runtime=runtime)
-        self.chat = _Namespace()
-        self.chat.completions = AsyncChatCompletion(self)
+        self.chat = AsyncChat(AsyncChatCompletion(self))
         self.completions = AsyncCompletion(self)
 
     async def abort(self, request_id: str) -> None:
@@ -392,8 +402,7 @@ class MLCEngine(MLCEngineBase):
                  runtime: Optional[EngineRuntime] = None):
         super().__init__("sync", model, device, model_lib=model_lib, mode=mode, engine_config=engine_config,
                          enable_tracing=enable_tracing, comm=comm, runtime=runtime)
-        self.chat = _Namespace()
-        self.chat.completions = ChatCompletion(self)
+        self.chat = Chat(ChatCompletion(self))
         self.completions = Completion(self)
 
     def abort(self, request_id: str) -> None:

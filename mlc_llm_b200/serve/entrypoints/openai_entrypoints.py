@@ -124,7 +124,7 @@ async def request_embeddings(request: openai.EmbeddingRequest):
         inputs = [inputs]
     elif inputs and isinstance(inputs[0], int):
         inputs = [inputs]
-    vectors, num_tokens = await engine.embed(list(inputs))
+    vectors, num_tokens = await engine.async_embed(list(inputs))
     if request.dimensions is not None:
         vectors = [engine.truncate(v, request.dimensions) for v in vectors]
     data = []

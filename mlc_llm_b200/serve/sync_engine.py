@@ -48,14 +48,60 @@ class SyncMLCEngine:
 
     def _on_outputs(self, outs: List[dict]) -> None:
         if self._user_callback is not None:
-            self._user_callback([RequestStreamOutput(o) for o in outs])
+            items = []
+            for o in outs:
+                o = o if isinstance(o, dict) else o.asdict()
+                has_delta = any(o["group_delta_token_ids"]) or any(r is not None for r in o["group_finish_reason"])
+                if o["request_final_usage_json_str"] is not None and has_delta:
+                    # callers of the callback API expect the usage record in an item of its own, after the
+                    # item with the last tokens
+                    items.append(RequestStreamOutput(dict(o, request_final_usage_json_str=None)))
+                    items.append(RequestStreamOutput(dict(o, group_delta_token_ids=[], group_delta_logprob_json_strs=[],
+                                                          group_finish_reason=[], group_extra_prefix_string=[])))
+                else:
+                    items.append(RequestStreamOutput(o))
+            self._user_callback(items)
         else:
             self._outputs.extend(outs)
 
     # ------------------------------------------------------------------ low-level API
-    def add_request(self, request_id: str, inputs: Sequence[Any], generation_config: Dict[str, Any]) -> None:
-        native = [np.asarray(x, dtype=np.int32) if not isinstance(x, tuple) else x for x in inputs]
-        self._engine.add_request(request_id, native, json.dumps(generation_config))
+    def create_request(self, request_id: str, inputs, generation_config):
+        """A ``Request`` for ``add_request`` (reference: ``serve/sync_engine.py:293``); ``inputs`` is one
+        ``Data`` item or a list of them."""
+        from .request import Request  # pylint: disable=import-outside-toplevel
+
+        return Request(request_id, inputs if isinstance(inputs, (list, tuple)) else [inputs], generation_config)
+
+    def _native_inputs(self, inputs: Sequence[Any]) -> List[Any]:
+        out = []
+        for x in inputs:
+            if isinstance(x, tuple):
+                out.append(x)
+            elif isinstance(x, str) or hasattr(x, "text"):
+                out.append(np.asarray(self.tokenizer.encode(x if isinstance(x, str) else x.text), dtype=np.int32))
+            elif hasattr(x, "token_ids"):
+                out.append(np.asarray(x.token_ids, dtype=np.int32))
+            elif hasattr(x, "embed_size"):  # ImageData -> embedding rows held by the executor
+                model = self.runtime.models[0]
+                if not hasattr(model, "image_embed"):
+                    raise ValueError("this model does not take image inputs")
+                emb = model.image_embed(x.image)
+                out.append(("embed", self.runtime.executor.hold_embedding(emb), int(emb.shape[0])))
+            else:
+                out.append(np.asarray(x, dtype=np.int32))
+        return out
+
+    def add_request(self, request_id, inputs: Optional[Sequence[Any]] = None,
+                    generation_config: Optional[Dict[str, Any]] = None) -> None:
+        """``add_request(request)`` with a ``Request`` from ``create_request``, or
+        ``add_request(request_id, inputs, generation_config)``."""
+        if inputs is None and hasattr(request_id, "inputs"):
+            request_id, inputs, generation_config = (request_id.request_id, request_id.inputs,
+                                                     request_id.generation_config)
+        cfg = generation_config or {}
+        if not isinstance(cfg, dict):
+            cfg = cfg.model_dump(exclude_none=True) if hasattr(cfg, "model_dump") else dict(vars(cfg))
+        self._engine.add_request(request_id, self._native_inputs(inputs), json.dumps(cfg))
 
     def abort_request(self, request_id: str) -> None:
         self._engine.abort_request(request_id)

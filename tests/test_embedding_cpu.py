@@ -33,7 +33,7 @@ def test_bert_embeddings_match_transformers(bert_dir):
     path, hf, tok = bert_dir
     eng = AsyncEmbeddingEngine(path, device="cpu")
     texts = ["hello world", "fast gpus", "a b c d e f"]
-    vecs, ntok = asyncio.run(eng.embed(texts))
+    vecs, ntok = asyncio.run(eng.async_embed(texts))
     assert eng.model_type == "encoder" and eng.pooling_strategy == "cls" and len(vecs) == 3
     for text, v in zip(texts, vecs):
         ids = [2] + tok.encode(text).ids + [3]

@@ -393,3 +393,28 @@ def test_generate_many_gathers_outputs_natively():
         assert eng.generate_many([], cfg) == []
     finally:
         eng.terminate()
+
+
+def test_request_objects_drive_the_step_loop(reference_outputs):
+    """``create_request`` / ``add_request(request)`` / ``step`` with a stream callback that unpacks the
+    outputs, as a caller of the low-level synchronous engine does."""
+    from mlc_llm_b200.serve import data
+
+    prompts, want = reference_outputs
+    got = {}
+
+    def on_outputs(outs):
+        for out in outs:
+            rid, singles = out.unpack()
+            if singles[0].request_final_usage_json_str is None:
+                got.setdefault(rid, []).extend(singles[0].delta_token_ids)
+
+    cfg = EngineConfig(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64,
+                       prefix_cache_mode="disable")
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=cfg, request_stream_callback=on_outputs)
+    for i in range(2):
+        req = eng.create_request(f"r{i}", data.TokenData(prompts[i]), dict(GREEDY, max_tokens=12))
+        eng.add_request(req)
+    while not eng.empty():
+        eng.step()
+    assert [got["r0"], got["r1"]] == want[:2]

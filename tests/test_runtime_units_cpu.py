@@ -360,3 +360,36 @@ def test_tensor_cache_round_trip_and_md5(tmp_path):
     shard.write_bytes(bytes(data))
     with pytest.raises(ValueError):
         list(TensorCache(str(tmp_path), verify_md5=True))
+
+
+def test_reference_module_paths_and_stream_output_unpack():
+    """Names a user of the reference imports: module paths, request objects, stream-output unpacking."""
+    from mlc_llm_b200.serve import data
+    from mlc_llm_b200.serve.engine import AsyncChat, Chat  # noqa: F401
+    from mlc_llm_b200.serve.event_trace_recorder import EventTraceRecorder
+    from mlc_llm_b200.serve.radix_tree import PagedRadixTree
+    from mlc_llm_b200.serve.request import Request
+    from mlc_llm_b200.tokenizers.streamer import StopStrHandler, TextStreamer  # noqa: F401
+    from mlc_llm_b200.tokenizers.tokenizers import Tokenizer  # noqa: F401
+
+    tree = PagedRadixTree()
+    tree.add(0)
+    tree.extend(0, [1, 2, 3])
+    assert tree.match([1, 2, 9])[0] == 2 and tree.get_length(0) == 3
+    rec = EventTraceRecorder()
+    rec.add_event("r0", "start")
+    assert "r0" in rec.dump_json()
+    req = Request("r0", [data.TokenData([1, 2])], {"max_tokens": 2})
+    assert req.inputs[0].token_ids == [1, 2]
+    out = data.RequestStreamOutput({"request_id": "r0", "group_delta_token_ids": [[4], [5, 6]],
+                                    "group_delta_logprob_json_strs": [[], []], "group_finish_reason": [None, "stop"],
+                                    "group_extra_prefix_string": ["", "x"], "request_final_usage_json_str": None})
+    rid, singles = out.unpack()
+    assert rid == "r0" and [s.delta_token_ids for s in singles] == [[4], [5, 6]]
+    assert singles[1].finish_reason == "stop" and singles[1].extra_prefix_string == "x"
+    last = data.RequestStreamOutput({"request_id": "r0", "group_delta_token_ids": [], "group_delta_logprob_json_strs": [],
+                                     "group_finish_reason": [], "group_extra_prefix_string": [],
+                                     "request_final_usage_json_str": "{}"})
+    assert last.unpack()[1][0].request_final_usage_json_str == "{}"
+    cfg = {"model_config": {"vision_config": {"image_size": 336, "patch_size": 14}}}
+    assert data.ImageData.get_embed_size(cfg) == 576 and data.ImageData.get_input_size(cfg) == 336
