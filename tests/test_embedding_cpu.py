@@ -1,6 +1,7 @@
 """Embedding engine: BERT encoder against ``transformers``; decoder-style last-token pooling."""
 import asyncio
 
+import numpy as np
 import pytest
 import torch
 
@@ -62,3 +63,23 @@ def test_decoder_embeddings_last_token_pooling():
     assert torch.allclose(torch.tensor(a[1]), torch.tensor(b[0]), atol=1e-5)  # batching does not change a vector
     assert abs(sum(x * x for x in a[0]) - 1.0) < 1e-4
     eng.terminate()
+
+
+def test_contrib_embeddings_wrapper(bert_dir):
+    from mlc_llm_b200.contrib.embeddings import MLCEmbeddings
+
+    path, _, _ = bert_dir
+    emb = MLCEmbeddings(path, device="cpu", chunk_size=2)
+    try:
+        texts = ["hello world", "fast gpus", "a b c d e f"]
+        mat = emb.embed(texts)
+        assert mat.shape == (3, 64) and np.allclose(np.linalg.norm(mat, axis=1), 1.0, atol=1e-4)
+        direct, _ = emb.engine.embed(texts)
+        assert np.allclose(mat, np.asarray(direct), atol=1e-6)       # batching does not change the vectors
+        assert np.allclose(emb.embed_query("fast gpus"), mat[1], atol=1e-5)
+        assert len(emb.embed_documents(texts)) == 3
+        emb.dimensions = 16
+        small = emb.embed(texts)
+        assert small.shape == (3, 16) and np.allclose(np.linalg.norm(small, axis=1), 1.0, atol=1e-4)
+    finally:
+        emb.terminate()
