@@ -17,9 +17,11 @@ def main(argv=None):
                    choices=["auto", "huggingface-torch", "huggingface-safetensor", "awq"])
     p.add_argument("--output", "-o", type=str, required=True)
     p.add_argument("--lora-adapter", type=str, default=None)
+    p.add_argument("--preshard", type=int, default=0,
+                   help="write tensor-parallel parameters once per rank for this many ranks")
     a = p.parse_args(argv)
     convert_weight(a.config, a.quantization, a.model_type, a.device, a.source, a.source_format, a.output,
-                   a.lora_adapter)
+                   a.lora_adapter, preshard=a.preshard)
 
 
 if __name__ == "__main__":

@@ -20,7 +20,10 @@ from ..support.auto_config import detect_config, detect_device, detect_model_typ
 def convert_weight(config: str, quantization: str, model_type: str = "auto", device: str = "auto",
                    source: str = "auto", source_format: str = "auto", output: str = ".",
                    lora_adapter: Optional[str] = None, verbose: bool = True,
-                   encode_format: str = "f32-to-bf16") -> dict:
+                   encode_format: str = "f32-to-bf16", preshard: int = 0) -> dict:
+    """``preshard`` > 1 (or ``MLC_INTERNAL_PRESHARD_NUM``) writes every tensor-parallel parameter once per
+    rank, already cut and quantised, as ``<name>_shard-<rank>`` (reference: ``support/preshard.py:16-17``);
+    replicated parameters are written once. Ranks then read their own records without slicing."""
     config_path, hf = detect_config(config)
     mt = detect_model_type(model_type, hf)
     quant = Q.get(quantization)
@@ -34,12 +37,34 @@ def convert_weight(config: str, quantization: str, model_type: str = "auto", dev
         for name, t in huggingface_loader.iter_mlc_params(src_dir, cfg, lora_adapter):
             yield name, t.to(dev)
 
+    shards = int(preshard or os.environ.get("MLC_INTERNAL_PRESHARD_NUM", 0) or 0)
+
+    def exported():
+        if shards <= 1:
+            yield from export_params(cfg, quant, on_device())
+            return
+        from ..models.loader import _shard_dense  # pylint: disable=import-outside-toplevel
+        from ..models.transformer import param_specs  # pylint: disable=import-outside-toplevel
+
+        specs = param_specs(cfg)
+        ep = cfg.expert_parallel
+        for name, w in on_device():
+            kind = specs.get(name, (None, "norm"))[1]
+            cuts = [_shard_dense(name, w, kind, cfg, shards, r, ep) for r in range(shards)]
+            if all(c is w for c in cuts):
+                yield from export_params(cfg, quant, iter([(name, w)]))
+                continue
+            for r, cut in enumerate(cuts):
+                for out_name, t in export_params(cfg, quant, iter([(name, cut)])):
+                    yield f"{out_name}_shard-{r}", t
+
     def records():
-        for name, t in export_params(cfg, quant, on_device()):
+        for name, t in exported():
             t = t.cpu()
             stats["bytes"] += t.numel() * t.element_size()
-            if not (name.endswith("q_scale") or name.endswith("weight_scale_inv")):
-                per_word = 32 // quant.bits if name.endswith("q_weight") and quant.kind == "group-quant" else 1
+            plain = name.split("_shard-")[0]
+            if not (plain.endswith("q_scale") or plain.endswith("weight_scale_inv")):
+                per_word = 32 // quant.bits if plain.endswith("q_weight") and quant.kind == "group-quant" else 1
                 stats["params"] += t.numel() * per_word
             if verbose:
                 print(f"[convert_weight] {name} {tuple(t.shape)} {t.dtype}")

@@ -193,3 +193,35 @@ def test_delivery_runs_only_what_the_log_lacks(hf_dir, tmp_path):
     diff = delivery.generate_model_delivery_diff(delivery.ModelDeliveryList.from_json(spec),
                                                  delivery.get_current_log(str(log_path)))
     assert len(diff.tasks) == 2 and all(t.gen_config_only for t in diff.tasks)
+
+
+def test_presharded_convert_gives_each_rank_its_slices(hf_dir, tmp_path):
+    """``--preshard 2``: records ``<name>_shard-<rank>``; a rank loading them gets exactly what it would cut
+    out of the unsharded artifact."""
+    import torch as _torch
+
+    from mlc_llm_b200 import quantization as Q
+    from mlc_llm_b200.models import config as mcfg
+    from mlc_llm_b200.models import loader
+
+    src, _, _ = hf_dir
+    plain, pre = str(tmp_path / "plain"), str(tmp_path / "pre")
+    for out in (plain, pre):
+        cli_gen.main([src, "--quantization", "q4f16_1", "--conv-template", "LM", "--output", out])
+    cli_convert.main([src, "--quantization", "q4f16_1", "--output", plain, "--device", "cpu"])
+    cli_convert.main([src, "--quantization", "q4f16_1", "--output", pre, "--device", "cpu", "--preshard", "2"])
+    names = TensorCache(pre).names()
+    assert "model.layers.0.self_attn.qkv_proj.q_weight_shard-1" in names
+    assert "model.layers.0.input_layernorm.weight" in names        # replicated: written once
+    chat = json.load(open(os.path.join(pre, "mlc-chat-config.json")))
+    cfg = mcfg.from_dict(chat["model_type"], chat["model_config"])
+    quant = Q.get("q4f16_1")
+    for rank in (0, 1):
+        a = loader.load_params(plain, cfg, quant, _torch.device("cpu"), 2, rank)
+        b = loader.load_params(pre, cfg, quant, _torch.device("cpu"), 2, rank)
+        assert set(a.linears) == set(b.linears) and set(a.tensors) == set(b.tensors)
+        for k in a.linears:
+            assert _torch.equal(a.linears[k].w, b.linears[k].w), k
+            assert _torch.equal(a.linears[k].scale, b.linears[k].scale), k
+        for k in a.tensors:
+            assert _torch.equal(a.tensors[k], b.tensors[k]), k
