@@ -210,7 +210,8 @@ __global__ void page_copy_kernel(uint8_t* __restrict__ pages, const int* __restr
 __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
                                     const int* __restrict__ src_slots, const int* __restrict__ dst_slots,
                                     int n, int layers, size_t src_layer_stride, size_t dst_layer_stride, int hkv,
-                                    int page, int row_bytes) {
+                                    int page, int row_bytes, int src_slot_limit, int dst_slot_limit,
+                                    int* __restrict__ status) {
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = static_cast<long long>(n) * layers * 2 * hkv;
@@ -220,6 +221,11 @@ __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __
   const int l = static_cast<int>((warp / (2 * hkv)) % layers);
   const int i = static_cast<int>(warp / (static_cast<long long>(2) * hkv * layers));
   const int ss = src_slots[i], ds = dst_slots[i];
+  // a slot outside either pool is never dereferenced: the row is skipped and the host is told
+  if (ss < 0 || ss >= src_slot_limit || ds < 0 || ds >= dst_slot_limit) {
+    if (lane == 0 && status) atomicCAS(status, 0, static_cast<int>(ERR_BAD_INDEX));
+    return;
+  }
   const size_t head_bytes = static_cast<size_t>(page) * row_bytes;
   const size_t so = l * src_layer_stride + ((static_cast<size_t>(ss / page) * 2 + kv) * hkv + h) * head_bytes +
                     static_cast<size_t>(ss % page) * row_bytes;
@@ -324,17 +330,23 @@ MLCB_API int mlcb_enable_peer_access(int device, int peer) {
   return static_cast<int>(err);
 }
 
-// Strides in bytes; row_bytes = head_dim * element size (multiple of 16).
+// Strides in bytes; row_bytes = head_dim * element size (multiple of 16). Slots must lie in
+// [0, src_pages * page) and [0, dst_pages * page): the host checks before the launch and the kernel
+// skips (and reports ERR_BAD_INDEX for) any row that is not.
 MLCB_API int mlcb_kv_slot_copy(const void* src, void* dst, const int* src_slots, const int* dst_slots, int n,
                                int layers, long long src_layer_stride, long long dst_layer_stride, int hkv,
-                               int page, int row_bytes, cudaStream_t stream) {
+                               int page, int row_bytes, int src_pages, int dst_pages, int* status,
+                               cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (row_bytes % 16) return -1;
+  if (row_bytes % 16 || page <= 0 || src_pages <= 0 || dst_pages <= 0) return -1;
+  if (static_cast<long long>(src_pages) * page > 0x7fffffffLL || static_cast<long long>(dst_pages) * page > 0x7fffffffLL)
+    return -1;
   const long long warps = static_cast<long long>(n) * layers * 2 * hkv;
   const long long blocks = (warps + 7) / 8;
   kv_slot_copy_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), src_slots, dst_slots, n, layers,
-      static_cast<size_t>(src_layer_stride), static_cast<size_t>(dst_layer_stride), hkv, page, row_bytes);
+      static_cast<size_t>(src_layer_stride), static_cast<size_t>(dst_layer_stride), hkv, page, row_bytes,
+      src_pages * page, dst_pages * page, status);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -732,7 +732,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         // Every split reduces its own share of the tile's tokens once all partial sums are parked,
         // so the reduction runs on `splits` SMs at once. The counter's low half counts arrivals,
         // its high half counts finished reducers; the last reducer zeroes it for the next launch.
-        // (Each CTA owns at most one split item, so waiting here cannot starve a sibling.)
+        // Every launcher keeps tiles * splits <= CTAs in the grid whenever splits > 1, so each CTA owns at
+        // most one split item and all siblings of a tile are resident at once: waiting here cannot
+        // starve a sibling.
         __threadfence();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ep_bar[0]);
@@ -1448,14 +1450,17 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
                         "caller-provided scratch",
                         tiles, MLCB_NOALLOC_MAX_TILES);
   const int total_kb = (K + BK - 1) / BK;
-  // this entry point always runs the split-K form (that is the variant that needs scratch)
+  // Split K only while every (tile, split) item gets a CTA of its own (tiles * splits <= SMs): the
+  // kernel's reducer waits for its sibling splits, which is only starvation-free when all of them
+  // are resident at once. Problems with more than SMs / 2 tiles, or a single K block, run unsplit
+  // and touch no scratch at all.
   int splits = sm_count() / static_cast<int>(tiles);
   if (splits > 8) splits = 8;
   if (splits > total_kb) splits = total_kb;
-  if (splits < 2) splits = total_kb >= 2 ? 2 : 1;
+  if (splits < 1) splits = 1;
   p.kb_per_split = (total_kb + splits - 1) / splits;
   p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
-  const long long need = tiles * p.splits * p.tn * BM * 4;
+  const long long need = p.splits > 1 ? tiles * p.splits * p.tn * BM * 4 : 0;
   if (need > static_cast<long long>(MLCB_NOALLOC_SCRATCH_BYTES))
     return noalloc_fail(MLCB_NOALLOC_TOO_LARGE,
                         "mlcb_gemm_noalloc: split-K scratch of %lld bytes exceeds the built-in %lld bytes "

@@ -99,7 +99,7 @@ def dump_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str,
         fmt = "raw"
         dt = dtype_name(t, logical_dtypes.get(name))
         if t.dtype == torch.float32 and encode_format == "f32-to-bf16":
-            raw = (t.detach().cpu().contiguous().numpy().view(np.uint32) >> 16).astype(np.uint16).tobytes()
+            raw = _f32_to_bf16_bytes(t)
             fmt = "f32-to-bf16"
         else:
             raw = _to_bytes(t)
@@ -120,6 +120,18 @@ def dump_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str,
     return doc
 
 
+def _f32_to_bf16_bytes(t: torch.Tensor) -> bytes:
+    """fp32 -> bf16 bit patterns with round-to-nearest-even, as the tvmjs writer of the reference's
+    artifacts does for finite values; Inf / NaN keep their upper half (adding the rounding bias to
+    them could carry into the sign / exponent)."""
+    u = t.detach().cpu().contiguous().numpy().view(np.uint32)
+    finite = (u & np.uint32(0x7F800000)) != np.uint32(0x7F800000)
+    bias = ((u >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF)
+    rounded = (u.astype(np.uint64) + bias.astype(np.uint64)) >> np.uint64(16)
+    out = np.where(finite, rounded, (u >> np.uint32(16)).astype(np.uint64))
+    return out.astype(np.uint16).tobytes()
+
+
 def update_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str,
                         encode_format: str = "f32-to-bf16") -> Dict:
     """Add (or replace) tensors in the tensor cache under ``out_dir`` without rewriting its existing
@@ -137,7 +149,7 @@ def update_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str
     for name, t in items:
         fmt = "raw"
         if t.dtype == torch.float32 and encode_format == "f32-to-bf16":
-            raw = (t.detach().cpu().contiguous().numpy().view(np.uint32) >> 16).astype(np.uint16).tobytes()
+            raw = _f32_to_bf16_bytes(t)
             fmt = "f32-to-bf16"
         else:
             raw = _to_bytes(t)
@@ -155,6 +167,11 @@ def update_tensor_cache(params: Iterator[Tuple[str, torch.Tensor]], out_dir: str
         f.write(buf)
     doc["records"].append({"dataPath": path, "format": "raw-shard", "nbytes": len(buf), "records": records,
                            "md5sum": hashlib.md5(buf).hexdigest()})
+    # the totals describe the records the index still names, not what the shard files hold
+    live = [r for shard in doc["records"] for r in shard["records"]]
+    meta = doc.setdefault("metadata", {})
+    meta["ParamSize"] = int(sum(int(np.prod(r["shape"], dtype=np.int64)) for r in live))
+    meta["ParamBytes"] = float(sum(r["nbytes"] for r in live))
     with open(index, "w", encoding="utf-8") as f:
         json.dump(doc, f, indent=2)
     return doc

@@ -35,7 +35,7 @@ class Router:  # pylint: disable=too-many-instance-attributes
                  ports: Optional[List[int]] = None, num_gpus: Optional[List[int]] = None,
                  enable_prefix_cache: bool = False, router_mode: Literal["disagg", "round-robin"] = "disagg",
                  pd_balance_factor: float = 0.0, device: str = "cuda", start_servers: bool = True,
-                 server_start_timeout: float = 900.0):
+                 server_start_timeout: float = 900.0, api_key: Optional[str] = None):
         hosts = hosts or ["127.0.0.1"]
         ports = ports or [8080]
         num_gpus = num_gpus or [1]
@@ -49,6 +49,8 @@ class Router:  # pylint: disable=too-many-instance-attributes
         self.num_servers = len(hosts)
         self.server_urls = [f"http://{h}:{p}" for h, p in zip(hosts, ports)]
         self.headers = {"Content-Type": "application/json"}
+        if api_key:  # the endpoints' microserving routes sit behind the same key as their OpenAI routes
+            self.headers["Authorization"] = f"Bearer {api_key}"
         self.num_running_requests = [0] * self.num_servers
         self.device_id_starts = [0]
         for n in num_gpus:
@@ -69,7 +71,7 @@ class Router:  # pylint: disable=too-many-instance-attributes
                     server_device = f"cuda:{self.device_id_starts[i]}"
                 srv = PopenServer(
                     model, server_device, model_lib=model_lib, mode="server", host=hosts[i], port=ports[i],
-                    enable_debug=True, gpu_ids=gpu_ids,
+                    enable_debug=True, gpu_ids=gpu_ids, api_key=api_key,
                     tensor_parallel_shards=num_gpus[i] if num_gpus[i] > 1 else None,
                     engine_config=EngineConfig(prefix_cache_mode="radix" if enable_prefix_cache else "disable",
                                                gpu_memory_utilization=0.8),

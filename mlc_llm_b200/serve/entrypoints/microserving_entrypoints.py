@@ -23,9 +23,9 @@ from ...protocol.microserving_protocol import (PrepRecvRequest, PrepRecvResponse
 from ...protocol.openai_api_protocol import CompletionRequest
 from .. import engine_base
 from ..server.server_context import ServerContext
-from .openai_entrypoints import _serve_stream
+from .openai_entrypoints import _check_api_key, _serve_stream
 
-app = fastapi.APIRouter()
+app = fastapi.APIRouter(dependencies=[fastapi.Depends(_check_api_key)])
 
 
 def _as_completion(request, disagg: DisaggConfig) -> CompletionRequest:
@@ -40,14 +40,14 @@ def _as_completion(request, disagg: DisaggConfig) -> CompletionRequest:
 def prep_recv_response(engine, response) -> PrepRecvResponse:
     """Wrap the engine's slot reservation with a handle of its KV pool, so the prefill engine knows
     where (which device memory) and at which slots to write."""
-    import base64  # pylint: disable=import-outside-toplevel
+    from .. import kv_handoff  # pylint: disable=import-outside-toplevel
 
     extra = json.loads(response.usage.extra["disagg"]) if response.usage and response.usage.extra and \
         "disagg" in response.usage.extra else {}
     reservation = json.loads(extra.get("kv_append_metadata") or "{}")
-    payload = {"pool": engine.runtime.executor.kv_export(0), "slots": reservation.get("slots", []),
-               "begin": reservation.get("begin", 0), "end": reservation.get("end", 0)}
-    return PrepRecvResponse(kv_append_metadata=base64.b64encode(json.dumps(payload).encode()).decode("ascii"),
+    payload = kv_handoff.encode_payload(engine.runtime.executor.kv_export(0), reservation.get("slots", []),
+                                        reservation.get("begin", 0), reservation.get("end", 0))
+    return PrepRecvResponse(kv_append_metadata=payload,
                             prefix_matched_length=int(extra.get("prefix_matched_length", 0)))
 
 

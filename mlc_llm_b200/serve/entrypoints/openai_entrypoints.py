@@ -44,10 +44,30 @@ async def list_models() -> openai.ListResponse:
     return openai.ListResponse(data=[openai.ModelResponse(id=m) for m in ctx.get_model_list()])
 
 
+def _debug_enabled() -> bool:
+    return bool(ServerContext.enable_debug)
+
+
+def _strip_debug(request) -> None:
+    """Without ``--enable-debug`` a client cannot set debug options (ignore_eos, pinned system prompts,
+    special requests, the disaggregation controls): the field is dropped before the engine sees it
+    (reference: ``openai_entrypoints.py:139-143,243-247``)."""
+    if not _debug_enabled():
+        request.debug_config = None
+
+
+def _public(response):
+    """Engine-internal statistics in ``usage.extra`` are for debug servers only."""
+    usage = getattr(response, "usage", None)
+    if usage is not None and getattr(usage, "extra", None) is not None and not _debug_enabled():
+        usage.extra = None
+    return response
+
+
 async def _sse(gen: AsyncGenerator, first) -> AsyncGenerator[str, None]:
-    yield f"data: {first.model_dump_json(by_alias=True, exclude_none=False)}\n\n"
+    yield f"data: {_public(first).model_dump_json(by_alias=True, exclude_none=False)}\n\n"
     async for chunk in gen:
-        yield f"data: {chunk.model_dump_json(by_alias=True, exclude_none=False)}\n\n"
+        yield f"data: {_public(chunk).model_dump_json(by_alias=True, exclude_none=False)}\n\n"
     yield "data: [DONE]\n\n"
 
 
@@ -70,6 +90,7 @@ async def request_completion(request: openai.CompletionRequest, raw_request: fas
     if engine is None:
         return _no_engine(request.model)
     request_id = engine_base.create_request_id("cmpl", request.user)
+    _strip_debug(request)
     try:
         if request.stream:
             return await _serve_stream(engine._handle_completion(request, request_id))  # pylint: disable=protected-access
@@ -88,6 +109,7 @@ async def request_chat_completion(request: openai.ChatCompletionRequest, raw_req
     if engine is None:
         return _no_engine(request.model)
     request_id = engine_base.create_request_id("chatcmpl", request.user)
+    _strip_debug(request)
     try:
         if request.stream:
             return await _serve_stream(engine._handle_chat_completion(request, request_id))  # pylint: disable=protected-access
@@ -105,7 +127,7 @@ async def _await_or_abort(coro, raw_request: fastapi.Request, engine, request_id
     while True:
         done, _ = await asyncio.wait({task}, timeout=0.5)
         if done:
-            return task.result()
+            return _public(task.result())
         if await raw_request.is_disconnected():
             task.cancel()
             await engine.abort(request_id)

@@ -35,6 +35,8 @@ _S_FLT = ("temperature", "top_p", "uniform", "penalties", "bias_value")
 
 # KV pools exported by engines of this process (disaggregated serving inside one process)
 _LOCAL_KV_POOLS: Dict[str, torch.Tensor] = {}
+_KV_DTYPES = {"torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32,
+              "torch.float8_e4m3fn": torch.float8_e4m3fn}
 
 
 def _pad4(n: int) -> int:
@@ -675,75 +677,103 @@ class ModelExecutor:
         pairs = torch.from_numpy(np.ascontiguousarray(copies, dtype=np.int32)).to(self.device)
         self.models[model_id].copy_pages(pairs)
 
-    def kv_export(self, model_id: int = 0) -> str:
-        """Opaque description of this engine's KV pool that a peer engine can write into: an
-        in-process registry key (engines sharing a process, CPU tests) plus, on GPUs, a CUDA IPC
-        handle of the pool (engines in different processes of one NVLink box)."""
-        import base64  # pylint: disable=import-outside-toplevel
-        import pickle  # pylint: disable=import-outside-toplevel
+    def kv_export(self, model_id: int = 0) -> dict:
+        """Fixed-format description of this engine's KV pool that a peer engine can write into: an
+        in-process registry key (engines sharing a process, CPU tests) plus, on GPUs, the 64 raw bytes
+        of a CUDA IPC memory handle and the pool's offset inside that allocation (engines in different
+        processes of one NVLink box). See ``serve/kv_handoff.py`` for the schema."""
         import uuid  # pylint: disable=import-outside-toplevel
+
+        from . import kv_handoff  # pylint: disable=import-outside-toplevel
 
         pool = self.models[model_id].kv_pages
         key = getattr(self, "_kv_export_key", None)
         if key is None:
             key = self._kv_export_key = uuid.uuid4().hex
             _LOCAL_KV_POOLS[key] = pool
-        desc = {"key": key, "pid": os.getpid(), "shape": list(pool.shape), "dtype": str(pool.dtype)}
+        handle, offset = b"", 0
         if pool.is_cuda:
-            from torch.multiprocessing.reductions import reduce_tensor  # pylint: disable=import-outside-toplevel
+            from ..ops._lib import check, lib  # pylint: disable=import-outside-toplevel
 
-            fn, args = reduce_tensor(pool)
-            desc["ipc"] = base64.b64encode(pickle.dumps((fn, args))).decode("ascii")
-        return base64.b64encode(json.dumps(desc).encode()).decode("ascii")
+            buf = (ctypes.c_ubyte * 64)()
+            off, size = ctypes.c_longlong(0), ctypes.c_longlong(0)
+            with torch.cuda.device(pool.device):
+                rc = lib().mlcb_ipc_export(ctypes.c_void_p(pool.data_ptr()), buf, ctypes.byref(off), ctypes.byref(size))
+            check(rc, "mlcb_ipc_export")
+            handle, offset = bytes(buf), int(off.value)
+        return kv_handoff.pool_descriptor(key, list(pool.shape), str(pool.dtype),
+                                          pool.device.index if pool.is_cuda else -1, handle, offset)
 
-    def _peer_pool(self, desc: dict) -> torch.Tensor:
+    def _peer_pool(self, desc: dict):
+        """(tensor or None, device pointer, pages) of the receiver's pool named by a verified descriptor."""
+        from . import kv_handoff  # pylint: disable=import-outside-toplevel
+
         if desc["pid"] == os.getpid() and desc["key"] in _LOCAL_KV_POOLS:
-            return _LOCAL_KV_POOLS[desc["key"]]
+            pool = _LOCAL_KV_POOLS[desc["key"]]
+            if list(pool.shape) != desc["shape"] or str(pool.dtype) != desc["dtype"]:
+                raise kv_handoff.HandoffError("pool descriptor does not match the registered pool")
+            return pool, (pool.data_ptr() if pool.is_cuda else 0)
         cache = self.__dict__.setdefault("_peer_pools", {})
-        if desc["key"] not in cache:
-            import base64  # pylint: disable=import-outside-toplevel
-            import pickle  # pylint: disable=import-outside-toplevel
+        entry = cache.get(desc["key"])
+        if entry is None:
+            if len(desc["handle"]) != 64 or not self.device.type == "cuda":
+                raise kv_handoff.HandoffError("the receiving engine did not export a device memory handle")
+            from ..ops._lib import check, lib  # pylint: disable=import-outside-toplevel
 
-            if "ipc" not in desc:
-                raise RuntimeError("the receiving engine did not export a device memory handle")
-            fn, args = pickle.loads(base64.b64decode(desc["ipc"]))
-            cache[desc["key"]] = fn(*args)  # maps the peer's pool (cudaIpcOpenMemHandle)
-        return cache[desc["key"]]
+            base, mapped = ctypes.c_void_p(0), ctypes.c_longlong(0)
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(desc["handle"])
+            with torch.cuda.device(self.device):
+                rc = lib().mlcb_ipc_open(buf, ctypes.byref(base), ctypes.byref(mapped))
+            check(rc, "mlcb_ipc_open (is the receiving engine on this NVLink box?)")
+            entry = cache[desc["key"]] = (int(base.value), int(mapped.value))
+        base, mapped = entry
+        need = int(np.prod(desc["shape"], dtype=np.int64)) * torch.empty(0, dtype=_KV_DTYPES[desc["dtype"]]).element_size()
+        if desc["offset"] + need > mapped:
+            raise kv_handoff.HandoffError("pool descriptor claims more memory than the mapped allocation holds")
+        return None, base + desc["offset"]
 
     def send_kv(self, model_id: int, src_slots: np.ndarray, metadata: str) -> None:
         """Prefill side of the hand-off: copy the KV rows at ``src_slots`` into the receiver's slots.
-        ``metadata`` = base64 JSON {"pool": <kv_export of the receiver>, "slots": [...]}."""
+        ``metadata`` is the signed payload of the receiver's ``prep_recv`` step
+        (``kv_handoff.encode_payload``); it is verified and range-checked before anything is launched."""
         self._enter()
-        import base64  # pylint: disable=import-outside-toplevel
+        from . import kv_handoff  # pylint: disable=import-outside-toplevel
 
-        meta = json.loads(base64.b64decode(metadata))
-        pool_desc = json.loads(base64.b64decode(meta["pool"]))
-        dst_slots = np.asarray(meta["slots"], dtype=np.int32)
-        src_slots = np.ascontiguousarray(src_slots, dtype=np.int32)
+        meta = kv_handoff.decode_payload(metadata)
+        pool_desc = meta["pool"]
+        dst_slots = np.asarray(meta["slots"], dtype=np.int64)
+        src_slots = np.ascontiguousarray(src_slots, dtype=np.int64)
         if len(dst_slots) != len(src_slots):
-            raise RuntimeError(f"KV hand-off size mismatch: {len(src_slots)} rows to send, {len(dst_slots)} reserved")
+            raise kv_handoff.HandoffError(
+                f"KV hand-off size mismatch: {len(src_slots)} rows to send, {len(dst_slots)} reserved")
         src = self.models[model_id].kv_pages
-        dst = self._peer_pool(pool_desc)
-        if list(dst.shape[2:]) != list(src.shape[2:]) or dst.shape[0] != src.shape[0] or dst.dtype != src.dtype:
-            raise RuntimeError("the two engines do not hold the same model / KV layout")
+        dshape = pool_desc["shape"]
+        if dshape[2:] != list(src.shape[2:]) or dshape[0] != src.shape[0] or pool_desc["dtype"] != str(src.dtype):
+            raise kv_handoff.HandoffError("the two engines do not hold the same model / KV layout")
         page = src.shape[4]
+        kv_handoff.check_slots(src_slots, src.shape[1], page, "source")
+        kv_handoff.check_slots(dst_slots, dshape[1], page, "destination")
+        dst, dst_ptr = self._peer_pool(pool_desc)
         if not src.is_cuda:
-            s, d = torch.from_numpy(src_slots).long(), torch.from_numpy(dst_slots).long()
+            if dst is None:
+                raise kv_handoff.HandoffError("a CPU engine can only hand KV to an engine of its own process")
+            s, d = torch.from_numpy(src_slots), torch.from_numpy(dst_slots)
             dst[:, d // page, :, :, d % page, :] = src[:, s // page, :, :, s % page, :]
             return
-        from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
-        import ctypes  # pylint: disable=import-outside-toplevel
+        from ..ops._lib import check, lib, ptr, status_word, stream_ptr  # pylint: disable=import-outside-toplevel
 
-        if dst.device != src.device:
-            rc = lib().mlcb_enable_peer_access(ctypes.c_int(src.device.index), ctypes.c_int(dst.device.index))
-            check(rc, f"peer access from GPU {src.device.index} to GPU {dst.device.index}")
-        ss = torch.from_numpy(src_slots).to(self.device)
-        ds = torch.from_numpy(dst_slots).to(self.device)
+        if pool_desc["device"] != src.device.index and dst is not None:
+            rc = lib().mlcb_enable_peer_access(ctypes.c_int(src.device.index), ctypes.c_int(pool_desc["device"]))
+            check(rc, f"peer access from GPU {src.device.index} to GPU {pool_desc['device']}")
+        ss = torch.from_numpy(src_slots.astype(np.int32)).to(self.device)
+        ds = torch.from_numpy(dst_slots.astype(np.int32)).to(self.device)
         es = src.element_size()
+        dst_layer_stride = int(np.prod(dshape[1:], dtype=np.int64))
         rc = lib().mlcb_kv_slot_copy(
-            ptr(src), ctypes.c_void_p(dst.data_ptr()), ptr(ss), ptr(ds), ctypes.c_int(len(src_slots)),
-            ctypes.c_int(src.shape[0]), ctypes.c_longlong(src.stride(0) * es), ctypes.c_longlong(dst.stride(0) * es),
-            ctypes.c_int(src.shape[3]), ctypes.c_int(page), ctypes.c_int(src.shape[5] * es), stream_ptr())
+            ptr(src), ctypes.c_void_p(dst_ptr), ptr(ss), ptr(ds), ctypes.c_int(len(src_slots)),
+            ctypes.c_int(src.shape[0]), ctypes.c_longlong(src.stride(0) * es), ctypes.c_longlong(dst_layer_stride * es),
+            ctypes.c_int(src.shape[3]), ctypes.c_int(page), ctypes.c_int(src.shape[5] * es),
+            ctypes.c_int(src.shape[1]), ctypes.c_int(dshape[1]), ptr(status_word(self.device)), stream_ptr())
         check(rc, "mlcb_kv_slot_copy")
         torch.cuda.synchronize(self.device)  # the receiver may start as soon as this call returns
 

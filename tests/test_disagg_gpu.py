@@ -110,10 +110,10 @@ def test_kv_slot_copy_between_gpus():
     ex_a, ex_b = ModelExecutor.__new__(ModelExecutor), ModelExecutor.__new__(ModelExecutor)
     for ex, m, d in ((ex_a, a, src_dev), (ex_b, b, dst_dev)):
         ex.models, ex.device, ex.comm = [m], d, None
-    import base64, json
+    from mlc_llm_b200.serve import kv_handoff
     src_slots = np.asarray([3, 17, 18, 40, 127], dtype=np.int32)
     dst_slots = [64, 5, 6, 99, 0]
-    meta = base64.b64encode(json.dumps({"pool": ex_b.kv_export(0), "slots": dst_slots}).encode()).decode()
+    meta = kv_handoff.encode_payload(ex_b.kv_export(0), dst_slots, 0, len(dst_slots))
     ex_a.send_kv(0, src_slots, meta)
     torch.cuda.synchronize(dst_dev)
     got, want = b.kv_pages.cpu(), a.kv_pages.cpu()

@@ -352,14 +352,35 @@ def test_tensor_cache_round_trip_and_md5(tmp_path):
     for k in ("a.weight", "b.q_weight", "c.scale"):
         assert torch.equal(got[k], tensors[k])
     assert torch.equal(got["e.fp8"].view(torch.uint8), tensors["e.fp8"].view(torch.uint8))
-    # float32 is stored as its upper 16 bits ("f32-to-bf16") and widened on load
-    assert torch.equal(got["d.bias"], tensors["d.bias"].view(torch.int32).bitwise_and(-65536).view(torch.float32))
+    # float32 is stored as bf16 ("f32-to-bf16", round to nearest even) and widened on load
+    assert torch.equal(got["d.bias"], tensors["d.bias"].bfloat16().float())
     shard = tmp_path / doc["records"][0]["dataPath"]
     data = bytearray(shard.read_bytes())
     data[0] ^= 0xFF
     shard.write_bytes(bytes(data))
     with pytest.raises(ValueError):
         list(TensorCache(str(tmp_path), verify_md5=True))
+
+
+def test_tensor_cache_bf16_rounding_and_updated_totals(tmp_path):
+    from mlc_llm_b200.loader.tensor_cache import update_tensor_cache
+
+    # values exactly between two bf16 neighbours (ties go to the even mantissa), just above and just
+    # below the midpoint, negative ones, and the specials
+    bits = torch.tensor([0x3F808000, 0x3F818000, 0x3F808001, 0x3F807FFF, 0xBF808000 - (1 << 32), 0x7F800000,
+                         0x7F7FFFFF, 0x00000001, 0x80000000 - (1 << 32)], dtype=torch.int64).to(torch.int32)
+    vals = bits.view(torch.float32)
+    nan = torch.tensor([float("nan")])
+    dump_tensor_cache(iter({"x": vals, "n": nan}.items()), str(tmp_path))
+    got = dict(iter(TensorCache(str(tmp_path))))
+    want = vals.bfloat16().float()
+    assert torch.equal(got["x"].view(torch.int32), want.view(torch.int32))
+    assert got["x"][0].item() == 1.0 and got["x"][1].view(torch.int32).item() == 0x3F820000   # ties to even
+    assert bool(torch.isnan(got["n"]).all())
+    doc = update_tensor_cache(iter({"x": torch.randn(40), "extra": torch.ones(3, 5).half()}.items()), str(tmp_path))
+    live = dict(iter(TensorCache(str(tmp_path))))
+    assert doc["metadata"]["ParamSize"] == sum(t.numel() for t in live.values()) == 40 + 15 + 1
+    assert doc["metadata"]["ParamBytes"] == 40 * 2 + 15 * 2 + 2
 
 
 def test_reference_module_paths_and_stream_output_unpack():
