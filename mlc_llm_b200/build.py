@@ -41,6 +41,10 @@ NVCC_FLAGS = [
 ]
 
 
+if os.environ.get("MLCB_GEMM_TRACE") == "1":  # per-role timestamps of the GEMM kernel (profiling builds only)
+    NVCC_FLAGS.append("-DMLCB_GEMM_TRACE")
+
+
 def _nvcc() -> str:
     cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     return cand

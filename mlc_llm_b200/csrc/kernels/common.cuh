@@ -65,23 +65,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the hardware parks the thread until the phase completes or
+// about `hint_ns` have passed, instead of returning at once. A waiter that polls without the hint
+// floods the shared-memory pipeline with barrier probes and slows every other warp of the SM.
+constexpr uint32_t MBAR_SUSPEND_NS = 200000;  // per probe; the bounded-wait loops re-check their limits after each
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(MBAR_SUSPEND_NS)
+      : "memory");
+  return ok != 0;
+}
 
 // Bounded wait. `abort_flag` lives in shared memory and is set by whichever role gives up first so
 // the others leave quickly; `status` is the global error word the host reads.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = global_timer_ns();
-  uint32_t spins = 0;
+  // The common case (a pipeline hand-off) completes inside the first parked probe and never reads
+  // the global timer.
+  if (mbar_try_wait_parked(bar, parity)) return true;
+  if (mbar_try_wait_parked(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3f) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+    if (mbar_try_wait_parked(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
 }
@@ -223,10 +238,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(MBAR_SUSPEND_NS)
       : "memory");
   return ok != 0;
 }
@@ -234,17 +249,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  unsigned long long t0 = global_timer_ns();
-  uint32_t spins = 0;
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
   while (true) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++spins & 0x3f) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
 }

@@ -2,18 +2,24 @@
 //
 // One persistent, warp-specialised kernel serves both serving phases and both weight formats:
 //   * W dense 16-bit (fp16 / bf16), loaded by TMA straight into the 128-byte-swizzled UMMA layout;
-//   * W int4 group-quantised (q4f16_1: 8 nibbles per uint32, one fp16 scale per 32 weights along K).
-//     The packed tile is fetched by TMA, four "dequant" warps expand it to fp16 in the swizzled
-//     layout ((nibble - 7) * scale, one rounding), and the tensor core consumes it from there.
+//   * W int4 group-quantised (q4f16_1: 8 nibbles per uint32, one fp16 scale per 32 weights along K),
+//     stored as tile records: the nibbles and the group scales of one 128-row x 64-k block sit in
+//     4608 consecutive bytes, records of one 128-row block follow each other along K. One untiled bulk
+//     copy fetches a record, "dequant" warps expand it to fp16 in the swizzled layout
+//     ((nibble - 7) * scale, one rounding), and the tensor core consumes it from there.
 //
 // The weight tile is the UMMA "A" operand (M = 128 output features), the token tile is the "B"
 // operand (N = TN tokens, 16..256), so each expanded weight tile is reused by up to 256 tokens and
 // small decode batches do not pad to 128 rows. Accumulators live in TMEM (two buffers of 256
 // columns, so the epilogue of one tile overlaps the main loop of the next).
 //
-// Roles (352 threads): warp 0 = TMA producer (activations), warp 1 = MMA issuer (+TMEM owner),
-// warps 2-5 = dequant, warps 6-9 = epilogue (TMEM -> registers -> global), warp 10 = TMA producer
-// of the packed weights (q4).
+// Roles, dense kernel (352 threads): warp 0 = TMA producer (activations + weights), warp 1 = MMA issuer
+// (+TMEM owner), warps 6-9 = epilogue (TMEM -> registers -> global).
+// Roles, kernels with a dequant stage (512 threads): a warp issues on scheduler (warp % 4), and the
+// three single-thread control roles are serial chains of dependent instructions whose speed sets the
+// pace of the whole pipeline, so they get scheduler 1 to themselves: warp 1 = MMA issuer, warp 5 = TMA
+// producer of the activations, warp 9 = producer of the packed weights. Dequant group 0 = warps 0, 2,
+// 3, 4, group 1 = warps 6, 7, 8, 10 (the groups take alternate K blocks), epilogue = warps 12-15.
 //
 // Reference counterparts: dense matmul dispatched to cuBLAS (compiler_pass/blas_dispatch.py:15-52)
 // and the fused dequantize+matmul produced by compiler_pass/fuse_dequantize_matmul_ewise.py:9-85
@@ -35,15 +41,22 @@ constexpr int RAW_STAGES = 6; // packed-weight ring (q4): deeper, so TMA latency
 constexpr int X_STAGE_BYTES = MAX_TN * BK * 2;   // 32 KiB
 constexpr int W_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int RAW_STAGE_BYTES = BM * (BK / 2);   // 4 KiB of packed nibbles
+// int4 tile record of one (128-row block, K block): [2 halves][128 rows][16 B of nibbles] then
+// [128 rows][2 fp16 group scales]. Row r's first 32 weights of the block are the 16 bytes at r * 16,
+// its last 32 the 16 bytes at 2048 + r * 16, its two scales the 4 bytes at 4096 + r * 4.
+constexpr int Q4_REC_BYTES = BM * (BK / 2) + BM * 4;
 constexpr int GEMM_THREADS = 352;      // dense kernel: warps 0-10
-constexpr int GEMM_THREADS_Q4 = 480;   // int4 kernel: plus a second dequant group, warps 11-14
+constexpr int GEMM_THREADS_Q4 = 512;   // kernels with a dequant stage: warps 0-15
+constexpr int MAX_NST = 8;             // deepest activation / expanded-weight ring
+constexpr int RING_BYTES = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES);  // shared memory of that ring
 constexpr int SCALE_DEPTH = 8;                   // group scales are fetched this many K blocks ahead
 constexpr int SCALE_STAGE_BYTES = BM * 4;        // two fp16 scales per weight row and K block
 constexpr int GEMM_SMEM = STAGES * (X_STAGE_BYTES + W_STAGE_BYTES) + RAW_STAGES * RAW_STAGE_BYTES +
                           SCALE_DEPTH * SCALE_STAGE_BYTES + 1024 + 512;
 
 struct GemmParams {
-  const void* scale;    // [N, K/32] fp16 (q4 only)
+  const void* scale;    // fp8: [N/128, K/128] fp32 block scales; int4: unused (scales travel in the tile records)
+  const void* w_tiles;  // int4: tile records [ceil(rows / 128)][K / 64][Q4_REC_BYTES]
   const void* bias;     // [N] in the activation dtype, may be null
   void* y;
   int* status;
@@ -55,6 +68,7 @@ struct GemmParams {
   int ab_fmt;           // 0 fp16, 1 bf16
   int splits;           // split-K factor (1 = none)
   int kb_per_split;     // K blocks handled by one work item
+  int nst;              // ring depth: as many (activation tile + 16 KiB weight tile) stages as fit, even, <= MAX_NST
   float* workspace;     // [tiles, splits, tn, BM] fp32 partial sums (split-K only)
   int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
   long long* trace;     // optional: per-role timestamps of CTA 0 (profiling aid, null = off)
@@ -155,10 +169,16 @@ __device__ __forceinline__ int rotate_k(int kb, int kb0, int kb1, int t) {
 }
 
 // Profiling aid: role `r` records clock64 for event slot `i` (CTA 0 only, when a buffer is given).
+#ifdef MLCB_GEMM_TRACE
 #define GEMM_TRACE(r, i)                                                               \
   do {                                                                                 \
     if (p.trace && blockIdx.x == 0 && (i) < 512) p.trace[(r) * 512 + (i)] = clock64(); \
   } while (0)
+#else
+#define GEMM_TRACE(r, i) \
+  do {                   \
+  } while (0)
+#endif
 
 template <typename OutT>
 __device__ __forceinline__ void store_out(void* y, size_t idx, float v) {
@@ -354,26 +374,33 @@ __global__ void __launch_bounds__(WF ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const GemmParams p) {
   constexpr bool Q4 = WF != 0;  // "has a dequant stage"
-  constexpr int NST = TWO ? 6 : STAGES;                                  // ring depth
-  constexpr int XSB = TWO ? X_STAGE_BYTES / 2 : X_STAGE_BYTES;           // activation bytes per stage
+  constexpr int W_MMA = 1;
+  constexpr int W_XPROD = Q4 ? 5 : 0;
+  constexpr int W_RAWPROD = 9;             // dequant kernels only
+  constexpr int W_EPI0 = Q4 ? 12 : 6;      // four consecutive warps; TMEM lane quarter = warp & 3
+  const int NST = p.nst;                                                 // ring depth
+  const int XSB = (TWO ? p.tn >> 1 : p.tn) * BK * 2;                     // activation bytes per stage
   const uint32_t rank = TWO ? cluster_ctarank() : 0;                     // 0 = leader
-  constexpr int RAW_BYTES = WF == 2 ? BM * BK : RAW_STAGE_BYTES;            // packed tile of one K block
-  // Ring depth in the same space, kept even: the two dequant groups take alternate K blocks, so with an
-  // even depth every slot belongs to one group, which then observes every phase of the slot's barriers
-  // (a waiter that skipped a phase could mistake an older completion for the one it needs).
-  constexpr int RAW_N = (RAW_STAGES * RAW_STAGE_BYTES / RAW_BYTES) & ~1;
+  constexpr int RAW_BYTES = WF == 2 ? BM * BK : Q4_REC_BYTES;               // packed tile of one K block
+  // Ring depth in the same space (int4 records carry their scales, so they also use the scale ring's
+  // bytes), kept even: the two dequant groups take alternate K blocks, so with an even depth every slot
+  // belongs to one group, which then observes every phase of the slot's barriers (a waiter that skipped
+  // a phase could mistake an older completion for the one it needs).
+  constexpr int RAW_SPACE = RAW_STAGES * RAW_STAGE_BYTES + (WF == 1 ? SCALE_DEPTH * SCALE_STAGE_BYTES : 0);
+  constexpr int RAW_N = (RAW_SPACE / RAW_BYTES) & ~1;
+  static_assert(RAW_N >= 2 && RAW_N <= RAW_STAGES, "packed-weight ring depth");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sx = smem;                                   // NST x XSB (4 x 32 KiB or 6 x 16 KiB)
+  uint8_t* sx = smem;                                   // NST x XSB
   uint8_t* sw = sx + NST * XSB;                         // NST x 16 KiB
-  uint8_t* sraw = sw + NST * W_STAGE_BYTES;             // RAW_STAGES x 4 KiB
+  uint8_t* sraw = smem + RING_BYTES;                    // RAW_STAGES x 4 KiB
   uint8_t* sscale = sraw + RAW_STAGES * RAW_STAGE_BYTES;  // SCALE_DEPTH x 512 B
   uint64_t* bars = reinterpret_cast<uint64_t*>(sscale + SCALE_DEPTH * SCALE_STAGE_BYTES);
   uint64_t* full = bars;                       // [NST] activation (and dense weight) tile landed
-  uint64_t* empty = full + NST;                // [NST] MMA done reading the stage
-  uint64_t* deq_full = empty + NST;            // [NST] expanded weight tile written
-  uint64_t* raw_full = deq_full + NST;         // [RAW_STAGES] packed weight tile landed
+  uint64_t* empty = full + MAX_NST;            // [NST] MMA done reading the stage
+  uint64_t* deq_full = empty + MAX_NST;        // [NST] expanded weight tile written
+  uint64_t* raw_full = deq_full + MAX_NST;     // [RAW_STAGES] packed weight tile landed
   uint64_t* raw_empty = raw_full + RAW_STAGES; // [RAW_STAGES] dequant warps done reading it
   uint64_t* acc_full = raw_empty + RAW_STAGES; // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
@@ -390,9 +417,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   if (threadIdx.x == 0) {
     // pair mode: the leader's barriers also collect the peer CTA's arrivals
     for (int s = 0; s < NST; ++s) {
-      mbar_init(&full[s], 1);
+      // full[s]: the producer's expect_tx arrival plus, with a dequant stage, one arrival per dequant warp
+      // (of both CTAs in pair mode, where the leader's barrier collects everything)
+      mbar_init(&full[s], Q4 ? (TWO ? 9 : 5) : 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&deq_full[s], TWO ? 8 : 4);
+      mbar_init(&deq_full[s], 1);  // unused
     }
     for (int s = 0; s < RAW_STAGES; ++s) {
       mbar_init(&raw_full[s], 1);
@@ -416,7 +445,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     }
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == W_MMA) {
     if (TWO) {
       tmem_alloc_pair(tmem_slot, 512);
       tmem_relinquish_pair();
@@ -432,7 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   const int num_tiles = sh_num_items;  // work items
 
-  if (warp == 0) {
+  if (warp == W_XPROD) {
     // ------------------------------------------------------------ TMA producer: activations
     // (and the dense weight tile). Ring of STAGES, recycled by the MMA.
     if (lane == 0) {
@@ -446,10 +475,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     cx.init(p, total_kb, num_tiles);
     int gathered_row = -1;  // token tile whose rows are known to have arrived
     bool failed = false;    // no early exit: the lanes meet again at every token-tile change
-    for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles)) {
-      const int s = ix % NST;
-      if (lane == 0 && ix >= NST && !failed)
-        failed = !mbar_wait(&empty[s], ((ix / NST) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER);
+    int s = 0;
+    uint32_t xph = 1;  // parity of empty[s] this pass waits for (the first pass over the ring waits for nothing)
+    for (uint32_t ix = 0; cx.valid(num_tiles); ++ix, cx.next(p, total_kb, num_tiles), ++s) {
+      if (s == NST) {
+        s = 0;
+        xph ^= 1;
+      }
+      if (ix >= static_cast<uint32_t>(NST) && !failed) {
+        const bool got = mbar_wait(&empty[s], xph, abort_flag, p.status, ERR_WAIT_PRODUCER);
+        failed = !__all_sync(0xffffffffu, got);
+      }
       if (p.ag_wait && cx.ti.x_row != gathered_row) {
         // rows of this token tile are pushed by their owners' kernels; one lane per 8-row group
         // (in pair mode each CTA waits for the half it loads)
@@ -477,30 +513,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 10) {
+  } else if (Q4 && warp == W_RAWPROD) {
     // ------------------------------------------------------------ TMA producer: packed weights
     // (q4). Ring of RAW_STAGES, recycled by the dequant warps as soon as they hold the nibbles in
     // registers, so this stream runs ahead of the MMA loop.
-    if (Q4 && lane == 0) {
-      tma_prefetch_desc(&tmap_w);
+    // (The whole warp walks the loop, lane 0 issues: uniform control flow keeps the bookkeeping cheap.)
+    {
+      if (WF == 2 && lane == 0) tma_prefetch_desc(&tmap_w);
       KCursor cr;
       cr.init(p, total_kb, num_tiles);
-      for (uint32_t ir = 0; cr.valid(num_tiles); ++ir, cr.next(p, total_kb, num_tiles)) {
-        const int s = ir % RAW_N;
-        if (ir >= RAW_N &&
-            !mbar_wait(&raw_empty[s], ((ir / RAW_N) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_PRODUCER))
-          break;
-        mbar_expect_tx(&raw_full[s], RAW_BYTES);
-        tma_load_2d(sraw + s * RAW_BYTES, &tmap_w, &raw_full[s], WF == 2 ? cr.ka * BK : cr.ka * (BK / 8),
-                    cr.ti.w_row);
+      int s = 0;
+      uint32_t rph = 1;
+      for (uint32_t ir = 0; cr.valid(num_tiles); ++ir, cr.next(p, total_kb, num_tiles), ++s) {
+        if (s == RAW_N) {
+          s = 0;
+          rph ^= 1;
+        }
+        if (ir >= RAW_N) {
+          bool ok = mbar_wait(&raw_empty[s], rph, abort_flag, p.status, ERR_WAIT_PRODUCER);
+          if (!__all_sync(0xffffffffu, ok)) break;
+        }
+        if (lane == 0) {
+          mbar_expect_tx(&raw_full[s], RAW_BYTES);
+          if constexpr (WF == 2) {
+            tma_load_2d(sraw + s * RAW_BYTES, &tmap_w, &raw_full[s], cr.ka * BK, cr.ti.w_row);
+          } else {
+            const uint8_t* rec = reinterpret_cast<const uint8_t*>(p.w_tiles) +
+                                 (static_cast<size_t>(cr.ti.w_row >> 7) * total_kb + cr.ka) * Q4_REC_BYTES;
+            bulk_load(sraw + s * RAW_BYTES, rec, Q4_REC_BYTES, &raw_full[s]);
+          }
+        }
+        __syncwarp();
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == W_MMA) {
     // ------------------------------------------------------------ MMA issuer
-    // (pair mode: the leader CTA issues for both; the peer's warp only owns its half of the TMEM)
+    // (pair mode: the leader CTA issues for both; the peer's warp only owns its half of the TMEM.)
+    // One lane runs the loop. Its speed sets the pace of the pipeline (every tcgen05 instruction and every
+    // barrier probe costs this thread some tens of cycles), so the loop carries no arithmetic that is not
+    // needed: one barrier per stage, ring position and parity as counters.
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(p.ab_fmt, TWO ? 2 * BM : BM, p.tn, 0, 0);
-      uint32_t it = 0, tile_i = 0;
+      uint32_t tile_i = 0, it = 0;  // `it` only feeds the trace
+      int s = 0;
+      uint32_t ph = 0;
+      const uint64_t adesc0 = umma_smem_desc(smem_u32(sw), 16, 1024);
+      const uint64_t bdesc0 = umma_smem_desc(smem_u32(sx), 16, 1024);
+      const uint32_t a_step = W_STAGE_BYTES >> 4, b_step = static_cast<uint32_t>(XSB) >> 4;  // per stage, 16-byte units
+      uint64_t adesc = adesc0, bdesc = bdesc0;
       bool ok = true;
       auto wait_bar = [&](uint64_t* bar, uint32_t parity, int code) {
         return TWO ? mbar_wait_cluster(bar, parity, abort_flag, p.status, code)
@@ -518,28 +578,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         const int kb0 = (t % p.splits) * p.kb_per_split;
         const int kb1 = min(total_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % NST;
-          const uint32_t ph = (it / NST) & 1;
-          ok = wait_bar(&full[s], ph, ERR_WAIT_TMA);
+          GEMM_TRACE(9, it);
+          // one barrier per stage: the activation tile's bytes and (with a dequant stage) the arrivals
+          // of the warps that wrote the expanded weight tile
+          ok = wait_bar(&full[s], ph, Q4 ? ERR_WAIT_DEQUANT : ERR_WAIT_TMA);
           if (!ok) break;
-          GEMM_TRACE(1, it);
-          if (Q4) {
-            ok = wait_bar(&deq_full[s], ph, ERR_WAIT_DEQUANT);
-            if (!ok) break;
-          }
           GEMM_TRACE(2, it);
           tc_fence_after();
-          const uint64_t adesc = umma_smem_desc(smem_u32(sw + s * W_STAGE_BYTES), 16, 1024);
-          const uint64_t bdesc = umma_smem_desc(smem_u32(sx + s * XSB), 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             // advancing 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
             if (TWO) umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
             else umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk) ? 1u : 0u);
           }
+          GEMM_TRACE(10, it);
           if (TWO) umma_commit_pair(&empty[s]);
           else umma_commit(&empty[s]);
           GEMM_TRACE(3, it);
+          adesc += a_step;
+          bdesc += b_step;
+          if (++s == NST) {
+            s = 0;
+            ph ^= 1;
+            adesc = adesc0;
+            bdesc = bdesc0;
+          }
         }
         if (ok) {
           if (TWO) umma_commit_pair(&acc_full[a]);
@@ -547,36 +610,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
       }
     }
-  } else if (warp < 6 || warp >= 11) {
-    // ------------------------------------------------------------ dequant warps (q4 only)
-    // Two groups of four warps (2-5 and 11-14) take alternate K blocks. One iteration is a chain of
-    // long-latency steps (barrier polls, shared loads, the proxy fence), about twice the time the
-    // tensor core needs for the block, so two chains in flight keep it fed.
-    if (Q4) {
-      const int grp = warp >= 11 ? 1 : 0;
-      const int row = (warp - (grp ? 11 : 2)) * 32 + lane;  // 0..127 inside the tile
-      const __half* scale = reinterpret_cast<const __half*>(p.scale);
-      const int groups_per_row = p.K / 32;
+  } else if (Q4 && warp < 11 && warp != W_XPROD && warp != W_RAWPROD) {
+    // ------------------------------------------------------------ dequant warps
+    // Two groups of four warps take alternate K blocks. One iteration is a chain of long-latency steps
+    // (barrier polls, shared loads, the proxy fence), longer than the tensor core needs for the block,
+    // so two chains in flight keep it fed.
+    {
+      const int grp = warp >= 6 ? 1 : 0;
+      // warps 0, 2, 3, 4 -> rows 0 / 32 / 64 / 96 of group 0; warps 6, 7, 8, 10 likewise for group 1
+      const int widx = grp ? (warp == 10 ? 3 : warp - 6) : (warp == 0 ? 0 : warp - 1);
+      const int row = widx * 32 + lane;  // 0..127 inside the tile
       bool ok = true;
-      // Group scales of a K block: two fp16 values per row, copied into shared memory
-      // SCALE_DEPTH blocks ahead with cp.async (one commit group per own iteration).
+      // K blocks this CTA walks over all of its work items (the groups need no tile bookkeeping)
+      uint32_t n_iters = 0;
+      for (int t = work_id(p); t < num_tiles; t += work_stride(p)) {
+        const int kb0 = (t % p.splits) * p.kb_per_split;
+        n_iters += static_cast<uint32_t>(min(total_kb, kb0 + p.kb_per_split) - kb0);
+      }
+      // fp8 only: the block scale of a K block (one fp32 per 128 x 128 block, the same word for every
+      // row of the tile) is copied into shared memory SCALE_DEPTH blocks ahead with cp.async (one
+      // commit group per own iteration). int4 records carry their scales with them.
       const uint32_t my_scale = smem_u32(sscale) + row * 4;
       auto fetch_scale = [&](const KCursor& c, uint32_t slot) {
-        const uint32_t dst = my_scale + slot * SCALE_STAGE_BYTES;
-        const bool live = c.valid(num_tiles) && (c.ti.nb * BM + row < p.N) &&
-                          (WF == 2 || c.ka * 2 + 1 < groups_per_row);
-        if (live) {
-          const void* src;
-          if (WF == 2)  // one fp32 scale per 128 x 128 block: the same word for every row of the tile
-            src = reinterpret_cast<const float*>(p.scale) +
-                  static_cast<size_t>(c.ti.w_row / 128) * ((p.K + 127) / 128) + (c.ka >> 1);
-          else
-            src = scale + static_cast<size_t>(c.ti.w_row + row) * groups_per_row + c.ka * 2;
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-        } else {
-          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
+        if constexpr (WF == 2) {
+          const uint32_t dst = my_scale + slot * SCALE_STAGE_BYTES;
+          const bool live = c.valid(num_tiles) && (c.ti.nb * BM + row < p.N);
+          if (live) {
+            const void* src = reinterpret_cast<const float*>(p.scale) +
+                              static_cast<size_t>(c.ti.w_row / 128) * ((p.K + 127) / 128) + (c.ka >> 1);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+          } else {
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(0u) : "memory");
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
       };
       auto advance2 = [&](KCursor& c) {
         if (c.valid(num_tiles)) c.next(p, total_kb, num_tiles);
@@ -586,40 +653,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       cs.init(p, total_kb, num_tiles);
       if (grp && cs.valid(num_tiles)) cs.next(p, total_kb, num_tiles);
       cp = cs;
-      for (int i = 0; i < SCALE_DEPTH / 2; ++i) {
-        fetch_scale(cp, grp + 2 * i);
-        advance2(cp);
+      if constexpr (WF == 2) {
+        for (int i = 0; i < SCALE_DEPTH / 2; ++i) {
+          fetch_scale(cp, grp + 2 * i);
+          advance2(cp);
+        }
       }
-      for (uint32_t it = grp; cs.valid(num_tiles) && ok; it += 2) {
-        const int s = it % NST;
-        const int rs = it % RAW_N;
-        const uint32_t slot = it % SCALE_DEPTH;
-        asm volatile("cp.async.wait_group %0;" ::"n"(SCALE_DEPTH / 2 - 1) : "memory");
-        uint32_t sc_bits;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc_bits) : "r"(my_scale + slot * SCALE_STAGE_BYTES) : "memory");
-        const __half2 sc = *reinterpret_cast<__half2*>(&sc_bits);
-        advance2(cs);
-        ok = mbar_wait(&raw_full[rs], (it / RAW_N) & 1, abort_flag, p.status, ERR_WAIT_TMA);
+      // ring positions of this group's K blocks: it = grp, grp + 2, ... (both ring depths are even)
+      int s = grp, rs = grp;
+      uint32_t eph = 1, rph = 0;  // parities of empty[s] (first pass: no wait) and raw_full[rs]
+      for (uint32_t it = grp; it < n_iters && ok; it += 2) {
+        uint32_t sc_bits = 0;
+        if constexpr (WF == 2) {
+          const uint32_t slot = it % SCALE_DEPTH;
+          asm volatile("cp.async.wait_group %0;" ::"n"(SCALE_DEPTH / 2 - 1) : "memory");
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc_bits) : "r"(my_scale + slot * SCALE_STAGE_BYTES) : "memory");
+        }
+        if constexpr (WF == 2) advance2(cs);
+        if (threadIdx.x == 64) GEMM_TRACE(6, it);
+        ok = mbar_wait(&raw_full[rs], rph, abort_flag, p.status, ERR_WAIT_TMA);
         ok = __all_sync(0xffffffffu, ok);  // the warp leaves together
         if (!ok) break;
         if (threadIdx.x == 64) GEMM_TRACE(4, it);
-        constexpr int RAW_ROW = RAW_BYTES / BM;  // 32 bytes of nibbles or 64 bytes of fp8 per row
-        const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_BYTES + row * RAW_ROW);
-        uint32_t words[RAW_ROW / 4];
+        constexpr int NWORDS = WF == 2 ? 16 : 8;  // 64 bytes of fp8 or 32 bytes of nibbles per row
+        uint32_t words[NWORDS];
+        if constexpr (WF == 2) {
+          const uint4* raw = reinterpret_cast<const uint4*>(sraw + rs * RAW_BYTES + row * 64);
 #pragma unroll
-        for (int i = 0; i < RAW_ROW / 16; ++i) {
-          const uint4 r = raw[i];
-          words[4 * i] = r.x; words[4 * i + 1] = r.y; words[4 * i + 2] = r.z; words[4 * i + 3] = r.w;
+          for (int i = 0; i < 4; ++i) {
+            const uint4 r = raw[i];
+            words[4 * i] = r.x; words[4 * i + 1] = r.y; words[4 * i + 2] = r.z; words[4 * i + 3] = r.w;
+          }
+        } else {
+          // consecutive lanes read consecutive 16-byte words: no bank conflicts
+          const uint8_t* rec = sraw + rs * RAW_BYTES;
+          const uint4 r0 = *reinterpret_cast<const uint4*>(rec + row * 16);
+          const uint4 r1 = *reinterpret_cast<const uint4*>(rec + BM * 16 + row * 16);
+          sc_bits = *reinterpret_cast<const uint32_t*>(rec + 2 * BM * 16 + row * 4);
+          words[0] = r0.x; words[1] = r0.y; words[2] = r0.z; words[3] = r0.w;
+          words[4] = r1.x; words[5] = r1.y; words[6] = r1.z; words[7] = r1.w;
         }
         // The packed slot is released further down, behind the proxy fence that also publishes the
         // expanded tile: its next writer is the TMA engine (async proxy) while these reads went through
         // the generic proxy, and without a fence in between the refill was seen overtaking the reads.
         // the expanded tile may only be overwritten once the MMA that read it has finished
-        if (it >= NST) {
-          ok = mbar_wait(&empty[s], ((it / NST) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_MMA);
+        if (it >= static_cast<uint32_t>(NST)) {
+          ok = mbar_wait(&empty[s], eph, abort_flag, p.status, ERR_WAIT_MMA);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
+        if (threadIdx.x == 64 && it < 500) GEMM_TRACE(7, it);
         uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
         if constexpr (WF == 2) {
           const float fs = __uint_as_float(sc_bits);
@@ -644,40 +727,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
           }
         } else {
+          const __half2 sc = *reinterpret_cast<__half2*>(&sc_bits);
+          // A nibble q in mantissa bits [0, 4) under exponent 0x6400 is the fp16 value 1024 + q; in bits
+          // [4, 8) under exponent 0x5400 it is 64 + q. Subtracting 1031 (71) is exact, so the product
+          // (q - 7) * s is rounded once. Device nibble order: pair (2j, 2j+1) of a word sits at bits
+          // [4j, 4j+4) and [16+4j, 20+4j), so one shift by 8 exposes pairs 2 and 3 to the same two masks.
+          const __half2 off_lo = __float2half2_rn(1031.f);
+          const __half2 off_hi = __float2half2_rn(71.f);
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-          const __half sv = (w < 4) ? __low2half(sc) : __high2half(sc);
-          const __half2 s2 = __half2half2(sv);
-          // 0x6400 | q is the fp16 value 1024 + q; subtracting 1031 is exact, so the product
-          // (q - 7) * s is rounded once
-          const __half2 off = __float2half2_rn(1031.f);
-          const uint32_t x = words[w];
-          uint32_t h[4];
+          for (int w = 0; w < 8; ++w) {
+            const __half2 s2 = __half2half2((w < 4) ? __low2half(sc) : __high2half(sc));
+            const uint32_t x = words[w];
+            const uint32_t y = x >> 8;
+            uint32_t v[4];
+            v[0] = (x & 0x000f000fu) | 0x64006400u;
+            v[1] = (x & 0x00f000f0u) | 0x54005400u;
+            v[2] = (y & 0x000f000fu) | 0x64006400u;
+            v[3] = (y & 0x00f000f0u) | 0x54005400u;
+            uint32_t h[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // device layout: nibble pair (2j, 2j+1) sits at bits [4j, 4j+4) and [16+4j, 20+4j)
-            uint32_t v = ((x >> (4 * j)) & 0x000f000fu) | 0x64006400u;
-            __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v), off), s2);
-            h[j] = *reinterpret_cast<uint32_t*>(&hv);
+            for (int j = 0; j < 4; ++j) {
+              const __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[j]), (j & 1) ? off_hi : off_lo), s2);
+              h[j] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
           }
-          *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) =
-              make_uint4(h[0], h[1], h[2], h[3]);
-        }
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
         if (lane == 0) {
           // pair mode: the leader's barrier counts the dequant warps of both CTAs
-          if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&deq_full[s]), 0));
-          else mbar_arrive(&deq_full[s]);
+          if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&full[s]), 0));
+          else mbar_arrive(&full[s]);
         }
         if (threadIdx.x == 64) GEMM_TRACE(5, it);
-        fetch_scale(cp, slot);  // refill the slot consumed above
-        advance2(cp);
+        if constexpr (WF == 2) {
+          fetch_scale(cp, it % SCALE_DEPTH);  // refill the slot consumed above
+          advance2(cp);
+        }
+        s += 2;
+        if (s >= NST) {
+          s -= NST;
+          eph ^= 1;
+        }
+        rs += 2;
+        if (rs >= RAW_N) {
+          rs -= RAW_N;
+          rph ^= 1;
+        }
       }
     }
-  } else if (warp < 10) {
+  } else if (warp >= W_EPI0 && warp < W_EPI0 + 4) {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tile_i = 0;
@@ -697,7 +798,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, ERR_WAIT_MMA);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
       if (!ok) break;
-      if (threadIdx.x == 192) GEMM_TRACE(6, tile_i);
+      if (threadIdx.x == W_EPI0 * 32) GEMM_TRACE(6, tile_i);
       tc_fence_after();
       if (ti.dummy) {  // odd feature-block count: this half of the pair tile has no output
         tc_fence_before();
@@ -741,7 +842,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         ok = mbar_wait(&ep_bar[0], 0, abort_flag, p.status, ERR_WAIT_EPILOGUE);  // two phases per tile
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (warp == 6) {
+        if (warp == W_EPI0) {
           int seen = 0;
           if (lane == 0) {
             atomicAdd(&p.counters[tile], 1);
@@ -782,7 +883,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
                 b4[u] = p.ab_fmt == 0 ? __half2float(reinterpret_cast<const __half*>(p.bias)[n4 + u])
                                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n4 + u]);
           }
-          const int ew = warp - 6;                 // epilogue warp 0..3
+          const int ew = warp - W_EPI0;            // epilogue warp 0..3
           for (int j0 = j_begin + ew; j0 < j_end; j0 += 16) {
             float4 acc[4];
 #pragma unroll
@@ -839,7 +940,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           ok = mbar_wait(&ep_bar[0], 1, abort_flag, p.status, ERR_WAIT_EPILOGUE);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if (warp == 6 && lane == 0) {
+          if (warp == W_EPI0 && lane == 0) {
             const int prev = atomicAdd(&p.counters[tile], 0x10000);
             if ((prev >> 16) == p.splits - 1) p.counters[tile] = 0;
           }
@@ -881,14 +982,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) release_acc(a);
-      if (threadIdx.x == 192) GEMM_TRACE(7, tile_i);
+      if (threadIdx.x == W_EPI0 * 32) GEMM_TRACE(7, tile_i);
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (TWO) cluster_sync_all();  // the peer's shared memory and TMEM stay valid until both are done
-  if (warp == 1) {
+  if (warp == W_MMA) {
     tc_fence_after();
     if (TWO) tmem_dealloc_pair(tmem_base, 512);
     else tmem_dealloc(tmem_base, 512);
@@ -999,6 +1100,13 @@ int sm_count() {
   return n[dev];
 }
 
+// Ring depth for a token tile of `tn` rows (half of it per CTA in pair mode): as many stages as fit.
+static int pick_nst(int tn, bool pair) {
+  const int xsb = (pair ? tn / 2 : tn) * BK * 2;
+  int n = (RING_BYTES / (xsb + W_STAGE_BYTES)) & ~1;
+  return n > MAX_NST ? MAX_NST : (n < 2 ? 2 : n);
+}
+
 static int pick_tn(int M) {
   if (M <= 16) return 16;
   int blocks = (M + MAX_TN - 1) / MAX_TN;
@@ -1012,12 +1120,15 @@ static int pick_tn(int M) {
 using namespace mlcb;
 
 static long long* g_gemm_trace = nullptr;
-// Debug hook: device buffer of 8 x 512 int64 that receives CTA 0's role timestamps (null = off).
+// Debug hook: device buffer of 12 x 512 int64 that receives CTA 0's role timestamps (null = off;
+// only builds with MLCB_GEMM_TRACE record anything).
 MLCB_API void mlcb_gemm_set_trace(long long* buf) { g_gemm_trace = buf; }
 
 // Returns 0 on success, a negative value for a rejected shape, a positive CUDA error otherwise.
 // x: [M, K] row-major (ldx elements) fp16/bf16.  w: dense [N, K] (same dtype) or, with
-// scale != nullptr, the device-layout packed int4 [N, K/8] uint32 with scale [N, K/32] fp16.
+// scale != nullptr, int4 tile records [ceil(N / 128)][K / 64][4608 bytes] (nibbles in device order
+// and fp16 group scales interleaved per 128-row x 64-k block, see Q4_REC_BYTES; `scale` only selects
+// the format and is not read).
 // Arguments of the fused tensor-parallel forms (mirrored by a ctypes structure on the Python side).
 struct MlcbFusedArgs {
   int rs_world, rs_rank, rs_rows, rs_epoch;
@@ -1074,6 +1185,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   }
   GemmParams p = {};
   p.scale = scale;
+  p.w_tiles = q4 ? w : nullptr;
   p.bias = bias;
   p.y = y;
   p.status = status;
@@ -1088,6 +1200,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   const bool pair = pair_mode_enabled(wf) && M > 32;
   if (pair) p.tn = (p.tn + 31) & ~31;
   p.pair = pair ? 1 : 0;
+  p.nst = pick_nst(p.tn, pair);
   p.num_m_blocks = (M + p.tn - 1) / p.tn;
   p.num_n_blocks = (N + BM - 1) / BM;
   p.out_dtype = out_dtype;
@@ -1141,10 +1254,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   const CUtensorMap* mx = get_tensor_map(x, 2, 2, xd, xs, xb, 1);
   const CUtensorMap* mw;
   if (q4) {
-    uint64_t wd[2] = {static_cast<uint64_t>(K / 8), static_cast<uint64_t>(N)};
-    uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
-    uint32_t wb[2] = {BK / 8, BM};
-    mw = get_tensor_map(w, 4, 2, wd, ws, wb, 0);
+    mw = mx;  // tile records are fetched with untiled bulk copies; the kernel ignores this map
   } else if (wf == 2) {
     uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     uint64_t ws[1] = {static_cast<uint64_t>(K)};
@@ -1259,7 +1369,8 @@ MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
 
 // Grouped GEMM for mixture-of-experts layers: rows [offsets[e], offsets[e+1]) of x (expert-major
 // permuted tokens, `total_rows` in all) are multiplied by expert e's weight slab w[e] ([N, K] dense
-// 16-bit, or packed int4 [N, K/8] + scale [N, K/32]); y has the same row order, [total_rows, N].
+// 16-bit, or int4 tile records of the stacked slabs, selected by scale != nullptr); y has the same row
+// order, [total_rows, N].
 // `offsets` is a device array of num_groups + 1 ints; the kernel derives its tile list from it, so
 // no host synchronisation is needed between routing and the expert matmuls.
 static int gemm_grouped_launch(const void* x, const void* w, const void* scale, void* y, const int* offsets,
@@ -1279,6 +1390,7 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   }
   GemmParams p = {};
   p.scale = scale;
+  p.w_tiles = q4 ? w : nullptr;
   p.bias = nullptr;
   p.y = y;
   p.status = status;
@@ -1289,6 +1401,7 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   // token tile sized for the average expert load (the box of the activation tensor map is fixed)
   const int avg = (rows_hint + num_groups - 1) / num_groups;
   p.tn = avg >= 192 ? 256 : avg >= 96 ? 128 : avg >= 48 ? 64 : avg >= 24 ? 32 : 16;
+  p.nst = pick_nst(p.tn, false);
   p.num_m_blocks = 0;
   p.num_n_blocks = N / BM;
   p.out_dtype = out_dtype;
@@ -1309,10 +1422,7 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   const CUtensorMap* mw;
   const uint64_t wrows = static_cast<uint64_t>(num_slabs) * N;
   if (q4) {
-    uint64_t wd[2] = {static_cast<uint64_t>(K / 8), wrows};
-    uint64_t ws[1] = {static_cast<uint64_t>(K / 8) * 4};
-    uint32_t wb[2] = {BK / 8, BM};
-    mw = get_tensor_map(w, 4, 2, wd, ws, wb, 0);
+    mw = mx;  // slab e's records start at tile row e * N / 128 (N is a multiple of 128 here)
   } else {
     uint64_t wd[2] = {static_cast<uint64_t>(K), wrows};
     uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -1436,6 +1546,7 @@ MLCB_API int mlcb_gemm_noalloc(const void* x, const void* w, void* y, int M, int
   p.K = K;
   p.ldy = ldy;
   p.tn = pick_tn(M);
+  p.nst = pick_nst(p.tn, false);
   p.num_m_blocks = (M + p.tn - 1) / p.tn;
   p.num_n_blocks = (N + BM - 1) / BM;
   p.out_dtype = ab_fmt;

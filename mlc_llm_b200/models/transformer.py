@@ -55,6 +55,8 @@ class ParamStore:
                 total += lw.scale.numel() * lw.scale.element_size()
             if lw.bias is not None:
                 total += lw.bias.numel() * lw.bias.element_size()
+            if getattr(lw, "_tiles", None) is not None:
+                total += lw._tiles.numel()  # pylint: disable=protected-access
         return total
 
 

@@ -29,7 +29,9 @@ class LinearWeight:
 
     kind ``dense``: ``w [N, K]``.  kind ``q4``: ``w`` is packed int4 ``[N, K/8]`` int32 (artifact
     nibble order on CPU, device order on GPU -- see ``quantization.to_device_layout_q4``) and
-    ``scale [N, K/32]``.  kind ``fp8_block``: ``w [N, K]`` e4m3, ``scale [N/128, K/128]`` fp32.
+    ``scale [N, K/32]``; on a GPU the tensor-core GEMM reads a second, tile-record form of the same
+    data (:meth:`q4_tiles`, ``quantization.to_tiled_q4``), the one-to-four-token GEMV the row-major
+    one.  kind ``fp8_block``: ``w [N, K]`` e4m3, ``scale [N/128, K/128]`` fp32.
     kind ``fp8_tensor``: fp8 ``w`` with a scalar ``scale``.
     """
 
@@ -43,6 +45,22 @@ class LinearWeight:
     device_layout: bool = False
     # dense fp16/bf16 copy used by kernels that do not take the packed form (built lazily)
     _dense: Optional[torch.Tensor] = None
+    # int4 tile records for the tensor-core GEMM (GPU only, built when the weight moves to the GPU)
+    _tiles: Optional[torch.Tensor] = None
+
+    def q4_tiles(self) -> torch.Tensor:
+        if self._tiles is None:
+            assert self.kind == "q4" and self.device_layout and self.w.is_cuda
+            self._tiles = Q.to_tiled_q4(self.w, self.scale)
+        return self._tiles
+
+    def q4_tileable(self, k: int) -> bool:
+        """The tensor-core int4 path needs 4-bit groups of 32, K a multiple of 64 and, for stacked
+        expert slabs, slabs of whole 128-row blocks."""
+        return (self.kind == "q4" and self.quant is not None and self.quant.bits == 4
+                and self.quant.group_size == 32 and k % 64 == 0 and self.scale is not None
+                and self.scale.dtype == torch.float16
+                and (self.w.dim() == 2 or self.w.shape[-2] % 128 == 0))
 
     def to(self, device) -> "LinearWeight":
         dev = torch.device(device)
@@ -52,9 +70,12 @@ class LinearWeight:
                 w, dl = Q.to_device_layout_q4(w), True
             elif dev.type == "cpu" and dl:
                 w, dl = Q.from_device_layout_q4(w.cpu()), False
-        return LinearWeight(self.kind, w.to(dev), None if self.scale is None else self.scale.to(dev),
-                            None if self.bias is None else self.bias.to(dev), self.quant,
-                            self.out_features, self.in_features, dl)
+        out = LinearWeight(self.kind, w.to(dev), None if self.scale is None else self.scale.to(dev),
+                           None if self.bias is None else self.bias.to(dev), self.quant,
+                           self.out_features, self.in_features, dl)
+        if dev.type == "cuda" and dl and out.q4_tileable(w.shape[-1] * 8):
+            out.q4_tiles()
+        return out
 
     def dense(self, dtype: torch.dtype) -> torch.Tensor:
         """Materialise the full-precision weight (used by oracles and by cold paths)."""
@@ -129,8 +150,7 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
     if m == 0:
         return y.reshape(*lead, n)
     ab = DTYPE_CODE[x2.dtype]
-    if lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and x2.dtype == torch.float16 \
-            and k % 64 == 0:
+    if x2.dtype == torch.float16 and lw.q4_tileable(k):
         assert lw.device_layout
         if m <= 4 and od in (torch.float16, torch.float32) and _GEMV_Q4:
             # one to four tokens: the memory-bound CUDA-core kernel beats the tensor-core one, whose
@@ -149,7 +169,8 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
                 return y.reshape(*lead, n)
             if rc > 0:
                 check(rc, f"mlcb_gemm_q4_lowm(M={m},N={n},K={k})")
-        rc = lib().mlcb_gemm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m),
+        tiles = lw.q4_tiles()
+        rc = lib().mlcb_gemm(ptr(x2), ptr(tiles), ptr(tiles), ptr(lw.bias), ptr(y), c_int(m),
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
                              stream_ptr())
@@ -464,12 +485,9 @@ def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
     if rows == 0:
         return y
     x2 = x if x.stride(-1) == 1 else x.contiguous()
-    q4 = lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and x.dtype == torch.float16 \
-        and k % 64 == 0
-    w = lw.w if (q4 or lw.kind == "dense") else lw.dense(x.dtype)
-    if lw.kind == "q4" and not q4:
-        w = lw.dense(x.dtype)
-    rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(lw.scale) if q4 else ptr(None), ptr(y), ptr(offsets),
+    q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+    w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
+    rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(offsets),
                                  c_int(e), c_int(rows), c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n),
                                  c_int(DTYPE_CODE[x.dtype]), c_int(DTYPE_CODE[od]), ptr(status_word(x.device)),
                                  stream_ptr())

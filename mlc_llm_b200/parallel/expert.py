@@ -162,12 +162,11 @@ class ExpertParallel:
 
     def _grouped(self, x: torch.Tensor, lw, rows: int, hint: int) -> torch.Tensor:
         n, k = lw.w.shape[1], x.shape[1]
-        q4 = lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and \
-            x.dtype == torch.float16 and k % 64 == 0
-        w = lw.w if (q4 or lw.kind == "dense") else lw.dense(x.dtype)
+        q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+        w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
         y = torch.empty(rows, n, dtype=x.dtype, device=x.device)
         rc = lib().mlcb_gemm_grouped_table(
-            ptr(x), ptr(w), ptr(lw.scale) if q4 else ptr(None), ptr(y), ptr(self.group_begin),
+            ptr(x), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(self.group_begin),
             ptr(self.group_count), ptr(self.group_slab), ctypes.c_int(self.world * self.e_local),
             ctypes.c_int(self.e_local), ctypes.c_int(rows), ctypes.c_int(hint), ctypes.c_int(n), ctypes.c_int(k),
             ctypes.c_int(x.stride(0)), ctypes.c_int(n), ctypes.c_int(DTYPE_CODE[x.dtype]),

@@ -144,11 +144,10 @@ class FusedCollectives:
     def _launch(self, x: torch.Tensor, lw: LinearWeight, y: Optional[torch.Tensor], n: int, od: torch.dtype,
                 args: FusedArgs, bias: bool) -> None:
         m, k = x.shape
-        q4 = lw.kind == "q4" and lw.quant.bits == 4 and lw.quant.group_size == 32 and \
-            x.dtype == torch.float16 and k % 64 == 0
-        w = lw.w if q4 else lw.dense(x.dtype)
+        q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+        w = lw.q4_tiles() if q4 else lw.dense(x.dtype)
         rc = lib().mlcb_gemm_fused(
-            ptr(x), ptr(w), ptr(lw.scale) if q4 else ptr(None), ptr(lw.bias) if bias else ptr(None), ptr(y),
+            ptr(x), ptr(w), ptr(w) if q4 else ptr(None), ptr(lw.bias) if bias else ptr(None), ptr(y),
             ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k), ctypes.c_int(x.stride(0)), ctypes.c_int(n),
             ctypes.c_int(DTYPE_CODE[x.dtype]), ctypes.c_int(DTYPE_CODE[od]), ptr(status_word(x.device)),
             *_gemm_scratch(x.device), ctypes.byref(args), stream_ptr())

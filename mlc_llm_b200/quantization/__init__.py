@@ -185,6 +185,34 @@ def from_device_layout_q4(qw: torch.Tensor) -> torch.Tensor:
     return out.to(torch.int32)
 
 
+Q4_TILE_ROWS, Q4_TILE_K, Q4_TILE_BYTES = 128, 64, 128 * 32 + 128 * 4
+
+
+def to_tiled_q4(qw_dev: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Tile records of the tensor-core GEMM: ``qw_dev [..., N, K/8]`` (int32, device nibble order) and
+    ``scale [..., N, K/32]`` (fp16) become ``uint8 [R/128, K/64, 4608]`` where ``R`` is the number of
+    rows of all leading slabs stacked (padded to a multiple of 128 with zero scales).  One record holds
+    one 128-row x 64-k block: ``[2 halves][128 rows][16 bytes of nibbles]`` followed by
+    ``[128 rows][2 fp16 scales]``, so that the kernel streams a whole K sweep of a row block as one
+    contiguous range and its threads read shared memory without bank conflicts."""
+    k8 = qw_dev.shape[-1]
+    if k8 % 8 != 0 or scale.shape[-1] * 4 != k8:
+        raise ValueError("tiled int4 layout needs K to be a multiple of 64 and one scale per 32 weights")
+    qw2 = qw_dev.reshape(-1, k8)
+    sc2 = scale.reshape(-1, scale.shape[-1]).to(torch.float16)
+    rows = qw2.shape[0]
+    pad = (-rows) % Q4_TILE_ROWS
+    if pad:
+        qw2 = torch.nn.functional.pad(qw2, (0, 0, 0, pad))
+        sc2 = torch.nn.functional.pad(sc2, (0, 0, 0, pad))
+    nb, kb = qw2.shape[0] // Q4_TILE_ROWS, k8 // 8
+    nib = qw2.reshape(nb, Q4_TILE_ROWS, kb, 2, 4).permute(0, 2, 3, 1, 4).contiguous()
+    nib = nib.view(torch.uint8).reshape(nb, kb, Q4_TILE_ROWS * 32)
+    scl = sc2.reshape(nb, Q4_TILE_ROWS, kb, 2).permute(0, 2, 1, 3).contiguous()
+    scl = scl.view(torch.uint8).reshape(nb, kb, Q4_TILE_ROWS * 4)
+    return torch.cat([nib, scl], dim=-1).contiguous()
+
+
 # ----------------------------------------------------------------------------- fp8
 FP8_MAX = {"float8_e4m3fn": 448.0, "float8_e5m2": 57344.0}
 _FP8_DT = {"float8_e4m3fn": torch.float8_e4m3fn, "float8_e5m2": torch.float8_e5m2}

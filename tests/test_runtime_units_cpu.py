@@ -414,3 +414,40 @@ def test_reference_module_paths_and_stream_output_unpack():
     assert last.unpack()[1][0].request_final_usage_json_str == "{}"
     cfg = {"model_config": {"vision_config": {"image_size": 336, "patch_size": 14}}}
     assert data.ImageData.get_embed_size(cfg) == 576 and data.ImageData.get_input_size(cfg) == 336
+
+
+def test_q4_tile_records_decode_to_the_dequantised_weight():
+    """The GPU GEMM's int4 tile records, decoded on the host exactly as the kernel's dequant threads do
+    (two 16-byte nibble words and one scale pair per row and K block; nibble q under exponent 0x6400 is
+    1024 + q, under 0x5400 it is 64 + q), give back ``(q - 7) * scale``."""
+    import numpy as np
+
+    from mlc_llm_b200 import quantization as Q
+
+    torch.manual_seed(3)
+    quant = Q.get("q4f16_1")
+    n, k = 200, 192                       # rows pad to 256: two row blocks, three K blocks
+    w = (torch.randn(n, k) * 0.05).half()
+    qw, qs = Q.group_quantize(w, quant)
+    want = Q.group_dequantize(qw, qs, quant, k=k).float().numpy()
+    tiles = Q.to_tiled_q4(Q.to_device_layout_q4(qw), qs)
+    assert tuple(tiles.shape) == (2, 3, Q.Q4_TILE_BYTES) and tiles.dtype == torch.uint8
+    raw = tiles.numpy()
+    got = np.zeros((256, k), dtype=np.float32)
+    for nb in range(2):
+        for kb in range(3):
+            rec = raw[nb, kb]
+            nib = rec[:4096].view(np.uint32).reshape(2, 128, 4)
+            scl = rec[4096:].view(np.float16).reshape(128, 2)
+            for half in range(2):
+                x = nib[half].astype(np.uint32)                    # [128 rows, 4 words]
+                y = x >> np.uint32(8)
+                v = np.stack([(x & 0x000F000F) | 0x64006400, (x & 0x00F000F0) | 0x54005400,
+                              (y & 0x000F000F) | 0x64006400, (y & 0x00F000F0) | 0x54005400], axis=-1)
+                h = v.astype(np.uint32).view(np.float16).reshape(128, 4, 4, 2).astype(np.float32)
+                h[:, :, 0::2, :] -= 1031.0
+                h[:, :, 1::2, :] -= 71.0
+                vals = h.reshape(128, 32) * scl[:, half:half + 1].astype(np.float32)
+                got[nb * 128:(nb + 1) * 128, kb * 64 + half * 32: kb * 64 + half * 32 + 32] = vals
+    assert np.array_equal(got[:n].astype(np.float16), want.astype(np.float16))
+    assert not got[n:].any()               # padding rows decode to zero
