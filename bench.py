@@ -210,6 +210,9 @@ def main(argv=None) -> int:
     value = toks / (total_ms / 1e3)
     steps_per_pass = json.loads(eng.debug_stats())
     engine_steps = steps_per_pass["num_prefill_steps"] + steps_per_pass["num_decode_steps"]
+    # the native engine's own split of a decode step's host time (ms per decode step, all passes so far)
+    native_ms = {k: round(v * 1e3 / max(1, steps_per_pass["num_decode_steps"]), 3)
+                 for k, v in steps_per_pass.get("decode_host_seconds", {}).items()}
 
     # ------------------------------------------------------------------ end to end, public API
     e2e = None
@@ -274,7 +277,7 @@ def main(argv=None) -> int:
                    "kv_page": 16, "kv_dtype": "fp16", "sampling": "greedy, ignore_eos"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "engine_steps_per_pass": engine_steps // max(1, args.warmup + args.steps),
-        "host_ms_per_engine_step": host_ms,
+        "host_ms_per_engine_step": host_ms, "native_engine_ms_per_decode_step": native_ms,
     }
     print(json.dumps(line))
     if comm is not None:

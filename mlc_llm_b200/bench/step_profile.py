@@ -74,7 +74,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = preset)")
     ap.add_argument("--out", default="")
     args = ap.parse_args(argv)
-    dev = torch.device("cuda")
+    dev = torch.device("cuda", 0)
     hf = dict(MODEL_PRESETS[args.model])
     if args.layers:
         hf["num_hidden_layers"] = args.layers
@@ -146,9 +146,11 @@ def main(argv=None):
     torch.cuda.synchronize()
     report["decode_untimed_ops"] = {"device_ms_per_step": s.elapsed_time(e) / 5,
                                     "wall_ms_per_step": (time.perf_counter() - t0) * 1e3 / 5}
+    graphs, ex.use_graphs = ex.use_graphs, False  # a graph replay would hide the operators from the timer
     timer.enabled = True
     decode_step()
     timer.enabled = False
+    ex.use_graphs = graphs
     report["decode"] = {"batch": args.batch, "ctx": args.ctx,
                         "kernel_ms_sum": round(sum(timer.totals.values()), 3),
                         "ops": {k: [round(v, 3), timer.counts[k]] for k, v in

@@ -68,6 +68,7 @@ struct GemmParams {
   int ab_fmt;           // 0 fp16, 1 bf16
   int splits;           // split-K factor (1 = none)
   int kb_per_split;     // K blocks handled by one work item
+  int cluster_split;    // split-K siblings form one thread-block cluster and reduce through distributed shared memory
   int nst;              // ring depth: as many (activation tile + 16 KiB weight tile) stages as fit, even, <= MAX_NST
   float* workspace;     // [tiles, splits, tn, BM] fp32 partial sums (split-K only)
   int* counters;        // [tiles] arrival counters, zero between launches (split-K only)
@@ -405,7 +406,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   uint64_t* acc_full = raw_empty + RAW_STAGES; // [2]
   uint64_t* acc_empty = acc_full + 2;          // [2]
   uint64_t* ep_bar = acc_empty + 2;            // [2] epilogue-group sync for the split-K reduction
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ep_bar + 2);
+  uint64_t* cl_bar = ep_bar + 2;               // [2] cluster split-K: all partial sums parked / all reducers done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cl_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -414,24 +416,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   if (threadIdx.x == 0) GEMM_TRACE(7, 510);
   __shared__ int sh_num_items;
 
-  if (threadIdx.x == 0) {
-    // pair mode: the leader's barriers also collect the peer CTA's arrivals
-    for (int s = 0; s < NST; ++s) {
+  if (threadIdx.x < 32) {
+    // one lane per barrier index (pair mode: the leader's barriers also collect the peer CTA's arrivals)
+    const int i = threadIdx.x;
+    if (i < NST) {
       // full[s]: the producer's expect_tx arrival plus, with a dequant stage, one arrival per dequant warp
       // (of both CTAs in pair mode, where the leader's barrier collects everything)
-      mbar_init(&full[s], Q4 ? (TWO ? 9 : 5) : 1);
-      mbar_init(&empty[s], 1);
-      mbar_init(&deq_full[s], 1);  // unused
+      mbar_init(&full[i], Q4 ? (TWO ? 9 : 5) : 1);
+      mbar_init(&empty[i], 1);
     }
-    for (int s = 0; s < RAW_STAGES; ++s) {
-      mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 4);
+    if (i < RAW_STAGES) {
+      mbar_init(&raw_full[i], 1);
+      mbar_init(&raw_empty[i], 4);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], TWO ? 8 : 4);
-      mbar_init(&ep_bar[a], 4);
+    if (i < 2) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], TWO ? 8 : 4);
+      mbar_init(&ep_bar[i], 4);
+      mbar_init(&cl_bar[i], p.cluster_split ? p.splits : 1);
     }
+    mbar_fence_init();
+  }
+  if (threadIdx.x == 0) {
     *abort_flag = 0;
     if (p.group_offsets) {
       int mbs = 0;
@@ -443,7 +449,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
     } else {
       sh_num_items = p.num_m_blocks * feature_blocks_per_item(p) * p.splits;
     }
-    mbar_fence_init();
   }
   if (warp == W_MMA) {
     if (TWO) {
@@ -456,7 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
-  if (TWO) cluster_sync_all();  // both CTAs' barriers and TMEM exist before anyone signals the peer
+  if (TWO || p.cluster_split) cluster_sync_all();  // every CTA's barriers (and TMEM) exist before anyone signals a peer
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_tiles = sh_num_items;  // work items
@@ -702,7 +707,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
-        if (threadIdx.x == 64 && it < 500) GEMM_TRACE(7, it);
+        if (threadIdx.x == 64 && it >= 8 && it < 500) GEMM_TRACE(7, it);
         uint8_t* dst_row = sw + s * W_STAGE_BYTES + row * 128;
         if constexpr (WF == 2) {
           const float fs = __uint_as_float(sc_bits);
@@ -778,7 +783,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
       }
     }
-  } else if (warp >= W_EPI0 && warp < W_EPI0 + 4) {
+  } else if (warp >= W_EPI0 && warp < W_EPI0 + 4 && !p.cluster_split) {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tile_i = 0;
@@ -888,19 +893,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             float4 acc[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) acc[u] = make_float4(b4[0], b4[1], b4[2], b4[3]);
-            for (int s2 = 0; s2 < p.splits; ++s2) {
-              const float* src = ws_tile + (static_cast<size_t>(s2) * p.tn) * BM + f4;
-              float4 v[4];
+            // sixteen loads (four siblings x four tokens) in flight before the first sum
+            for (int s0 = 0; s0 < p.splits; s0 += 4) {
+              float4 v[4][4];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int j = j0 + 4 * u;
-                v[u] = j < j_end ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(j) * BM))
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int ds = 0; ds < 4; ++ds) {
+                const bool s_ok = s0 + ds < p.splits;
+                const float* src = ws_tile + (static_cast<size_t>(s_ok ? s0 + ds : 0) * p.tn) * BM + f4;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int j = j0 + 4 * u;
+                  v[ds][u] = (s_ok && j < j_end) ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(j) * BM))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
               }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
-              }
+              for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  acc[u].x += v[ds][u].x; acc[u].y += v[ds][u].y; acc[u].z += v[ds][u].z; acc[u].w += v[ds][u].w;
+                }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -983,6 +995,140 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) release_acc(a);
       if (threadIdx.x == W_EPI0 * 32) GEMM_TRACE(7, tile_i);
+    }
+  }
+
+  // ------------------------------------------------------------ split-K inside a thread-block cluster
+  // The siblings of a tile are the CTAs of one cluster (cluster rank = split index), one work item
+  // each. Once its main loop is done every warp of a CTA helps: the partial sums go from TMEM to the
+  // CTA's own shared memory (the rings are idle by then), and each CTA reduces its share of the tile's
+  // tokens by reading every sibling's copy through distributed shared memory. No global scratch, no
+  // global-memory flags; remote shared memory answers slowly, so many warps keep many loads in flight.
+  if (p.cluster_split) {
+    constexpr int NW = Q4 ? 16 : 8;  // participating warps: the same number for each TMEM lane quarter
+    __syncwarp();
+    bool ok = true;
+    const int t = work_id(p);
+    const bool have = t < num_tiles;  // every CTA of the cluster has an item (grid = tiles * splits)
+    const int sp = have ? t % p.splits : 0;
+    TileInfo ti = {};
+    if (have) ti = decode_tile(p, t / p.splits);
+    float* stage = reinterpret_cast<float*>(smem);  // [token][feature] fp32, tn x 128
+    if (have && warp < NW) {
+      ok = mbar_wait(&acc_full[0], 0, abort_flag, p.status, ERR_WAIT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        const int q = warp & 3, g = warp >> 2;
+        const int row = q * 32 + lane;
+        for (int c = g * 32; c < p.tn; c += (NW / 4) * 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j < p.tn) stage[(c + j) * BM + row] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+      }
+    }
+    if (threadIdx.x == 0) GEMM_TRACE(7, 2);
+    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int r2 = 0; r2 < p.splits; ++r2) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[0]), r2));
+    if (have && warp < NW) {
+      const bool got = mbar_wait_cluster(&cl_bar[0], 0, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, got && ok && *abort_flag == 0);
+      if (threadIdx.x == 0) GEMM_TRACE(7, 3);
+      if (ok) {
+        const int nb = ti.nb, m0 = ti.x_row;
+        const int jmax = ti.m_valid;
+        int per = (jmax + p.splits - 1) / p.splits;
+        if (p.rs_world) per = (per + 31) & ~31;  // whole 32-token chunks, so each chunk has one reducing CTA
+        const int j_begin = min(jmax, sp * per);
+        const int j_end = min(jmax, j_begin + per);
+        const int f4 = lane * 4;                 // feature offset inside the tile
+        const int n4 = nb * BM + f4;             // first output feature of this thread
+        float b4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.bias) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (n4 + u < p.N)
+              b4[u] = p.ab_fmt == 0 ? __half2float(reinterpret_cast<const __half*>(p.bias)[n4 + u])
+                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n4 + u]);
+        }
+        const uint32_t stage_u32 = smem_u32(stage) + f4 * 4;
+        // warp w takes tokens j_begin + w, + NW, ...; four tokens x four siblings = sixteen loads in flight
+        for (int j0 = j_begin + warp; j0 < j_end; j0 += 4 * NW) {
+          float4 acc[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[u] = make_float4(b4[0], b4[1], b4[2], b4[3]);
+          for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float4 v[4][4];
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds) {
+              const bool s_ok = s0 + ds < p.splits;
+              const uint32_t src = mapa_u32(stage_u32, s_ok ? s0 + ds : 0);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = j0 + NW * u;
+                v[ds][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (s_ok && j < j_end)
+                  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                               : "=f"(v[ds][u].x), "=f"(v[ds][u].y), "=f"(v[ds][u].z), "=f"(v[ds][u].w)
+                               : "r"(src + static_cast<uint32_t>(j) * (BM * 4)));
+              }
+            }
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                acc[u].x += v[ds][u].x; acc[u].y += v[ds][u].y; acc[u].z += v[ds][u].z; acc[u].w += v[ds][u].w;
+              }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j0 + NW * u;
+            if (j >= j_end) continue;
+            const int esize = p.out_dtype == 2 ? 4 : 2;
+            char* rowp = out_row_ptr(p, m0 + j, esize);
+            const float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+            if (n4 + 3 < p.N && (p.ldy & 3) == 0) {
+              if (p.out_dtype == 0) {
+                __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
+                uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(rowp) + n4) = pk;
+              } else if (p.out_dtype == 1) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+                uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(rowp) + n4) = pk;
+              } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(rowp) + n4) = acc[u];
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (n4 + e >= p.N) continue;
+                if (p.out_dtype == 0) store_out<__half>(rowp, n4 + e, o[e]);
+                else if (p.out_dtype == 1) store_out<__nv_bfloat16>(rowp, n4 + e, o[e]);
+                else store_out<float>(rowp, n4 + e, o[e]);
+              }
+            }
+          }
+        }
+        if (p.rs_world && j_end > j_begin)
+          rs_signal_chunks(p, (m0 + j_begin) >> 5, (j_end - j_begin + 31) >> 5, p.num_n_blocks * NW, lane);
+      }
+    }
+    if (threadIdx.x == 0) GEMM_TRACE(7, 4);
+    // A CTA's shared memory must outlive its siblings' reads: every CTA reports when it has finished
+    // reading (a CTA that gave up reports as well) and waits for all reports before it leaves.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int r2 = 0; r2 < p.splits; ++r2) mbar_arrive_cluster(mapa_u32(smem_u32(&cl_bar[1]), r2));
+      mbar_wait_cluster(&cl_bar[1], 0, abort_flag, p.status, ERR_WAIT_EPILOGUE);
+      GEMM_TRACE(7, 5);
     }
   }
 
@@ -1159,6 +1305,18 @@ static bool pair_mode_enabled(int wf) {
 // Test hook: 1 = every format, 0 = off, 2 = default policy.
 MLCB_API void mlcb_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 
+// Split-K reduction inside thread-block clusters (MLCB_GEMM_CLUSTER_SPLIT=0 falls back to the
+// reduction through global scratch, which the CTA-pair kernels and the allocation-free entry point use).
+static int g_cluster_split = -1;
+static bool cluster_split_enabled() {
+  if (g_cluster_split < 0) {
+    const char* e = getenv("MLCB_GEMM_CLUSTER_SPLIT");
+    g_cluster_split = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_cluster_split == 1;
+}
+MLCB_API void mlcb_gemm_set_cluster_split(int on) { g_cluster_split = on ? 1 : 0; }
+
 static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
                        int* status, float* workspace, long long workspace_bytes, int* counters,
@@ -1291,6 +1449,28 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   }
   int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.splits > 1 && cluster_split_enabled()) {
+    // the `splits` siblings of a tile are consecutive work items: one cluster each, reduced on chip
+    p.cluster_split = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles);
+    cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err;
+    if (q4) err = cudaLaunchKernelEx(&cfg, gemm_kernel<1, false>, *mx, *mw, p);
+    else if (wf == 2) err = cudaLaunchKernelEx(&cfg, gemm_kernel<2, false>, *mx, *mw, p);
+    else err = cudaLaunchKernelEx(&cfg, gemm_kernel<0, false>, *mx, *mw, p);
+    count_launch();
+    return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
+  }
   if (q4)
     gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else if (wf == 2)
