@@ -1317,6 +1317,40 @@ static bool cluster_split_enabled() {
 }
 MLCB_API void mlcb_gemm_set_cluster_split(int on) { g_cluster_split = on ? 1 : 0; }
 
+// How many clusters of `size` CTAs of the single-CTA kernel the current device holds at once (cached).
+static int max_active_clusters(int wf, int size) {
+  static int cache[64][3][9] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (size < 1 || size > 8) return 0;
+  int& slot = cache[dev][wf][size];
+  if (slot == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(size * 64);
+    cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t err = wf == 1   ? cudaOccupancyMaxActiveClusters(&n, gemm_kernel<1, false>, &cfg)
+                      : wf == 2 ? cudaOccupancyMaxActiveClusters(&n, gemm_kernel<2, false>, &cfg)
+                                : cudaOccupancyMaxActiveClusters(&n, gemm_kernel<0, false>, &cfg);
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    slot = n > 0 ? n : -1;
+  }
+  return slot > 0 ? slot : 0;
+}
+MLCB_API int mlcb_gemm_max_active_clusters(int wf, int size) { return max_active_clusters(wf, size); }
+
 static int gemm_launch(const void* x, const void* w, const void* scale, const void* bias, void* y,
                        int M, int N, int K, int ldx, int ldy, int ab_fmt, int out_dtype,
                        int* status, float* workspace, long long workspace_bytes, int* counters,
@@ -1447,9 +1481,22 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     count_launch();
     return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
   }
+  // Clusters of `splits` CTAs: only as many as the GPU can hold at once (the clusters of a second wave
+  // would double the run time); with fewer, split less or fall back to the reduction through global scratch.
+  if (p.splits > 1 && cluster_split_enabled()) {
+    const int out_tiles = p.num_m_blocks * p.num_n_blocks;
+    const int total_kb = (K + BK - 1) / BK;
+    int sp = p.splits;
+    while (sp > 1 && max_active_clusters(wf, sp) < out_tiles) --sp;
+    if (sp > 1 && sp != p.splits) {
+      p.kb_per_split = (total_kb + sp - 1) / sp;
+      p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+    }
+    if (sp <= 1 || max_active_clusters(wf, p.splits) < out_tiles) p.cluster_split = -1;  // not this time
+  }
   int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
-  if (p.splits > 1 && cluster_split_enabled()) {
+  if (p.splits > 1 && cluster_split_enabled() && p.cluster_split == 0) {
     // the `splits` siblings of a tile are consecutive work items: one cluster each, reduced on chip
     p.cluster_split = 1;
     cudaLaunchConfig_t cfg = {};
@@ -1471,6 +1518,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     count_launch();
     return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
   }
+  p.cluster_split = 0;
   if (q4)
     gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else if (wf == 2)
