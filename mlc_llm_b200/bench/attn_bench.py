@@ -10,7 +10,7 @@ import torch
 
 from .. import ops
 from ..ops.attention import AttentionPlan, build_tiles, choose_splits
-from .kernel_bench import _peaks, _time
+from .kernel_bench import _peaks, _time, _time_graph
 
 
 def _plan(batch: int, ctx: int, append: int, hq: int, hkv: int, dev) -> AttentionPlan:
@@ -50,6 +50,7 @@ def bench_attention(which: str, small: bool):
         fn = lambda: ops.paged_attention(q[:, : hq * d], kv, q_seq, plan.q_kvlen, plan.page_indptr,
                                          plan.page_indices, hq, hkv, d, 16, d ** -0.5, plan=plan)
         med, best = _time(fn)
+        in_graph = _time_graph(fn)   # the kernel alone: the eager figure carries the host's launch time
         ops.check_status(dev)
         kv_bytes = pages * 2 * hkv * 16 * d * 2
         if kind == "attn_decode":
@@ -60,7 +61,8 @@ def bench_attention(which: str, small: bool):
         roof_ms = max(flops / (tf * 1e12), byt / (hbm * 1e9)) * 1e3
         rec = {"kernel": kind, "batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "ms_median": round(med, 4),
                "ms_best": round(best, 4), "tflops": round(flops / med / 1e9, 1),
-               "gbs": round(byt / med / 1e6, 1), "frac_of_roofline": round(roof_ms / med, 3), "peaks": how}
+               "gbs": round(byt / med / 1e6, 1), "frac_of_roofline": round(roof_ms / med, 3), "ms_in_graph": round(in_graph, 4),
+               "frac_of_roofline_in_graph": round(roof_ms / in_graph, 3), "peaks": how}
         print(json.dumps(rec), flush=True)
         out.append(rec)
         del kv, q

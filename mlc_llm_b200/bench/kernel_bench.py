@@ -47,6 +47,31 @@ def _time(fn, iters=10, warmup=3, flush=None):
     return times[len(times) // 2], times[0]
 
 
+def _time_graph(fn, reps: int = 5, replays: int = 3) -> float:
+    """Milliseconds per call with the host out of the picture: ``reps`` calls captured in one CUDA graph,
+    replayed ``replays`` times between two events.  For kernels of a few tens of microseconds the eager
+    figure of :func:`_time` includes the time the host needs to issue the launch."""
+    fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(reps):
+                fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(replays):
+        graph.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / (reps * replays)
+
+
 def bench_gemm(small: bool, q4: bool):
     dev = torch.device("cuda")
     hbm, tf, how = _peaks()

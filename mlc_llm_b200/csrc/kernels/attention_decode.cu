@@ -1,14 +1,16 @@
 // Paged-KV decode attention (head_dim 128, 16-token pages): the KV stream is the whole cost, so the
-// kernel is organised around keeping many page loads in flight per SM.
+// kernel is organised around keeping many page loads in flight per SM, without gaps.
 //
-// A CTA owns one (sequence, kv head) and at most 16 query rows -- the G = hq / hkv heads of the kv
-// group times the few tokens appended this step (1 for plain decode, up to 16 / G for short verify
-// chunks). A producer warp streams pages through an 8-deep ring with TMA tile loads (128-byte
-// swizzle; 8 KB per page: K and V of the kv head). Four consumer warps take pages round-robin, each
-// running its own online softmax over m16n8k16 tensor-core tiles (S = Q.K^T from ldmatrix'd K, then
-// O += P.V from transposed-ldmatrix'd V with P taken straight from the S accumulators), so there is
-// no block-wide synchronisation in the loop. The four partial states are merged through shared
-// memory at the end. Three CTAs fit per SM (64 KB ring each), i.e. ~190 KB of loads in flight.
+// A work unit is one (sequence, kv head, KV split) and at most 16 query rows -- the G = hq / hkv heads
+// of the kv group times the few tokens appended this step (1 for plain decode, up to 16 / G for short
+// verify chunks). CTAs are persistent (two per SM) and walk units blockIdx, blockIdx + grid, ...: a
+// producer warp streams the pages of one unit after the other through an 8-deep ring with TMA tile loads
+// (128-byte swizzle; 8 KB per page: K and V of the kv head), so the loads of the next unit are already in
+// flight while the consumers finish the current one and there is no ramp-up / drain per unit. Four
+// consumer warps take the pages round-robin, each running its own online softmax over
+// m16n8k16 tensor-core tiles (S = Q.K^T from ldmatrix'd K, then O += P.V from transposed-ldmatrix'd V
+// with P taken straight from the S accumulators), so there is no block-wide synchronisation in the page
+// loop. The four partial states of a unit are merged through a scratch area of shared memory.
 //
 // The math uses the warp-level mma path on purpose: with <= 16 query rows the 128-row tcgen05 tile
 // would spend its time on barrier round trips per KV block, while this kernel never leaves
@@ -21,10 +23,16 @@
 
 namespace mlcb {
 
+// Ring depth: a multiple of the four consumer warps. Page number g (counted over all units of the CTA)
+// goes to slot g % DEC_STAGES and to warp g % 4, so every slot is always read by the same warp, which
+// therefore sees every phase of the slot's barriers in order (a waiter that skipped a phase could take
+// an older completion of the same parity for the one it needs).
 constexpr int DEC_STAGES = 8;
+static_assert(DEC_STAGES % 4 == 0, "a ring slot must belong to one consumer warp");
 constexpr int DEC_PAGE_BYTES = 8192;  // K (2 halves x 16 rows x 128 B) + V (same)
 constexpr int DEC_THREADS = 160;
-constexpr int DEC_SMEM = DEC_STAGES * DEC_PAGE_BYTES + 1024 + 256;
+constexpr int DEC_MERGE_BYTES = 4 * 16 * 128 * 4 + 4 * 16 * 2 * 4;  // four warps' O rows and (m, l) pairs
+constexpr int DEC_SMEM = DEC_STAGES * DEC_PAGE_BYTES + DEC_MERGE_BYTES + 1024 + 256;
 
 struct DecParams {
   const void* q;          // row stride q_stride elements, head h at column h * 128
@@ -41,6 +49,7 @@ struct DecParams {
   int* status;
   long long q_stride;
   int hq, hkv, group, splits;
+  int num_units;          // items * hkv * splits
   float scale_log2;
   int is_bf16;
 };
@@ -78,72 +87,103 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// One work unit: which pages, which rows.
+struct DecUnit {
+  int item, hk, split, qstart, ntok, valid_rows, pg_begin, npg;
+  const int* pages;
+};
+__device__ __forceinline__ DecUnit dec_unit(const DecParams& p, int u) {
+  DecUnit d;
+  d.split = u % p.splits;
+  const int r = u / p.splits;
+  d.hk = r % p.hkv;
+  d.item = r / p.hkv;
+  const int b = p.item_seq[d.item];
+  d.qstart = p.item_qstart[d.item];
+  d.ntok = p.item_ntok[d.item];
+  d.valid_rows = d.ntok * p.group;
+  const int kv_max = p.q_kvlen[d.qstart + d.ntok - 1];
+  d.pages = p.page_indices + p.page_indptr[b];
+  const int total_pages = (kv_max + 15) / 16;
+  const int per_split = (total_pages + p.splits - 1) / p.splits;
+  d.pg_begin = d.split * per_split;
+  d.npg = max(0, min(total_pages, d.pg_begin + per_split) - d.pg_begin);
+  return d;
+}
+
 template <bool BF16>
-__global__ void __launch_bounds__(DEC_THREADS, 3)
+__global__ void __launch_bounds__(DEC_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + DEC_STAGES * DEC_PAGE_BYTES);
+  float* sm_o = reinterpret_cast<float*>(smem + DEC_STAGES * DEC_PAGE_BYTES);  // [4 warps][16 rows][128]
+  float* sm_ml = sm_o + 4 * 16 * 128;                                          // [4][16][2]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + DEC_STAGES * DEC_PAGE_BYTES + DEC_MERGE_BYTES);
   uint64_t* empty = full + DEC_STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DEC_STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int item = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = p.group;
-  const int b = p.item_seq[item];
-  const int qstart = p.item_qstart[item];
-  const int ntok = p.item_ntok[item];
-  const int valid_rows = ntok * G;
-  const int kv_max = p.q_kvlen[qstart + ntok - 1];
-  const int* pages = p.page_indices + p.page_indptr[b];
-  const int total_pages = (kv_max + 15) / 16;
-  const int per_split = (total_pages + p.splits - 1) / p.splits;
-  const int pg_begin = split * per_split;
-  const int pg_end = min(total_pages, pg_begin + per_split);
-  const int npg = max(0, pg_end - pg_begin);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    *abort_flag = 0;
+  if (threadIdx.x < DEC_STAGES) {
+    mbar_init(&full[threadIdx.x], 1);
+    mbar_init(&empty[threadIdx.x], 1);
     mbar_fence_init();
   }
+  if (threadIdx.x == 0) *abort_flag = 0;
   __syncthreads();
 
-  // per-warp softmax state, merged at the end (consumer warps only)
-  float o[16][4];
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
   if (warp == 4) {
-    // ---------------------------------------------------------------- producer
+    // ---------------------------------------------------------------- producer: the pages of this
+    // CTA's units back to back; `g` counts pages over all units, so the ring never drains in between
     if (lane == 0) {
       tma_prefetch_desc(&tmap_kv);
-      for (int i = 0; i < npg; ++i) {
-        const int s = i % DEC_STAGES;
-        if (i >= DEC_STAGES) {
-          if (!mbar_wait(&empty[s], ((i / DEC_STAGES) - 1) & 1, abort_flag, p.status, ERR_WAIT_PRODUCER)) break;
+      int s = 0;
+      uint32_t eph = 1;  // parity of empty[s] to wait for (first pass over the ring: nothing)
+      uint32_t g = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        const DecUnit d = dec_unit(p, u);
+        for (int i = 0; i < d.npg; ++i, ++g) {
+          if (g >= DEC_STAGES && !mbar_wait(&empty[s], eph, abort_flag, p.status, ERR_WAIT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          int page = d.pages[d.pg_begin + i];
+          if (page < 0) page = 0;
+          mbar_expect_tx(&full[s], DEC_PAGE_BYTES);
+          uint8_t* dst = smem + s * DEC_PAGE_BYTES;
+          const int krow = ((page * 2 + 0) * p.hkv + d.hk) * 16;
+          const int vrow = ((page * 2 + 1) * p.hkv + d.hk) * 16;
+          tma_load_2d(dst, &tmap_kv, &full[s], 0, krow);
+          tma_load_2d(dst + 2048, &tmap_kv, &full[s], 64, krow);
+          tma_load_2d(dst + 4096, &tmap_kv, &full[s], 0, vrow);
+          tma_load_2d(dst + 6144, &tmap_kv, &full[s], 64, vrow);
+          if (++s == DEC_STAGES) {
+            s = 0;
+            eph ^= 1;
+          }
         }
-        int page = pages[pg_begin + i];
-        if (page < 0) page = 0;
-        mbar_expect_tx(&full[s], DEC_PAGE_BYTES);
-        uint8_t* dst = smem + s * DEC_PAGE_BYTES;
-        const int krow = ((page * 2 + 0) * p.hkv + hk) * 16;
-        const int vrow = ((page * 2 + 1) * p.hkv + hk) * 16;
-        tma_load_2d(dst, &tmap_kv, &full[s], 0, krow);
-        tma_load_2d(dst + 2048, &tmap_kv, &full[s], 64, krow);
-        tma_load_2d(dst + 4096, &tmap_kv, &full[s], 0, vrow);
-        tma_load_2d(dst + 6144, &tmap_kv, &full[s], 64, vrow);
       }
     }
-  } else {
-    // ---------------------------------------------------------------- consumers
-    const int r0 = lane >> 2;       // fragment rows r0 and r0 + 8
-    const int cpair = (lane & 3) * 2;
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  const int r0 = lane >> 2;       // fragment rows r0 and r0 + 8
+  const int cpair = (lane & 3) * 2;
+  const int mi = lane >> 3, mr = lane & 7;  // ldmatrix lane roles
+  uint32_t g0 = 0;                // pages of the units before this one (ring position of the unit's page 0)
+  bool ok = true;
+  for (int u = blockIdx.x; u < p.num_units; u += gridDim.x) {
+    const DecUnit d = dec_unit(p, u);
+    const int qstart = d.qstart, hk = d.hk, valid_rows = d.valid_rows, npg = d.npg;
+    // per-warp softmax state, merged at the end of the unit
+    float o[16][4];
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     // Q fragments (A operand), 8 k-steps of 16 along head_dim
     uint32_t qa[8][4];
     {
@@ -164,12 +204,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
     }
     const int kvlen0 = r0 < valid_rows ? p.q_kvlen[qstart + r0 / G] : 0;
     const int kvlen1 = (r0 + 8) < valid_rows ? p.q_kvlen[qstart + (r0 + 8) / G] : 0;
-    // ldmatrix lane roles
-    const int mi = lane >> 3, mr = lane & 7;
-    bool ok = true;
-    for (int i = warp; i < npg && ok; i += 4) {
-      const int s = i % DEC_STAGES;
-      ok = mbar_wait(&full[s], (i / DEC_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
+    // this warp's pages of the unit: those whose number over all units is congruent to the warp index
+    for (int i = (warp - static_cast<int>(g0 & 3u)) & 3; i < npg && ok; i += 4) {
+      const uint32_t g = g0 + static_cast<uint32_t>(i);
+      const int s = g % DEC_STAGES;
+      ok = mbar_wait(&full[s], (g / DEC_STAGES) & 1, abort_flag, p.status, ERR_WAIT_TMA);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       const uint32_t kbase = smem_u32(smem + s * DEC_PAGE_BYTES);
@@ -191,7 +230,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
         }
       }
       // ---- mask + online softmax (rows r0 and r0 + 8)
-      const int pos_base = (pg_begin + i) * 16;
+      const int pos_base = (d.pg_begin + i) * 16;
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
@@ -246,26 +285,27 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }
+    g0 += static_cast<uint32_t>(npg);
     // row sums live spread over the 4 lanes of a quad
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  }
 
-  // ------------------------------------------------------------------ merge the four warps
-  // (the ring is drained: every full barrier a consumer waited on has completed)
-  __syncthreads();
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][128]
-  float* sm_ml = sm_o + 4 * 16 * 128;                           // [4][16][2]
-  if (warp < 4) {
-    const int r0 = lane >> 2, cpair = (lane & 3) * 2;
+    // ---------------------------------------------------------------- merge the four warps of the unit
+    // (named barrier over the 128 consumer threads; the producer keeps streaming the next unit's pages)
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       float* d0 = sm_o + ((warp * 16 + r0) * 128 + j * 8 + cpair);
       float* d1 = sm_o + ((warp * 16 + r0 + 8) * 128 + j * 8 + cpair);
-      d0[0] = o[j][0]; d0[1] = o[j][1];
-      d1[0] = o[j][2]; d1[1] = o[j][3];
+      if (r0 < valid_rows) {
+        d0[0] = o[j][0];
+        d0[1] = o[j][1];
+      }
+      if (r0 + 8 < valid_rows) {
+        d1[0] = o[j][2];
+        d1[1] = o[j][3];
+      }
     }
     if ((lane & 3) == 0) {
       sm_ml[(warp * 16 + r0) * 2] = m0;
@@ -273,9 +313,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
       sm_ml[(warp * 16 + r0 + 8) * 2] = m1;
       sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = l1;
     }
-  }
-  __syncthreads();
-  if (warp < 4) {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
     // warp w finalises rows w, w + 4, ...; lane handles 4 consecutive head_dim elements
     for (int row = warp; row < valid_rows; row += 4) {
       float M = -INFINITY;
@@ -296,7 +334,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
       }
       const int tok = qstart + row / G, head = hk * G + row % G;
       if (p.splits > 1) {
-        const size_t base = ((static_cast<size_t>(item) * p.hkv + hk) * p.splits + split) * 16 + row;
+        const size_t base = ((static_cast<size_t>(d.item) * p.hkv + hk) * p.splits + d.split) * 16 + row;
         *reinterpret_cast<float4*>(p.part_o + base * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         if (lane == 0) {
           p.part_ml[base * 2] = M;
@@ -314,6 +352,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
               L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
       }
     }
+    // the scratch area is rewritten by the next unit; after the barrier all four warps read the same
+    // abort flag, so they leave together if any wait of any of them ran out
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*abort_flag) break;
+    ok = true;
   }
 }
 
@@ -403,7 +446,9 @@ MLCB_API int mlcb_attn_decode(const void* q, const void* kv_pages, void* out, fl
   p.splits = splits;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.is_bf16 = dtype == 1;
-  dim3 grid(num_items, hkv, splits);
+  p.num_units = num_items * hkv * splits;
+  const int max_ctas = 2 * sm_count();
+  dim3 grid(p.num_units < max_ctas ? p.num_units : max_ctas);
   if (dtype == 1)
     attn_decode_kernel<true><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
   else

@@ -192,6 +192,21 @@ __global__ void row_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __rest
 }
 
 // Copies whole KV pages (all layers are handled by the caller looping or by a large row): used for
+// tok[i] = last[src[i]] where src[i] >= 0 (deferred-read decode steps: the tokens one step sampled are
+// the next step's inputs and stay on the device). A source row outside `last` is reported, not read.
+__global__ void token_feed_kernel(int* __restrict__ tok, const int* __restrict__ src, const int* __restrict__ last,
+                                  int n, int n_last, int* __restrict__ status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = src[i];
+  if (s < 0) return;
+  if (s >= n_last) {
+    if (status) atomicCAS(status, 0, static_cast<int>(ERR_BAD_INDEX));
+    return;
+  }
+  tok[i] = last[s];
+}
+
 // copy-on-write of a partially filled last page when a sequence is forked.
 __global__ void page_copy_kernel(uint8_t* __restrict__ pages, const int* __restrict__ src_dst,
                                  size_t page_bytes, size_t layer_stride, int pairs) {
@@ -312,6 +327,14 @@ MLCB_API int mlcb_wkv5(const float* r, const float* k, const float* v, const flo
 
 // Lets kernels running on `device` dereference memory of `peer` (both in this process's view).
 // Returns 0 when access is (already) enabled.
+MLCB_API int mlcb_token_feed(int* tok, const int* src, const int* last, int n, int n_last, int* status,
+                             cudaStream_t stream) {
+  if (n <= 0) return 0;
+  token_feed_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tok, src, last, n, n_last, status);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
 MLCB_API int mlcb_enable_peer_access(int device, int peer) {
   if (device == peer) return 0;
   int can = 0;

@@ -98,6 +98,27 @@ class PyModelBackend : public ModelBackend {
     if (d.contains("top_probs")) out.top_probs = FromArray<float>(d["top_probs"]);
     return out;
   }
+  static SampleOutput SampleFromDict(const py::object& res) {
+    SampleOutput out;
+    if (res.is_none()) return out;
+    py::dict d = res.cast<py::dict>();
+    out.tokens = FromArray<int32_t>(d["tokens"]);
+    if (d.contains("probs")) out.probs = FromArray<float>(d["probs"]);
+    if (d.contains("top_tokens")) out.top_tokens = FromArray<int32_t>(d["top_tokens"]);
+    if (d.contains("top_probs")) out.top_probs = FromArray<float>(d["top_probs"]);
+    return out;
+  }
+  bool LaunchSample(int model_id, const ForwardPlan& plan, const std::vector<int32_t>& token_ids,
+                    const std::vector<int32_t>& token_src, const SampleParams& sampling) override {
+    py::gil_scoped_acquire gil;
+    if (!py::hasattr(impl_, "forward_sample_launch")) return false;
+    return impl_.attr("forward_sample_launch")(model_id, PlanToDict(plan), ToArray(token_ids), ToArray(token_src),
+                                               SampleParamsToDict(sampling)).cast<bool>();
+  }
+  SampleOutput WaitSample(int model_id) override {
+    py::gil_scoped_acquire gil;
+    return SampleFromDict(impl_.attr("forward_sample_wait")(model_id));
+  }
   VerifyOutput ForwardVerify(int model_id, const ForwardPlan& plan, const std::vector<int32_t>& token_ids,
                              const VerifyParams& v) override {
     py::gil_scoped_acquire gil;

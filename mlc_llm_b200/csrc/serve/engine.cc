@@ -1,6 +1,7 @@
 #include "engine.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cmath>
 #include <sstream>
 #include <stdexcept>
@@ -100,6 +101,7 @@ class EngineImpl : public Engine {
       if (v.is_object()) default_gen_ = GenerationConfig::DefaultsFromModelConfig(v.as_object());
     }
     spec_ = cfg_.speculative_mode != SpeculativeMode::kDisable && models_.size() > 1;
+    if (const char* env = std::getenv("MLCB_PIPELINED_DECODE")) pipelined_decode_ = env[0] != '0';
     feature_fed_draft_ = cfg_.speculative_mode == SpeculativeMode::kEagle ||
                          cfg_.speculative_mode == SpeculativeMode::kMedusa;
     if (spec_) draft_slots_.Resize(static_cast<int>(cfg_.max_num_sequence) * DraftSlotsPerSequence());
@@ -117,6 +119,8 @@ class EngineImpl : public Engine {
     Object o;
     o["num_prefill_steps"] = num_prefill_steps_;
     o["num_decode_steps"] = num_decode_steps_;
+    o["num_pipelined_decode_steps"] = num_pipelined_steps_;
+    o["num_dropped_pipelined_tokens"] = num_dropped_tokens_;
     o["num_verify_steps"] = num_verify_steps_;
     o["num_preemptions"] = num_preemptions_;
     o["num_running"] = static_cast<int64_t>(running_.size());
@@ -363,13 +367,26 @@ class EngineImpl : public Engine {
     auto it = states_.find(request_id);
     if (it == states_.end()) return;
     RequestState* rs = it->second.get();
+    ForgetInflight(rs);
     Trace(request_id, "abort");
     for (auto& e : rs->entries) ReleaseEntry(e, /*recycle=*/false);
     RemoveFromQueues(rs);
     states_.erase(it);
   }
 
+  // A decode step whose result was never read is read and thrown away (its requests are gone).
+  void DiscardInflightDecode() {
+    if (inflight_.active && backend_) {
+      try {
+        backend_->WaitSample(0);
+      } catch (...) {  // the step itself may be what failed
+      }
+    }
+    inflight_ = InflightDecode();
+  }
+
   void AbortAllRequests() override {
+    DiscardInflightDecode();
     std::vector<std::string> ids;
     for (auto& kv : states_) ids.push_back(kv.first);
     for (auto& id : ids) AbortRequest(id);
@@ -390,10 +407,20 @@ class EngineImpl : public Engine {
 
   void Step() override {
     touched_.clear();
+    // A decode step whose tokens have not been read yet is finished first whenever the next thing to do
+    // is not another plain decode step (new requests to prefill, forced tokens, ...).
+    if (inflight_.active && !PipelinedDecodePossible()) {
+      FinishInflightDecode();
+      const double t0 = NowSeconds();
+      PostProcess();
+      t_post_ += NowSeconds() - t0;
+      return;
+    }
     StepJumpForward();
-    bool did = StepPrefill();
+    bool did = inflight_.active ? false : StepPrefill();
     if (!did) {
       if (spec_) did = StepSpecDecode();
+      else if (PipelinedDecodePossible()) did = StepDecodePipelined();
       else did = StepDecode();
     }
     if (did) {
@@ -906,8 +933,157 @@ class EngineImpl : public Engine {
     return false;
   }
 
+  // ---------------------------------------------------------------- pipelined decode
+  // Plain decode steps overlap the host with the device: step n + 1 is planned and queued while step n
+  // still runs, its input tokens being the tokens step n samples, which stay on the device; step n's
+  // tokens reach the host (and the request's stream) while step n + 1 runs. A sequence that turns out
+  // to have ended with step n (stop token, stop string) has then been scheduled once too often: the
+  // extra token is dropped and its KV entry goes away with the sequence. Ends by length are known in
+  // advance and are not scheduled again. Anything that needs the newest token on the host before the
+  // next step can be planned (grammar masks, repetition penalties, speculative decoding, forced
+  // tokens, a second model) takes the ordinary synchronous path.
+  struct InflightRow {
+    RequestState* rs;  // null once the request was aborted
+    int idx;
+  };
+  struct InflightDecode {
+    bool active = false;
+    std::vector<InflightRow> rows;
+    int num_top_logprobs = 0;
+    double t_launch = 0;
+  };
+
+  // The request object goes away: whatever the unread step still samples for it is dropped on arrival.
+  void ForgetInflight(const RequestState* rs) {
+    for (auto& row : inflight_.rows)
+      if (row.rs == rs) row.rs = nullptr;
+  }
+
+  bool EntryNeedsHostToken(const RequestState& rs, const RequestStateEntry& e) const {
+    const GenerationConfig& g = rs.request.cfg;
+    return e.grammar_handle >= 0 || g.frequency_penalty != 0 || g.presence_penalty != 0 ||
+           g.repetition_penalty != 1.0 || rs.request.cfg.debug_config.disagg_config.kind != DisaggRequestKind::kNone;
+  }
+
+  bool PipelinedDecodePossible() const {
+    if (!pipelined_decode_ || pipelined_pause_ || spec_ || kv_.size() != 1 || !waiting_.empty() || running_.empty())
+      return false;
+    for (const RequestState* rs : running_) {
+      if (rs->disagg_reserved_end >= 0) return false;
+      for (const RequestStateEntry& e : rs->entries) {
+        if (e.status == EntryStatus::kPending) return false;
+        if (e.status != EntryStatus::kAlive) continue;
+        if (!e.mstates[0].inputs.empty() || EntryNeedsHostToken(*rs, e)) return false;
+      }
+    }
+    return true;
+  }
+
+  // Tokens an entry may still be scheduled for, counting the one in flight.
+  bool ReachesLengthLimit(const RequestState& rs, const RequestStateEntry& e) const {
+    const int64_t produced = static_cast<int64_t>(e.committed_tokens.size()) + (e.inflight_row >= 0 ? 1 : 0);
+    if (rs.request.cfg.max_tokens >= 0 && produced >= rs.request.cfg.max_tokens) return true;
+    return rs.request.prompt_tokens + produced >= cfg_.max_single_sequence_length;
+  }
+
+  void FinishInflightDecode() {
+    if (!inflight_.active) return;
+    const double tb = NowSeconds();
+    SampleOutput out = backend_->WaitSample(0);
+    const double tc = NowSeconds();
+    InflightDecode done = std::move(inflight_);
+    inflight_ = InflightDecode();
+    for (size_t i = 0; i < done.rows.size(); ++i) {
+      RequestState* rs = done.rows[i].rs;
+      if (rs == nullptr) {  // the request ended (or was aborted) with the step before: one token too many
+        ++num_dropped_tokens_;
+        continue;
+      }
+      RequestStateEntry& e = rs->entries[done.rows[i].idx];
+      if (e.inflight_row == static_cast<int>(i)) e.inflight_row = -1;
+      if (e.status != EntryStatus::kAlive) {  // ended with the step before: one token too many
+        ++num_dropped_tokens_;
+        continue;
+      }
+      rs->metrics.decode_tokens += 1;
+      CommitToken({rs, done.rows[i].idx},
+                  RowResult(out, static_cast<int>(i), done.num_top_logprobs, rs->request.cfg));
+    }
+    t_backend_ += tc - tb;
+    t_commit_ += NowSeconds() - tc;
+    ++num_decode_steps_;
+    ++num_pipelined_steps_;
+    const double dt = NowSeconds() - done.t_launch;
+    metrics_.engine_decode_time_sum += dt;
+    metrics_.UpdateDecodeTimeByBatchSize(static_cast<int>(done.rows.size()), dt);
+  }
+
+  bool StepDecodePipelined() {
+    const double t0 = NowSeconds();
+    std::vector<EntryRef> ready;
+    for (RequestState* rs : running_)
+      for (int i = 0; i < static_cast<int>(rs->entries.size()); ++i) {
+        RequestStateEntry& e = rs->entries[i];
+        if (e.status != EntryStatus::kAlive || !e.mstates[0].inputs.empty()) continue;
+        if (e.committed_tokens.empty() && e.inflight_row < 0) continue;
+        if (ReachesLengthLimit(*rs, e)) continue;  // its last token is in flight or waits for post-processing
+        ready.push_back({rs, i});
+      }
+    if (static_cast<int64_t>(ready.size()) > cfg_.max_num_sequence) ready.resize(cfg_.max_num_sequence);
+    bool launched = false;
+    InflightDecode next;
+    if (!ready.empty()) {
+      int64_t need = 0;
+      for (auto& r : ready) need += kv_[0]->PagesNeeded(r.e().mstates[0].internal_id, 1);
+      if (!EnsurePages(need)) {
+        // out of pages: preemption works on settled state, so settle first and let the ordinary path decide
+        FinishInflightDecode();
+        pipelined_pause_ = true;
+        return true;
+      }
+      TraceBatch(ready, "start decode");
+      std::vector<int64_t> seq_ids;
+      std::vector<int32_t> lens(ready.size(), 1), token_ids, token_src;
+      SampleParams sp;
+      for (size_t i = 0; i < ready.size(); ++i) {
+        RequestStateEntry& e = ready[i].e();
+        seq_ids.push_back(e.mstates[0].internal_id);
+        token_src.push_back(e.inflight_row);
+        token_ids.push_back(e.inflight_row >= 0 ? 0 : e.committed_tokens.back().token);
+        AddSampleRow(&sp, ready[i], static_cast<int32_t>(i));
+      }
+      const double ta = NowSeconds();
+      ForwardPlan plan = kv_[0]->BeginForward(seq_ids, lens);
+      const double tb = NowSeconds();
+      launched = backend_->LaunchSample(0, plan, token_ids, token_src, sp);
+      t_assemble_ += ta - t0;
+      t_plan_ += tb - ta;
+      t_backend_ += NowSeconds() - tb;
+      if (!launched) {
+        // the backend cannot defer this step: undo the plan, settle, and stay on the ordinary path
+        for (int64_t id : seq_ids) kv_[0]->PopN(id, 1);
+        FinishInflightDecode();
+        pipelined_decode_ = false;
+        return true;
+      }
+      next.active = true;
+      next.num_top_logprobs = sp.num_top_logprobs;
+      next.t_launch = t0;
+      for (size_t i = 0; i < ready.size(); ++i) next.rows.push_back({ready[i].rs, ready[i].idx});
+    }
+    if (!launched && !inflight_.active) return false;
+    // the step before this one: its tokens reach the host while the new step runs
+    FinishInflightDecode();
+    if (launched) {
+      for (size_t i = 0; i < next.rows.size(); ++i) next.rows[i].rs->entries[next.rows[i].idx].inflight_row = static_cast<int>(i);
+      inflight_ = std::move(next);
+    }
+    return true;
+  }
+
   bool StepDecode() {
     const double t0 = NowSeconds();
+    pipelined_pause_ = false;
     std::vector<EntryRef> ready = ReadyToDecode();
     if (ready.empty()) return false;
     if (!FitDecodeBatch(&ready, 1)) return false;
@@ -1468,6 +1644,7 @@ class EngineImpl : public Engine {
       if (rs->num_unfinished == 0) {
         Trace(req.id, "finish");
         RemoveFromQueues(rs);
+        ForgetInflight(rs);
         states_.erase(req.id);
       }
     }
@@ -1494,8 +1671,12 @@ class EngineImpl : public Engine {
   std::mt19937_64 seed_rng_;
   double t_assemble_ = 0, t_plan_ = 0, t_backend_ = 0, t_commit_ = 0, t_post_ = 0;
   bool spec_ = false;
+  bool pipelined_decode_ = true;   // MLCB_PIPELINED_DECODE=0 switches the deferred-read decode path off
+  bool pipelined_pause_ = false;   // one ordinary step is due (memory pressure) before pipelining resumes
+  InflightDecode inflight_;
   bool feature_fed_draft_ = false;  // EAGLE / Medusa: the draft head consumes the target's hidden states
   int64_t num_prefill_steps_ = 0, num_decode_steps_ = 0, num_verify_steps_ = 0, num_preemptions_ = 0;
+  int64_t num_pipelined_steps_ = 0, num_dropped_tokens_ = 0;
 };
 
 // ====================================================================== mock echo engine

@@ -121,6 +121,16 @@ class ModelBackend {
                                      const std::vector<int32_t>& token_ids,
                                      const std::vector<int64_t>& embed_handles,
                                      const SampleParams& sampling) = 0;
+  // Deferred-read form of ForwardSample for decode batches: the call returns once the work is queued.
+  // `token_src[i] >= 0` says that token i is the one sampled for row token_src[i] of the previous
+  // LaunchSample call on this model, which the backend still holds on the device (token_ids[i] is
+  // ignored then). Returns false when the backend cannot run this step that way (nothing was done).
+  virtual bool LaunchSample(int /*model_id*/, const ForwardPlan& /*plan*/, const std::vector<int32_t>& /*token_ids*/,
+                            const std::vector<int32_t>& /*token_src*/, const SampleParams& /*sampling*/) {
+    return false;
+  }
+  // Blocks for the result of the oldest LaunchSample call that has not been read yet.
+  virtual SampleOutput WaitSample(int /*model_id*/) { throw std::runtime_error("no deferred sample to wait for"); }
   // Main-model pass over draft token trees followed by on-device acceptance.
   virtual VerifyOutput ForwardVerify(int model_id, const ForwardPlan& plan,
                                      const std::vector<int32_t>& token_ids,
@@ -186,6 +196,7 @@ struct RequestStateEntry {
   std::string finish_reason;
   std::string extra_prefix_string;
   bool kv_released = false;
+  int inflight_row = -1;                    // row of this entry in the decode step whose result is not read yet
   double NextUniform() { return std::uniform_real_distribution<double>(0.0, 1.0)(rng); }
 };
 

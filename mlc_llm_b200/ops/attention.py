@@ -82,7 +82,7 @@ def choose_splits(num_items: int, hkv: int, max_pages: int, device: torch.device
     if key not in _SM_COUNT:
         _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
     ctas = num_items * hkv
-    target = 3 * _SM_COUNT[key]
+    target = 2 * _SM_COUNT[key]  # the decode kernel keeps two persistent CTAs per SM
     if ctas >= target or max_pages < 16:
         return 1
     return int(max(1, min(32, target // max(1, ctas), max_pages // 8)))

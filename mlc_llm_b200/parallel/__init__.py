@@ -27,7 +27,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-_OPS = {"forward": 1, "move": 2, "shutdown": 3, "reset": 4}
+_OPS = {"forward": 1, "move": 2, "shutdown": 3, "reset": 4, "forward_async": 5}
 _OPS_INV = {v: k for k, v in _OPS.items()}
 _DT = {np.dtype(np.int32): 0, np.dtype(np.float32): 1, np.dtype(np.int64): 2}
 _DT_INV = {0: np.int32, 1: np.float32, 2: np.int64}
@@ -80,6 +80,10 @@ class Communicator:
         self.world_group = dist.group.WORLD
         self._header = torch.zeros(_HEADER_WORDS, dtype=torch.int64,
                                    device=device if backend == "nccl" else torch.device("cpu"))
+        # Step descriptors travel over a host-side (gloo) group: a worker then receives the next step's
+        # descriptor while its GPU still runs the current step, instead of behind it in stream order.
+        self.ctl_group = dist.new_group(backend="gloo") if (backend == "nccl" and world > 1) else None
+        self._ctl_header = torch.zeros(_HEADER_WORDS, dtype=torch.int64)
         self.fused = None  # parallel.fused.FusedCollectives when enabled
         self.launches = 0
 
@@ -93,6 +97,13 @@ class Communicator:
                 dist.all_reduce(x, group=self.tp_group)
             self.launches += 1
         return x
+
+    def broadcast_tokens(self, tokens: torch.Tensor) -> None:
+        """The tokens rank 0 sampled, to every rank of its tensor-parallel group, device to device
+        (they are the next step's inputs and never visit the host on the way)."""
+        if self.tp_size > 1:
+            dist.broadcast(tokens, src=self.pp_rank * self.tp_size, group=self.tp_group)
+            self.launches += 1
 
     # ---------------------------------------------------------------- pipeline stages (NCCL p2p)
     def send_to_next_stage(self, x: torch.Tensor) -> None:
@@ -153,8 +164,13 @@ class Communicator:
             words += (w + 3) & ~3
         hdr[3] = words
         h = torch.tensor(hdr + [0] * (_HEADER_WORDS - len(hdr)), dtype=torch.int64)
-        self._header.copy_(h)
-        dist.broadcast(self._header, src=0)
+        host_side = self.ctl_group is not None or self.backend != "nccl"
+        if host_side:
+            self._ctl_header.copy_(h)
+            dist.broadcast(self._ctl_header, src=0, group=self.ctl_group)
+        else:
+            self._header.copy_(h)
+            dist.broadcast(self._header, src=0)
         if words:
             buf = np.zeros(words, dtype=np.int32)
             off = 0
@@ -165,19 +181,30 @@ class Communicator:
                     buf[off:off + w] = a.reshape(-1).view(np.int32)
                 off += (w + 3) & ~3
             t = torch.from_numpy(buf)
-            if self.backend == "nccl":
+            if host_side:
+                dist.broadcast(t, src=0, group=self.ctl_group)
+            else:
                 t = t.to(self.device, non_blocking=True)
-            dist.broadcast(t, src=0)
+                dist.broadcast(t, src=0)
 
     def receive_step(self):
         """Ranks > 0: block for the next descriptor. Returns (op, model_id, arrays)."""
-        dist.broadcast(self._header, src=0)
-        hdr = self._header.cpu().tolist()
+        host_side = self.ctl_group is not None or self.backend != "nccl"
+        if host_side:
+            dist.broadcast(self._ctl_header, src=0, group=self.ctl_group)
+            hdr = self._ctl_header.tolist()
+        else:
+            dist.broadcast(self._header, src=0)
+            hdr = self._header.cpu().tolist()
         op, model_id, count, words = _OPS_INV[hdr[0]], hdr[1], hdr[2], hdr[3]
         arrays: Dict[str, np.ndarray] = {}
         if words:
-            t = torch.empty(words, dtype=torch.int32, device=self.device if self.backend == "nccl" else "cpu")
-            dist.broadcast(t, src=0)
+            if host_side:
+                t = torch.empty(words, dtype=torch.int32)
+                dist.broadcast(t, src=0, group=self.ctl_group)
+            else:
+                t = torch.empty(words, dtype=torch.int32, device=self.device)
+                dist.broadcast(t, src=0)
             buf = t.cpu().numpy()
         else:
             buf = np.zeros(0, dtype=np.int32)
@@ -207,7 +234,7 @@ _ARRAY_NAMES = ["token_ids", "positions", "slots", "q_seq", "q_kvlen", "q_kvstar
                 "s_logit_token_index", "s_top_k", "s_pen_row", "s_pen_token", "s_pen_count", "s_bias_row",
                 "s_bias_token", "s_mask_rows", "s_mask_bits", "s_prob_slots", "s_temperature", "s_top_p",
                 "s_uniform", "s_penalties", "s_bias_value", "tile_seq", "tile_qstart", "tile_ntok", "dec_seq", "dec_qstart",
-                "dec_ntok"]
+                "dec_ntok", "token_src"]
 _NAME_ID = {n: i for i, n in enumerate(_ARRAY_NAMES)}
 _ID_NAME = dict(enumerate(_ARRAY_NAMES))
 

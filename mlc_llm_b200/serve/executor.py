@@ -114,15 +114,23 @@ class StagingBuffer:
         cap = max(n, self.capacity * 2, 1 << 12)
         self.generation = getattr(self, "generation", 0) + 1  # device addresses change: drop CUDA graphs
         pin = self.device.type == "cuda"
-        self.host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
-        self.host_np = self.host.numpy()
+        # two pinned host buffers used in turn: with deferred-read decode steps the host packs step n + 1
+        # while the copy of step n may still be queued behind step n - 1's kernels
+        self.hosts = [torch.empty(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2 if pin else 1)]
+        self.hosts_np = [h.numpy() for h in self.hosts]
+        self.turn = 0
+        self.host, self.host_np = self.hosts[0], self.hosts_np[0]
         self.dev = torch.empty(cap, dtype=torch.int32, device=self.device) if pin else self.host
         self.capacity = cap
 
     def upload(self, arrays: Dict[str, np.ndarray]) -> Dict[str, torch.Tensor]:
         total = sum(_pad4(a.size * (2 if a.dtype.itemsize == 8 else 1)) for a in arrays.values())
         if total > self.capacity:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)  # queued copies still read the old buffers
             self._grow(total)
+        self.turn = (self.turn + 1) % len(self.hosts)
+        self.host, self.host_np = self.hosts[self.turn], self.hosts_np[self.turn]
         off = 0
         layout = []
         # Fixed-size forward arrays first, the page list (the one array that grows from step to step
@@ -195,6 +203,11 @@ class ModelExecutor:
         self.host_times: Dict[str, float] = {"pack": 0.0, "broadcast": 0.0, "upload": 0.0, "forward": 0.0,
                                              "logits_sample": 0.0, "readback": 0.0, "calls": 0.0}
         self.graph_launches = 0
+        # deferred-read decode steps: tokens of the last launched step (device), results not read yet
+        self._last_tokens: Dict[int, torch.Tensor] = {}
+        self._pending: "collections.deque[dict]" = collections.deque()
+        self._readback_turn = 0
+        self._readback_bufs: List[Dict[str, torch.Tensor]] = [{}, {}]
 
     # ------------------------------------------------------------------ embeddings (multimodal)
     def _enter(self) -> None:
@@ -215,6 +228,8 @@ class ModelExecutor:
     def reset(self) -> None:
         self.embeddings.clear()
         self.features.clear()
+        self._pending.clear()
+        self._last_tokens.clear()
 
     def synchronize(self) -> None:
         if self.device.type == "cuda":
@@ -463,6 +478,117 @@ class ModelExecutor:
             self.d2h_bytes += tok.nbytes
             return {"tokens": tok, "probs": np.ones(n_rows, dtype=np.float32)}
         return self._sample(logits, dev, sp, n_rows)
+
+    # ------------------------------------------------------------------ deferred-read decode steps
+    def _feed_tokens(self, model_id: int, dev: Dict[str, torch.Tensor]) -> None:
+        """``token_ids[i] = last_tokens[token_src[i]]`` where ``token_src[i] >= 0``: the tokens the previous
+        launched step sampled become this step's inputs without visiting the host."""
+        last = self._last_tokens.get(model_id)
+        if last is None:
+            raise RuntimeError("a decode step refers to the tokens of a step this executor never launched")
+        tok, src = dev["token_ids"], dev["token_src"]
+        if tok.is_cuda:
+            from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
+
+            rc = lib().mlcb_token_feed(ptr(tok), ptr(src), ptr(last), ctypes.c_int(tok.numel()),
+                                       ctypes.c_int(last.numel()), ptr(ops.status_word(self.device)), stream_ptr())
+            check(rc, "mlcb_token_feed")
+        else:
+            pick = src >= 0
+            tok[pick] = last[src[pick].long()]
+
+    def _readback(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        """Queue a device -> pinned host copy of ``t``; the buffers alternate between two steps."""
+        if not t.is_cuda:
+            return t
+        bufs = self._readback_bufs[self._readback_turn]
+        buf = bufs.get(name)
+        if buf is None or buf.numel() < t.numel() or buf.dtype != t.dtype:
+            buf = bufs[name] = torch.empty(max(t.numel(), 1024), dtype=t.dtype, pin_memory=True)
+        out = buf[: t.numel()].view(t.shape)
+        out.copy_(t, non_blocking=True)
+        return out
+
+    def forward_sample_launch(self, model_id: int, plan: dict, token_ids: np.ndarray, token_src: np.ndarray,
+                              sp: dict) -> bool:
+        """Queue one decode step and return without reading its result (``forward_sample_wait`` does).
+        Returns False, having done nothing, for steps that need the synchronous path."""
+        model = self.models[model_id]
+        n_rows = len(sp["logit_token_index"])
+        if (model_id in self.spec_heads or self._pipeline(model_id) or getattr(model, "stateful", False)
+                or n_rows == 0 or len(sp["prob_slots"]) or len(sp["pen_row"]) or len(sp["mask_rows"])
+                or len(self._pending) >= 2):
+            return False
+        self._enter()
+        ht, clock = self.host_times, time.perf_counter
+        t0 = clock()
+        arrays = self._pack(plan, token_ids, sp, model_id)
+        arrays["token_src"] = np.ascontiguousarray(token_src, dtype=np.int32)
+        feed = bool((arrays["token_src"] >= 0).any())
+        t1 = clock()
+        if self.comm is not None:
+            self.comm.broadcast_step("forward_async", model_id,
+                                     {k: v for k, v in arrays.items()
+                                      if not k.startswith("s_") or k == "s_logit_token_index"}, {})
+        t2 = clock()
+        dev = self.staging.upload(arrays)
+        self.h2d_bytes += self.staging.last_words * 4
+        t3 = clock()
+        if feed:
+            self._feed_tokens(model_id, dev)
+        hidden = self._run_model(model_id, plan, dev, None)
+        t4 = clock()
+        logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
+        res: Dict[str, torch.Tensor] = {}
+        if self._is_plain_greedy(sp):
+            tokens = ops.argmax(logits)
+        else:
+            self._process_logits(logits, dev, sp)
+            probs = ops.softmax_temperature(logits, dev["s_temperature"])
+            top_k = dev["s_top_k"] if int(np.max(sp["top_k"])) > 0 else None
+            tokens, tprobs = ops.sample(probs, None, dev["s_uniform"], dev["s_top_p"], top_k)
+            tokens = tokens.to(torch.int32)
+            k = int(sp["num_top_logprobs"])
+            if k > 0:
+                _, tp, ti = ops.take_probs(probs, None, tokens, k)
+                res["top_probs"] = self._readback("top_probs", tp.reshape(-1).float())
+                res["top_tokens"] = self._readback("top_tokens", ti.reshape(-1).to(torch.int32))
+                # logprobs are reported on the unrenormalised distribution
+                tprobs = probs[torch.arange(n_rows, device=probs.device), tokens.long()]
+            res["probs"] = self._readback("probs", tprobs.float())
+        self._last_tokens[model_id] = tokens
+        if self.comm is not None:
+            self.comm.broadcast_tokens(tokens)
+        res["tokens"] = self._readback("tokens", tokens)
+        event = None
+        if tokens.is_cuda:
+            event = torch.cuda.Event()
+            event.record()
+        self._readback_turn ^= 1
+        self._pending.append({"model": model_id, "res": res, "event": event, "rows": n_rows})
+        t5 = clock()
+        ht["pack"] += t1 - t0
+        ht["broadcast"] += t2 - t1
+        ht["upload"] += t3 - t2
+        ht["forward"] += t4 - t3
+        ht["logits_sample"] += t5 - t4
+        ht["calls"] += 1
+        return True
+
+    def forward_sample_wait(self, model_id: int) -> dict:
+        """Result of the oldest launched step that has not been read."""
+        if not self._pending:
+            raise RuntimeError("no launched decode step to wait for")
+        t0 = time.perf_counter()
+        item = self._pending.popleft()
+        if item["event"] is not None:
+            item["event"].synchronize()
+        out = {k: np.array(v.numpy() if not v.is_cuda else v.cpu().numpy()) for k, v in item["res"].items()}
+        if "probs" not in out:
+            out["probs"] = np.ones(item["rows"], dtype=np.float32)
+        self.d2h_bytes += sum(v.nbytes for k, v in out.items() if k in item["res"])
+        self.host_times["readback"] += time.perf_counter() - t0
+        return out
 
     def _sample(self, logits: torch.Tensor, dev: Dict[str, torch.Tensor], sp: dict, n_rows: int) -> dict:
         """Logit processing, softmax, sampling and read-back of one row per entry of ``sp``."""
@@ -788,6 +914,16 @@ class ModelExecutor:
         plan = {k: arrays[k] for k in _INT_KEYS}
         plan["tree_mask"] = arrays["tree_mask"]
         plan["max_seq_len"] = int(arrays["seq_lens"].max()) if arrays["seq_lens"].size else 0
+        if op == "forward_async":
+            # deferred-read decode step: inputs may be the tokens rank 0 sampled in the step before, and
+            # this step's tokens arrive the same way (device to device) once rank 0 has sampled them
+            if bool((arrays["token_src"] >= 0).any()):
+                self._feed_tokens(model_id, dev)
+            self._run_model(model_id, plan, dev, None)
+            tokens = torch.empty(int(arrays["s_logit_token_index"].size), dtype=torch.int32, device=self.device)
+            self.comm.broadcast_tokens(tokens)
+            self._last_tokens[model_id] = tokens
+            return
         hidden = self._run_model(model_id, plan, dev, None)
         model = self.models[model_id]
         if self._pipeline(model_id) and model.last_stage and self.comm.tp_rank == 0 \

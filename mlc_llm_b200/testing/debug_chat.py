@@ -88,16 +88,18 @@ class DebugChat:
         from ..serve.sync_engine import SyncMLCEngine  # pylint: disable=import-outside-toplevel
 
         self.debug_dir = debug_dir
-        saved = os.environ.get("MLCB_CUDA_GRAPH")
+        saved = {k: os.environ.get(k) for k in ("MLCB_CUDA_GRAPH", "MLCB_PIPELINED_DECODE")}
         os.environ["MLCB_CUDA_GRAPH"] = "0"  # graph replays would bypass the operator layer
+        os.environ["MLCB_PIPELINED_DECODE"] = "0"  # one engine step = one model call = one token
         try:
             self.engine = SyncMLCEngine(model, device, engine_config=EngineConfig(
                 mode="local", max_num_sequence=1, prefix_cache_mode="disable"))
         finally:
-            if saved is None:
-                os.environ.pop("MLCB_CUDA_GRAPH", None)
-            else:
-                os.environ["MLCB_CUDA_GRAPH"] = saved
+            for k, v in saved.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
         self.instrument = instrument or DebugInstrument(os.path.join(debug_dir, "prefill"))
 
     def generate(self, prompt, generate_len: int) -> List[int]:

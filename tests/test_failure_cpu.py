@@ -22,7 +22,7 @@ def test_exception_in_a_step_fails_requests_and_engine_recovers():
                     engine_config=EngineConfig(max_num_sequence=4, prefill_chunk_size=64, max_total_sequence_length=1024))
     try:
         ex = eng.runtime.executor
-        orig = ex.forward_sample
+        orig, orig_launch = ex.forward_sample, ex.forward_sample_launch
         calls = {"n": 0}
 
         def flaky(*a, **k):
@@ -31,7 +31,13 @@ def test_exception_in_a_step_fails_requests_and_engine_recovers():
                 raise RuntimeError("injected failure in the model call")
             return orig(*a, **k)
 
-        ex.forward_sample = flaky
+        def flaky_launch(*a, **k):   # decode steps whose result is read one step later
+            calls["n"] += 1
+            if calls["n"] == 3:
+                raise RuntimeError("injected failure in the model call")
+            return orig_launch(*a, **k)
+
+        ex.forward_sample, ex.forward_sample_launch = flaky, flaky_launch
         rng = np.random.default_rng(0)
         prompts = [rng.integers(10, 31000, 12).tolist() for _ in range(3)]
         res = eng.generate_many(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
@@ -41,7 +47,6 @@ def test_exception_in_a_step_fails_requests_and_engine_recovers():
         assert ok.choices[0].finish_reason == "length" and ok.usage.completion_tokens == 5
         # streaming consumers see the error too
         calls["n"] = 0
-        ex.forward_sample = flaky
         reasons = []
         for chunk in eng.chat.completions.create(messages=[{"role": "user", "content": "hello there"}], max_tokens=8,
                                                  temperature=0.0, stream=True):

@@ -246,7 +246,7 @@ def test_logit_edits_and_take_probs_and_verify():
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("hq,hkv", [(8, 2), (8, 1), (4, 4), (32, 8)])
 @pytest.mark.parametrize("mode,splits", [("prefill", 1), ("decode", 1), ("mixed", 1), ("decode", 3),
-                                         ("verify", 1), ("verify", 2)])
+                                         ("verify", 1), ("verify", 2), ("decode_many", 1), ("decode_many", 2)])
 def test_attention_tcgen05(dtype, hq, hkv, mode, splits):
     from mlc_llm_b200.ops.attention import AttentionPlan, build_tiles
 
@@ -256,6 +256,12 @@ def test_attention_tcgen05(dtype, hq, hkv, mode, splits):
         lens, appended = [70, 200, 33, 129], [70, 200, 33, 129]
     elif mode == "decode":
         lens, appended = [1, 17, 64, 65, 300, 128], [1, 1, 1, 1, 1, 1]
+    elif mode == "decode_many":
+        # more (sequence, kv head) units than the persistent decode kernel has CTAs: every CTA walks
+        # several units of different lengths, so its page ring carries on across unit boundaries
+        rng = np.random.default_rng(4)
+        lens = [int(x) for x in rng.integers(1, 420, 330)]
+        appended = [1] * len(lens)
     elif mode == "verify":
         lens, appended = [33, 500, 7, 260], [3, 4, 2, 4]
     else:
