@@ -103,6 +103,16 @@ struct GemmParams {
   // All-gather prologue: token rows of X become readable once their 8-row group flag reaches ag_epoch.
   const int* ag_wait;
   int ag_epoch;
+  // ---- all-reduce form (see ar_tail): the GEMM writes this rank's partial sums to `y`, which is this
+  // rank's copy of a symmetric buffer; the kernel's tail then sums the copies of all ranks (one multimem
+  // load per 16 bytes through the NVSwitch, or plain peer loads without a multicast mapping), adds the
+  // residual, applies RMSNorm and leaves residual and normalised rows in local memory, on every rank.
+  int ar_world, ar_rank, ar_epoch;
+  const void* ar_mc;                   // multicast address of the partial-sum buffer, or null
+  const unsigned long long* ar_peers;  // [world] every rank's partial-sum buffer (plain peer loads)
+  const unsigned long long* ar_flags;  // [world] per rank: int arrival epochs [world]
+  int* ar_counter;                     // local: CTAs of this launch that have stored their tiles
+  void* ar_xn;                         // local [M, N]: normalised rows
   // CTA pairs (cta_group::2): two CTAs of a cluster share each UMMA; see gemm_kernel<.., true>.
   int pair;
 };
@@ -328,6 +338,164 @@ __device__ __forceinline__ void rs_tail_rows(const GemmParams& p, int warp, int 
                                epoch);
     }
   }
+}
+
+// All-reduce tail. Every CTA of the launch has stored its tiles of this rank's partial sums when it gets
+// here. (1) The last CTA of this rank to arrive tells every rank (a release store of the call number
+// into slot `rank` of each rank's flag array). (2) Every CTA waits until all ranks have told this rank.
+// (3) Rows are dealt to the warps of the grid: a warp sums the row over the ranks -- one
+// multimem.ld_reduce per 16 bytes, reduced inside the NVSwitch with fp32 accumulation, or `world` plain
+// peer loads -- adds the residual row (kept whole on every rank, updated in place), and writes the
+// RMS-normalised row for the next GEMM. All waits are bounded.
+template <typename T>
+__device__ __forceinline__ void ar_tail_rows(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
+  const int world = p.ar_world;
+  const int epoch = p.ar_epoch + (p.epoch_base ? __ldg(p.epoch_base) : 0);
+  if (threadIdx.x == 0) GEMM_TRACE(7, 8);
+  __syncthreads();  // every output store of the CTA happens before thread 0's fence below
+  if (threadIdx.x == 0) GEMM_TRACE(7, 9);
+  {  // (with one rank this is the grid-wide barrier alone: a row needs the tiles of every CTA)
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const int prev = atomicAdd(p.ar_counter, 1);
+      abort_flag[1] = (prev == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (abort_flag[1] && threadIdx.x < world) {
+      if (threadIdx.x == 0) *p.ar_counter = 0;
+      __threadfence_system();
+      flag_store_release_sys(reinterpret_cast<int*>(p.ar_flags[threadIdx.x]) + p.ar_rank, epoch);
+    }
+    if (warp == 0) {
+      const int* mine = reinterpret_cast<const int*>(p.ar_flags[p.ar_rank]);
+      if (lane < world) flag_wait_ge(mine + lane, epoch, abort_flag, p.status, ERR_WAIT_PEER);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) GEMM_TRACE(7, 10);
+    if (*abort_flag) return;
+  }
+  // Rows are dealt to the CTAs (row = blockIdx.x, + gridDim.x, ...), RB rows at a time, so that every SM
+  // pulls its share through the switch at once and every thread has several loads in flight: a thread
+  // owns the 16-byte vectors threadIdx.x, + blockDim.x, ... of each row; the row's sum of squares is
+  // reduced over the CTA through shared memory.
+  const int nvec = p.N >> 3;  // 16-byte vectors per row
+  T* residual = reinterpret_cast<T*>(p.rs_residual);
+  T* xn = reinterpret_cast<T*>(p.ar_xn);
+  const T* nw = reinterpret_cast<const T*>(p.rs_norm_w);
+  const bool use_mc = p.ar_mc != nullptr && world > 1;
+  constexpr int RB = 4;    // rows per round
+  constexpr int VPT = 2;   // vectors per thread, row and pass (a wider row takes more passes)
+  __shared__ float ar_ss[RB][17];
+  const int nwarps = blockDim.x >> 5;
+  for (int row0 = blockIdx.x * RB; row0 < p.M; row0 += gridDim.x * RB) {
+    float ss[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) ss[r] = 0.f;
+    for (int vb = threadIdx.x; vb < nvec; vb += blockDim.x * VPT) {
+      uint4 rv[RB][VPT], sv[RB][VPT];
+#pragma unroll
+      for (int r = 0; r < RB; ++r)
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+          const int v = vb + u * blockDim.x;
+          const bool live = row0 + r < p.M && v < nvec;
+          const size_t off = static_cast<size_t>(row0 + r) * p.N + v * 8;
+          rv[r][u] = live ? *reinterpret_cast<const uint4*>(residual + off) : make_uint4(0, 0, 0, 0);
+          sv[r][u] = make_uint4(0, 0, 0, 0);
+          if (!live) continue;
+          if (use_mc) {
+            const char* src = reinterpret_cast<const char*>(p.ar_mc) + off * sizeof(T);
+            if (p.out_dtype == 0)
+              asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(sv[r][u].x), "=r"(sv[r][u].y), "=r"(sv[r][u].z), "=r"(sv[r][u].w)
+                           : "l"(src));
+            else
+              asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(sv[r][u].x), "=r"(sv[r][u].y), "=r"(sv[r][u].z), "=r"(sv[r][u].w)
+                           : "l"(src));
+          }
+        }
+      if (!use_mc) {
+        // plain peer loads; the sum over the ranks is rounded to the storage type, as an all-reduce of
+        // 16-bit tensors is
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+#pragma unroll
+          for (int u = 0; u < VPT; ++u) {
+            const int v = vb + u * blockDim.x;
+            if (row0 + r >= p.M || v >= nvec) continue;
+            const size_t off = static_cast<size_t>(row0 + r) * p.N + v * 8;
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < world; ++q) {
+              const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(
+                  reinterpret_cast<const char*>(p.ar_peers[q]) + off * sizeof(T)));
+              const T* ph = reinterpret_cast<const T*>(&pv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sum[e] += Cvt<T>::to_f(ph[e]);
+            }
+            T* sh = reinterpret_cast<T*>(&sv[r][u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sh[e] = Cvt<T>::from_f(sum[e]);
+          }
+      }
+#pragma unroll
+      for (int r = 0; r < RB; ++r)
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+          const int v = vb + u * blockDim.x;
+          if (row0 + r >= p.M || v >= nvec) continue;
+          const T* rh = reinterpret_cast<const T*>(&rv[r][u]);
+          const T* sh = reinterpret_cast<const T*>(&sv[r][u]);
+          uint4 ov;
+          T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            oh[e] = Cvt<T>::from_f(Cvt<T>::to_f(rh[e]) + Cvt<T>::to_f(sh[e]));
+            const float x = Cvt<T>::to_f(oh[e]);  // the norm sees the rounded residual
+            ss[r] += x * x;
+          }
+          *reinterpret_cast<uint4*>(residual + static_cast<size_t>(row0 + r) * p.N + v * 8) = ov;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
+      if (lane == 0) ar_ss[r][warp] = ss[r];
+    }
+    __syncthreads();
+    float inv[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      float tot = 0.f;
+      for (int w = 0; w < nwarps; ++w) tot += ar_ss[r][w];
+      inv[r] = rsqrtf(tot / static_cast<float>(p.N) + p.rs_eps);
+    }
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(nw + v * 8);
+      const T* wh = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        if (row0 + r >= p.M) continue;
+        const size_t off = static_cast<size_t>(row0 + r) * p.N + v * 8;
+        const uint4 rv = *reinterpret_cast<const uint4*>(residual + off);  // this thread's own stores
+        const T* rh = reinterpret_cast<const T*>(&rv);
+        uint4 ov;
+        T* oh = reinterpret_cast<T*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          oh[e] = Cvt<T>::from_f(Cvt<T>::to_f(rh[e]) * inv[r] * (Cvt<T>::to_f(wh[e]) + p.rs_w_offset));
+        *reinterpret_cast<uint4*>(xn + off) = ov;
+      }
+    }
+    __syncthreads();  // ar_ss is rewritten by the next round
+  }
+}
+
+__device__ __forceinline__ void ar_tail(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
+  if (p.out_dtype == 0) ar_tail_rows<__half>(p, warp, lane, abort_flag);
+  else ar_tail_rows<__nv_bfloat16>(p, warp, lane, abort_flag);
+  if (threadIdx.x == 0) GEMM_TRACE(7, 11);
 }
 
 __device__ __forceinline__ void rs_tail(const GemmParams& p, int warp, int lane, volatile int* abort_flag) {
@@ -1149,6 +1317,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   // adds them to the residual stream (kept only on the owner), normalises, and writes the
   // normalised row into every rank's gather buffer, followed by the group's flag.
   if (p.rs_world && *abort_flag == 0) rs_tail(p, warp, lane, abort_flag);
+  if (p.ar_world && *abort_flag == 0) ar_tail(p, warp, lane, abort_flag);
 }
 
 // ---------------------------------------------------------------- host side
@@ -1289,6 +1458,14 @@ struct MlcbFusedArgs {
   const void* ag_wait;
   int ag_epoch, reserved;
   const int* epoch_base;  // optional device word added to rs_epoch / ag_epoch (CUDA-graph replays)
+  // all-reduce form (ar_world > 0; uses rs_residual, rs_norm_w, rs_eps, rs_w_offset as well): `y` must be
+  // this rank's partial-sum buffer
+  int ar_world, ar_rank, ar_epoch, ar_pad;
+  const void* ar_mc;
+  const unsigned long long* ar_peers;
+  const unsigned long long* ar_flags;
+  void* ar_counter;
+  void* ar_xn;
 };
 
 // CTA-pair kernels: MLCB_GEMM_PAIR = "0" never, "1" every weight format, unset = dense 16-bit weights
@@ -1357,6 +1534,9 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
                        int num_counters, cudaStream_t stream, const MlcbFusedArgs* f, int wf_hint = 0) {
   if (M <= 0 || N <= 0) return 0;
   const bool rs = f && f->rs_world > 0;
+  if (f && f->ar_world > 0 && (f->ar_world > 8 || N % 8 != 0 || out_dtype > 1 || ldy != N || rs || !f->ar_xn ||
+                              !f->rs_residual || !f->rs_norm_w || !f->ar_flags || !f->ar_counter || !f->ar_peers))
+    return -5;
   if (rs && (f->rs_world > 8 || f->rs_rows % 32 != 0 || N % 8 != 0 || out_dtype > 1 ||
              static_cast<long long>(f->rs_rows) * f->rs_world < M))
     return -5;
@@ -1414,6 +1594,14 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     p.ag_wait = static_cast<const int*>(f->ag_wait);
     p.ag_epoch = f->ag_epoch;
     p.epoch_base = f->epoch_base;
+    p.ar_world = f->ar_world;
+    p.ar_rank = f->ar_rank;
+    p.ar_epoch = f->ar_epoch;
+    p.ar_mc = f->ar_mc;
+    p.ar_peers = f->ar_peers;
+    p.ar_flags = f->ar_flags;
+    p.ar_counter = static_cast<int*>(f->ar_counter);
+    p.ar_xn = f->ar_xn;
   }
   // split-K when the output tiles alone cannot fill the GPU (decode-sized M with a narrow N)
   {

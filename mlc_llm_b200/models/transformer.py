@@ -318,6 +318,25 @@ class DecoderModel:
         x = x.contiguous()
         f.scatter_residual(x)
         layers = list(self.layers)
+        if f.mode == "ar":
+            # all-reduce form: every rank keeps the whole residual stream; the row-parallel GEMMs reduce
+            # over the ranks in their own tail (+ residual + norm), the column-parallel ones are plain
+            h = self._norm(x, f"model.layers.{layers[0]}.input_layernorm")
+            for pos, li in enumerate(layers):
+                pre = f"model.layers.{li}."
+                qkv = ops.linear(h, self.p.linears[pre + "self_attn.qkv_proj"])
+                ctx = self._attention_core(li, qkv, b)
+                h = f.gemm_ar_norm(ctx, self.p.linears[pre + "self_attn.o_proj"],
+                                   self.p.tensors[pre + "post_attention_layernorm.weight"], c.rms_norm_eps,
+                                   c.norm_weight_offset)
+                g = ops.linear(h, self.p.linears[pre + "mlp.gate_up_proj"])
+                a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
+                nxt = f"model.layers.{layers[pos + 1]}.input_layernorm" if pos + 1 < len(layers) else "model.norm"
+                h = f.gemm_ar_norm(a, self.p.linears[pre + "mlp.down_proj"], self.p.tensors[nxt + ".weight"],
+                                   c.rms_norm_eps, c.norm_weight_offset)
+            f.end()
+            self._final_normed = h
+            return h
         h = self._norm(x, f"model.layers.{layers[0]}.input_layernorm")
         for pos, li in enumerate(layers):
             pre = f"model.layers.{li}."

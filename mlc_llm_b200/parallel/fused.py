@@ -23,6 +23,7 @@ after the MLP (``model/llama/llama_model.py:211-214``) followed by the fused add
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -44,6 +45,9 @@ class FusedArgs(ctypes.Structure):
         ("ag_xn", ctypes.c_void_p), ("ag_flag", ctypes.c_void_p),
         ("ag_wait", ctypes.c_void_p), ("ag_epoch", ctypes.c_int), ("reserved", ctypes.c_int),
         ("epoch_base", ctypes.c_void_p),
+        ("ar_world", ctypes.c_int), ("ar_rank", ctypes.c_int), ("ar_epoch", ctypes.c_int), ("ar_pad", ctypes.c_int),
+        ("ar_mc", ctypes.c_void_p), ("ar_peers", ctypes.c_void_p), ("ar_flags", ctypes.c_void_p),
+        ("ar_counter", ctypes.c_void_p), ("ar_xn", ctypes.c_void_p),
     ]
 
 
@@ -55,9 +59,18 @@ class FusedCollectives:
     """Symmetric buffers + launch helpers for one tensor-parallel group."""
 
     def __init__(self, hidden: int, dtype: torch.dtype, max_tokens: int, device: torch.device,
-                 group=None, world_size: int = 1):
+                 group=None, world_size: int = 1, mode: Optional[str] = None):
         assert dtype in (torch.float16, torch.bfloat16)
         self.hidden, self.dtype, self.device = hidden, dtype, device
+        # "ar": GEMM + in-kernel all-reduce through NVSwitch multicast loads (+ residual + RMSNorm), every
+        # rank keeps the whole residual stream; "rs": the reduce-scatter / all-gather pair of kernels with
+        # peer stores, residual rows scattered over the ranks
+        self.mode = mode or os.environ.get("MLCB_FUSED_TP_MODE", "ar")
+        if self.mode not in ("ar", "rs"):
+            raise ValueError(f"unknown fused tensor-parallel mode {self.mode!r}")
+        if self.mode == "ar":
+            self._init_ar(max_tokens, group, world_size)
+            return
         esize = 2
         self.rows_cap = _round_up(-(-max_tokens // max(1, world_size)), 32)
         world = max(1, world_size)
@@ -94,6 +107,62 @@ class FusedCollectives:
         self.tokens = 0
         self.launches = 0
 
+    # ------------------------------------------------------------------ all-reduce form
+    def _init_ar(self, max_tokens: int, group, world_size: int) -> None:
+        hidden, esize = self.hidden, 2
+        world = max(1, world_size)
+        self.rows_cap = _round_up(-(-max_tokens // world), 32)
+        cap = world * self.rows_cap
+        part_bytes = _round_up(cap * hidden * esize, 4096)           # one parity
+        self.off_part = [0, part_bytes]
+        self.off_arflag = 2 * part_bytes
+        total = self.off_arflag + 256
+        self.buf = SymmetricBuffer(total, group, self.device) if world > 1 else LocalBuffer(total, self.device)
+        self.world, self.rank = self.buf.world_size, self.buf.rank
+        assert self.world == world
+        # peer address tables: [partial sums parity 0][parity 1][arrival flags], 8 slots each
+        table = torch.zeros(3, 8, dtype=torch.int64)
+        for r in range(self.world):
+            table[0, r] = self.buf.peer_ptr(r, self.off_part[0])
+            table[1, r] = self.buf.peer_ptr(r, self.off_part[1])
+            table[2, r] = self.buf.peer_ptr(r, self.off_arflag)
+        self.table = table.to(self.device)
+        self.ar_counter = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.residual = torch.zeros(cap, hidden, dtype=self.dtype, device=self.device)
+        self.xn_local = torch.zeros(cap, hidden, dtype=self.dtype, device=self.device)
+        self.epoch_dev = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.base = self.call = 0
+        self.rows = self.rows_cap
+        self.tokens = 0
+        self.launches = 0
+        self.multimem = self.buf.mc_ptr != 0
+
+    def gemm_ar_norm(self, x: torch.Tensor, lw: LinearWeight, norm_w: torch.Tensor, eps: float,
+                     w_offset: float = 0.0) -> torch.Tensor:
+        """``residual += sum_ranks(x @ W^T)`` on every rank; returns ``rmsnorm(residual)`` ``[tokens, hidden]``
+        in local memory. One launch: the GEMM stores this rank's partial sums in its copy of a symmetric
+        buffer, the kernel's tail waits for all ranks and reduces through the multicast mapping."""
+        assert self.mode == "ar" and x.shape[0] == self.tokens and x.is_contiguous()
+        n = lw.out_features or lw.w.shape[0]
+        assert n == self.hidden
+        self.call += 1
+        parity = self.epoch & 1
+        a = FusedArgs()
+        a.ar_world, a.ar_rank, a.ar_epoch = self.world, self.rank, self.call
+        a.epoch_base = self.epoch_dev.data_ptr()
+        a.ar_mc = (self.buf.mc_ptr + self.off_part[parity]) if self.multimem else None
+        a.ar_peers = self.table[parity].data_ptr()
+        a.ar_flags = self.table[2].data_ptr()
+        a.ar_counter = self.ar_counter.data_ptr()
+        a.ar_xn = self.xn_local.data_ptr()
+        a.rs_residual = self.residual.data_ptr()
+        a.rs_norm_w = norm_w.data_ptr()
+        a.rs_eps, a.rs_w_offset = float(eps), float(w_offset)
+        y = self.buf.view(self.off_part[parity], (self.world * self.rows_cap, self.hidden), self.dtype)[: self.tokens]
+        # a bias of a row-parallel layer is added once, by rank 0
+        self._launch(x, lw, y, n, x.dtype, a, bias=self.rank == 0 and lw.bias is not None)
+        return self.xn_local[: self.tokens]
+
     # ------------------------------------------------------------------ per-forward state
     def begin(self, tokens: int) -> None:
         """Fix the row partition of this forward call (every rank passes the same token count)."""
@@ -129,6 +198,9 @@ class FusedCollectives:
     def scatter_residual(self, x: torch.Tensor) -> None:
         """Start of a forward: this rank's rows of the (replicated) embedding output become its part
         of the residual stream."""
+        if self.mode == "ar":
+            self.residual[: self.tokens].copy_(x)
+            return
         own = self.owned()
         if len(own):
             self.residual[: len(own)].copy_(x[own.start: own.stop])

@@ -12,6 +12,7 @@ memory is never handed to library kernels and never read through TMA.
 
 from __future__ import annotations
 
+import os
 from typing import List
 
 import torch
@@ -33,6 +34,14 @@ class SymmetricBuffer:
         self.rank = int(self.handle.rank)
         self.world_size = int(self.handle.world_size)
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        # multicast address of the allocation (NVLS: one load / store / reduction reaches every rank's
+        # copy inside the NVSwitch); 0 when the fabric or the driver offers none
+        self.mc_ptr = 0
+        if os.environ.get("MLCB_MULTIMEM", "1") != "0":
+            try:
+                self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            except Exception:  # pylint: disable=broad-except
+                self.mc_ptr = 0
         self.nbytes = nbytes
         torch.cuda.synchronize(device)
         dist.barrier(group)
@@ -58,6 +67,7 @@ class LocalBuffer:
         self.local = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         self.rank, self.world_size = 0, 1
         self.ptrs = [self.local.data_ptr()]
+        self.mc_ptr = 0
         self.nbytes = nbytes
 
     peer_ptr = SymmetricBuffer.peer_ptr

@@ -357,7 +357,7 @@ def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
         return ops.LinearWeight("q4", qw, qs, None, quant, w.shape[0], w.shape[1]).to(DEV)
 
     l_o, l_up = mk(w_o), mk(w_up)
-    fc = FusedCollectives(hidden, dt, 1024, torch.device(DEV))
+    fc = FusedCollectives(hidden, dt, 1024, torch.device(DEV), mode="rs")
     for rep in range(3):  # several epochs over the same buffers
         fc.begin(tokens)
         fc.scatter_residual(res0)
@@ -374,6 +374,42 @@ def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
         _close(fc.residual[:tokens], res, tol, tol)
         _close(xn, want_xn, tol, tol)
         _close(y, want_y, 10 * tol, 10 * tol)
+
+
+@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
+@pytest.mark.parametrize("tokens,k", [(256, 2048), (37, 512), (1000, 1024), (5, 64)])
+def test_fused_all_reduce_gemm_single_rank(quant_name, tokens, k):
+    """World size 1 runs the GEMM + all-reduce + residual + RMSNorm kernel in its degenerate form: the
+    grid-wide barrier, the call numbers over several launches and the tail's arithmetic against the
+    unfused ops (the sum over ranks has a single term)."""
+    from mlc_llm_b200.parallel.fused import FusedCollectives
+
+    torch.manual_seed(6)
+    hidden = 512
+    quant = Q.get(quant_name)
+    dt = quant.torch_dtype
+    x = (torch.randn(tokens, k) * 0.5).to(dt).to(DEV)
+    res0 = (torch.randn(tokens, hidden) * 0.5).to(dt).to(DEV)
+    nw = (1 + 0.1 * torch.randn(hidden)).to(dt).to(DEV)
+    w_o = (torch.randn(hidden, k) * 0.05).to(dt)
+    if quant.kind == "no-quant":
+        l_o = ops.LinearWeight("dense", w_o, None, None, None, hidden, k).to(DEV)
+    else:
+        qw, qs = Q.group_quantize(w_o, quant)
+        l_o = ops.LinearWeight("q4", qw, qs, None, quant, hidden, k).to(DEV)
+    fc = FusedCollectives(hidden, dt, 1024, torch.device(DEV), mode="ar")
+    res = res0.clone()
+    fc.begin(tokens)
+    fc.scatter_residual(res0)
+    for rep in range(4):  # the residual carries over from call to call, as it does from layer to layer
+        xn = fc.gemm_ar_norm(x, l_o, nw, 1e-5).clone()
+        ops.check_status(torch.device(DEV))
+        o = ops.linear(x, l_o)
+        want_xn = ops.add_rmsnorm(o, res, nw, 1e-5)
+        tol = 3e-2 if dt == torch.bfloat16 else 4e-3
+        _close(fc.residual[:tokens], res, tol * (rep + 1), tol * (rep + 1))
+        _close(xn, want_xn, tol * (rep + 1), tol * (rep + 1))
+    fc.end()
 
 
 @pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
