@@ -12,6 +12,18 @@ Two numbers are reported:
   thread, stream-back thread, detokenisation), wall-clock, including per-step H2D of the step's
   index arrays from pinned memory and D2H of the sampled tokens.
 
+``--config`` selects one of the target workloads (the default, 2, is the headline):
+
+* ``2``      Llama-3-8B q4f16_1, tensor parallel over the N ranks, 256 x 512 -> 256;
+* ``3``      Llama-3-70B bf16, tensor parallel over N ranks (meant for 8), 512 requests with prompt lengths
+             uniform in [128, 2048] and 512 output tokens;
+* ``3-fp8``  the same with block-scaled e4m3 weights;
+* ``4``      Mixtral-8x7B bf16 with the experts sharded over the ranks (all-to-all dispatch / combine),
+             256 x 1024 -> 256;
+* ``5``      Llama-3-70B bf16 on 2 pipeline stages x N/2 tensor-parallel ranks with the prefix cache on
+             (64 requests share a 1536-token prefix, 128-token suffixes) and speculative decoding (a random
+             2-layer draft model proposing 4 tokens per step), 256 output tokens.
+
 ``--impl reference`` would run the unmodified reference implementation; it cannot be installed in
 this environment (its build needs the TVM / tokenizers-cpp / xgrammar submodules, which are empty
 directories), so that arm prints an ``unavailable`` line.
@@ -39,6 +51,19 @@ def _reference_arm():
                        "(add_subdirectory has no CMakeLists.txt); apache-tvm-ffi is not in the wheelhouse",
     }))
     return 0
+
+
+# The target workloads. prompt_len is (low, high): lengths are uniform in that range.
+WORKLOADS = {
+    "2": dict(model="llama-3-8b", quant="q4f16_1", requests=256, prompt_len=(512, 512), output_len=256),
+    "3": dict(model="llama-3-70b", quant="q0bf16", requests=512, prompt_len=(128, 2048), output_len=512),
+    "3-fp8": dict(model="llama-3-70b", quant="fp8_e4m3fn_bf16_block_scale", requests=512, prompt_len=(128, 2048),
+                  output_len=512),
+    "4": dict(model="mixtral-8x7b", quant="q0bf16", requests=256, prompt_len=(1024, 1024), output_len=256,
+              model_args="&expert_parallel=true"),
+    "5": dict(model="llama-3-70b", quant="q0bf16", requests=64, prompt_len=(128, 128), output_len=256,
+              shared_prefix=1536, pipeline_stages=2, draft="llama-3-draft-2l", draft_length=4),
+}
 
 
 class ClockSampler:
@@ -101,15 +126,25 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default="llama-3-8b")
-    ap.add_argument("--quant", default="q4f16_1")
-    ap.add_argument("--requests", type=int, default=256)
-    ap.add_argument("--prompt-len", type=int, default=512)
-    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--config", default="2", choices=sorted(WORKLOADS))
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--quant", default=None)
+    ap.add_argument("--requests", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--output-len", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return _reference_arm()
+    wl = dict(WORKLOADS[args.config])
+    for k in ("model", "quant", "requests", "output_len"):
+        if getattr(args, k) is not None:
+            wl[k] = getattr(args, k)
+    if args.prompt_len is not None:
+        wl["prompt_len"] = (args.prompt_len, args.prompt_len)
+    args.model, args.quant, args.requests, args.output_len = wl["model"], wl["quant"], wl["requests"], wl["output_len"]
+    lo, hi = wl["prompt_len"]
+    args.prompt_len = hi
 
     import torch
 
@@ -123,22 +158,35 @@ def main(argv=None) -> int:
             raise SystemExit("for --gpus N > 1 launch with torch.distributed.run --nproc-per-node N")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
-    comm = parallel.Communicator(tp_size=world, pp_size=1) if world > 1 else None
+    pp = int(wl.get("pipeline_stages", 1)) if world > 1 else 1
+    if world % pp:
+        raise SystemExit(f"config {args.config} needs a multiple of {pp} GPUs")
+    comm = parallel.Communicator(tp_size=world // pp, pp_size=pp) if world > 1 else None
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
 
-    model = f"random://{args.model}?quant={args.quant}&seed=0"
-    total_tokens = args.requests * (args.prompt_len + args.output_len)
+    model = f"random://{args.model}?quant={args.quant}&seed=0{wl.get('model_args', '')}"
+    shared = int(wl.get("shared_prefix", 0))
+    total_tokens = args.requests * (shared + args.prompt_len + args.output_len)
+    extra = {}
+    if wl.get("draft"):
+        extra = dict(additional_models=[f"random://{wl['draft']}?quant={args.quant}&seed=1"],
+                     speculative_mode="small_draft", spec_draft_length=int(wl["draft_length"]))
     cfg = EngineConfig(mode="server", max_num_sequence=args.requests, prefill_chunk_size=8192,
                        max_total_sequence_length=total_tokens + 16 * args.requests + 8192,
-                       prefix_cache_mode="disable", gpu_memory_utilization=0.90)
+                       prefix_cache_mode="radix" if shared else "disable", gpu_memory_utilization=0.90,
+                       tensor_parallel_shards=world // pp if world > 1 else None,
+                       pipeline_parallel_stages=pp if pp > 1 else None, **extra)
     rng = np.random.default_rng(1234)
     gen_cfg = {"max_tokens": args.output_len, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
     vocab_hi = 32000
 
     def make_prompts():
-        # fresh prompts every pass so no pass benefits from an earlier one
-        return [rng.integers(0, vocab_hi, args.prompt_len).tolist() for _ in range(args.requests)]
+        # fresh prompts every pass so no pass benefits from an earlier one (a shared prefix is shared
+        # within a pass only)
+        prefix = rng.integers(0, vocab_hi, shared).tolist() if shared else []
+        lens = rng.integers(lo, hi + 1, args.requests)
+        return [prefix + rng.integers(0, vocab_hi, int(n)).tolist() for n in lens]
 
     # ------------------------------------------------------------------ worker ranks
     if rank != 0:
@@ -269,10 +317,15 @@ def main(argv=None) -> int:
         "value": value, "unit": "output tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp16 activations, int4-group weights (q4f16_1)"
-        if args.quant == "q4f16_1" else args.quant, "data": "synthetic (uniform-random token ids, random-init weights)",
-        "config": {"model": f"{args.model} {args.quant}", "global_batch": args.requests,
-                   "seq_len": args.prompt_len + args.output_len, "prompt_len": args.prompt_len,
-                   "output_len": args.output_len, "parallelism": f"tp{world}",
+        if args.quant == "q4f16_1" else ("bf16" if args.quant == "q0bf16" else args.quant), "data": "synthetic (uniform-random token ids, random-init weights)",
+        "config": {"workload": args.config, "model": f"{args.model} {args.quant}", "global_batch": args.requests,
+                   "seq_len": shared + args.prompt_len + args.output_len,
+                   "prompt_len": args.prompt_len if lo == hi else f"uniform[{lo},{hi}]", "shared_prefix": shared,
+                   "output_len": args.output_len,
+                   "parallelism": (f"pp{pp}xtp{world // pp}" if pp > 1 else
+                                   (f"ep{world}" if "expert_parallel" in wl.get("model_args", "") and world > 1
+                                    else f"tp{world}")),
+                   "speculative": f"{wl['draft']} x{wl['draft_length']}" if wl.get("draft") else None,
                    "l2": "inputs larger than L2 (weights and KV cache far exceed 126 MB)",
                    "kv_page": 16, "kv_dtype": "fp16", "sampling": "greedy, ignore_eos"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
