@@ -907,9 +907,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
           // [4j, 4j+4) and [16+4j, 20+4j), so one shift by 8 exposes pairs 2 and 3 to the same two masks.
           const __half2 off_lo = __float2half2_rn(1031.f);
           const __half2 off_hi = __float2half2_rn(71.f);
+          // bf16 models (q4bf16_1): the record's scales are bf16; (q - 7) is exact in fp16, the product with
+          // the scale is formed in fp32 and rounded once to bf16
+          const bool bf = p.ab_fmt == 1;
+          const float fs_lo = __uint_as_float(sc_bits << 16), fs_hi = __uint_as_float(sc_bits & 0xffff0000u);
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
             const __half2 s2 = __half2half2((w < 4) ? __low2half(sc) : __high2half(sc));
+            const float fs = (w < 4) ? fs_lo : fs_hi;
             const uint32_t x = words[w];
             const uint32_t y = x >> 8;
             uint32_t v[4];
@@ -920,8 +925,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
             uint32_t h[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const __half2 hv = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[j]), (j & 1) ? off_hi : off_lo), s2);
-              h[j] = *reinterpret_cast<const uint32_t*>(&hv);
+              const __half2 centred = __hsub2(*reinterpret_cast<__half2*>(&v[j]), (j & 1) ? off_hi : off_lo);
+              if (bf) {
+                float2 f = __half22float2(centred);
+                f.x *= fs;
+                f.y *= fs;
+                const __nv_bfloat162 o = __float22bfloat162_rn(f);
+                h[j] = *reinterpret_cast<const uint32_t*>(&o);
+              } else {
+                const __half2 hv = __hmul2(centred, s2);
+                h[j] = *reinterpret_cast<const uint32_t*>(&hv);
+              }
             }
             *reinterpret_cast<uint4*>(dst_row + ((w ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
           }
@@ -1543,7 +1557,7 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
   const int wf = scale == nullptr ? 0 : ((wf_hint == 2 || (f && f->reserved == 2)) ? 2 : 1);
   const bool q4 = wf == 1;
   if (K % 8 != 0 || ldx % 8 != 0) return -1;
-  if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
+  if (q4 && K % 64 != 0) return -2;  // (scales in the tile records are in the activation dtype)
   if (wf == 2 && K % 64 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set[64] = {};
@@ -1807,7 +1821,7 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
   const bool q4 = scale != nullptr;
   if (K % 8 != 0 || ldx % 8 != 0 || N % BM != 0) return -1;
-  if (q4 && (K % 64 != 0 || ab_fmt != 0)) return -2;
+  if (q4 && K % 64 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   static bool attr_set[64] = {};
   if (first_use_on_device(attr_set)) {

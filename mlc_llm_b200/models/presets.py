@@ -75,6 +75,18 @@ MODEL_PRESETS = {
         "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
     },
+    # small models whose every sharded dimension divides by 8 (multi-rank tests up to 8 GPUs)
+    "tiny-llama-tp8": {
+        "model_type": "llama", "hidden_size": 1024, "intermediate_size": 2048, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+    },
+    "tiny-mixtral-tp8": {
+        "model_type": "mixtral", "hidden_size": 1024, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+        "num_local_experts": 8, "num_experts_per_tok": 2,
+    },
     "llama-3-8b": {
         "model_type": "llama", "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
         "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,

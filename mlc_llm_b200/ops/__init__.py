@@ -59,7 +59,7 @@ class LinearWeight:
         expert slabs, slabs of whole 128-row blocks."""
         return (self.kind == "q4" and self.quant is not None and self.quant.bits == 4
                 and self.quant.group_size == 32 and k % 64 == 0 and self.scale is not None
-                and self.scale.dtype == torch.float16
+                and self.scale.dtype in (torch.float16, torch.bfloat16)
                 and (self.w.dim() == 2 or self.w.shape[-2] % 128 == 0))
 
     def to(self, device) -> "LinearWeight":
@@ -150,9 +150,9 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
     if m == 0:
         return y.reshape(*lead, n)
     ab = DTYPE_CODE[x2.dtype]
-    if x2.dtype == torch.float16 and lw.q4_tileable(k):
+    if lw.q4_tileable(k) and x2.dtype == lw.scale.dtype:
         assert lw.device_layout
-        if m <= 4 and od in (torch.float16, torch.float32) and _GEMV_Q4:
+        if m <= 4 and od in (torch.float16, torch.float32) and _GEMV_Q4 and x2.dtype == torch.float16:
             # one to four tokens: the memory-bound CUDA-core kernel beats the tensor-core one, whose
             # dequantise stage is sized for wide token tiles
             rc = lib().mlcb_gemv_q4(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
@@ -161,7 +161,7 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
                 return y.reshape(*lead, n)
             if rc > 0:
                 check(rc, f"mlcb_gemv_q4(M={m},N={n},K={k})")
-        elif m <= 16 and od in (torch.float16, torch.float32) and _LOWM_Q4:
+        elif m <= 16 and od in (torch.float16, torch.float32) and _LOWM_Q4 and x2.dtype == torch.float16:
             # five to sixteen tokens: nibbles expanded in registers into warp-level MMA fragments
             rc = lib().mlcb_gemm_q4_lowm(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
                                          c_int(k), c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[od]), stream_ptr())
@@ -485,7 +485,7 @@ def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
     if rows == 0:
         return y
     x2 = x if x.stride(-1) == 1 else x.contiguous()
-    q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+    q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
     w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
     rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(offsets),
                                  c_int(e), c_int(rows), c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n),

@@ -162,7 +162,7 @@ class ExpertParallel:
 
     def _grouped(self, x: torch.Tensor, lw, rows: int, hint: int) -> torch.Tensor:
         n, k = lw.w.shape[1], x.shape[1]
-        q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+        q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
         w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
         y = torch.empty(rows, n, dtype=x.dtype, device=x.device)
         rc = lib().mlcb_gemm_grouped_table(

@@ -216,7 +216,7 @@ class FusedCollectives:
     def _launch(self, x: torch.Tensor, lw: LinearWeight, y: Optional[torch.Tensor], n: int, od: torch.dtype,
                 args: FusedArgs, bias: bool) -> None:
         m, k = x.shape
-        q4 = x.dtype == torch.float16 and lw.q4_tileable(k)
+        q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
         w = lw.q4_tiles() if q4 else lw.dense(x.dtype)
         rc = lib().mlcb_gemm_fused(
             ptr(x), ptr(w), ptr(w) if q4 else ptr(None), ptr(lw.bias) if bias else ptr(None), ptr(y),

@@ -190,7 +190,7 @@ Q4_TILE_ROWS, Q4_TILE_K, Q4_TILE_BYTES = 128, 64, 128 * 32 + 128 * 4
 
 def to_tiled_q4(qw_dev: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Tile records of the tensor-core GEMM: ``qw_dev [..., N, K/8]`` (int32, device nibble order) and
-    ``scale [..., N, K/32]`` (fp16) become ``uint8 [R/128, K/64, 4608]`` where ``R`` is the number of
+    ``scale [..., N, K/32]`` (fp16, or bf16 for bf16 models: the records keep the two bytes as they are) become ``uint8 [R/128, K/64, 4608]`` where ``R`` is the number of
     rows of all leading slabs stacked (padded to a multiple of 128 with zero scales).  One record holds
     one 128-row x 64-k block: ``[2 halves][128 rows][16 bytes of nibbles]`` followed by
     ``[128 rows][2 fp16 scales]``, so that the kernel streams a whole K sweep of a row block as one
@@ -199,7 +199,9 @@ def to_tiled_q4(qw_dev: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     if k8 % 8 != 0 or scale.shape[-1] * 4 != k8:
         raise ValueError("tiled int4 layout needs K to be a multiple of 64 and one scale per 32 weights")
     qw2 = qw_dev.reshape(-1, k8)
-    sc2 = scale.reshape(-1, scale.shape[-1]).to(torch.float16)
+    if scale.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("tile records hold 16-bit scales")
+    sc2 = scale.reshape(-1, scale.shape[-1])
     rows = qw2.shape[0]
     pad = (-rows) % Q4_TILE_ROWS
     if pad:

@@ -49,6 +49,29 @@ def main():
     eng = SyncMLCEngine(model, dev, engine_config=cfg, comm=comm)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (40, 9, 23)]
+    logits_out = os.environ.get("MLCB_TEST_LOGITS_OUT")
+    captured = []
+    if logits_out:
+        # numerics runs: keep the logits of every sampling call (greedy sampling goes through ops.argmax);
+        # prompts cross several 32-row chunks of the fused collectives, the last chunk uneven
+        from mlc_llm_b200 import ops
+
+        prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (70, 33, 41)]
+        orig_argmax = ops.argmax
+
+        def keep(x):
+            captured.append(x.detach().float().cpu().numpy())
+            return orig_argmax(x)
+
+        ops.argmax = keep
+        zero = os.environ.get("MLCB_TEST_ZERO_SHARD")
+        if zero:
+            # oracle with one rank's contribution to a row-parallel projection removed (see the numerics tests)
+            zw, zr = (int(v) for v in zero.split(","))
+            lw = eng.runtime.models[0].p.linears["model.layers.0.self_attn.o_proj"]
+            k = lw.w.shape[1]
+            lw.w[:, zr * k // zw:(zr + 1) * k // zw] = 0
+            lw._dense = None
     try:
         _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
     except Exception as err:  # pylint: disable=broad-except
@@ -57,6 +80,8 @@ def main():
         print("FAILURE " + json.dumps({"rank": rank, "error": str(err)[:300]}), flush=True)
         os._exit(0)
     comm.shutdown_workers()
+    if logits_out:
+        np.savez(logits_out, *captured)
     rt = eng.runtime
     print("FLAGS " + json.dumps({"fused_tp": bool(getattr(rt, "fused_tp", False)),
                                  "graph_replays": int(rt.executor.graph_replays),

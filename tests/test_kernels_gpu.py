@@ -60,6 +60,25 @@ def test_gemm_q4f16(m, n, k):
     _close(y, yr, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(7, 256, 128), (64, 512, 4096), (600, 1376, 256)])
+def test_gemm_q4bf16(m, n, k):
+    """bf16 models with int4 group weights (q4bf16_1): bf16 scales in the tile records, bf16 activations."""
+    torch.manual_seed(2)
+    quant = Q.get("q4bf16_1")
+    w = (torch.randn(n, k) * 0.02).bfloat16()
+    qw, qs = Q.group_quantize(w, quant)
+    assert qs.dtype == torch.bfloat16
+    lw = ops.LinearWeight("q4", qw, qs, None, quant, n, k).to(DEV)
+    assert lw.q4_tileable(k)
+    x = (torch.randn(m, k) * 0.5).bfloat16().to(DEV)
+    y = ops.linear(x, lw)
+    ops.check_status(x.device)
+    assert y.dtype == torch.bfloat16
+    wd = Q.group_dequantize(qw, qs, quant, k=k)
+    yr = ref.linear_dense(x.cpu(), wd)
+    _close(y, yr, 3e-2, 3e-2)
+
+
 def test_q4_device_layout_roundtrip():
     qw = torch.randint(-2**31, 2**31 - 1, (64, 32), dtype=torch.int64).to(torch.int32)
     assert torch.equal(Q.from_device_layout_q4(Q.to_device_layout_q4(qw)), qw)
@@ -449,7 +468,11 @@ def test_expert_parallel_exchange_single_rank(quant_name, tokens):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("m,n,k", [(1, 256, 256), (33, 384, 512), (256, 1024, 4096), (700, 512, 1024)])
-def test_fp8_block_scale_linear(dtype, m, n, k):
+def test_fp8_block_scale_linear(dtype, m, n, k, monkeypatch):
+    """fp8 weights, 16-bit activations (the weights are expanded inside the 16-bit GEMM)."""
+    from mlc_llm_b200.ops import fp8 as fp8_ops
+
+    monkeypatch.setattr(fp8_ops, "_FP8_ACT", False)
     torch.manual_seed(3)
     w = torch.randn(n, k) * 0.05
     qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
@@ -461,6 +484,47 @@ def test_fp8_block_scale_linear(dtype, m, n, k):
     want = x.float() @ Q.fp8_block_dequantize(qw, sc, (128, 128)).float().t()
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
     _close(y, want, tol, tol * want.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k", [(1, 128), (37, 512), (300, 4096)])
+def test_fp8_activation_quantisation_matches_the_reference_formula(dtype, m, k):
+    from mlc_llm_b200.ops.fp8 import act_quant_fp8
+
+    torch.manual_seed(4)
+    x = (torch.randn(m, k) * torch.rand(m, 1) * 3).to(dtype)
+    x[0, :5] = 0
+    xq, st = act_quant_fp8(x.to(DEV))
+    q_ref, s_ref = Q.fp8_rowwise_group_quantize(x.float(), 128, "float8_e4m3fn")
+    assert torch.equal(st[:, :m].t().cpu(), s_ref)
+    assert torch.equal(xq.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(17, 256, 256), (33, 384, 512), (256, 1024, 4096), (700, 512, 1024),
+                                   (2048, 640, 1280)])
+def test_fp8_w8a8_linear(dtype, m, n, k):
+    """fp8 weights and fp8 activations on the fp8 tensor-core path. The oracle is the fp32 product of the two
+    dequantised operands (activations quantised per row and 128-element group by the reference formula), so
+    the tolerance only has to cover fp32 summation order and the rounding of the output."""
+    torch.manual_seed(5)
+    w = torch.randn(n, k) * 0.05
+    qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
+    quant = Q.get("fp8_e4m3fn_bf16_block_scale")
+    x = (torch.randn(m, k) * 0.5).to(dtype)
+    bias = (torch.randn(n) * 0.1).to(dtype)
+    lw = ops.LinearWeight("fp8_block", qw.to(DEV), sc.float().to(DEV), bias.to(DEV), quant, n, k)
+    y = ops.linear(x.to(DEV), lw)
+    ops.check_status(torch.device(DEV))
+    xq, xs = Q.fp8_rowwise_group_quantize(x.float(), 128, "float8_e4m3fn")
+    x_deq = xq.float() * xs.repeat_interleave(128, dim=1)[:, :k]
+    want = x_deq @ Q.fp8_block_dequantize(qw, sc, (128, 128)).float().t() + bias.float()
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    _close(y, want, tol, tol * want.abs().max().item())
+    # and the end-to-end error against unquantised activations stays at the few-percent level of e4m3
+    full = x.float() @ Q.fp8_block_dequantize(qw, sc, (128, 128)).float().t() + bias.float()
+    rel = (y.float().cpu() - full).norm() / full.norm()
+    assert rel < 0.05, rel
 
 
 @pytest.fixture
