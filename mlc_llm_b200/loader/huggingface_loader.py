@@ -522,6 +522,16 @@ class HFCheckpoint:
         if not hasattr(self, "_open_file"):
             self._open_file: Optional[str] = None
             self._open = None
+        # AWQ checkpoints: a linear layer arrives as (qweight, qzeros, scales); it is offered under the
+        # name of the 16-bit weight it stands for and expanded when read
+        self.awq: Dict[str, str] = {}
+        for name in list(self.name_to_file):
+            if name.endswith(".qweight"):
+                base = name[: -len(".qweight")]
+                if base + ".qzeros" in self.name_to_file and base + ".scales" in self.name_to_file \
+                        and base + ".weight" not in self.name_to_file:
+                    self.awq[base + ".weight"] = base
+                    self.name_to_file[base + ".weight"] = self.name_to_file[name]
 
     def _load_file(self, fname: str) -> None:
         if self._open_file == fname:
@@ -556,10 +566,21 @@ class HFCheckpoint:
                 return (b.float() @ a.float()) * scale
         return None
 
+    def _raw(self, real: str) -> torch.Tensor:
+        self._load_file(self.name_to_file[real])
+        return self._open[real]
+
     def get(self, name: str) -> torch.Tensor:
         real = self.resolve(name)
         if real is None:
             raise KeyError(name)
+        if real in self.awq:
+            from ..quantization import awq_dequantize  # pylint: disable=import-outside-toplevel
+
+            base = self.awq[real]
+            w = awq_dequantize(self._raw(base + ".qweight"), self._raw(base + ".qzeros"), self._raw(base + ".scales"))
+            delta = self._lora_delta(real)
+            return w if delta is None else (w.float() + delta).to(w.dtype)
         delta = self._lora_delta(real)
         if delta is not None:
             self._load_file(self.name_to_file[real])

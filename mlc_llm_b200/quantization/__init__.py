@@ -80,8 +80,9 @@ QUANTIZATION: Dict[str, Quantization] = {
     "q4bf16_1": _group("q4bf16_1", 4, "bfloat16", 32),
     "q4f32_1": _group("q4f32_1", 4, "float32", 32),
     "q4f16_2": _group("q4f16_2", 4, "float16", 32, "NK", qe=False, qf=False),
-    "q4f16_autoawq": Quantization("q4f16_autoawq", "awq", "float16", bits=4, group_size=128),
-    "q4f16_ft": Quantization("q4f16_ft", "ft-quant", "float16", bits=4, group_size=0),
+    # AWQ checkpoints (qweight / qzeros / scales triples) are expanded to 16-bit weights when they are read
+    # (loader/huggingface_loader.py), so at run time this is a 16-bit model
+    "q4f16_autoawq": Quantization("q4f16_autoawq", "no-quant", "float16"),
     "e5m2_e5m2_f16": Quantization("e5m2_e5m2_f16", "fp8-per-tensor", "float16", bits=8,
                                   weight_dtype="float8_e5m2", activation_dtype="float8_e5m2"),
     "e4m3_e4m3_f16": Quantization("e4m3_e4m3_f16", "fp8-per-tensor", "float16", bits=8,
@@ -101,6 +102,10 @@ QUANTIZATION: Dict[str, Quantization] = {
 
 
 def get(name: str) -> Quantization:
+    if name == "q4f16_ft":
+        raise ValueError("q4f16_ft stores weights in the pre-shuffled layout of FasterTransformer's mixed-input "
+                         "CUTLASS GEMM, which this build has no kernel for; use q4f16_1 (the same 4-bit group "
+                         "quantisation, tensor-core kernel included)")
     if name not in QUANTIZATION:
         raise ValueError(f"unknown quantization {name!r}; known: {sorted(QUANTIZATION)}")
     return QUANTIZATION[name]
@@ -183,6 +188,47 @@ def from_device_layout_q4(qw: torch.Tensor) -> torch.Tensor:
         out |= (lo << (4 * (2 * j))) | (hi << (4 * (2 * j + 1)))
     out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
     return out.to(torch.int32)
+
+
+# ----------------------------------------------------------------------------- AWQ checkpoints
+# AutoAWQ "GEMM" layout (reference: quantization/awq_quantization.py:133-176, quantization/utils.py:15-48):
+# qweight [K, N/8] and qzeros [K/g, N/8] pack eight 4-bit values per 32-bit word with output column j of a
+# word at nibble (j % 2) * 4 + j // 2; scales [K/g, N]; W[n, k] = (q[k, n] - z[k / g, n]) * s[k / g, n].
+_AWQ_NIBBLE = [(j % 2) * 4 + j // 2 for j in range(8)]
+
+
+def _awq_unpack(words: torch.Tensor) -> torch.Tensor:
+    """``[R, C/8]`` int32 -> ``[R, C]`` values 0..15."""
+    x = words.to(torch.int64) & 0xFFFFFFFF
+    cols = [(x >> (4 * _AWQ_NIBBLE[j])) & 0xF for j in range(8)]
+    return torch.stack(cols, dim=-1).reshape(words.shape[0], words.shape[1] * 8)
+
+
+def awq_pack(values: torch.Tensor) -> torch.Tensor:
+    """Inverse of the unpacking above (``[R, C]`` values 0..15 -> ``[R, C/8]`` int32); used to write AWQ-format
+    tensors and in tests."""
+    r, c = values.shape
+    v = values.to(torch.int64).reshape(r, c // 8, 8)
+    out = torch.zeros(r, c // 8, dtype=torch.int64)
+    for j in range(8):
+        out |= (v[..., j] & 0xF) << (4 * _AWQ_NIBBLE[j])
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+    return out.to(torch.int32)
+
+
+def awq_dequantize(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor,
+                   out_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """AWQ tensors of one linear layer -> the dense weight ``[N, K]``.  The group size follows from the
+    shapes (``K / scales.shape[0]``)."""
+    k, n = qweight.shape[0], qweight.shape[1] * 8
+    groups = scales.shape[0]
+    if k % groups or scales.shape[1] != n or qzeros.shape[0] != groups:
+        raise ValueError("inconsistent AWQ tensor shapes")
+    g = k // groups
+    q = _awq_unpack(qweight).float()                                   # [K, N]
+    z = _awq_unpack(qzeros)[:, :n].float().repeat_interleave(g, dim=0)  # [K, N]
+    s = scales.float().repeat_interleave(g, dim=0)
+    return ((q - z) * s).t().contiguous().to(out_dtype)
 
 
 Q4_TILE_ROWS, Q4_TILE_K, Q4_TILE_BYTES = 128, 64, 128 * 32 + 128 * 4

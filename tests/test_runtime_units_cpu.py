@@ -451,3 +451,32 @@ def test_q4_tile_records_decode_to_the_dequantised_weight():
                 got[nb * 128:(nb + 1) * 128, kb * 64 + half * 32: kb * 64 + half * 32 + 32] = vals
     assert np.array_equal(got[:n].astype(np.float16), want.astype(np.float16))
     assert not got[n:].any()               # padding rows decode to zero
+
+
+def test_awq_checkpoint_tensors_expand_to_the_dense_weight(tmp_path):
+    """AutoAWQ layout (packed columns in the order 0 2 4 6 1 3 5 7 per word, per-group zero points): the
+    loader offers ``<layer>.weight`` for a (qweight, qzeros, scales) triple."""
+    from safetensors.torch import save_file
+
+    from mlc_llm_b200 import quantization as Q
+    from mlc_llm_b200.loader.huggingface_loader import HFCheckpoint
+
+    torch.manual_seed(9)
+    k, n, g = 256, 64, 128
+    q = torch.randint(0, 16, (k, n))
+    z = torch.randint(0, 16, (k // g, n))
+    s = (torch.rand(k // g, n) * 0.02 + 0.001).half()
+    want = ((q.float() - z.repeat_interleave(g, 0).float()) * s.float().repeat_interleave(g, 0)).t().half()
+    qweight, qzeros = Q.awq_pack(q), Q.awq_pack(z)
+    # spot-check the nibble order: output column 1 of a word sits in bits 16..19
+    assert ((int(qweight[0, 0]) & 0xFFFFFFFF) >> 16) & 0xF == int(q[0, 1])
+    assert torch.equal(Q.awq_dequantize(qweight, qzeros, s), want)
+    save_file({"model.layers.0.mlp.down_proj.qweight": qweight, "model.layers.0.mlp.down_proj.qzeros": qzeros,
+               "model.layers.0.mlp.down_proj.scales": s, "model.norm.weight": torch.ones(n).half()},
+              str(tmp_path / "model.safetensors"))
+    ck = HFCheckpoint(str(tmp_path))
+    assert torch.equal(ck.get("model.layers.0.mlp.down_proj.weight"), want)
+    assert torch.equal(ck.get("model.norm.weight"), torch.ones(n).half())
+    with pytest.raises(ValueError):
+        Q.get("q4f16_ft")
+    assert Q.get("q4f16_autoawq").kind == "no-quant"
