@@ -55,7 +55,8 @@ def _reference_arm():
 
 # The target workloads. prompt_len is (low, high): lengths are uniform in that range.
 WORKLOADS = {
-    "2": dict(model="llama-3-8b", quant="q4f16_1", requests=256, prompt_len=(512, 512), output_len=256),
+    "2": dict(model="llama-3-8b", quant="q4f16_1", requests=256, prompt_len=(512, 512), output_len=256,
+              tp1_check=True),
     "3": dict(model="llama-3-70b", quant="q0bf16", requests=512, prompt_len=(128, 2048), output_len=512),
     "3-fp8": dict(model="llama-3-70b", quant="fp8_e4m3fn_bf16_block_scale", requests=512, prompt_len=(128, 2048),
                   output_len=512),
@@ -133,6 +134,9 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--output-len", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tp1-check", choices=("auto", "on", "off"), default="auto",
+                    help="at N > 1: compare 8 fixed greedy requests with a 1-rank run of the same weights "
+                         "(auto: only for models whose unsharded copy is cheap to build)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return _reference_arm()
@@ -181,6 +185,14 @@ def main(argv=None) -> int:
     gen_cfg = {"max_tokens": args.output_len, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
     vocab_hi = 32000
 
+    # correctness line at N > 1 (outside the timed region): 8 fixed greedy requests, 32 tokens each, through
+    # the N-rank engine and, after the ranks have parted, through a 1-rank engine of the same weights
+    tp1_check = world > 1 and pp == 1 and (args.tp1_check == "on" or
+                                           (args.tp1_check == "auto" and wl.get("tp1_check", False)))
+    check_rng = np.random.default_rng(99)
+    check_prompts = [check_rng.integers(0, vocab_hi, 64).tolist() for _ in range(8)]
+    check_cfg = {"max_tokens": 32, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+
     def make_prompts():
         # fresh prompts every pass so no pass benefits from an earlier one (a shared prefix is shared
         # within a pass only)
@@ -194,7 +206,7 @@ def main(argv=None) -> int:
 
         cfg.model = model
         rt = EngineRuntime(cfg, device, comm=comm)
-        passes = (args.warmup + args.steps) * (1 if args.no_e2e else 2)
+        passes = (args.warmup + args.steps) * (1 if args.no_e2e else 2) + (1 if tp1_check else 0)
         for _ in range(passes):
             comm.barrier()
             torch.cuda.synchronize()
@@ -261,6 +273,16 @@ def main(argv=None) -> int:
     # the native engine's own split of a decode step's host time (ms per decode step, all passes so far)
     native_ms = {k: round(v * 1e3 / max(1, steps_per_pass["num_decode_steps"]), 3)
                  for k, v in steps_per_pass.get("decode_host_seconds", {}).items()}
+
+    check_tokens = None
+    if tp1_check:
+        comm.barrier()
+        _, check_out = eng.generate(check_prompts, check_cfg)
+        check_tokens = [t[0] for t in check_out]
+        torch.cuda.synchronize()
+        comm.shutdown_workers()
+        comm.barrier()
+        comm.max_over_ranks(0.0)
 
     # ------------------------------------------------------------------ end to end, public API
     e2e = None
@@ -332,9 +354,33 @@ def main(argv=None) -> int:
         "engine_steps_per_pass": engine_steps // max(1, args.warmup + args.steps),
         "host_ms_per_engine_step": host_ms, "native_engine_ms_per_decode_step": native_ms,
     }
-    print(json.dumps(line))
     if comm is not None:
         comm.destroy()
+    if check_tokens is not None:
+        import gc
+
+        del eng
+        gc.collect()
+        torch.cuda.empty_cache()
+        os.environ["MLCB_FUSED_TP"] = "0"
+        one = SyncMLCEngine(model, device, engine_config=EngineConfig(
+            mode="server", max_num_sequence=8, prefill_chunk_size=8192, max_total_sequence_length=4096,
+            prefix_cache_mode="disable", gpu_memory_utilization=0.5))
+        _, ref_out = one.generate(check_prompts, check_cfg)
+        prefix = []
+        for a, b in zip(check_tokens, (t[0] for t in ref_out)):
+            n = 0
+            while n < min(len(a), len(b)) and a[n] == b[n]:
+                n += 1
+            prefix.append(n)
+        # the ranks add their partial sums in another order than one GPU does, so with random weights a
+        # sequence can part ways with the 1-rank run at a near-tie and never return: the first token and the
+        # matched prefix length say more than the count of fully equal sequences
+        line["tokens_match_tp1"] = {"requests": len(prefix), "tokens_each": 32,
+                                    "first_token_equal": sum(1 for n in prefix if n >= 1),
+                                    "all_32_equal": sum(1 for n in prefix if n >= 32),
+                                    "matched_prefix_lengths": prefix}
+    print(json.dumps(line))
     return 0
 
 

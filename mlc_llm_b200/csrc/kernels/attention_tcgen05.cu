@@ -54,7 +54,21 @@ struct AttnTcParams {
   int hq, hkv, group;
   float scale_log2;         // sm_scale * log2(e)
   int is_bf16;
+  // masked variant (the EXT instantiation): a position j of the sequence is visible to query token t when
+  //   j <  q_kvlen[t]:  j >= q_kvstart[t] (sliding window / chunk start) or j < sink
+  //   j >= q_kvlen[t]:  bit (j - q_kvlen[t]) of tree_mask[t] is set (token-tree verification: the tree's
+  //                     tokens sit behind the committed prefix, each sees its ancestors and itself)
+  const int* q_kvstart;                  // [T] or null
+  const unsigned long long* tree_mask;   // [T] or null
+  int sink;
+  float cap_pre, cap_log2;  // logit soft-capping: cap_log2 * tanh(raw * cap_pre); cap_log2 == 0 means none
 };
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -80,6 +94,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <bool EXT>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -108,8 +123,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p
   const int qstart = p.tile_qstart[tile];
   const int ntok = p.tile_ntok[tile];
   const int valid_rows = ntok * G;
-  const int kv_max = p.q_kvlen[qstart + ntok - 1];
-  const int nblk = (kv_max + ATT_BLK - 1) / ATT_BLK;
+  int kv_max = p.q_kvlen[qstart + ntok - 1];
+  // blocks of 64 positions the tile visits: all of [0, kv_max) unless a window hides a run of whole blocks
+  // between the sink blocks and the first position any token of the tile still sees
+  int sink_blks = 0, skip = 0;
+  if (EXT) {
+    if (p.tree_mask) {
+      int extra = 0;
+      for (int i = 0; i < ntok; ++i) extra = max(extra, 64 - __clzll(p.tree_mask[qstart + i] | 1ull));
+      kv_max += extra;
+    }
+    if (p.q_kvstart) {
+      int first = p.q_kvstart[qstart];
+      for (int i = 1; i < ntok; ++i) first = min(first, p.q_kvstart[qstart + i]);
+      sink_blks = (p.sink + ATT_BLK - 1) / ATT_BLK;
+      skip = max(0, first / ATT_BLK - sink_blks);
+    }
+  }
+  const int nblk = max(0, (kv_max + ATT_BLK - 1) / ATT_BLK - skip);
+  auto block_of = [&](int j) { return EXT ? (j < sink_blks ? j : j + skip) : j; };
   const int* pages = p.page_indices + p.page_indptr[b];
   const int npages = p.page_indptr[b + 1] - p.page_indptr[b];
 
@@ -152,7 +184,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p
         }
         mbar_expect_tx(&k_full[s], ATT_KV_BYTES);
         for (int pg = 0; pg < ATT_BLK / ATT_PAGE; ++pg) {
-          int pi = j * (ATT_BLK / ATT_PAGE) + pg;
+          int pi = block_of(j) * (ATT_BLK / ATT_PAGE) + pg;
           if (pi >= npages) pi = npages - 1;  // rows past the sequence are masked by the softmax
           int page = pages[pi];
           if (page < 0) page = 0;
@@ -168,7 +200,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p
         }
         mbar_expect_tx(&v_full[s], ATT_KV_BYTES);
         for (int pg = 0; pg < ATT_BLK / ATT_PAGE; ++pg) {
-          int pi = j * (ATT_BLK / ATT_PAGE) + pg;
+          int pi = block_of(j) * (ATT_BLK / ATT_PAGE) + pg;
           if (pi >= npages) pi = npages - 1;
           int page = pages[pi];
           if (page < 0) page = 0;
@@ -249,6 +281,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p
       if (lane == 0) mbar_arrive(q_ready);
     }
     const int kvlen = row_valid ? p.q_kvlen[tok] : 0;
+    int win_start = 0;
+    unsigned long long tmask = 0ull;
+    if (EXT && row_valid) {
+      if (p.q_kvstart) win_start = p.q_kvstart[tok];
+      if (p.tree_mask) tmask = p.tree_mask[tok];
+    }
+    auto visible = [&](int pos) -> bool {
+      if (!EXT) return pos < kvlen;
+      if (pos < kvlen) return pos >= win_start || pos < p.sink;
+      const int r = pos - kvlen;
+      return r < 64 && ((tmask >> r) & 1ull);
+    };
     float m_ref = -INFINITY;   // scaled (log2) reference maximum used for exp2
     float l = 0.f;
     bool ok = true;
@@ -265,13 +309,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p
         tmem_ld32(taddr, r0);
         tmem_ld32(taddr + 32, r1);
         tmem_ld_wait();
-        const int base = j * ATT_BLK;
+        const int base = block_of(j) * ATT_BLK;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          float a = __uint_as_float(r0[c]) * p.scale_log2;
-          float bq = __uint_as_float(r1[c]) * p.scale_log2;
-          a = (base + c < kvlen) ? a : -INFINITY;
-          bq = (base + 32 + c < kvlen) ? bq : -INFINITY;
+          float a, bq;
+          if (EXT && p.cap_log2 != 0.f) {
+            a = p.cap_log2 * tanh_approx(__uint_as_float(r0[c]) * p.cap_pre);
+            bq = p.cap_log2 * tanh_approx(__uint_as_float(r1[c]) * p.cap_pre);
+          } else {
+            a = __uint_as_float(r0[c]) * p.scale_log2;
+            bq = __uint_as_float(r1[c]) * p.scale_log2;
+          }
+          a = visible(base + c) ? a : -INFINITY;
+          bq = visible(base + 32 + c) ? bq : -INFINITY;
           pvals[c] = a;
           pvals[32 + c] = bq;
           mx = fmaxf(mx, fmaxf(a, bq));
@@ -384,11 +434,14 @@ using namespace mlcb;
 
 // kv_pages: one layer's cache [num_pages, 2, hkv, 16, 128]. Tiles are (sequence, query-token range)
 // pairs prepared by the caller; the grid is (tiles, hkv).
+// q_kvstart / tree_mask (either may be null), sink and softcap select the masked instantiation (see
+// AttnTcParams); with all of them absent the plain causal kernel runs.
 MLCB_API int mlcb_attn_tc(const void* q, const void* kv_pages, void* out, float* lse, const int* tile_seq,
                           const int* tile_qstart, const int* tile_ntok, const int* q_kvlen,
                           const int* page_indptr, const int* page_indices, int num_tiles, long long q_stride,
                           int hq, int hkv, long long num_pages, float sm_scale, int dtype, int* status,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const int* q_kvstart, const unsigned long long* tree_mask,
+                          int sink, float softcap) {
   if (num_tiles <= 0) return 0;
   if (hq % hkv) return -1;
   const int group = hq / hkv;
@@ -399,7 +452,8 @@ MLCB_API int mlcb_attn_tc(const void* q, const void* kv_pages, void* out, float*
   if ((q_stride * 2) % 16) return -3;
   static bool attr_set[64] = {};
   if (first_use_on_device(attr_set)) {
-    cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    cudaFuncSetAttribute(attn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    cudaFuncSetAttribute(attn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
   }
   uint64_t dims[2] = {ATT_D, static_cast<uint64_t>(num_pages) * 2 * hkv * ATT_PAGE};
   uint64_t strides[1] = {ATT_D * 2};
@@ -423,8 +477,16 @@ MLCB_API int mlcb_attn_tc(const void* q, const void* kv_pages, void* out, float*
   p.group = group;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.is_bf16 = dtype == 1;
+  p.q_kvstart = q_kvstart;
+  p.tree_mask = tree_mask;
+  p.sink = q_kvstart ? sink : 0;
+  p.cap_pre = softcap > 0.f ? sm_scale / softcap : 0.f;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   dim3 grid(num_tiles, hkv);
-  attn_tc_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(*mkv, p);
+  if (q_kvstart || tree_mask || softcap > 0.f)
+    attn_tc_kernel<true><<<grid, ATT_THREADS, ATT_SMEM, stream>>>(*mkv, p);
+  else
+    attn_tc_kernel<false><<<grid, ATT_THREADS, ATT_SMEM, stream>>>(*mkv, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

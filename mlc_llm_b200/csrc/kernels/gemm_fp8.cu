@@ -12,7 +12,9 @@
 // with the token and the group, so it cannot stay inside one TMEM accumulator: every group is
 // multiplied into a fresh accumulator (two of them take turns) and eight "promotion" warps add it,
 // scaled, to fp32 registers while the tensor core works on the next group (the weight tile is the UMMA
-// A operand, so a thread owns one output feature and 64 of the tile's tokens).
+// A operand, so a thread owns one output feature and 64 of the tile's up to 128 tokens). Measured: a
+// 256-token tile with sixteen promotion warps is slower (0.75 vs 0.96 PFLOP/s at 8192 x 10240 x 8192), the
+// promotion arithmetic then outweighs what the wider tensor-core instruction saves.
 //
 // Roles (320 threads): warp 0 = TMA producer (fp8 weights, fp8 activations, activation scales), warp 1 =
 // MMA issuer (+ TMEM owner), warps 2-9 = promotion / epilogue.
@@ -27,11 +29,12 @@ constexpr int F8_BM = 128;        // weight rows per tile == UMMA M
 constexpr int F8_BK = 128;        // fp8 elements per stage == one scale group == 128 bytes
 constexpr int F8_TN = 128;        // tokens per tile (UMMA N), at most
 constexpr int F8_STAGES = 6;
+constexpr int F8_PROMO = 8;       // promotion warps: two per TMEM lane quarter, 64 token columns each
 constexpr int F8_W_BYTES = F8_BM * F8_BK;   // 16 KiB
 constexpr int F8_X_BYTES = F8_TN * F8_BK;   // 16 KiB
 constexpr int F8_S_BYTES = F8_TN * 4;       // activation scales of the stage's group
 constexpr int F8_STAGE_BYTES = F8_W_BYTES + F8_X_BYTES;
-constexpr int F8_THREADS = 320;
+constexpr int F8_THREADS = 64 + 32 * F8_PROMO;
 constexpr int F8_SMEM = F8_STAGES * (F8_STAGE_BYTES + F8_S_BYTES) + 1024 + 256;
 
 struct Fp8Params {
@@ -44,6 +47,17 @@ struct Fp8Params {
   int tn, num_m_blocks, num_n_blocks;
   int out_dtype;          // 0 fp16, 1 bf16
 };
+
+// 32 lanes x 16 columns of 32-bit values: thread t of the warp gets lane (base_lane + t).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -66,11 +80,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 
   if (threadIdx.x < F8_STAGES) {
     mbar_init(&full[threadIdx.x], 1);
-    mbar_init(&empty[threadIdx.x], 1 + 8);
+    mbar_init(&empty[threadIdx.x], 1 + F8_PROMO);
   }
   if (threadIdx.x < 2) {
     mbar_init(&acc_full[threadIdx.x], 1);
-    mbar_init(&acc_empty[threadIdx.x], 8);
+    mbar_init(&acc_empty[threadIdx.x], F8_PROMO);
   }
   if (threadIdx.x == 0) *abort_flag = 0;
   if (threadIdx.x < 32) mbar_fence_init();
@@ -152,11 +166,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     int s = 0;
     uint32_t ga = 0;
     bool ok = true;
+    __shared__ __align__(16) float comb_all[F8_PROMO][64];
+    float* comb = comb_all[warp - 2];
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int mb = t / p.num_n_blocks, nb = t - mb * p.num_n_blocks;
       const int m0 = mb * p.tn, n = nb * F8_BM + row;
       const int c0 = half * 64;
-      const bool cols_live = c0 < p.tn;  // tiles of 16..64 tokens: the second half has nothing to do
+      const bool cols_live = c0 < p.tn;  // narrow tiles: the warps of the higher column ranges have nothing to do
       float acc[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc[j] = 0.f;
@@ -168,26 +184,33 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        // token scale x weight-block scale of this warp's 64 columns, formed once per column (two per lane)
+        // instead of once per lane and column
+        {
+          const float2 sa2 = *reinterpret_cast<const float2*>(ss + s * F8_TN + c0 + 2 * lane);
+          *reinterpret_cast<float2*>(comb + 2 * lane) = make_float2(sa2.x * swg, sa2.y * swg);
+          __syncwarp();
+        }
         if (cols_live) {
 #pragma unroll
-          for (int c = 0; c < 64; c += 32) {
+          for (int c = 0; c < 64; c += 16) {
             if (c0 + c >= p.tn) continue;
-            uint32_t r[32];
-            tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * F8_TN + c0 + c, r);
+            uint32_t r[16];
+            tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * F8_TN + c0 + c, r);
             tmem_ld_wait();
-            const float4* sv = reinterpret_cast<const float4*>(ss + s * F8_TN + c0 + c);
+            const float4* sv = reinterpret_cast<const float4*>(comb + c);
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
+            for (int j4 = 0; j4 < 4; ++j4) {
               const float4 sa = sv[j4];  // the same address for every lane: a broadcast
-              acc[c + 4 * j4 + 0] = fmaf(__uint_as_float(r[4 * j4 + 0]), sa.x * swg, acc[c + 4 * j4 + 0]);
-              acc[c + 4 * j4 + 1] = fmaf(__uint_as_float(r[4 * j4 + 1]), sa.y * swg, acc[c + 4 * j4 + 1]);
-              acc[c + 4 * j4 + 2] = fmaf(__uint_as_float(r[4 * j4 + 2]), sa.z * swg, acc[c + 4 * j4 + 2]);
-              acc[c + 4 * j4 + 3] = fmaf(__uint_as_float(r[4 * j4 + 3]), sa.w * swg, acc[c + 4 * j4 + 3]);
+              acc[c + 4 * j4 + 0] = fmaf(__uint_as_float(r[4 * j4 + 0]), sa.x, acc[c + 4 * j4 + 0]);
+              acc[c + 4 * j4 + 1] = fmaf(__uint_as_float(r[4 * j4 + 1]), sa.y, acc[c + 4 * j4 + 1]);
+              acc[c + 4 * j4 + 2] = fmaf(__uint_as_float(r[4 * j4 + 2]), sa.z, acc[c + 4 * j4 + 2]);
+              acc[c + 4 * j4 + 3] = fmaf(__uint_as_float(r[4 * j4 + 3]), sa.w, acc[c + 4 * j4 + 3]);
             }
           }
         }
         tc_fence_before();
-        __syncwarp();
+        __syncwarp();  // (also: every lane is done with `comb` before the next group rewrites it)
         if (lane == 0) {
           mbar_arrive(&acc_empty[a]);
           mbar_arrive(&empty[s]);  // the stage's scales have been read

@@ -118,11 +118,25 @@ class DecoderModel:
         """(src, dst) page copies for copy-on-write, applied to every layer."""
         if pairs.numel() == 0:
             return
+        if self.kv_pages.is_cuda and pairs.dtype == torch.int32 and pairs.is_cuda:
+            # one launch for all layers; destinations are freshly allocated pages, so no pair reads what
+            # another writes
+            from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
+            import ctypes  # pylint: disable=import-outside-toplevel
+
+            kv = self.kv_pages
+            es = kv.element_size()
+            check(lib().mlcb_page_copy(ptr(kv), ptr(pairs.contiguous()), ctypes.c_int(pairs.numel() // 2),
+                                       ctypes.c_int(kv.shape[0]), ctypes.c_longlong(kv.stride(1) * es),
+                                       ctypes.c_longlong(kv.stride(0) * es), stream_ptr()), "mlcb_page_copy")
+            return
         src, dst = pairs[0::2].long(), pairs[1::2].long()
         self.kv_pages[:, dst] = self.kv_pages[:, src]
 
     def move_tokens(self, moves: torch.Tensor) -> None:
-        """(src_slot, dst_slot) token moves (tree commit), applied to every layer."""
+        """(src_slot, dst_slot) token moves (tree commit), applied to every layer. A destination may be
+        another move's source (accepted nodes slide towards the front), so all rows are gathered before any
+        is written: indexing does that, one kernel moving rows in place would not."""
         if moves.numel() == 0:
             return
         src, dst = moves[0::2].long(), moves[1::2].long()
@@ -303,7 +317,11 @@ class DecoderModel:
                  and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
                  and c.gated_mlp and c.position_embedding != "learned" and "residual_scale" not in c.extra
                  and "mla" not in c.extra and "llama4" not in c.extra
-                 and self.first_stage and self.last_stage and self.dtype in (torch.float16, torch.bfloat16))
+                 and self.dtype in (torch.float16, torch.bfloat16))
+        # a pipeline stage hands the whole residual stream to the next one: only the all-reduce form keeps it
+        # whole on every rank
+        if not (self.first_stage and self.last_stage) and getattr(fused, "mode", "") != "ar":
+            plain = False
         self.fused = fused if plain else None
         return self.fused is not None
 
@@ -331,10 +349,20 @@ class DecoderModel:
                                    c.norm_weight_offset)
                 g = ops.linear(h, self.p.linears[pre + "mlp.gate_up_proj"])
                 a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
-                nxt = f"model.layers.{layers[pos + 1]}.input_layernorm" if pos + 1 < len(layers) else "model.norm"
+                if pos + 1 < len(layers):
+                    nxt = f"model.layers.{layers[pos + 1]}.input_layernorm"
+                elif self.last_stage:
+                    nxt = "model.norm"
+                else:
+                    # the next stage normalises with its own first layer's weight; this call's norm output is
+                    # not used, only the residual it leaves behind
+                    nxt = pre + "post_attention_layernorm"
                 h = f.gemm_ar_norm(a, self.p.linears[pre + "mlp.down_proj"], self.p.tensors[nxt + ".weight"],
                                    c.rms_norm_eps, c.norm_weight_offset)
             f.end()
+            if not self.last_stage:
+                self._final_normed = None
+                return f.residual[: x.shape[0]].clone()
             self._final_normed = h
             return h
         h = self._norm(x, f"model.layers.{layers[0]}.input_layernorm")

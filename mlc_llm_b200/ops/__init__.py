@@ -296,14 +296,16 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
         return res.reshape(t, hq * d)
     out = torch.empty(t, hq * d, dtype=q.dtype, device=q.device)
     lse = torch.empty(t, hq, dtype=torch.float32, device=q.device) if return_lse else None
-    if plan is not None and plan.use_tensor_core and tree_mask is None and softcap == 0.0 \
-            and q_kvstart is None and d == 128 and page == 16 and q.dtype in (torch.float16, torch.bfloat16):
+    masked = tree_mask is not None or softcap != 0.0 or q_kvstart is not None
+    if plan is not None and plan.use_tensor_core and d == 128 and page == 16 \
+            and q.dtype in (torch.float16, torch.bfloat16) and not (masked and plan.num_dec):
         from .attention import attention_decode, attention_tcgen05  # pylint: disable=import-outside-toplevel
 
         if plan.num_dec:
             attention_decode(q, kv_pages, out, lse, plan, hq, hkv, sm_scale)
         if plan.num_tiles:
-            attention_tcgen05(q, kv_pages, out, lse, plan, hq, hkv, sm_scale)
+            attention_tcgen05(q, kv_pages, out, lse, plan, hq, hkv, sm_scale, q_kvstart=q_kvstart, sink=sink,
+                              tree_mask=tree_mask, softcap=softcap)
     else:
         rc = lib().mlcb_attn_simt(ptr(q), ptr(kv_pages), ptr(out), ptr(lse), ptr(q_seq), ptr(q_kvlen),
                                   ptr(q_kvstart), ptr(tree_mask), ptr(page_indptr), ptr(page_indices),

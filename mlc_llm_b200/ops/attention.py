@@ -12,18 +12,21 @@ import torch
 from ._lib import DTYPE_CODE, check, lib, ptr, status_word, stream_ptr
 
 
-def build_tiles(q_indptr: np.ndarray, group: int) -> Dict[str, np.ndarray]:
+def build_tiles(q_indptr: np.ndarray, group: int, decode_items: bool = True) -> Dict[str, np.ndarray]:
     """Split the appended tokens of a batch into work items for the two attention kernels.
 
     Sequences whose chunk fits 16 query rows (``tokens * group <= 16``: decode and short verify
     chunks) become one item each for the decode kernel (``dec_seq``, ``dec_qstart``, ``dec_ntok``).
     The others are cut into tiles of ``128 // group`` tokens for the tcgen05 kernel (``tile_seq``,
     ``tile_qstart``, ``tile_ntok``). All arrays are int32; ``*_qstart`` are global token indices.
+    ``decode_items=False`` sends every sequence to the tcgen05 kernel: the forwards that need its masked
+    variant (windows, sinks, soft-capping, token trees), which the decode kernel does not have.
     """
     tpt = max(1, 128 // group)
     q_indptr = np.asarray(q_indptr, dtype=np.int64)
     lens_all = np.diff(q_indptr)
-    small = (lens_all * group <= 16) & (lens_all > 0) if group <= 16 else np.zeros(len(lens_all), bool)
+    small = (lens_all * group <= 16) & (lens_all > 0) if group <= 16 and decode_items \
+        else np.zeros(len(lens_all), bool)
     dec_idx = np.nonzero(small)[0]
     out = {"dec_seq": dec_idx.astype(np.int32), "dec_qstart": q_indptr[dec_idx].astype(np.int32),
            "dec_ntok": lens_all[dec_idx].astype(np.int32)}
@@ -62,14 +65,17 @@ class AttentionPlan:
 
 def attention_tcgen05(q: torch.Tensor, kv_pages: torch.Tensor, out: torch.Tensor,
                       lse: Optional[torch.Tensor], plan: AttentionPlan, hq: int, hkv: int,
-                      sm_scale: float) -> None:
-    """``q``: [T, hq*128] view (row stride may be larger); ``kv_pages``: one layer's cache."""
+                      sm_scale: float, q_kvstart: Optional[torch.Tensor] = None, sink: int = 0,
+                      tree_mask: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+    """``q``: [T, hq*128] view (row stride may be larger); ``kv_pages``: one layer's cache.
+    ``q_kvstart`` (+ ``sink``), ``tree_mask`` and ``softcap`` select the kernel's masked variant."""
     rc = lib().mlcb_attn_tc(ptr(q), ptr(kv_pages), ptr(out), ptr(lse), ptr(plan.tile_seq),
                             ptr(plan.tile_qstart), ptr(plan.tile_ntok), ptr(plan.q_kvlen),
                             ptr(plan.page_indptr), ptr(plan.page_indices), ctypes.c_int(plan.num_tiles),
                             ctypes.c_longlong(q.stride(0)), ctypes.c_int(hq), ctypes.c_int(hkv),
                             ctypes.c_longlong(kv_pages.shape[0]), ctypes.c_float(sm_scale),
-                            ctypes.c_int(DTYPE_CODE[q.dtype]), ptr(status_word(q.device)), stream_ptr())
+                            ctypes.c_int(DTYPE_CODE[q.dtype]), ptr(status_word(q.device)), stream_ptr(),
+                            ptr(q_kvstart), ptr(tree_mask), ctypes.c_int(int(sink)), ctypes.c_float(float(softcap)))
     check(rc, "mlcb_attn_tc")
 
 

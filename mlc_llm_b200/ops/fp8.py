@@ -26,9 +26,11 @@ _W8A8_MIN_TOKENS = 17
 
 def act_quant_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """``x [M, K]`` (fp16 / bf16) -> (e4m3 ``[M, K]``, fp32 scales ``[K / 128, ld]``, transposed, one per row
-    and 128-element group: ``max(|x|, 1e-10) / 448``).  ``ld`` is M rounded up to 128."""
+    and 128-element group: ``max(|x|, 1e-10) / 448``).  ``ld`` >= M leaves room for the last token tile."""
     m, k = x.shape
-    ld = (m + 127) // 128 * 128
+    # the GEMM reads one contiguous run of scales per token tile (up to 256 tokens, tile count x tile width
+    # can exceed M by a sixteenth): leave that room
+    ld = (m + m // 16 + 256 + 127) // 128 * 128
     xq = torch.empty(m, k, dtype=torch.float8_e4m3fn, device=x.device)
     scale_t = torch.zeros((k + 127) // 128, ld, dtype=torch.float32, device=x.device)
     x2 = x if x.stride(-1) == 1 else x.contiguous()

@@ -43,6 +43,48 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
+def graph_bucket(n: int) -> int:
+    """Batch size a decode step of ``n`` sequences is padded to before it is run from a CUDA graph: the next
+    power of two up to 32, then the next multiple of 16. A serving trace whose batch drifts by a few
+    sequences per step then replays a handful of graphs instead of capturing one per batch size."""
+    if n <= 32:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+    return (n + 15) // 16 * 16
+
+
+def pad_decode_arrays(arrays: Dict[str, np.ndarray], target: int) -> None:
+    """Append ``target - n`` stand-in sequences to the packed arrays of a pure decode step (in place).
+
+    A stand-in feeds token 0 at position 0, appends nothing to the cache (slot -1) and attends to the first
+    token of page 0, so its row stays finite and nothing it computes is read: the sampling rows index
+    the real sequences only."""
+    n = int(arrays["q_indptr"].size) - 1
+    extra = target - n
+    if extra <= 0:
+        return
+    i32 = np.int32
+
+    def cat(key, tail):
+        arrays[key] = np.concatenate([arrays[key], np.asarray(tail, dtype=i32)])
+
+    cat("token_ids", np.zeros(extra))
+    cat("positions", np.zeros(extra))
+    cat("slots", np.full(extra, -1))
+    cat("q_seq", np.arange(n, target))
+    cat("q_kvlen", np.ones(extra))
+    last = int(arrays["page_indptr"][-1])
+    cat("page_indptr", last + 1 + np.arange(extra))
+    cat("page_indices", np.zeros(extra))
+    cat("q_indptr", n + 1 + np.arange(extra))
+    cat("seq_lens", np.ones(extra))
+    cat("append_lens", np.ones(extra))
+    if "token_src" in arrays:
+        cat("token_src", np.full(extra, -1))
+
+
 class FeatureStore:
     """Target-model features (final-normed hidden states) of the positions that a speculative draft
     head (EAGLE, Medusa) has not consumed yet, per sequence, plus the head's own latest prediction.
@@ -186,8 +228,10 @@ class ModelExecutor:
         # not complete under capture in a two-rank run and stays on eager launches.
         self.use_graphs = device.type == "cuda" and os.environ.get("MLCB_CUDA_GRAPH", "1") != "0"
         self._graphs: Dict[tuple, dict] = {}
+        self.graph_buckets = os.environ.get("MLCB_GRAPH_BUCKETS", "1") != "0"
         self._graph_pool = None
         self.graph_replays = 0
+        self.graph_eligible_steps = 0  # steps that could run from a graph (replayed, captured or first seen)
         self._nvtx = device.type == "cuda" and os.environ.get("MLCB_NVTX", "0") == "1"
         # speculative draft heads fed with the target's features: model id -> "eagle" | "medusa"
         self.spec_heads: Dict[int, str] = {}
@@ -251,8 +295,7 @@ class ModelExecutor:
             b.q_indptr = qi
             b.start_positions = np.asarray([int(pos[qi[i]]) if qi[i + 1] > qi[i] else 0
                                             for i in range(len(qi) - 1)])
-        if "tile_seq" in dev and self._tc_attention_ok(model) and b.tree_mask is None \
-                and b.q_kvstart is None:
+        if "tile_seq" in dev and self._tc_attention_ok(model):
             from ..ops.attention import AttentionPlan  # pylint: disable=import-outside-toplevel
 
             from ..ops.attention import choose_splits  # pylint: disable=import-outside-toplevel
@@ -269,8 +312,13 @@ class ModelExecutor:
 
     def _tc_attention_ok(self, model: DecoderModel) -> bool:
         return (self.use_tensor_core_attention and model.d == 128 and model.page == 16
-                and model.cfg.layer_attn_kinds is None and model.cfg.attn_logit_softcap == 0
                 and model.kv_dtype in (torch.float16, torch.bfloat16))
+
+    @staticmethod
+    def _masked_attention(model: DecoderModel) -> bool:
+        """Models some of whose layers always need the masked attention variant (windows or chunks per
+        layer, logit soft-capping)."""
+        return model.cfg.layer_attn_kinds is not None or model.cfg.attn_logit_softcap != 0
 
     def _pack(self, plan: dict, token_ids: np.ndarray, sp: Optional[dict], model_id: int = 0
               ) -> Dict[str, np.ndarray]:
@@ -279,10 +327,15 @@ class ModelExecutor:
             arrays[k] = np.ascontiguousarray(plan[k], dtype=np.int32)
         arrays["tree_mask"] = np.ascontiguousarray(plan["tree_mask"], dtype=np.uint64).view(np.int64)
         model = self.models[model_id]
-        if self._tc_attention_ok(model) and arrays["tree_mask"].size == 0 and arrays["q_kvstart"].size == 0:
+        if self._pads_decode(model_id, arrays):
+            pad_decode_arrays(arrays, graph_bucket(int(arrays["q_indptr"].size) - 1))
+        if self._tc_attention_ok(model):
             from ..ops.attention import build_tiles  # pylint: disable=import-outside-toplevel
 
-            arrays.update(build_tiles(arrays["q_indptr"], model.hq // model.hkv))
+            # the decode kernel has no masked variant: windows, trees and soft-capping go to the tcgen05 kernel
+            plain = (arrays["tree_mask"].size == 0 and arrays["q_kvstart"].size == 0
+                     and not self._masked_attention(model))
+            arrays.update(build_tiles(arrays["q_indptr"], model.hq // model.hkv, decode_items=plain))
         if sp is not None:
             for k in _S_INT:
                 arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.int32)
@@ -290,12 +343,35 @@ class ModelExecutor:
                 arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.float32)
         return arrays
 
+    def _graph_candidate(self, model_id: int) -> bool:
+        """What a model must be for any of its steps to run from a CUDA graph (see ``_graph_ok``)."""
+        model = self.models[model_id]
+        multi = self.comm is not None and self.comm.world_size > 1
+        if multi and getattr(model, "fused", None) is None:
+            return False
+        return (self.use_graphs and not self._pipeline(model_id) and getattr(model, "ep", None) is None
+                and not getattr(model, "stateful", False) and self._tc_attention_ok(model)
+                and not self._masked_attention(model))
+
+    def _pads_decode(self, model_id: int, arrays: Dict[str, np.ndarray]) -> bool:
+        """Pure decode steps (one appended token per sequence, no tree, window or copy-on-write) of a model
+        that runs from graphs are padded to a bucket size (``MLCB_GRAPH_BUCKETS=0`` keeps exact shapes)."""
+        if not self.graph_buckets or not self._graph_candidate(model_id):
+            return False
+        qi = arrays["q_indptr"]
+        n = int(qi.size) - 1
+        model = self.models[model_id]
+        return (n > 0 and int(qi[-1]) == n and arrays["token_ids"].size == n
+                and arrays["tree_mask"].size == 0 and arrays["q_kvstart"].size == 0
+                and arrays["page_copies"].size == 0 and (model.hq // model.hkv) <= 16)
+
     def _run_model(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor],
                    embed_handles: Optional[np.ndarray]) -> torch.Tensor:
         model = self.models[model_id]
         if dev["page_copies"].numel():
             model.copy_pages(dev["page_copies"])
         if self._graph_ok(model_id, dev, embed_handles):
+            self.graph_eligible_steps += 1
             return self._run_graph(model_id, plan, dev)
         return self._run_eager(model_id, plan, dev, embed_handles)
 
@@ -306,15 +382,10 @@ class ModelExecutor:
         launches then depends on the batch shape only.  Across ranks only the fused tensor-parallel
         forward is captured: its collectives are this library's kernels over peer memory (call numbers
         come from device memory), so the graph holds no NCCL call."""
-        model = self.models[model_id]
-        multi = self.comm is not None and self.comm.world_size > 1
-        if multi and getattr(model, "fused", None) is None:
-            return False
-        return (self.use_graphs and embed_handles is None and not self._pipeline(model_id)
-                and getattr(model, "ep", None) is None and not getattr(model, "stateful", False)
+        return (self._graph_candidate(model_id) and embed_handles is None
                 and "dec_seq" in dev and dev["dec_seq"].numel() > 0 and dev["tile_seq"].numel() == 0
                 and dev["page_copies"].numel() == 0 and dev["tree_mask"].numel() == 0
-                and dev["q_kvstart"].numel() == 0 and self._tc_attention_ok(model))
+                and dev["q_kvstart"].numel() == 0)
 
     def _run_graph(self, model_id: int, plan: dict, dev: Dict[str, torch.Tensor]) -> torch.Tensor:
         from ..ops.attention import choose_splits  # pylint: disable=import-outside-toplevel
@@ -328,7 +399,7 @@ class ModelExecutor:
         if entry is None:
             # first sight of a shape: run it eagerly (lazy one-time set-up must not happen under capture;
             # every rank takes the same decision from the same broadcast arrays)
-            if len(self._graphs) >= 32:
+            if len(self._graphs) >= 64:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = {"graph": None}
             return self._run_eager(model_id, plan, dev, None)
@@ -523,8 +594,10 @@ class ModelExecutor:
         ht, clock = self.host_times, time.perf_counter
         t0 = clock()
         arrays = self._pack(plan, token_ids, sp, model_id)
-        arrays["token_src"] = np.ascontiguousarray(token_src, dtype=np.int32)
-        feed = bool((arrays["token_src"] >= 0).any())
+        src = np.ascontiguousarray(token_src, dtype=np.int32)
+        pad = int(arrays["token_ids"].size) - int(src.size)  # stand-in sequences of a padded decode batch
+        arrays["token_src"] = np.concatenate([src, np.full(pad, -1, np.int32)]) if pad > 0 else src
+        feed = bool((src >= 0).any())
         t1 = clock()
         if self.comm is not None:
             self.comm.broadcast_step("forward_async", model_id,

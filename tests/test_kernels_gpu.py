@@ -664,3 +664,97 @@ def test_bounded_device_wait_reports_through_the_status_word():
     x = torch.randn(8, 64, device=dev, dtype=torch.float16)
     y = ops.rmsnorm(x, torch.ones(64, device=dev, dtype=torch.float16), 1e-5, 0.0)
     assert torch.isfinite(y).all()
+
+
+@pytest.mark.gpu
+def test_page_copy_all_layers_one_launch():
+    """Copy-on-write page copies: (src, dst) pairs applied to every layer by one kernel, against indexing."""
+    import ctypes
+
+    from mlc_llm_b200.ops._lib import check, lib, ptr, stream_ptr
+
+    torch.manual_seed(0)
+    kv = torch.randn(3, 20, 2, 4, 16, 128, device="cuda", dtype=torch.float16)
+    pairs = torch.tensor([1, 7, 3, 9, 1, 12], dtype=torch.int32, device="cuda")
+    want = kv.clone()
+    want[:, pairs[1::2].long()] = want[:, pairs[0::2].long()]
+    es = kv.element_size()
+    check(lib().mlcb_page_copy(ptr(kv), ptr(pairs), ctypes.c_int(3), ctypes.c_int(kv.shape[0]),
+                               ctypes.c_longlong(kv.stride(1) * es), ctypes.c_longlong(kv.stride(0) * es),
+                               stream_ptr()), "mlcb_page_copy")
+    torch.cuda.synchronize()
+    assert torch.equal(kv, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (16, 2), (4, 4)])
+@pytest.mark.parametrize("case", ["window", "window_sink", "softcap", "tree", "tree_window_softcap", "decode_window"])
+def test_attention_tcgen05_masked(dtype, hq, hkv, case):
+    """Windows (with and without sinks, whole blocks skipped), logit soft-capping and token-tree masks on the
+    tensor-core kernel, against the fp32 reference of the same visibility rule."""
+    from mlc_llm_b200.ops.attention import AttentionPlan, build_tiles
+
+    torch.manual_seed(12)
+    d, page = 128, 16
+    window = sink = 0
+    softcap = 0.0
+    tree = None
+    if case in ("window", "window_sink"):
+        lens, appended = [700, 90, 300, 1500], [130, 90, 5, 1]
+        window, sink = 256, (0 if case == "window" else 70)
+    elif case == "decode_window":
+        lens, appended = [900, 40, 257, 513, 2000], [1, 1, 1, 1, 1]
+        window, sink = 256, 4
+    elif case == "softcap":
+        lens, appended = [200, 77, 300], [200, 3, 1]
+        softcap = 30.0
+    else:
+        # token trees of 5, 7 and 3 nodes behind prefixes of 300, 61 and 0 tokens
+        parents = [[-1, 0, 0, 1, 3], [-1, -1, 0, 1, 1, 4, 2], [-1, 0, 1]]
+        prefix = [300, 61, 0]
+        appended = [len(p) for p in parents]
+        lens = [a + b for a, b in zip(prefix, appended)]
+        tree = parents
+        if case == "tree_window_softcap":
+            window, sink, softcap = 128, 16, 20.0
+    kv, indptr, indices = _mk_paged(len(lens), lens, hkv, d, page, dtype)
+    q_seq, q_kvlen, q_indptr, masks = [], [], [0], []
+    for b, (l, a) in enumerate(zip(lens, appended)):
+        node_masks = []
+        for i in range(a):
+            q_seq.append(b)
+            if tree is None:
+                q_kvlen.append(l - a + i + 1)
+            else:
+                q_kvlen.append(l - a)
+                par = tree[b][i]
+                node_masks.append((node_masks[par] if par >= 0 else 0) | (1 << i))
+        masks.extend(node_masks)
+        q_indptr.append(len(q_seq))
+    t = len(q_seq)
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d) * (3.0 if softcap else 0.7)).to(dtype)
+    q_seq = torch.tensor(q_seq, dtype=torch.int32)
+    q_kvlen = torch.tensor(q_kvlen, dtype=torch.int32)
+    kvstart = torch.clamp(q_kvlen - window, min=0).to(torch.int32) if window else None
+    tmask = torch.tensor(masks, dtype=torch.int64) if tree is not None else None
+    scale = d ** -0.5
+    o_ref, lse_ref = ops.paged_attention(qkv[:, : hq * d], kv, q_seq, q_kvlen, indptr, indices, hq, hkv, d,
+                                         page, scale, q_kvstart=kvstart, sink=sink, tree_mask=tmask,
+                                         softcap=softcap, return_lse=True)
+    tiles = build_tiles(np.asarray(q_indptr), hq // hkv, decode_items=False)
+    assert len(tiles["dec_seq"]) == 0
+    dev = lambda a: torch.as_tensor(a).to(DEV)
+    plan = AttentionPlan(dev(tiles["tile_seq"]), dev(tiles["tile_qstart"]), dev(tiles["tile_ntok"]),
+                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]))
+    qg = qkv.to(DEV)
+    from mlc_llm_b200.ops._lib import lib
+
+    lib().mlcb_launch_count.restype = __import__("ctypes").c_longlong
+    o, lse = ops.paged_attention(qg[:, : hq * d], kv.to(DEV), q_seq.to(DEV), q_kvlen.to(DEV), indptr.to(DEV),
+                                 indices.to(DEV), hq, hkv, d, page, scale,
+                                 q_kvstart=None if kvstart is None else kvstart.to(DEV), sink=sink,
+                                 tree_mask=None if tmask is None else tmask.to(DEV), softcap=softcap,
+                                 return_lse=True, plan=plan)
+    ops.check_status(qg.device)
+    _close(o, o_ref, 2e-2, 2e-2)
+    _close(lse, lse_ref, 1e-2, 1e-2)

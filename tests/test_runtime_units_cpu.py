@@ -480,3 +480,35 @@ def test_awq_checkpoint_tensors_expand_to_the_dense_weight(tmp_path):
     with pytest.raises(ValueError):
         Q.get("q4f16_ft")
     assert Q.get("q4f16_autoawq").kind == "no-quant"
+
+
+def test_decode_batches_are_padded_to_graph_buckets():
+    """Stand-in sequences appended to a pure decode step: consistent index arrays, nothing written to the
+    cache (slot -1), one readable token each."""
+    import numpy as np
+
+    from mlc_llm_b200.serve.executor import graph_bucket, pad_decode_arrays
+
+    assert [graph_bucket(n) for n in range(1, 10)] == [1, 2, 4, 4, 8, 8, 8, 8, 16]
+    assert graph_bucket(33) == 48 and graph_bucket(256) == 256 and graph_bucket(257) == 272
+    n = 5
+    i32 = np.int32
+    arrays = {
+        "token_ids": np.arange(10, 10 + n, dtype=i32), "positions": np.array([7, 3, 20, 1, 16], i32),
+        "slots": np.array([23, 35, 68, 81, 96], i32), "q_seq": np.arange(n, dtype=i32),
+        "q_kvlen": np.array([8, 4, 21, 2, 17], i32), "page_indptr": np.array([0, 1, 2, 4, 5, 7], i32),
+        "page_indices": np.array([1, 2, 3, 4, 5, 6, 7], i32), "q_indptr": np.arange(n + 1, dtype=i32),
+        "seq_lens": np.array([8, 4, 21, 2, 17], i32), "append_lens": np.ones(n, i32),
+        "token_src": np.array([0, -1, 2, 3, -1], i32),
+    }
+    before = {k: v.copy() for k, v in arrays.items()}
+    pad_decode_arrays(arrays, graph_bucket(n))
+    for k, v in before.items():
+        assert (arrays[k][: v.size] == v).all() and arrays[k].dtype == i32
+    assert arrays["token_ids"].size == 8 and arrays["q_indptr"].tolist() == list(range(9))
+    assert arrays["slots"][n:].tolist() == [-1] * 3 and arrays["token_src"][n:].tolist() == [-1] * 3
+    assert arrays["page_indptr"].tolist() == [0, 1, 2, 4, 5, 7, 8, 9, 10]
+    assert arrays["page_indices"].size == 10 and arrays["q_kvlen"][n:].tolist() == [1, 1, 1]
+    assert arrays["q_seq"].tolist() == list(range(8))
+    pad_decode_arrays(arrays, 8)  # already at the bucket: unchanged
+    assert arrays["token_ids"].size == 8
