@@ -59,6 +59,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--apply-chat-template", action="store_true")
+    p.add_argument("--loogle-task", type=str, default="shortdep_qa",
+                   help="LooGLE test set: shortdep_qa, longdep_qa, longdep_summarization or shortdep_cloze")
     p.add_argument("--num-process-workers", type=int, default=None)
     p.add_argument("--disable-tqdm", action="store_true")
     p.add_argument("--max-schedule-gap", type=float, default=0.5)

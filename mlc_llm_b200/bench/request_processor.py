@@ -5,6 +5,7 @@ timestamp replay) and the metric analyser."""
 from __future__ import annotations
 
 import asyncio
+import copy
 import random
 import time
 from typing import Callable, List, Optional
@@ -20,6 +21,16 @@ class RequestProcessor:
         raise NotImplementedError
 
 
+def _each(records):
+    """Every record that is sent: plain ones and the members of groups."""
+    for r in records:
+        members = getattr(r, "records", None)
+        if members is None:
+            yield r
+        else:
+            yield from members
+
+
 class SampleRequests(RequestProcessor):
     def __init__(self, num_requests: int, take_first_x_requests: bool = False):
         self.n, self.first = num_requests, take_first_x_requests
@@ -28,7 +39,7 @@ class SampleRequests(RequestProcessor):
         if len(records) < self.n:
             # recycle when the dataset is smaller than the run
             records = [records[i % len(records)] for i in range(self.n)]
-            records = [RequestRecord(**{**r.__dict__}) for r in records]
+            records = [copy.deepcopy(r) for r in records]
         elif self.first:
             records = records[: self.n]
         else:
@@ -43,7 +54,7 @@ class AttachModelName(RequestProcessor):
         self.model = model
 
     def __call__(self, records):
-        for r in records:
+        for r in _each(records):
             r.chat_cmpl["model"] = self.model
         return records
 
@@ -53,7 +64,7 @@ class AttachSamplingOptions(RequestProcessor):
         self.t, self.p, self.ignore_eos = temperature, top_p, ignore_eos
 
     def __call__(self, records):
-        for r in records:
+        for r in _each(records):
             r.chat_cmpl["temperature"] = self.t
             r.chat_cmpl["top_p"] = self.p
             r.chat_cmpl.setdefault("frequency_penalty", 0.0)
@@ -130,6 +141,19 @@ class Executor(RequestProcessor):
         self.disable_tqdm = disable_tqdm
 
 
+async def _send(ep, rec) -> List[RequestRecord]:
+    """One record through the endpoint; the members of a group go in order, one at a time."""
+    members = getattr(rec, "records", None)
+    if members is None:
+        return [await ep(rec)]
+    out = []
+    for m in members:
+        if m.timestamp is None:
+            m.timestamp = rec.timestamp
+        out.append(await ep(m))
+    return out
+
+
 class FixedConcurrentRequestExecutor(Executor):
     """Keeps ``num_concurrent`` requests in flight until the workload is exhausted."""
 
@@ -145,7 +169,7 @@ class FixedConcurrentRequestExecutor(Executor):
                 async def worker():
                     while queue:
                         rec = queue.pop()
-                        done.append(await ep(rec))
+                        done.extend(await _send(ep, rec))
 
                 await asyncio.gather(*[worker() for _ in range(min(self.n, len(records)))])
             return done
@@ -169,9 +193,9 @@ class FixTimestampExecutor(Executor):
                     delay = (rec.timestamp or 0.0) - (time.monotonic() - t0)
                     if delay > 0:
                         await asyncio.sleep(delay)
-                    return await ep(rec)
+                    return await _send(ep, rec)
 
-                return list(await asyncio.gather(*[fire(r) for r in records]))
+                return [r for group in await asyncio.gather(*[fire(r) for r in records]) for r in group]
 
         return asyncio.run(run())
 

@@ -50,6 +50,15 @@ class RequestRecord:
     input_token_ids: Optional[List[int]] = None  # token-id prompts go to /v1/completions
 
 
+@dataclasses.dataclass
+class GroupedRequestRecord(RequestRecord):
+    """Requests that belong together (the questions on one long document, the turns of one agent trace):
+    an executor sends them one after the other from the same worker, so each can reuse the KV prefix the
+    previous one left in the server (reference: ``GroupedRequestRecord``, ``bench/request_record.py``)."""
+
+    records: List[RequestRecord] = dataclasses.field(default_factory=list)
+
+
 _QUANTILES = (25, 50, 75, 90, 95, 99)
 
 

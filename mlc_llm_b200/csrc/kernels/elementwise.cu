@@ -57,6 +57,95 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual
   }
 }
 
+// ------------------------------------------------------------------ LayerNorm (+ residual add)
+// One CTA per token: out = (v - mean(v)) * rsqrt(var(v) + eps) * w + b, with v = x (+ residual, written
+// back). `b` may be null. Statistics in fp32 from the row kept in shared memory (two passes over smem,
+// one over global memory).
+template <typename T, bool ADD>
+__global__ void layernorm_kernel(const T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ w,
+                                 const T* __restrict__ b, T* __restrict__ out, int hidden, float eps) {
+  extern __shared__ float row[];  // hidden floats + 32 scratch
+  float* scratch = row + hidden;
+  const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+  float sum = 0.f;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + base + i);
+    const T* xe = reinterpret_cast<const T*>(&xv);
+    float v[8];
+    if (ADD) {
+      uint4 rv = *reinterpret_cast<const uint4*>(residual + base + i);
+      const T* re = reinterpret_cast<const T*>(&rv);
+      T o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = Cvt<T>::from_f(Cvt<T>::to_f(xe[j]) + Cvt<T>::to_f(re[j]));
+        v[j] = Cvt<T>::to_f(o[j]);
+      }
+      *reinterpret_cast<uint4*>(residual + base + i) = *reinterpret_cast<uint4*>(o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = Cvt<T>::to_f(xe[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      row[i + j] = v[j];
+      sum += v[j];
+    }
+  }
+  const float mean = block_sum(sum, scratch) / hidden;
+  float sq = 0.f;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float dlt = row[i + j] - mean;  // each thread re-reads only what it wrote
+      sq += dlt * dlt;
+    }
+  }
+  __syncthreads();  // block_sum's scratch is reused
+  const float inv = rsqrtf(block_sum(sq, scratch) / hidden + eps);
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+    const T* we = reinterpret_cast<const T*>(&wv);
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (b) bv = *reinterpret_cast<const uint4*>(b + i);
+    const T* be = reinterpret_cast<const T*>(&bv);
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      o[j] = Cvt<T>::from_f((row[i + j] - mean) * inv * Cvt<T>::to_f(we[j]) + (b ? Cvt<T>::to_f(be[j]) : 0.f));
+    *reinterpret_cast<uint4*>(out + base + i) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ------------------------------------------------------------------ plain activations
+// out = act(in), elementwise. act: 0 = SiLU, 1 = GELU(tanh), 2 = GELU(erf), 3 = relu(x)^2.
+template <typename T>
+__global__ void act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total_vec, int act) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_vec; v += stride) {
+    uint4 xv = *reinterpret_cast<const uint4*>(in + v * 8);
+    const T* xe = reinterpret_cast<const T*>(&xv);
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = Cvt<T>::to_f(xe[j]);
+      float r;
+      if (act == 0) {
+        r = a / (1.f + __expf(-a));
+      } else if (act == 1) {
+        r = 0.5f * a * (1.f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+      } else if (act == 2) {
+        r = 0.5f * a * (1.f + erff(a * 0.7071067811865476f));
+      } else {
+        const float p = fmaxf(a, 0.f);
+        r = p * p;
+      }
+      o[j] = Cvt<T>::from_f(r);
+    }
+    *reinterpret_cast<uint4*>(out + v * 8) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
 // ------------------------------------------------------------------ SiLU(gate) * up
 // in: [T, 2*I] (gate half then up half), out: [T, I]. act: 0 = SiLU, 1 = GELU(tanh).
 template <typename T>
@@ -397,6 +486,46 @@ MLCB_API int mlcb_rmsnorm(const void* x, void* residual, const void* w, void* ou
     LAUNCH(__nv_bfloat16)
   }
 #undef LAUNCH
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_layernorm(const void* x, void* residual, const void* w, const void* b, void* out, int tokens,
+                            int hidden, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden % 8) return -1;
+  int threads = hidden / 8;
+  if (threads > 1024) threads = 1024;
+  threads = (threads + 31) / 32 * 32;
+  const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+#define LAUNCH(T)                                                                                         \
+  if (residual)                                                                                           \
+    layernorm_kernel<T, true><<<tokens, threads, smem, stream>>>((const T*)x, (T*)residual, (const T*)w,  \
+                                                                 (const T*)b, (T*)out, hidden, eps);      \
+  else                                                                                                    \
+    layernorm_kernel<T, false><<<tokens, threads, smem, stream>>>((const T*)x, nullptr, (const T*)w,      \
+                                                                  (const T*)b, (T*)out, hidden, eps);
+  if (dtype == 0) {
+    LAUNCH(__half)
+  } else {
+    LAUNCH(__nv_bfloat16)
+  }
+#undef LAUNCH
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_act(const void* in, void* out, long long elems, int act, int dtype, cudaStream_t stream) {
+  if (elems <= 0) return 0;
+  if (elems % 8) return -1;
+  const size_t total = static_cast<size_t>(elems / 8);
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  if (dtype == 0)
+    act_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)in, (__half*)out, total, act);
+  else
+    act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, total, act);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

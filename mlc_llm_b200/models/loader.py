@@ -136,7 +136,10 @@ def random_params(cfg: ModelConfig, quant: Q.Quantization, seed: int, device: to
     """Weights ~ N(0, std) (norm weights = 1 - offset, biases = 0), identical on every rank before
     sharding because each tensor has its own generator seeded by (seed, name)."""
     layers = layers if layers is not None else range(cfg.num_hidden_layers)
-    gen_device = gen_device or device
+    # CPU and CUDA generators give different streams: MLCB_RANDOM_INIT_DEVICE=cpu makes a GPU run and a CPU
+    # run of the same seed hold the same weights (numerics tests against a CPU oracle)
+    forced = os.environ.get("MLCB_RANDOM_INIT_DEVICE")
+    gen_device = torch.device(forced) if forced else (gen_device or device)
     store = ParamStore()
     biases: Dict[str, torch.Tensor] = {}
     ep = cfg.expert_parallel and tp > 1

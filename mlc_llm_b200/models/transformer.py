@@ -154,7 +154,7 @@ class DecoderModel:
                 w = torch.ones(x.shape[-1], dtype=x.dtype, device=x.device)
             elif c.norm_weight_offset:
                 w = w + c.norm_weight_offset  # "LayerNorm1P": the stored weight is the deviation from one
-            return ops.reference.layernorm(x, w, b, c.rms_norm_eps)
+            return ops.layernorm(x, w, b, c.rms_norm_eps)
         return ops.rmsnorm(x, w, c.rms_norm_eps, c.norm_weight_offset)
 
     def _add_norm(self, delta, residual, name):
@@ -163,6 +163,10 @@ class DecoderModel:
         if c.norm_type == "rms":
             return ops.add_rmsnorm(delta, residual, self.p.tensors[name + ".weight"], c.rms_norm_eps,
                                    c.norm_weight_offset)
+        if c.norm_type == "layernorm" and not c.norm_weight_offset and (name + ".weight") in self.p.tensors \
+                and delta.is_contiguous() and residual.is_contiguous():
+            return ops.layernorm(delta, self.p.tensors[name + ".weight"], self.p.tensors.get(name + ".bias"),
+                                 c.rms_norm_eps, residual=residual)
         residual.add_(delta)
         return self._norm(residual, name)
 
@@ -294,12 +298,7 @@ class DecoderModel:
             a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
         else:
             u = ops.linear(h, self.p.linears[pre + "up_proj"])
-            if c.hidden_act == "relu2":
-                a = torch.relu(u) ** 2
-            elif c.hidden_act == "gelu":
-                a = torch.nn.functional.gelu(u.float()).to(u.dtype)
-            else:
-                a = torch.nn.functional.gelu(u.float(), approximate="tanh").to(u.dtype)
+            a = ops.activation(u, c.hidden_act if c.hidden_act in ("relu2", "gelu", "silu") else "gelu_tanh")
         return ops.linear(a, self.p.linears[pre + "down_proj"])
 
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:

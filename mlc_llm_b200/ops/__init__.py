@@ -45,6 +45,7 @@ class LinearWeight:
     device_layout: bool = False
     # dense fp16/bf16 copy used by kernels that do not take the packed form (built lazily)
     _dense: Optional[torch.Tensor] = None
+    _block_scale: Optional[torch.Tensor] = None
     # int4 tile records for the tensor-core GEMM (GPU only, built when the weight moves to the GPU)
     _tiles: Optional[torch.Tensor] = None
 
@@ -76,6 +77,23 @@ class LinearWeight:
         if dev.type == "cuda" and dl and out.q4_tileable(w.shape[-1] * 8):
             out.q4_tiles()
         return out
+
+    def block_scale(self) -> torch.Tensor:
+        """fp32 scales ``[ceil(N/128), ceil(K/128)]`` of an fp8 weight as the block-scaled GEMM kernels read
+        them. A per-tensor scale is one value repeated, so per-tensor fp8 checkpoints run on the same
+        kernels (reference: the per-tensor mode dequantises inside its matmul,
+        ``python/mlc_llm/quantization/per_tensor_quantization.py``)."""
+        if self.kind == "fp8_block":
+            if self.scale.dtype != torch.float32 or not self.scale.is_contiguous():
+                self.scale = self.scale.float().contiguous()
+            return self.scale
+        if self.kind != "fp8_tensor":
+            raise ValueError(self.kind)
+        if self._block_scale is None:
+            n, k = self.w.shape[-2], self.w.shape[-1]
+            self._block_scale = self.scale.float().reshape(-1)[:1].expand(
+                (n + 127) // 128 * ((k + 127) // 128)).reshape((n + 127) // 128, (k + 127) // 128).contiguous()
+        return self._block_scale
 
     def dense(self, dtype: torch.dtype) -> torch.Tensor:
         """Materialise the full-precision weight (used by oracles and by cold paths)."""
@@ -174,7 +192,8 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
                              c_int(n), c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
                              stream_ptr())
-    elif lw.kind == "fp8_block" and k % 64 == 0 and lw.w.dtype == torch.float8_e4m3fn:
+    elif lw.kind in ("fp8_block", "fp8_tensor") and k % 64 == 0 and lw.w.dtype == torch.float8_e4m3fn \
+            and lw.w.dim() == 2:
         from .fp8 import linear_fp8_block  # pylint: disable=import-outside-toplevel
 
         return linear_fp8_block(x2, lw, od).reshape(*lead, n)
@@ -214,6 +233,56 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: f
                             c_int(x.shape[1]), c_float(eps), c_float(w_offset),
                             c_int(DTYPE_CODE[x.dtype]), stream_ptr())
     check(rc, "mlcb_rmsnorm(add)")
+    return out
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float,
+              residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm over the last dimension; with ``residual``: ``residual += x`` in place first and the norm
+    is taken of the sum (reference: ``nn.LayerNorm`` in e.g. ``python/mlc_llm/model/gpt2/gpt2_model.py``)."""
+    h = x.shape[-1]
+    ok = (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and h % 8 == 0 and h <= 12000
+          and w.dtype == x.dtype and (b is None or b.dtype == x.dtype))
+    if not ok:
+        if residual is not None:
+            residual.add_(x)
+            x = residual
+        return ref.layernorm(x, w, b, eps)
+    x2 = x.reshape(-1, h)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if residual is not None:
+        assert residual.is_contiguous() and residual.shape == x.shape
+    out = torch.empty_like(x2)
+    rc = lib().mlcb_layernorm(ptr(x2), ptr(residual), ptr(w.contiguous()), ptr(None if b is None else b.contiguous()),
+                              ptr(out), c_int(x2.shape[0]), c_int(h), c_float(eps), c_int(DTYPE_CODE[x.dtype]),
+                              stream_ptr())
+    check(rc, "mlcb_layernorm")
+    return out.reshape(x.shape)
+
+
+_ACT_CODE = {"silu": 0, "gelu_tanh": 1, "gelu": 2, "relu2": 3}
+
+
+def activation(x: torch.Tensor, act: str) -> torch.Tensor:
+    """Elementwise ``silu`` / ``gelu`` (erf) / ``gelu_tanh`` / ``relu2`` (squared ReLU)."""
+    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0 and x.is_contiguous()):
+        xf = x.float()
+        if act == "silu":
+            y = torch.nn.functional.silu(xf)
+        elif act == "gelu":
+            y = torch.nn.functional.gelu(xf)
+        elif act == "gelu_tanh":
+            y = torch.nn.functional.gelu(xf, approximate="tanh")
+        elif act == "relu2":
+            y = torch.relu(xf) ** 2
+        else:
+            raise ValueError(act)
+        return y.to(x.dtype)
+    out = torch.empty_like(x)
+    rc = lib().mlcb_act(ptr(x), ptr(out), ctypes.c_longlong(x.numel()), c_int(_ACT_CODE[act]),
+                        c_int(DTYPE_CODE[x.dtype]), stream_ptr())
+    check(rc, "mlcb_act")
     return out
 
 

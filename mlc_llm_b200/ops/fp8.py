@@ -49,8 +49,8 @@ def linear_fp8_w8a8(x: torch.Tensor, lw, out_dtype: Optional[torch.dtype] = None
     if m == 0:
         return y
     xq, xs = act_quant_fp8(x)
-    scale = lw.scale if lw.scale.dtype == torch.float32 else lw.scale.float()
-    rc = lib().mlcb_gemm_fp8_w8a8(ptr(xq), ptr(xs), ptr(lw.w), ptr(scale.contiguous()), ptr(lw.bias), ptr(y), c_int(m),
+    scale = lw.block_scale()
+    rc = lib().mlcb_gemm_fp8_w8a8(ptr(xq), ptr(xs), ptr(lw.w), ptr(scale), ptr(lw.bias), ptr(y), c_int(m),
                                   c_int(n), c_int(k), c_int(n), c_int(xs.shape[1]), c_int(DTYPE_CODE[od]),
                                   ptr(status_word(x.device)), stream_ptr())
     check(rc, f"mlcb_gemm_fp8_w8a8(M={m},N={n},K={k})")
@@ -64,7 +64,7 @@ def linear_fp8_block(x: torch.Tensor, lw, out_dtype: Optional[torch.dtype] = Non
     m, k = x.shape
     n = lw.w.shape[0]
     od = out_dtype or x.dtype
-    if tuple(lw.quant.block_size) != (128, 128) if lw.quant is not None else False:
+    if lw.kind == "fp8_block" and lw.quant is not None and tuple(lw.quant.block_size) != (128, 128):
         raise ValueError("only 128 x 128 scale blocks are supported")
     if _FP8_ACT and m >= _W8A8_MIN_TOKENS and k % 128 == 0 and od in (torch.float16, torch.bfloat16) \
             and (lw.bias is None or lw.bias.dtype == od):
@@ -73,8 +73,8 @@ def linear_fp8_block(x: torch.Tensor, lw, out_dtype: Optional[torch.dtype] = Non
     if m == 0:
         return y
     x2 = x if x.stride(-1) == 1 else x.contiguous()
-    scale = lw.scale if lw.scale.dtype == torch.float32 else lw.scale.float()
-    rc = lib().mlcb_gemm_fp8(ptr(x2), ptr(lw.w), ptr(scale.contiguous()), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
+    scale = lw.block_scale()
+    rc = lib().mlcb_gemm_fp8(ptr(x2), ptr(lw.w), ptr(scale), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
                              c_int(k), c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[x.dtype]),
                              c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), *_gemm_scratch(x.device),
                              stream_ptr())

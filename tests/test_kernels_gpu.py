@@ -758,3 +758,44 @@ def test_attention_tcgen05_masked(dtype, hq, hkv, case):
     ops.check_status(qg.device)
     _close(o, o_ref, 2e-2, 2e-2)
     _close(lse, lse_ref, 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("m", [3, 40, 300])
+def test_fp8_per_tensor_linear_runs_on_the_block_scale_kernels(m):
+    """A per-tensor fp8 weight is a block-scaled one whose blocks share one scale: no dense copy is made."""
+    torch.manual_seed(8)
+    n, k = 384, 512
+    w = torch.randn(n, k) * 0.05
+    qw, sc = Q.fp8_per_tensor_quantize(w, "float8_e4m3fn")
+    x = (torch.randn(m, k) * 0.5).to(torch.bfloat16)
+    lw = ops.LinearWeight("fp8_tensor", qw.to(DEV), sc.float().to(DEV), None, None, n, k)
+    y = ops.linear(x.to(DEV), lw)
+    ops.check_status(torch.device(DEV))
+    assert lw._dense is None and lw.block_scale().shape == (3, 4)
+    want = x.float() @ (qw.float() * sc.float()).t()
+    rel = (y.float().cpu() - want).norm() / want.norm()
+    assert rel < 0.05, rel
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [768, 4096, 5120])
+def test_layernorm_and_plain_activations(dtype, hidden):
+    torch.manual_seed(9)
+    t = 37
+    x = (torch.randn(t, hidden) * 2 + 0.3).to(dtype)
+    res = torch.randn(t, hidden).to(dtype)
+    w = (torch.rand(hidden) + 0.5).to(dtype)
+    b = (torch.randn(hidden) * 0.1).to(dtype)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    for bias in (b, None):
+        want = ref.layernorm(x, w, bias, 1e-5)
+        got = ops.layernorm(x.to(DEV), w.to(DEV), None if bias is None else bias.to(DEV), 1e-5)
+        _close(got, want, tol, tol)
+    # fused residual add: the sum is written back and normalised
+    r_dev = res.to(DEV).clone()
+    got = ops.layernorm(x.to(DEV), w.to(DEV), b.to(DEV), 1e-5, residual=r_dev)
+    summed = (x.float() + res.float()).to(dtype)
+    _close(r_dev, summed, tol, tol)
+    _close(got, ref.layernorm(summed, w, b, 1e-5), tol, tol)
+    for act in ("silu", "gelu", "gelu_tanh", "relu2"):
+        _close(ops.activation(x.to(DEV), act), ops.activation(x, act), tol, tol)
