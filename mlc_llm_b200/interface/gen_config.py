@@ -15,7 +15,7 @@ from ..protocol.mlc_chat_config import MLCChatConfig
 from ..support.auto_config import detect_config, detect_model_type
 
 TOKENIZER_FILES = ["tokenizer.model", "tokenizer.json", "vocab.json", "merges.txt", "added_tokens.json",
-                   "tokenizer_config.json"]
+                   "tokenizer_config.json", "tokenizer_model"]
 
 CONV_TEMPLATES = set(ConvTemplateRegistry.names())
 
@@ -87,6 +87,12 @@ def gen_config(config: str, model_type: str, quantization: str, conv_template: s
                 chat.tokenizer_files.append("tokenizer.json")
             except Exception:  # pylint: disable=broad-except
                 pass
+        if not chat.tokenizer_files and any(f.endswith(".tiktoken") for f in os.listdir(src_dir)):
+            # tiktoken rank file (first-generation Qwen and others): converted once to the HuggingFace form
+            from ..support.convert_tiktoken import convert_tiktoken  # pylint: disable=import-outside-toplevel
+
+            convert_tiktoken(src_dir, output)
+            chat.tokenizer_files.extend(["tokenizer.json", "vocab.json", "merges.txt"])
         if chat.tokenizer_files:
             from ..tokenizers import Tokenizer  # pylint: disable=import-outside-toplevel
 

@@ -2,8 +2,9 @@
 
 ``Tokenizer`` finds the tokenizer files of a model directory in the reference's search order
 (``cpp/tokenizers/tokenizers.cc:143-195``): ``tokenizer.json`` (HuggingFace) -> ``tokenizer.model``
-(SentencePiece) -> ``vocab.json`` + ``merges.txt`` (byte-level BPE).  Encoding is done by the
-HuggingFace / SentencePiece libraries; decoding, streaming detokenisation and stop-string matching
+(SentencePiece) -> ``vocab.json`` + ``merges.txt`` (byte-level BPE) -> ``tokenizer_model`` (RWKV world
+vocabulary, ``rwkv_world.py``).  Encoding is done by the HuggingFace / SentencePiece libraries (the world
+vocabulary by a byte trie here); decoding, streaming detokenisation and stop-string matching
 run in the native runtime from the post-processed token table.
 """
 
@@ -85,6 +86,14 @@ class Tokenizer:
                     "strip_space_in_decode": False}
             return _core.Tokenizer(vocab, json.dumps(info),
                                    lambda s: hf.encode(s, add_special_tokens=False).ids, []), info
+        world = os.path.join(directory, "tokenizer_model")
+        if os.path.isfile(path) and os.path.basename(path) == "tokenizer_model":
+            world = path
+        if os.path.exists(world):
+            from .rwkv_world import load_for_runtime  # pylint: disable=import-outside-toplevel
+
+            vocab, info, encode, special = load_for_runtime(world)
+            return _core.Tokenizer(vocab, json.dumps(info), encode, special), info
         raise ValueError(f"Cannot find any tokenizer under {path}")
 
     @staticmethod
