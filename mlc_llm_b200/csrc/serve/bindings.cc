@@ -501,9 +501,12 @@ PYBIND11_MODULE(_core, m) {
           mi.max_batch_size = geti("max_batch_size", 128);
           mi.pipeline_parallel_stages = static_cast<int>(geti("pipeline_parallel_stages", 1));
           mi.kv_bytes_per_element = static_cast<int>(geti("kv_bytes_per_element", 2));
+          mi.rnn_state_bytes_per_sequence = geti("rnn_state_bytes_per_sequence", 0);
+          mi.hidden_size = geti("hidden_size", 0);
           infos.push_back(mi);
         }
-        CapacityResult r = InferCapacity(cfg, infos, gpu_total_bytes);
+        CapacityResult r = cfg.kv_state_kind == "rnn_state" ? InferRNNStateCapacity(cfg, infos, gpu_total_bytes)
+                                                            : InferCapacity(cfg, infos, gpu_total_bytes);
         py::dict out;
         out["config_json"] = r.config.AsJSON().dump();
         out["num_pages"] = r.num_pages;

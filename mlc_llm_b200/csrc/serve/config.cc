@@ -365,4 +365,55 @@ CapacityResult InferCapacity(const EngineConfig& user, const std::vector<ModelCa
   return res;
 }
 
+CapacityResult InferRNNStateCapacity(const EngineConfig& user, const std::vector<ModelCapacityInfo>& models,
+                                     int64_t gpu_total_bytes) {
+  if (models.empty()) throw std::runtime_error("InferRNNStateCapacity: no model");
+  if (user.max_single_sequence_length > 0)
+    throw std::runtime_error("a recurrent state has no per-sequence length limit: max_single_sequence_length (" +
+                             std::to_string(user.max_single_sequence_length) + ") must not be set");
+  CapacityResult res;
+  EngineConfig c = user;
+  int64_t model_prefill_chunk = INT64_MAX, model_max_batch = INT64_MAX;
+  for (auto& m : models) {
+    model_prefill_chunk = std::min(model_prefill_chunk, m.prefill_chunk_size);
+    model_max_batch = std::min(model_max_batch, m.max_batch_size);
+  }
+  if (c.prefill_chunk_size <= 0) c.prefill_chunk_size = std::min<int64_t>(model_prefill_chunk, 4096);
+  if (c.max_num_sequence <= 0)
+    c.max_num_sequence = c.mode == EngineMode::kInteractive ? 1 : std::min<int64_t>(4, model_max_batch);
+  if (c.max_total_sequence_length <= 0) c.max_total_sequence_length = 32768;
+  double state_per_snapshot = 0, workspace = 0, logit_ws = 0, params = 0;
+  for (auto& m : models) {
+    if (m.rnn_state_bytes_per_sequence <= 0)
+      throw std::runtime_error("InferRNNStateCapacity: the model reports no recurrent state size");
+    state_per_snapshot += static_cast<double>(c.max_num_sequence) * m.rnn_state_bytes_per_sequence;
+    const int64_t hidden = m.hidden_size > 0 ? m.hidden_size : m.head_dim * m.num_qo_heads;
+    workspace += c.prefill_chunk_size * 4.0 + c.max_num_sequence * 4.0 +
+                 (c.prefill_chunk_size * 2.0 + c.max_num_sequence) * hidden * 2.0;
+    logit_ws += c.max_num_sequence * 20.0 + c.max_num_sequence * m.vocab_size * 16.125;
+    params += static_cast<double>(m.params_bytes);
+  }
+  const double budget = gpu_total_bytes * c.gpu_memory_utilization - params - workspace - logit_ws;
+  const int64_t fit = static_cast<int64_t>(budget / state_per_snapshot);
+  std::ostringstream rep;
+  rep << "memory plan (recurrent state): total " << gpu_total_bytes / (1 << 20) << " MB x "
+      << c.gpu_memory_utilization << ", params " << static_cast<int64_t>(params) / (1 << 20) << " MB, workspace "
+      << static_cast<int64_t>(workspace + logit_ws) / (1 << 20) << " MB, state "
+      << static_cast<int64_t>(state_per_snapshot) / (1 << 10) << " KB per snapshot of " << c.max_num_sequence
+      << " sequences -> at most " << fit << " snapshots";
+  if (fit <= 0)
+    throw std::runtime_error("Insufficient GPU memory for the recurrent state: " + rep.str() +
+                             "; quantise the weights or lower the prefill chunk size");
+  c.max_history_size = c.max_history_size > 0 ? std::min(c.max_history_size, fit) : fit;
+  c.max_single_sequence_length = c.max_total_sequence_length;
+  if (c.prefix_cache_max_num_recycling_seqs < 0) c.prefix_cache_max_num_recycling_seqs = 0;
+  // the engine still hands out token slots page by page (positions only; no KV memory stands behind them)
+  res.num_pages = (c.max_total_sequence_length + c.kv_cache_page_size - 1) / c.kv_cache_page_size +
+                  2 * c.max_num_sequence + 1;
+  res.kv_bytes_per_token = 0;
+  res.config = c;
+  res.report = rep.str();
+  return res;
+}
+
 }  // namespace mlcb

@@ -114,6 +114,10 @@ struct ModelCapacityInfo {
   int64_t max_batch_size = 128;
   int pipeline_parallel_stages = 1;
   int kv_bytes_per_element = 2;
+  // recurrent-state models: bytes of state one sequence holds (all layers), and the hidden size that the
+  // workspace estimate needs (these models have no attention heads to derive it from)
+  int64_t rnn_state_bytes_per_sequence = 0;
+  int64_t hidden_size = 0;
 };
 
 struct CapacityResult {
@@ -122,6 +126,15 @@ struct CapacityResult {
   double kv_bytes_per_token = 0;
   std::string report;
 };
+
+// Recurrent-state models (kv_state_kind "rnn_state"): no KV pages; the batch size and how many state
+// snapshots per sequence (`max_history_size`) fit beside the weights. Counterpart of the reference's
+// InferrableEngineConfig::InferForRNNState (cpp/serve/config.cc:903-1060): a user-set
+// max_single_sequence_length is an error, the prefill chunk defaults to min(model, 4096), the batch size
+// to 1 (interactive) or min(4, model), the token capacity to 32768, and max_history_size to what the memory
+// left after weights and workspaces holds (at least one snapshot per sequence, or the call fails).
+CapacityResult InferRNNStateCapacity(const EngineConfig& user, const std::vector<ModelCapacityInfo>& models,
+                                     int64_t gpu_total_bytes);
 
 // Fills max_num_sequence / max_total_sequence_length / max_single_sequence_length /
 // prefill_chunk_size for the configured mode given `gpu_total_bytes` of device memory.

@@ -103,6 +103,13 @@ class RwkvModel(DecoderModel):
         if moves.numel():
             raise NotImplementedError("a recurrent state cannot drop rejected draft tokens")
 
+    def state_bytes_per_sequence(self) -> int:
+        """What one sequence's recurrent state occupies (two shift vectors and one matrix state per head and
+        layer): the engine's capacity inference sizes the batch by it."""
+        c, n = self.cfg, len(self.layers)
+        es = torch.empty((), dtype=self.dtype).element_size()
+        return n * (2 * c.hidden_size * es + self.heads * c.head_dim * c.head_dim * 4)
+
     def _fresh_state(self) -> Dict[str, torch.Tensor]:
         c, n = self.cfg, len(self.layers)
         return {"att_x": torch.zeros(n, c.hidden_size, dtype=self.dtype, device=self.device),

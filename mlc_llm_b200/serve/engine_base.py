@@ -342,6 +342,9 @@ class EngineRuntime:
                 "prefill_chunk_size": mcfg.prefill_chunk_size, "max_batch_size": mcfg.max_batch_size,
                 "pipeline_parallel_stages": mcfg.pipeline_parallel_stages,
                 "kv_bytes_per_element": 4 if model.kv_dtype == torch.float32 else 2,
+                "hidden_size": mcfg.hidden_size,
+                "rnn_state_bytes_per_sequence": int(model.state_bytes_per_sequence())
+                if hasattr(model, "state_bytes_per_sequence") else 0,
             })
         if self.device.type == "cuda":
             total = torch.cuda.get_device_properties(self.device).total_memory

@@ -512,3 +512,37 @@ def test_decode_batches_are_padded_to_graph_buckets():
     assert arrays["q_seq"].tolist() == list(range(8))
     pad_decode_arrays(arrays, 8)  # already at the bucket: unchanged
     assert arrays["token_ids"].size == 8
+
+
+def test_recurrent_state_capacity_inference():
+    """Batch size, token capacity and snapshot count of a recurrent-state model from the memory left beside the
+    weights; a per-sequence length limit is refused."""
+    import json
+
+    import pytest
+
+    from mlc_llm_b200 import _core
+
+    info = {"params_bytes": 3 << 30, "num_layers": 24, "vocab_size": 65536, "prefill_chunk_size": 8192,
+            "max_batch_size": 80, "hidden_size": 2048, "rnn_state_bytes_per_sequence": 24 * (2 * 2048 * 2 + 32 * 64 * 64 * 4)}
+
+    def infer(total, **cfg):
+        base = {"kv_state_kind": "rnn_state", "mode": "local", "gpu_memory_utilization": 0.85}
+        base.update(cfg)
+        res = _core.infer_capacity(json.dumps(base), [info], int(total))
+        return json.loads(res["config_json"]), res
+
+    c, res = infer(16 << 30)
+    assert c["max_num_sequence"] == 4 and c["prefill_chunk_size"] == 4096 and c["max_total_sequence_length"] == 32768
+    per_snapshot = 4 * info["rnn_state_bytes_per_sequence"]
+    assert 0 < c["max_history_size"] <= ((16 << 30) * 0.85 - (3 << 30)) / per_snapshot
+    assert c["max_history_size"] > ((16 << 30) * 0.85 - (3 << 30)) / per_snapshot * 0.8
+    assert "recurrent state" in res["report"] and res["kv_bytes_per_token"] == 0
+    c, _ = infer(16 << 30, mode="interactive", max_history_size=3)
+    assert c["max_num_sequence"] == 1 and c["max_history_size"] == 3
+    c, _ = infer(16 << 30, mode="server", max_num_sequence=64, max_total_sequence_length=100000)
+    assert c["max_num_sequence"] == 64 and c["max_total_sequence_length"] == 100000
+    with pytest.raises(Exception, match="max_single_sequence_length"):
+        infer(16 << 30, max_single_sequence_length=4096)
+    with pytest.raises(Exception, match="Insufficient GPU memory"):
+        infer(3 << 30)
