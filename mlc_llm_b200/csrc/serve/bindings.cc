@@ -595,6 +595,16 @@ PYBIND11_MODULE(_core, m) {
              return new JsonFFIEngine(fn, std::move(tokenizer), conv_json, model_name, cb);
            }))
       .def("chat_completion", &JsonFFIEngine::ChatCompletion, py::call_guard<py::gil_scoped_release>())
+      .def("set_image_embedder",
+           [](JsonFFIEngine& e, py::object fn) {
+             auto holder = std::make_shared<py::object>(std::move(fn));
+             e.SetImageEmbedder([holder](const std::string& bytes) {
+               py::gil_scoped_acquire gil;
+               py::tuple r = (*holder)(py::bytes(bytes)).cast<py::tuple>();
+               return std::make_pair(r[0].cast<int64_t>(), r[1].cast<int32_t>());
+             });
+           })
+      .def_static("decode_data_url", [](const std::string& url) { return py::bytes(JsonFFIEngine::DecodeDataURL(url)); })
       .def("abort", &JsonFFIEngine::Abort, py::call_guard<py::gil_scoped_release>())
       .def("get_last_error", &JsonFFIEngine::GetLastError)
       .def("reload", &JsonFFIEngine::Reload, py::call_guard<py::gil_scoped_release>())

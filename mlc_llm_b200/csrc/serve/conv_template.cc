@@ -26,7 +26,10 @@ std::string Placeholder(const std::string& role) {
 }
 }  // namespace
 
-std::string RenderConversation(const std::string& conv_json, const std::string& messages_json) {
+const char* const kImagePlaceholder = "\x02<|mlcb-image|>\x03";
+
+std::string RenderConversation(const std::string& conv_json, const std::string& messages_json,
+                               std::vector<std::string>* image_urls) {
   json::Value cv = json::parse(conv_json);
   json::Value mv = json::parse(messages_json);
   const json::Object& c = cv.as_object();
@@ -66,8 +69,21 @@ std::string RenderConversation(const std::string& conv_json, const std::string& 
       } else if (ct->is_array()) {
         for (auto& part : ct->as_array()) {
           const json::Object& po = part.as_object();
-          if (json::get_or<std::string>(po, "type", "") == "text") text += json::get_or<std::string>(po, "text", "");
-          else throw std::runtime_error("only text content parts are supported by the native renderer");
+          const std::string type = json::get_or<std::string>(po, "type", "");
+          if (type == "text") {
+            text += json::get_or<std::string>(po, "text", "");
+          } else if (type == "image_url" && image_urls != nullptr) {
+            const json::Value* iu = po.find("image_url");
+            std::string url;
+            if (iu && iu->is_string()) url = iu->as_string();
+            else if (iu && iu->is_object()) url = json::get_or<std::string>(iu->as_object(), "url", "");
+            if (url.empty()) throw std::runtime_error("an image_url content part needs a url");
+            image_urls->push_back(url);
+            text += kImagePlaceholder;
+            text += "\n";  // an image is followed by a newline, as in the Python renderer
+          } else {
+            throw std::runtime_error("unsupported content part type \"" + type + "\"");
+          }
         }
         has = true;
       }

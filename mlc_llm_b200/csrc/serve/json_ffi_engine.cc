@@ -14,6 +14,36 @@ int64_t UnixSeconds() {
 }
 }  // namespace
 
+std::string JsonFFIEngine::DecodeDataURL(const std::string& url) {
+  const std::string marker = ";base64,";
+  const size_t at = url.find(marker);
+  if (url.compare(0, 5, "data:") != 0 || at == std::string::npos)
+    throw std::runtime_error("image_url must be a data URL (data:image/...;base64,...)");
+  std::string out;
+  out.reserve((url.size() - at) * 3 / 4);
+  uint32_t acc = 0;
+  int bits = 0;
+  for (size_t i = at + marker.size(); i < url.size(); ++i) {
+    const unsigned char ch = static_cast<unsigned char>(url[i]);
+    int v;
+    if (ch >= 'A' && ch <= 'Z') v = ch - 'A';
+    else if (ch >= 'a' && ch <= 'z') v = ch - 'a' + 26;
+    else if (ch >= '0' && ch <= '9') v = ch - '0' + 52;
+    else if (ch == '+' || ch == '-') v = 62;
+    else if (ch == '/' || ch == '_') v = 63;
+    else if (ch == '=' || ch == '\n' || ch == '\r' || ch == ' ') continue;
+    else throw std::runtime_error("image_url: character outside the base64 alphabet");
+    acc = (acc << 6) | static_cast<uint32_t>(v);
+    bits += 6;
+    if (bits >= 8) {
+      bits -= 8;
+      out.push_back(static_cast<char>((acc >> bits) & 0xff));
+    }
+  }
+  if (out.empty()) throw std::runtime_error("image_url: empty payload");
+  return out;
+}
+
 JsonFFIEngine::JsonFFIEngine(ThreadedEngine::EngineFactory factory, std::shared_ptr<Tokenizer> tokenizer,
                              std::string conv_template_json, std::string model_name, JSONCallback callback)
     : tokenizer_(std::move(tokenizer)),
@@ -36,21 +66,43 @@ bool JsonFFIEngine::ChatCompletion(const std::string& request_json, const std::s
     if (messages == nullptr || !messages->is_array() || messages->as_array().empty())
       throw std::runtime_error("\"messages\" must be a non-empty array");
     // 1. conversation template -> prompt text -> token ids
-    const std::string prompt = RenderConversation(conv_json_, messages->dump());
+    std::vector<std::string> image_urls;
+    const std::string prompt = RenderConversation(conv_json_, messages->dump(), &image_urls);
+    if (!image_urls.empty() && !image_embedder_)
+      throw std::runtime_error("this model does not take image inputs");
     Request request;
     request.id = request_id;
-    InputItem item;
-    item.tokens = tokenizer_->Encode(prompt);
     json::Value conv = json::parse(conv_json_);
+    std::vector<int32_t> prefix_ids;
     if (conv.is_object()) {
-      if (const json::Value* pre = conv.as_object().find("system_prefix_token_ids"); pre && pre->is_array()) {
-        std::vector<int32_t> ids;
-        for (auto& v : pre->as_array()) ids.push_back(static_cast<int32_t>(v.as_int()));
-        item.tokens.insert(item.tokens.begin(), ids.begin(), ids.end());
-      }
+      if (const json::Value* pre = conv.as_object().find("system_prefix_token_ids"); pre && pre->is_array())
+        for (auto& v : pre->as_array()) prefix_ids.push_back(static_cast<int32_t>(v.as_int()));
     }
-    request.prompt_tokens = static_cast<int64_t>(item.tokens.size());
-    request.inputs.push_back(std::move(item));
+    // text pieces between the image placeholders become token items, the images embedding items
+    const std::string mark = kImagePlaceholder;
+    size_t from = 0, image = 0;
+    while (true) {
+      const size_t at = image < image_urls.size() ? prompt.find(mark, from) : std::string::npos;
+      const std::string piece = prompt.substr(from, at == std::string::npos ? std::string::npos : at - from);
+      InputItem item;
+      if (!piece.empty()) item.tokens = tokenizer_->Encode(piece);
+      if (from == 0) item.tokens.insert(item.tokens.begin(), prefix_ids.begin(), prefix_ids.end());
+      if (!item.tokens.empty()) {
+        request.prompt_tokens += static_cast<int64_t>(item.tokens.size());
+        request.inputs.push_back(std::move(item));
+      }
+      if (at == std::string::npos) break;
+      const auto rows = image_embedder_(DecodeDataURL(image_urls[image++]));
+      if (rows.first < 0 || rows.second <= 0) throw std::runtime_error("the image could not be embedded");
+      InputItem img;
+      img.kind = 1;
+      img.embed_handle = rows.first;
+      img.embed_len = rows.second;
+      request.prompt_tokens += rows.second;
+      request.inputs.push_back(std::move(img));
+      from = at + mark.size();
+    }
+    if (request.inputs.empty()) throw std::runtime_error("the rendered prompt is empty");
     // 2. generation config: request fields over the model defaults, plus the template's stop rules
     json::Object gen;
     for (auto& m : req.members()) {

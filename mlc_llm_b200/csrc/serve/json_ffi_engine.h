@@ -22,6 +22,14 @@ class JsonFFIEngine {
  public:
   // Receives a JSON array of chat.completion.chunk objects.
   using JSONCallback = std::function<void(const std::string& chunks_json)>;
+  // Turns the bytes of an encoded image (PNG, JPEG, ...) into prompt embedding rows held by the model
+  // backend; returns (embedding handle, number of rows). Counterpart of the image path of the reference's
+  // JSON FFI (cpp/json_ffi/image_utils.cc decodes the data URL, the model's image_embed function makes the
+  // rows); decoding the pixels and running the vision tower are the host's part here.
+  using ImageEmbedder = std::function<std::pair<int64_t, int32_t>(const std::string& image_bytes)>;
+  void SetImageEmbedder(ImageEmbedder fn) { image_embedder_ = std::move(fn); }
+  // Bytes of a "data:<mime>;base64,<payload>" URL; throws on anything else.
+  static std::string DecodeDataURL(const std::string& url);
 
   JsonFFIEngine(ThreadedEngine::EngineFactory factory, std::shared_ptr<Tokenizer> tokenizer,
                 std::string conv_template_json, std::string model_name, JSONCallback callback);
@@ -49,6 +57,7 @@ class JsonFFIEngine {
   std::shared_ptr<Tokenizer> tokenizer_;
   std::string conv_json_, model_;
   JSONCallback callback_;
+  ImageEmbedder image_embedder_;
   std::mutex mu_;
   std::unordered_map<std::string, RequestState> states_;
   std::string last_error_;

@@ -55,6 +55,8 @@ class JSONFFIEngine:
         conv_json = json.dumps(self.runtime.conv_template.to_json_dict())
         self._ffi = _core.JsonFFIEngine(lambda cfg: self.runtime.make_core_engine(cfg, None),
                                         self.tokenizer.handle, conv_json, model, self._on_chunks)
+        if hasattr(self.runtime.models[0], "image_embed"):
+            self._ffi.set_image_embedder(self._embed_image)
         self._threads = [threading.Thread(target=self._ffi.run_background_loop, daemon=True),
                          threading.Thread(target=self._ffi.run_background_stream_back_loop, daemon=True)]
         for t in self._threads:
@@ -62,6 +64,20 @@ class JSONFFIEngine:
         self._ffi.reload(self.runtime.complete_config_json)
         self.chat = _Chat(self)
         self._terminated = False
+
+    def _embed_image(self, image_bytes: bytes):
+        """Encoded image bytes (the native side has already taken them out of the data URL) -> embedding rows
+        held by the executor: (handle, number of rows)."""
+        import io  # pylint: disable=import-outside-toplevel
+
+        from PIL import Image  # pylint: disable=import-outside-toplevel
+
+        from ..models.vision import preprocess_image  # pylint: disable=import-outside-toplevel
+
+        img = Image.open(io.BytesIO(image_bytes)).convert("RGB")
+        pixels, _ = preprocess_image(img, self.runtime.models_info[0].chat_config)
+        emb = self.runtime.models[0].image_embed(pixels)
+        return self.runtime.executor.hold_embedding(emb), int(emb.shape[0])
 
     def _on_chunks(self, chunks_json: str) -> None:
         for chunk in json.loads(chunks_json):

@@ -75,6 +75,13 @@ MODEL_PRESETS = {
         "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
     },
+    # alternating sliding-window / full layers, attention and final logit soft-capping (masked attention paths)
+    "tiny-gemma2-gpu": {
+        "model_type": "gemma2", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 4096, "sliding_window": 48,
+        "attn_logit_softcapping": 30.0, "final_logit_softcapping": 20.0, "query_pre_attn_scalar": 128,
+    },
     # small models whose every sharded dimension divides by 8 (multi-rank tests up to 8 GPUs)
     "tiny-llama-tp8": {
         "model_type": "llama", "hidden_size": 1024, "intermediate_size": 2048, "num_hidden_layers": 2,

@@ -166,6 +166,68 @@ def test_varying_batch_replays_bucketed_graphs(monkeypatch):
     assert all(a[0][0] == b[0][0] for a, b in zip(got, want))
 
 
+def _tokens(model, device, prompts, cfg, **engine_kw):
+    from mlc_llm_b200.serve.config import EngineConfig
+    from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
+
+    ecfg = dict(mode="server", max_num_sequence=8, prefill_chunk_size=128, max_total_sequence_length=4096,
+                prefix_cache_mode="disable")
+    ecfg.update(engine_kw)
+    eng = SyncMLCEngine(model, device, engine_config=EngineConfig(**ecfg))
+    _, toks = eng.generate(prompts, cfg)
+    return [t[0] for t in toks], eng
+
+
+def _agreement(a, b):
+    return float(np.mean([np.mean(np.asarray(x) == np.asarray(y)) for x, y in zip(a, b)]))
+
+
+@pytest.mark.parametrize("case", ["gemma2", "window_sink"])
+def test_masked_attention_models_match_the_cpu_engine(case, monkeypatch):
+    """Per-layer sliding windows with logit soft-capping (gemma2) and an engine-wide window with attention
+    sinks run on the tensor-core attention kernel's masked variant; greedy tokens against the CPU engine
+    holding the same weights. Prompts are longer than the window and cross prefill chunks."""
+    from mlc_llm_b200.ops import _lib
+
+    monkeypatch.setenv("MLCB_RANDOM_INIT_DEVICE", "cpu")
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (150, 40, 97, 260)]
+    cfg = {"max_tokens": 12, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+    if case == "gemma2":
+        model, kw = "random://tiny-gemma2-gpu?quant=q0f16&seed=4", {}
+    else:
+        model, kw = "random://tiny-llama-gpu?quant=q0f16&seed=4", dict(sliding_window_size=64, attention_sink_size=4)
+    lib = _lib.lib()
+    lib.mlcb_launch_count.restype = __import__("ctypes").c_longlong
+    got, eng = _tokens(model, "cuda", prompts, cfg, **kw)
+    _lib.check_status(torch.device("cuda"))
+    assert eng.runtime.executor._tc_attention_ok(eng.runtime.models[0])  # not the CUDA-core fallback
+    want, _ = _tokens(model, "cpu", prompts, cfg, **kw)
+    assert all(a[0] == b[0] for a, b in zip(got, want))
+    assert _agreement(got, want) >= 0.85, (got, want)
+
+
+def test_speculative_decoding_on_the_gpu_keeps_greedy_outputs():
+    """Draft-and-verify with a small draft model: the verify step's token trees go through the tensor-core
+    attention kernel's tree mask; greedy outputs equal plain greedy decoding up to near-ties."""
+    from mlc_llm_b200.ops import _lib
+
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (33, 70, 12, 129)]
+    cfg = {"max_tokens": 24, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+    model = "random://tiny-llama-gpu?quant=q0f16&seed=3"
+    want, _ = _tokens(model, "cuda", prompts, cfg)
+    for mode_kw in (dict(spec_draft_length=3), dict(spec_draft_length=4, spec_tree_width=2)):
+        got, eng = _tokens(model, "cuda", prompts, cfg, speculative_mode="small_draft",
+                           additional_models=["random://tiny-llama-gpu?quant=q0f16&seed=3"], **mode_kw)
+        _lib.check_status(torch.device("cuda"))
+        stats = json.loads(eng.debug_stats()) if hasattr(eng, "debug_stats") else {}
+        assert all(len(t) == 24 for t in got)
+        assert all(a[0] == b[0] for a, b in zip(got, want))
+        # the draft is the target itself, so nearly every proposal is accepted and outputs agree
+        assert _agreement(got, want) >= 0.9, (mode_kw, got, want, stats)
+
+
 def test_smoke_entry():
     import __graft_entry__ as g
 

@@ -126,6 +126,42 @@ def test_image_request_through_the_chat_api():
         eng.terminate()
 
 
+def test_image_request_through_the_json_ffi_engine():
+    """The native JSON front end takes image content parts: it pulls the bytes out of the data URL, the host
+    embeds them, and the rows sit between the text pieces of the rendered prompt."""
+    from PIL import Image
+
+    from mlc_llm_b200 import _core
+    from mlc_llm_b200.json_ffi.engine import JSONFFIEngine
+    from mlc_llm_b200.serve.config import EngineConfig
+
+    img = Image.fromarray((np.random.default_rng(0).random((40, 60, 3)) * 255).astype(np.uint8))
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    assert _core.JsonFFIEngine.decode_data_url(url) == buf.getvalue()
+    with pytest.raises(Exception, match="data URL"):
+        _core.JsonFFIEngine.decode_data_url("http://example.com/cat.png")
+    eng = JSONFFIEngine("random://tiny-llava?quant=q0f32&seed=2", "cpu", mode="server",
+                        engine_config=EngineConfig(max_num_sequence=4, max_total_sequence_length=1024,
+                                                   prefill_chunk_size=64))
+    try:
+        def usage(messages):
+            last = None
+            for chunk in eng.chat.completions.create(messages=messages, max_tokens=4, temperature=0.0,
+                                                     stream_options={"include_usage": True}):
+                last = chunk
+            return last.usage
+
+        text_only = usage([{"role": "user", "content": "what is this"}])
+        with_image = usage([{"role": "user", "content": [{"type": "text", "text": "what is this"},
+                                                         {"type": "image_url", "image_url": {"url": url}}]}])
+        assert with_image.prompt_tokens == text_only.prompt_tokens + 4 + 1
+        assert with_image.completion_tokens == 4
+    finally:
+        eng.terminate()
+
+
 # ---------------------------------------------------------------------------- Phi-3-vision
 def test_phi3v_hd_geometry():
     """Tile grid and prompt-row count of the high-definition transform for the sizes the full model uses
