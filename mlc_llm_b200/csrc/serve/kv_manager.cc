@@ -123,9 +123,11 @@ int64_t KVManager::PagesNeeded(int64_t seq_id, int64_t n) const {
   return std::max<int64_t>(0, need - have);
 }
 
-void KVManager::TrimWindow(Seq& s) {
+void KVManager::TrimWindow(Seq& s, int64_t first_new_pos) {
   if (s.window <= 0) return;
-  const int64_t first_visible = s.len - s.window;  // positions below this (and >= sink) are dead
+  // the first token of the chunk being appended still sees `window` positions ending at itself: only what
+  // lies below that (and is no sink) is dead for every token of the chunk
+  const int64_t first_visible = first_new_pos + 1 - s.window;
   if (first_visible <= s.sink) return;
   const int64_t first_page = (s.sink + page_size_ - 1) / page_size_;
   const int64_t end_page = first_visible / page_size_;  // pages entirely below first_visible
@@ -195,7 +197,7 @@ ForwardPlan KVManager::BeginForward(const std::vector<int64_t>& seq_ids,
     tree_off += n;
     s.len += n;
     total_len_ += n;
-    if (!tree_parents) TrimWindow(s);
+    if (!tree_parents) TrimWindow(s, base);
     plan.seq_lens.push_back(static_cast<int32_t>(s.len));
     plan.page_indices.insert(plan.page_indices.end(), s.pages.begin(), s.pages.end());
     plan.page_indptr.push_back(static_cast<int32_t>(plan.page_indices.size()));

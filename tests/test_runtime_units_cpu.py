@@ -91,6 +91,24 @@ def test_kv_manager_sliding_window_releases_pages():
     assert len(plan["q_kvstart"]) == 16
 
 
+def test_kv_manager_window_keeps_what_the_first_token_of_a_chunk_sees():
+    """A chunk longer than the window: its first token still attends `window` positions back, so only pages
+    below that may go when the chunk is appended."""
+    kv = _core.KVManager(64, 16, 4)
+    kv.add_sequence(0)
+    kv.enable_sliding_window(0, 32, 0)
+    kv.begin_forward([0], [64])
+    plan = kv.begin_forward([0], [64])          # positions 64..127
+    pages = kv.sequence_pages(0)
+    first_start = int(plan["q_kvstart"][0])     # 64 + 1 - 32 = 33
+    assert first_start == 33
+    assert all(p >= 0 for p in pages[first_start // 16:])   # page 2 (positions 32..47) onwards are live
+    assert pages[0] < 0 and pages[1] < 0                    # positions 0..31 are dead for every token
+    plan = kv.begin_forward([0], [1])           # position 128: sees 97..128
+    pages = kv.sequence_pages(0)
+    assert all(p < 0 for p in pages[:6]) and all(p >= 0 for p in pages[6:])
+
+
 # ------------------------------------------------------------------ prefix cache
 def test_prefix_cache_reuse_fork_and_recycle():
     removed = []
