@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the hot kernels, reported against measured peaks.
 
-``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|gemv_q4|lowm_q4|attn_decode|attn_prefill|rope|norm|sampling|moe|all] [--small]``
+``python -m mlc_llm_b200.bench.kernel_bench [gemm|gemm_q4|gemm_fp8|gemv_q4|lowm_q4|attn_decode|attn_prefill|rope|norm|sampling|moe|all] [--small]``
 
 Timing follows the usual hygiene: warm-up, CUDA events on the launching stream, and a buffer larger
 than L2 written between timed launches so every launch starts cold.  ``--small`` shrinks the
@@ -245,6 +245,45 @@ def bench_misc(which: str, small: bool):
     return out
 
 
+def bench_gemm_fp8(small: bool):
+    """Block-scaled e4m3 weights: fp8 x fp8 tensor-core product with on-the-fly activation quantisation
+    (W8A8), the same weights expanded inside the 16-bit GEMM (W8A16), this package's bf16 GEMM and cuBLAS
+    bf16 on the same shape. Graph-timed (host out of the picture); operands exceed L2 on the large shapes."""
+    from ..ops import fp8 as f8  # pylint: disable=import-outside-toplevel
+
+    dev = torch.device("cuda")
+    _, tf, how = _peaks()
+    quant = Q.get("fp8_e4m3fn_bf16_block_scale")
+    shapes = [(8192, 10240, 8192), (8192, 8192, 3584), (2048, 8192, 8192), (512, 8192, 8192), (256, 8192, 8192)]
+    if small:
+        shapes = [(2048, 8192, 8192)]
+    out = []
+    for m, n, k in shapes:
+        x = (torch.randn(m, k, device=dev) * 0.5).bfloat16()
+        w = torch.randn(n, k, device=dev) * 0.05
+        qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
+        lw = ops.LinearWeight("fp8_block", qw, sc.float(), None, quant, n, k)
+        ld = ops.dense_weight(w.bfloat16())
+        del w
+        t_a8 = _time_graph(lambda: ops.linear(x, lw)) * 1e3
+        t_q = _time_graph(lambda: f8.act_quant_fp8(x)) * 1e3
+        keep = f8._FP8_ACT  # pylint: disable=protected-access
+        f8._FP8_ACT = False  # pylint: disable=protected-access
+        t_a16 = _time_graph(lambda: ops.linear(x, lw)) * 1e3
+        f8._FP8_ACT = keep  # pylint: disable=protected-access
+        t_bf = _time_graph(lambda: ops.linear(x, ld)) * 1e3
+        t_cb = _time_graph(lambda: torch.matmul(x, ld.w.t())) * 1e3
+        ops.check_status(dev)
+        flops = 2.0 * m * n * k
+        out.append({"kernel": "gemm_fp8_w8a8", "M": m, "N": n, "K": k, "us": round(t_a8, 1),
+                    "of_which_act_quant_us": round(t_q, 1), "w8a16_us": round(t_a16, 1), "own_bf16_us": round(t_bf, 1),
+                    "cublas_bf16_us": round(t_cb, 1), "tflops": round(flops / t_a8 / 1e6, 1),
+                    "frac_of_bf16_peak": round(flops / t_a8 / 1e6 / tf, 3), "vs_own_bf16": round(t_bf / t_a8, 2),
+                    "vs_w8a16": round(t_a16 / t_a8, 2), "peaks": how})
+        print(json.dumps(out[-1]), flush=True)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("which", nargs="?", default="all")
@@ -254,6 +293,8 @@ def main(argv=None):
     res = []
     if args.which in ("gemm", "all"):
         res += bench_gemm(args.small, q4=False)
+    if args.which in ("gemm_fp8", "all"):
+        res += bench_gemm_fp8(args.small)
     if args.which in ("gemv_q4", "all"):
         bench_gemv_q4(args.small)
     if args.which in ("lowm_q4", "all"):

@@ -198,6 +198,33 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, T* __restrict__ kv_pages
   T* row = qkv + static_cast<size_t>(t) * heads * d;
   // rotate q and k heads
   const int pairs = (hq + hkv) * half;
+  const int jg = half >> 3;  // groups of eight rotary pairs per head
+  if (half > 0 && (half & 7) == 0 && (d & 7) == 0 && blockDim.x % jg == 0) {
+    // a thread keeps one group of eight frequencies (its sines and cosines are computed once) and walks
+    // the heads with 16-byte loads and stores of the two halves
+    const int g = threadIdx.x % jg, j0 = g * 8;
+    float sn[8], cs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      sincosf(p * inv_freq[j0 + j], &sn[j], &cs[j]);
+      sn[j] *= attn_factor;
+      cs[j] *= attn_factor;
+    }
+    for (int h = threadIdx.x / jg; h < hq + hkv; h += blockDim.x / jg) {
+      T* hp = row + h * d + j0;
+      uint4 lo = *reinterpret_cast<const uint4*>(hp), hi = *reinterpret_cast<const uint4*>(hp + half);
+      T* le = reinterpret_cast<T*>(&lo);
+      T* he = reinterpret_cast<T*>(&hi);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = Cvt<T>::to_f(le[j]), b = Cvt<T>::to_f(he[j]);
+        le[j] = Cvt<T>::from_f(a * cs[j] - b * sn[j]);
+        he[j] = Cvt<T>::from_f(b * cs[j] + a * sn[j]);
+      }
+      *reinterpret_cast<uint4*>(hp) = lo;
+      *reinterpret_cast<uint4*>(hp + half) = hi;
+    }
+  } else
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int h = i / half, j = i % half;
     float s, c;

@@ -27,7 +27,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-_OPS = {"forward": 1, "move": 2, "shutdown": 3, "reset": 4, "forward_async": 5}
+_OPS = {"forward": 1, "move": 2, "shutdown": 3, "reset": 4, "forward_async": 5, "forward_part": 6}
 _OPS_INV = {v: k for k, v in _OPS.items()}
 _DT = {np.dtype(np.int32): 0, np.dtype(np.float32): 1, np.dtype(np.int64): 2}
 _DT_INV = {0: np.int32, 1: np.float32, 2: np.int64}

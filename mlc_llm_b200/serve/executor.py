@@ -85,6 +85,51 @@ def pad_decode_arrays(arrays: Dict[str, np.ndarray], target: int) -> None:
         cat("token_src", np.full(extra, -1))
 
 
+def split_plan(plan: dict, token_ids: np.ndarray, sp: dict, s: int):
+    """Cut one forward plan at sequence ``s`` into two that can run one after the other: sequences
+    ``[0, s)`` and ``[s, n)`` with their tokens, pages and logit rows (indices rebased). The first part
+    carries only its logit rows; the second carries the sampling parameters of all rows, since the rows of
+    both parts are sampled together once the second part's logits exist. Copy-on-write page copies run with
+    the first part."""
+    qi = np.asarray(plan["q_indptr"], dtype=np.int64)
+    pi = np.asarray(plan["page_indptr"], dtype=np.int64)
+    n = qi.size - 1
+    if not 0 < s < n:
+        raise ValueError(f"cannot split {n} sequences at {s}")
+    t, pg = int(qi[s]), int(pi[s])
+    tok_keys = ("positions", "slots", "q_seq", "q_kvlen", "q_kvstart", "tree_mask")
+    seq_keys = ("seq_lens", "append_lens", "seq_ids")
+    parts = []
+    for lo_s, hi_s, lo_t, hi_t, lo_p, hi_p in ((0, s, 0, t, 0, pg), (s, n, t, int(qi[-1]), pg, int(pi[-1]))):
+        p = {}
+        for k in tok_keys:
+            a = np.asarray(plan[k])
+            p[k] = a[lo_t:hi_t] if a.size else a
+        p["q_seq"] = np.asarray(p["q_seq"]) - lo_s
+        for k in seq_keys:
+            if k in plan:
+                p[k] = np.asarray(plan[k])[lo_s:hi_s]
+        p["q_indptr"] = qi[lo_s:hi_s + 1] - lo_t
+        p["page_indptr"] = pi[lo_s:hi_s + 1] - lo_p
+        p["page_indices"] = np.asarray(plan["page_indices"])[lo_p:hi_p]
+        p["page_copies"] = np.asarray(plan["page_copies"]) if lo_s == 0 else np.zeros(0, np.int32)
+        p["max_seq_len"] = int(np.max(p["seq_lens"])) if len(p["seq_lens"]) else 0
+        parts.append(p)
+    rows = np.asarray(sp["logit_token_index"], dtype=np.int64)
+    first = rows < t
+    if first.any() and not first[: int(first.sum())].all():
+        raise ValueError("logit rows are not ordered by sequence")
+    sp_a = {k: (np.zeros(0, np.float32) if k in _S_FLT else np.zeros(0, np.int32)) for k in _S_INT + _S_FLT}
+    for k, v in sp.items():
+        if k not in sp_a:
+            sp_a[k] = v[:0] if isinstance(v, (np.ndarray, list)) else v
+    sp_a["logit_token_index"] = rows[first]
+    sp_b = dict(sp)
+    sp_b["logit_token_index"] = rows[~first] - t
+    tok = np.asarray(token_ids)
+    return [(parts[0], tok[:t], sp_a), (parts[1], tok[t:], sp_b)]
+
+
 class FeatureStore:
     """Target-model features (final-normed hidden states) of the positions that a speculative draft
     head (EAGLE, Medusa) has not consumed yet, per sequence, plus the head's own latest prediction.
@@ -232,6 +277,10 @@ class ModelExecutor:
         self._graph_pool = None
         self.graph_replays = 0
         self.graph_eligible_steps = 0  # steps that could run from a graph (replayed, captured or first seen)
+        # pipeline stages: steps with at least this many tokens run as two micro-batches (0 = never)
+        self.pp_microbatch_min_tokens = int(os.environ.get("MLCB_PP_MICROBATCH_MIN_TOKENS", "512"))
+        self.pp_microbatch_steps = 0
+        self._part_logits: List[torch.Tensor] = []
         self._nvtx = device.type == "cuda" and os.environ.get("MLCB_NVTX", "0") == "1"
         # speculative draft heads fed with the target's features: model id -> "eagle" | "medusa"
         self.spec_heads: Dict[int, str] = {}
@@ -459,14 +508,45 @@ class ModelExecutor:
     def _pipeline(self, model_id: int) -> bool:
         return self.comm is not None and self.comm.pp_size > 1 and model_id == 0
 
-    def _logits(self, model_id: int, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    def _pipeline_parts(self, model_id: int, plan: dict, token_ids: np.ndarray, embed_handles, sp: dict):
+        """Prefill-sized steps of a pipelined model run as two micro-batches: while a later stage works on
+        the first half of the sequences, the stage before it already computes the second half (the hand-over
+        is a stream-ordered NCCL send, so nothing waits on the host). Every stage reads its weights once per
+        part, so steps with few tokens, which are bound by those reads, stay whole. The last stage keeps the
+        first part's logits and returns the rows of both parts in one message.
+        Returns ``None`` (run whole) or ``(device arrays of the last part, hidden of the last part)``."""
+        if not self._pipeline(model_id) or embed_handles is not None or self.spec_heads \
+                or self.pp_microbatch_min_tokens <= 0:
+            return None
+        qi = np.asarray(plan["q_indptr"], dtype=np.int64)
+        n, total = qi.size - 1, int(qi[-1]) if qi.size else 0
+        if n < 2 or total < self.pp_microbatch_min_tokens:
+            return None
+        s = int(np.searchsorted(qi, total / 2.0))
+        s = min(max(s, 1), n - 1)
+        parts = split_plan(plan, token_ids, sp, s)
+        dev = hidden = None
+        for i, (p, tok, spx) in enumerate(parts):
+            arrays = self._pack(p, tok, spx, model_id)
+            self.comm.broadcast_step("forward" if i == len(parts) - 1 else "forward_part", model_id,
+                                     {k: v for k, v in arrays.items()
+                                      if not k.startswith("s_") or k == "s_logit_token_index"}, {})
+            dev = self.staging.upload(arrays)
+            self.h2d_bytes += self.staging.last_words * 4
+            hidden = self._run_model(model_id, p, dev, None)
+        self.pp_microbatch_steps += 1
+        return dev, hidden
+
+    def _logits(self, model_id: int, hidden: torch.Tensor, rows: torch.Tensor, n_rows: Optional[int] = None
+                ) -> torch.Tensor:
         """Logits of the selected rows on the rank that hosts the engine. With pipeline stages the
         last stage computes them and returns them to rank 0 (reference: ``SendFromLastGroupToWorker0``,
         ``cpp/multi_gpu/builtin.cc:27-87``)."""
         model = self.models[model_id]
         if not self._pipeline(model_id):
             return model.logits(hidden, rows)
-        out = torch.empty(int(rows.numel()), model.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        out = torch.empty(int(rows.numel()) if n_rows is None else int(n_rows), model.cfg.vocab_size,
+                          dtype=torch.float32, device=self.device)
         self.comm.recv_logits_from_last_stage(out)
         return out
 
@@ -513,22 +593,29 @@ class ModelExecutor:
         ht, clock = self.host_times, time.perf_counter
         t0 = clock()
         n_rows = len(sp["logit_token_index"])
-        arrays = self._pack(plan, token_ids, sp, model_id)
-        t1 = clock()
-        if self.comm is not None:
-            self.comm.broadcast_step("forward", model_id,
-                                     {k: v for k, v in arrays.items()
-                                      if not k.startswith("s_") or k == "s_logit_token_index"}, {})
-        t2 = clock()
-        dev = self.staging.upload(arrays)
-        self.h2d_bytes += self.staging.last_words * 4
-        t3 = clock()
-        if model_id in self.spec_heads:
-            logits = self._forward_spec_head(model_id, plan, dev, n_rows)
-            if logits is None:
-                return None
-            return self._sample(logits, dev, sp, n_rows)
-        hidden = self._run_model(model_id, plan, dev, embed_handles)
+        parts = self._pipeline_parts(model_id, plan, token_ids, embed_handles, sp)
+        if parts is not None:
+            # the parts were packed, announced and launched one after the other; `dev` holds the last one's
+            # arrays, with the sampling parameters of every row
+            dev, hidden = parts
+            t1 = t2 = t3 = clock()
+        else:
+            arrays = self._pack(plan, token_ids, sp, model_id)
+            t1 = clock()
+            if self.comm is not None:
+                self.comm.broadcast_step("forward", model_id,
+                                         {k: v for k, v in arrays.items()
+                                          if not k.startswith("s_") or k == "s_logit_token_index"}, {})
+            t2 = clock()
+            dev = self.staging.upload(arrays)
+            self.h2d_bytes += self.staging.last_words * 4
+            t3 = clock()
+            if model_id in self.spec_heads:
+                logits = self._forward_spec_head(model_id, plan, dev, n_rows)
+                if logits is None:
+                    return None
+                return self._sample(logits, dev, sp, n_rows)
+            hidden = self._run_model(model_id, plan, dev, embed_handles)
         t4 = clock()
         ht["pack"] += t1 - t0
         ht["broadcast"] += t2 - t1
@@ -539,7 +626,7 @@ class ModelExecutor:
             self._remember_features(plan, self.models[0].final_features(hidden), None)
         if n_rows == 0:
             return None
-        logits = self._logits(model_id, hidden, dev["s_logit_token_index"])
+        logits = self._logits(model_id, hidden, dev["s_logit_token_index"], n_rows)
         if self._is_plain_greedy(sp):
             tokens = ops.argmax(logits)
             t5 = clock()
@@ -999,6 +1086,12 @@ class ModelExecutor:
             return
         hidden = self._run_model(model_id, plan, dev, None)
         model = self.models[model_id]
-        if self._pipeline(model_id) and model.last_stage and self.comm.tp_rank == 0 \
-                and "s_logit_token_index" in dev and dev["s_logit_token_index"].numel():
-            self.comm.send_logits_to_rank0(model.logits(hidden, dev["s_logit_token_index"]))
+        if self._pipeline(model_id) and model.last_stage and self.comm.tp_rank == 0:
+            rows = dev.get("s_logit_token_index")
+            if rows is not None and rows.numel():
+                self._part_logits.append(model.logits(hidden, rows))
+            if op == "forward" and self._part_logits:
+                # one message for the rows of every part of the step
+                out = self._part_logits[0] if len(self._part_logits) == 1 else torch.cat(self._part_logits)
+                self._part_logits = []
+                self.comm.send_logits_to_rank0(out)

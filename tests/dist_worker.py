@@ -85,6 +85,7 @@ def main():
     rt = eng.runtime
     print("FLAGS " + json.dumps({"fused_tp": bool(getattr(rt, "fused_tp", False)),
                                  "graph_replays": int(rt.executor.graph_replays),
+                                 "pp_microbatch_steps": int(rt.executor.pp_microbatch_steps),
                                  "fused_launches": int(rt.models[0].fused.launches) if getattr(rt.models[0], "fused", None) else 0}),
           flush=True)
     print("RESULT " + json.dumps([t[0] for t in toks]), flush=True)

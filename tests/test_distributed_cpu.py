@@ -47,3 +47,15 @@ def test_pp2_matches_single_rank():
     single = _run(1, model, port=29543)
     pp2 = _run(2, model, port=29544, extra_env={"MLCB_TEST_PP": "2"})
     assert single == pp2
+
+
+def test_pp2_micro_batches_match_single_rank():
+    """The same with prefill steps cut into two micro-batches (the threshold lowered so the short test prompts
+    qualify): stage 1 works on the first half while stage 0 computes the second, the last stage returns the
+    logit rows of both halves in one message; tokens stay exactly those of the single-process run."""
+    model = "random://tiny-llama?quant=q0f32&seed=5"
+    single = _run(1, model, port=29545)
+    pp2, flags = _run(2, model, port=29546, extra_env={"MLCB_TEST_PP": "2", "MLCB_PP_MICROBATCH_MIN_TOKENS": "16"},
+                      want_flags=True)
+    assert single == pp2
+    assert flags["pp_microbatch_steps"] >= 1
