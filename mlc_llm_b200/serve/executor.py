@@ -496,10 +496,13 @@ class ModelExecutor:
         else:
             x = model.embed(dev["token_ids"])
             if embed_handles is not None:
+                # rows of held embeddings (images) replace the table lookups: one gather per image, indexed
+                # on the device by the row numbers the engine put in place of token ids
                 idx = np.nonzero(embed_handles >= 0)[0]
-                tok = np.asarray(dev["token_ids"].cpu())
-                for i in idx:
-                    x[i] = self.embeddings[int(embed_handles[i])][int(tok[i])].to(x.dtype)
+                for h in np.unique(embed_handles[idx]):
+                    sel = torch.from_numpy(idx[embed_handles[idx] == h]).to(self.device)
+                    rows = dev["token_ids"][sel].long()
+                    x[sel] = self.embeddings[int(h)].to(x.dtype)[rows]
         h = model.forward(x, b)
         if staged and not model.last_stage:
             self.comm.send_to_next_stage(h)
