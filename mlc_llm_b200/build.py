@@ -168,6 +168,54 @@ def build_core(verbose: bool = False) -> Path:
     return out
 
 
+def build_selftest(sanitizer: str = "") -> Path:
+    """The native runtime (everything of ``csrc/serve`` except the Python bindings) linked with
+    ``csrc/selftest/runtime_selftest.cc`` into a stand-alone program, optionally under a sanitizer:
+    ``"address"`` (AddressSanitizer + UndefinedBehaviorSanitizer), ``"thread"`` (ThreadSanitizer) or ``""``."""
+    if sanitizer not in ("", "address", "thread"):
+        raise ValueError(f"unknown sanitizer {sanitizer!r}")
+    src_dir = CSRC / "serve"
+    sources = [s for s in sorted(src_dir.glob("*.cc")) if s.name != "bindings.cc"]
+    sources.append(CSRC / "selftest" / "runtime_selftest.cc")
+    headers = sorted(src_dir.glob("*.h"))
+    tag = sanitizer or "plain"
+    obj_dir = OBJ_DIR / f"selftest_{tag}"
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    flags = ["-O1", "-g", "-std=c++17", "-pthread", "-fno-omit-frame-pointer", "-I", str(src_dir)]
+    if sanitizer == "address":
+        flags += ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+    elif sanitizer == "thread":
+        flags += ["-fsanitize=thread"]
+    # not every installed g++ ships the sanitizer run-time libraries: take the first one that links a probe
+    cxx = None
+    probe = obj_dir / "probe.cc"
+    probe.write_text("int main() { return 0; }\n")
+    for cand in dict.fromkeys([os.environ.get("CXX"), "/usr/bin/g++", shutil.which("g++"), shutil.which("clang++")]):
+        if not cand or not os.path.exists(cand):
+            continue
+        ok = subprocess.run([cand, *flags, str(probe), "-o", str(obj_dir / "probe")], capture_output=True)
+        if ok.returncode == 0:
+            cxx = cand
+            break
+    if cxx is None:
+        raise FileNotFoundError(f"no C++ compiler here links with the {sanitizer or 'plain'} sanitizer run time")
+    objs, jobs = [], []
+    for s in sources:
+        o = obj_dir / (s.stem + ".o")
+        objs.append(o)
+        if _newer(s, headers, o):
+            jobs.append((s, o))
+    if jobs:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for f in [ex.submit(_run, [cxx, *flags, "-c", str(s), "-o", str(o)], obj_dir / (o.stem + ".log"))
+                      for s, o in jobs]:
+                f.result()
+    out = obj_dir / "runtime_selftest"
+    if jobs or not out.exists():
+        _run([cxx, *flags, "-o", str(out), *map(str, objs)], obj_dir / "link.log")
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_core(verbose)
     build_kernels(verbose)
