@@ -53,6 +53,71 @@ __global__ void moe_router_kernel(const T* __restrict__ logits, float* __restric
   }
 }
 
+// Group-limited routing (DeepSeek-V2; reference: python/mlc_llm/op/moe_misc.py:238-368): softmax over all
+// experts, keep the `topk_group` expert groups whose best expert scores highest, then the top k experts inside
+// the kept groups. One thread per token; ties go to the lower index, as in the plain router.
+template <typename T>
+__global__ void moe_router_grouped_kernel(const T* __restrict__ logits, float* __restrict__ weights,
+                                          int* __restrict__ experts, int tokens, int E, int k, int n_group,
+                                          int topk_group, int renorm) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const T* row = logits + static_cast<size_t>(t) * E;
+  const int gs = E / n_group;
+  float gbest[32];
+  float mx = -INFINITY;
+  for (int g = 0; g < n_group; ++g) {
+    float b = -INFINITY;
+    for (int e = g * gs; e < (g + 1) * gs; ++e) b = fmaxf(b, Cvt<T>::to_f(row[e]));
+    gbest[g] = b;
+    mx = fmaxf(mx, b);
+  }
+  float denom = 0.f;
+  for (int e = 0; e < E; ++e) denom += __expf(Cvt<T>::to_f(row[e]) - mx);
+  unsigned keep = 0u;
+  for (int j = 0; j < topk_group; ++j) {
+    int best = -1;
+    float bv = -INFINITY;
+    for (int g = 0; g < n_group; ++g)
+      if (!((keep >> g) & 1u) && (best < 0 || gbest[g] > bv)) {
+        best = g;
+        bv = gbest[g];
+      }
+    keep |= 1u << best;
+  }
+  float topv[8];
+  int topi[8];
+  for (int j = 0; j < k; ++j) {
+    topv[j] = -INFINITY;
+    topi[j] = -1;
+  }
+  for (int g = 0; g < n_group; ++g) {
+    if (!((keep >> g) & 1u)) continue;
+    for (int e = g * gs; e < (g + 1) * gs; ++e) {
+      const float v = Cvt<T>::to_f(row[e]);
+      int pos = k;
+      while (pos > 0 && v > topv[pos - 1]) --pos;
+      if (pos < k) {
+        for (int j = k - 1; j > pos; --j) {
+          topv[j] = topv[j - 1];
+          topi[j] = topi[j - 1];
+        }
+        topv[pos] = v;
+        topi[pos] = e;
+      }
+    }
+  }
+  float sum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    topv[j] = topi[j] >= 0 ? __expf(topv[j] - mx) / denom : 0.f;
+    sum += topv[j];
+  }
+  for (int j = 0; j < k; ++j) {
+    weights[static_cast<size_t>(t) * k + j] = renorm ? topv[j] / sum : topv[j];
+    experts[static_cast<size_t>(t) * k + j] = topi[j] >= 0 ? topi[j] : 0;
+  }
+}
+
 // Single-CTA permutation: counts per expert, exclusive scan, then a slot for every (token, j) pair.
 // offsets [E + 1]; sorted_pos [n] = row of pair i in expert-major order; src_token [n] = token of row.
 __global__ void __launch_bounds__(1024)
@@ -142,6 +207,23 @@ MLCB_API int mlcb_moe_router(const void* logits, float* weights, int* experts, i
     moe_router_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((const __nv_bfloat16*)logits, weights, experts, tokens, E, k, mode, renorm);
   else
     moe_router_kernel<float><<<blocks, 128, 0, stream>>>((const float*)logits, weights, experts, tokens, E, k, mode, renorm);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_moe_router_grouped(const void* logits, float* weights, int* experts, int tokens, int E, int k,
+                                     int n_group, int topk_group, int renorm, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (k > 8 || k < 1 || n_group < 1 || n_group > 32 || E % n_group || topk_group < 1 || topk_group > n_group ||
+      topk_group * (E / n_group) < k)
+    return -1;
+  const int blocks = (tokens + 127) / 128;
+  if (dtype == 0)
+    moe_router_grouped_kernel<__half><<<blocks, 128, 0, stream>>>((const __half*)logits, weights, experts, tokens, E, k, n_group, topk_group, renorm);
+  else if (dtype == 1)
+    moe_router_grouped_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((const __nv_bfloat16*)logits, weights, experts, tokens, E, k, n_group, topk_group, renorm);
+  else
+    moe_router_grouped_kernel<float><<<blocks, 128, 0, stream>>>((const float*)logits, weights, experts, tokens, E, k, n_group, topk_group, renorm);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -18,6 +18,19 @@ def _group_limited_router(logits: torch.Tensor, k: int, n_group: int, topk_group
     """DeepSeek-V2 routing: softmax over all experts, keep the ``topk_group`` expert groups with the
     best single score, then the top ``k`` experts inside them (reference: ``op/moe_misc.py:238-368``)."""
     t, e = logits.shape
+    if logits.is_cuda and k <= 8 and n_group <= 32 and e % n_group == 0:
+        from ..ops._lib import DTYPE_CODE, check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
+        import ctypes  # pylint: disable=import-outside-toplevel
+
+        lg = logits.contiguous()
+        w = torch.empty(t, k, dtype=torch.float32, device=lg.device)
+        idx = torch.empty(t, k, dtype=torch.int32, device=lg.device)
+        rc = lib().mlcb_moe_router_grouped(ptr(lg), ptr(w), ptr(idx), ctypes.c_int(t), ctypes.c_int(e), ctypes.c_int(k),
+                                           ctypes.c_int(n_group), ctypes.c_int(topk_group),
+                                           ctypes.c_int(1 if renorm else 0), ctypes.c_int(DTYPE_CODE[lg.dtype]),
+                                           stream_ptr())
+        check(rc, "mlcb_moe_router_grouped")
+        return w, idx
     probs = torch.softmax(logits.float(), dim=-1)
     group_best = probs.view(t, n_group, e // n_group).max(dim=-1).values
     keep = torch.zeros_like(group_best).scatter_(1, torch.topk(group_best, topk_group, dim=-1).indices, 1.0)

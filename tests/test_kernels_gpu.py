@@ -799,3 +799,18 @@ def test_layernorm_and_plain_activations(dtype, hidden):
     _close(got, ref.layernorm(summed, w, b, 1e-5), tol, tol)
     for act in ("silu", "gelu", "gelu_tanh", "relu2"):
         _close(ops.activation(x.to(DEV), act), ops.activation(x, act), tol, tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("e,n_group,topk_group,k,renorm", [(160, 8, 3, 6, False), (64, 8, 4, 6, True), (16, 4, 2, 2, True)])
+def test_group_limited_router_kernel(dtype, e, n_group, topk_group, k, renorm):
+    """DeepSeek-V2 routing on the GPU against the tensor-operation form on the CPU (same selection, same weights)."""
+    from mlc_llm_b200.models.moe import _group_limited_router
+
+    torch.manual_seed(13)
+    logits = (torch.randn(301, e) * 2).to(dtype)
+    w_ref, i_ref = _group_limited_router(logits.float(), k, n_group, topk_group, renorm)
+    w, i = _group_limited_router(logits.to(DEV), k, n_group, topk_group, renorm)
+    assert torch.equal(i.cpu().sort(dim=1).values, i_ref.sort(dim=1).values)
+    order, order_ref = i.cpu().argsort(dim=1), i_ref.argsort(dim=1)
+    _close(w.cpu().gather(1, order), w_ref.gather(1, order_ref), 1e-4, 1e-6)
