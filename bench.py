@@ -357,29 +357,33 @@ def main(argv=None) -> int:
     if comm is not None:
         comm.destroy()
     if check_tokens is not None:
-        import gc
+        try:
+            import gc
 
-        del eng
-        gc.collect()
-        torch.cuda.empty_cache()
-        os.environ["MLCB_FUSED_TP"] = "0"
-        one = SyncMLCEngine(model, device, engine_config=EngineConfig(
-            mode="server", max_num_sequence=8, prefill_chunk_size=8192, max_total_sequence_length=4096,
-            prefix_cache_mode="disable", gpu_memory_utilization=0.5))
-        _, ref_out = one.generate(check_prompts, check_cfg)
-        prefix = []
-        for a, b in zip(check_tokens, (t[0] for t in ref_out)):
-            n = 0
-            while n < min(len(a), len(b)) and a[n] == b[n]:
-                n += 1
-            prefix.append(n)
-        # the ranks add their partial sums in another order than one GPU does, so with random weights a
-        # sequence can part ways with the 1-rank run at a near-tie and never return: the first token and the
-        # matched prefix length say more than the count of fully equal sequences
-        line["tokens_match_tp1"] = {"requests": len(prefix), "tokens_each": 32,
-                                    "first_token_equal": sum(1 for n in prefix if n >= 1),
-                                    "all_32_equal": sum(1 for n in prefix if n >= 32),
-                                    "matched_prefix_lengths": prefix}
+            del eng
+            gc.collect()
+            torch.cuda.empty_cache()
+            os.environ["MLCB_FUSED_TP"] = "0"
+            one = SyncMLCEngine(model, device, engine_config=EngineConfig(
+                mode="server", max_num_sequence=8, prefill_chunk_size=8192, max_total_sequence_length=4096,
+                prefix_cache_mode="disable", gpu_memory_utilization=0.5))
+            _, ref_out = one.generate(check_prompts, check_cfg)
+            prefix = []
+            for a, b in zip(check_tokens, (t[0] for t in ref_out)):
+                n = 0
+                while n < min(len(a), len(b)) and a[n] == b[n]:
+                    n += 1
+                prefix.append(n)
+            # the ranks add their partial sums in another order than one GPU does, so with random weights a
+            # sequence can part ways with the 1-rank run at a near-tie and never return: the first token and the
+            # matched prefix length say more than the count of fully equal sequences
+            line["tokens_match_tp1"] = {"requests": len(prefix), "tokens_each": 32,
+                                        "first_token_equal": sum(1 for n in prefix if n >= 1),
+                                        "all_32_equal": sum(1 for n in prefix if n >= 32),
+                                        "matched_prefix_lengths": prefix}
+        except Exception as err:  # pylint: disable=broad-except
+            # the timed result stands on its own: a failed check is reported, not fatal
+            line["tokens_match_tp1"] = {"error": str(err)[:200]}
     print(json.dumps(line))
     return 0
 
