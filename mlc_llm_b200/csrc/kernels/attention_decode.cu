@@ -52,7 +52,19 @@ struct DecParams {
   int num_units;          // items * hkv * splits
   float scale_log2;
   int is_bf16;
+  // masked variant (same visibility rule as the tcgen05 kernel: window start + sinks below q_kvlen, ancestor
+  // bits of a token tree at and above it; logit soft-capping). All null / zero for the plain causal form.
+  const int* q_kvstart;
+  const unsigned long long* tree_mask;
+  int sink;
+  float cap_pre, cap_log2;
 };
+
+__device__ __forceinline__ float dec_tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -90,7 +102,13 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
 // One work unit: which pages, which rows.
 struct DecUnit {
   int item, hk, split, qstart, ntok, valid_rows, pg_begin, npg;
+  int sink_pg, skip;  // pages [sink_pg, sink_pg + skip) lie wholly outside every row's window: never fetched
   const int* pages;
+  // i-th page the unit visits -> index into the sequence's page list
+  __device__ __forceinline__ int page_index(int i) const {
+    const int li = pg_begin + i;
+    return li < sink_pg ? li : li + skip;
+  }
 };
 __device__ __forceinline__ DecUnit dec_unit(const DecParams& p, int u) {
   DecUnit d;
@@ -102,16 +120,29 @@ __device__ __forceinline__ DecUnit dec_unit(const DecParams& p, int u) {
   d.qstart = p.item_qstart[d.item];
   d.ntok = p.item_ntok[d.item];
   d.valid_rows = d.ntok * p.group;
-  const int kv_max = p.q_kvlen[d.qstart + d.ntok - 1];
+  int kv_max = p.q_kvlen[d.qstart + d.ntok - 1];
+  d.sink_pg = 0;
+  d.skip = 0;
+  if (p.tree_mask) {
+    int extra = 0;
+    for (int i = 0; i < d.ntok; ++i) extra = max(extra, 64 - __clzll(p.tree_mask[d.qstart + i] | 1ull));
+    kv_max += extra;
+  }
+  if (p.q_kvstart) {
+    int first = p.q_kvstart[d.qstart];
+    for (int i = 1; i < d.ntok; ++i) first = min(first, p.q_kvstart[d.qstart + i]);
+    d.sink_pg = (p.sink + 15) / 16;
+    d.skip = max(0, first / 16 - d.sink_pg);
+  }
   d.pages = p.page_indices + p.page_indptr[b];
-  const int total_pages = (kv_max + 15) / 16;
+  const int total_pages = max(0, (kv_max + 15) / 16 - d.skip);
   const int per_split = (total_pages + p.splits - 1) / p.splits;
   d.pg_begin = d.split * per_split;
   d.npg = max(0, min(total_pages, d.pg_begin + per_split) - d.pg_begin);
   return d;
 }
 
-template <bool BF16>
+template <bool BF16, bool EXT>
 __global__ void __launch_bounds__(DEC_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -150,8 +181,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
             ok = false;
             break;
           }
-          int page = d.pages[d.pg_begin + i];
-          if (page < 0) page = 0;
+          int page = d.pages[d.page_index(i)];
+          if (page < 0) page = 0;  // released by a sliding window: every position of it is masked
           mbar_expect_tx(&full[s], DEC_PAGE_BYTES);
           uint8_t* dst = smem + s * DEC_PAGE_BYTES;
           const int krow = ((page * 2 + 0) * p.hkv + d.hk) * 16;
@@ -204,6 +235,24 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
     }
     const int kvlen0 = r0 < valid_rows ? p.q_kvlen[qstart + r0 / G] : 0;
     const int kvlen1 = (r0 + 8) < valid_rows ? p.q_kvlen[qstart + (r0 + 8) / G] : 0;
+    int start0 = 0, start1 = 0;
+    unsigned long long tm0 = 0ull, tm1 = 0ull;
+    if (EXT) {
+      if (p.q_kvstart) {
+        if (r0 < valid_rows) start0 = p.q_kvstart[qstart + r0 / G];
+        if (r0 + 8 < valid_rows) start1 = p.q_kvstart[qstart + (r0 + 8) / G];
+      }
+      if (p.tree_mask) {
+        if (r0 < valid_rows) tm0 = p.tree_mask[qstart + r0 / G];
+        if (r0 + 8 < valid_rows) tm1 = p.tree_mask[qstart + (r0 + 8) / G];
+      }
+    }
+    auto visible = [&](int pos, int kvlen, int start, unsigned long long tm) -> bool {
+      if (!EXT) return pos < kvlen;
+      if (pos < kvlen) return pos >= start || pos < p.sink;
+      const int r = pos - kvlen;
+      return r < 64 && ((tm >> r) & 1ull);
+    };
     // this warp's pages of the unit: those whose number over all units is congruent to the warp index
     for (int i = (warp - static_cast<int>(g0 & 3u)) & 3; i < npg && ok; i += 4) {
       const uint32_t g = g0 + static_cast<uint32_t>(i);
@@ -230,16 +279,23 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams 
         }
       }
       // ---- mask + online softmax (rows r0 and r0 + 8)
-      const int pos_base = (d.pg_begin + i) * 16;
+      const int pos_base = d.page_index(i) * 16;
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int pos = pos_base + nt * 8 + cpair + c;
-          float v0 = sacc[nt][c] * p.scale_log2, v1 = sacc[nt][2 + c] * p.scale_log2;
-          v0 = pos < kvlen0 ? v0 : -INFINITY;
-          v1 = pos < kvlen1 ? v1 : -INFINITY;
+          float v0, v1;
+          if (EXT && p.cap_log2 != 0.f) {
+            v0 = p.cap_log2 * dec_tanh_approx(sacc[nt][c] * p.cap_pre);
+            v1 = p.cap_log2 * dec_tanh_approx(sacc[nt][2 + c] * p.cap_pre);
+          } else {
+            v0 = sacc[nt][c] * p.scale_log2;
+            v1 = sacc[nt][2 + c] * p.scale_log2;
+          }
+          v0 = visible(pos, kvlen0, start0, tm0) ? v0 : -INFINITY;
+          v1 = visible(pos, kvlen1, start1, tm1) ? v1 : -INFINITY;
           sacc[nt][c] = v0;
           sacc[nt][2 + c] = v1;
           mx0 = fmaxf(mx0, v0);
@@ -407,7 +463,8 @@ MLCB_API int mlcb_attn_decode(const void* q, const void* kv_pages, void* out, fl
                               const int* page_indptr, const int* page_indices, int num_items,
                               long long q_stride, int hq, int hkv, long long num_pages, float sm_scale,
                               int dtype, int splits, float* part_o, float* part_ml, int* status,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const int* q_kvstart, const unsigned long long* tree_mask,
+                              int sink, float softcap) {
   if (num_items <= 0) return 0;
   if (hq % hkv) return -1;
   const int group = hq / hkv;
@@ -418,8 +475,10 @@ MLCB_API int mlcb_attn_decode(const void* q, const void* kv_pages, void* out, fl
     return -3;
   static bool attr_set[64] = {};
   if (first_use_on_device(attr_set)) {
-    cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
-    cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+    cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
   }
   uint64_t dims[2] = {128, static_cast<uint64_t>(num_pages) * 2 * hkv * 16};
   uint64_t strides[1] = {256};
@@ -447,12 +506,24 @@ MLCB_API int mlcb_attn_decode(const void* q, const void* kv_pages, void* out, fl
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.is_bf16 = dtype == 1;
   p.num_units = num_items * hkv * splits;
+  p.q_kvstart = q_kvstart;
+  p.tree_mask = tree_mask;
+  p.sink = q_kvstart ? sink : 0;
+  p.cap_pre = softcap > 0.f ? sm_scale / softcap : 0.f;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   const int max_ctas = 2 * sm_count();
   dim3 grid(p.num_units < max_ctas ? p.num_units : max_ctas);
-  if (dtype == 1)
-    attn_decode_kernel<true><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
-  else
-    attn_decode_kernel<false><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
+  const bool ext = q_kvstart || tree_mask || softcap > 0.f;
+  if (ext) {
+    if (dtype == 1)
+      attn_decode_kernel<true, true><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
+    else
+      attn_decode_kernel<false, true><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
+  } else if (dtype == 1) {
+    attn_decode_kernel<true, false><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
+  } else {
+    attn_decode_kernel<false, false><<<grid, DEC_THREADS, DEC_SMEM, stream>>>(*mkv, p);
+  }
   count_launch();
   if (splits > 1) {
     dim3 g2(num_items, hkv);

@@ -365,13 +365,13 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
         return res.reshape(t, hq * d)
     out = torch.empty(t, hq * d, dtype=q.dtype, device=q.device)
     lse = torch.empty(t, hq, dtype=torch.float32, device=q.device) if return_lse else None
-    masked = tree_mask is not None or softcap != 0.0 or q_kvstart is not None
     if plan is not None and plan.use_tensor_core and d == 128 and page == 16 \
-            and q.dtype in (torch.float16, torch.bfloat16) and not (masked and plan.num_dec):
+            and q.dtype in (torch.float16, torch.bfloat16):
         from .attention import attention_decode, attention_tcgen05  # pylint: disable=import-outside-toplevel
 
         if plan.num_dec:
-            attention_decode(q, kv_pages, out, lse, plan, hq, hkv, sm_scale)
+            attention_decode(q, kv_pages, out, lse, plan, hq, hkv, sm_scale, q_kvstart=q_kvstart, sink=sink,
+                             tree_mask=tree_mask, softcap=softcap)
         if plan.num_tiles:
             attention_tcgen05(q, kv_pages, out, lse, plan, hq, hkv, sm_scale, q_kvstart=q_kvstart, sink=sink,
                               tree_mask=tree_mask, softcap=softcap)

@@ -19,8 +19,7 @@ def build_tiles(q_indptr: np.ndarray, group: int, decode_items: bool = True) -> 
     chunks) become one item each for the decode kernel (``dec_seq``, ``dec_qstart``, ``dec_ntok``).
     The others are cut into tiles of ``128 // group`` tokens for the tcgen05 kernel (``tile_seq``,
     ``tile_qstart``, ``tile_ntok``). All arrays are int32; ``*_qstart`` are global token indices.
-    ``decode_items=False`` sends every sequence to the tcgen05 kernel: the forwards that need its masked
-    variant (windows, sinks, soft-capping, token trees), which the decode kernel does not have.
+    ``decode_items=False`` sends every sequence to the tcgen05 kernel.
     """
     tpt = max(1, 128 // group)
     q_indptr = np.asarray(q_indptr, dtype=np.int64)
@@ -96,8 +95,10 @@ def choose_splits(num_items: int, hkv: int, max_pages: int, device: torch.device
 
 def attention_decode(q: torch.Tensor, kv_pages: torch.Tensor, out: torch.Tensor,
                      lse: Optional[torch.Tensor], plan: AttentionPlan, hq: int, hkv: int,
-                     sm_scale: float) -> None:
-    """Decode-kernel launch for the items of ``plan`` with at most 16 query rows each."""
+                     sm_scale: float, q_kvstart: Optional[torch.Tensor] = None, sink: int = 0,
+                     tree_mask: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+    """Decode-kernel launch for the items of ``plan`` with at most 16 query rows each; the mask arguments
+    select its masked variant (same rule as :func:`attention_tcgen05`)."""
     splits = plan.dec_splits
     part_o = part_ml = None
     if splits > 1:
@@ -109,5 +110,6 @@ def attention_decode(q: torch.Tensor, kv_pages: torch.Tensor, out: torch.Tensor,
                                 ctypes.c_longlong(q.stride(0)), ctypes.c_int(hq), ctypes.c_int(hkv),
                                 ctypes.c_longlong(kv_pages.shape[0]), ctypes.c_float(sm_scale),
                                 ctypes.c_int(DTYPE_CODE[q.dtype]), ctypes.c_int(splits), ptr(part_o),
-                                ptr(part_ml), ptr(status_word(q.device)), stream_ptr())
+                                ptr(part_ml), ptr(status_word(q.device)), stream_ptr(), ptr(q_kvstart),
+                                ptr(tree_mask), ctypes.c_int(int(sink)), ctypes.c_float(float(softcap)))
     check(rc, "mlcb_attn_decode")

@@ -381,10 +381,7 @@ class ModelExecutor:
         if self._tc_attention_ok(model):
             from ..ops.attention import build_tiles  # pylint: disable=import-outside-toplevel
 
-            # the decode kernel has no masked variant: windows, trees and soft-capping go to the tcgen05 kernel
-            plain = (arrays["tree_mask"].size == 0 and arrays["q_kvstart"].size == 0
-                     and not self._masked_attention(model))
-            arrays.update(build_tiles(arrays["q_indptr"], model.hq // model.hkv, decode_items=plain))
+            arrays.update(build_tiles(arrays["q_indptr"], model.hq // model.hkv))
         if sp is not None:
             for k in _S_INT:
                 arrays["s_" + k] = np.ascontiguousarray(sp[k], dtype=np.int32)

@@ -689,7 +689,8 @@ def test_page_copy_all_layers_one_launch():
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("hq,hkv", [(8, 2), (16, 2), (4, 4)])
 @pytest.mark.parametrize("case", ["window", "window_sink", "softcap", "tree", "tree_window_softcap", "decode_window"])
-def test_attention_tcgen05_masked(dtype, hq, hkv, case):
+@pytest.mark.parametrize("decode_items,splits", [(False, 1), (True, 1), (True, 3)])
+def test_attention_tcgen05_masked(dtype, hq, hkv, case, decode_items, splits):
     """Windows (with and without sinks, whole blocks skipped), logit soft-capping and token-tree masks on the
     tensor-core kernel, against the fp32 reference of the same visibility rule."""
     from mlc_llm_b200.ops.attention import AttentionPlan, build_tiles
@@ -741,11 +742,16 @@ def test_attention_tcgen05_masked(dtype, hq, hkv, case):
     o_ref, lse_ref = ops.paged_attention(qkv[:, : hq * d], kv, q_seq, q_kvlen, indptr, indices, hq, hkv, d,
                                          page, scale, q_kvstart=kvstart, sink=sink, tree_mask=tmask,
                                          softcap=softcap, return_lse=True)
-    tiles = build_tiles(np.asarray(q_indptr), hq // hkv, decode_items=False)
-    assert len(tiles["dec_seq"]) == 0
+    # decode-sized items go to the decode kernel's masked variant, the rest to the tcgen05 kernel's;
+    # `splits` also cuts the decode items' (window-compacted) page ranges
+    tiles = build_tiles(np.asarray(q_indptr), hq // hkv, decode_items=decode_items)
     dev = lambda a: torch.as_tensor(a).to(DEV)
     plan = AttentionPlan(dev(tiles["tile_seq"]), dev(tiles["tile_qstart"]), dev(tiles["tile_ntok"]),
-                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]))
+                         q_kvlen.to(DEV), indptr.to(DEV), indices.to(DEV), len(tiles["tile_seq"]),
+                         dec_seq=dev(tiles["dec_seq"]), dec_qstart=dev(tiles["dec_qstart"]),
+                         dec_ntok=dev(tiles["dec_ntok"]), num_dec=len(tiles["dec_seq"]), dec_splits=splits)
+    if decode_items and (case == "decode_window" or (case == "tree" and hq // hkv <= 4)):
+        assert plan.num_dec > 0
     qg = qkv.to(DEV)
     from mlc_llm_b200.ops._lib import lib
 
