@@ -564,3 +564,39 @@ def test_recurrent_state_capacity_inference():
         infer(16 << 30, max_single_sequence_length=4096)
     with pytest.raises(Exception, match="Insufficient GPU memory"):
         infer(3 << 30)
+
+
+def test_split_plan_cuts_a_forward_at_a_sequence_boundary():
+    """Both halves are self-contained plans (rebased indices), page copies go with the first, the logit rows are
+    divided by sequence and the second half keeps the sampling parameters of every row."""
+    import numpy as np
+
+    from mlc_llm_b200 import _core
+    from mlc_llm_b200.serve.executor import split_plan
+
+    kv = _core.KVManager(64, 16, 8)
+    for i in range(3):
+        kv.add_sequence(i)
+    lens = [20, 7, 33]
+    plan = dict(kv.begin_forward([0, 1, 2], lens))
+    plan["max_seq_len"] = 33
+    toks = np.arange(60, dtype=np.int32)
+    sp = {"logit_token_index": np.array([19, 26, 59], np.int32), "temperature": np.array([0.0, 0.5, 1.0], np.float32),
+          "top_p": np.ones(3, np.float32), "uniform": np.zeros(3, np.float32), "top_k": np.zeros(3, np.int32),
+          "penalties": np.zeros(0, np.float32), "pen_row": np.zeros(0, np.int32), "pen_token": np.zeros(0, np.int32),
+          "pen_count": np.zeros(0, np.int32), "bias_row": np.zeros(0, np.int32), "bias_token": np.zeros(0, np.int32),
+          "bias_value": np.zeros(0, np.float32), "mask_rows": np.zeros(0, np.int32), "mask_bits": np.zeros(0, np.int32),
+          "prob_slots": np.zeros(0, np.int32), "num_top_logprobs": 0}
+    (pa, ta, sa), (pb, tb, sb) = split_plan(plan, toks, sp, 2)
+    assert ta.tolist() == list(range(27)) and tb.tolist() == list(range(27, 60))
+    assert pa["q_indptr"].tolist() == [0, 20, 27] and pb["q_indptr"].tolist() == [0, 33]
+    assert pa["q_seq"].tolist() == [0] * 20 + [1] * 7 and pb["q_seq"].tolist() == [0] * 33
+    full_pi, full_pages = np.asarray(plan["page_indptr"]), np.asarray(plan["page_indices"])
+    assert pa["page_indptr"].tolist() == full_pi[:3].tolist()
+    assert pb["page_indptr"].tolist() == (full_pi[2:] - full_pi[2]).tolist()
+    assert np.concatenate([pa["page_indices"], pb["page_indices"]]).tolist() == full_pages.tolist()
+    assert np.concatenate([pa["slots"], pb["slots"]]).tolist() == np.asarray(plan["slots"]).tolist()
+    assert pa["max_seq_len"] == 20 and pb["max_seq_len"] == 33
+    assert sa["logit_token_index"].tolist() == [19, 26] and sb["logit_token_index"].tolist() == [32]
+    assert len(sa["temperature"]) == 0 and sb["temperature"].tolist() == [0.0, 0.5, 1.0]
+    assert len(pb["page_copies"]) == 0
