@@ -99,12 +99,21 @@ class BertModel:
         x = self._ln(x, "embed.ln")
         heads, d = c.num_attention_heads, c.hidden_size // c.num_attention_heads
         bias = (1.0 - attention_mask[:, None, None, :].to(torch.float32)) * -1e4
+        # right-padded batches (what the tokenizer produces) are described by their lengths alone
+        lens = attention_mask.sum(dim=1).to(torch.int32)
+        right_padded = bool((attention_mask.cumsum(1) == torch.arange(1, s + 1, device=attention_mask.device)
+                             ).to(attention_mask.dtype).eq(attention_mask).all())
+        use_kernel = x.is_cuda and right_padded and x.dtype in (torch.float16, torch.bfloat16)
         for i in range(c.num_hidden_layers):
             p = f"layers.{i}."
             qkv = ops.linear(x.reshape(b * s, -1), self.lin[p + "qkv"]).view(b, s, 3, heads, d)
-            q, k, v = (qkv[:, :, j].transpose(1, 2) for j in range(3))
-            a = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bias)
-            a = a.transpose(1, 2).reshape(b * s, heads * d).to(x.dtype)
+            if use_kernel:
+                a = ops.encoder_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], key_lens=lens)
+                a = a.reshape(b * s, heads * d)
+            else:
+                q, k, v = (qkv[:, :, j].transpose(1, 2) for j in range(3))
+                a = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bias)
+                a = a.transpose(1, 2).reshape(b * s, heads * d).to(x.dtype)
             x = self._ln(x + ops.linear(a, self.lin[p + "attn_out"]).view(b, s, -1), p + "attn_ln")
             h = ops.linear(x.reshape(b * s, -1), self.lin[p + "up"])
             h = torch.nn.functional.gelu(h.float()).to(x.dtype)

@@ -244,11 +244,10 @@ class VisionTower:
             b = f"{v}encoder.layers.{i}."
             h = self._ln(x, b + "layer_norm1")
             flat = h.reshape(-1, self.hidden)
-            q = ops.linear(flat, self.lin[b + "self_attn.q_proj"]).view(n, -1, self.heads, d).transpose(1, 2)
-            k = ops.linear(flat, self.lin[b + "self_attn.k_proj"]).view(n, -1, self.heads, d).transpose(1, 2)
-            val = ops.linear(flat, self.lin[b + "self_attn.v_proj"]).view(n, -1, self.heads, d).transpose(1, 2)
-            att = torch.softmax((q.float() @ k.float().transpose(-1, -2)) / math.sqrt(d), dim=-1)
-            ctx = (att @ val.float()).to(self.dtype).transpose(1, 2).reshape(-1, self.hidden)
+            q = ops.linear(flat, self.lin[b + "self_attn.q_proj"]).view(n, -1, self.heads, d)
+            k = ops.linear(flat, self.lin[b + "self_attn.k_proj"]).view(n, -1, self.heads, d)
+            val = ops.linear(flat, self.lin[b + "self_attn.v_proj"]).view(n, -1, self.heads, d)
+            ctx = ops.encoder_attention(q, k, val, scale=1.0 / math.sqrt(d)).to(self.dtype).reshape(-1, self.hidden)
             x = x + ops.linear(ctx, self.lin[b + "self_attn.out_proj"]).view(n, -1, self.hidden)
             h = self._ln(x, b + "layer_norm2").reshape(-1, self.hidden)
             h = self.act(ops.linear(h, self.lin[b + "mlp.fc1"]).float()).to(self.dtype)

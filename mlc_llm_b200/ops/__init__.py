@@ -385,6 +385,38 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
     return (out, lse) if return_lse else out
 
 
+def encoder_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_lens: Optional[torch.Tensor] = None,
+                      causal: bool = False, scale: Optional[float] = None) -> torch.Tensor:
+    """Attention over whole sequences (vision towers, BERT-style encoders). ``q``, ``k``, ``v``: ``[B, S, H, D]``
+    views (last dimension contiguous); ``key_lens``: int32 ``[B]`` number of valid keys per batch entry.
+    Returns a contiguous ``[B, S, H, D]`` tensor."""
+    b, s, h, d = q.shape
+    scale = float(scale) if scale is not None else d ** -0.5
+    if q.is_cuda and q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype \
+            and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and k.shape == q.shape == v.shape:
+        out = torch.empty(b, s, h, d, dtype=q.dtype, device=q.device)
+        kl = None if key_lens is None else key_lens.to(torch.int32).contiguous()
+        ll = ctypes.c_longlong
+        rc = lib().mlcb_attn_encoder(ptr(q), ptr(k), ptr(v), ptr(out), ptr(kl), c_int(b), c_int(s), c_int(h), c_int(d),
+                                     ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)),
+                                     ll(k.stride(1)), ll(k.stride(2)), ll(v.stride(0)), ll(v.stride(1)),
+                                     ll(v.stride(2)), c_float(scale), c_int(1 if causal else 0),
+                                     c_int(DTYPE_CODE[q.dtype]), stream_ptr())
+        if rc == 0:
+            return out
+        if rc > 0:
+            check(rc, "mlcb_attn_encoder")
+    # head dims the kernel does not have, fp32, CPU: tensor operations in fp32
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+    att = (qf @ kf.transpose(-1, -2)) * scale
+    if key_lens is not None:
+        pad = torch.arange(s, device=q.device)[None, :] >= key_lens.to(q.device)[:, None]
+        att = att.masked_fill(pad[:, None, None, :], float("-inf"))
+    if causal:
+        att = att.masked_fill(torch.ones(s, s, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    return (torch.softmax(att, dim=-1) @ vf).transpose(1, 2).to(q.dtype).contiguous()
+
+
 # --------------------------------------------------------------------------- logits / sampling
 def softmax_temperature(logits: torch.Tensor, temperature: torch.Tensor, active_vocab: int = 0):
     if not logits.is_cuda:

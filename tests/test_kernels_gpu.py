@@ -820,3 +820,27 @@ def test_group_limited_router_kernel(dtype, e, n_group, topk_group, k, renorm):
     assert torch.equal(i.cpu().sort(dim=1).values, i_ref.sort(dim=1).values)
     order, order_ref = i.cpu().argsort(dim=1), i_ref.argsort(dim=1)
     _close(w.cpu().gather(1, order), w_ref.gather(1, order_ref), 1e-4, 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d", [32, 64, 96, 128])
+@pytest.mark.parametrize("case", ["plain", "padded", "causal", "packed_qkv"])
+def test_encoder_attention(dtype, d, case):
+    """Whole-sequence attention (vision towers, BERT) against fp32 tensor operations: sequence lengths off the
+    64-row tile size, per-batch key lengths, causal masking, and q / k / v as strided views of one projection."""
+    torch.manual_seed(14)
+    b, s, h = 3, 197, 4
+    if case == "packed_qkv":
+        qkv = (torch.randn(b, s, 3, h, d) * 0.8).to(dtype)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        qkv_d = qkv.to(DEV)
+        qd, kd, vd = qkv_d[:, :, 0], qkv_d[:, :, 1], qkv_d[:, :, 2]
+    else:
+        q, k, v = ((torch.randn(b, s, h, d) * 0.8).to(dtype) for _ in range(3))
+        qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    lens = torch.tensor([197, 64, 5], dtype=torch.int32) if case == "padded" else None
+    want = ops.encoder_attention(q.float(), k.float(), v.float(), key_lens=lens, causal=case == "causal")
+    got = ops.encoder_attention(qd, kd, vd, key_lens=None if lens is None else lens.to(DEV), causal=case == "causal")
+    assert got.shape == (b, s, h, d) and got.is_contiguous()
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    _close(got, want, tol, tol)
