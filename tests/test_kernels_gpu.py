@@ -817,9 +817,15 @@ def test_group_limited_router_kernel(dtype, e, n_group, topk_group, k, renorm):
     logits = (torch.randn(301, e) * 2).to(dtype)
     w_ref, i_ref = _group_limited_router(logits.float(), k, n_group, topk_group, renorm)
     w, i = _group_limited_router(logits.to(DEV), k, n_group, topk_group, renorm)
-    assert torch.equal(i.cpu().sort(dim=1).values, i_ref.sort(dim=1).values)
-    order, order_ref = i.cpu().argsort(dim=1), i_ref.argsort(dim=1)
-    _close(w.cpu().gather(1, order), w_ref.gather(1, order_ref), 1e-4, 1e-6)
+    # fp16 logits tie often and the two sides break ties differently: compare what is tie-proof, the sorted
+    # weights, and check that every chosen expert carries the weight it was given
+    _close(w.cpu().sort(dim=1).values, w_ref.sort(dim=1).values, 1e-4, 1e-6)
+    probs = torch.softmax(logits.float(), dim=-1)
+    own = probs.gather(1, i.cpu().long())
+    if renorm:
+        own = own / own.sum(dim=1, keepdim=True)
+    _close(w.cpu(), own, 1e-4, 1e-6)
+    assert all(len(set(row)) == k for row in i.cpu().tolist())
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
