@@ -819,7 +819,12 @@ def test_group_limited_router_kernel(dtype, e, n_group, topk_group, k, renorm):
     w, i = _group_limited_router(logits.to(DEV), k, n_group, topk_group, renorm)
     # fp16 logits tie often and the two sides break ties differently: compare what is tie-proof, the sorted
     # weights, and check that every chosen expert carries the weight it was given
-    _close(w.cpu().sort(dim=1).values, w_ref.sort(dim=1).values, 1e-4, 1e-6)
+    # (with fp16 logits even whole groups tie at the cut, so there only the self-consistency checks apply)
+    if dtype == torch.float32:
+        _close(w.cpu().sort(dim=1).values, w_ref.sort(dim=1).values, 1e-4, 1e-6)
+        assert torch.equal(i.cpu().sort(dim=1).values, i_ref.sort(dim=1).values)
+    groups_used = (i.cpu() // (e // n_group))
+    assert all(len(set(row)) <= topk_group for row in groups_used.tolist())
     probs = torch.softmax(logits.float(), dim=-1)
     own = probs.gather(1, i.cpu().long())
     if renorm:
