@@ -4,8 +4,9 @@
 // kernel sends each (token, slot) pair's hidden row straight into the receive region of the rank that
 // owns the chosen expert (peer stores over NVLink), expert-major within the sender's region, together
 // with the per-expert counts and the pair ids; the receiver turns the counts into the group table of
-// the grouped tensor-core GEMM. The combine kernel sends every expert output row back to the slot of
-// its (token, slot) pair on the token's home rank, where the weighted sum over the k slots runs.
+// the grouped tensor-core GEMM. The combine kernel sends every expert output row to the slot of its
+// (token, slot) pair on every rank, and every rank takes the weighted sum over the k slots of all tokens:
+// the tensor-parallel attention that follows wants every token on every rank, so no gather is needed.
 // Buffers are written by exactly one sender per region and guarded by epoch flags (release / acquire
 // at system scope); all waits are bounded.
 //
@@ -21,10 +22,16 @@ struct EpParams {
   const unsigned long long* disp_meta;  // [world] ints  [world(src)][e_local + 1]: rows per local expert, total
   const unsigned long long* disp_pair;  // [world] ints  [world(src)][cap]: pair id of each row at its home rank
   const unsigned long long* disp_flag;  // [world] ints  [world(src)]
-  const unsigned long long* comb_y;     // [world] rows  [pairs_cap][hidden]
+  const unsigned long long* comb_y;     // [world] rows  [pairs of all ranks][hidden]
   const unsigned long long* comb_flag;  // [world] ints  [world(expert rank)]
   int* done_counter;                    // local, zero between launches
   int* status;
+  // The call number of an exchange lives in device memory, so that a captured forward stays valid when it is
+  // replayed: every kernel of a call uses *epoch_base + epoch, and the call's last kernel (the flag wait of the
+  // combine) moves *epoch_base on. A null epoch_base means `epoch` is the absolute number.
+  int* epoch_base;
+  int pair_base;                        // global id of this rank's first (token, slot) pair
+  __device__ __forceinline__ int call_epoch() const { return epoch + (epoch_base ? *epoch_base : 0); }
 };
 
 // One warp per (token, slot) pair.
@@ -44,7 +51,7 @@ ep_dispatch_kernel(const T* __restrict__ x, const int* __restrict__ experts, con
       uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.disp_x[dst]) +
                                             (static_cast<size_t>(p.rank) * p.cap + row) * p.hidden * sizeof(T));
       for (int v = lane; v < p.hidden / 8; v += 32) out[v] = src[v];
-      if (lane == 0) reinterpret_cast<int*>(p.disp_pair[dst])[p.rank * p.cap + row] = pair;
+      if (lane == 0) reinterpret_cast<int*>(p.disp_pair[dst])[p.rank * p.cap + row] = p.pair_base + pair;
     } else if (lane == 0 && p.status) {
       atomicCAS(p.status, 0, ERR_CAPACITY);
     }
@@ -72,7 +79,7 @@ ep_dispatch_kernel(const T* __restrict__ x, const int* __restrict__ experts, con
   if (is_last) {
     __threadfence_system();
     if (threadIdx.x < p.world)
-      flag_store_release_sys(reinterpret_cast<int*>(p.disp_flag[threadIdx.x]) + p.rank, p.epoch);
+      flag_store_release_sys(reinterpret_cast<int*>(p.disp_flag[threadIdx.x]) + p.rank, p.call_epoch());
   }
 }
 
@@ -83,7 +90,7 @@ __global__ void ep_build_groups_kernel(const EpParams p, int* __restrict__ group
                                        int* __restrict__ group_slab, int* __restrict__ rows_of_src) {
   const int* flags = reinterpret_cast<const int*>(p.disp_flag[p.rank]);
   const int* meta = reinterpret_cast<const int*>(p.disp_meta[p.rank]);
-  if (threadIdx.x < p.world) flag_wait_ge(flags + threadIdx.x, p.epoch, nullptr, p.status, ERR_WAIT_PEER);
+  if (threadIdx.x < p.world) flag_wait_ge(flags + threadIdx.x, p.call_epoch(), nullptr, p.status, ERR_WAIT_PEER);
   __syncthreads();
   for (int g = threadIdx.x; g < p.world * p.e_local; g += blockDim.x) {
     const int src = g / p.e_local, e = g % p.e_local;
@@ -107,9 +114,14 @@ ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ rows_of_
   if (src < p.world && row < min(p.cap, rows_of_src[src])) {
     const int pair = __ldcg(reinterpret_cast<const int*>(p.disp_pair[p.rank]) + idx);
     const uint4* in = reinterpret_cast<const uint4*>(y + static_cast<size_t>(idx) * p.hidden);
-    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.comb_y[src]) +
-                                          static_cast<size_t>(pair) * p.hidden * sizeof(T));
-    for (int v = lane; v < p.hidden / 8; v += 32) out[v] = in[v];
+    // every rank sums every token (the attention that follows wants all tokens everywhere): the row goes to
+    // all ranks, at its global pair slot
+    for (int v = lane; v < p.hidden / 8; v += 32) {
+      const uint4 val = in[v];
+      for (int dst = 0; dst < p.world; ++dst)
+        reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.comb_y[dst]) +
+                                 static_cast<size_t>(pair) * p.hidden * sizeof(T))[v] = val;
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -123,12 +135,16 @@ ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ rows_of_
   if (is_last) {
     __threadfence_system();
     if (threadIdx.x < p.world)
-      flag_store_release_sys(reinterpret_cast<int*>(p.comb_flag[threadIdx.x]) + p.rank, p.epoch);
+      flag_store_release_sys(reinterpret_cast<int*>(p.comb_flag[threadIdx.x]) + p.rank, p.call_epoch());
   }
 }
 
-__global__ void ep_wait_flags_kernel(const int* flags, int n, int epoch, int* status) {
-  if (threadIdx.x < n) flag_wait_ge(flags + threadIdx.x, epoch, nullptr, status, ERR_WAIT_PEER);
+// Last kernel of an exchange: waits for every expert rank's combine flag, then moves the call number on.
+__global__ void ep_wait_flags_kernel(const int* flags, int n, int epoch, int* epoch_base, int* status) {
+  const int want = epoch + (epoch_base ? *epoch_base : 0);
+  if (threadIdx.x < n) flag_wait_ge(flags + threadIdx.x, want, nullptr, status, ERR_WAIT_PEER);
+  __syncthreads();
+  if (threadIdx.x == 0 && epoch_base) *epoch_base = want;
 }
 
 }  // namespace mlcb
@@ -145,6 +161,8 @@ struct MlcbEpArgs {
   const unsigned long long* comb_flag;
   void* done_counter;
   void* status;
+  void* epoch_base;
+  int pair_base;
 };
 
 static EpParams to_params(const MlcbEpArgs* a) {
@@ -155,6 +173,8 @@ static EpParams to_params(const MlcbEpArgs* a) {
   p.comb_y = a->comb_y; p.comb_flag = a->comb_flag;
   p.done_counter = static_cast<int*>(a->done_counter);
   p.status = static_cast<int*>(a->status);
+  p.epoch_base = static_cast<int*>(a->epoch_base);
+  p.pair_base = a->pair_base;
   return p;
 }
 
@@ -193,8 +213,9 @@ MLCB_API int mlcb_ep_combine_send(const void* y, const int* rows_of_src, const M
   return static_cast<int>(cudaGetLastError());
 }
 
-MLCB_API int mlcb_ep_wait_flags(const int* flags, int n, int epoch, int* status, cudaStream_t stream) {
-  ep_wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
+MLCB_API int mlcb_ep_wait_flags(const int* flags, int n, int epoch, int* epoch_base, int* status,
+                                cudaStream_t stream) {
+  ep_wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, epoch_base, status);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -312,8 +312,14 @@ class DecoderModel:
         architecture has the plain pre-norm RMSNorm block structure they implement; otherwise the
         model keeps the NCCL all-reduce path. Returns whether the fused path is on."""
         c = self.cfg
+        # mixture-of-experts layers qualify when whole experts live on the ranks (their exchange is this
+        # package's kernels, the block's output then only has to be added to the residual stream) and no
+        # shared expert needs a reduction of its own
+        moe_ok = c.num_experts == 0 or (
+            getattr(self, "ep", None) is not None and getattr(fused, "mode", "") == "ar"
+            and c.shared_expert_intermediate_size <= 0 and c.moe_router != "llama4_sigmoid")
         plain = (c.norm_type == "rms" and not c.parallel_residual and not c.post_attention_norm
-                 and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and c.num_experts == 0
+                 and not c.post_mlp_norm and not c.extra.get("no_pre_norm") and moe_ok
                  and c.gated_mlp and c.position_embedding != "learned" and "residual_scale" not in c.extra
                  and "mla" not in c.extra and "llama4" not in c.extra
                  and self.dtype in (torch.float16, torch.bfloat16))
@@ -346,8 +352,6 @@ class DecoderModel:
                 h = f.gemm_ar_norm(ctx, self.p.linears[pre + "self_attn.o_proj"],
                                    self.p.tensors[pre + "post_attention_layernorm.weight"], c.rms_norm_eps,
                                    c.norm_weight_offset)
-                g = ops.linear(h, self.p.linears[pre + "mlp.gate_up_proj"])
-                a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
                 if pos + 1 < len(layers):
                     nxt = f"model.layers.{layers[pos + 1]}.input_layernorm"
                 elif self.last_stage:
@@ -356,6 +360,17 @@ class DecoderModel:
                     # the next stage normalises with its own first layer's weight; this call's norm output is
                     # not used, only the residual it leaves behind
                     nxt = pre + "post_attention_layernorm"
+                if c.is_moe_layer(li):
+                    # expert-parallel block: every rank ends up with the output of all tokens, which joins the
+                    # residual stream by the add + norm kernel (no collective of its own)
+                    from .moe import moe_block  # pylint: disable=import-outside-toplevel
+
+                    out = moe_block(self, li, h)
+                    h = ops.add_rmsnorm(out.contiguous(), f.residual[: x.shape[0]], self.p.tensors[nxt + ".weight"],
+                                        c.rms_norm_eps, c.norm_weight_offset)
+                    continue
+                g = ops.linear(h, self.p.linears[pre + "mlp.gate_up_proj"])
+                a = ops.act_mul(g, "silu" if c.hidden_act == "silu" else "gelu")
                 h = f.gemm_ar_norm(a, self.p.linears[pre + "mlp.down_proj"], self.p.tensors[nxt + ".weight"],
                                    c.rms_norm_eps, c.norm_weight_offset)
             f.end()

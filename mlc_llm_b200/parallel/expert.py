@@ -9,11 +9,13 @@ Every rank owns ``E / world`` whole experts and a contiguous slice of the batch'
    per-expert counts and the pair ids, then raises this rank's flag at every destination;
 3. ``mlcb_ep_build_groups`` (receiver) waits for all senders and builds the GEMM's group table;
 4. two grouped GEMMs with the activation in between run on the received rows;
-5. ``mlcb_ep_combine_send`` returns each output row to its pair's slot at the token's home rank;
-6. the home rank waits for all expert ranks and takes the weighted sum over the k slots.
+5. ``mlcb_ep_combine_send`` sends each output row to its pair's slot on *every* rank;
+6. every rank waits for all expert ranks and takes the weighted sum over the k slots of all tokens (the
+   attention that follows is tensor parallel and wants every token on every rank, so no gather follows).
 
-The token slices are finally concatenated with one NCCL all-gather, because the attention that follows
-is tensor parallel and wants every token on every rank.
+Call numbers (the epochs the flags carry) live in device memory and the last kernel of an exchange moves
+them on, so a forward with these exchanges inside can be captured in a CUDA graph and replayed; nothing in the
+exchange is an NCCL call.
 
 The reference shards experts over their width instead (``model/mixtral/mixtral_model.py:144-145``)
 and has no all-to-all; that layout remains available (``expert_parallel=False``) and is the numerics
@@ -42,6 +44,7 @@ class EpArgs(ctypes.Structure):
         ("disp_x", ctypes.c_void_p), ("disp_meta", ctypes.c_void_p), ("disp_pair", ctypes.c_void_p),
         ("disp_flag", ctypes.c_void_p), ("comb_y", ctypes.c_void_p), ("comb_flag", ctypes.c_void_p),
         ("done_counter", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("epoch_base", ctypes.c_void_p), ("pair_base", ctypes.c_int),
     ]
 
 
@@ -66,7 +69,7 @@ class ExpertParallel:
         x_bytes = _up(world * self.cap * hidden * es)
         meta_bytes = _up(world * (self.e_local + 1) * 4)
         pair_bytes = _up(world * self.cap * 4)
-        comb_bytes = _up(self.tokens_cap * top_k * hidden * es)
+        comb_bytes = _up(world * self.tokens_cap * top_k * hidden * es)   # the pairs of all ranks
         # two parities of every data region, one set of flags
         self.off = {}
         cur = 0
@@ -90,7 +93,10 @@ class ExpertParallel:
         self.group_count = torch.zeros(g, dtype=torch.int32, device=device)
         self.group_slab = torch.zeros(g, dtype=torch.int32, device=device)
         self.rows_of_src = torch.zeros(8, dtype=torch.int32, device=device)
-        self.epoch = 0
+        # number of finished exchanges: `epoch_dev` on the device (moved on by the last kernel of each
+        # exchange), `base` its host mirror (which buffer parity the next exchange uses)
+        self.epoch_dev = torch.zeros(4, dtype=torch.int32, device=device)
+        self.base = 0
         self.launches = 0
 
     def token_slice(self, tokens: int) -> range:
@@ -98,11 +104,17 @@ class ExpertParallel:
         lo = min(tokens, self.rank * per)
         return range(lo, min(tokens, lo + per))
 
-    def _args(self, pairs: int) -> EpArgs:
-        par = self.epoch & 1
+    def note_replay(self, calls: int) -> None:
+        """A captured forward with ``calls`` exchanges was replayed (the device counter moved by itself)."""
+        self.base += calls
+
+    def _args(self, pairs: int, pair_base: int) -> EpArgs:
+        par = (self.base + 1) & 1
         a = EpArgs()
         a.world, a.rank, a.e_local, a.k = self.world, self.rank, self.e_local, self.k
-        a.hidden, a.cap, a.epoch, a.pairs = self.hidden, self.cap, self.epoch, pairs
+        a.hidden, a.cap, a.epoch, a.pairs = self.hidden, self.cap, 1, pairs   # epoch: relative to *epoch_base
+        a.epoch_base = self.epoch_dev.data_ptr()
+        a.pair_base = pair_base
         a.disp_x = self.table[self.row[f"x{par}"]].data_ptr()
         a.disp_meta = self.table[self.row[f"meta{par}"]].data_ptr()
         a.disp_pair = self.table[self.row[f"pair{par}"]].data_ptr()
@@ -113,17 +125,21 @@ class ExpertParallel:
         a.status = status_word(self.device).data_ptr()
         return a
 
-    def ffn(self, x: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor, w13, w2,
+    def ffn(self, h: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor, w13, w2,
             act: str = "silu") -> torch.Tensor:
-        """Expert FFN of this rank's token slice ``x [t, hidden]`` with routing ``weights / experts
-        [t, k]``; ``w13 / w2`` hold this rank's ``e_local`` experts. Returns ``[t, hidden]``."""
+        """Expert FFN of all tokens ``h [T, hidden]`` (replicated on the ranks) with routing ``weights /
+        experts [T, k]``; this rank dispatches its slice of the tokens, runs its ``e_local`` experts (``w13 /
+        w2``) on what it receives, and sums the outputs of all tokens. Returns ``[T, hidden]``."""
+        total = h.shape[0]
+        sl = self.token_slice(total)
+        x, experts_own = h[sl.start: sl.stop], experts[sl.start: sl.stop]
         t = x.shape[0]
         if t > self.tokens_cap:
             raise ValueError(f"{t} tokens exceed the expert-parallel buffers ({self.tokens_cap} per rank)")
-        self.epoch += 1
-        par = self.epoch & 1
+        par = (self.base + 1) & 1
         pairs = t * self.k
-        a = self._args(pairs)
+        a = self._args(pairs, sl.start * self.k)
+        experts = experts_own
         dt = DTYPE_CODE[x.dtype]
         x = x.contiguous()
         if pairs:
@@ -150,15 +166,23 @@ class ExpertParallel:
                                         stream_ptr())
         check(rc, "mlcb_ep_combine_send")
         flags = self.buf.peer_ptr(self.rank, self.off["cflag"])
-        rc = lib().mlcb_ep_wait_flags(ctypes.c_void_p(flags), ctypes.c_int(self.world), ctypes.c_int(self.epoch),
-                                      ptr(status_word(self.device)), stream_ptr())
+        rc = lib().mlcb_ep_wait_flags(ctypes.c_void_p(flags), ctypes.c_int(self.world), ctypes.c_int(1),
+                                      ptr(self.epoch_dev), ptr(status_word(self.device)), stream_ptr())
         check(rc, "mlcb_ep_wait_flags")
+        self.base += 1
         self.launches += 6
-        if not pairs:
-            return torch.zeros(0, self.hidden, dtype=self.dtype, device=self.device)
-        comb = self.buf.view(self.off[f"comb{par}"], (self.tokens_cap * self.k, self.hidden), self.dtype)[:pairs]
-        ident = torch.arange(pairs, dtype=torch.int32, device=self.device)
+        all_pairs = total * self.k
+        comb = self.buf.view(self.off[f"comb{par}"], (self.world * self.tokens_cap * self.k, self.hidden),
+                             self.dtype)[:all_pairs]
+        ident = self._ident(all_pairs)
         return ops.moe_combine(comb, weights.contiguous(), ident, None)
+
+    def _ident(self, n: int) -> torch.Tensor:
+        """0 .. n-1 (the combine reads pair p of the buffer for pair p); one allocation, grown on demand."""
+        cur = getattr(self, "_ident_buf", None)
+        if cur is None or cur.numel() < n:
+            cur = self._ident_buf = torch.arange(max(n, 4096), dtype=torch.int32, device=self.device)
+        return cur[:n]
 
     def _grouped(self, x: torch.Tensor, lw, rows: int, hint: int) -> torch.Tensor:
         n, k = lw.w.shape[1], x.shape[1]
@@ -177,20 +201,10 @@ class ExpertParallel:
 
 def expert_parallel_ffn(model, h: torch.Tensor, weights: torch.Tensor, experts: torch.Tensor, w13, w2
                         ) -> torch.Tensor:
-    """MoE FFN of all tokens ``h [T, hidden]`` (replicated on the ranks): each rank handles its token
-    slice through the all-to-all exchange, then the slices are all-gathered."""
+    """MoE FFN of all tokens ``h [T, hidden]`` (replicated on the ranks): each rank dispatches its token
+    slice through the all-to-all exchange and every rank receives the expert outputs of all tokens."""
     ep: Optional[ExpertParallel] = getattr(model, "ep", None)
     if ep is None:
         raise RuntimeError("expert parallelism was requested but its buffers were not created")
-    t = h.shape[0]
-    sl = ep.token_slice(t)
     act = "silu" if model.cfg.hidden_act == "silu" else "gelu"
-    out = ep.ffn(h[sl.start: sl.stop], weights[sl.start: sl.stop], experts[sl.start: sl.stop], w13, w2, act)
-    if ep.world == 1:
-        return out
-    per = -(-t // ep.world)
-    padded = torch.zeros(per, h.shape[1], dtype=h.dtype, device=h.device)
-    padded[: out.shape[0]] = out
-    gathered = torch.empty(per * ep.world, h.shape[1], dtype=h.dtype, device=h.device)
-    dist.all_gather_into_tensor(gathered, padded, group=ep.group)
-    return gathered[:t]
+    return ep.ffn(h, weights, experts, w13, w2, act)

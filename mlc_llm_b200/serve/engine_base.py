@@ -374,6 +374,14 @@ class EngineRuntime:
         fused_mode = os.environ.get("MLCB_FUSED_TP", "auto")
         use_fused = fused_mode == "1" or (fused_mode == "auto" and tp in (2, 4, 8))
         # "1" on a single GPU runs the same kernels with one rank (peer tables point at local memory)
+        for m in self.models:
+            if m.cfg.expert_parallel and m.cfg.num_experts > 0 and tp > 1 and self.device.type == "cuda":
+                from ..parallel.expert import ExpertParallel  # pylint: disable=import-outside-toplevel
+
+                max_tokens = max(int(full.get("prefill_chunk_size") or 2048),
+                                 int(full["max_num_sequence"]) * ((full.get("spec_draft_length") or 0) + 1))
+                m.ep = ExpertParallel(m.cfg.num_experts, m.cfg.num_experts_per_tok, m.cfg.hidden_size, m.dtype,
+                                      max_tokens, self.device, group=comm.tp_group, world_size=tp)
         if (tp > 1 or fused_mode == "1") and self.device.type == "cuda" and use_fused:
             # fused GEMM+collective kernels over symmetric peer buffers (main model only)
             from ..parallel.fused import FusedCollectives  # pylint: disable=import-outside-toplevel
@@ -385,14 +393,6 @@ class EngineRuntime:
                 fused = FusedCollectives(main_model.cfg.hidden_size, main_model.dtype, max_tokens, self.device,
                                          group=comm.tp_group if tp > 1 else None, world_size=tp)
                 self.fused_tp = main_model.enable_fused(fused)
-        for m in self.models:
-            if m.cfg.expert_parallel and m.cfg.num_experts > 0 and tp > 1 and self.device.type == "cuda":
-                from ..parallel.expert import ExpertParallel  # pylint: disable=import-outside-toplevel
-
-                max_tokens = max(int(full.get("prefill_chunk_size") or 2048),
-                                 int(full["max_num_sequence"]) * ((full.get("spec_draft_length") or 0) + 1))
-                m.ep = ExpertParallel(m.cfg.num_experts, m.cfg.num_experts_per_tok, m.cfg.hidden_size, m.dtype,
-                                      max_tokens, self.device, group=comm.tp_group, world_size=tp)
         slots = int(full["max_num_sequence"]) * 2 * ((full.get("spec_draft_length") or 4) + 1) \
             if full.get("speculative_mode", "disable") != "disable" else 0
         self.executor = ModelExecutor(self.models, self.device, comm, max_draft_slots=slots)

@@ -395,7 +395,14 @@ class ModelExecutor:
         multi = self.comm is not None and self.comm.world_size > 1
         if multi and getattr(model, "fused", None) is None:
             return False
-        return (self.use_graphs and not self._pipeline(model_id) and getattr(model, "ep", None) is None
+        # (an expert-parallel model qualifies through the fused forward: its exchanges are this package's
+        # kernels with call numbers in device memory; its NCCL forward is not captured)
+        ep_ok = getattr(model, "ep", None) is None or (
+            getattr(model, "fused", None) is not None
+            # the exchange buffers alternate between two parities: a replayed forward must start on the parity
+            # it was captured with, so it has to contain an even number of exchanges
+            and sum(1 for li in model.layers if model.cfg.is_moe_layer(li)) % 2 == 0)
+        return (self.use_graphs and not self._pipeline(model_id) and ep_ok
                 and not getattr(model, "stateful", False) and self._tc_attention_ok(model)
                 and not self._masked_attention(model))
 
@@ -460,6 +467,8 @@ class ModelExecutor:
             before = lib().mlcb_launch_count()
             fused = getattr(model, "fused", None)
             base = fused.base if fused is not None else 0
+            ep = getattr(model, "ep", None)
+            ep_base = ep.base if ep is not None else 0
             multi = self.comm is not None and self.comm.world_size > 1
             with torch.cuda.graph(graph, pool=self._graph_pool,
                                   capture_error_mode="thread_local" if multi else "global"):
@@ -471,11 +480,19 @@ class ModelExecutor:
                 calls, fused.base = fused.base - base, base
                 if calls % 2:
                     raise RuntimeError("a captured fused forward must make an even number of reduce-scatter calls")
-            entry.update(graph=graph, hidden=hidden, normed=normed, fused_calls=calls,
+            ep_calls = 0
+            if ep is not None:
+                # the same for the expert exchanges; buffer parities repeat only after an even number of them
+                ep_calls, ep.base = ep.base - ep_base, ep_base
+                if ep_calls % 2:
+                    raise RuntimeError("a captured forward must make an even number of expert exchanges")
+            entry.update(graph=graph, hidden=hidden, normed=normed, fused_calls=calls, ep_calls=ep_calls,
                          launches=int(lib().mlcb_launch_count() - before))
         entry["graph"].replay()
         if entry.get("fused_calls"):
             model.fused.note_replay(entry["fused_calls"])
+        if entry.get("ep_calls"):
+            model.ep.note_replay(entry["ep_calls"])
         self.graph_replays += 1
         self.graph_launches += entry["launches"]  # kernels a replay launches (the C counter sees captures only)
         model._final_normed = entry["normed"]  # pylint: disable=protected-access

@@ -117,9 +117,16 @@ def test_tensor_parallel_logits_match_the_oracle(world, mode):
 
 
 @pytest.mark.parametrize("world", [pytest.param(n, marks=_need(n)) for n in (2, 4, 8)])
-def test_expert_parallel_logits_match_the_oracle(world):
-    got, _ = _worker_logits(world, MIXTRAL + "&expert_parallel=true", "cuda", 29630 + world, {"MLCB_FUSED_TP": "0"})
-    _check(got, _oracle(MIXTRAL), (world, "ep"), routed=True)
+@pytest.mark.parametrize("mode", ["nccl_attention", "fused_graph"])
+def test_expert_parallel_logits_match_the_oracle(world, mode):
+    """Experts sharded whole over the ranks (dispatch / combine exchanges). ``nccl_attention``: the attention's
+    all-reduce is NCCL, eager launches; ``fused_graph``: fused all-reduce kernels and the whole decode forward,
+    exchanges included, replayed from CUDA graphs."""
+    env = {"MLCB_FUSED_TP": "0"} if mode == "nccl_attention" else {"MLCB_FUSED_TP": "1", "MLCB_CUDA_GRAPH": "1"}
+    got, flags = _worker_logits(world, MIXTRAL + "&expert_parallel=true", "cuda", 29630 + world, env)
+    if mode == "fused_graph":
+        assert flags["fused_tp"] and flags["graph_replays"] > 0
+    _check(got, _oracle(MIXTRAL), (world, "ep", mode), routed=True)
 
 
 @pytest.mark.parametrize("world", [pytest.param(n, marks=_need(n)) for n in (2, 4, 8)])
