@@ -150,9 +150,11 @@ __global__ void act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t
 // in: [T, 2*I] (gate half then up half), out: [T, I]. act: 0 = SiLU, 1 = GELU(tanh).
 template <typename T>
 __global__ void act_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
-                               size_t total_vec, int act) {
+                               size_t total_vec, int act, const int* __restrict__ live_rows) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   const int vec_per_row = inter / 8;
+  // a device-side row count (expert-parallel buffers: only the rows that arrived are worked on)
+  if (live_rows) total_vec = min(total_vec, static_cast<size_t>(max(0, live_rows[0])) * vec_per_row);
   for (size_t v = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total_vec;
        v += stride) {
     const size_t t = v / vec_per_row;
@@ -558,17 +560,17 @@ MLCB_API int mlcb_act(const void* in, void* out, long long elems, int act, int d
 }
 
 MLCB_API int mlcb_act_mul(const void* in, void* out, int tokens, int inter, int act, int dtype,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const int* live_rows) {
   if (tokens <= 0) return 0;
   if (inter % 8) return -1;
   size_t total = static_cast<size_t>(tokens) * (inter / 8);
   int blocks = static_cast<int>((total + 255) / 256);
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   if (dtype == 0)
-    act_mul_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)in, (__half*)out, inter, total, act);
+    act_mul_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)in, (__half*)out, inter, total, act, live_rows);
   else
     act_mul_kernel<__nv_bfloat16>
-        <<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total, act);
+        <<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total, act, live_rows);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -83,36 +83,68 @@ ep_dispatch_kernel(const T* __restrict__ x, const int* __restrict__ experts, con
   }
 }
 
-// Receiver: wait for every sender's flag, then build the group table of the grouped GEMM. Group
-// g = src * e_local + e covers rows [begin, begin + count) of this rank's receive buffer and uses
-// weight slab e. rows_of_src[src] = rows received from src.
+// Receiver: wait for every sender's flag, then lay the received rows out expert by expert. A sender's region
+// holds its rows expert-major, so the rows of local expert e arrive as `world` segments (one per sender).
+// The table describes them in expert-major order, segment g = e * world + src: where the segment sits in the
+// receive buffer (seg_src), where it goes in the compact buffer (seg_dst), how long it is (seg_cnt). The
+// grouped GEMM then sees one group per local expert (group e = compact rows [group_begin[e], + group_count[e]),
+// weight slab e), so every expert's weights are streamed once, not once per sender. live[0] = rows received.
 __global__ void ep_build_groups_kernel(const EpParams p, int* __restrict__ group_begin, int* __restrict__ group_count,
-                                       int* __restrict__ group_slab, int* __restrict__ rows_of_src) {
+                                       int* __restrict__ group_slab, int* __restrict__ seg_src,
+                                       int* __restrict__ seg_dst, int* __restrict__ seg_cnt, int* __restrict__ live) {
   const int* flags = reinterpret_cast<const int*>(p.disp_flag[p.rank]);
   const int* meta = reinterpret_cast<const int*>(p.disp_meta[p.rank]);
   if (threadIdx.x < p.world) flag_wait_ge(flags + threadIdx.x, p.call_epoch(), nullptr, p.status, ERR_WAIT_PEER);
   __syncthreads();
-  for (int g = threadIdx.x; g < p.world * p.e_local; g += blockDim.x) {
-    const int src = g / p.e_local, e = g % p.e_local;
-    const int* m = meta + src * (p.e_local + 1);
-    int begin = src * p.cap;
-    for (int i = 0; i < e; ++i) begin += __ldcg(m + i);
-    group_begin[g] = begin;
-    group_count[g] = __ldcg(m + e);
-    group_slab[g] = e;
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < p.e_local; ++e) {
+      group_begin[e] = run;
+      group_slab[e] = e;
+      for (int src = 0; src < p.world; ++src) {
+        const int* m = meta + src * (p.e_local + 1);
+        int begin = src * p.cap;
+        for (int i = 0; i < e; ++i) begin += __ldcg(m + i);
+        const int cnt = __ldcg(m + e);
+        const int g = e * p.world + src;
+        seg_src[g] = begin;
+        seg_dst[g] = run;
+        seg_cnt[g] = cnt;
+        run += cnt;
+      }
+      group_count[e] = run - group_begin[e];
+    }
+    live[0] = run;
   }
-  if (threadIdx.x < p.world) rows_of_src[threadIdx.x] = __ldcg(meta + threadIdx.x * (p.e_local + 1) + p.e_local);
 }
 
-// One warp per received row: send the expert output back to its pair's slot at the home rank.
+// One warp per compact row: copy the row (and its pair id) from its segment of the receive buffer.
 template <typename T>
 __global__ void __launch_bounds__(256)
-ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ rows_of_src, const EpParams p) {
+ep_compact_kernel(const T* __restrict__ recv, T* __restrict__ xc, const int* __restrict__ pair_in,
+                  int* __restrict__ pair_out, const int* __restrict__ seg_src, const int* __restrict__ seg_dst,
+                  const int* __restrict__ seg_cnt, const int* __restrict__ live, int segments, int hidden) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int idx = blockIdx.x * 8 + warp;  // src * cap + row
-  const int src = idx / p.cap, row = idx % p.cap;
-  if (src < p.world && row < min(p.cap, rows_of_src[src])) {
-    const int pair = __ldcg(reinterpret_cast<const int*>(p.disp_pair[p.rank]) + idx);
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= live[0]) return;
+  int g = 0;
+  while (g + 1 < segments && r >= seg_dst[g] + seg_cnt[g]) ++g;  // segments are in compact-row order
+  const int src_row = seg_src[g] + (r - seg_dst[g]);
+  const uint4* in = reinterpret_cast<const uint4*>(recv + static_cast<size_t>(src_row) * hidden);
+  uint4* out = reinterpret_cast<uint4*>(xc + static_cast<size_t>(r) * hidden);
+  for (int v = lane; v < hidden / 8; v += 32) out[v] = __ldcg(in + v);
+  if (lane == 0) pair_out[r] = __ldcg(pair_in + src_row);
+}
+
+// One warp per compact row: send the expert output to its pair's slot on every rank.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ live, const int* __restrict__ pairs,
+                       const EpParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * 8 + warp;  // compact row
+  if (idx < live[0]) {
+    const int pair = pairs[idx];
     const uint4* in = reinterpret_cast<const uint4*>(y + static_cast<size_t>(idx) * p.hidden);
     // every rank sums every token (the attention that follows wants all tokens everywhere): the row goes to
     // all ranks, at its global pair slot
@@ -194,21 +226,42 @@ MLCB_API int mlcb_ep_dispatch(const void* x, const int* experts, const int* sort
 }
 
 MLCB_API int mlcb_ep_build_groups(const MlcbEpArgs* a, int* group_begin, int* group_count, int* group_slab,
-                                  int* rows_of_src, cudaStream_t stream) {
-  ep_build_groups_kernel<<<1, 256, 0, stream>>>(to_params(a), group_begin, group_count, group_slab, rows_of_src);
+                                  int* seg_src, int* seg_dst, int* seg_cnt, int* live, cudaStream_t stream) {
+  ep_build_groups_kernel<<<1, 32, 0, stream>>>(to_params(a), group_begin, group_count, group_slab, seg_src, seg_dst,
+                                               seg_cnt, live);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
-// y [world * cap, hidden]: expert outputs in the receive layout.
-MLCB_API int mlcb_ep_combine_send(const void* y, const int* rows_of_src, const MlcbEpArgs* a, int dtype,
+// recv / pair_in: this rank's receive buffer [rows_max, hidden] and the pair ids of its rows; xc / pair_out: the
+// compact, expert-major copy (rows [0, live[0])).
+MLCB_API int mlcb_ep_compact(const void* recv, void* xc, const int* pair_in, int* pair_out, const int* seg_src,
+                             const int* seg_dst, const int* seg_cnt, const int* live, int segments, int rows_max,
+                             int hidden, int dtype, cudaStream_t stream) {
+  if (rows_max <= 0) return 0;
+  if (hidden % 8) return -1;
+  const int grid = (rows_max + 7) / 8;
+  if (dtype == 0)
+    ep_compact_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(recv), static_cast<__half*>(xc),
+                                                        pair_in, pair_out, seg_src, seg_dst, seg_cnt, live, segments,
+                                                        hidden);
+  else
+    ep_compact_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(recv),
+                                                               static_cast<__nv_bfloat16*>(xc), pair_in, pair_out,
+                                                               seg_src, seg_dst, seg_cnt, live, segments, hidden);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+// y [.., hidden]: expert outputs of the compact rows [0, live[0]); pairs: their global pair ids.
+MLCB_API int mlcb_ep_combine_send(const void* y, const int* live, const int* pairs, const MlcbEpArgs* a, int dtype,
                                   cudaStream_t stream) {
   const EpParams p = to_params(a);
   const int grid = (p.world * p.cap + 7) / 8;
   if (dtype == 0)
-    ep_combine_send_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(y), rows_of_src, p);
+    ep_combine_send_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(y), live, pairs, p);
   else
-    ep_combine_send_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), rows_of_src, p);
+    ep_combine_send_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), live, pairs, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

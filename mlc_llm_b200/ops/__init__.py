@@ -286,7 +286,9 @@ def activation(x: torch.Tensor, act: str) -> torch.Tensor:
     return out
 
 
-def act_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
+def act_mul(x: torch.Tensor, act: str = "silu", live_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(gate) * up`` of ``[.., 2 * I]`` rows. ``live_rows`` (int32 device scalar): only that many leading rows
+    are computed, the rest of the output is left as allocated."""
     if not x.is_cuda:
         return ref.act_mul(x, act)
     assert x.is_contiguous()
@@ -294,7 +296,8 @@ def act_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
     out = torch.empty(*x.shape[:-1], inter, dtype=x.dtype, device=x.device)
     tokens = x.numel() // x.shape[-1]
     rc = lib().mlcb_act_mul(ptr(x), ptr(out), c_int(tokens), c_int(inter),
-                            c_int(0 if act == "silu" else 1), c_int(DTYPE_CODE[x.dtype]), stream_ptr())
+                            c_int(0 if act == "silu" else 1), c_int(DTYPE_CODE[x.dtype]), stream_ptr(),
+                            ptr(live_rows))
     check(rc, "mlcb_act_mul")
     return out
 

@@ -7,7 +7,9 @@ Every rank owns ``E / world`` whole experts and a contiguous slice of the batch'
 1. ``moe_permute`` orders this rank's (token, slot) pairs by expert (hence by destination rank);
 2. ``mlcb_ep_dispatch`` writes each pair's hidden row into the destination's receive region, plus the
    per-expert counts and the pair ids, then raises this rank's flag at every destination;
-3. ``mlcb_ep_build_groups`` (receiver) waits for all senders and builds the GEMM's group table;
+3. ``mlcb_ep_build_groups`` (receiver) waits for all senders and builds the table of received segments,
+   ``mlcb_ep_compact`` copies them expert-major into one contiguous buffer (one GEMM group per local expert:
+   an expert's weights are streamed once per exchange, not once per sender);
 4. two grouped GEMMs with the activation in between run on the received rows;
 5. ``mlcb_ep_combine_send`` sends each output row to its pair's slot on *every* rank;
 6. every rank waits for all expert ranks and takes the weighted sum over the k slots of all tokens (the
@@ -88,11 +90,18 @@ class ExpertParallel:
         self.table = table.to(device)
         self.row = {n: i for i, n in enumerate(names)}
         self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        # one GEMM group per local expert over the compact (expert-major) copy of the received rows; the
+        # received rows of an expert come as one segment per sender
         g = self.world * self.e_local
-        self.group_begin = torch.zeros(g, dtype=torch.int32, device=device)
-        self.group_count = torch.zeros(g, dtype=torch.int32, device=device)
-        self.group_slab = torch.zeros(g, dtype=torch.int32, device=device)
-        self.rows_of_src = torch.zeros(8, dtype=torch.int32, device=device)
+        self.group_begin = torch.zeros(self.e_local, dtype=torch.int32, device=device)
+        self.group_count = torch.zeros(self.e_local, dtype=torch.int32, device=device)
+        self.group_slab = torch.zeros(self.e_local, dtype=torch.int32, device=device)
+        self.seg_src = torch.zeros(g, dtype=torch.int32, device=device)
+        self.seg_dst = torch.zeros(g, dtype=torch.int32, device=device)
+        self.seg_cnt = torch.zeros(g, dtype=torch.int32, device=device)
+        self.live = torch.zeros(4, dtype=torch.int32, device=device)
+        self.xc = torch.zeros(world * self.cap, hidden, dtype=dtype, device=device)
+        self.pair_c = torch.zeros(world * self.cap, dtype=torch.int32, device=device)
         # number of finished exchanges: `epoch_dev` on the device (moved on by the last kernel of each
         # exchange), `base` its host mirror (which buffer parity the next exchange uses)
         self.epoch_dev = torch.zeros(4, dtype=torch.int32, device=device)
@@ -153,16 +162,26 @@ class ExpertParallel:
         check(rc, "mlcb_ep_dispatch")
         a.done_counter = self.done[1:].data_ptr()
         rc = lib().mlcb_ep_build_groups(ctypes.byref(a), ptr(self.group_begin), ptr(self.group_count),
-                                        ptr(self.group_slab), ptr(self.rows_of_src), stream_ptr())
+                                        ptr(self.group_slab), ptr(self.seg_src), ptr(self.seg_dst),
+                                        ptr(self.seg_cnt), ptr(self.live), stream_ptr())
         check(rc, "mlcb_ep_build_groups")
         rows = self.world * self.cap
         recv = self.buf.view(self.off[f"x{par}"], (rows, self.hidden), self.dtype)
-        # expected live rows: every rank routes about 1/world of its pairs here
-        hint = max(1, self.tokens_cap * self.k)
-        h1 = self._grouped(recv, w13, rows, hint)
-        y = self._grouped(ops.act_mul(h1, act), w2, rows, hint)
+        pair_in = self.buf.peer_ptr(self.rank, self.off[f"pair{par}"])
+        # expert-major compaction: each local expert's rows from all senders become one contiguous group, so its
+        # weights are read once per exchange
+        rc = lib().mlcb_ep_compact(ptr(recv), ptr(self.xc), ctypes.c_void_p(pair_in), ptr(self.pair_c),
+                                   ptr(self.seg_src), ptr(self.seg_dst), ptr(self.seg_cnt), ptr(self.live),
+                                   ctypes.c_int(self.world * self.e_local), ctypes.c_int(rows),
+                                   ctypes.c_int(self.hidden), ctypes.c_int(dt), stream_ptr())
+        check(rc, "mlcb_ep_compact")
+        # buffers are sized for the worst case; the work is bounded by what can arrive in this exchange
+        bound = min(rows, _up(total * self.k, 32))
+        hint = max(1, min(bound, -(-total * self.k // self.world)))
+        h1 = self._grouped(self.xc, w13, bound, hint)
+        y = self._grouped(ops.act_mul(h1, act, live_rows=self.live), w2, bound, hint)
         a.done_counter = self.done[2:].data_ptr()
-        rc = lib().mlcb_ep_combine_send(ptr(y), ptr(self.rows_of_src), ctypes.byref(a), ctypes.c_int(dt),
+        rc = lib().mlcb_ep_combine_send(ptr(y), ptr(self.live), ptr(self.pair_c), ctypes.byref(a), ctypes.c_int(dt),
                                         stream_ptr())
         check(rc, "mlcb_ep_combine_send")
         flags = self.buf.peer_ptr(self.rank, self.off["cflag"])
@@ -170,7 +189,7 @@ class ExpertParallel:
                                       ptr(self.epoch_dev), ptr(status_word(self.device)), stream_ptr())
         check(rc, "mlcb_ep_wait_flags")
         self.base += 1
-        self.launches += 6
+        self.launches += 7
         all_pairs = total * self.k
         comb = self.buf.view(self.off[f"comb{par}"], (self.world * self.tokens_cap * self.k, self.hidden),
                              self.dtype)[:all_pairs]
@@ -191,7 +210,7 @@ class ExpertParallel:
         y = torch.empty(rows, n, dtype=x.dtype, device=x.device)
         rc = lib().mlcb_gemm_grouped_table(
             ptr(x), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(self.group_begin),
-            ptr(self.group_count), ptr(self.group_slab), ctypes.c_int(self.world * self.e_local),
+            ptr(self.group_count), ptr(self.group_slab), ctypes.c_int(self.e_local),
             ctypes.c_int(self.e_local), ctypes.c_int(rows), ctypes.c_int(hint), ctypes.c_int(n), ctypes.c_int(k),
             ctypes.c_int(x.stride(0)), ctypes.c_int(n), ctypes.c_int(DTYPE_CODE[x.dtype]),
             ctypes.c_int(DTYPE_CODE[x.dtype]), ptr(status_word(x.device)), stream_ptr())
