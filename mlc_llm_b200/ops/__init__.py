@@ -117,6 +117,25 @@ def dense_weight(w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Linear
     return LinearWeight("dense", w, None, bias, None, w.shape[0], w.shape[1])
 
 
+_WARNED_DENSE = set()
+
+
+def _warn_dense_fallback(lw: "LinearWeight", k: int) -> None:
+    """Quantisation layouts without a kernel of their own (3-bit groups, K-major ``*_0`` packing, fp32 scales,
+    K not a multiple of 64, ...) run on a dequantised 16-bit copy of the weight: correct, but the memory saving
+    is gone. Said once per layout, not silently."""
+    name = getattr(lw.quant, "name", None) or lw.kind
+    key = (name, k % 64 == 0)
+    if key in _WARNED_DENSE:
+        return
+    _WARNED_DENSE.add(key)
+    import logging  # pylint: disable=import-outside-toplevel
+
+    logging.getLogger("mlc_llm_b200").warning(
+        "quantization %s (K = %d) has no packed-weight kernel: its linear layers run on a dequantised 16-bit copy "
+        "of the weights (full 16-bit memory footprint)", name, k)
+
+
 _GEMM_SCRATCH = {}
 GEMM_WORKSPACE_BYTES = 32 << 20
 GEMM_COUNTERS = 4096
@@ -198,6 +217,8 @@ def linear(x: torch.Tensor, lw: LinearWeight, out_dtype: Optional[torch.dtype] =
 
         return linear_fp8_block(x2, lw, od).reshape(*lead, n)
     else:
+        if lw.kind != "dense" and lw._dense is None:
+            _warn_dense_fallback(lw, k)
         w = lw.dense(x2.dtype)
         rc = lib().mlcb_gemm(ptr(x2), ptr(w), ptr(None), ptr(lw.bias), ptr(y), c_int(m), c_int(n),
                              c_int(k), c_int(x2.stride(0)), c_int(n), c_int(ab),
