@@ -75,6 +75,21 @@ MODEL_PRESETS = {
         "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 32000,
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
     },
+    # LayerNorm families (GPU numerics of the LayerNorm / plain-activation kernels at model level)
+    "tiny-gpt2-gpu": {
+        "model_type": "gpt2", "n_embd": 256, "n_head": 2, "n_layer": 2, "n_positions": 1024, "n_inner": 1024,
+        "vocab_size": 32000, "layer_norm_epsilon": 1e-5,
+    },
+    "tiny-neox-gpu": {
+        "model_type": "gpt_neox", "hidden_size": 256, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 2, "vocab_size": 32000, "layer_norm_eps": 1e-5, "rotary_pct": 0.25,
+        "rotary_emb_base": 10000, "max_position_embeddings": 2048, "use_parallel_residual": True,
+    },
+    "tiny-starcoder2-gpu": {
+        "model_type": "starcoder2", "hidden_size": 256, "intermediate_size": 1024, "num_hidden_layers": 2,
+        "num_attention_heads": 2, "num_key_value_heads": 1, "vocab_size": 32000, "norm_epsilon": 1e-5,
+        "rope_theta": 10000.0, "max_position_embeddings": 2048,
+    },
     # alternating sliding-window / full layers, attention and final logit soft-capping (masked attention paths)
     "tiny-gemma2-gpu": {
         "model_type": "gemma2", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
