@@ -85,9 +85,15 @@ class BertModel:
         tensors = {dst: torch.cat([get(s) for s in srcs], 0) for dst, srcs in hf_names(cfg)}
         return BertModel(cfg, tensors, device, dtype)
 
-    def _ln(self, x, name):
-        return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), self.t[name + ".weight"].float(),
-                                              self.t[name + ".bias"].float(), self.cfg.layer_norm_eps).to(x.dtype)
+    def _ln(self, x, name, delta=None):
+        """LayerNorm of ``x`` (of ``x + delta`` when given): the LayerNorm kernel on the GPU."""
+        w, b = self.t[name + ".weight"], self.t[name + ".bias"]
+        if delta is None:
+            return ops.layernorm(x, w, b, self.cfg.layer_norm_eps)
+        shape = x.shape
+        res = x.reshape(-1, shape[-1]).contiguous()
+        out = ops.layernorm(delta.reshape(-1, shape[-1]).contiguous(), w, b, self.cfg.layer_norm_eps, residual=res)
+        return out.reshape(shape)
 
     @torch.no_grad()
     def forward(self, input_ids: torch.Tensor, attention_mask: torch.Tensor) -> torch.Tensor:
@@ -114,8 +120,8 @@ class BertModel:
                 q, k, v = (qkv[:, :, j].transpose(1, 2) for j in range(3))
                 a = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bias)
                 a = a.transpose(1, 2).reshape(b * s, heads * d).to(x.dtype)
-            x = self._ln(x + ops.linear(a, self.lin[p + "attn_out"]).view(b, s, -1), p + "attn_ln")
+            x = self._ln(x, p + "attn_ln", delta=ops.linear(a, self.lin[p + "attn_out"]).view(b, s, -1))
             h = ops.linear(x.reshape(b * s, -1), self.lin[p + "up"])
-            h = torch.nn.functional.gelu(h.float()).to(x.dtype)
-            x = self._ln(x + ops.linear(h, self.lin[p + "down"]).view(b, s, -1), p + "out_ln")
+            h = ops.activation(h, "gelu" if c.hidden_act == "gelu" else "gelu_tanh")
+            x = self._ln(x, p + "out_ln", delta=ops.linear(h, self.lin[p + "down"]).view(b, s, -1))
         return x

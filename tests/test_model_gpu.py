@@ -234,3 +234,36 @@ def test_smoke_entry():
     import __graft_entry__ as g
 
     g.smoke()
+
+
+def test_bert_encoder_on_the_gpu_matches_the_cpu():
+    """BERT on the GPU (encoder-attention, LayerNorm and GELU kernels, fp16) against the fp32 CPU model with the
+    same weights, on a right-padded batch."""
+    from mlc_llm_b200.models.bert import BertConfig, BertModel, hf_names
+
+    torch.manual_seed(21)
+    cfg = BertConfig(vocab_size=1000, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                     intermediate_size=512, max_position_embeddings=128)
+    shapes = {"embed.word": (1000, 256), "embed.position": (128, 256), "embed.token_type": (2, 256)}
+    tensors = {}
+    for name, _ in hf_names(cfg):
+        if name in shapes:
+            tensors[name] = torch.randn(*shapes[name]) * 0.05
+        elif name.endswith("ln.weight"):
+            tensors[name] = torch.rand(256) + 0.5
+        elif name.endswith("ln.bias"):
+            tensors[name] = torch.randn(256) * 0.05
+        elif name.endswith(".weight"):
+            out_in = {"qkv": (768, 256), "attn_out": (256, 256), "up": (512, 256), "down": (256, 512)}
+            tensors[name] = torch.randn(*out_in[name.split(".")[-2]]) * 0.05
+        else:
+            width = {"qkv": 768, "attn_out": 256, "up": 512, "down": 256}[name.split(".")[-2]]
+            tensors[name] = torch.randn(width) * 0.02
+    ids = torch.randint(0, 1000, (3, 70))
+    mask = torch.ones(3, 70, dtype=torch.long)
+    mask[1, 40:] = 0
+    mask[2, 9:] = 0
+    want = BertModel(cfg, tensors, torch.device("cpu")).forward(ids, mask)
+    got = BertModel(cfg, tensors, torch.device("cuda")).forward(ids.cuda(), mask.cuda()).float().cpu()
+    valid = mask.bool()
+    assert (got[valid] - want[valid]).abs().max() < 3e-2, (got[valid] - want[valid]).abs().max()
