@@ -118,7 +118,7 @@ __global__ void layernorm_kernel(const T* __restrict__ x, T* __restrict__ residu
 }
 
 // ------------------------------------------------------------------ plain activations
-// out = act(in), elementwise. act: 0 = SiLU, 1 = GELU(tanh), 2 = GELU(erf), 3 = relu(x)^2.
+// out = act(in), elementwise. act: 0 = SiLU, 1 = GELU(tanh), 2 = GELU(erf), 3 = relu(x)^2, 4 = x * sigmoid(1.702 x).
 template <typename T>
 __global__ void act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total_vec, int act) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -136,9 +136,11 @@ __global__ void act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t
         r = 0.5f * a * (1.f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
       } else if (act == 2) {
         r = 0.5f * a * (1.f + erff(a * 0.7071067811865476f));
-      } else {
+      } else if (act == 3) {
         const float p = fmaxf(a, 0.f);
         r = p * p;
+      } else {
+        r = a / (1.f + __expf(-1.702f * a));
       }
       o[j] = Cvt<T>::from_f(r);
     }

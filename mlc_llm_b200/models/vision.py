@@ -159,6 +159,8 @@ class VisionTower:
         self.size = int(vision["image_size"])
         self.eps = float(vision.get("layer_norm_eps", 1e-5))
         self.act = _ACT[vision.get("hidden_act", "quick_gelu")]
+        self.act_name = {"quick_gelu": "quick_gelu", "gelu": "gelu",
+                         "gelu_pytorch_tanh": "gelu_tanh"}[vision.get("hidden_act", "quick_gelu")]
         self.proj_act = _ACT[projector_act]
         self.feature_layer = feature_layer
         self.select = select
@@ -223,8 +225,7 @@ class VisionTower:
 
     # ------------------------------------------------------------------ forward
     def _ln(self, x: torch.Tensor, name: str) -> torch.Tensor:
-        return F.layer_norm(x.float(), (x.shape[-1],), self.t[name + ".weight"].float(),
-                            self.t[name + ".bias"].float(), self.eps).to(x.dtype)
+        return ops.layernorm(x, self.t[name + ".weight"], self.t[name + ".bias"], self.eps)
 
     def features(self, pixels: torch.Tensor) -> torch.Tensor:
         """``[N, 3, S, S]`` -> hidden states of the selected block, ``[N, 1 + patches, hidden]``."""
@@ -250,7 +251,7 @@ class VisionTower:
             ctx = ops.encoder_attention(q, k, val, scale=1.0 / math.sqrt(d)).to(self.dtype).reshape(-1, self.hidden)
             x = x + ops.linear(ctx, self.lin[b + "self_attn.out_proj"]).view(n, -1, self.hidden)
             h = self._ln(x, b + "layer_norm2").reshape(-1, self.hidden)
-            h = self.act(ops.linear(h, self.lin[b + "mlp.fc1"]).float()).to(self.dtype)
+            h = ops.activation(ops.linear(h, self.lin[b + "mlp.fc1"]), self.act_name)
             x = x + ops.linear(h, self.lin[b + "mlp.fc2"]).view(n, -1, self.hidden)
         return x
 

@@ -282,11 +282,12 @@ def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: 
     return out.reshape(x.shape)
 
 
-_ACT_CODE = {"silu": 0, "gelu_tanh": 1, "gelu": 2, "relu2": 3}
+_ACT_CODE = {"silu": 0, "gelu_tanh": 1, "gelu": 2, "relu2": 3, "quick_gelu": 4}
 
 
 def activation(x: torch.Tensor, act: str) -> torch.Tensor:
-    """Elementwise ``silu`` / ``gelu`` (erf) / ``gelu_tanh`` / ``relu2`` (squared ReLU)."""
+    """Elementwise ``silu`` / ``gelu`` (erf) / ``gelu_tanh`` / ``relu2`` (squared ReLU) / ``quick_gelu``
+    (``x * sigmoid(1.702 x)``, CLIP)."""
     if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0 and x.is_contiguous()):
         xf = x.float()
         if act == "silu":
@@ -297,6 +298,8 @@ def activation(x: torch.Tensor, act: str) -> torch.Tensor:
             y = torch.nn.functional.gelu(xf, approximate="tanh")
         elif act == "relu2":
             y = torch.relu(xf) ** 2
+        elif act == "quick_gelu":
+            y = xf * torch.sigmoid(1.702 * xf)
         else:
             raise ValueError(act)
         return y.to(x.dtype)

@@ -803,7 +803,7 @@ def test_layernorm_and_plain_activations(dtype, hidden):
     summed = (x.float() + res.float()).to(dtype)
     _close(r_dev, summed, tol, tol)
     _close(got, ref.layernorm(summed, w, b, 1e-5), tol, tol)
-    for act in ("silu", "gelu", "gelu_tanh", "relu2"):
+    for act in ("silu", "gelu", "gelu_tanh", "relu2", "quick_gelu"):
         _close(ops.activation(x.to(DEV), act), ops.activation(x, act), tol, tol)
 
 
