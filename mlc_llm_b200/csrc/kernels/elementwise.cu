@@ -371,6 +371,55 @@ __global__ void kv_slot_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __
   for (int v = lane; v < row_bytes / 16; v += 32) dp[v] = sp[v];
 }
 
+// One decode token of the gated delta rule (Qwen3.5 linear-attention layers; reference:
+// python/mlc_llm/model/qwen35/qwen35_model.py:219-365), in place on the slot-indexed state pool:
+//   S <- exp(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  out = S^T q
+// state: [slots, H, DK, DV] fp32; q, k: [B, H, DK]; v, out: [B, H, DV]; g, beta: [B, H]. One CTA per (head,
+// sequence), thread j owns column j of the head's state and keeps it in registers between the two passes, so
+// the state is read once and written once.
+template <int DK>
+__global__ void gdn_step_kernel(float* __restrict__ state, const int* __restrict__ slots, const float* __restrict__ q,
+                                const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ g,
+                                const float* __restrict__ beta, float* __restrict__ out, int H, int DV) {
+  // 2 * DV threads: thread (half, j) keeps rows [half * DK / 2, (half + 1) * DK / 2) of column j in registers
+  constexpr int HK = DK / 2;
+  extern __shared__ float gdn_sm[];  // ks[DK], qs[DK], red[2][DV]
+  float* ks = gdn_sm;
+  float* qs = gdn_sm + DK;
+  float* red = gdn_sm + 2 * DK;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int half = threadIdx.x / DV, j = threadIdx.x - half * DV;
+  const size_t bh = static_cast<size_t>(b) * H + h;
+  for (int i = threadIdx.x; i < DK; i += blockDim.x) {
+    ks[i] = k[bh * DK + i];
+    qs[i] = q[bh * DK + i];
+  }
+  __syncthreads();
+  float* S = state + ((static_cast<size_t>(slots[b]) * H + h) * DK + half * HK) * DV + j;
+  const float eg = __expf(g[bh]);
+  float s[HK];
+  float part = 0.f;
+#pragma unroll
+  for (int i = 0; i < HK; ++i) {
+    s[i] = S[static_cast<size_t>(i) * DV] * eg;
+    part += s[i] * ks[half * HK + i];
+  }
+  red[half * DV + j] = part;
+  __syncthreads();
+  const float u = (v[bh * DV + j] - (red[j] + red[DV + j])) * beta[bh];
+  __syncthreads();
+  part = 0.f;
+#pragma unroll
+  for (int i = 0; i < HK; ++i) {
+    s[i] += ks[half * HK + i] * u;
+    S[static_cast<size_t>(i) * DV] = s[i];
+    part += s[i] * qs[half * HK + i];
+  }
+  red[half * DV + j] = part;
+  __syncthreads();
+  if (half == 0) out[bh * DV + j] = red[j] + red[DV + j];
+}
+
 // RWKV-5 recurrence (reference: python/mlc_llm/model/rwkv5/rwkv5_model.py:64-123). One CTA per
 // (head, sequence); thread i owns row i of the head's matrix state (value dimension i, all key dimensions)
 // in registers and walks the sequence's tokens in order:
@@ -517,6 +566,24 @@ MLCB_API int mlcb_rmsnorm(const void* x, void* residual, const void* w, void* ou
     LAUNCH(__nv_bfloat16)
   }
 #undef LAUNCH
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+MLCB_API int mlcb_gdn_step(float* state, const int* slots, const float* q, const float* k, const float* v,
+                           const float* g, const float* beta, float* out, int B, int H, int DK, int DV,
+                           cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (DV > 512 || DV < 32 || DV % 32) return -1;
+  dim3 grid(H, B);
+  const int threads = 2 * DV;
+  const size_t smem = (2 * static_cast<size_t>(DK) + 2 * DV) * sizeof(float);
+  if (DK == 128)
+    gdn_step_kernel<128><<<grid, threads, smem, stream>>>(state, slots, q, k, v, g, beta, out, H, DV);
+  else if (DK == 64)
+    gdn_step_kernel<64><<<grid, threads, smem, stream>>>(state, slots, q, k, v, g, beta, out, H, DV);
+  else
+    return -1;
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -48,6 +48,31 @@ def gated_delta_step(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: t
     return torch.einsum("bhkv,bhk->bhv", state, q)
 
 
+def _gdn_step_kernel(rec_all: torch.Tensor, slots, q, k, v, g, beta, out: torch.Tensor, rows) -> bool:
+    """The decode step as one kernel, in place on the state pool ``rec_all [slots, H, dk, dv]`` (no gather /
+    scatter of the states). Returns False when the kernel does not apply (CPU, other head sizes)."""
+    if not rec_all.is_cuda or rec_all.dtype != torch.float32 or not rec_all.is_contiguous() \
+            or q.shape[-1] not in (64, 128) or v.shape[-1] > 512 or v.shape[-1] % 32:
+        return False
+    import ctypes  # pylint: disable=import-outside-toplevel
+
+    from ..ops._lib import check, lib, ptr, stream_ptr  # pylint: disable=import-outside-toplevel
+
+    b, h, dk = q.shape
+    dv = v.shape[-1]
+    slots_t = torch.as_tensor(slots, device=rec_all.device).to(torch.int32).contiguous()
+    res = torch.empty(b, h, dv, dtype=torch.float32, device=rec_all.device)
+    rc = lib().mlcb_gdn_step(ptr(rec_all), ptr(slots_t), ptr(q.float().contiguous()), ptr(k.float().contiguous()),
+                             ptr(v.float().contiguous()), ptr(g.float().contiguous()), ptr(beta.float().contiguous()),
+                             ptr(res), ctypes.c_int(b), ctypes.c_int(h), ctypes.c_int(dk), ctypes.c_int(dv),
+                             stream_ptr())
+    if rc < 0:
+        return False
+    check(rc, "mlcb_gdn_step")
+    out[rows] = res
+    return True
+
+
 def gated_delta_chunk(state: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                       g: torch.Tensor, beta: torch.Tensor, chunk: int = 64) -> torch.Tensor:
     """The same recurrence for ``n`` consecutive tokens of one sequence, ``chunk`` tokens per step, as
@@ -221,9 +246,10 @@ class Qwen35Model(DecoderModel):
             window = torch.cat([conv_all[slots], mixed[rows].unsqueeze(-1)], dim=-1)   # [B, conv_dim, K]
             conv_all[slots] = window[:, :, 1:]
             q, k, v = heads((window * w.unsqueeze(0)).sum(-1))
-            state = rec_all[slots]
-            out[rows] = gated_delta_step(state, q, k, v, g[rows], beta[rows])
-            rec_all[slots] = state
+            if not _gdn_step_kernel(rec_all, slots, q, k, v, g[rows], beta[rows], out, rows):
+                state = rec_all[slots]
+                out[rows] = gated_delta_step(state, q, k, v, g[rows], beta[rows])
+                rec_all[slots] = state
         else:
             for j, (start, n) in enumerate(zip(ctx["starts"], ctx["lens"])):
                 slot = slots[j]

@@ -855,3 +855,29 @@ def test_encoder_attention(dtype, d, case):
     assert got.shape == (b, s, h, d) and got.is_contiguous()
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
     _close(got, want, tol, tol)
+
+
+@pytest.mark.parametrize("dk,dv", [(128, 128), (64, 128), (128, 256)])
+def test_gated_delta_step_kernel(dk, dv):
+    """One decode token of the gated delta rule, in place on a slot-indexed state pool, against the tensor form."""
+    from mlc_llm_b200.models.qwen35 import _gdn_step_kernel, gated_delta_step
+
+    torch.manual_seed(15)
+    slots_cap, b, h = 9, 5, 4
+    pool = torch.randn(slots_cap, h, dk, dv) * 0.3
+    slots = [7, 0, 3, 8, 2]
+    q = torch.nn.functional.normalize(torch.randn(b, h, dk), dim=-1) * dk ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(b, h, dk), dim=-1)
+    v = torch.randn(b, h, dv)
+    g = -torch.rand(b, h)
+    beta = torch.rand(b, h)
+    state = pool[slots].clone()
+    want = gated_delta_step(state, q, k, v, g, beta)
+    want_pool = pool.clone()
+    want_pool[slots] = state
+    pool_d = pool.to(DEV)
+    out = torch.zeros(b, h, dv, device=DEV)
+    rows = torch.arange(b, device=DEV)
+    assert _gdn_step_kernel(pool_d, slots, q.to(DEV), k.to(DEV), v.to(DEV), g.to(DEV), beta.to(DEV), out, rows)
+    _close(out, want, 1e-4, 1e-5)
+    _close(pool_d, want_pool, 1e-4, 1e-5)
