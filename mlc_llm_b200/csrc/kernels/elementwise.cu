@@ -574,7 +574,8 @@ MLCB_API int mlcb_gdn_step(float* state, const int* slots, const float* q, const
                            const float* g, const float* beta, float* out, int B, int H, int DK, int DV,
                            cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (DV > 512 || DV < 32 || DV % 32) return -1;
+  // the register file bounds the CTA: 2 * DV threads each holding DK / 2 state values
+  if (DV < 32 || DV % 32 || DV * DK > 128 * 128) return -1;
   dim3 grid(H, B);
   const int threads = 2 * DV;
   const size_t smem = (2 * static_cast<size_t>(DK) + 2 * DV) * sizeof(float);

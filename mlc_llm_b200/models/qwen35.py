@@ -52,7 +52,7 @@ def _gdn_step_kernel(rec_all: torch.Tensor, slots, q, k, v, g, beta, out: torch.
     """The decode step as one kernel, in place on the state pool ``rec_all [slots, H, dk, dv]`` (no gather /
     scatter of the states). Returns False when the kernel does not apply (CPU, other head sizes)."""
     if not rec_all.is_cuda or rec_all.dtype != torch.float32 or not rec_all.is_contiguous() \
-            or q.shape[-1] not in (64, 128) or v.shape[-1] > 512 or v.shape[-1] % 32:
+            or q.shape[-1] not in (64, 128) or v.shape[-1] % 32 or q.shape[-1] * v.shape[-1] > 128 * 128:
         return False
     import ctypes  # pylint: disable=import-outside-toplevel
 
