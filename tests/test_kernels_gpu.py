@@ -881,3 +881,33 @@ def test_gated_delta_step_kernel(dk, dv):
     assert _gdn_step_kernel(pool_d, slots, q.to(DEV), k.to(DEV), v.to(DEV), g.to(DEV), beta.to(DEV), out, rows)
     _close(out, want, 1e-4, 1e-5)
     _close(pool_d, want_pool, 1e-4, 1e-5)
+
+
+def test_sampling_cutoffs_top_k_and_top_p():
+    """The multi-way cutoff search: top-k alone, top-p alone and both, on peaked and on flat rows; the sampled token
+    always lies in the set the CPU reference keeps, and its reported probability is the renormalised one."""
+    torch.manual_seed(16)
+    n, v = 12, 128256
+    logits = torch.randn(n, v) * torch.tensor([0.5, 1, 2, 3, 4, 6] * 2).view(n, 1)
+    temp = torch.ones(n)
+    p = ops.softmax_temperature(logits.to(DEV), temp.to(DEV))
+    p_cpu = p.cpu()
+    sorted_p, order = p_cpu.sort(dim=1, descending=True)
+    for top_p, top_k in ((1.0, 5), (1.0, 1), (0.9, 0), (0.5, 40), (0.999, 3), (0.2, 1000)):
+        for u0 in (0.0, 0.37, 0.93, 0.9999):
+            u = torch.full((n,), u0)
+            tp = torch.full((n,), top_p)
+            tk = torch.full((n,), top_k, dtype=torch.int32) if top_k else None
+            tok, pr = ops.sample(p, None, u.to(DEV), tp.to(DEV), None if tk is None else tk.to(DEV))
+            tok, pr = tok.cpu().long(), pr.cpu()
+            for r in range(n):
+                # the kept set: smallest prefix of the sorted row reaching top_p, capped at top_k
+                csum = sorted_p[r].cumsum(0)
+                need = top_p * csum[-1]
+                m = v if top_p >= 1.0 else int((csum < need - 1e-6).sum().item()) + 1
+                if top_k:
+                    m = min(m, top_k)
+                floor = sorted_p[r][m - 1].item()
+                assert p_cpu[r, tok[r]].item() >= floor * (1 - 1e-5), (top_p, top_k, u0, r)
+                kept = sorted_p[r][:m].sum().item()
+                assert abs(pr[r].item() - p_cpu[r, tok[r]].item() / kept) < 2e-3 * max(1.0, pr[r].item())
