@@ -145,6 +145,7 @@ __device__ __forceinline__ DecUnit dec_unit(const DecParams& p, int u) {
 template <bool BF16, bool EXT>
 __global__ void __launch_bounds__(DEC_THREADS, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecParams p) {
+  pdl_launch_dependents();  // the output projection that follows may set itself up meanwhile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));

@@ -372,6 +372,16 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Block-wide reductions through a 32-float scratch array in shared memory.
+// Programmatic dependent launch. A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs; pdl_wait() is where it blocks until the predecessor has finished
+// and its memory is visible, so everything before it must neither read what a predecessor writes nor write
+// global memory. pdl_launch_dependents() is the predecessor's side: once every CTA has executed it (or exited),
+// the dependent grid may be scheduled. Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   v = warp_sum(v);

@@ -15,6 +15,7 @@ template <typename T, bool ADD>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
                                const T* __restrict__ w, T* __restrict__ out, int hidden, float eps,
                                float w_offset) {
+  pdl_launch_dependents();  // a GEMM that follows may set itself up while these rows are normalised
   extern __shared__ float row[];  // hidden floats + 32 scratch
   float* scratch = row + hidden;
   const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
@@ -153,6 +154,7 @@ __global__ void act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t
 template <typename T>
 __global__ void act_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                size_t total_vec, int act, const int* __restrict__ live_rows) {
+  pdl_launch_dependents();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   const int vec_per_row = inter / 8;
   // a device-side row count (expert-parallel buffers: only the rows that arrived are worked on)

@@ -542,6 +542,7 @@ template <int WF, bool TWO>
 __global__ void __launch_bounds__(WF ? GEMM_THREADS_Q4 : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
             const GemmParams p) {
+  pdl_launch_dependents();      // the next kernel may be scheduled as SMs become free (it waits for this one)
   constexpr bool Q4 = WF != 0;  // "has a dequant stage"
   constexpr int W_MMA = 1;
   constexpr int W_XPROD = Q4 ? 5 : 0;
@@ -608,6 +609,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     if (p.group_offsets) {
+      pdl_wait();  // the group table is written by kernels before this one
       int mbs = 0;
       for (int e = 0; e < p.num_groups; ++e) {
         const int cnt = p.group_count ? p.group_count[e] : p.group_offsets[e + 1] - p.group_offsets[e];
@@ -633,6 +635,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_tiles = sh_num_items;  // work items
+  // Launched as a programmatic dependent, this kernel has come this far (barriers, TMEM) while its predecessor
+  // was still running. Everything that reads activations, flags or tables, or writes global memory, waits here
+  // for it; the packed-weight producer does not (weights are constants): it fills its ring in the meantime.
+  if (!(Q4 && warp == W_RAWPROD && !p.group_offsets)) pdl_wait();
 
   if (warp == W_XPROD) {
     // ------------------------------------------------------------ TMA producer: activations
@@ -718,6 +724,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ 
         }
         __syncwarp();
       }
+      pdl_wait();  // (returns at once by now) this warp also takes part in the reductions and tails below
     }
   } else if (warp == W_MMA) {
     // ------------------------------------------------------------ MMA issuer
@@ -1499,6 +1506,17 @@ MLCB_API void mlcb_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 // Split-K reduction inside thread-block clusters (MLCB_GEMM_CLUSTER_SPLIT=0 falls back to the
 // reduction through global scratch, which the CTA-pair kernels and the allocation-free entry point use).
 static int g_cluster_split = -1;
+// MLCB_PDL=0 launches the GEMMs the ordinary way (each waits for the full completion of its predecessor before
+// any of its CTAs starts).
+static bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("MLCB_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 static bool cluster_split_enabled() {
   if (g_cluster_split < 0) {
     const char* e = getenv("MLCB_GEMM_CLUSTER_SPLIT");
@@ -1680,13 +1698,15 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
     cfg.dynamicSmemBytes = GEMM_SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t err;
     if (q4) err = cudaLaunchKernelEx(&cfg, gemm_kernel<1, true>, *mx, *mw, p);
     else if (wf == 2) err = cudaLaunchKernelEx(&cfg, gemm_kernel<2, true>, *mx, *mw, p);
@@ -1717,13 +1737,15 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
     cfg.dynamicSmemBytes = GEMM_SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t err;
     if (q4) err = cudaLaunchKernelEx(&cfg, gemm_kernel<1, false>, *mx, *mw, p);
     else if (wf == 2) err = cudaLaunchKernelEx(&cfg, gemm_kernel<2, false>, *mx, *mw, p);
@@ -1732,14 +1754,24 @@ static int gemm_launch(const void* x, const void* w, const void* scale, const vo
     return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
   }
   p.cluster_split = 0;
-  if (q4)
-    gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
-  else if (wf == 2)
-    gemm_kernel<2, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
-  else
-    gemm_kernel<0, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
-  count_launch();
-  return static_cast<int>(cudaGetLastError());
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(wf ? GEMM_THREADS_Q4 : GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t err;
+    if (q4) err = cudaLaunchKernelEx(&cfg, gemm_kernel<1, false>, *mx, *mw, p);
+    else if (wf == 2) err = cudaLaunchKernelEx(&cfg, gemm_kernel<2, false>, *mx, *mw, p);
+    else err = cudaLaunchKernelEx(&cfg, gemm_kernel<0, false>, *mx, *mw, p);
+    count_launch();
+    return static_cast<int>(err != cudaSuccess ? err : cudaGetLastError());
+  }
 }
 
 MLCB_API int mlcb_gemm(const void* x, const void* w, const void* scale, const void* bias, void* y,
