@@ -1851,9 +1851,12 @@ MLCB_API long long mlcb_launch_count() { return mlcb::g_launch_count; }
 static int gemm_grouped_launch(const void* x, const void* w, const void* scale, void* y, const int* offsets,
                                const int* group_count, const int* group_slab, int num_groups, int num_slabs,
                                int total_rows, int rows_hint, int N, int K, int ldx, int ldy, int ab_fmt,
-                               int out_dtype, int* status, cudaStream_t stream) {
+                               int out_dtype, int* status, cudaStream_t stream, bool fp8 = false) {
   if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
-  const bool q4 = scale != nullptr;
+  // weight format: packed int4 records (scale != null), e4m3 with fp32 128 x 128 block scales (fp8; `scale` holds
+  // them, slab after slab), or dense 16-bit
+  const bool q4 = scale != nullptr && !fp8;
+  if (fp8 && (!scale || K % 128 != 0)) return -2;
   if (K % 8 != 0 || ldx % 8 != 0 || N % BM != 0) return -1;
   if (q4 && K % 64 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
@@ -1898,6 +1901,11 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   const uint64_t wrows = static_cast<uint64_t>(num_slabs) * N;
   if (q4) {
     mw = mx;  // slab e's records start at tile row e * N / 128 (N is a multiple of 128 here)
+  } else if (fp8) {
+    uint64_t wd[2] = {static_cast<uint64_t>(K), wrows};
+    uint64_t ws[1] = {static_cast<uint64_t>(K)};
+    uint32_t wb[2] = {BK, BM};
+    mw = get_tensor_map(w, 1, 2, wd, ws, wb, 0);
   } else {
     uint64_t wd[2] = {static_cast<uint64_t>(K), wrows};
     uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -1910,10 +1918,24 @@ static int gemm_grouped_launch(const void* x, const void* w, const void* scale, 
   const int grid = max_tiles < sm_count() ? static_cast<int>(max_tiles) : sm_count();
   if (q4)
     gemm_kernel<1, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
+  else if (fp8)
+    gemm_kernel<2, false><<<grid, GEMM_THREADS_Q4, GEMM_SMEM, stream>>>(*mx, *mw, p);
   else
     gemm_kernel<0, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(*mx, *mw, p);
   count_launch();
   return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped GEMM over block-scaled e4m3 expert weights [slabs, N, K] with fp32 scales [slabs, N / 128, K / 128]
+// (weights expanded to the activation dtype on the way to the tensor core; reference: the grouped fp8 GEMM of
+// python/mlc_llm/op/cutlass.py:281-375). group_count / group_slab may be null (groups = consecutive slabs).
+MLCB_API int mlcb_gemm_grouped_fp8(const void* x, const void* w, const void* scale, void* y, const int* group_begin,
+                                   const int* group_count, const int* group_slab, int num_groups, int num_slabs,
+                                   int buffer_rows, int rows_hint, int N, int K, int ldx, int ldy, int ab_fmt,
+                                   int out_dtype, int* status, cudaStream_t stream) {
+  return gemm_grouped_launch(x, w, scale, y, group_begin, group_count, group_slab, num_groups, num_slabs,
+                             buffer_rows, rows_hint > 0 ? rows_hint : 1, N, K, ldx, ldy, ab_fmt, out_dtype, status,
+                             stream, true);
 }
 
 MLCB_API int mlcb_gemm_grouped(const void* x, const void* w, const void* scale, void* y, const int* offsets,

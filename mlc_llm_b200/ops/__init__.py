@@ -615,6 +615,16 @@ def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
     if rows == 0:
         return y
     x2 = x if x.stride(-1) == 1 else x.contiguous()
+    if lw.kind in ("fp8_block", "fp8_tensor") and lw.w.dtype == torch.float8_e4m3fn and k % 128 == 0 \
+            and n % 128 == 0 and x.dtype in (torch.float16, torch.bfloat16):
+        # expert weights stay fp8 in memory; the kernel expands them tile by tile
+        scale = _expert_block_scale(lw)
+        rc = lib().mlcb_gemm_grouped_fp8(ptr(x2), ptr(lw.w), ptr(scale), ptr(y), ptr(offsets), ptr(None), ptr(None),
+                                         c_int(e), c_int(e), c_int(rows), c_int(rows), c_int(n), c_int(k),
+                                         c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[x.dtype]),
+                                         c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
+        check(rc, f"mlcb_gemm_grouped_fp8(rows={rows},E={e},N={n},K={k})")
+        return y
     q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
     w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
     rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(offsets),
@@ -623,6 +633,21 @@ def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
                                  stream_ptr())
     check(rc, f"mlcb_gemm_grouped(rows={rows},E={e},N={n},K={k})")
     return y
+
+
+def _expert_block_scale(lw: LinearWeight) -> torch.Tensor:
+    """fp32 block scales ``[E, N / 128, K / 128]`` of stacked fp8 expert weights (a per-tensor scale per expert, or
+    one for all, is repeated over the grid)."""
+    if lw.kind == "fp8_block":
+        if lw.scale.dtype != torch.float32 or not lw.scale.is_contiguous():
+            lw.scale = lw.scale.float().contiguous()
+        return lw.scale
+    if lw._block_scale is None:
+        e, n, k = lw.w.shape
+        per_expert = lw.scale.float().reshape(-1)
+        per_expert = per_expert if per_expert.numel() == e else per_expert[:1].expand(e)
+        lw._block_scale = per_expert.view(e, 1, 1).expand(e, n // 128, k // 128).contiguous()
+    return lw._block_scale
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, sorted_pos: torch.Tensor,

@@ -911,3 +911,29 @@ def test_sampling_cutoffs_top_k_and_top_p():
                 assert p_cpu[r, tok[r]].item() >= floor * (1 - 1e-5), (top_p, top_k, u0, r)
                 kept = sorted_p[r][:m].sum().item()
                 assert abs(pr[r].item() - p_cpu[r, tok[r]].item() / kept) < 2e-3 * max(1.0, pr[r].item())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens", [1, 37, 700])
+def test_grouped_gemm_fp8_block_scale_experts(dtype, tokens):
+    """Stacked e4m3 expert weights with 128 x 128 block scales through the grouped GEMM (no dense copy): against
+    the fp32 product with the dequantised weights."""
+    torch.manual_seed(17)
+    e, n, k = 4, 256, 384
+    w = torch.randn(e, n, k) * 0.05
+    qw, sc = Q.fp8_block_quantize(w, (128, 128), "float8_e4m3fn")
+    quant = Q.get("fp8_e4m3fn_bf16_block_scale")
+    lw = ops.LinearWeight("fp8_block", qw.to(DEV), sc.float().to(DEV), None, quant, n, k)
+    counts = torch.tensor([tokens // 2, 0, tokens - tokens // 2 - tokens // 5, tokens // 5])
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(torch.int32)
+    x = (torch.randn(tokens, k) * 0.5).to(dtype)
+    y = ops.grouped_linear(x.to(DEV), lw, offsets.to(DEV))
+    ops.check_status(torch.device(DEV))
+    assert lw._dense is None
+    wd = Q.fp8_block_dequantize(qw, sc, (128, 128)).float()
+    want = torch.zeros(tokens, n)
+    off = offsets.tolist()
+    for i in range(e):
+        want[off[i]:off[i + 1]] = x[off[i]:off[i + 1]].float() @ wd[i].t()
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    _close(y, want, tol, tol * max(1e-3, want.abs().max().item()))
