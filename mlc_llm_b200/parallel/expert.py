@@ -205,6 +205,17 @@ class ExpertParallel:
 
     def _grouped(self, x: torch.Tensor, lw, rows: int, hint: int) -> torch.Tensor:
         n, k = lw.w.shape[1], x.shape[1]
+        if lw.kind in ("fp8_block", "fp8_tensor") and lw.w.dtype == torch.float8_e4m3fn and k % 128 == 0 \
+                and n % 128 == 0:
+            y = torch.empty(rows, n, dtype=x.dtype, device=x.device)
+            rc = lib().mlcb_gemm_grouped_fp8(
+                ptr(x), ptr(lw.w), ptr(ops._expert_block_scale(lw)), ptr(y), ptr(self.group_begin),  # pylint: disable=protected-access
+                ptr(self.group_count), ptr(self.group_slab), ctypes.c_int(self.e_local), ctypes.c_int(self.e_local),
+                ctypes.c_int(rows), ctypes.c_int(hint), ctypes.c_int(n), ctypes.c_int(k), ctypes.c_int(x.stride(0)),
+                ctypes.c_int(n), ctypes.c_int(DTYPE_CODE[x.dtype]), ctypes.c_int(DTYPE_CODE[x.dtype]),
+                ptr(status_word(x.device)), stream_ptr())
+            check(rc, "mlcb_gemm_grouped_fp8")
+            return y
         q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
         w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
         y = torch.empty(rows, n, dtype=x.dtype, device=x.device)

@@ -431,7 +431,7 @@ def test_fused_all_reduce_gemm_single_rank(quant_name, tokens, k):
     fc.end()
 
 
-@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
+@pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16", "fp8_e4m3fn_bf16_block_scale"])
 @pytest.mark.parametrize("tokens", [1, 37, 300])
 def test_expert_parallel_exchange_single_rank(quant_name, tokens):
     """World size 1 runs dispatch -> group table -> grouped GEMMs -> combine through this GPU's own
@@ -450,6 +450,9 @@ def test_expert_parallel_exchange_single_rank(quant_name, tokens):
     def mk(w):
         if quant.kind == "no-quant":
             return ops.LinearWeight("dense", w, None, None, None, w.shape[1], w.shape[2]).to(DEV)
+        if quant.kind == "fp8-block-scale":
+            fw, fs = Q.fp8_block_quantize(w.float(), (128, 128), "float8_e4m3fn")
+            return ops.LinearWeight("fp8_block", fw.to(DEV), fs.float().to(DEV), None, quant, w.shape[1], w.shape[2])
         qw, qs = Q.group_quantize(w, quant)
         return ops.LinearWeight("q4", qw, qs, None, quant, w.shape[1], w.shape[2]).to(DEV)
 
