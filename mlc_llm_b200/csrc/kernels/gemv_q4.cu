@@ -135,8 +135,17 @@ template <typename TO, int MMAX, int KS, bool PREFETCH>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
     gemv_q4_split_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w,
                          const __half* __restrict__ scale, const __half* __restrict__ bias, TO* __restrict__ y,
-                         int m_count, int N, int K, int ldx, int ldy) {
+                         int m_count, int N, int K, int ldx, int ldy, const int* __restrict__ slab_of_row) {
   __shared__ float partial[GEMV_WARPS][GEMV_ROWS][MMAX];
+  if (slab_of_row) {
+    // grouped form (mixture-of-experts decode): blockIdx.y is a row of x / y, multiplied by the weight slab
+    // (expert) named for it; w / scale hold the slabs one after the other, [slabs, N, K / 8] and [slabs, N, K / 32]
+    const size_t slab = static_cast<size_t>(slab_of_row[blockIdx.y]);
+    w += slab * N * (static_cast<size_t>(K) >> 3);
+    scale += slab * N * (static_cast<size_t>(K) >> 5);
+    x += static_cast<size_t>(blockIdx.y) * ldx;
+    y += static_cast<size_t>(blockIdx.y) * ldy;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int GROUPS_PER_CTA = GEMV_WARPS / KS;     // row groups per CTA
   const int rg = warp / KS, ks = warp % KS;           // row group inside the CTA, K slice of this warp
@@ -290,7 +299,7 @@ MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const
 #define GEMV_SPLIT(TO, MM, KS, PF)                                                                          \
   gemv_q4_split_kernel<TO, MM, KS, PF><<<grid2, GEMV_WARPS * 32, 0, stream>>>(                               \
       static_cast<const __half*>(x), static_cast<const uint32_t*>(w), static_cast<const __half*>(scale),     \
-      static_cast<const __half*>(bias), static_cast<TO*>(y), M, N, K, ldx, ldy)
+      static_cast<const __half*>(bias), static_cast<TO*>(y), M, N, K, ldx, ldy, nullptr)
 #define GEMV_SPLIT_KS(TO, MM, PF)                                     \
   do {                                                                \
     if (ks == 1) GEMV_SPLIT(TO, MM, 1, PF);                           \
@@ -328,6 +337,43 @@ MLCB_API int mlcb_gemv_q4(const void* x, const void* w, const void* scale, const
     else GEMV_LAUNCH(float, 4);
   }
 #undef GEMV_LAUNCH
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped matrix-vector products for mixture-of-experts decode (reference: the single-token expert GEMV of
+// python/mlc_llm/op/moe_matmul.py:12-74): row r of x [rows, K] is multiplied by slab slab_of_row[r] of the stacked
+// weights w [slabs, N, K / 8] / scale [slabs, N, K / 32]; y [rows, N]. One grid row per row of x, so a handful
+// of (token, expert) pairs stream only the experts they use, at the GEMV's memory-bound rate.
+MLCB_API int mlcb_gemv_q4_grouped(const void* x, const void* w, const void* scale, void* y, const int* slab_of_row,
+                                  int rows, int N, int K, int ldx, int ldy, int out_dtype, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (rows > 64 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || !slab_of_row) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -1;
+  if (out_dtype != 0 && out_dtype != 2) return -1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long row_groups = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+  int ks = 1;
+  while (ks < GEMV_WARPS && row_groups * ks * rows < static_cast<long long>(sms) * 32 && (K >> 5) >= 32 * ks * 2) ks *= 2;
+  const int groups_per_cta = GEMV_WARPS / ks;
+  dim3 grid(static_cast<unsigned>((row_groups + groups_per_cta - 1) / groups_per_cta), static_cast<unsigned>(rows));
+#define GEMV_GROUPED(TO, KS)                                                                                 \
+  gemv_q4_split_kernel<TO, 1, KS, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(                               \
+      static_cast<const __half*>(x), static_cast<const uint32_t*>(w), static_cast<const __half*>(scale), nullptr, \
+      static_cast<TO*>(y), 1, N, K, ldx, ldy, slab_of_row)
+#define GEMV_GROUPED_KS(TO)               \
+  do {                                    \
+    if (ks == 1) GEMV_GROUPED(TO, 1);     \
+    else if (ks == 2) GEMV_GROUPED(TO, 2); \
+    else if (ks == 4) GEMV_GROUPED(TO, 4); \
+    else GEMV_GROUPED(TO, 8);             \
+  } while (0)
+  if (out_dtype == 0) GEMV_GROUPED_KS(__half);
+  else GEMV_GROUPED_KS(float);
+#undef GEMV_GROUPED_KS
+#undef GEMV_GROUPED
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -117,6 +117,8 @@ def dense_weight(w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Linear
     return LinearWeight("dense", w, None, bias, None, w.shape[0], w.shape[1])
 
 
+# grouped (mixture-of-experts) products with at most this many rows take the GEMV form
+_MOE_GEMV_MAX_ROWS = int(os.environ.get("MLCB_MOE_GEMV_MAX_ROWS", "8"))
 _WARNED_DENSE = set()
 
 
@@ -625,6 +627,20 @@ def grouped_linear(x: torch.Tensor, lw: LinearWeight, offsets: torch.Tensor,
                                          c_int(DTYPE_CODE[od]), ptr(status_word(x.device)), stream_ptr())
         check(rc, f"mlcb_gemm_grouped_fp8(rows={rows},E={e},N={n},K={k})")
         return y
+    if rows <= _MOE_GEMV_MAX_ROWS and lw.kind == "q4" and lw.device_layout and x.dtype == torch.float16 \
+            and lw.scale is not None and lw.scale.dtype == torch.float16 and k % 32 == 0 \
+            and lw.quant is not None and lw.quant.bits == 4 and lw.quant.group_size == 32 \
+            and od in (torch.float16, torch.float32):
+        # a handful of (token, expert) pairs (single-stream decode): memory-bound GEMV over the experts in use;
+        # the expert of every row follows from the offsets without leaving the device
+        slab = torch.searchsorted(offsets[1:].contiguous(), torch.arange(rows, device=x.device, dtype=offsets.dtype),
+                                  right=True).to(torch.int32)
+        rc = lib().mlcb_gemv_q4_grouped(ptr(x2), ptr(lw.w), ptr(lw.scale), ptr(y), ptr(slab), c_int(rows), c_int(n),
+                                        c_int(k), c_int(x2.stride(0)), c_int(n), c_int(DTYPE_CODE[od]), stream_ptr())
+        if rc == 0:
+            return y
+        if rc > 0:
+            check(rc, "mlcb_gemv_q4_grouped")
     q4 = lw.q4_tileable(k) and x.dtype == lw.scale.dtype
     w = lw.q4_tiles() if q4 else (lw.w if lw.kind == "dense" else lw.dense(x.dtype))
     rc = lib().mlcb_gemm_grouped(ptr(x2), ptr(w), ptr(w) if q4 else ptr(None), ptr(y), ptr(offsets),

@@ -314,7 +314,7 @@ def test_attention_tcgen05(dtype, hq, hkv, mode, splits):
 
 
 @pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1"])
-@pytest.mark.parametrize("tokens", [1, 37, 700])
+@pytest.mark.parametrize("tokens", [1, 4, 37, 700])
 def test_moe_block_kernels(quant_name, tokens):
     torch.manual_seed(21)
     e, k, hidden, inter = 8, 2, 256, 512
