@@ -30,12 +30,13 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--output-len", type=int, default=48)
     ap.add_argument("--out", default="")
+    ap.add_argument("--model-args", default="", help='appended to the model string, e.g. "&expert_parallel=true"')
     args = ap.parse_args(argv)
     rank, world, local = parallel.env_world()
     comm = parallel.Communicator(tp_size=world, pp_size=1) if world > 1 else None
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    model = f"random://{args.model}?quant={args.quant}&seed=0"
+    model = f"random://{args.model}?quant={args.quant}&seed=0{args.model_args}"
     r, p, o = args.requests, args.prompt_len, args.output_len
     cfg = EngineConfig(mode="server", max_num_sequence=r, prefill_chunk_size=8192,
                        max_total_sequence_length=r * (p + o) + 16 * r + 8192, prefix_cache_mode="disable",
