@@ -161,6 +161,68 @@ moe_permute_kernel(const int* __restrict__ experts, int n, int k, int E, int* __
   }
 }
 
+// The same permutation with the pairs split over the 32 warps of the CTA (the form above walks every pair
+// once per expert with one warp, which costs a chain of dependent loads when there are few experts).
+// Pass 1 counts per (expert, warp) with match_any, a scan over (expert, warp) gives each warp its first
+// row inside every expert, pass 2 places the pairs: pairs of one expert stay in index order.
+__global__ void __launch_bounds__(1024)
+moe_permute_split_kernel(const int* __restrict__ experts, int n, int k, int E, int* __restrict__ offsets,
+                         int* __restrict__ sorted_pos, int* __restrict__ src_token) {
+  extern __shared__ int sh[];  // cnt[E][32], total[E]
+  int* cnt = sh;
+  int* total = sh + E * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < E * 32; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const int per_warp = ((n + 31) / 32 + 31) / 32 * 32;  // pairs of one warp, a multiple of 32
+  const int begin = warp * per_warp, end = min(n, begin + per_warp);
+  const unsigned lt = (1u << lane) - 1;
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int e = i < end ? experts[i] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (m & lt) == 0) cnt[e * 32 + warp] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = cnt[e * 32 + w];
+      cnt[e * 32 + w] = run;  // first row of warp w inside expert e, relative to the expert
+      run += c;
+    }
+    total[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = total[e];
+      offsets[e] = run;
+      total[e] = run;
+      run += c;
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int e = i < end ? experts[i] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int pos = total[e] + cnt[e * 32 + warp] + __popc(m & lt);
+      sorted_pos[i] = pos;
+      src_token[pos] = i / k;
+    }
+    __syncwarp();
+    if (e >= 0 && (m & lt) == 0) cnt[e * 32 + warp] += __popc(m);
+    __syncwarp();
+  }
+}
+
 // out[t, :] = sum_j w[t, j] * y[sorted_pos[t * k + j], :]  (+ add[t, :] if given)
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ w,
@@ -232,7 +294,10 @@ MLCB_API int mlcb_moe_permute(const int* experts, int n, int k, int E, int* offs
                               int* src_token, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (E > 4096) return -1;
-  moe_permute_kernel<<<1, 1024, 2 * E * sizeof(int), stream>>>(experts, n, k, E, offsets, sorted_pos, src_token);
+  if (E <= 256)
+    moe_permute_split_kernel<<<1, 1024, 33 * E * sizeof(int), stream>>>(experts, n, k, E, offsets, sorted_pos, src_token);
+  else
+    moe_permute_kernel<<<1, 1024, 2 * E * sizeof(int), stream>>>(experts, n, k, E, offsets, sorted_pos, src_token);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -351,6 +351,23 @@ def test_moe_block_kernels(quant_name, tokens):
     _close(o_gpu, o_cpu, 3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("tokens,k,e", [(1, 2, 8), (7, 2, 8), (256, 2, 8), (300, 8, 128), (8192, 2, 8), (1000, 6, 256),
+                                        (50, 4, 384)])
+def test_moe_permute_is_the_stable_expert_major_order(tokens, k, e):
+    """Offsets, row of every pair and source token of every row equal a stable sort by expert, for few and
+    many experts (both kernels) and for pair counts below and above one pass of the CTA."""
+    g = torch.Generator().manual_seed(tokens + e)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(tokens)]).to(torch.int32)
+    if tokens > 8:  # a skewed case: most pairs on one expert
+        idx[: tokens // 2, 0] = 1
+    off_c, pos_c, src_c = ops.moe_permute(idx, e)
+    off_g, pos_g, src_g = ops.moe_permute(idx.to(DEV), e)
+    torch.cuda.synchronize()
+    assert torch.equal(off_c, off_g.cpu())
+    assert torch.equal(pos_c, pos_g.cpu())
+    assert torch.equal(src_c, src_g.cpu())
+
+
 @pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
 @pytest.mark.parametrize("tokens,k", [(256, 2048), (37, 512), (1000, 1024)])
 def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
