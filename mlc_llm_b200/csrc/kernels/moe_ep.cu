@@ -143,7 +143,12 @@ ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ live, co
                        const EpParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int idx = blockIdx.x * 8 + warp;  // compact row
-  if (idx < live[0]) {
+  // the grid covers the worst case; only the CTAs that hold rows (and CTA 0, so that the flags are always
+  // written) take part in the completion count
+  const int rows = live[0];
+  const int ctas = max(1, (rows + 7) / 8);
+  if (static_cast<int>(blockIdx.x) >= ctas) return;
+  if (idx < rows) {
     const int pair = pairs[idx];
     const uint4* in = reinterpret_cast<const uint4*>(y + static_cast<size_t>(idx) * p.hidden);
     // every rank sums every token (the attention that follows wants all tokens everywhere): the row goes to
@@ -160,7 +165,7 @@ ep_combine_send_kernel(const T* __restrict__ y, const int* __restrict__ live, co
   __shared__ int is_last;
   if (threadIdx.x == 0) {
     const int prev = atomicAdd(p.done_counter, 1);
-    is_last = prev == static_cast<int>(gridDim.x) - 1;
+    is_last = prev == ctas - 1;
     if (is_last) *p.done_counter = 0;
   }
   __syncthreads();
