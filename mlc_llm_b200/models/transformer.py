@@ -179,10 +179,10 @@ class DecoderModel:
     def _attention_mla(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
         """Multi-head latent attention with the latent expanded before caching: q / k heads are
         [rotary | no-position] (the rotary key part is shared by all heads), values are zero-padded to
-        the q / k width, and the paged kernels run an ordinary multi-head problem."""
+        the q / k width, and the paged kernels run an ordinary multi-head problem. Under tensor parallelism
+        a rank holds ``num_heads / tp`` heads of the up-projections and of ``o_proj``'s input; the latent
+        projections are computed whole on every rank (they are small) and the caller all-reduces the output."""
         c, m = self.cfg, self.cfg.extra["mla"]
-        if self.tp > 1:
-            raise NotImplementedError("multi-head latent attention is not sharded across ranks yet")
         pre = f"model.layers.{li}.self_attn."
         t = h.shape[0]
         hq, d = self.hq, self.d
@@ -701,6 +701,10 @@ def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
     elif name.endswith("gate_up_proj"):
         segs = [full_rows // 2, full_rows // 2]
     elif name.endswith("mlp.up_proj"):
+        segs = [full_rows]
+    elif cfg.extra.get("mla") and name.endswith(("self_attn.q_b_proj", "self_attn.q_proj", "self_attn.kv_b_proj")):
+        # latent attention: the per-head up-projections are head-major, so a rank keeps the rows of its heads;
+        # the down-projections to the latents (q_a, kv_a) stay whole on every rank
         segs = [full_rows]
     else:
         return None

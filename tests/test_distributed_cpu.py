@@ -33,7 +33,9 @@ def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_e
     return result
 
 
-@pytest.mark.parametrize("model", ["random://tiny-llama?quant=q0f32&seed=5"])
+@pytest.mark.parametrize("model", ["random://tiny-llama?quant=q0f32&seed=5",
+                                   # latent attention with its heads split over the ranks + sharded experts
+                                   "random://tiny-deepseek-v2?quant=q0f32&seed=5"])
 def test_tp2_matches_single_rank(model):
     single = _run(1, model, port=29541)
     tp2 = _run(2, model, port=29542)

@@ -133,3 +133,12 @@ def test_expert_parallel_logits_match_the_oracle(world, mode):
 def test_pipeline_parallel_logits_match_the_oracle(world):
     got, _ = _worker_logits(world, LLAMA, "cuda", 29640 + world, {"MLCB_TEST_PP": "2"})
     _check(got, _oracle(LLAMA), (world, "pp2 x tp%d" % (world // 2)))
+
+
+@pytest.mark.parametrize("world", [pytest.param(2, marks=_need(2))])
+def test_latent_attention_heads_split_over_ranks(world):
+    """DeepSeek-V2 form: the per-head up-projections of the latent attention and ``o_proj`` are split by heads,
+    the latent projections stay whole; routed and shared experts are split on their width."""
+    model = "random://tiny-deepseek-v2?quant=q0f16&seed=5"
+    got, _ = _worker_logits(world, model, "cuda", 29650 + world, {"MLCB_FUSED_TP": "0"})
+    _check(got, _oracle(model), (world, "mla tp"), routed=True)
