@@ -100,7 +100,8 @@ class Communicator:
 
     def broadcast_tokens(self, tokens: torch.Tensor) -> None:
         """The tokens rank 0 sampled, to every rank of its tensor-parallel group, device to device
-        (they are the next step's inputs and never visit the host on the way)."""
+        (they are the next step's inputs and never visit the host on the way). Also carries the feature rows
+        of an EAGLE draft call: any tensor whose shape and dtype the ranks agree on."""
         if self.tp_size > 1:
             dist.broadcast(tokens, src=self.pp_rank * self.tp_size, group=self.tp_group)
             self.launches += 1

@@ -289,8 +289,11 @@ class ModelExecutor:
                 self.spec_heads[mi] = "eagle"
             elif mi > 0 and m.cfg.extra.get("medusa"):
                 self.spec_heads[mi] = "medusa"
-        if self.spec_heads and comm is not None and comm.world_size > 1:
-            raise NotImplementedError("EAGLE / Medusa draft heads run on single-process engines only")
+        # Tensor-parallel engines: a Medusa head is a few small matrices and no state, so rank 0 evaluates it
+        # alone (every rank holds a copy); an EAGLE head is a sharded decoder layer that all ranks run, and rank
+        # 0, which alone keeps the feature store, sends them the feature rows of each call.
+        if self.spec_heads and comm is not None and comm.pp_size > 1:
+            raise NotImplementedError("EAGLE / Medusa draft heads are not available with pipeline stages")
         self.features = FeatureStore()
         # wall-clock seconds the host spent per phase of forward_sample (profiling aid)
         self.host_times: Dict[str, float] = {"pack": 0.0, "broadcast": 0.0, "upload": 0.0, "forward": 0.0,
@@ -619,7 +622,7 @@ class ModelExecutor:
         else:
             arrays = self._pack(plan, token_ids, sp, model_id)
             t1 = clock()
-            if self.comm is not None:
+            if self.comm is not None and self.spec_heads.get(model_id) != "medusa":
                 self.comm.broadcast_step("forward", model_id,
                                          {k: v for k, v in arrays.items()
                                           if not k.startswith("s_") or k == "s_logit_token_index"}, {})
@@ -864,6 +867,8 @@ class ModelExecutor:
             if own is not None and first <= own[0] < first + (b - a) and (t is None or own[0] >= s0 + t.shape[0]):
                 prev[a + (own[0] - first)] = own[1].to(x.dtype)
             all_true.append(covered == b - a)
+        if self.comm is not None:
+            self.comm.broadcast_tokens(prev)  # the other ranks fuse the same rows (see worker_step)
         x = head.fuse_embed_hidden(x, prev)
         h = head.forward(x, self._batch_info(dev, plan, head))
         for i, sid in enumerate(ids):
@@ -1100,6 +1105,16 @@ class ModelExecutor:
             tokens = torch.empty(int(arrays["s_logit_token_index"].size), dtype=torch.int32, device=self.device)
             self.comm.broadcast_tokens(tokens)
             self._last_tokens[model_id] = tokens
+            return
+        if self.spec_heads.get(model_id) == "eagle":
+            # this rank's shard of the draft head: the feature rows come from rank 0, the output stays here
+            head = self.models[model_id]
+            if dev["page_copies"].numel():
+                head.copy_pages(dev["page_copies"])
+            x = head.embed(dev["token_ids"])
+            prev = torch.empty(x.shape[0], self.models[0].cfg.hidden_size, dtype=x.dtype, device=self.device)
+            self.comm.broadcast_tokens(prev)
+            head.forward(head.fuse_embed_hidden(x, prev), self._batch_info(dev, plan, head))
             return
         hidden = self._run_model(model_id, plan, dev, None)
         model = self.models[model_id]

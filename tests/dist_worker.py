@@ -25,6 +25,11 @@ def main():
     cfg = EngineConfig(model=model, mode="server", max_num_sequence=8, prefill_chunk_size=64,
                        max_total_sequence_length=1024, prefix_cache_mode="disable",
                        tensor_parallel_shards=world // pp, pipeline_parallel_stages=pp)
+    spec = os.environ.get("MLCB_TEST_SPEC", "")
+    if spec:  # "eagle=<model string>" / "medusa=<model string>": a feature-fed draft head beside the model
+        cfg.speculative_mode, head = spec.split("=", 1)
+        cfg.spec_draft_length = 3
+        cfg.additional_models = [head]
     exit_after = int(os.environ.get("MLCB_TEST_WORKER_EXIT_AFTER", "0"))
     if rank != 0:
         rt = EngineRuntime(cfg, dev, comm=comm)
@@ -86,6 +91,7 @@ def main():
     print("FLAGS " + json.dumps({"fused_tp": bool(getattr(rt, "fused_tp", False)),
                                  "graph_replays": int(rt.executor.graph_replays),
                                  "pp_microbatch_steps": int(rt.executor.pp_microbatch_steps),
+                                 "num_verify_steps": int(json.loads(eng.debug_stats()).get("num_verify_steps", 0)),
                                  "fused_launches": int(rt.models[0].fused.launches) if getattr(rt.models[0], "fused", None) else 0}),
           flush=True)
     print("RESULT " + json.dumps([t[0] for t in toks]), flush=True)

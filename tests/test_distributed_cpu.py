@@ -61,3 +61,15 @@ def test_pp2_micro_batches_match_single_rank():
                       want_flags=True)
     assert single == pp2
     assert flags["pp_microbatch_steps"] >= 1
+
+
+@pytest.mark.parametrize("mode,head", [("eagle", "random://tiny-eagle?quant=q0f32&seed=3"),
+                                       ("medusa", "random://tiny-medusa?quant=q0f32&seed=4")])
+def test_tp2_with_a_feature_fed_draft_head_matches_plain_decoding(mode, head):
+    """EAGLE: every rank runs its shard of the draft layer on feature rows that rank 0 sends; Medusa: rank 0
+    evaluates the heads alone. Greedy speculative output is the plain single-process output."""
+    model = "random://tiny-llama?quant=q0f32&seed=5"
+    single = _run(1, model, port=29547)
+    tp2, flags = _run(2, model, port=29548, extra_env={"MLCB_TEST_SPEC": f"{mode}={head}"}, want_flags=True)
+    assert single == tp2
+    assert flags["num_verify_steps"] > 0
