@@ -103,6 +103,12 @@ MODEL_PRESETS = {
         "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 32000,
         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096,
     },
+    # one-block EAGLE head for tiny-llama-tp8
+    "tiny-eagle-tp8": {
+        "model_type": "eagle", "hidden_size": 1024, "intermediate_size": 2048, "num_hidden_layers": 1,
+        "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 32000,
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 4096, "bias": True,
+    },
     "tiny-mixtral-tp8": {
         "model_type": "mixtral", "hidden_size": 1024, "intermediate_size": 1024, "num_hidden_layers": 2,
         "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 32000,

@@ -66,3 +66,18 @@ def test_pp2_nccl_p2p_matches_single_gpu():
     pp2 = _run(2, model, "cuda", port=29558, extra_env={"MLCB_TEST_PP": "2", "NCCL_NVLS_ENABLE": "0"})
     agree = np.mean([np.mean(np.asarray(a) == np.asarray(b)) for a, b in zip(single, pp2)])
     assert agree >= 0.9, (single, pp2)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_eagle_head_runs_sharded_and_keeps_the_greedy_output():
+    """Two ranks, fused tensor-parallel target + an EAGLE head whose layer is sharded the same way: rank 0 sends
+    the feature rows of every draft call to rank 1. Greedy tokens stay those of plain TP2 decoding (a near-tie
+    between the verification batch and the one-token step may move a late token in fp16)."""
+    model = "random://tiny-llama-tp8?quant=q0f16&seed=5"
+    plain = _run(2, model, "cuda", port=29571)
+    spec, flags = _run(2, model, "cuda", port=29572, want_flags=True,
+                       extra_env={"MLCB_TEST_SPEC": "eagle=random://tiny-eagle-tp8?quant=q0f16&seed=3"})
+    assert flags["num_verify_steps"] > 0
+    same = sum(int(a == b) for p, s in zip(plain, spec) for a, b in zip(p, s))
+    total = sum(len(p) for p in plain)
+    assert [p[0] for p in plain] == [s[0] for s in spec] and same >= 0.5 * total, (plain, spec)
