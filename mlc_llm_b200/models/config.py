@@ -509,7 +509,9 @@ def _deepseek_v2(cfg, mt):
         extra["softmax_mscale"] = 1.0 if factor <= 1 else 0.1 * float(scaling["mscale_all_dim"]) * math.log(factor) + 1.0
     extra["mla"] = {"q_lora_rank": _get(cfg, "q_lora_rank"), "kv_lora_rank": int(_get(cfg, "kv_lora_rank", default=512)),
                     "qk_nope_head_dim": nope, "qk_rope_head_dim": rope,
-                    "v_head_dim": int(_get(cfg, "v_head_dim", default=128))}
+                    "v_head_dim": int(_get(cfg, "v_head_dim", default=128)),
+                    # "expanded": per-head keys / values are cached; "latent": the latent itself is cached
+                    "cache": str(_get(cfg, "mla_cache", default="expanded"))}
     d["extra"] = extra
     return d
 

@@ -61,6 +61,16 @@ MODEL_PRESETS = {
         "first_k_dense_replace": 1, "topk_method": "group_limited_greedy", "n_group": 4, "topk_group": 2,
         "routed_scaling_factor": 1.0, "norm_topk_prob": False,
     },
+    # the same with the compressed cache: one [rotary key | latent] row per token instead of per-head keys / values
+    "tiny-deepseek-v2-latent": {
+        "model_type": "deepseek_v2", "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 3,
+        "num_attention_heads": 4, "num_key_value_heads": 4, "vocab_size": 32000, "rms_norm_eps": 1e-6,
+        "rope_theta": 10000.0, "max_position_embeddings": 4096, "q_lora_rank": None, "kv_lora_rank": 128,
+        "qk_nope_head_dim": 128, "qk_rope_head_dim": 64, "v_head_dim": 128, "n_routed_experts": 8,
+        "n_shared_experts": 2, "num_experts_per_tok": 2, "moe_intermediate_size": 256,
+        "first_k_dense_replace": 1, "topk_method": "group_limited_greedy", "n_group": 4, "topk_group": 2,
+        "routed_scaling_factor": 1.0, "norm_topk_prob": False, "mla_cache": "latent",
+    },
     "tiny-rwkv5": {
         "model_type": "rwkv5", "hidden_size": 128, "num_hidden_layers": 2, "head_size": 32, "vocab_size": 32000,
         "layer_norm_epsilon": 1e-5, "rescale_every": 0,

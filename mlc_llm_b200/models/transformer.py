@@ -13,6 +13,7 @@ tensor-parallel sharding, batch_prefill / batch_decode / batch_verify entry poin
 from __future__ import annotations
 
 import dataclasses
+import os
 import math
 from typing import Dict, List, Optional
 
@@ -96,10 +97,25 @@ class DecoderModel:
                 # YaRN checkpoints trained with `mscale_all_dim` fold its square into the softmax scale
                 self.sm_scale *= float(config.extra["softmax_mscale"]) ** 2
 
+        # Latent attention caches either per-head keys / values expanded from the latent ("expanded") or the
+        # latent itself plus the shared rotary key ("latent": one row of rope + rank values per token and layer
+        # for all heads, queries and outputs go through the absorbed up-projections).
+        mla = config.extra.get("mla")
+        self.mla_latent = bool(mla) and (os.environ.get("MLCB_MLA_CACHE") or mla.get("cache", "expanded")) == "latent"
+        self._mla_absorbed: dict = {}
+        if self.mla_latent:
+            self.cache_kv_heads = 1
+            self.cache_head_dim = (mla["qk_rope_head_dim"] + mla["kv_lora_rank"] + 1) // 2  # K and V halves of a row
+
     # ------------------------------------------------------------------ KV cache
     def create_kv_cache(self, num_pages: int, page_size: int = 16) -> None:
         self.page = page_size
         n = len(self.layers)
+        if self.mla_latent:
+            m = self.cfg.extra["mla"]
+            self.kv_pages = torch.zeros(n, num_pages, 1, 1, page_size, m["qk_rope_head_dim"] + m["kv_lora_rank"],
+                                        dtype=self.kv_dtype, device=self.device)
+            return
         self.kv_pages = torch.zeros(n, num_pages, 2, self.hkv, page_size, self.d, dtype=self.kv_dtype,
                                     device=self.device)
 
@@ -112,7 +128,11 @@ class DecoderModel:
         return self.dtype if self.dtype != torch.float32 or self.device.type == "cpu" else torch.float16
 
     def kv_bytes_per_token(self) -> int:
-        return 2 * self.hkv * self.d * len(self.layers) * (2 if self.kv_dtype != torch.float32 else 4)
+        es = 2 if self.kv_dtype != torch.float32 else 4
+        if self.mla_latent:
+            m = self.cfg.extra["mla"]
+            return (m["qk_rope_head_dim"] + m["kv_lora_rank"]) * len(self.layers) * es
+        return 2 * self.hkv * self.d * len(self.layers) * es
 
     def copy_pages(self, pairs: torch.Tensor) -> None:
         """(src, dst) page copies for copy-on-write, applied to every layer."""
@@ -196,12 +216,58 @@ class DecoderModel:
         ckv = ops.linear(h, self.p.linears[pre + "kv_a_proj_with_mqa"])
         latent = ops.rmsnorm(ckv[:, :rank].contiguous(), self.p.tensors[pre + "kv_a_layernorm.weight"],
                              c.rms_norm_eps, 0.0)
+        if self.mla_latent:
+            return self._attention_mla_latent(li, q.view(t, hq, d), ckv[:, rank:], latent, b)
         kv = ops.linear(latent, self.p.linears[pre + "kv_b_proj"]).view(t, hq, nope + vd)
         k = torch.cat([ckv[:, rank:].unsqueeze(1).expand(t, hq, rope), kv[..., :nope]], dim=-1)
         v = torch.nn.functional.pad(kv[..., nope:], (0, d - vd))
         qkv = torch.cat([q.view(t, hq, d), k, v], dim=1).reshape(t, 3 * hq * d).contiguous()
         ctx = self._attention_core(li, qkv, b).view(t, hq, d)[..., :vd].reshape(t, hq * vd).contiguous()
         return ops.linear(ctx, self.p.linears[pre + "o_proj"])
+
+    def _mla_up_projections(self, li: int):
+        """Per-head key and value up-projections of layer ``li`` as dense batched-matmul operands:
+        ``w_uk [hq, nope, rank]`` (absorbed into the queries) and ``w_uv_t [hq, rank, v]`` (applied to the
+        attention-weighted latents)."""
+        got = self._mla_absorbed.get(li)
+        if got is None:
+            m = self.cfg.extra["mla"]
+            nope, vd, rank = m["qk_nope_head_dim"], m["v_head_dim"], m["kv_lora_rank"]
+            lw = self.p.linears[f"model.layers.{li}.self_attn.kv_b_proj"]
+            w = lw.dense(self.dtype).view(self.hq, nope + vd, rank)
+            got = (w[:, :nope, :].contiguous(), w[:, nope:, :].transpose(1, 2).contiguous())
+            if lw.kind != "dense":
+                lw._dense = None  # pylint: disable=protected-access  (the two copies above replace it)
+            self._mla_absorbed[li] = got
+        return got
+
+    def _attention_mla_latent(self, li: int, q: torch.Tensor, k_rope: torch.Tensor, latent: torch.Tensor,
+                              b: BatchInfo) -> torch.Tensor:
+        """Latent attention over the compressed cache. ``q [T, hq, rope + nope]`` (rotary part first),
+        ``k_rope [T, rope]`` (unrotated, shared by all heads), ``latent [T, rank]`` (normalised).
+        Scores are ``q_rope . k_rope + (q_nope W_uk) . latent``, the context is ``(softmax . latent) W_uv``:
+        the same numbers as expanding keys and values from the latent, without ever storing them."""
+        c, m = self.cfg, self.cfg.extra["mla"]
+        pre = f"model.layers.{li}.self_attn."
+        t, hq = q.shape[0], self.hq
+        nope, rope, vd, rank = m["qk_nope_head_dim"], m["qk_rope_head_dim"], m["v_head_dim"], m["kv_lora_rank"]
+        w_uk, w_uv_t = self._mla_up_projections(li)
+        local = self._kv_layer(li)
+        cache = self.kv_pages[local]
+        # rotate the rotary parts with the rotary kernel (hq query heads and one key head of width `rope`;
+        # slot -1: nothing is appended by that call)
+        rot = torch.cat([q[..., :rope].reshape(t, hq * rope), k_rope, torch.zeros_like(k_rope)], dim=1).contiguous()
+        if self.inv_freq is not None:
+            ops.rope_append(rot, cache, b.positions, torch.full_like(b.slots, -1), self.inv_freq, hq, 1, rope, rope,
+                            self.page, self.rope_attn_factor)
+        q_lat = torch.bmm(q[..., rope:].transpose(0, 1), w_uk).transpose(0, 1)          # [T, hq, rank]
+        q_abs = torch.cat([rot[:, : hq * rope].view(t, hq, rope), q_lat], dim=-1).contiguous()
+        rows = torch.cat([rot[:, hq * rope: (hq + 1) * rope], latent], dim=-1).to(cache.dtype).contiguous()
+        ops.mla_append(rows, cache, b.slots, self.page)
+        ctx = ops.mla_attention(q_abs.to(cache.dtype), cache, b.q_seq, b.q_kvlen, b.page_indptr, b.page_indices,
+                                rope, rank, self.page, self.sm_scale, q_kvstart=b.q_kvstart, tree_mask=b.tree_mask)
+        v = torch.bmm(ctx.to(self.dtype).transpose(0, 1), w_uv_t).transpose(0, 1)       # [T, hq, v]
+        return ops.linear(v.reshape(t, hq * vd).contiguous(), self.p.linears[pre + "o_proj"])
 
     def _attention(self, li: int, h: torch.Tensor, b: BatchInfo) -> torch.Tensor:
         if self.cfg.extra.get("mla"):

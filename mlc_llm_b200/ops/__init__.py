@@ -414,6 +414,46 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
     return (out, lse) if return_lse else out
 
 
+def mla_append(rows: torch.Tensor, cache: torch.Tensor, slot: torch.Tensor, page: int) -> None:
+    """Latent-attention cache write: row ``t`` of ``rows [T, D]`` (= [rotated rotary key | normalised latent]) goes
+    to slot ``slot[t]`` of one layer's cache ``[num_pages, 1, 1, page, D]`` (reference: ``append_mla_kv``,
+    ``python/mlc_llm/model/deepseek_v2/deepseek_v2_model.py:338-344``)."""
+    if not rows.is_cuda:
+        ref.mla_append(rows, cache, slot, page)
+        return
+    assert rows.is_contiguous() and cache.is_contiguous() and rows.dtype == cache.dtype
+    rc = lib().mlcb_mla_append(ptr(rows), ptr(cache), ptr(slot), c_int(rows.shape[0]), c_int(rows.shape[1]),
+                               c_ll(cache.shape[0] * page), c_int(DTYPE_CODE[rows.dtype]),
+                               ptr(status_word(rows.device)), stream_ptr())
+    check(rc, "mlcb_mla_append")
+
+
+def mla_attention(q: torch.Tensor, cache: torch.Tensor, q_seq: torch.Tensor, q_kvlen: torch.Tensor,
+                  page_indptr: torch.Tensor, page_indices: torch.Tensor, rope: int, rank: int, page: int,
+                  sm_scale: float, q_kvstart: Optional[torch.Tensor] = None, sink: int = 0,
+                  tree_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Latent attention in its absorbed form: ``q [T, hq, rope + rank]`` (per head: rotated rotary part, then the
+    no-position part already multiplied by the key up-projection) against the compressed cache, whose one row per
+    token is shared by all heads. Returns the attention-weighted latents ``[T, hq, rank]``; the caller applies the
+    value up-projection (reference: the absorbed ``cross_attention`` of the MLA cache,
+    ``python/mlc_llm/model/deepseek_v2/deepseek_v2_model.py:346-385``)."""
+    t, hq, d = q.shape
+    if not q.is_cuda:
+        return ref.mla_attention(q, cache, q_seq, q_kvlen, page_indptr, page_indices, rope, rank, page, sm_scale,
+                                 q_kvstart, sink, tree_mask)
+    assert q.is_contiguous() and cache.is_contiguous() and q.dtype == cache.dtype and d == rope + rank
+    out = torch.empty(t, hq, rank, dtype=q.dtype, device=q.device)
+    rc = lib().mlcb_attn_mla(ptr(q), ptr(cache), ptr(out), ptr(q_seq), ptr(q_kvlen), ptr(q_kvstart), ptr(tree_mask),
+                             ptr(page_indptr), ptr(page_indices), c_int(t), c_int(hq * d), c_int(hq), c_int(rope),
+                             c_int(rank), c_int(page), c_int(cache.shape[0]), c_int(sink), c_float(sm_scale),
+                             c_int(DTYPE_CODE[q.dtype]), ptr(status_word(q.device)), stream_ptr())
+    if rc == -1:
+        raise ValueError(f"latent attention kernel: rope {rope} and rank {rank} must be multiples of 64 with "
+                         f"rope + rank <= 576, in fp16 or bf16")
+    check(rc, "mlcb_attn_mla")
+    return out
+
+
 def encoder_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_lens: Optional[torch.Tensor] = None,
                       causal: bool = False, scale: Optional[float] = None) -> torch.Tensor:
     """Attention over whole sequences (vision towers, BERT-style encoders). ``q``, ``k``, ``v``: ``[B, S, H, D]``

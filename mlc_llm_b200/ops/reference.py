@@ -213,6 +213,44 @@ def paged_attention(q: torch.Tensor, kv_pages: torch.Tensor, q_seq: torch.Tensor
     return (out, lse) if return_lse else out
 
 
+def mla_append(rows: torch.Tensor, cache: torch.Tensor, slot: torch.Tensor, page: int) -> None:
+    """``rows [T, D]`` into the slots of a latent cache ``[num_pages, 1, 1, page, D]``; negative slots are skipped."""
+    valid = slot >= 0
+    if valid.any():
+        sl = slot[valid].long()
+        cache[sl // page, 0, 0, sl % page, :] = rows[valid].to(cache.dtype)
+
+
+def mla_attention(q: torch.Tensor, cache: torch.Tensor, q_seq: torch.Tensor, q_kvlen: torch.Tensor,
+                  page_indptr: torch.Tensor, page_indices: torch.Tensor, rope: int, rank: int, page: int,
+                  sm_scale: float, q_kvstart: Optional[torch.Tensor] = None, sink: int = 0,
+                  tree_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Absorbed latent attention: ``q [T, hq, rope + rank]`` against cached rows ``[rope | latent]`` shared by all
+    heads; returns the softmax-weighted latents ``[T, hq, rank]``. Visibility as in :func:`paged_attention`."""
+    t, hq, d = q.shape
+    out = torch.zeros(t, hq, rank, dtype=q.dtype, device=q.device)
+    for i in range(t):
+        b = int(q_seq[i])
+        n = int(q_kvlen[i])
+        tm = int(tree_mask[i]) if tree_mask is not None else 0
+        total = n + (tm.bit_length() if tm else 0)
+        if total == 0:
+            continue
+        pages = page_indices[int(page_indptr[b]) : int(page_indptr[b + 1])].long()
+        npg = (total + page - 1) // page
+        rows = cache[pages[:npg], 0, 0].reshape(npg * page, d)[:total].float()
+        idx = torch.arange(total, device=q.device)
+        start = int(q_kvstart[i]) if q_kvstart is not None else 0
+        vis = (idx < n) & ((idx < sink) | (idx >= start))
+        if tm:
+            vis[n:] = torch.tensor([(tm >> j) & 1 for j in range(total - n)], dtype=torch.bool, device=q.device)
+        s = (q[i].float() @ rows.T) * sm_scale
+        s = s.masked_fill(~vis.view(1, -1), -float("inf"))
+        p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
+        out[i] = (p @ rows[:, rope:]).to(q.dtype)
+    return out
+
+
 # --------------------------------------------------------------------------- logits / sampling
 def softmax_temperature(logits: torch.Tensor, temperature: torch.Tensor,
                         active_vocab: int = 0) -> torch.Tensor:

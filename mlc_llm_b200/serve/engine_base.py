@@ -336,7 +336,8 @@ class EngineRuntime:
             self.models.append(model)
             infos.append({
                 "params_bytes": store.nbytes(), "num_layers": mcfg.num_hidden_layers,
-                "num_qo_heads": model.hq, "num_kv_heads": model.hkv, "head_dim": mcfg.head_dim,
+                "num_qo_heads": model.hq, "num_kv_heads": getattr(model, "cache_kv_heads", model.hkv),
+                "head_dim": getattr(model, "cache_head_dim", mcfg.head_dim),
                 "vocab_size": mcfg.vocab_size, "context_window_size": mcfg.context_window_size,
                 "sliding_window_size": mcfg.sliding_window_size,
                 "prefill_chunk_size": mcfg.prefill_chunk_size, "max_batch_size": mcfg.max_batch_size,

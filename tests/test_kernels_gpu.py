@@ -351,6 +351,69 @@ def test_moe_block_kernels(quant_name, tokens):
     _close(o_gpu, o_cpu, 3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,rope,rank", [(4, 64, 128), (16, 64, 512), (5, 64, 192), (8, 128, 256)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_latent_attention_kernel(dtype, hq, rope, rank, masked):
+    """Absorbed latent attention over the compressed cache against the fp32 reference on the same 16-bit values:
+    a prefill chunk on top of a cached prefix, decode tokens of other lengths (among them one row and a
+    non-multiple of the four rows the kernel keeps in flight), scattered pages; with ``masked`` also window
+    starts with sink rows and tree masks."""
+    torch.manual_seed(hq + rank)
+    page, d = 16, rope + rank
+    kv_lens = [75, 1, 34, 130]
+    q_lens = [11, 1, 1, 3]
+    n_pages = 40
+    perm = torch.randperm(n_pages - 1)[: sum((n + page - 1) // page for n in kv_lens)] + 1
+    indptr, indices, at = [0], [], 0
+    for n in kv_lens:
+        k = (n + page - 1) // page
+        indices += perm[at: at + k].tolist()
+        at += k
+        indptr.append(len(indices))
+    cache = torch.zeros(n_pages, 1, 1, page, d, dtype=dtype)
+    rows, slots, q_seq, q_kvlen = [], [], [], []
+    for b, n in enumerate(kv_lens):
+        r = (torch.randn(n, d) * 0.5).to(dtype)
+        rows.append(r)
+        pg = torch.tensor(indices[indptr[b]: indptr[b + 1]])
+        slots.append(pg[torch.arange(n) // page] * page + torch.arange(n) % page)
+        for j in range(q_lens[b]):
+            q_seq.append(b)
+            q_kvlen.append(n - q_lens[b] + j + 1)
+    rows, slots = torch.cat(rows), torch.cat(slots).to(torch.int32)
+    t = len(q_seq)
+    q = (torch.randn(t, hq, d) * 0.5).to(dtype)
+    q_seq, q_kvlen = torch.tensor(q_seq, dtype=torch.int32), torch.tensor(q_kvlen, dtype=torch.int32)
+    kvstart = tree = None
+    sink = 0
+    if masked:
+        sink = 2
+        kvstart = torch.clamp(q_kvlen - 20, min=0).to(torch.int32)
+        # the three tokens of the last sequence form a small tree behind the committed rows: a root and two
+        # children that see the root and themselves
+        q_kvlen[-3:] = kv_lens[-1] - 3
+        kvstart[-3:] = 0
+        tree = torch.zeros(t, dtype=torch.int64)
+        tree[-3], tree[-2], tree[-1] = 0b001, 0b011, 0b101
+    ipt, idx = torch.tensor(indptr, dtype=torch.int32), torch.tensor(indices, dtype=torch.int32)
+    # the slot of a stand-in row is negative: it must be skipped
+    rows_in = torch.cat([rows, torch.full((1, d), 7.0, dtype=dtype)])
+    slots_in = torch.cat([slots, torch.tensor([-1], dtype=torch.int32)])
+    ops.mla_append(rows_in.float(), cache_f := cache.float(), slots_in, page)
+    want = ref.mla_attention(q.float(), cache_f, q_seq, q_kvlen, ipt, idx, rope, rank, page, 0.09, kvstart, sink, tree)
+    cache_g = cache.to(DEV)
+    ops.mla_append(rows_in.to(DEV), cache_g, slots_in.to(DEV), page)
+    torch.cuda.synchronize()
+    assert torch.equal(cache_g.cpu().float(), cache_f)
+    mv = lambda x: None if x is None else x.to(DEV)
+    got = ops.mla_attention(q.to(DEV), cache_g, mv(q_seq), mv(q_kvlen), mv(ipt), mv(idx), rope, rank, page, 0.09,
+                            mv(kvstart), sink, mv(tree))
+    ops.check_status(torch.device(DEV))
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    _close(got.float().cpu(), want, tol, tol)
+
+
 @pytest.mark.parametrize("tokens,k,e", [(1, 2, 8), (7, 2, 8), (256, 2, 8), (300, 8, 128), (8192, 2, 8), (1000, 6, 256),
                                         (50, 4, 384)])
 def test_moe_permute_is_the_stable_expert_major_order(tokens, k, e):

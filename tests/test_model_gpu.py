@@ -34,6 +34,7 @@ def _batch(plan, device):
 @pytest.mark.parametrize("preset,quant", [("tiny-llama-gpu", "q0f16"), ("tiny-llama-gpu", "q4f16_1"),
                                           ("tiny-llama-gpu", "q0bf16"), ("tiny-mixtral-gpu", "q0f16"),
                                           ("tiny-mixtral-gpu", "q4f16_1"), ("tiny-deepseek-v2", "q0f16"),
+                                          ("tiny-deepseek-v2-latent", "q0f16"), ("tiny-deepseek-v2-latent", "q0bf16"),
                                           ("tiny-gpt2-gpu", "q0f16"), ("tiny-neox-gpu", "q0f16"),
                                           ("tiny-starcoder2-gpu", "q0f16"), ("tiny-gemma2-gpu", "q0bf16")])
 def test_forward_matches_cpu(preset, quant):
