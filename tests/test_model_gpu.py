@@ -68,6 +68,28 @@ def test_forward_matches_cpu(preset, quant):
     assert (outs[0] - outs[1]).abs().max() < tol, (outs[0] - outs[1]).abs().max()
 
 
+def test_engine_latent_cache_gpu():
+    """The engine on the GPU with the compressed latent cache (decode steps replayed from CUDA graphs, chunked
+    prefill, several sequences) against the same engine with expanded keys / values."""
+    from mlc_llm_b200.serve.config import EngineConfig
+    from mlc_llm_b200.serve.sync_engine import SyncMLCEngine
+
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, 32000, int(n)).tolist() for n in (90, 7, 33, 150)]
+    cfg = {"max_tokens": 12, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+    outs = []
+    for extra in ("", "&mla_cache=latent"):
+        eng = SyncMLCEngine("random://tiny-deepseek-v2?quant=q0f16&seed=0" + extra, "cuda",
+                            engine_config=EngineConfig(mode="server", max_num_sequence=8, prefill_chunk_size=64,
+                                                       max_total_sequence_length=4096))
+        assert eng.runtime.models[0].mla_latent == bool(extra)
+        _, toks = eng.generate(prompts, cfg)
+        outs.append([t[0] for t in toks])
+        del eng
+    same = sum(int(a == b) for x, y in zip(*outs) for a, b in zip(x, y))
+    assert [x[0] for x in outs[0]] == [y[0] for y in outs[1]] and same >= 0.7 * 48, outs
+
+
 def test_engine_end_to_end_gpu():
     from mlc_llm_b200.ops import _lib
     from mlc_llm_b200.serve.config import EngineConfig
