@@ -492,7 +492,8 @@ def _deepseek_v2(cfg, mt):
     experts with shared experts and group-limited routing (reference:
     ``python/mlc_llm/model/deepseek_v2/deepseek_v2_model.py``).  Here every head's q / k is laid out as
     [rotary | no-position] and values are padded to that width, so the paged attention kernels see a
-    plain multi-head problem; the latent is expanded before it is cached."""
+    plain multi-head problem; the latent is expanded before it is cached, or, with ``mla_cache = "latent"``,
+    cached itself and attended to through absorbed up-projections (``DecoderModel._attention_mla_latent``)."""
     d = _common(cfg, mt)
     nope = int(_get(cfg, "qk_nope_head_dim", default=128))
     rope = int(_get(cfg, "qk_rope_head_dim", default=64))
