@@ -88,7 +88,15 @@ class RwkvModel(DecoderModel):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         c = self.cfg
-        self.heads = c.hidden_size // c.head_dim
+        # tensor parallelism: a rank keeps `heads` whole heads of the time-mix block (their projections, decay,
+        # bonus, group norm and matrix state) and a slice of the channel-mix width; token-shift vectors and the
+        # residual stream are whole on every rank (reference: rwkv6_model.py shard strategies)
+        total = c.hidden_size // c.head_dim
+        if total % self.tp:
+            raise ValueError(f"{total} heads cannot be split over {self.tp} ranks")
+        self.heads = total // self.tp
+        rank = self.comm.tp_rank if (self.comm is not None and self.tp > 1) else 0
+        self._lo, self._hi = rank * self.heads * c.head_dim, (rank + 1) * self.heads * c.head_dim
         self.states: "collections.OrderedDict[int, Dict[str, torch.Tensor]]" = collections.OrderedDict()
 
     # ------------------------------------------------------------------ state
@@ -131,6 +139,16 @@ class RwkvModel(DecoderModel):
     # ------------------------------------------------------------------ forward
     def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
         return self.p.tensors["model.embeddings.weight"][token_ids.long()].to(self.dtype)
+
+    def _own(self, t: torch.Tensor) -> torch.Tensor:
+        """This rank's heads of a per-channel parameter whose last dimension(s) span all heads."""
+        if self.tp == 1:
+            return t
+        c = self.cfg
+        if t.shape[-1] == c.hidden_size:
+            return t[..., self._lo:self._hi]
+        return t.reshape(*t.shape[:-2], c.hidden_size)[..., self._lo:self._hi].reshape(
+            *t.shape[:-2], self.heads, c.head_dim)
 
     def _ln(self, x: torch.Tensor, name: str) -> torch.Tensor:
         return F.layer_norm(x.float(), (x.shape[-1],), self.p.tensors[name + ".weight"].float(),
@@ -177,27 +195,27 @@ class RwkvModel(DecoderModel):
                 mixed = lambda j, name: h + dx * (tp[a + name] + m5[j])
                 xw, xk, xv, xr, xg = (mixed(0, "time_maa_w"), mixed(1, "time_maa_k"), mixed(2, "time_maa_v"),
                                       mixed(3, "time_maa_r"), mixed(4, "time_maa_g"))
-                dec = tp[a + "time_decay"].float().view(1, n, hs) + (
-                    torch.tanh(xw.float() @ tp[a + "time_decay_w1"].float()) @ tp[a + "time_decay_w2"].float()
+                dec = self._own(tp[a + "time_decay"]).float().view(1, n, hs) + (
+                    torch.tanh(xw.float() @ tp[a + "time_decay_w1"].float()) @ self._own(tp[a + "time_decay_w2"]).float()
                 ).view(t_all, n, hs)
                 w = torch.exp(-torch.exp(dec)).contiguous()
             else:
                 mix = lambda name: h * self.p.tensors[a + name] + sx * (1.0 - self.p.tensors[a + name])
                 xr, xk, xv, xg = (mix("time_mix_receptance"), mix("time_mix_key"), mix("time_mix_value"),
                                   mix("time_mix_gate"))
-                w = self.p.tensors[a + "time_decay"].float()
+                w = self._own(self.p.tensors[a + "time_decay"]).float()
             r = ops.linear(xr, self.p.linears[a + "receptance"]).float().view(t_all, n, hs)
             k = ops.linear(xk, self.p.linears[a + "key"]).float().view(t_all, n, hs)
             v = ops.linear(xv, self.p.linears[a + "value"]).float().view(t_all, n, hs)
             g = F.silu(ops.linear(xg, self.p.linears[a + "gate"]).float())
-            u = self.p.tensors[a + "time_faaaa"].float()
+            u = self._own(self.p.tensors[a + "time_faaaa"]).float()
             out = wkv5_batch(r, k, v, w, u, [states[i]["kv"] for i in live], pos, live_indptr)
             newest = h.index_select(0, lasts)
             for j, i in enumerate(live):
                 states[i]["att_x"][pos] = newest[j]
-            out = F.group_norm(out.view(t_all, n * hs), n, self.p.tensors[a + "ln_x.weight"].float(),
-                               self.p.tensors[a + "ln_x.bias"].float(), eps=1e-5)
-            x = x + ops.linear((out * g).to(self.dtype), self.p.linears[a + "output"])
+            out = F.group_norm(out.view(t_all, n * hs), n, self._own(self.p.tensors[a + "ln_x.weight"]).float(),
+                               self._own(self.p.tensors[a + "ln_x.bias"]).float(), eps=1e-5)
+            x = x + self._reduce(ops.linear((out * g).to(self.dtype), self.p.linears[a + "output"]))
             # ---- channel mix
             h = self._ln(x, pre + "ln2")
             prev = torch.stack([states[i]["ffn_x"][pos] for i in live])
@@ -214,7 +232,7 @@ class RwkvModel(DecoderModel):
                 states[i]["ffn_x"][pos] = newest[j]
             rr = torch.sigmoid(ops.linear(xr, self.p.linears[f + "receptance"]).float())
             kk = torch.square(torch.relu(ops.linear(xk, self.p.linears[f + "key"]).float())).to(self.dtype)
-            x = x + (rr * ops.linear(kk, self.p.linears[f + "value"]).float()).to(self.dtype)
+            x = x + (rr * self._reduce(ops.linear(kk, self.p.linears[f + "value"])).float()).to(self.dtype)
             rescale = int(c.extra.get("rescale_every", 0))
             if rescale > 0 and (li + 1) % rescale == 0:
                 x = x / 2.0

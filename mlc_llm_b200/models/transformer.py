@@ -768,6 +768,11 @@ def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
         segs = [full_rows // 2, full_rows // 2]
     elif name.endswith("mlp.up_proj"):
         segs = [full_rows]
+    elif cfg.extra.get("rwkv") and name.endswith(("attention.receptance", "attention.key", "attention.value",
+                                                   "attention.gate", "feed_forward.key")):
+        # recurrent models: a rank keeps whole heads of the time-mix projections and a slice of the channel-mix
+        # width (reference: the shard strategies of python/mlc_llm/model/rwkv6/rwkv6_model.py)
+        segs = [full_rows]
     elif cfg.extra.get("mla") and name.endswith(("self_attn.q_b_proj", "self_attn.q_proj", "self_attn.kv_b_proj")):
         # latent attention: the per-head up-projections are head-major, so a rank keeps the rows of its heads;
         # the down-projections to the latents (q_a, kv_a) stay whole on every rank
@@ -783,4 +788,5 @@ def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
 
 
 def column_sharded(name: str) -> bool:
-    return name.endswith("self_attn.o_proj") or name.endswith("down_proj")
+    return name.endswith(("self_attn.o_proj", "down_proj")) or (
+        name.startswith("model.blocks.") and name.endswith(("attention.output", "feed_forward.value")))  # RWKV

@@ -316,9 +316,9 @@ class EngineRuntime:
             if mcfg.extra.get("rwkv"):
                 from ..models.rwkv import RwkvModel  # pylint: disable=import-outside-toplevel
 
-                if tp > 1 or pp > 1 or len(self.models_info) > 1:
-                    raise ValueError("recurrent-state models run on one GPU, without a draft model")
-                model = RwkvModel(mcfg, quant, store, self.device, None, layers)
+                if pp > 1 or len(self.models_info) > 1:
+                    raise ValueError("recurrent-state models run without pipeline stages and without a draft model")
+                model = RwkvModel(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
                 cfg.prefix_cache_mode = "disable"  # a recurrent state cannot be shared or rolled back
                 cfg.kv_state_kind = "rnn_state"
             elif mcfg.extra.get("gdn"):

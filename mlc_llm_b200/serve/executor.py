@@ -379,6 +379,9 @@ class ModelExecutor:
             arrays[k] = np.ascontiguousarray(plan[k], dtype=np.int32)
         arrays["tree_mask"] = np.ascontiguousarray(plan["tree_mask"], dtype=np.uint64).view(np.int64)
         model = self.models[model_id]
+        if getattr(model, "stateful", False):
+            # recurrent models pick their state by sequence id: the other ranks need the ids too
+            arrays["seq_ids"] = np.ascontiguousarray(plan["seq_ids"], dtype=np.int32)
         if self._pads_decode(model_id, arrays):
             pad_decode_arrays(arrays, graph_bucket(int(arrays["q_indptr"].size) - 1))
         if self._tc_attention_ok(model):
@@ -1096,6 +1099,8 @@ class ModelExecutor:
         plan = {k: arrays[k] for k in _INT_KEYS}
         plan["tree_mask"] = arrays["tree_mask"]
         plan["max_seq_len"] = int(arrays["seq_lens"].max()) if arrays["seq_lens"].size else 0
+        if "seq_ids" in arrays:
+            plan["seq_ids"] = arrays["seq_ids"]
         if op == "forward_async":
             # deferred-read decode step: inputs may be the tokens rank 0 sampled in the step before, and
             # this step's tokens arrive the same way (device to device) once rank 0 has sampled them

@@ -63,6 +63,15 @@ def test_pp2_micro_batches_match_single_rank():
     assert flags["pp_microbatch_steps"] >= 1
 
 
+@pytest.mark.parametrize("model", ["random://tiny-rwkv5?quant=q0f32&seed=5", "random://tiny-rwkv6?quant=q0f32&seed=5"])
+def test_tp2_recurrent_model_matches_single_rank(model):
+    """RWKV over two ranks: whole heads of the time-mix block (projections, decay, bonus, group norm, matrix
+    state) and half the channel-mix width per rank; the workers find a sequence's state by the broadcast ids."""
+    single = _run(1, model, port=29549)
+    tp2 = _run(2, model, port=29550)
+    assert single == tp2
+
+
 @pytest.mark.parametrize("mode,head", [("eagle", "random://tiny-eagle?quant=q0f32&seed=3"),
                                        ("medusa", "random://tiny-medusa?quant=q0f32&seed=4")])
 def test_tp2_with_a_feature_fed_draft_head_matches_plain_decoding(mode, head):
