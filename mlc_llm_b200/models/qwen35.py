@@ -117,10 +117,16 @@ class Qwen35Model(DecoderModel):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         c = self.cfg
-        if self.tp > 1:
-            raise NotImplementedError("the gated delta-rule layers are not sharded: run Qwen3.5 on one GPU")
         g = c.extra["gdn"]
-        self.nk, self.nv = int(g["num_key_heads"]), int(g["num_value_heads"])
+        # tensor parallelism: a rank keeps `nk / tp` key heads and the `nv / tp` value heads that go with them
+        # (projection rows, convolution channels, decay / gate parameters, recurrent state); `out_proj` is split
+        # on its input and the caller sums the partial outputs like an attention block's
+        self.nk_all, self.nv_all = int(g["num_key_heads"]), int(g["num_value_heads"])
+        if self.nk_all % self.tp or self.nv_all % self.tp:
+            raise ValueError(f"{self.nk_all} key / {self.nv_all} value heads cannot be split over {self.tp} ranks")
+        self.nk, self.nv = self.nk_all // self.tp, self.nv_all // self.tp
+        self.rank = self.comm.tp_rank if (self.comm is not None and self.tp > 1) else 0
+        self._gdn_params: dict = {}
         self.dk, self.dv = int(g["key_head_dim"]), int(g["value_head_dim"])
         self.kernel = int(g["conv_kernel"])
         self.key_dim, self.value_dim = self.nk * self.dk, self.nv * self.dv
@@ -211,18 +217,38 @@ class Qwen35Model(DecoderModel):
         ctx = (ctx.float() * torch.sigmoid(gate.float())).to(h.dtype)
         return ops.linear(ctx, self.p.linears[pre + "o_proj"])
 
+    def _own_gdn_params(self, li: int) -> dict:
+        """This rank's part of the unsharded small parameters of a gated delta-rule layer."""
+        got = self._gdn_params.get(li)
+        if got is None:
+            pre = f"model.layers.{li}.linear_attn."
+            tp = self.p.tensors
+            ba, conv, a_log, dt = (tp[pre + "in_proj_ba.weight"], tp[pre + "conv1d.weight"], tp[pre + "A_log"],
+                                   tp[pre + "dt_bias"])
+            if self.tp > 1:
+                r, nv, kd, vd = self.rank, self.nv, self.key_dim, self.value_dim
+                kd_all, vd_all = kd * self.tp, vd * self.tp
+                v0 = slice(r * nv, (r + 1) * nv)
+                ba = torch.cat([ba[v0], ba[self.nv_all + r * nv: self.nv_all + (r + 1) * nv]]).contiguous()
+                conv = torch.cat([conv[r * kd:(r + 1) * kd], conv[kd_all + r * kd: kd_all + (r + 1) * kd],
+                                  conv[2 * kd_all + r * vd: 2 * kd_all + (r + 1) * vd]]).contiguous()
+                a_log, dt = a_log[v0].contiguous(), dt[v0].contiguous()
+            got = self._gdn_params[li] = {"ba": ba, "conv": conv, "A_log": a_log, "dt_bias": dt}
+        return got
+
     def _gated_delta_net(self, li: int, h: torch.Tensor) -> torch.Tensor:
         pre = f"model.layers.{li}.linear_attn."
         t_all = h.shape[0]
         tp = self.p.tensors
+        own = self._own_gdn_params(li)
         ctx = self._ctx
         layer = self._lin_of[li]
         proj = ops.linear(h, self.p.linears[pre + "in_proj_qkvz"]).float()
         mixed, z = proj[:, : self.conv_dim], proj[:, self.conv_dim:]
-        ba = h.float() @ tp[pre + "in_proj_ba.weight"].float().t()
+        ba = h.float() @ own["ba"].float().t()
         beta = torch.sigmoid(ba[:, : self.nv])
-        g = -tp[pre + "A_log"].exp() * F.softplus(ba[:, self.nv:] + tp[pre + "dt_bias"])
-        w = tp[pre + "conv1d.weight"]                                    # [conv_dim, K]
+        g = -own["A_log"].exp() * F.softplus(ba[:, self.nv:] + own["dt_bias"])
+        w = own["conv"]                                                  # [conv_dim, K]
         slots = ctx["slots"]
         conv_all = self.conv_state[layer]
         rec_all = self.rec_state[layer]

@@ -768,6 +768,13 @@ def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
         segs = [full_rows // 2, full_rows // 2]
     elif name.endswith("mlp.up_proj"):
         segs = [full_rows]
+    elif cfg.extra.get("gdn") and name.endswith("linear_attn.in_proj_qkvz"):
+        # gated delta-rule mixer: key heads and value heads are split over the ranks together
+        g = cfg.extra["gdn"]
+        kd, vd = g["num_key_heads"] * g["key_head_dim"], g["num_value_heads"] * g["value_head_dim"]
+        segs = [kd, kd, vd, vd]
+    elif name.endswith("self_attn.gate_proj"):
+        segs = [full_rows]  # output gate of the attention heads: split like the heads
     elif cfg.extra.get("rwkv") and name.endswith(("attention.receptance", "attention.key", "attention.value",
                                                    "attention.gate", "feed_forward.key")):
         # recurrent models: a rank keeps whole heads of the time-mix projections and a slice of the channel-mix
@@ -788,5 +795,5 @@ def shard_rows(name: str, cfg: ModelConfig, tp: int, rank: int, full_rows: int):
 
 
 def column_sharded(name: str) -> bool:
-    return name.endswith(("self_attn.o_proj", "down_proj")) or (
+    return name.endswith(("self_attn.o_proj", "down_proj", "linear_attn.out_proj")) or (
         name.startswith("model.blocks.") and name.endswith(("attention.output", "feed_forward.value")))  # RWKV

@@ -324,9 +324,10 @@ class EngineRuntime:
             elif mcfg.extra.get("gdn"):
                 from ..models.qwen35 import Qwen35Model  # pylint: disable=import-outside-toplevel
 
-                if tp > 1 or pp > 1 or len(self.models_info) > 1:
-                    raise ValueError("hybrid recurrent-state models run on one GPU, without a draft model")
-                model = Qwen35Model(mcfg, quant, store, self.device, None, layers)
+                if pp > 1 or len(self.models_info) > 1:
+                    raise ValueError("hybrid recurrent-state models run without pipeline stages and without a "
+                                     "draft model")
+                model = Qwen35Model(mcfg, quant, store, self.device, comm if tp > 1 else None, layers)
                 cfg.prefix_cache_mode = "disable"  # the recurrent half of the state cannot be shared or rolled back
                 cfg.kv_state_kind = "hybrid"
             else:

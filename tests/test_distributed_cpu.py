@@ -63,10 +63,13 @@ def test_pp2_micro_batches_match_single_rank():
     assert flags["pp_microbatch_steps"] >= 1
 
 
-@pytest.mark.parametrize("model", ["random://tiny-rwkv5?quant=q0f32&seed=5", "random://tiny-rwkv6?quant=q0f32&seed=5"])
+@pytest.mark.parametrize("model", ["random://tiny-rwkv5?quant=q0f32&seed=5", "random://tiny-rwkv6?quant=q0f32&seed=5",
+                                   "random://tiny-qwen35?quant=q0f32&seed=5"])
 def test_tp2_recurrent_model_matches_single_rank(model):
     """RWKV over two ranks: whole heads of the time-mix block (projections, decay, bonus, group norm, matrix
-    state) and half the channel-mix width per rank; the workers find a sequence's state by the broadcast ids."""
+    state) and half the channel-mix width per rank; the workers find a sequence's state by the broadcast ids.
+    Qwen3.5: key and value heads of the gated delta-rule layers (projection rows, convolution channels, decay
+    parameters, state) and the gated attention heads are split the same way."""
     single = _run(1, model, port=29549)
     tp2 = _run(2, model, port=29550)
     assert single == tp2
