@@ -1366,7 +1366,7 @@ class EngineImpl : public Engine {
     const int k = DraftLengthFor(static_cast<int>(ready.size()));
     if (k == 0) return StepDecode();
     int64_t max_nodes = k;  // chain; a tree of width w has w + w^2 + ... + w^k nodes
-    if (!feature_fed_draft_ && cfg_.spec_tree_width > 1) {
+    if (cfg_.spec_tree_width > 1) {
       max_nodes = 0;
       int64_t level = 1;
       for (int d = 0; d < k; ++d) {
@@ -1388,7 +1388,10 @@ class EngineImpl : public Engine {
     // ---- draft phase: k rounds of the small model
     double t0 = NowSeconds();
     TraceBatch(ready, "start draft");
-    const int width = feature_fed_draft_ ? 1 : std::max(1, cfg_.spec_tree_width);
+    // Draft heads fed with the target's features grow trees the same way (reference:
+    // cpp/serve/engine_actions/eagle_batch_draft.cc:38-186): the executor gives every node of an EAGLE tree its
+    // parent's predicted feature, and every leaf of a Medusa tree the distribution of the head of its depth.
+    const int width = std::max(1, cfg_.spec_tree_width);
     // speculative entries each sequence leaves in the draft model's KV (dropped after verification)
     std::vector<int64_t> spec_kv(ready.size(), k - 1);
     if (width > 1) DraftTree(ready, k, width, &spec_kv);

@@ -146,6 +146,9 @@ class FeatureStore:
     def __init__(self):
         self.rows: "collections.OrderedDict[int, tuple]" = collections.OrderedDict()
         self.pred: Dict[int, tuple] = {}
+        # draft trees: the head's outputs for every node of the tree it was last fed (row j = node j); a node
+        # of the next, larger tree continues from its parent's row
+        self.tree: Dict[int, torch.Tensor] = {}
 
     def put(self, seq: int, start: int, feats: torch.Tensor) -> None:
         """Rows for positions ``start ..``; anything stored from ``start`` on is replaced."""
@@ -161,9 +164,11 @@ class FeatureStore:
             feats = feats[-self.CAP_ROWS:]
         self.rows[seq] = (start, feats)
         self.pred.pop(seq, None)
+        self.tree.pop(seq, None)
         while len(self.rows) > self.CAP_SEQS:
             old, _ = self.rows.popitem(last=False)
             self.pred.pop(old, None)
+            self.tree.pop(old, None)
 
     def end(self, seq: int) -> int:
         """One past the last position whose true feature is known (0: none)."""
@@ -185,6 +190,7 @@ class FeatureStore:
     def clear(self) -> None:
         self.rows.clear()
         self.pred.clear()
+        self.tree.clear()
 
 
 class StagingBuffer:
@@ -846,6 +852,11 @@ class ModelExecutor:
             for j in sorted(set(which.tolist())):
                 sel = torch.as_tensor(np.nonzero(which == j)[0], dtype=torch.long, device=self.device)
                 logits[sel] = head.medusa_logits(feats.index_select(0, sel), int(j))
+            if n_rows != len(ids):
+                # draft tree: every leaf of a sequence asks for the distribution of the same head (a Medusa
+                # head does not see the drafted tokens), so the sequence's row is repeated for its leaves
+                seq_of_row = dev["q_seq"].index_select(0, dev["s_logit_token_index"].long()).long()
+                logits = logits.index_select(0, seq_of_row)
             return logits
         # ---- EAGLE: token at position p is fused with the feature of position p - 1
         if dev["page_copies"].numel():
@@ -853,9 +864,25 @@ class ModelExecutor:
         x = head.embed(dev["token_ids"])
         prev = torch.zeros(x.shape[0], hsz, dtype=x.dtype, device=self.device)
         all_true = []
+        masks = np.asarray(plan["tree_mask"]).astype(np.uint64) if len(plan["tree_mask"]) else None
         for i, sid in enumerate(ids):
             a, b = int(qi[i]), int(qi[i + 1])
             if b <= a:
+                all_true.append(False)
+                continue
+            if masks is not None:
+                # a draft tree fed as one chunk (node j = row a + j, ancestors in its mask): a child of the root
+                # continues from the head's output at the last committed token, any other node from the output
+                # the head gave for its parent when the previous, smaller tree was fed
+                own, old = self.features.pred.get(sid), self.features.tree.get(sid)
+                for j in range(b - a):
+                    below = int(masks[a + j]) & ((1 << j) - 1)
+                    parent = below.bit_length() - 1
+                    if parent < 0:
+                        if own is not None and own[0] == int(pos[a + j]) - 1:
+                            prev[a + j] = own[1].to(x.dtype)
+                    elif old is not None and parent < old.shape[0]:
+                        prev[a + j] = old[parent].to(x.dtype)
                 all_true.append(False)
                 continue
             s0, t = self.features.span(sid)
@@ -877,6 +904,9 @@ class ModelExecutor:
         for i, sid in enumerate(ids):
             a, b = int(qi[i]), int(qi[i + 1])
             if b <= a:
+                continue
+            if masks is not None:
+                self.features.tree[sid] = h[a:b].detach().clone()  # the root's output (pred) stays as it is
                 continue
             if all_true[i]:
                 self.features.trim(sid, int(pos[b - 1]) - 1)

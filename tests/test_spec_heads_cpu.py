@@ -176,3 +176,111 @@ def test_eagle_and_medusa_checkpoints_load_from_huggingface_names(tmp_path):
     mstore = loader.load_hf_params(str(tmp_path / "medusa"), mcfg, Q.get("q0f32"), torch.device("cpu"))
     assert torch.equal(mstore.linears["medusa_head.2.1"].w, msd["medusa_head.2.1.weight"])
     assert torch.equal(mstore.linears["medusa_head.1.0.linear"].bias, msd["medusa_head.1.0.linear.bias"])
+
+
+def _tree_engine(mode, width):
+    kw = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=32,
+              prefix_cache_mode="disable", speculative_mode=mode, spec_draft_length=3, spec_tree_width=width,
+              additional_models=[HEADS[mode]])
+    return SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+
+
+@pytest.mark.parametrize("mode", ["eagle", "medusa"])
+def test_draft_trees_keep_the_greedy_output(mode):
+    """``spec_tree_width = 2``: every round gives each leaf two children (14 nodes after three rounds); the
+    verified output is still the plain greedy output."""
+    prompts = _prompts(3, seed=3)
+    _, want = _engine().generate(prompts, GREEDY)
+    eng = _tree_engine(mode, 2)
+    _, got = eng.generate(prompts, GREEDY)
+    assert [t[0] for t in got] == [t[0] for t in want]
+    import json
+
+    stats = json.loads(eng.debug_stats())
+    assert stats["num_verify_steps"] > 0 and stats["num_running"] == 0
+
+
+def test_medusa_tree_accepts_a_second_choice_that_a_chain_misses():
+    """Heads whose best guess is always wrong and whose second guess is always right: a chain accepts nothing,
+    a tree of width two accepts every level, so it needs far fewer verification steps. Sampling runs at a low
+    temperature rather than at zero: at zero a draft distribution is one-hot and has no second choice."""
+    import json
+
+    prompt = _prompts(1, seed=5)[0]
+    _, plain = _engine().generate([prompt], dict(GREEDY, max_tokens=16))
+    full = prompt + plain[0][0]
+
+    def rigged(eng):
+        head, ex = eng.runtime.models[1], eng.runtime.executor
+        orig = ex._forward_spec_head
+        state = {}
+
+        def spec_head(model_id, plan, dev, n_rows):
+            # the newest committed token's position tells which tokens come next
+            state["last"] = int(np.asarray(plan["positions"])[int(np.asarray(plan["q_indptr"])[1]) - 1])
+            return orig(model_id, plan, dev, n_rows)
+
+        def medusa_logits(feats, which):
+            lg = torch.full((feats.shape[0], head.cfg.vocab_size), -10.0)
+            # called for draft round `which`: the chunk's last token sits `which` levels below the newest
+            # committed token, so the token this head should predict is at position last + 1
+            nxt = state["last"] + 1
+            right = full[nxt] if nxt < len(full) else 0
+            lg[:, (right + 1) % head.cfg.vocab_size] = 5.0   # best guess: wrong
+            lg[:, right] = 4.995                              # second guess: right (0.7 % at this temperature)
+            return lg
+
+        ex._forward_spec_head, head.medusa_logits = spec_head, medusa_logits
+
+    steps = {}
+    for width in (1, 2):
+        eng = _tree_engine("medusa", width)
+        rigged(eng)
+        _, got = eng.generate([prompt], dict(GREEDY, max_tokens=16, temperature=1e-3, seed=7))
+        assert got[0][0][:4] == plain[0][0][:4]  # peaked distributions: sampling follows the arg-max
+        steps[width] = json.loads(eng.debug_stats())["num_verify_steps"]
+    assert steps[2] * 2 <= steps[1], steps
+
+
+def test_eagle_tree_nodes_continue_from_their_parents_output():
+    """In every tree round a node is fused with the head's output for its parent from the round before (children
+    of the root: with the head's output at the last committed token)."""
+    eng = _tree_engine("eagle", 2)
+    head, ex = eng.runtime.models[1], eng.runtime.executor
+    calls = []
+    orig_fuse, orig_forward, orig_spec = head.fuse_embed_hidden, head.forward, ex._forward_spec_head
+
+    def spec_head(model_id, plan, dev, n_rows):
+        calls.append({"mask": [int(m) for m in np.asarray(plan["tree_mask"]).astype(np.uint64).tolist()],
+                      "qi": np.asarray(plan["q_indptr"]).tolist()})
+        return orig_spec(model_id, plan, dev, n_rows)
+
+    def fuse(x, prev):
+        calls[-1]["prev"] = prev.detach().clone()
+        return orig_fuse(x, prev)
+
+    def forward(x, b):
+        h = orig_forward(x, b)
+        calls[-1]["h"] = h.detach().clone()
+        return h
+
+    ex._forward_spec_head, head.fuse_embed_hidden, head.forward = spec_head, fuse, forward
+    eng.generate(_prompts(1, seed=9), dict(GREEDY, max_tokens=6))
+    checked = 0
+    for at in range(1, len(calls)):
+        before, cur = calls[at - 1], calls[at]
+        if not cur["mask"]:
+            continue
+        n = len(cur["mask"])
+        for j, m in enumerate(cur["mask"]):
+            parent = (m & ((1 << j) - 1)).bit_length() - 1
+            if parent < 0:
+                # the newest chain call before this draft phase's tree rounds ended at the last committed token
+                root = next(c for c in reversed(calls[:at]) if not c["mask"])
+                assert torch.equal(cur["prev"][j], root["h"][-1])
+            else:
+                assert before["mask"] and parent < len(before["mask"])
+                assert torch.equal(cur["prev"][j], before["h"][parent])
+            checked += 1
+        assert n in (2, 6)  # levels of two and of two + four nodes are fed
+    assert checked >= 8
