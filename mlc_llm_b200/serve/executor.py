@@ -797,7 +797,15 @@ class ModelExecutor:
         out = {}
         k = int(sp["num_top_logprobs"])
         if k > 0:
-            _, tp, ti = ops.take_probs(probs, None, tokens if tokens.device == probs.device
+            rank = probs
+            if len(sp["prob_slots"]) and float(np.min(sp["temperature"])) < 1e-5:
+                # children of a draft tree are the draft's k best tokens; under greedy sampling the sampling
+                # distribution is one-hot and ranks nothing below the first, so those rows are ranked by the
+                # plain softmax (the stored draft distribution stays the one-hot one: the verifier accepts a
+                # lower-ranked child exactly when the target's arg-max is that token)
+                temp = dev["s_temperature"]
+                rank = ops.softmax_temperature(logits, torch.where(temp < 1e-5, torch.ones_like(temp), temp))
+            _, tp, ti = ops.take_probs(rank, None, tokens if tokens.device == probs.device
                                        else tokens.to(probs.device), k)
             out["top_probs"] = tp.reshape(-1).float().cpu().numpy()
             out["top_tokens"] = ti.reshape(-1).to(torch.int32).cpu().numpy()

@@ -202,8 +202,9 @@ def test_draft_trees_keep_the_greedy_output(mode):
 
 def test_medusa_tree_accepts_a_second_choice_that_a_chain_misses():
     """Heads whose best guess is always wrong and whose second guess is always right: a chain accepts nothing,
-    a tree of width two accepts every level, so it needs far fewer verification steps. Sampling runs at a low
-    temperature rather than at zero: at zero a draft distribution is one-hot and has no second choice."""
+    a tree of width two accepts every level, so it needs far fewer verification steps. Both under greedy
+    sampling (the draft's sampling distribution is one-hot there: children are ranked by the plain softmax) and
+    at a low temperature."""
     import json
 
     prompt = _prompts(1, seed=5)[0]
@@ -232,14 +233,18 @@ def test_medusa_tree_accepts_a_second_choice_that_a_chain_misses():
 
         ex._forward_spec_head, head.medusa_logits = spec_head, medusa_logits
 
-    steps = {}
-    for width in (1, 2):
-        eng = _tree_engine("medusa", width)
-        rigged(eng)
-        _, got = eng.generate([prompt], dict(GREEDY, max_tokens=16, temperature=1e-3, seed=7))
-        assert got[0][0][:4] == plain[0][0][:4]  # peaked distributions: sampling follows the arg-max
-        steps[width] = json.loads(eng.debug_stats())["num_verify_steps"]
-    assert steps[2] * 2 <= steps[1], steps
+    for temperature in (0.0, 1e-3):
+        steps = {}
+        for width in (1, 2):
+            eng = _tree_engine("medusa", width)
+            rigged(eng)
+            _, got = eng.generate([prompt], dict(GREEDY, max_tokens=16, temperature=temperature, seed=7))
+            if temperature == 0.0:
+                assert got[0][0] == plain[0][0]
+            else:
+                assert got[0][0][:4] == plain[0][0][:4]  # peaked distributions: sampling follows the arg-max
+            steps[width] = json.loads(eng.debug_stats())["num_verify_steps"]
+        assert steps[2] * 2 <= steps[1], (temperature, steps)
 
 
 def test_eagle_tree_nodes_continue_from_their_parents_output():
