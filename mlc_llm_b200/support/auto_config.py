@@ -78,7 +78,13 @@ def detect_weight(source: str, config_path: str, source_format: str = "auto") ->
     if source_format == "huggingface-torch" and not has_pt:
         raise ValueError(f"no pytorch_model*.bin under {path}")
     if source_format == "awq":
-        raise ValueError("AWQ checkpoints are not supported by this build")
+        # AutoAWQ checkpoints are safetensors (or torch) files whose linear layers are (qweight, qzeros, scales)
+        # triples: the HuggingFace reader expands them (loader/huggingface_loader.py), so only the container matters
+        if has_st:
+            return path, "huggingface-safetensor"
+        if has_pt:
+            return path, "huggingface-torch"
+        raise ValueError(f"no AWQ weights (*.safetensors or pytorch_model*.bin) under {path}")
     return path, source_format
 
 

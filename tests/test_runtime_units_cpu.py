@@ -600,3 +600,17 @@ def test_split_plan_cuts_a_forward_at_a_sequence_boundary():
     assert sa["logit_token_index"].tolist() == [19, 26] and sb["logit_token_index"].tolist() == [32]
     assert len(sa["temperature"]) == 0 and sb["temperature"].tolist() == [0.0, 0.5, 1.0]
     assert len(pb["page_copies"]) == 0
+
+
+def test_detect_weight_formats(tmp_path):
+    """``--source-format awq`` names the container the AWQ triples sit in; a missing container is an error."""
+    import pytest as _pytest
+
+    from mlc_llm_b200.support.auto_config import detect_weight
+
+    (tmp_path / "config.json").write_text("{}")
+    with _pytest.raises(ValueError):
+        detect_weight(str(tmp_path), str(tmp_path / "config.json"), "awq")
+    (tmp_path / "model.safetensors").write_bytes(b"")
+    assert detect_weight(str(tmp_path), str(tmp_path / "config.json"), "awq") == (str(tmp_path), "huggingface-safetensor")
+    assert detect_weight("auto", str(tmp_path / "config.json"), "auto") == (str(tmp_path), "huggingface-safetensor")
