@@ -11,7 +11,13 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (B200)")
 
 
+_MULTI_RANK_FILES = ("test_distributed_gpu.py", "test_distributed_numerics_gpu.py", "test_disagg_gpu.py")
+
+
 def pytest_collection_modifyitems(config, items):
+    # single-GPU tests first: the multi-rank GPU files spawn process groups of 2 to 8 ranks and take most of the
+    # suite's time, so a stop at the first failure (-x) there should not hide the kernel and model tests
+    items.sort(key=lambda it: 1 if os.path.basename(str(it.fspath)) in _MULTI_RANK_FILES else 0)
     try:
         import torch
 
