@@ -432,7 +432,7 @@ def test_moe_permute_is_the_stable_expert_major_order(tokens, k, e):
 
 
 @pytest.mark.parametrize("quant_name", ["q0f16", "q4f16_1", "q0bf16"])
-@pytest.mark.parametrize("tokens,k", [(256, 2048), (37, 512), (1000, 1024)])
+@pytest.mark.parametrize("tokens,k", [(256, 2048), (37, 512), (1000, 1024), (70, 128)])
 def test_fused_collective_gemm_single_rank(quant_name, tokens, k):
     """World size 1 runs the fused reduce-scatter / all-gather kernels in their degenerate form: the
     pushes go to this GPU's own buffers, so one GPU checks the epilogue addressing, the flags, the
