@@ -26,7 +26,7 @@ class PopenServer:  # pylint: disable=too-many-instance-attributes
                  enable_tracing: bool = False, host: str = "127.0.0.1", port: int = 8082,
                  tensor_parallel_shards: Optional[int] = None, pipeline_parallel_stages: Optional[int] = None,
                  gpu_ids: Optional[List[int]] = None, extra_env: Optional[Dict[str, str]] = None,
-                 api_key: Optional[str] = None) -> None:
+                 api_key: Optional[str] = None, embedding_model: Optional[str] = None) -> None:
         self.model, self.device, self.model_lib, self.mode = model, device, model_lib, mode
         self.engine_config = engine_config
         self.enable_debug, self.enable_tracing = enable_debug, enable_tracing
@@ -36,6 +36,7 @@ class PopenServer:  # pylint: disable=too-many-instance-attributes
         self.gpu_ids = gpu_ids
         self.extra_env = dict(extra_env or {})
         self.api_key = api_key
+        self.embedding_model = embedding_model  # served beside the chat model on /v1/embeddings
         self._proc: Optional[subprocess.Popen] = None
 
     @property
@@ -53,6 +54,8 @@ class PopenServer:  # pylint: disable=too-many-instance-attributes
             cmd.append("--enable-tracing")
         if self.api_key:
             cmd += ["--api-key", self.api_key]
+        if self.embedding_model:
+            cmd += ["--embedding-model", self.embedding_model]
         overrides = []
         if self.engine_config is not None:
             for key, value in dataclasses.asdict(self.engine_config).items():

@@ -83,3 +83,47 @@ def test_contrib_embeddings_wrapper(bert_dir):
         assert small.shape == (3, 16) and np.allclose(np.linalg.norm(small, axis=1), 1.0, atol=1e-4)
     finally:
         emb.terminate()
+
+
+def test_embeddings_over_rest(bert_dir):
+    """``/v1/embeddings`` of a server started with ``--embedding-model``: float and base64 encodings, the
+    ``dimensions`` truncation (re-normalised), token usage; the vectors are those of the engine called directly
+    (reference: ``tests/python/serve/server/test_embedding_server.py``)."""
+    import base64
+    import socket
+    import struct
+
+    import requests
+
+    from mlc_llm_b200.serve.server import PopenServer
+
+    path, _hf, _tok = bert_dir
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    srv = PopenServer("random://tiny-llama?quant=q0f32&seed=3", "cpu", mode="local", port=port, embedding_model=path)
+    srv.start(timeout=240)
+    try:
+        texts = ["hello world", "fast gpus"]
+        r = requests.post(srv.base_url + "/v1/embeddings", json={"model": path, "input": texts}, timeout=60)
+        assert r.status_code == 200, r.text
+        body = r.json()
+        vecs = [np.asarray(d["embedding"], dtype=np.float32) for d in body["data"]]
+        assert [d["index"] for d in body["data"]] == [0, 1] and body["usage"]["prompt_tokens"] > 0
+        eng = AsyncEmbeddingEngine(path, device="cpu")
+        want, n_tok = asyncio.run(eng.async_embed(texts))
+        assert body["usage"]["prompt_tokens"] == n_tok
+        for got, ref in zip(vecs, want):
+            assert np.allclose(got, np.asarray(ref, dtype=np.float32), atol=1e-5)
+            assert abs(float(np.linalg.norm(got)) - 1.0) < 1e-4
+        r = requests.post(srv.base_url + "/v1/embeddings",
+                          json={"model": path, "input": "hello world", "encoding_format": "base64", "dimensions": 16},
+                          timeout=60)
+        assert r.status_code == 200, r.text
+        raw = base64.b64decode(r.json()["data"][0]["embedding"])
+        short = np.asarray(struct.unpack(f"<{len(raw) // 4}f", raw), dtype=np.float32)
+        assert short.shape == (16,) and abs(float(np.linalg.norm(short)) - 1.0) < 1e-4
+        head = vecs[0][:16] / np.linalg.norm(vecs[0][:16])
+        assert np.allclose(short, head, atol=1e-5)
+    finally:
+        srv.terminate()
