@@ -1111,6 +1111,10 @@ class ModelExecutor:
             return
         from ..ops._lib import check, lib, ptr, status_word, stream_ptr  # pylint: disable=import-outside-toplevel
 
+        if src.shape[2] != 2:
+            # the slot-copy kernel addresses pages as [K | V] x heads; the compressed latent cache has one row
+            raise kv_handoff.HandoffError("the compressed latent cache (mla_cache=latent) cannot be handed off "
+                                          "between GPU engines; use the expanded cache on disaggregated endpoints")
         if pool_desc["device"] != src.device.index and dst is not None:
             rc = lib().mlcb_enable_peer_access(ctypes.c_int(src.device.index), ctypes.c_int(pool_desc["device"]))
             check(rc, f"peer access from GPU {src.device.index} to GPU {pool_desc['device']}")
