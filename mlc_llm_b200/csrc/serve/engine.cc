@@ -688,7 +688,10 @@ class EngineImpl : public Engine {
     } else {
       for (auto& kv : kv_) kv->AddSequence(id);
     }
-    if (cfg_.sliding_window_size > 0 && e.child_indices.empty())
+    // every sequence is windowed, parents of parallel samples too: the window is part of what a token sees
+    // (a mask), and pages that fall out of it are reference-counted, so sharing them with forks is safe;
+    // forked children inherit the window (KVManager::ForkSequence)
+    if (cfg_.sliding_window_size > 0)
       for (auto& kv : kv_)
         kv->EnableSlidingWindow(id, static_cast<int32_t>(cfg_.sliding_window_size),
                                 static_cast<int32_t>(std::max<int64_t>(0, cfg_.attention_sink_size)));

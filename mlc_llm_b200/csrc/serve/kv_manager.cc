@@ -58,14 +58,21 @@ void KVManager::ForkSequence(int64_t parent_id, int64_t child_id, int64_t fork_p
   const Seq& parent = Get(parent_id);
   if (fork_pos < 0) fork_pos = parent.len;
   if (fork_pos > parent.len) throw std::runtime_error("KVManager: fork position beyond parent");
-  if (parent.window > 0 && parent.dropped_until > 0)
-    throw std::runtime_error("KVManager: cannot fork a sequence whose window already dropped pages");
+  // A windowed parent may have let pages go. The child inherits the window, and its first new token (position
+  // fork_pos) sees positions from fork_pos + 1 - window on: the fork is sound when nothing dropped lies there.
+  if (parent.window > 0 && parent.dropped_until > 0 &&
+      std::max<int64_t>(fork_pos + 1 - parent.window, parent.sink) < parent.dropped_until)
+    throw std::runtime_error("KVManager: cannot fork a sequence below what its window already dropped");
   Seq child;
+  child.window = parent.window;
+  child.sink = parent.sink;
+  child.dropped_until = parent.window > 0 ? std::min<int64_t>(parent.dropped_until, fork_pos / page_size_ * page_size_) : 0;
   const int64_t full = fork_pos / page_size_;
   const int64_t rem = fork_pos % page_size_;
   if (rem != 0 && free_pages_.empty()) throw std::runtime_error("KVManager: out of KV pages");
   child.pages.assign(parent.pages.begin(), parent.pages.begin() + full);
-  for (int32_t p : child.pages) ++refcnt_[p];
+  for (int32_t p : child.pages)
+    if (p >= 0) ++refcnt_[p];  // -1: a page the window dropped
   if (rem != 0) {
     int32_t np = AllocPage();
     pending_copies_.push_back(parent.pages[full]);

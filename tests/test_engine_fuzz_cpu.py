@@ -31,14 +31,16 @@ def _workload(seed, count=12, gen=(2, 14)):
 _ALONE = {}
 
 
-def _alone(prompt, max_tokens):
-    key = (tuple(prompt), max_tokens)
+def _alone(prompt, max_tokens, window=()):
+    """Greedy tokens of one prompt on an engine of its own (``window``: the sliding-window settings, which change
+    what a token sees and so belong to the oracle too)."""
+    key = (tuple(prompt), max_tokens, window)
     if key not in _ALONE:
-        if "eng" not in _ALONE:
-            _ALONE["eng"] = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(
+        if ("eng", window) not in _ALONE:
+            _ALONE[("eng", window)] = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(
                 mode="server", max_num_sequence=4, max_total_sequence_length=2048, prefill_chunk_size=256,
-                prefix_cache_mode="disable"))
-        _, toks = _ALONE["eng"].generate([prompt], dict(GREEDY, max_tokens=max_tokens))
+                prefix_cache_mode="disable", **dict(window)))
+        _, toks = _ALONE[("eng", window)].generate([prompt], dict(GREEDY, max_tokens=max_tokens))
         _ALONE[key] = toks[0][0]
     return _ALONE[key]
 
@@ -52,6 +54,15 @@ CONFIGS = {
     "preempting_radix_draft": dict(max_num_sequence=6, max_total_sequence_length=160, prefill_chunk_size=32,
                                    prefix_cache_mode="radix", speculative_mode="small_draft", spec_draft_length=2,
                                    additional_models=[DRAFT], _gen=(80, 140)),
+    # a window of 40 positions behind 4 sink positions: pages fall out of the window while sequences run
+    "window_sink": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=32,
+                        prefix_cache_mode="disable", sliding_window_size=40, attention_sink_size=4, _gen=(20, 60)),
+    "eagle_tree_radix": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=48,
+                             prefix_cache_mode="radix", speculative_mode="eagle", spec_draft_length=2,
+                             spec_tree_width=2, additional_models=["random://tiny-eagle?quant=q0f32&seed=3"]),
+    "medusa_tight": dict(max_num_sequence=4, max_total_sequence_length=400, prefill_chunk_size=32,
+                         prefix_cache_mode="disable", speculative_mode="medusa", spec_draft_length=3,
+                         additional_models=["random://tiny-medusa?quant=q0f32&seed=4"]),
     "hybrid_prefill": dict(max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=48,
                            prefix_cache_mode="radix", prefill_mode="hybrid"),
     "draft_tree_radix": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=64,
@@ -102,9 +113,10 @@ def test_random_schedules_keep_every_request_exact(name, seed):
         step += 1
         assert step < 3000, "the engine does not drain"
     limit = int(eng.engine_config.max_single_sequence_length)
+    window = tuple((k, cfg[k]) for k in ("sliding_window_size", "attention_sink_size") if k in cfg)
     for r in reqs:
         # a sequence ends with "length" at the engine's single-sequence limit as well as at max_tokens
-        want = _alone(r["prompt"], r["max_tokens"])[: max(0, limit - len(r["prompt"]))]
+        want = _alone(r["prompt"], r["max_tokens"], window)[: max(0, limit - len(r["prompt"]))]
         for j in range(r["n"]):
             have = got.get((r["id"], j), [])
             if r["id"] in aborted and (r["id"], j) not in finished:

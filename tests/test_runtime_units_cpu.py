@@ -109,6 +109,39 @@ def test_kv_manager_window_keeps_what_the_first_token_of_a_chunk_sees():
     assert all(p < 0 for p in pages[:6]) and all(p >= 0 for p in pages[6:])
 
 
+def test_kv_manager_forks_of_a_windowed_sequence_inherit_the_window():
+    """Parallel samples of a windowed sequence: the child shares the live pages (reference counts), carries the
+    holes of the dropped ones, keeps the window for its own tokens, and both can be removed in any order. A fork
+    at a position whose window reaches into dropped pages is refused."""
+    import pytest as _pytest
+
+    kv = _core.KVManager(64, 16, 8)
+    kv.add_sequence(0)
+    kv.enable_sliding_window(0, 32, 0)
+    kv.begin_forward([0], [100])
+    kv.begin_forward([0], [1])                   # position 100 sees 69..100: pages 0..3 (positions 0..63) are gone
+    parent_pages = kv.sequence_pages(0)
+    assert all(p < 0 for p in parent_pages[:4]) and all(p >= 0 for p in parent_pages[4:])
+    free_before = kv.num_available_pages()
+    kv.fork_sequence(0, 1, -1)
+    child_pages = kv.sequence_pages(1)
+    assert child_pages[:6] == parent_pages[:6] and child_pages[6] != parent_pages[6]   # last partial page copied
+    assert kv.num_available_pages() == free_before - 1
+    plan = kv.begin_forward([1], [1])            # the child's token at position 101 sees 70..101
+    assert int(plan["q_kvstart"][0]) == 70
+    for _ in range(40):
+        kv.begin_forward([1], [1])
+    assert all(p < 0 for p in kv.sequence_pages(1)[:6])          # the child's window moved on by itself
+    assert all(p >= 0 for p in kv.sequence_pages(0)[4:])         # the parent still holds what it sees
+    with _pytest.raises(RuntimeError):
+        kv.fork_sequence(0, 2, 80)               # a token at position 80 would see 49..80: page 3 is gone
+    kv.fork_sequence(0, 3, 96)                   # position 96 sees 65..96: all there
+    kv.remove_sequence(0)
+    kv.remove_sequence(1)
+    kv.remove_sequence(3)
+    assert kv.num_available_pages() == 64
+
+
 # ------------------------------------------------------------------ prefix cache
 def test_prefix_cache_reuse_fork_and_recycle():
     removed = []
