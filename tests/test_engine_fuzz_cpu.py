@@ -57,6 +57,13 @@ CONFIGS = {
     # a window of 40 positions behind 4 sink positions: pages fall out of the window while sequences run
     "window_sink": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=32,
                         prefix_cache_mode="disable", sliding_window_size=40, attention_sink_size=4, _gen=(20, 60)),
+    "window_radix_draft": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=32,
+                               prefix_cache_mode="radix", sliding_window_size=40, attention_sink_size=4,
+                               speculative_mode="small_draft", spec_draft_length=2, additional_models=[DRAFT],
+                               _gen=(20, 60)),
+    "window_tight": dict(max_num_sequence=6, max_total_sequence_length=160, prefill_chunk_size=32,
+                         prefix_cache_mode="disable", sliding_window_size=48, attention_sink_size=0,
+                         _gen=(60, 110)),
     "eagle_tree_radix": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=48,
                              prefix_cache_mode="radix", speculative_mode="eagle", spec_draft_length=2,
                              spec_tree_width=2, additional_models=["random://tiny-eagle?quant=q0f32&seed=3"]),
