@@ -140,3 +140,33 @@ def test_random_schedules_keep_every_request_exact(name, seed):
         assert stats["kv_total_sequence_length"] == 0
     eng.reset()
     assert json.loads(eng.debug_stats())["kv_total_sequence_length"] == 0
+
+
+@pytest.mark.parametrize("recycling", [1, 8])
+@pytest.mark.parametrize("draft", [False, True])
+def test_multi_round_conversations_reuse_their_own_history(recycling, draft):
+    """Four interleaved conversations of three rounds: a round's prompt is the previous prompt, the previous answer
+    and new tokens, so the radix cache can continue the finished sequence (or, once recycled away, cannot). With
+    room for one or for eight recycled sequences, with and without a draft model, answers equal the uncached ones
+    and hits show up as prefill tokens saved."""
+    rng = np.random.default_rng(4)
+    kw = dict(max_num_sequence=6, max_total_sequence_length=2048, prefill_chunk_size=48, prefix_cache_mode="radix",
+              prefix_cache_max_num_recycling_seqs=recycling)
+    if draft:
+        kw.update(speculative_mode="small_draft", spec_draft_length=2, additional_models=[DRAFT])
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(mode="server", **kw))
+    convs = [rng.integers(10, 31000, int(n)).tolist() for n in (30, 12, 55, 21)]
+    fed = 0
+    for rnd in range(3):
+        prompts = [list(c) for c in convs]
+        _, toks = eng.generate(prompts, dict(GREEDY, max_tokens=9))
+        fed += sum(len(p) for p in prompts)
+        for i, c in enumerate(convs):
+            assert toks[i][0] == _alone(prompts[i], 9), (rnd, i)
+            convs[i] = c + toks[i][0] + rng.integers(10, 31000, int(rng.integers(2, 9))).tolist()
+    m = eng.metrics()
+    prefilled = int(m.get("prefill_tokens_sum", m.get("sum_engine_prefill_tokens", -1)))
+    if prefilled >= 0:
+        assert prefilled < fed                   # later rounds did not recompute all of their history
+        if recycling == 8:
+            assert prefilled < 0.7 * fed
