@@ -48,6 +48,7 @@ py::dict PlanToDict(const ForwardPlan& p) {
   d["q_kvstart"] = ToArray(p.q_kvstart);
   d["tree_mask"] = ToArray(p.tree_mask);
   d["page_copies"] = ToArray(p.page_copies);
+  d["seq_forks"] = ToArray(p.seq_forks);
   d["max_append"] = p.max_append;
   d["max_seq_len"] = p.max_seq_len;
   return d;

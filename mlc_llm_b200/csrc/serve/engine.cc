@@ -1065,6 +1065,7 @@ class EngineImpl : public Engine {
       if (!launched) {
         // the backend cannot defer this step: undo the plan, settle, and stay on the ordinary path
         for (int64_t id : seq_ids) kv_[0]->PopN(id, 1);
+        kv_[0]->RequeuePlanSideEffects(plan);  // copy-on-write page copies and forks ride on the next plan
         FinishInflightDecode();
         pipelined_decode_ = false;
         return true;

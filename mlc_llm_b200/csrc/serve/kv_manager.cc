@@ -13,6 +13,7 @@ KVManager::KVManager(int64_t num_pages, int page_size, int64_t max_num_sequence)
 void KVManager::Clear() {
   seqs_.clear();
   pending_copies_.clear();
+  pending_forks_.clear();
   total_len_ = 0;
   refcnt_.assign(static_cast<size_t>(num_pages_), 0);
   free_pages_.clear();
@@ -82,6 +83,13 @@ void KVManager::ForkSequence(int64_t parent_id, int64_t child_id, int64_t fork_p
   child.len = fork_pos;
   total_len_ += fork_pos;
   seqs_[child_id] = std::move(child);
+  pending_forks_.push_back(parent_id);
+  pending_forks_.push_back(child_id);
+}
+
+void KVManager::RequeuePlanSideEffects(const ForwardPlan& plan) {
+  pending_copies_.insert(pending_copies_.begin(), plan.page_copies.begin(), plan.page_copies.end());
+  pending_forks_.insert(pending_forks_.begin(), plan.seq_forks.begin(), plan.seq_forks.end());
 }
 
 void KVManager::RemoveSequence(int64_t seq_id) {
@@ -162,6 +170,7 @@ ForwardPlan KVManager::BeginForward(const std::vector<int64_t>& seq_ids,
   plan.page_indptr.push_back(0);
   plan.q_indptr.push_back(0);
   plan.page_copies.swap(pending_copies_);
+  plan.seq_forks.swap(pending_forks_);
   bool any_window = false;
   for (int64_t id : seq_ids) any_window |= Get(id).window > 0;
   size_t tree_off = 0;

@@ -36,6 +36,9 @@ struct ForwardPlan {
   std::vector<uint64_t> tree_mask;    // ancestor bit masks (empty unless a token tree is appended)
   // device copies to run before the forward: (src_page, dst_page) pairs
   std::vector<int32_t> page_copies;
+  // (parent id, child id) of every fork since the last plan: models that keep a recurrent state per sequence
+  // copy the parent's state to the child before the forward
+  std::vector<int64_t> seq_forks;
   int32_t max_append = 0;
   int32_t max_seq_len = 0;
 };
@@ -75,6 +78,9 @@ class KVManager {
   int64_t NumSequences() const { return static_cast<int64_t>(seqs_.size()); }
   // Device copies queued by ForkSequence (copy-on-write), drained by the next BeginForward.
   const std::vector<int32_t>& pending_copies() const { return pending_copies_; }
+  // A plan whose forward will not run after all (its appended tokens are popped by the caller): the page copies
+  // and forks it carried still have to reach the model with the next plan.
+  void RequeuePlanSideEffects(const ForwardPlan& plan);
   // Export / import of a sequence's page list (prefill/decode disaggregation).
   std::vector<int32_t> SequencePages(int64_t seq_id) const;
 
@@ -99,6 +105,7 @@ class KVManager {
   std::vector<int32_t> refcnt_;
   std::unordered_map<int64_t, Seq> seqs_;
   std::vector<int32_t> pending_copies_;
+  std::vector<int64_t> pending_forks_;
   int64_t total_len_ = 0;
 };
 

@@ -192,9 +192,21 @@ class Qwen35Model(DecoderModel):
         self.slot_of[seq_id] = slot
         return slot
 
+    def _fork_state(self, parent: int, child: int) -> None:
+        """Parallel samples: the child gets a slot holding a copy of the state its parent reached."""
+        src = self.slot_of.pop(parent, None)
+        if src is None:
+            return
+        self.slot_of[parent] = src  # most recently used: taking a slot for the child must not evict it
+        dst = self._slot(child, 0)
+        self.conv_state[:, dst] = self.conv_state[:, src]
+        self.rec_state[:, dst] = self.rec_state[:, src]
+
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, b: BatchInfo) -> torch.Tensor:
         self._ensure_state()
+        for parent, child in np.asarray(getattr(b, "seq_forks", ())).reshape(-1, 2).tolist():
+            self._fork_state(int(parent), int(child))
         qi = np.asarray(b.q_indptr)
         ids = [int(s) for s in np.asarray(b.seq_ids).tolist()]
         pos0 = np.asarray(b.start_positions)

@@ -167,6 +167,11 @@ class RwkvModel(DecoderModel):
         ids = [int(s) for s in np.asarray(b.seq_ids).tolist()]
         pos0 = np.asarray(b.start_positions)
         live = [i for i in range(len(ids)) if qi[i + 1] > qi[i]]
+        for parent, child in np.asarray(getattr(b, "seq_forks", ())).reshape(-1, 2).tolist():
+            # parallel samples: the child continues from a copy of the state its parent reached
+            st = self.states.get(int(parent))
+            if st is not None:
+                self.states[int(child)] = {k: v.clone() for k, v in st.items()}
         states = {i: self._state_of(ids[i], int(pos0[i])) for i in live}
         firsts = torch.as_tensor([int(qi[i]) for i in live], dtype=torch.long, device=x.device)
         lasts = torch.as_tensor([int(qi[i + 1]) - 1 for i in live], dtype=torch.long, device=x.device)

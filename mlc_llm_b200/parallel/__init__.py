@@ -235,7 +235,7 @@ _ARRAY_NAMES = ["token_ids", "positions", "slots", "q_seq", "q_kvlen", "q_kvstar
                 "s_logit_token_index", "s_top_k", "s_pen_row", "s_pen_token", "s_pen_count", "s_bias_row",
                 "s_bias_token", "s_mask_rows", "s_mask_bits", "s_prob_slots", "s_temperature", "s_top_p",
                 "s_uniform", "s_penalties", "s_bias_value", "tile_seq", "tile_qstart", "tile_ntok", "dec_seq", "dec_qstart",
-                "dec_ntok", "token_src", "seq_ids"]
+                "dec_ntok", "token_src", "seq_ids", "seq_forks"]
 _NAME_ID = {n: i for i, n in enumerate(_ARRAY_NAMES)}
 _ID_NAME = dict(enumerate(_ARRAY_NAMES))
 

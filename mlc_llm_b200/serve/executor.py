@@ -350,6 +350,7 @@ class ModelExecutor:
             qi = np.asarray(plan["q_indptr"])
             pos = np.asarray(plan["positions"])
             b.seq_ids = np.asarray(plan["seq_ids"])
+            b.seq_forks = np.asarray(plan.get("seq_forks", ()), dtype=np.int64).reshape(-1, 2)
             b.q_indptr = qi
             b.start_positions = np.asarray([int(pos[qi[i]]) if qi[i + 1] > qi[i] else 0
                                             for i in range(len(qi) - 1)])
@@ -388,6 +389,7 @@ class ModelExecutor:
         if getattr(model, "stateful", False):
             # recurrent models pick their state by sequence id: the other ranks need the ids too
             arrays["seq_ids"] = np.ascontiguousarray(plan["seq_ids"], dtype=np.int32)
+            arrays["seq_forks"] = np.ascontiguousarray(plan.get("seq_forks", ()), dtype=np.int32)
         if self._pads_decode(model_id, arrays):
             pad_decode_arrays(arrays, graph_bucket(int(arrays["q_indptr"].size) - 1))
         if self._tc_attention_ok(model):
@@ -1143,6 +1145,7 @@ class ModelExecutor:
         plan["max_seq_len"] = int(arrays["seq_lens"].max()) if arrays["seq_lens"].size else 0
         if "seq_ids" in arrays:
             plan["seq_ids"] = arrays["seq_ids"]
+            plan["seq_forks"] = arrays.get("seq_forks", np.zeros(0, dtype=np.int32))
         if op == "forward_async":
             # deferred-read decode step: inputs may be the tokens rank 0 sampled in the step before, and
             # this step's tokens arrive the same way (device to device) once rank 0 has sampled them

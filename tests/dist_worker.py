@@ -78,7 +78,11 @@ def main():
             lw.w[:, zr * k // zw:(zr + 1) * k // zw] = 0
             lw._dense = None
     try:
-        _, toks = eng.generate(prompts, {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}})
+        gen = {"max_tokens": 8, "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+        samples = int(os.environ.get("MLCB_TEST_N", "1"))
+        if samples > 1:
+            gen["n"] = samples  # parallel samples: forks with copy-on-write of the last partial page
+        _, toks = eng.generate(prompts, gen)
     except Exception as err:  # pylint: disable=broad-except
         if not exit_after:
             raise
@@ -94,7 +98,7 @@ def main():
                                  "num_verify_steps": int(json.loads(eng.debug_stats()).get("num_verify_steps", 0)),
                                  "fused_launches": int(rt.models[0].fused.launches) if getattr(rt.models[0], "fused", None) else 0}),
           flush=True)
-    print("RESULT " + json.dumps([t[0] for t in toks]), flush=True)
+    print("RESULT " + json.dumps([t[0] for t in toks] if samples == 1 else toks), flush=True)
     comm.destroy()
 
 

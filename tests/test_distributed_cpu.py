@@ -51,6 +51,17 @@ def test_pp2_matches_single_rank():
     assert single == pp2
 
 
+def test_pp2_parallel_samples_keep_their_copied_pages():
+    """``n = 2`` over two pipeline stages: the first decode step is offered to the deferred-read path, which a
+    pipeline declines; the copy-on-write page copies of the forks that rode on that discarded plan must reach
+    the model with the next one (prompt lengths 40, 9 and 23 all leave a partial last page)."""
+    model = "random://tiny-llama?quant=q0f32&seed=5"
+    single = _run(1, model, port=29563, extra_env={"MLCB_TEST_N": "2"})
+    pp2 = _run(2, model, port=29564, extra_env={"MLCB_TEST_PP": "2", "MLCB_TEST_N": "2"})
+    assert single == pp2
+    assert all(s[0] == s[1] for s in single)  # greedy samples of one prompt are equal
+
+
 def test_pp2_micro_batches_match_single_rank():
     """The same with prefill steps cut into two micro-batches (the threshold lowered so the short test prompts
     qualify): stage 1 works on the first half while stage 0 computes the second, the last stage returns the

@@ -418,3 +418,29 @@ def test_request_objects_drive_the_step_loop(reference_outputs):
     while not eng.empty():
         eng.step()
     assert [got["r0"], got["r1"]] == want[:2]
+
+
+def test_declined_deferred_step_keeps_the_fork_page_copies():
+    """Parallel samples fork the prompt's sequence; the copy of its last partial page rides on the next plan.
+    When that plan is a deferred-read decode step the backend declines (pipeline stages, draft heads, recurrent
+    models do), the engine pops the step and plans again: the copies must ride on the new plan."""
+    prompt = _prompts(1, lo=40, hi=41, seed=9)[0]       # 40 tokens: two full pages and eight rows of a third
+    _, want = _engine(prefix_cache_mode="disable").generate([prompt], dict(GREEDY, max_tokens=6))
+    eng = _engine(prefix_cache_mode="disable")
+    ex = eng.runtime.executor
+    seen = {"declined": [], "sync": []}
+    orig = ex._forward_sample
+
+    def sync(model_id, plan, token_ids, embed_handles, sp):
+        seen["sync"].append(list(map(int, plan["page_copies"])))
+        return orig(model_id, plan, token_ids, embed_handles, sp)
+
+    def launch(model_id, plan, token_ids, token_src, sp):
+        seen["declined"].append(list(map(int, plan["page_copies"])))
+        return False
+
+    ex._forward_sample, ex.forward_sample_launch = sync, launch
+    _, got = eng.generate([prompt], dict(GREEDY, max_tokens=6, n=2))
+    assert got[0] == [want[0][0], want[0][0]]
+    assert len(seen["declined"]) == 1 and len(seen["declined"][0]) == 4     # two (source, destination) pairs
+    assert seen["declined"][0] in seen["sync"]

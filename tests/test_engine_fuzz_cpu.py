@@ -31,15 +31,16 @@ def _workload(seed, count=12, gen=(2, 14)):
 _ALONE = {}
 
 
-def _alone(prompt, max_tokens, window=()):
+def _alone(prompt, max_tokens, window=(), model=MODEL):
     """Greedy tokens of one prompt on an engine of its own (``window``: the sliding-window settings, which change
     what a token sees and so belong to the oracle too)."""
-    key = (tuple(prompt), max_tokens, window)
+    key = (tuple(prompt), max_tokens, window, model)
+    window = window + (("_model", model),) if model != MODEL else window
     if key not in _ALONE:
         if ("eng", window) not in _ALONE:
-            _ALONE[("eng", window)] = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(
+            _ALONE[("eng", window)] = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(
                 mode="server", max_num_sequence=4, max_total_sequence_length=2048, prefill_chunk_size=256,
-                prefix_cache_mode="disable", **dict(window)))
+                prefix_cache_mode="disable", **{k: v for k, v in window if k != "_model"}))
         _, toks = _ALONE[("eng", window)].generate([prompt], dict(GREEDY, max_tokens=max_tokens))
         _ALONE[key] = toks[0][0]
     return _ALONE[key]
@@ -70,6 +71,11 @@ CONFIGS = {
     "medusa_tight": dict(max_num_sequence=4, max_total_sequence_length=400, prefill_chunk_size=32,
                          prefix_cache_mode="disable", speculative_mode="medusa", spec_draft_length=3,
                          additional_models=["random://tiny-medusa?quant=q0f32&seed=4"]),
+    # recurrent-state families: a sequence's state is found by its id, a preempted sequence starts over
+    "rwkv6_tight": dict(_model="random://tiny-rwkv6?quant=q0f32&seed=5", max_num_sequence=4,
+                        max_total_sequence_length=1024, prefill_chunk_size=32),
+    "qwen35_hybrid_state": dict(_model="random://tiny-qwen35?quant=q0f32&seed=5", max_num_sequence=5,
+                                max_total_sequence_length=1024, prefill_chunk_size=32, _gen=(4, 30)),
     "hybrid_prefill": dict(max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=48,
                            prefix_cache_mode="radix", prefill_mode="hybrid"),
     "draft_tree_radix": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=64,
@@ -98,7 +104,8 @@ def test_random_schedules_keep_every_request_exact(name, seed):
 
     cfg = dict(CONFIGS[name])
     gen = cfg.pop("_gen", (2, 14))
-    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(mode="server", **cfg),
+    model = cfg.pop("_model", MODEL)
+    eng = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(mode="server", **cfg),
                         request_stream_callback=on_outputs)
     reqs = _workload(seed, gen=gen)
     pending = sorted(reqs, key=lambda r: r["arrive"])
@@ -123,7 +130,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
     window = tuple((k, cfg[k]) for k in ("sliding_window_size", "attention_sink_size") if k in cfg)
     for r in reqs:
         # a sequence ends with "length" at the engine's single-sequence limit as well as at max_tokens
-        want = _alone(r["prompt"], r["max_tokens"], window)[: max(0, limit - len(r["prompt"]))]
+        want = _alone(r["prompt"], r["max_tokens"], window, model)[: max(0, limit - len(r["prompt"]))]
         for j in range(r["n"]):
             have = got.get((r["id"], j), [])
             if r["id"] in aborted and (r["id"], j) not in finished:
@@ -136,7 +143,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
     if name.startswith("preempting") and seed == 0:
         assert stats["num_preemptions"] >= 1  # this schedule is known to outgrow the pool
     # sequences are gone: what is still allocated belongs to prefix-cache entries kept for reuse
-    if CONFIGS[name]["prefix_cache_mode"] == "disable":
+    if CONFIGS[name].get("prefix_cache_mode") == "disable":
         assert stats["kv_total_sequence_length"] == 0
     eng.reset()
     assert json.loads(eng.debug_stats())["kv_total_sequence_length"] == 0
