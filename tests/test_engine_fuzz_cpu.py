@@ -76,6 +76,8 @@ CONFIGS = {
                         max_total_sequence_length=1024, prefill_chunk_size=32),
     "qwen35_hybrid_state": dict(_model="random://tiny-qwen35?quant=q0f32&seed=5", max_num_sequence=5,
                                 max_total_sequence_length=1024, prefill_chunk_size=32, _gen=(4, 30)),
+    "qwen35_tight": dict(_model="random://tiny-qwen35?quant=q0f32&seed=5", max_num_sequence=6,
+                         max_total_sequence_length=160, prefill_chunk_size=32, _gen=(60, 110)),
     "hybrid_prefill": dict(max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=48,
                            prefix_cache_mode="radix", prefill_mode="hybrid"),
     "draft_tree_radix": dict(max_num_sequence=6, max_total_sequence_length=1024, prefill_chunk_size=64,
@@ -177,3 +179,20 @@ def test_multi_round_conversations_reuse_their_own_history(recycling, draft):
         assert prefilled < fed                   # later rounds did not recompute all of their history
         if recycling == 8:
             assert prefilled < 0.7 * fed
+
+
+def test_preempted_hybrid_state_sequences_start_over():
+    """Qwen3.5 (paged attention layers beside a recurrent state) in a pool its sequences outgrow: a preempted
+    sequence is prefilled again from position 0, which must also reset its recurrent state."""
+    model = "random://tiny-qwen35?quant=q0f32&seed=5"
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(10, 31000, int(rng.integers(20, 60))).tolist() for _ in range(6)]
+    gen = dict(GREEDY, max_tokens=120)
+    roomy = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(
+        mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64))
+    _, want = roomy.generate(prompts, gen)
+    tight = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(
+        mode="server", max_num_sequence=6, max_total_sequence_length=224, prefill_chunk_size=64))
+    _, got = tight.generate(prompts, gen)
+    assert [t[0] for t in got] == [t[0] for t in want]
+    assert json.loads(tight.debug_stats())["num_preemptions"] >= 1
