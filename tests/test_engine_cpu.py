@@ -444,3 +444,49 @@ def test_declined_deferred_step_keeps_the_fork_page_copies():
     assert got[0] == [want[0][0], want[0][0]]
     assert len(seen["declined"]) == 1 and len(seen["declined"][0]) == 4     # two (source, destination) pairs
     assert seen["declined"][0] in seen["sync"]
+
+
+def test_concurrent_disaggregated_hand_offs_and_plain_requests():
+    """Four client threads drive eight requests against one prefill and one decode engine: six go through
+    prepare_receive / remote_send / start_generation (half of them share a 48-token stem, so the decode side's
+    prefix cache shortens what is sent), two are ordinary requests to the decode engine in between. Every text
+    equals the plain engine's."""
+    import concurrent.futures as cf
+
+    from mlc_llm_b200.serve.entrypoints.microserving_entrypoints import prep_recv_response
+
+    cfg = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64)
+    plain = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    p_eng = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    d_eng = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**cfg))
+    rng = np.random.default_rng(5)
+    stem = rng.integers(10, 31000, 48).tolist()
+    prompts = [(stem if i % 2 else []) + rng.integers(10, 31000, int(rng.integers(5, 70))).tolist() for i in range(8)]
+    greedy = dict(max_tokens=10, temperature=0.0)
+
+    def run(i):
+        prompt, rid = prompts[i], f"dis-{i}"
+        if i % 4 == 3:
+            return d_eng.completions.create(prompt=prompt, debug_config={"ignore_eos": True}, **greedy).choices[0].text
+        prep = d_eng.completions.create(prompt=prompt, max_tokens=1, request_id=rid, debug_config={
+            "disagg_config": {"kind": "prepare_receive", "kv_window_begin": 0, "kv_window_end": -1}})
+        meta = prep_recv_response(d_eng, prep)
+        end = len(prompt) - 1
+        if meta.prefix_matched_length < end:
+            p_eng.completions.create(prompt=prompt, max_tokens=1, request_id=rid, debug_config={
+                "disagg_config": {"kind": "remote_send", "kv_window_begin": meta.prefix_matched_length,
+                                  "kv_window_end": end, "kv_append_metadata": meta.kv_append_metadata,
+                                  "dst_group_offset": 0}})
+        out = d_eng.completions.create(prompt=prompt, request_id=rid, debug_config={
+            "ignore_eos": True, "disagg_config": {"kind": "start_generation", "kv_window_begin": end}}, **greedy)
+        return out.choices[0].text
+
+    try:
+        want = [plain.completions.create(prompt=p, debug_config={"ignore_eos": True}, **greedy).choices[0].text
+                for p in prompts]
+        with cf.ThreadPoolExecutor(4) as pool:
+            got = list(pool.map(run, range(len(prompts))))
+        assert got == want
+    finally:
+        for e in (plain, p_eng, d_eng):
+            e.terminate()
