@@ -76,6 +76,10 @@ CONFIGS = {
                         max_total_sequence_length=1024, prefill_chunk_size=32),
     "qwen35_hybrid_state": dict(_model="random://tiny-qwen35?quant=q0f32&seed=5", max_num_sequence=5,
                                 max_total_sequence_length=1024, prefill_chunk_size=32, _gen=(4, 30)),
+    # compressed latent cache (one row per token for all heads) against the expanded-cache oracle
+    "deepseek_latent_radix": dict(_model="random://tiny-deepseek-v2?quant=q0f32&seed=5&mla_cache=latent",
+                                  _oracle="random://tiny-deepseek-v2?quant=q0f32&seed=5", max_num_sequence=6,
+                                  max_total_sequence_length=400, prefill_chunk_size=32, prefix_cache_mode="radix"),
     "qwen35_tight": dict(_model="random://tiny-qwen35?quant=q0f32&seed=5", max_num_sequence=6,
                          max_total_sequence_length=160, prefill_chunk_size=32, _gen=(60, 110)),
     "hybrid_prefill": dict(max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=48,
@@ -107,6 +111,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
     cfg = dict(CONFIGS[name])
     gen = cfg.pop("_gen", (2, 14))
     model = cfg.pop("_model", MODEL)
+    oracle = cfg.pop("_oracle", model)
     eng = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(mode="server", **cfg),
                         request_stream_callback=on_outputs)
     reqs = _workload(seed, gen=gen)
@@ -132,7 +137,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
     window = tuple((k, cfg[k]) for k in ("sliding_window_size", "attention_sink_size") if k in cfg)
     for r in reqs:
         # a sequence ends with "length" at the engine's single-sequence limit as well as at max_tokens
-        want = _alone(r["prompt"], r["max_tokens"], window, model)[: max(0, limit - len(r["prompt"]))]
+        want = _alone(r["prompt"], r["max_tokens"], window, oracle)[: max(0, limit - len(r["prompt"]))]
         for j in range(r["n"]):
             have = got.get((r["id"], j), [])
             if r["id"] in aborted and (r["id"], j) not in finished:
