@@ -86,6 +86,15 @@ def test_tp2_recurrent_model_matches_single_rank(model):
     assert single == tp2
 
 
+def test_tp2_recurrent_model_with_parallel_samples():
+    """``n = 2`` on two ranks: the fork pairs travel with the step descriptor, so the worker rank copies the
+    state of the sequence its samples continue from as rank 0 does."""
+    model = "random://tiny-rwkv6?quant=q0f32&seed=5"
+    single = _run(1, model, port=29565, extra_env={"MLCB_TEST_N": "2"})
+    tp2 = _run(2, model, port=29566, extra_env={"MLCB_TEST_N": "2"})
+    assert single == tp2 and all(s[0] == s[1] for s in single)
+
+
 @pytest.mark.parametrize("mode,head", [("eagle", "random://tiny-eagle?quant=q0f32&seed=3"),
                                        ("medusa", "random://tiny-medusa?quant=q0f32&seed=4")])
 def test_tp2_with_a_feature_fed_draft_head_matches_plain_decoding(mode, head):
