@@ -25,23 +25,30 @@ def _workload(seed, count=12, gen=(2, 14)):
         reqs.append({"id": f"q{i}", "prompt": stem + tail, "max_tokens": int(rng.integers(*gen)),
                      "n": 2 if rng.random() < 0.2 else 1, "arrive": int(rng.integers(0, 12)),
                      "abort_after": int(rng.integers(1, 6)) if rng.random() < 0.25 else None})
+    # logit processing that depends on what the request has generated so far (drawn after everything else, so the
+    # schedules above stay what they were)
+    extras = [{}, {}, {"repetition_penalty": 1.3}, {"frequency_penalty": 0.6, "presence_penalty": 0.4},
+              {"logit_bias": {str(int(t)): 6.0 for t in rng.integers(10, 31000, 3)}}]
+    for r in reqs:
+        r["extra"] = extras[int(rng.integers(0, len(extras)))]
     return reqs
 
 
 _ALONE = {}
 
 
-def _alone(prompt, max_tokens, window=(), model=MODEL):
+def _alone(prompt, max_tokens, window=(), model=MODEL, extra=None):
     """Greedy tokens of one prompt on an engine of its own (``window``: the sliding-window settings, which change
     what a token sees and so belong to the oracle too)."""
-    key = (tuple(prompt), max_tokens, window, model)
+    extra = extra or {}
+    key = (tuple(prompt), max_tokens, window, model, json.dumps(extra, sort_keys=True))
     window = window + (("_model", model),) if model != MODEL else window
     if key not in _ALONE:
         if ("eng", window) not in _ALONE:
             _ALONE[("eng", window)] = SyncMLCEngine(model, "cpu", engine_config=EngineConfig(
                 mode="server", max_num_sequence=4, max_total_sequence_length=2048, prefill_chunk_size=256,
                 prefix_cache_mode="disable", **{k: v for k, v in window if k != "_model"}))
-        _, toks = _ALONE[("eng", window)].generate([prompt], dict(GREEDY, max_tokens=max_tokens))
+        _, toks = _ALONE[("eng", window)].generate([prompt], dict(GREEDY, max_tokens=max_tokens, **extra))
         _ALONE[key] = toks[0][0]
     return _ALONE[key]
 
@@ -122,7 +129,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
         while pending and pending[0]["arrive"] <= step:
             r = pending.pop(0)
             eng.add_request(r["id"], [np.asarray(r["prompt"], dtype=np.int32)],
-                            dict(GREEDY, max_tokens=r["max_tokens"], n=r["n"]))
+                            dict(GREEDY, max_tokens=r["max_tokens"], n=r["n"], **r["extra"]))
             live_since[r["id"]] = step
         for r in reqs:
             if (r["abort_after"] is not None and r["id"] in live_since and r["id"] not in aborted
@@ -137,7 +144,7 @@ def test_random_schedules_keep_every_request_exact(name, seed):
     window = tuple((k, cfg[k]) for k in ("sliding_window_size", "attention_sink_size") if k in cfg)
     for r in reqs:
         # a sequence ends with "length" at the engine's single-sequence limit as well as at max_tokens
-        want = _alone(r["prompt"], r["max_tokens"], window, oracle)[: max(0, limit - len(r["prompt"]))]
+        want = _alone(r["prompt"], r["max_tokens"], window, oracle, r["extra"])[: max(0, limit - len(r["prompt"]))]
         for j in range(r["n"]):
             have = got.get((r["id"], j), [])
             if r["id"] in aborted and (r["id"], j) not in finished:
