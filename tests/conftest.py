@@ -18,6 +18,8 @@ def pytest_collection_modifyitems(config, items):
     # single-GPU tests first: the multi-rank GPU files spawn process groups of 2 to 8 ranks and take most of the
     # suite's time, so a stop at the first failure (-x) there should not hide the kernel and model tests
     items.sort(key=lambda it: 1 if os.path.basename(str(it.fspath)) in _MULTI_RANK_FILES else 0)
+    # the randomised GPU schedules judge by token agreement, which fp16 near-ties can dent: they go last
+    items.sort(key=lambda it: 1 if os.path.basename(str(it.fspath)) == "test_zzz_engine_fuzz_gpu.py" else 0)
     try:
         import torch
 
