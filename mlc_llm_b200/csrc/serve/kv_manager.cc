@@ -42,7 +42,39 @@ int32_t KVManager::AllocPage() {
 
 void KVManager::ReleasePage(int32_t p) {
   if (p < 0) return;
-  if (--refcnt_[p] == 0) free_pages_.push_back(p);
+  if (--refcnt_[p] != 0) return;
+  free_pages_.push_back(p);
+  // a copy that was to fill this page is moot now; leaving it queued would let it write into whoever gets the
+  // page next
+  for (size_t i = 0; i + 1 < pending_copies_.size();) {
+    if (pending_copies_[i + 1] == p) {
+      const int32_t src = pending_copies_[i];
+      pending_copies_.erase(pending_copies_.begin() + i, pending_copies_.begin() + i + 2);
+      ReleasePage(src);  // the reference QueueCopy took
+      i = 0;             // the recursion may have edited the list
+    } else {
+      i += 2;
+    }
+  }
+}
+
+// The device runs all queued copies of a plan in ONE launch, so no pair may read a page that another pair writes,
+// and a source must keep its content until that launch: a source that is itself waiting to be filled is replaced
+// by the page it will be filled from (a fresh copy destination holds nothing else yet), and every source is held
+// by a reference of its own until the plan that carries the pair is made.
+void KVManager::QueueCopy(int32_t src, int32_t dst) {
+  for (bool again = true; again;) {
+    again = false;
+    for (size_t i = 0; i + 1 < pending_copies_.size(); i += 2)
+      if (pending_copies_[i + 1] == src) {
+        src = pending_copies_[i];
+        again = true;
+        break;
+      }
+  }
+  ++refcnt_[src];
+  pending_copies_.push_back(src);
+  pending_copies_.push_back(dst);
 }
 
 void KVManager::AddSequence(int64_t seq_id) {
@@ -76,8 +108,7 @@ void KVManager::ForkSequence(int64_t parent_id, int64_t child_id, int64_t fork_p
     if (p >= 0) ++refcnt_[p];  // -1: a page the window dropped
   if (rem != 0) {
     int32_t np = AllocPage();
-    pending_copies_.push_back(parent.pages[full]);
-    pending_copies_.push_back(np);
+    QueueCopy(parent.pages[full], np);
     child.pages.push_back(np);
   }
   child.len = fork_pos;
@@ -88,7 +119,21 @@ void KVManager::ForkSequence(int64_t parent_id, int64_t child_id, int64_t fork_p
 }
 
 void KVManager::RequeuePlanSideEffects(const ForwardPlan& plan) {
-  pending_copies_.insert(pending_copies_.begin(), plan.page_copies.begin(), plan.page_copies.end());
+  std::vector<int32_t> again;
+  for (size_t i = 0; i + 1 < plan.page_copies.size(); i += 2) {
+    const int32_t src = plan.page_copies[i], dst = plan.page_copies[i + 1];
+    if (refcnt_[dst] == 0) continue;  // its owner is gone
+    if (refcnt_[src] == 0) {
+      // free since the plan was made, untouched because the plan's forward never ran: take it back
+      free_pages_.erase(std::find(free_pages_.begin(), free_pages_.end(), src));
+      refcnt_[src] = 1;
+    } else {
+      ++refcnt_[src];
+    }
+    again.push_back(src);
+    again.push_back(dst);
+  }
+  pending_copies_.insert(pending_copies_.begin(), again.begin(), again.end());
   pending_forks_.insert(pending_forks_.begin(), plan.seq_forks.begin(), plan.seq_forks.end());
 }
 
@@ -113,8 +158,7 @@ void KVManager::PopN(int64_t seq_id, int64_t n) {
   if (!s.pages.empty() && s.len % page_size_ != 0 && s.pages.back() >= 0 &&
       refcnt_[s.pages.back()] > 1) {
     int32_t np = AllocPage();
-    pending_copies_.push_back(s.pages.back());
-    pending_copies_.push_back(np);
+    QueueCopy(s.pages.back(), np);
     ReleasePage(s.pages.back());
     s.pages.back() = np;
   }
@@ -171,6 +215,9 @@ ForwardPlan KVManager::BeginForward(const std::vector<int64_t>& seq_ids,
   plan.q_indptr.push_back(0);
   plan.page_copies.swap(pending_copies_);
   plan.seq_forks.swap(pending_forks_);
+  // the sources stay intact until this plan's copy launch: whatever takes such a page from now on writes to it
+  // later in stream order
+  for (size_t i = 0; i + 1 < plan.page_copies.size(); i += 2) ReleasePage(plan.page_copies[i]);
   bool any_window = false;
   for (int64_t id : seq_ids) any_window |= Get(id).window > 0;
   size_t tree_off = 0;

@@ -94,6 +94,7 @@ class KVManager {
   };
   int32_t AllocPage();
   void ReleasePage(int32_t p);
+  void QueueCopy(int32_t src, int32_t dst);
   void TrimWindow(Seq& s, int64_t first_new_pos);
   Seq& Get(int64_t id);
   const Seq& Get(int64_t id) const;
