@@ -208,3 +208,47 @@ def test_preempted_hybrid_state_sequences_start_over():
     _, got = tight.generate(prompts, gen)
     assert [t[0] for t in got] == [t[0] for t in want]
     assert json.loads(tight.debug_stats())["num_preemptions"] >= 1
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_nested_prefixes_under_eviction(seed):
+    """Twenty requests over three nested stems (A, A+B, A+B+C) and unrelated prompts, in a pool that cannot keep
+    everything cached: the radix cache forks, extends, recycles and evicts while requests run, one system prompt
+    is pinned. Every answer equals the uncached one."""
+    rng = np.random.default_rng(100 + seed)
+    a = rng.integers(10, 31000, 22).tolist()
+    b = a + rng.integers(10, 31000, 17).tolist()
+    c = b + rng.integers(10, 31000, 26).tolist()
+    stems = [[], a, b, c]
+    eng_got = {}
+
+    def on_outputs(outs):
+        for out in outs:
+            rid, singles = out.unpack()
+            if singles[0].request_final_usage_json_str is None:
+                eng_got.setdefault(rid, []).extend(singles[0].delta_token_ids)
+
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(
+        mode="server", max_num_sequence=5, max_total_sequence_length=420, prefill_chunk_size=32,
+        prefix_cache_mode="radix", prefix_cache_max_num_recycling_seqs=2), request_stream_callback=on_outputs)
+    reqs = []
+    for i in range(20):
+        stem = stems[int(rng.integers(0, 4))]
+        cut = len(stem) if rng.random() < 0.7 else int(rng.integers(0, len(stem) + 1))   # sometimes mid-stem
+        prompt = stem[:cut] + rng.integers(10, 31000, int(rng.integers(1, 30))).tolist()
+        reqs.append((f"p{i}", prompt, int(rng.integers(2, 20)), int(rng.integers(0, 25))))
+    pending = sorted(reqs, key=lambda r: r[3])
+    step = 0
+    while pending or not eng.empty():
+        while pending and pending[0][3] <= step:
+            rid, prompt, max_tokens, _ = pending.pop(0)
+            debug = dict(GREEDY["debug_config"], pinned_system_prompt=(rid == "p0"))
+            eng.add_request(rid, [np.asarray(prompt, dtype=np.int32)],
+                            dict(GREEDY, max_tokens=max_tokens, debug_config=debug))
+        eng.step()
+        step += 1
+        assert step < 4000
+    for rid, prompt, max_tokens, _ in reqs:
+        assert eng_got.get(rid, []) == _alone(prompt, max_tokens), rid
+    stats = json.loads(eng.debug_stats())
+    assert stats["num_running"] == 0 and stats["num_waiting"] == 0
