@@ -647,3 +647,37 @@ def test_detect_weight_formats(tmp_path):
     (tmp_path / "model.safetensors").write_bytes(b"")
     assert detect_weight(str(tmp_path), str(tmp_path / "config.json"), "awq") == (str(tmp_path), "huggingface-safetensor")
     assert detect_weight("auto", str(tmp_path / "config.json"), "auto") == (str(tmp_path), "huggingface-safetensor")
+
+
+def test_text_streamer_and_stop_strings_on_random_unicode():
+    """Random strings of one- to four-byte characters, fed to the streamer in random bursts: the pieces join to
+    the plain decoding and no piece before the end holds a replacement character. A stop string cut at a random
+    place of the text stops the handler there, however the text is split into tokens."""
+    rng = np.random.default_rng(0)
+    tok = Tokenizer.synthetic(1000)
+    alphabet = list("abc xyz.,") + list("éüñß") + list("✓€漢字") + list("😀🚀")
+    for _ in range(60):
+        text = "".join(alphabet[int(i)] for i in rng.integers(0, len(alphabet), int(rng.integers(1, 40))))
+        ids = tok.encode(text)
+        st = TextStreamer(tok)
+        pieces, at = [], 0
+        while at < len(ids):
+            n = int(rng.integers(1, 5))
+            pieces.append(st.put(ids[at:at + n]))
+            at += n
+        assert all("�" not in p for p in pieces)
+        pieces.append(st.finish())
+        assert "".join(pieces) == tok.decode(ids) == text
+        if len(text) < 4:
+            continue
+        a = int(rng.integers(1, len(text) - 1))
+        b = int(rng.integers(a + 1, min(len(text), a + 6) + 1))
+        stop = text[a:b]
+        handler = StopStrHandler([stop], tok)
+        out = []
+        for i in ids:
+            out.extend(handler.put(i))
+            if handler.stop_triggered:
+                break
+        assert handler.stop_triggered, (text, stop)
+        assert tok.decode(out) == text[: text.index(stop)], (text, stop)
