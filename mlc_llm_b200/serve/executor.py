@@ -187,6 +187,15 @@ class FeatureStore:
             if k > 0:
                 self.rows[seq] = (s0 + k, t[k:])
 
+    def fork(self, parent: int, child: int) -> None:
+        """Parallel samples: the child continues from what is known about its parent (rows are never edited in
+        place, so sharing the tensors is safe)."""
+        cur = self.rows.get(parent)
+        if cur is not None:
+            self.rows[child] = cur
+        if parent in self.pred:
+            self.pred[child] = self.pred[parent]
+
     def clear(self) -> None:
         self.rows.clear()
         self.pred.clear()
@@ -624,6 +633,8 @@ class ModelExecutor:
         ht, clock = self.host_times, time.perf_counter
         t0 = clock()
         n_rows = len(sp["logit_token_index"])
+        if self.spec_heads:
+            self._fork_features(plan)
         parts = self._pipeline_parts(model_id, plan, token_ids, embed_handles, sp)
         if parts is not None:
             # the parts were packed, announced and launched one after the other; `dev` holds the last one's
@@ -820,6 +831,11 @@ class ModelExecutor:
         return out
 
     # ------------------------------------------------------------------ EAGLE / Medusa draft heads
+    def _fork_features(self, plan: dict) -> None:
+        """Forks reported by a plan (of the target's or of the head's KV manager) carry the features along."""
+        for parent, child in np.asarray(plan.get("seq_forks", ()), dtype=np.int64).reshape(-1, 2).tolist():
+            self.features.fork(int(parent), int(child))
+
     def _remember_features(self, plan: dict, feats: torch.Tensor, rows_of_seq: Optional[List[List[int]]]) -> None:
         """Store the target's features of this forward: all rows of every sequence (prefill, decode), or
         only ``rows_of_seq[i]`` (verification: the root and the accepted nodes, which sit at consecutive
@@ -937,6 +953,8 @@ class ModelExecutor:
     def _forward_verify(self, model_id: int, plan: dict, token_ids: np.ndarray, vp: dict) -> dict:
         self._enter()
         sp = vp["sampling"]
+        if self.spec_heads:
+            self._fork_features(plan)
         arrays = self._pack(plan, token_ids, sp, model_id)
         if self.comm is not None:
             self.comm.broadcast_step("forward", model_id,

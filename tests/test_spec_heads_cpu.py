@@ -289,3 +289,34 @@ def test_eagle_tree_nodes_continue_from_their_parents_output():
             checked += 1
         assert n in (2, 6)  # levels of two and of two + four nodes are fed
     assert checked >= 8
+
+
+def test_parallel_samples_inherit_the_target_features():
+    """``n = 2`` with an EAGLE head: a sample forks from the prompt's sequence, and the head's first call for it
+    must see the target's true features of the prompt (carried over with the fork), not zeros."""
+    eng = _engine("eagle")
+    head, ex = eng.runtime.models[1], eng.runtime.executor
+    seen = []
+    orig_fuse, orig_spec = head.fuse_embed_hidden, ex._forward_spec_head
+
+    def spec_head(model_id, plan, dev, n_rows):
+        seen.append({"ids": [int(s) for s in np.asarray(plan["seq_ids"]).tolist()],
+                     "qi": np.asarray(plan["q_indptr"]).tolist(), "pos": np.asarray(plan["positions"]).tolist()})
+        return orig_spec(model_id, plan, dev, n_rows)
+
+    def fuse(x, prev):
+        seen[-1]["prev"] = prev.detach().clone()
+        return orig_fuse(x, prev)
+
+    ex._forward_spec_head, head.fuse_embed_hidden = spec_head, fuse
+    prompt = _prompts(1, seed=12)[0]
+    _, plain = _engine().generate([prompt], GREEDY)
+    _, got = eng.generate([prompt], dict(GREEDY, n=2))
+    assert got[0] == [plain[0][0], plain[0][0]]
+    parent = seen[0]["ids"][0]
+    first_child_call = next(c for c in seen if parent not in c["ids"])
+    assert len(first_child_call["ids"]) == 2
+    for i in range(2):
+        a, b = first_child_call["qi"][i], first_child_call["qi"][i + 1]
+        rows = first_child_call["prev"][a:b]
+        assert b > a and bool((rows.abs().sum(dim=-1) > 0).all()), "a sample's first draft call saw zero features"
