@@ -490,3 +490,55 @@ def test_concurrent_disaggregated_hand_offs_and_plain_requests():
     finally:
         for e in (plain, p_eng, d_eng):
             e.terminate()
+
+
+def test_async_streams_with_random_cancellations():
+    """Sixteen concurrent streams; a third of them are aborted after a random number of chunks (some right away,
+    some through cancellation of the consuming task). The survivors' texts equal what the same prompts give one
+    by one, and the engine answers a fresh request afterwards."""
+    rng = np.random.default_rng(77)
+    prompts = _prompts(16, seed=50)
+    lengths = [int(rng.integers(4, 30)) for _ in prompts]
+    kill_after = [int(rng.integers(0, 5)) if rng.random() < 0.33 else None for _ in prompts]
+    eng = AsyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(mode="server", max_num_sequence=6,
+                                                                  max_total_sequence_length=1024,
+                                                                  prefill_chunk_size=48))
+    greedy = dict(temperature=0.0, debug_config={"ignore_eos": True})
+
+    async def run():
+        async def one(i):
+            text, chunks = "", 0
+            stream = await eng.completions.create(prompt=prompts[i], max_tokens=lengths[i], stream=True,
+                                                  request_id=f"s{i}", **greedy)
+            async for chunk in stream:
+                text += "".join(ch.text for ch in chunk.choices)
+                chunks += 1
+                if kill_after[i] is not None and chunks > kill_after[i]:
+                    await eng.abort(f"s{i}")
+                    break
+            await stream.aclose()
+            return text
+
+        tasks = [asyncio.ensure_future(one(i)) for i in range(len(prompts))]
+        await asyncio.sleep(0.05)
+        tasks[3].cancel()                      # a consumer that simply goes away
+        results = await asyncio.gather(*tasks, return_exceptions=True)
+        await eng.abort("s3")
+        alone = []
+        for i in range(len(prompts)):
+            out = await eng.completions.create(prompt=prompts[i], max_tokens=lengths[i], **greedy)
+            alone.append(out.choices[0].text)
+        return results, alone
+
+    try:
+        results, alone = asyncio.run(asyncio.wait_for(run(), timeout=240))
+    finally:
+        eng.terminate()
+    for i, (got, want) in enumerate(zip(results, alone)):
+        if i == 3:
+            continue
+        assert isinstance(got, str), (i, got)
+        if kill_after[i] is None:
+            assert got == want, i
+        else:
+            assert want.startswith(got), i
