@@ -64,6 +64,52 @@ def test_chat_stream_sse(server):
     assert chunks[-1]["usage"]["completion_tokens"] > 0 and chunks[-1]["choices"] == []
 
 
+def test_client_disconnects_abort_their_requests(server):
+    """Streams that the client closes after two events, beside streams read to the end: the server aborts the
+    abandoned generations (their tokens stop being produced: the completion counter settles far below what they
+    asked for) and keeps serving."""
+    import concurrent.futures as cf
+    import time
+
+    def metric(name):
+        text = requests.get(server.base_url + "/metrics", timeout=30).text
+        return float(next(ln.split()[-1] for ln in text.splitlines() if ln.startswith(name)))
+
+    before = metric("completion_tokens_sum")
+
+    def stream(i):
+        body = {"model": MODEL, "prompt": f"request {i}", "max_tokens": 2000 if i % 2 else 12, "stream": True,
+                "temperature": 0.0, "debug_config": {"ignore_eos": True}}
+        seen = 0
+        with requests.post(server.base_url + "/v1/completions", json=body, headers=H, stream=True, timeout=120) as r:
+            assert r.status_code == 200
+            for ln in r.iter_lines():
+                if not ln:
+                    continue
+                seen += 1
+                if i % 2 and seen == 2:
+                    return "left"               # leaving the block closes the connection
+                if ln == b"data: [DONE]":
+                    return "done"
+        return "eof"
+
+    with cf.ThreadPoolExecutor(6) as pool:
+        results = list(pool.map(stream, range(6)))
+    assert results == ["done", "left"] * 3
+    settled, last = None, -1.0
+    for _ in range(60):                         # the aborts land within a few engine steps
+        now = metric("completion_tokens_sum")
+        if now == last:
+            settled = now
+            break
+        last = now
+        time.sleep(0.5)
+    assert settled is not None and settled - before < 3 * 12 + 3 * 400
+    r = requests.post(server.base_url + "/v1/completions", headers=H, timeout=60,
+                      json={"model": MODEL, "prompt": "still there?", "max_tokens": 3})
+    assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 3
+
+
 def test_bad_request_is_400(server):
     body = {"model": MODEL, "messages": [{"role": "user", "content": "x"}], "max_tokens": 4, "temperature": -1}
     r = requests.post(server.base_url + "/v1/chat/completions", json=body, headers=H, timeout=60)
