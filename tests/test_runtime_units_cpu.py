@@ -681,3 +681,41 @@ def test_text_streamer_and_stop_strings_on_random_unicode():
                 break
         assert handler.stop_triggered, (text, stop)
         assert tok.decode(out) == text[: text.index(stop)], (text, stop)
+
+
+def test_every_template_renders_alike_in_python_and_native_code():
+    """All registered templates, random conversations (with and without a system message, one to four turns, a
+    list-of-text-parts content now and then): the Python renderer and the C++ one of the JSON FFI engine give the
+    same prompt."""
+    rng = np.random.default_rng(3)
+    words = ["Hi", "Tell me more.", "Why?", "ok", "Summarise: a b c", "1 + 1 = ?", "Danke schön ✓", ""]
+    checked = 0
+    for name in ConvTemplateRegistry.names():
+        conv = ConvTemplateRegistry.get_conv_template(name)
+        for _ in range(4):
+            msgs = []
+            if rng.random() < 0.5:
+                msgs.append({"role": "system", "content": "You are terse."})
+            turns = int(rng.integers(1, 5))
+            for t in range(turns):
+                text = words[int(rng.integers(0, len(words)))]
+                content = [{"type": "text", "text": text}] if rng.random() < 0.2 else text
+                msgs.append({"role": "user", "content": content})
+                if t + 1 < turns:
+                    msgs.append({"role": "assistant", "content": words[int(rng.integers(0, len(words) - 1))]})
+            c = Conversation.from_json_dict(conv.to_json_dict())
+            c.messages = []
+            for m in msgs:
+                if m["role"] == "system":
+                    c.system_message = m["content"]
+                else:
+                    c.messages.append((m["role"], m["content"]))
+            c.messages.append(("assistant", None))
+            try:
+                py = "".join(p for p in c.as_prompt() if isinstance(p, str))
+            except ValueError:
+                continue                      # a template without that role
+            native = _core.conv_template_render(json.dumps(conv.to_json_dict()), json.dumps(msgs))
+            assert py == native, (name, msgs)
+            checked += 1
+    assert checked >= 150
