@@ -125,7 +125,9 @@ void KVManager::RequeuePlanSideEffects(const ForwardPlan& plan) {
     if (refcnt_[dst] == 0) continue;  // its owner is gone
     if (refcnt_[src] == 0) {
       // free since the plan was made, untouched because the plan's forward never ran: take it back
-      free_pages_.erase(std::find(free_pages_.begin(), free_pages_.end(), src));
+      auto it = std::find(free_pages_.begin(), free_pages_.end(), src);
+      if (it == free_pages_.end()) continue;  // cannot happen: a page without holders is on the free list
+      free_pages_.erase(it);
       refcnt_[src] = 1;
     } else {
       ++refcnt_[src];
