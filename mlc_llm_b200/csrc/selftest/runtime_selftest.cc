@@ -71,6 +71,36 @@ void TestKVManager(uint64_t seed) {
       }
       CHECK(plan.slots.size() == total && plan.positions.size() == total);
       CHECK(plan.page_indptr.size() == ids.size() + 1);
+      // the copies of one plan run in one launch: no pair writes what another reads or writes
+      {
+        std::set<int32_t> srcs, dsts;
+        for (size_t i = 0; i + 1 < plan.page_copies.size(); i += 2) {
+          srcs.insert(plan.page_copies[i]);
+          CHECK(dsts.insert(plan.page_copies[i + 1]).second);
+        }
+        for (int32_t d : dsts) CHECK(!srcs.count(d));
+      }
+      if (rng() % 5 == 0) {
+        // a plan whose forward does not run after all: its rows are popped, its copies ride on the next plan
+        for (size_t i = 0; i < ids.size(); ++i) {
+          kv.PopN(ids[i], lens[i]);
+          len[ids[i]] -= lens[i];
+        }
+        kv.RequeuePlanSideEffects(plan);
+        std::vector<int32_t> ones(ids.size(), 1);
+        int64_t again = 0;
+        for (int64_t id : ids) again += kv.PagesNeeded(id, 1);
+        if (again <= kv.NumAvailablePages()) {
+          ForwardPlan next = kv.BeginForward(ids, ones);
+          for (int64_t id : ids) len[id] += 1;
+          for (size_t i = 0; i + 1 < plan.page_copies.size(); i += 2) {
+            bool found = false;
+            for (size_t j = 0; j + 1 < next.page_copies.size(); j += 2)
+              found |= next.page_copies[j + 1] == plan.page_copies[i + 1];
+            CHECK(found);  // every destination that is still owned gets its copy
+          }
+        }
+      }
       // no two appended tokens share a slot
       std::set<int32_t> seen(plan.slots.begin(), plan.slots.end());
       CHECK(seen.size() == total);
