@@ -541,8 +541,43 @@ class EngineImpl : public Engine {
     Touch(r.rs);
   }
 
-  // Appends the sampling parameters of one row.
-  void AddSampleRow(SampleParams* sp, EntryRef r, int32_t logit_token_index) {
+  // Appends the sampling parameters of one row. `path`: draft tokens that precede this row's position beyond the
+  // committed ones (the row of a draft-tree node, or of a draft round, follows its ancestors): the penalties
+  // count them and the grammar mask is the one of the state after them, as if they had been committed.
+  void AddSampleRow(SampleParams* sp, EntryRef r, int32_t logit_token_index,
+                    const std::vector<int32_t>* path = nullptr) {
+    RequestStateEntry& e = r.e();
+    const GenerationConfig& g = r.rs->request.cfg;
+    if (path && path->empty()) path = nullptr;
+    if (path) {
+      const bool pen = g.frequency_penalty != 0 || g.presence_penalty != 0 || g.repetition_penalty != 1.0;
+      const bool gram = e.grammar_handle >= 0 && grammar_;
+      if (!pen && !gram) path = nullptr;
+    }
+    int accepted = 0;
+    bool dead = false;  // the path leaves the grammar: the node can never be accepted, any mask will do
+    if (path) {
+      for (int32_t t : *path) ++e.appeared_token_ids[t];
+      if (e.grammar_handle >= 0 && grammar_)
+        for (int32_t t : *path) {
+          if (IsStopToken(r.rs->request, t) || !grammar_->AcceptToken(e.grammar_handle, t)) {
+            dead = true;
+            break;
+          }
+          ++accepted;
+        }
+    }
+    AddSampleRowNow(sp, r, logit_token_index, dead);
+    if (path) {
+      if (accepted > 0) grammar_->Rollback(e.grammar_handle, accepted);
+      for (int32_t t : *path) {
+        auto it = e.appeared_token_ids.find(t);
+        if (it != e.appeared_token_ids.end() && --it->second <= 0) e.appeared_token_ids.erase(it);
+      }
+    }
+  }
+
+  void AddSampleRowNow(SampleParams* sp, EntryRef r, int32_t logit_token_index, bool skip_grammar) {
     RequestStateEntry& e = r.e();
     const GenerationConfig& g = r.rs->request.cfg;
     const int row = static_cast<int>(sp->logit_token_index.size());
@@ -566,7 +601,7 @@ class EngineImpl : public Engine {
       sp->bias_token.push_back(b.first);
       sp->bias_value.push_back(b.second);
     }
-    if (e.grammar_handle >= 0 && grammar_) {
+    if (e.grammar_handle >= 0 && grammar_ && !skip_grammar) {
       std::vector<int32_t> bits = grammar_->NextTokenBitmask(e.grammar_handle);
       sp->mask_rows.push_back(row);
       sp->mask_bits.insert(sp->mask_bits.end(), bits.begin(), bits.end());
@@ -1472,7 +1507,11 @@ class EngineImpl : public Engine {
         vp.draft_prob_slots.push_back(ds.draft_slots[j]);
         vp.parents.push_back(ds.draft_parents[j]);
         vp.uniform.push_back(static_cast<float>(e.NextUniform()));
-        AddSampleRow(&vp.sampling, r, off + 1 + j);
+        // the row after node j: its ancestors' tokens and its own precede it
+        std::vector<int32_t> path;
+        for (int a = j; a >= 0; a = ds.draft_parents[a]) path.push_back(ds.draft_tokens[a].token);
+        std::reverse(path.begin(), path.end());
+        AddSampleRow(&vp.sampling, r, off + 1 + j, &path);
       }
       vp.node_indptr.push_back(static_cast<int32_t>(vp.draft_tokens.size()));
       vp.final_uniform.push_back(static_cast<float>(e.NextUniform()));

@@ -320,3 +320,32 @@ def test_parallel_samples_inherit_the_target_features():
         a, b = first_child_call["qi"][i], first_child_call["qi"][i + 1]
         rows = first_child_call["prev"][a:b]
         assert b > a and bool((rows.abs().sum(dim=-1) > 0).all()), "a sample's first draft call saw zero features"
+
+
+@pytest.mark.parametrize("spec", [dict(speculative_mode="small_draft", spec_draft_length=3,
+                                       additional_models=["random://tiny-llama?quant=q0f32&seed=2"]),
+                                  dict(speculative_mode="small_draft", spec_draft_length=2, spec_tree_width=2,
+                                       additional_models=["random://tiny-llama?quant=q0f32&seed=2"]),
+                                  dict(speculative_mode="eagle", spec_draft_length=2,
+                                       additional_models=[HEADS["eagle"]])])
+def test_json_mode_under_speculative_decoding_equals_plain_json_mode(spec):
+    """A schema-constrained request verified over draft tokens: the row after a draft node must be masked with the
+    grammar state after that node's path (and penalised with its tokens), not with the state of the last
+    committed token; a draft token outside the grammar is never accepted. Output equals plain constrained
+    decoding, for one sample and for two."""
+    import json
+
+    schema = json.dumps({"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"}},
+                         "required": ["name", "age"]})
+    gen = {"temperature": 0.0, "max_tokens": 30, "repetition_penalty": 1.1,
+           "response_format": {"type": "json_object", "schema": schema}}
+    prompts = _prompts(3, seed=21)
+    _, want = _engine().generate(prompts, gen)
+    kw = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=32,
+              prefix_cache_mode="disable", **spec)
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+    _, got = eng.generate(prompts, gen)
+    assert [g[0] for g in got] == [w[0] for w in want]
+    assert json.loads(eng.debug_stats())["num_verify_steps"] > 0
+    _, two = eng.generate(prompts[:1], dict(gen, n=2))
+    assert two[0] == [want[0][0], want[0][0]]
