@@ -252,3 +252,22 @@ def test_nested_prefixes_under_eviction(seed):
         assert eng_got.get(rid, []) == _alone(prompt, max_tokens), rid
     stats = json.loads(eng.debug_stats())
     assert stats["num_running"] == 0 and stats["num_waiting"] == 0
+
+
+def test_json_mode_survives_preemption():
+    """Schema-constrained requests in a pool they outgrow: a preempted request is prefilled again with the tokens
+    it had produced, and its grammar state must still stand where those tokens left it."""
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(10, 31000, int(n)).tolist() for n in (25, 40, 31, 52, 18, 44)]
+    schema = json.dumps({"type": "object", "properties": {"a": {"type": "array", "items": {"type": "integer"}}},
+                         "required": ["a"]})
+    gen = {"temperature": 0.0, "max_tokens": 100, "response_format": {"type": "json_object", "schema": schema}}
+    base = dict(mode="server", prefill_chunk_size=32, prefix_cache_mode="disable")
+    roomy = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(max_num_sequence=8,
+                                                                   max_total_sequence_length=2048, **base))
+    _, want = roomy.generate(prompts, gen)
+    tight = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(max_num_sequence=6,
+                                                                   max_total_sequence_length=224, **base))
+    _, got = tight.generate(prompts, gen)
+    assert [t[0] for t in got] == [t[0] for t in want]
+    assert json.loads(tight.debug_stats())["num_preemptions"] >= 1
