@@ -11,7 +11,20 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+_SINGLE = {}
+
+
 def _run(world: int, model: str, device: str = "cpu", port: int = 29531, extra_env=None, want_flags=False, timeout=600):
+    # single-rank baselines repeat across tests: run each (model, device, settings) once
+    key = (model, device, tuple(sorted((extra_env or {}).items())))
+    if world == 1 and not want_flags:
+        if key not in _SINGLE:
+            _SINGLE[key] = _run_ranks(1, model, device, port, extra_env, False, timeout)
+        return _SINGLE[key]
+    return _run_ranks(world, model, device, port, extra_env, want_flags, timeout)
+
+
+def _run_ranks(world: int, model: str, device: str, port: int, extra_env, want_flags, timeout):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker.py"),
            model, device]
