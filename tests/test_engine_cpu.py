@@ -542,3 +542,24 @@ def test_async_streams_with_random_cancellations():
             assert got == want, i
         else:
             assert want.startswith(got), i
+
+
+@pytest.mark.parametrize("spec", [dict(spec_draft_length=4), dict(spec_draft_length=3, spec_tree_width=2)])
+def test_fully_accepted_drafts_stop_where_plain_decoding_stops(spec, reference_outputs):
+    """A draft model with the target's own weights: every proposal is accepted, so several tokens are committed per
+    verification. A stop token or the length limit that falls inside such a run must end the request at the same
+    token as one-by-one decoding."""
+    prompts, _ = reference_outputs
+    prompts = prompts[:3]
+    plain = _engine(prefix_cache_mode="disable")
+    eng = _engine(prefix_cache_mode="disable", speculative_mode="small_draft", additional_models=[MODEL], **spec)
+    _, full = plain.generate(prompts, dict(GREEDY, max_tokens=20))
+    for i, p in enumerate(prompts):
+        for cut in (5, 6, 7, 11):
+            gen = dict(GREEDY, max_tokens=20, stop_token_ids=[int(full[i][0][cut])])
+            assert eng.generate([p], gen)[1][0][0] == plain.generate([p], gen)[1][0][0], (i, cut)
+    for max_tokens in (1, 2, 3, 5, 6, 7):
+        gen = dict(GREEDY, max_tokens=max_tokens)
+        assert [t[0] for t in eng.generate(prompts, gen)[1]] == [t[0][:max_tokens] for t in full]
+    stats = json.loads(eng.debug_stats())
+    assert stats["num_verify_steps"] > 0
