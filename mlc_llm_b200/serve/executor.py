@@ -1002,7 +1002,15 @@ class ModelExecutor:
             row += 1 + (ne - nb)
         d = self.device
         self._ensure_draft_storage(int(slot_of_row.max()) if total_rows else 0)
-        draft_rows = ops.row_gather(self.draft_probs, torch.from_numpy(slot_of_row).to(d))
+        if bool((next_sibling >= 0).any()):
+            # A draft tree: its children are the draft's k best tokens, chosen, not drawn. The acceptance rule
+            # min(1, p / q) is only unbiased for candidates DRAWN from q; for chosen candidates the draft
+            # distribution of a child is the point mass on its token: accept with probability p(token), on a
+            # rejection drop the token from p and renormalise. (Under greedy sampling both rules coincide.)
+            draft_rows = torch.zeros(total_rows, probs.shape[1], dtype=probs.dtype, device=d)
+            draft_rows.scatter_(1, torch.from_numpy(draft_tok.astype(np.int64)).to(d).unsqueeze(1), 1.0)
+        else:
+            draft_rows = ops.row_gather(self.draft_probs, torch.from_numpy(slot_of_row).to(d))
         parent_ptr = torch.from_numpy(roots.copy()).to(d)
         ops.verify_tree(draft_rows, torch.from_numpy(draft_tok).to(d), probs,
                         torch.from_numpy(first_child).to(d), torch.from_numpy(next_sibling).to(d),

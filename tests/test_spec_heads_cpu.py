@@ -349,3 +349,55 @@ def test_json_mode_under_speculative_decoding_equals_plain_json_mode(spec):
     assert json.loads(eng.debug_stats())["num_verify_steps"] > 0
     _, two = eng.generate(prompts[:1], dict(gen, n=2))
     assert two[0] == [want[0][0], want[0][0]]
+
+
+def test_chosen_tree_children_keep_the_target_distribution():
+    """Draft-tree children are the draft's best tokens, chosen rather than drawn, so they are verified against
+    point-mass draft rows: accept with probability p(token), otherwise drop the token from p. Over many draws
+    the token that ends up at the first position is distributed as the target's p (with the min(1, p / q) rule
+    and q = p, the best token would be taken every time)."""
+    from mlc_llm_b200 import ops
+
+    torch.manual_seed(0)
+    p = torch.tensor([0.05, 0.4, 0.25, 0.2, 0.1])
+    n = 6000
+    children = [1, 2]                                   # the two best tokens
+    rows = 3 * n
+    model = p.repeat(rows, 1).clone()
+    draft_tok = torch.zeros(rows, dtype=torch.int32)
+    first_child = torch.full((rows,), -1, dtype=torch.int32)
+    next_sibling = torch.full((rows,), -1, dtype=torch.int32)
+    roots = torch.arange(n, dtype=torch.int32) * 3
+    first_child[roots.long()] = roots + 1
+    next_sibling[(roots + 1).long()] = roots + 2
+    draft_tok[(roots + 1).long()], draft_tok[(roots + 2).long()] = children[0], children[1]
+    draft = torch.zeros(rows, 5)
+    draft.scatter_(1, draft_tok.long().unsqueeze(1), 1.0)
+    uniform = torch.rand(rows)
+    parent = roots.clone()
+    ops.verify_tree(draft, draft_tok, model, first_child, next_sibling, uniform, parent)
+    final, _ = ops.sample(model, parent, torch.rand(n), torch.ones(n), None)
+    out = torch.where(parent == roots, final.to(torch.int64), draft_tok[parent.long()].to(torch.int64))
+    freq = torch.bincount(out, minlength=5).float() / n
+    assert torch.allclose(freq, p, atol=0.025), freq
+
+
+def test_tree_verification_in_the_engine_does_not_collapse_to_the_best_token():
+    """A draft model with the target's weights and a tree of width two at temperature one: with point-mass draft
+    rows a chosen child is accepted with the (small) probability the target gives it; with the drawn-candidate
+    rule it would be accepted every time and sampling would turn into arg-max decoding."""
+    prompt = _prompts(1, seed=31)[0]
+    kw = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=64,
+              prefix_cache_mode="disable", speculative_mode="small_draft", spec_draft_length=2, spec_tree_width=2,
+              additional_models=[MODEL])
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+    plain = _engine()
+    same = 0
+    for seed in range(24):
+        # the first token is drawn after the prefill; the second comes out of a verification of the tree under it
+        _, toks = eng.generate([prompt], {"temperature": 1.0, "seed": seed, "max_tokens": 2,
+                                          "debug_config": {"ignore_eos": True}})
+        first, second = toks[0][0]
+        _, best = plain.generate([prompt + [first]], dict(GREEDY, max_tokens=1))
+        same += int(second == best[0][0][0])
+    assert same <= 8, same
