@@ -969,6 +969,15 @@ class ModelExecutor:
         probs = ops.softmax_temperature(logits, dev["s_temperature"])
         if float(np.min(sp["top_p"])) < 1.0:
             ops.renorm_top_p(probs, None, dev["s_top_p"])
+        top_k = np.asarray(sp["top_k"])
+        if top_k.size and int(top_k.max()) > 0:
+            # the verified distribution is the one plain decoding samples from: the k best of the top-p set
+            for k in sorted(set(int(v) for v in top_k.tolist() if 0 < v < probs.shape[1])):
+                rows = torch.from_numpy(np.nonzero(top_k == k)[0]).to(probs.device)
+                sub = probs.index_select(0, rows)
+                kth = torch.topk(sub, k, dim=-1).values[:, -1:]
+                sub = torch.where(sub >= kth, sub, torch.zeros_like(sub))
+                probs.index_copy_(0, rows, sub / sub.sum(dim=-1, keepdim=True).clamp_min(1e-30))
         # flat node table: row r of `probs` is node r; roots carry no draft token
         node_indptr = np.asarray(vp["node_indptr"])
         nseq = len(node_indptr) - 1

@@ -401,3 +401,18 @@ def test_tree_verification_in_the_engine_does_not_collapse_to_the_best_token():
         _, best = plain.generate([prompt + [first]], dict(GREEDY, max_tokens=1))
         same += int(second == best[0][0][0])
     assert same <= 8, same
+
+
+@pytest.mark.parametrize("spec", [dict(spec_draft_length=3), dict(spec_draft_length=2, spec_tree_width=2)])
+def test_top_k_applies_to_the_verified_distribution(spec):
+    """``top_k = 1`` at temperature one leaves a single token per position, so sampling is arg-max decoding; the
+    verification of draft tokens must see that truncated distribution too."""
+    prompts = _prompts(3, seed=41)
+    _, want = _engine().generate(prompts, dict(GREEDY, max_tokens=10))
+    kw = dict(mode="server", max_num_sequence=8, max_total_sequence_length=2048, prefill_chunk_size=32,
+              prefix_cache_mode="disable", speculative_mode="small_draft",
+              additional_models=["random://tiny-llama?quant=q0f32&seed=2"], **spec)
+    eng = SyncMLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+    _, got = eng.generate(prompts, {"temperature": 1.0, "top_k": 1, "seed": 9, "max_tokens": 10,
+                                    "debug_config": {"ignore_eos": True}})
+    assert [t[0] for t in got] == [t[0] for t in want]
