@@ -128,6 +128,7 @@ class PyModelBackend : public ModelBackend {
     vd["draft_tokens"] = ToArray(v.draft_tokens);
     vd["draft_prob_slots"] = ToArray(v.draft_prob_slots);
     vd["parents"] = ToArray(v.parents);
+    vd["want_logprobs"] = v.want_logprobs;
     vd["uniform"] = ToArray(v.uniform);
     vd["final_uniform"] = ToArray(v.final_uniform);
     vd["sampling"] = SampleParamsToDict(v.sampling);
@@ -137,6 +138,10 @@ class PyModelBackend : public ModelBackend {
     out.accepted_nodes = FromArray<int32_t>(d["accepted_nodes"]);
     out.final_tokens = FromArray<int32_t>(d["final_tokens"]);
     if (d.contains("final_probs")) out.final_probs = FromArray<float>(d["final_probs"]);
+    if (d.contains("accepted_probs")) out.accepted_probs = FromArray<float>(d["accepted_probs"]);
+    if (d.contains("top_tokens")) out.top_tokens = FromArray<int32_t>(d["top_tokens"]);
+    if (d.contains("top_probs")) out.top_probs = FromArray<float>(d["top_probs"]);
+    if (d.contains("num_top")) out.num_top = d["num_top"].cast<int32_t>();
     return out;
   }
   void MoveKVTokens(int model_id, const std::vector<int32_t>& moves) override {

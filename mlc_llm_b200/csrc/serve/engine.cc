@@ -1497,6 +1497,7 @@ class EngineImpl : public Engine {
       lens.push_back(nodes + 1);
       token_ids.push_back(e.committed_tokens.back().token);
       tree_parents.push_back(-1);
+      vp.want_logprobs |= r.rs->request.cfg.logprobs;
       // row for the root (distribution after the last committed token)
       AddSampleRow(&vp.sampling, r, off);
       for (int j = 0; j < nodes; ++j) {
@@ -1539,12 +1540,28 @@ class EngineImpl : public Engine {
       // the tree's, not the accepted path's.
       const int64_t draft_valid = (feature_fed_draft_ || width > 1) ? 0 : std::min<int64_t>(accepted, k - 1);
       if (spec_kv[i] - draft_valid > 0) kv_[1]->PopN(ds.internal_id, spec_kv[i] - draft_valid);
+      // reported probabilities are the target's (the draft's own would describe another model)
+      const GenerationConfig& gcfg = r.rs->request.cfg;
+      auto fill_top = [&](SampleResult* s, size_t row) {
+        s->top.clear();
+        if (!gcfg.logprobs || vo.num_top <= 0) return;
+        for (int t = 0; t < gcfg.top_logprobs && t < vo.num_top; ++t) {
+          const size_t at = row * static_cast<size_t>(vo.num_top) + static_cast<size_t>(t);
+          if (at < vo.top_tokens.size()) s->top.emplace_back(vo.top_tokens[at], vo.top_probs[at]);
+        }
+      };
       for (int j = beg; j < end; ++j) {
-        CommitToken(r, ds.draft_tokens[vo.accepted_nodes[j]]);
+        SampleResult s = ds.draft_tokens[vo.accepted_nodes[j]];
+        if (static_cast<size_t>(j) < vo.accepted_probs.size()) {
+          s.prob = vo.accepted_probs[j];
+          fill_top(&s, static_cast<size_t>(j));
+        }
+        CommitToken(r, s);
       }
       SampleResult fin;
       fin.token = vo.final_tokens[i];
       fin.prob = vo.final_probs.empty() ? 1.f : vo.final_probs[i];
+      if (!vo.accepted_probs.empty() || vo.num_top > 0) fill_top(&fin, vo.accepted_nodes.size() + i);
       CommitToken(r, fin);
       r.rs->metrics.decode_tokens += accepted + 1;
       metrics_.spec_decode.Update(k, accepted);

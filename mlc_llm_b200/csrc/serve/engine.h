@@ -103,6 +103,7 @@ struct VerifyParams {
   std::vector<float> uniform;              // per node
   std::vector<float> final_uniform;        // per sequence, for the bonus / resampled token
   SampleParams sampling;                   // per row = per (root + node) of every sequence
+  bool want_logprobs = false;              // some request reports log-probabilities: return the target's
 };
 
 struct VerifyOutput {
@@ -110,6 +111,13 @@ struct VerifyOutput {
   std::vector<int32_t> accepted_nodes;     // accepted node indices (chunk-local), path order
   std::vector<int32_t> final_tokens;       // per sequence: token sampled after the accepted path
   std::vector<float> final_probs;
+  // when log-probabilities are asked for: the target's probability of every accepted token (same order as
+  // accepted_nodes) and, with num_top > 0, its num_top best (token, probability) pairs for every accepted token
+  // followed by every final token
+  std::vector<float> accepted_probs;
+  std::vector<int32_t> top_tokens;
+  std::vector<float> top_probs;
+  int32_t num_top = 0;
 };
 
 class ModelBackend {

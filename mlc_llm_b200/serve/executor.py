@@ -1043,10 +1043,37 @@ class ModelExecutor:
             keep = [[int(qi[s_])] + [int(qi[s_]) + 1 + n for n in accepted_nodes[accepted_indptr[s_]:accepted_indptr[s_ + 1]]]
                     for s_ in range(nseq)]
             self._remember_features(plan, feats, keep)
-        return {"accepted_indptr": np.asarray(accepted_indptr, dtype=np.int32),
-                "accepted_nodes": np.asarray(accepted_nodes, dtype=np.int32),
-                "final_tokens": tokens.to(torch.int32).cpu().numpy(),
-                "final_probs": tprobs.float().cpu().numpy()}
+        out = {"accepted_indptr": np.asarray(accepted_indptr, dtype=np.int32),
+               "accepted_nodes": np.asarray(accepted_nodes, dtype=np.int32),
+               "final_tokens": tokens.to(torch.int32).cpu().numpy(),
+               "final_probs": tprobs.float().cpu().numpy()}
+        if bool(vp.get("want_logprobs", False)) or int(sp["num_top_logprobs"]) > 0:
+            # what is reported for a committed token is the TARGET's probability of it (on the distribution before
+            # top-p / top-k and before the residual updates of the verification), not the draft's: recompute the
+            # rows that produced the accepted tokens and the final ones from the processed logits
+            src_rows, toks = [], []
+            for s_ in range(nseq):
+                for n in accepted_nodes[accepted_indptr[s_]:accepted_indptr[s_ + 1]]:
+                    r = int(roots[s_]) + 1 + int(n)
+                    src_rows.append(int(parent_row[r]))
+                    toks.append(int(draft_tok[r]))
+            src_rows += [int(v) for v in last.tolist()]
+            toks += [int(v) for v in out["final_tokens"].tolist()]
+            sel = torch.as_tensor(src_rows, dtype=torch.long, device=d)
+            base = ops.softmax_temperature(logits.index_select(0, sel).contiguous(),
+                                           dev["s_temperature"].index_select(0, sel).contiguous())
+            tok_t = torch.as_tensor(toks, dtype=torch.long, device=d)
+            own = base.gather(1, tok_t.unsqueeze(1)).squeeze(1).float().cpu().numpy()
+            n_acc = len(accepted_nodes)
+            out["accepted_probs"] = own[:n_acc]
+            out["final_probs"] = own[n_acc:]
+            k_top = int(sp["num_top_logprobs"])
+            if k_top > 0:
+                tp, ti = torch.topk(base, k_top, dim=-1)
+                out["top_probs"] = tp.reshape(-1).float().cpu().numpy()
+                out["top_tokens"] = ti.reshape(-1).to(torch.int32).cpu().numpy()
+                out["num_top"] = k_top
+        return out
 
     def move_kv_tokens(self, model_id: int, moves: np.ndarray) -> None:
         self._enter()

@@ -416,3 +416,34 @@ def test_top_k_applies_to_the_verified_distribution(spec):
     _, got = eng.generate(prompts, {"temperature": 1.0, "top_k": 1, "seed": 9, "max_tokens": 10,
                                     "debug_config": {"ignore_eos": True}})
     assert [t[0] for t in got] == [t[0] for t in want]
+
+
+@pytest.mark.parametrize("spec", [dict(speculative_mode="small_draft", spec_draft_length=3,
+                                       additional_models=[MODEL]),                    # everything accepted
+                                  dict(speculative_mode="small_draft", spec_draft_length=3,
+                                       additional_models=["random://tiny-llama?quant=q0f32&seed=2"]),
+                                  dict(speculative_mode="small_draft", spec_draft_length=2, spec_tree_width=2,
+                                       additional_models=[MODEL])])
+def test_logprobs_under_speculative_decoding_are_the_targets(spec):
+    """The probability and the best alternatives reported for a committed token are the target model's, whether
+    the token was proposed by a draft and accepted, or sampled after the accepted path: equal to plain decoding."""
+    from mlc_llm_b200.serve.engine import MLCEngine
+
+    prompt = _prompts(1, seed=51)[0]
+    kw = dict(mode="server", max_num_sequence=4, max_total_sequence_length=1024, prefill_chunk_size=64,
+              prefix_cache_mode="disable")
+    req = dict(prompt=prompt, max_tokens=9, temperature=0.0, logprobs=True, top_logprobs=3,
+               debug_config={"ignore_eos": True})
+    plain = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw))
+    eng = MLCEngine(MODEL, "cpu", engine_config=EngineConfig(**kw, **spec))
+    try:
+        want = plain.completions.create(**req).choices[0].logprobs.content
+        got = eng.completions.create(**req).choices[0].logprobs.content
+    finally:
+        plain.terminate()
+        eng.terminate()
+    assert [c.token for c in got] == [c.token for c in want]
+    for g, w in zip(got, want):
+        assert abs(g.logprob - w.logprob) < 1e-3
+        assert [t.token for t in g.top_logprobs] == [t.token for t in w.top_logprobs]
+        assert all(abs(a.logprob - b.logprob) < 1e-3 for a, b in zip(g.top_logprobs, w.top_logprobs))
